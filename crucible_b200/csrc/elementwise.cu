@@ -1,0 +1,194 @@
+// Row-wise kernels: embedding gather, RMSNorm, SwiGLU activation, row gather,
+// and rotary encoding fused with the write of keys and values into the paged
+// cache.  All arithmetic is fp32; T is the storage type of activations
+// (float for the 32-bit engine, __nv_bfloat16 for the bfloat16 engine).
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// embedding: out[t, :] = float(table[ids[t], :])
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                  float* __restrict__ out, int width, int vocab) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    // ids are validated on the host; an id outside the table still must not
+    // read outside it
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    const T* row = table + (size_t)id * width;
+    float* dst = out + (size_t)t * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = cb_to_float(row[i]);
+}
+
+CB_EXPORT int cb_embed_rows(const void* table, int table_dtype, const int* ids, float* out,
+                            int n_rows, int width, int vocab, void* stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = width >= 256 ? 256 : 64;
+    if (table_dtype == CB_F32)
+        embed_rows_kernel<float><<<n_rows, threads, 0, (cudaStream_t)stream>>>(
+            (const float*)table, ids, out, width, vocab);
+    else
+        embed_rows_kernel<__nv_bfloat16><<<n_rows, threads, 0, (cudaStream_t)stream>>>(
+            (const __nv_bfloat16*)table, ids, out, width, vocab);
+    return cb_last_error();
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm: y = x * (1/sqrt(mean(x^2) + eps)) * gain     (x fp32, gain fp32)
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
+                               T* __restrict__ out, int width, float eps) {
+    __shared__ float scratch[32];
+    const float* row = x + (size_t)blockIdx.x * width;
+    T* dst = out + (size_t)blockIdx.x * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = row[i];
+        ss = fmaf(v, v, ss);
+    }
+    const float total = cb_block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(total / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        dst[i] = cb_from_float<T>(row[i] * r * gain[i]);
+}
+
+CB_EXPORT int cb_rmsnorm(const float* x, const float* gain, void* out, int out_dtype,
+                         int n_rows, int width, float eps, void* stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (out_dtype == CB_F32)
+        rmsnorm_kernel<float><<<n_rows, threads, 0, (cudaStream_t)stream>>>(
+            x, gain, (float*)out, width, eps);
+    else
+        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, (cudaStream_t)stream>>>(
+            x, gain, (__nv_bfloat16*)out, width, eps);
+    return cb_last_error();
+}
+
+// ---------------------------------------------------------------------------
+// SwiGLU activation on a fused [T, 2I] gate|up buffer: h = g / (1 + exp(-g)) * u
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out,
+                              int inter, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / inter;
+        const int c = (int)(i - t * inter);
+        const float g = cb_to_float(gate_up[t * 2 * inter + c]);
+        const float u = cb_to_float(gate_up[t * 2 * inter + inter + c]);
+        out[i] = cb_from_float<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+CB_EXPORT int cb_swiglu(const void* gate_up, void* out, int dtype, int n_rows, int inter,
+                        void* stream) {
+    const size_t total = (size_t)n_rows * inter;
+    if (total == 0) return 0;
+    const int threads = 256;
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == CB_F32)
+        swiglu_kernel<float><<<(int)blocks, threads, 0, (cudaStream_t)stream>>>(
+            (const float*)gate_up, (float*)out, inter, total);
+    else
+        swiglu_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, (cudaStream_t)stream>>>(
+            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+    return cb_last_error();
+}
+
+// ---------------------------------------------------------------------------
+// gather of fp32 rows: out[i, :] = x[rows[i], :]
+// ---------------------------------------------------------------------------
+__global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                   float* __restrict__ out, int width) {
+    const float* src = x + (size_t)rows[blockIdx.x] * width;
+    float* dst = out + (size_t)blockIdx.x * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+}
+
+CB_EXPORT int cb_gather_rows(const float* x, const int* rows, float* out, int n_rows, int width,
+                             void* stream) {
+    if (n_rows <= 0) return 0;
+    gather_rows_kernel<<<n_rows, 128, 0, (cudaStream_t)stream>>>(x, rows, out, width);
+    return cb_last_error();
+}
+
+// ---------------------------------------------------------------------------
+// Rotary encoding of q and k (half-split pairing) fused with the cache write.
+// qkv: [T, (Hq + 2 Hkv) * hd]; q is rotated in place; rotated k and plain v go
+// to the token's page: cache[page][slot][kv_head][feature].
+// One block per (token, head); heads 0..Hq-1 are q, then Hkv k heads, then
+// Hkv v heads.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_kv_append_kernel(T* __restrict__ qkv, const float* __restrict__ cos_t,
+                                      const float* __restrict__ sin_t, int rotary_dim,
+                                      const int* __restrict__ positions,
+                                      const int* __restrict__ row_request,
+                                      const int* __restrict__ block_table, int table_stride,
+                                      T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                      int n_heads, int n_kv_heads, int head_dim,
+                                      int page_tokens, int write_cache) {
+    const int t = blockIdx.x;
+    const int h = blockIdx.y;
+    const int row_width = (n_heads + 2 * n_kv_heads) * head_dim;
+    T* src = qkv + (size_t)t * row_width + (size_t)h * head_dim;
+    const int pos = positions[t];
+    const bool is_q = h < n_heads;
+    const bool is_k = !is_q && h < n_heads + n_kv_heads;
+    T* dst = nullptr;
+    if (!is_q) {
+        if (!write_cache) return;
+        const int r = row_request[t];
+        const int page = block_table[(size_t)r * table_stride + pos / page_tokens];
+        const int slot = pos % page_tokens;
+        const int kvh = is_k ? h - n_heads : h - n_heads - n_kv_heads;
+        T* base = is_k ? k_cache : v_cache;
+        dst = base + (((size_t)page * page_tokens + slot) * n_kv_heads + kvh) * head_dim;
+    }
+    if (is_q || is_k) {
+        const int half = rotary_dim / 2;
+        T* out = is_q ? src : dst;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float c = cos_t[(size_t)pos * half + i];
+            const float s = sin_t[(size_t)pos * half + i];
+            const float x1 = cb_to_float(src[i]);
+            const float x2 = cb_to_float(src[i + half]);
+            out[i] = cb_from_float<T>(x1 * c - x2 * s);
+            out[i + half] = cb_from_float<T>(x1 * s + x2 * c);
+        }
+        if (is_k)
+            for (int i = rotary_dim + threadIdx.x; i < head_dim; i += blockDim.x) out[i] = src[i];
+    } else {
+        for (int i = threadIdx.x; i < head_dim; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+CB_EXPORT int cb_rope_kv_append(void* qkv, int dtype, const float* cos_t, const float* sin_t,
+                                int rotary_dim, const int* positions, const int* row_request,
+                                const int* block_table, int table_stride, void* k_cache,
+                                void* v_cache, int n_rows, int n_heads, int n_kv_heads,
+                                int head_dim, int page_tokens, int write_cache, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return CB_ERR_UNSUPPORTED;
+    dim3 grid(n_rows, n_heads + 2 * n_kv_heads);
+    const int threads = head_dim >= 128 ? 64 : 32;
+    if (dtype == CB_F32)
+        rope_kv_append_kernel<float><<<grid, threads, 0, (cudaStream_t)stream>>>(
+            (float*)qkv, cos_t, sin_t, rotary_dim, positions, row_request, block_table,
+            table_stride, (float*)k_cache, (float*)v_cache, n_heads, n_kv_heads, head_dim,
+            page_tokens, write_cache);
+    else
+        rope_kv_append_kernel<__nv_bfloat16><<<grid, threads, 0, (cudaStream_t)stream>>>(
+            (__nv_bfloat16*)qkv, cos_t, sin_t, rotary_dim, positions, row_request, block_table,
+            table_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_heads, n_kv_heads,
+            head_dim, page_tokens, write_cache);
+    return cb_last_error();
+}
+
+CB_EXPORT const char* cb_error_string(int code) {
+    if (code == CB_ERR_UNSUPPORTED) return "sizes or options this kernel does not take";
+    return cudaGetErrorString((cudaError_t)code);
+}

@@ -1,0 +1,196 @@
+// Token selection on the device: greedy (argmax) and temperature sampling over
+// the top-k candidates, one block per logits row.
+//
+// Rules, from the reference's sampler (engine/src/sampling.rs):
+//  * greedy: the highest logit, ties to the lowest index, NaN never wins
+//    (:141-149; kernel engine/kernels/kernels.cu:1201-1212);
+//  * sampled: candidates are the k best in canonical order (logit descending,
+//    token id ascending; :161-163) found by radix selection on a 64-bit key
+//    (value key << 32 | ~id; :178-202); weights exp((v - max) / T) in fp32,
+//    non-finite -> 0; sum and walk in fp64; threshold = u * sum; the first
+//    candidate whose running sum reaches it wins (:243-283).  u is one uniform
+//    number per sampled token, drawn by the host from the request's own
+//    generator, so a request's sequence does not depend on its neighbours.
+//  * temperature <= 0 means greedy and uses no randomness (:290-298).
+#include "common.cuh"
+
+namespace {
+
+constexpr int SAMPLE_THREADS = 1024;
+constexpr int MAX_TOP_K = 1024;
+
+// Order-preserving map from a logit to an unsigned key: NaN lowest (0), -0.0 as
+// +0.0 (sampling.rs:178-186).
+__device__ __forceinline__ uint32_t value_key(float v) {
+    uint32_t u = __float_as_uint(v);
+    if (u == 0x80000000u) u = 0u;
+    if ((u & 0x7fffffffu) > 0x7f800000u) return 0u;
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ unsigned long long sort_key(float v, int id) {
+    return ((unsigned long long)value_key(v) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)id);
+}
+
+__device__ void block_argmax(const float* row, int vocab, int* out_id, float* s_val, int* s_idx) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float x = row[i];
+        if (x > bv || (x == bv && i < bi)) { bv = x; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { s_val[warp] = bv; s_idx[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        for (int w = 1; w < nw; ++w)
+            if (s_val[w] > bv || (s_val[w] == bv && s_idx[w] < bi)) { bv = s_val[w]; bi = s_idx[w]; }
+        *out_id = bi == 0x7fffffff ? 0 : bi;   // every logit NaN: token 0
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_rows_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
+                   const int* __restrict__ top_k, const float* __restrict__ uniform,
+                   int* __restrict__ out_ids) {
+    __shared__ float s_val[32];
+    __shared__ int s_idx[32];
+    __shared__ unsigned int hist[256];
+    __shared__ unsigned long long cand[MAX_TOP_K];
+    __shared__ unsigned long long prefix_sh;
+    __shared__ int remaining_sh;
+    __shared__ unsigned int n_cand;
+
+    const int row_i = blockIdx.x;
+    const float* row = logits + (size_t)row_i * vocab;
+    const float temp = temperature ? temperature[row_i] : 0.f;
+    if (!(temp > 0.f)) {
+        block_argmax(row, vocab, out_ids + row_i, s_val, s_idx);
+        return;
+    }
+    int k = top_k[row_i];
+    k = k < 1 ? 1 : (k > vocab ? vocab : k);
+    if (k > MAX_TOP_K) k = MAX_TOP_K;          // the launcher refuses larger k
+
+    // Radix selection of the k-th largest 64-bit key, 8 bits per pass from the top.
+    if (threadIdx.x == 0) { prefix_sh = 0ull; remaining_sh = k; }
+    __syncthreads();
+    for (int pass = 0; pass < 8; ++pass) {
+        const int shift = 56 - 8 * pass;
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0u;
+        __syncthreads();
+        const unsigned long long prefix = prefix_sh;
+        const unsigned long long mask = pass == 0 ? 0ull : (~0ull << (shift + 8));
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const unsigned long long key = sort_key(row[i], i);
+            if ((key & mask) == prefix) atomicAdd(&hist[(unsigned)(key >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int rem = remaining_sh;
+            int d = 255;
+            for (; d > 0; --d) {
+                if ((int)hist[d] >= rem) break;
+                rem -= (int)hist[d];
+            }
+            prefix_sh = prefix | ((unsigned long long)d << shift);
+            remaining_sh = rem;
+        }
+        __syncthreads();
+    }
+    const unsigned long long kth = prefix_sh;   // exactly k keys are >= kth (keys are unique)
+
+    if (threadIdx.x == 0) n_cand = 0u;
+    for (int i = threadIdx.x; i < MAX_TOP_K; i += blockDim.x) cand[i] = 0ull;
+    __syncthreads();
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const unsigned long long key = sort_key(row[i], i);
+        if (key >= kth) {
+            const unsigned int slot = atomicAdd(&n_cand, 1u);
+            if (slot < MAX_TOP_K) cand[slot] = key;
+        }
+    }
+    __syncthreads();
+    // Bitonic sort, descending, over the smallest power of two >= k.
+    int n = 1;
+    while (n < k) n <<= 1;
+    for (int size = 2; size <= n; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int i = threadIdx.x; i < n; i += blockDim.x) {
+                const int j = i ^ stride;
+                if (j > i) {
+                    const bool desc = (i & size) == 0;
+                    const unsigned long long a = cand[i], b = cand[j];
+                    if (desc ? a < b : a > b) { cand[i] = b; cand[j] = a; }
+                }
+            }
+            __syncthreads();
+        }
+    }
+    if (threadIdx.x == 0) {
+        const int best = (int)(0xffffffffu - (uint32_t)(cand[0] & 0xffffffffull));
+        float vmax = -INFINITY;
+        for (int i = 0; i < k; ++i) {
+            const int id = (int)(0xffffffffu - (uint32_t)(cand[i] & 0xffffffffull));
+            const float v = row[id];
+            if (v > vmax) vmax = v;
+        }
+        double sum = 0.0;
+        for (int i = 0; i < k; ++i) {
+            const int id = (int)(0xffffffffu - (uint32_t)(cand[i] & 0xffffffffull));
+            const float w = expf((row[id] - vmax) / temp);
+            sum += isfinite(w) ? (double)w : 0.0;
+        }
+        int chosen = best;
+        if (sum > 0.0) {
+            const double threshold = (double)uniform[row_i] * sum;
+            double acc = 0.0;
+            chosen = (int)(0xffffffffu - (uint32_t)(cand[k - 1] & 0xffffffffull));
+            for (int i = 0; i < k; ++i) {
+                const int id = (int)(0xffffffffu - (uint32_t)(cand[i] & 0xffffffffull));
+                const float w = expf((row[id] - vmax) / temp);
+                acc += isfinite(w) ? (double)w : 0.0;
+                if (acc >= threshold) { chosen = id; break; }
+            }
+        }
+        out_ids[row_i] = chosen;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+argmax_rows_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out_ids) {
+    __shared__ float s_val[32];
+    __shared__ int s_idx[32];
+    block_argmax(logits + (size_t)blockIdx.x * vocab, vocab, out_ids + blockIdx.x, s_val, s_idx);
+}
+
+}  // namespace
+
+CB_EXPORT int cb_argmax_rows(const float* logits, int n_rows, int vocab, int* out_ids,
+                             void* stream) {
+    if (n_rows <= 0) return 0;
+    argmax_rows_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>(logits, vocab, out_ids);
+    return cb_last_error();
+}
+
+// temperature[row] <= 0: greedy.  max_top_k is the largest k among the rows;
+// the launcher refuses k above the kernel's candidate capacity.
+CB_EXPORT int cb_sample_rows(const float* logits, int n_rows, int vocab, const float* temperature,
+                             const int* top_k, const float* uniform, int max_top_k, int* out_ids,
+                             void* stream) {
+    if (n_rows <= 0) return 0;
+    if (max_top_k > MAX_TOP_K) return CB_ERR_UNSUPPORTED;
+    sample_rows_kernel<<<n_rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(
+        logits, vocab, temperature, top_k, uniform, out_ids);
+    return cb_last_error();
+}
+
+CB_EXPORT int cb_sample_max_top_k() { return MAX_TOP_K; }

@@ -1,0 +1,155 @@
+"""What one step looks like to the model: the packed batch and its storage.
+
+`StepLayout` fixes where each piece of a step's integer metadata lies inside
+one int32 buffer, as a function of the step's row, request and wanted-row
+counts only; the host fills a pinned copy and uploads it with a single copy.
+`StepContext` is what parts see: device views of that metadata, the cache
+storage of each group, per-request state, and named scratch buffers.
+
+The packed-batch idea follows the reference's packed prefill
+(`engine/src/gpu_model.rs:256-272`, `:2872-2896`: owners, positions, segments,
+final rows) extended so that a decoded token is simply a portion of length one.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+
+@dataclass(frozen=True)
+class StepLayout:
+    n_tokens: int
+    n_requests: int
+    n_logit_rows: int
+    table_strides: Tuple[int, ...]
+
+    def offsets(self) -> Dict[str, Tuple[int, int]]:
+        t, r, f = self.n_tokens, self.n_requests, self.n_logit_rows
+        out, at = {}, 0
+        for name, n in (("token_ids", t), ("positions", t), ("row_request", t),
+                        ("logit_rows", f), ("req_row_start", r + 1), ("req_context_len", r),
+                        ("req_first_pos", r), ("req_state_slot", r)):
+            out[name] = (at, n)
+            at += (n + 3) // 4 * 4            # keep every piece 16-byte aligned
+        for g, stride in enumerate(self.table_strides):
+            out[f"table{g}"] = (at, r * stride)
+            at += (r * stride + 3) // 4 * 4
+        out["_total"] = (0, at)
+        return out
+
+
+class CacheStorage:
+    """Device pages of one cache group: [slot, K|V, page, token, kv_head, feature]."""
+
+    def __init__(self, n_slots: int, n_pages: int, page_tokens: int, kv_heads: int,
+                 head_dim: int, dtype: torch.dtype, device):
+        self.page_tokens = page_tokens
+        self.n_pages = n_pages
+        self.kv_heads = kv_heads
+        self.head_dim = head_dim
+        self.kv = torch.zeros((n_slots, 2, n_pages, page_tokens, kv_heads, head_dim),
+                              dtype=dtype, device=device)
+
+    def keys(self, slot: int) -> torch.Tensor:
+        return self.kv[slot, 0]
+
+    def values(self, slot: int) -> torch.Tensor:
+        return self.kv[slot, 1]
+
+
+class Scratch:
+    """Named device buffers that persist between steps (stable addresses while
+    their size suffices), so a step allocates nothing once warmed up."""
+
+    def __init__(self, device):
+        self.device = device
+        self._flat: Dict[str, torch.Tensor] = {}
+        self.generation = 0          # bumped whenever a buffer moves
+
+    def get(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        numel = 1
+        for s in shape:
+            numel *= int(s)
+        key = f"{name}:{dtype}"
+        flat = self._flat.get(key)
+        if flat is None or flat.numel() < numel:
+            flat = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+            self._flat[key] = flat
+            self.generation += 1
+        return flat[:numel].view(*shape)
+
+    def reserve(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> None:
+        self.get(name, shape, dtype)
+
+
+class StepContext:
+    """Everything a part may know about the step being run."""
+
+    def __init__(self, *, layout: StepLayout, meta: torch.Tensor, caches: List[CacheStorage],
+                 state: Optional[torch.Tensor], scratch: Scratch, dtype: torch.dtype,
+                 host: "HostStep"):
+        self.layout = layout
+        self.dtype = dtype
+        self.n_tokens = layout.n_tokens
+        self.n_requests = layout.n_requests
+        self.n_logit_rows = layout.n_logit_rows
+        self._caches = caches
+        self._state = state
+        self._scratch = scratch
+        self.host = host
+        off = layout.offsets()
+
+        def view(name):
+            a, n = off[name]
+            return meta[a:a + n]
+
+        self.token_ids = view("token_ids")
+        self.positions = view("positions")
+        self.row_request = view("row_request")
+        self.logit_rows = view("logit_rows")
+        self.req_row_start = view("req_row_start")
+        self.req_context_len = view("req_context_len")
+        self.req_first_pos = view("req_first_pos")
+        self.req_state_slot = view("req_state_slot")
+        self._tables = [view(f"table{g}").view(layout.n_requests, s)
+                        for g, s in enumerate(layout.table_strides)]
+
+    def cache(self, group: int) -> CacheStorage:
+        return self._caches[group]
+
+    def block_table(self, group: int) -> torch.Tensor:
+        return self._tables[group]
+
+    def state(self, binding) -> Optional[torch.Tensor]:
+        """The mixer's bytes inside every request's state slot: uint8
+        [n_slots, state_bytes]; index it with `req_state_slot`."""
+        if self._state is None or binding.state_bytes == 0:
+            return None
+        return self._state[:, binding.state_offset:binding.state_offset + binding.state_bytes]
+
+    def scratch(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        return self._scratch.get(name, shape, dtype)
+
+
+@dataclass
+class HostStep:
+    """Host-side copy of the step's shape, for parts that pick a launch shape."""
+    request_ids: list
+    new_tokens: List[int]            # per request: tokens run in this step
+    first_pos: List[int]             # per request: position of its first new token
+    context_len: List[int]           # per request: tokens held after this step
+    state_slots: List[int]
+
+    @property
+    def all_single_token(self) -> bool:
+        return all(n == 1 for n in self.new_tokens)
+
+    @property
+    def max_context_len(self) -> int:
+        return max(self.context_len) if self.context_len else 0
+
+    @property
+    def max_new_tokens(self) -> int:
+        return max(self.new_tokens) if self.new_tokens else 0

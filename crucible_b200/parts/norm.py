@@ -1,0 +1,36 @@
+"""RMSNorm: y_i = x_i * rsqrt(mean(x^2) + eps) * gain_i, scale first, then gain.
+
+Formula and order: `model.py:113-118` (whole norm in fp32, gain multiplied in
+fp32), `engine/kernels/kernels.cu:143-157`.  The input is the fp32 residual
+stream; the statistics and both multiplications are 32-bit in either engine
+dtype, and only the result is rounded to the engine dtype.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..config.model_config import NormSpec
+from .base import NORMS, Norm, TensorDecl
+
+
+class RMSNorm(Norm):
+    def __init__(self, spec: NormSpec):
+        self.spec = spec
+        self.gain = None
+        self.dtype = None
+
+    def tensors(self):
+        return [TensorDecl("gain", (self.spec.width,), role="vector")]
+
+    def bind(self, tensors, dtype, device):
+        self.gain = tensors["gain"]
+        self.dtype = dtype
+
+    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
+        out = ctx.scratch("norm.out", (x.shape[0], self.spec.width), self.dtype)
+        ops.rmsnorm(x, self.gain, self.spec.eps, out)
+        return out
+
+
+NORMS.register("rmsnorm", RMSNorm)

@@ -1,0 +1,3 @@
+from .safetensors_io import SafetensorsError, SafetensorsFile, write_safetensors
+from .loader import WeightError, load_weights
+from .random_init import random_tensors, write_random_model

@@ -1,0 +1,171 @@
+"""Trace replay on the GPU against the plain implementation, in float32 and in
+bfloat16: each request alone and whole; most of it in one step and the last 32
+tokens one by one; in portions of changing size down to two tokens; and mixed,
+up to four live requests, portions of some beside decoded tokens of others,
+with so few pages that they are used again."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import helpers
+from helpers import TINY, TOLERANCE, Trace
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"tiny-a": [7, 33, 64, 150], "tiny-b": [1, 17, 50, 95, 130]}
+
+
+def _vocab(name):
+    return TINY[name]["config"]["vocab_size"]
+
+
+def _requests(name):
+    return {f"r{i}": helpers.random_tokens(_vocab(name), n, 100 + i)
+            for i, n in enumerate(LENGTHS[name])}
+
+
+def _check(name, dtype, model_dir, trace, out_dir, requests, max_tokens):
+    helpers.replay_in_process(model_dir, dtype, trace, out_dir, max_tokens,
+                              TINY[name]["page_tokens"])
+    got = helpers.collect(trace, out_dir, _vocab(name))
+    assert got, "the trace asked for nothing"
+    worst = 0.0
+    for rid, tokens in requests.items():
+        ref = helpers.plain_logits(model_dir, tokens)
+        keys = sorted(k for k in got if k[0] == rid)
+        assert keys, f"no logits for {rid}"
+        mine = np.stack([got[k] for k in keys])
+        theirs = np.stack([ref[k[1]] for k in keys])
+        err = helpers.relative_error(mine, theirs)
+        if err > TOLERANCE[dtype]:
+            # name the first wrong place: what is special about it?
+            for k in keys:
+                e = helpers.relative_error(got[k], ref[k[1]])
+                if e > TOLERANCE[dtype]:
+                    pytest.fail(f"{name} {dtype}: request {rid} first differs at position "
+                                f"{k[1]} (relative error {e:.3g}, allowed {TOLERANCE[dtype]})")
+        worst = max(worst, err)
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny-a", "tiny-b"])
+def test_each_request_alone_and_whole(tmp_path, name, dtype):
+    model_dir = helpers.make_folder(tmp_path, name)
+    requests = _requests(name)
+    trace = Trace()
+    for rid, tokens in requests.items():
+        trace.step([(rid, tokens, list(range(len(tokens))))], end=[rid])
+    _check(name, dtype, model_dir, trace, str(tmp_path / "out"), requests, 192)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny-a", "tiny-b"])
+def test_prompt_then_last_32_one_by_one(tmp_path, name, dtype):
+    model_dir = helpers.make_folder(tmp_path, name)
+    requests = {k: v for k, v in _requests(name).items() if len(v) > 40}
+    trace = Trace()
+    for rid, tokens in requests.items():
+        head = len(tokens) - 32
+        trace.step([(rid, tokens[:head], [head - 1])])
+        for i in range(head, len(tokens)):
+            trace.step([(rid, [tokens[i]], [0])], end=[rid] if i == len(tokens) - 1 else [])
+    _check(name, dtype, model_dir, trace, str(tmp_path / "out"), requests, 192)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny-a", "tiny-b"])
+def test_portions_of_changing_size(tmp_path, name, dtype):
+    model_dir = helpers.make_folder(tmp_path, name)
+    requests = {k: v for k, v in _requests(name).items() if len(v) >= 33}
+    sizes = [24, 7, 2, 13, 2, 31, 5, 17, 3, 40]
+    trace = Trace()
+    for rid, tokens in requests.items():
+        at, i = 0, 0
+        while at < len(tokens):
+            n = min(sizes[i % len(sizes)], len(tokens) - at)
+            if len(tokens) - at - n == 1:      # never leave a single token: portions go down to two
+                n += 1
+            last = at + n == len(tokens)
+            trace.step([(rid, tokens[at:at + n], list(range(n)))], end=[rid] if last else [])
+            at += n
+            i += 1
+    _check(name, dtype, model_dir, trace, str(tmp_path / "out"), requests, 192)
+
+
+def _mixed_trace(requests, chunk, seed):
+    """Up to four live requests; portions of prompts beside single tokens of
+    requests that have reached their last 12 tokens ("decoding"); a request
+    is sometimes left out of a step; finished requests free their pages for
+    the ones still waiting."""
+    import random
+    rng = random.Random(seed)
+    waiting = list(requests)
+    live = {}
+    trace = Trace()
+    while waiting or live:
+        while waiting and len(live) < 4:
+            live[waiting.pop(0)] = 0
+        entries, ended = [], []
+        for rid in list(live):
+            tokens = requests[rid]
+            at = live[rid]
+            if len(live) > 1 and rng.random() < 0.2:
+                continue                                   # sits this step out
+            decode_from = max(1, len(tokens) - 12)
+            if at >= decode_from:
+                n = 1
+            else:
+                n = min(rng.choice([chunk, chunk // 2, 5, 2]), decode_from - at)
+                if decode_from - at - n == 1 and n > 1:
+                    n += 1 if at + n + 1 <= decode_from else 0
+            want = list(range(n)) if n <= 2 or rng.random() < 0.5 else [n - 1]
+            entries.append((rid, tokens[at:at + n], want))
+            live[rid] = at + n
+            if live[rid] == len(tokens):
+                ended.append(rid)
+        if entries:
+            trace.step(entries, end=ended)
+        for rid in ended:
+            del live[rid]
+    return trace
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny-a", "tiny-b"])
+def test_mixed_requests_with_pages_used_again(tmp_path, name, dtype):
+    model_dir = helpers.make_folder(tmp_path, name)
+    base = _requests(name)
+    # twice as many requests as fit at once, so that pages are used again
+    requests = dict(base)
+    for i, (rid, tokens) in enumerate(list(base.items())):
+        requests[f"s{i}"] = helpers.random_tokens(_vocab(name), max(2, len(tokens) - 3), 500 + i)
+    trace = _mixed_trace(requests, 24, seed=7)
+    # four live requests, each rounded up to a multiple of 64
+    longest = sorted((-(-len(t) // 64) * 64 for t in requests.values()), reverse=True)
+    max_tokens = sum(longest[:4])
+    _check(name, dtype, model_dir, trace, str(tmp_path / "out"), requests, max_tokens)
+
+
+def test_trace_run_program(tmp_path):
+    """The program itself, as a user runs it: standard input, files, done lines."""
+    name = "tiny-a"
+    model_dir = helpers.make_folder(tmp_path, name)
+    tokens = helpers.random_tokens(_vocab(name), 40, 9)
+    trace = Trace()
+    trace.step([("a", tokens[:30], [29])])
+    trace.step([("a", tokens[30:], [0, 9])], end=["a"])
+    out = str(tmp_path / "out")
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), os.pardir)
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model",
+                           model_dir, "--dtype", "float32", "--out", out, "--max-tokens", "64"],
+                          input=trace.text(), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr
+    assert proc.stdout.split() == ["done", "0", "done", "1"]
+    got = helpers.collect(trace, out, _vocab(name))
+    ref = helpers.plain_logits(model_dir, tokens)
+    for (rid, pos), row in got.items():
+        assert helpers.relative_error(row, ref[pos]) <= TOLERANCE["float32"]
