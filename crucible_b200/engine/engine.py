@@ -56,6 +56,7 @@ class EngineOptions:
     n_pages: Optional[int] = None         # per cache group; default: max_requests full contexts
     max_requests: int = 16                # the reference's --max-batch default (main.rs:143)
     device: str = "cuda:0"
+    graph: bool = True                    # replay decode-only steps as CUDA graphs
 
 
 class Engine:
@@ -94,6 +95,7 @@ class Engine:
         self.scratch = Scratch(self.device)
         self._meta_dev = None
         self._meta_host = None
+        self._sampler = None
 
     def _meta_buffers(self, n: int):
         if self._meta_dev is None or self._meta_dev.numel() < n:
@@ -102,6 +104,27 @@ class Engine:
             self._meta_host = torch.empty(cap, dtype=torch.int32, pin_memory=True)
             self.scratch.generation += 1
         return self._meta_host, self._meta_dev
+
+    # -- what the scheduler needs of an executor ----------------------------------
+
+    @property
+    def vocab_size(self) -> int:
+        return self.config.vocab_size
+
+    @property
+    def max_context(self) -> int:
+        return self.config.max_context
+
+    @property
+    def max_device_top_k(self) -> int:
+        from .. import ops
+        return ops.max_device_top_k()
+
+    def sample(self, logits: torch.Tensor, rows) -> List[int]:
+        if self._sampler is None:
+            from ..sampling.sampler import Sampler
+            self._sampler = Sampler(self.device, self.config.vocab_size)
+        return self._sampler.sample(logits, rows)
 
     # -- requests ---------------------------------------------------------------
 
