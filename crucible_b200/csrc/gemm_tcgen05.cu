@@ -1,0 +1,307 @@
+// C[M,N] = A[M,K] . W[N,K]^T in bfloat16 on the 5th-generation tensor cores:
+// TMA brings 128 x 64 tiles of A and BN x 64 tiles of W into shared memory
+// (128-byte swizzle), one thread issues tcgen05.mma (M = 128, N = BN, K = 16)
+// into an fp32 accumulator in tensor memory, and four warps read it back with
+// tcgen05.ld for the epilogue.  Roles: warp 0 loads, warp 1 owns tensor memory
+// and issues the MMAs, warps 2-5 do the epilogue.  One output tile per block.
+//
+// Epilogues (fused where it saves memory traffic):
+//   STORE_BF16  C bf16 = acc
+//   STORE_F32   C fp32 = acc                      (logits)
+//   ACCUM_F32   C fp32 += acc                     (residual add in 32 bits)
+//   SWIGLU_BF16 W = [Wg; Wu] ([2I, K]); the tile holds BN/2 gate rows and the
+//               BN/2 matching up rows; C[M, I] bf16 = silu(g) * u in fp32
+//
+// Sizes: any M, N; K a multiple of 8 (a TMA row stride must be a multiple of
+// 16 bytes) with lda, ldw multiples of 8 and 16-byte aligned bases; tails in
+// M, N and K are zero-filled by TMA and masked at the store.  Anything else is
+// refused by the launcher (the caller then runs the CUDA-core product).
+//
+// Reference counterpart: `gemm_f32_wmma` (engine/kernels/kernels.cu:2420-2520),
+// fp16 wmma tiles 16x64 / 64x64.
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                 // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+
+enum Epilogue { STORE_BF16 = 0, STORE_F32 = 1, ACCUM_F32 = 2, SWIGLU_BF16 = 3 };
+
+template <int BN, int STAGES>
+struct SharedStorage {
+    alignas(1024) uint8_t a[STAGES][BM * BK * 2];
+    alignas(1024) uint8_t b[STAGES][BN * BK * 2];
+    alignas(8) uint64_t full_bar[STAGES];
+    uint64_t empty_bar[STAGES];
+    uint64_t tmem_full_bar;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(192, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                    const __grid_constant__ CUtensorMap map_w, void* __restrict__ c_ptr, int M,
+                    int N, int K, int ldc, int inter, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    using Storage = SharedStorage<BN, STAGES>;
+    Storage& s = *reinterpret_cast<Storage*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM;
+    const int n_tile = blockIdx.x;
+    const int k_blocks = (K + BK - 1) / BK;
+    volatile int* abort_flag = &s.abort_flag;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr uint32_t STAGE_BYTES = (BM + BN) * BK * 2;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) {
+            tc::mbar_init(&s.full_bar[i], 1);
+            tc::mbar_init(&s.empty_bar[i], 1);
+        }
+        tc::mbar_init(&s.tmem_full_bar, 1);
+        s.abort_flag = 0;
+        tc::fence_barrier_init();
+        tc::prefetch_tensormap(&map_a);
+        tc::prefetch_tensormap(&map_w);
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(&s.tmem_base, TMEM_COLS);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem_acc = s.tmem_base;
+
+    if (warp == 0) {
+        // ---- producer: one thread feeds the ring of stages -------------------
+        if (lane == 0) {
+            int armed = 0;
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int st = kb % STAGES;
+                const uint32_t round = kb / STAGES;
+                if (round > 0 && !tc::mbar_wait(&s.empty_bar[st], (round - 1) & 1, abort_flag)) {
+                    tc::give_up(abort_flag, status, tc::ST_PRODUCER_TIMEOUT);
+                    break;
+                }
+                tc::mbar_expect_tx(&s.full_bar[st], STAGE_BYTES);
+                tc::tma_load_2d(s.a[st], &map_a, &s.full_bar[st], kb * BK, m0);
+                if (EPI == SWIGLU_BF16) {
+                    const int half = BN / 2;
+                    tc::tma_load_2d(s.b[st], &map_w, &s.full_bar[st], kb * BK, n_tile * half);
+                    tc::tma_load_2d(s.b[st] + half * BK * 2, &map_w, &s.full_bar[st], kb * BK,
+                                    inter + n_tile * half);
+                } else {
+                    tc::tma_load_2d(s.b[st], &map_w, &s.full_bar[st], kb * BK, n_tile * BN);
+                }
+                armed = kb + 1;
+            }
+            if (*abort_flag) {
+                // let our own copies land before the block's shared memory goes away
+                const int first = armed > STAGES ? armed - STAGES : 0;
+                for (int kb = first; kb < armed; ++kb) {
+                    const int st = kb % STAGES;
+                    for (uint32_t i = 0; i < tc::WAIT_LIMIT; ++i)
+                        if (tc::mbar_try_wait(&s.full_bar[st], (kb / STAGES) & 1)) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer --------------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc::instr_desc_bf16(BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                const int st = kb % STAGES;
+                if (!tc::mbar_wait(&s.full_bar[st], (kb / STAGES) & 1, abort_flag)) {
+                    tc::give_up(abort_flag, status, tc::ST_MMA_TIMEOUT);
+                    ok = false;
+                    break;
+                }
+                tc::tc_fence_after_sync();
+                const uint64_t a_desc = tc::smem_desc_sw128(tc::smem_u32(s.a[st]));
+                const uint64_t b_desc = tc::smem_desc_sw128(tc::smem_u32(s.b[st]));
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // advancing 16 elements along K = 32 bytes = 2 descriptor units
+                    tc::umma_bf16(tmem_acc, a_desc + 2 * k, b_desc + 2 * k, idesc,
+                                  (kb > 0 || k > 0) ? 1u : 0u);
+                }
+                tc::umma_commit(&s.empty_bar[st]);      // stage free once these MMAs are done
+            }
+            if (ok) tc::umma_commit(&s.tmem_full_bar);   // accumulator complete
+        }
+    } else {
+        // ---- epilogue: warps 2..5, lane quarter = warp % 4 -----------------------
+        const int quarter = warp & 3;
+        const int row = m0 + quarter * 32 + lane;
+        bool ok = tc::mbar_wait(&s.tmem_full_bar, 0, abort_flag);
+        if (!ok && !*abort_flag) tc::give_up(abort_flag, status, tc::ST_EPILOGUE_TIMEOUT);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tc::tc_fence_after_sync();
+            const uint32_t lane_addr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
+            if (EPI == SWIGLU_BF16) {
+                constexpr int HALF = BN / 2;
+                __nv_bfloat16* C = (__nv_bfloat16*)c_ptr;
+#pragma unroll 1
+                for (int c0 = 0; c0 < HALF; c0 += 16) {
+                    uint32_t g[16], u[16];
+                    tc::tmem_ld_32x16(lane_addr + c0, g);
+                    tc::tmem_ld_32x16(lane_addr + HALF + c0, u);
+                    tc::tmem_ld_wait();
+                    const int col0 = n_tile * HALF + c0;
+                    if (row < M) {
+                        __nv_bfloat16* dst = C + (size_t)row * ldc + col0;
+                        if (col0 + 16 <= inter && ((ldc & 7) == 0)) {
+                            uint32_t packed[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const float g0 = __uint_as_float(g[2 * j]);
+                                const float g1 = __uint_as_float(g[2 * j + 1]);
+                                const float h0 = g0 / (1.0f + __expf(-g0)) * __uint_as_float(u[2 * j]);
+                                const float h1 = g1 / (1.0f + __expf(-g1)) * __uint_as_float(u[2 * j + 1]);
+                                __nv_bfloat162 v = __floats2bfloat162_rn(h0, h1);
+                                packed[j] = *reinterpret_cast<uint32_t*>(&v);
+                            }
+                            uint4* d4 = reinterpret_cast<uint4*>(dst);
+                            d4[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                            d4[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                if (col0 + j < inter) {
+                                    const float gv = __uint_as_float(g[j]);
+                                    dst[j] = __float2bfloat16_rn(gv / (1.0f + __expf(-gv)) *
+                                                                 __uint_as_float(u[j]));
+                                }
+                            }
+                        }
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t r[32];
+                    tc::tmem_ld_32x32(lane_addr + c0, r);
+                    tc::tmem_ld_wait();
+                    const int col0 = n_tile * BN + c0;
+                    if (row >= M || col0 >= N) continue;
+                    const bool full = col0 + 32 <= N;
+                    if (EPI == STORE_BF16) {
+                        __nv_bfloat16* dst = (__nv_bfloat16*)c_ptr + (size_t)row * ldc + col0;
+                        if (full && (ldc & 7) == 0) {
+                            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                uint32_t p[4];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    __nv_bfloat162 v = __floats2bfloat162_rn(
+                                        __uint_as_float(r[q * 8 + 2 * j]),
+                                        __uint_as_float(r[q * 8 + 2 * j + 1]));
+                                    p[j] = *reinterpret_cast<uint32_t*>(&v);
+                                }
+                                d4[q] = make_uint4(p[0], p[1], p[2], p[3]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                        }
+                    } else {
+                        float* dst = (float*)c_ptr + (size_t)row * ldc + col0;
+                        if (full && (ldc & 3) == 0) {
+                            float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                       __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                                if (EPI == ACCUM_F32) {
+                                    const float4 o = d4[q];
+                                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                                }
+                                d4[q] = v;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (col0 + j < N) {
+                                    const float v = __uint_as_float(r[j]);
+                                    dst[j] = EPI == ACCUM_F32 ? dst[j] + v : v;
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::tc_fence_after_sync();
+        tc::tmem_dealloc(tmem_acc, TMEM_COLS);
+    }
+}
+
+template <int BN, int STAGES, int EPI>
+int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, int K, int ldc,
+           int inter, int* status, cudaStream_t stream) {
+    using Storage = SharedStorage<BN, STAGES>;
+    const int smem = (int)sizeof(Storage) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, EPI>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int n_cols = EPI == SWIGLU_BF16 ? 2 * inter : N;
+    dim3 grid((n_cols + BN - 1) / BN, (M + BM - 1) / BM);
+    gemm_tcgen05_kernel<BN, STAGES, EPI><<<grid, 192, smem, stream>>>(ma, mw, C, M, N, K, ldc,
+                                                                      inter, status);
+    return cb_last_error();
+}
+
+template <int BN, int STAGES>
+int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N,
+               int K, int ldc, int inter, int* status, cudaStream_t stream) {
+    switch (epi) {
+        case STORE_BF16: return launch<BN, STAGES, STORE_BF16>(ma, mw, C, M, N, K, ldc, inter, status, stream);
+        case STORE_F32: return launch<BN, STAGES, STORE_F32>(ma, mw, C, M, N, K, ldc, inter, status, stream);
+        case ACCUM_F32: return launch<BN, STAGES, ACCUM_F32>(ma, mw, C, M, N, K, ldc, inter, status, stream);
+        case SWIGLU_BF16: return launch<BN, STAGES, SWIGLU_BF16>(ma, mw, C, M, N, K, ldc, inter, status, stream);
+    }
+    return CB_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+
+// W is [N, K] (for SWIGLU_BF16: [2 * inter, K], N = inter and C is [M, inter]).
+// bn: tile width, 64, 128 or 256.  status: device int, stays 0 unless a wait ran out.
+CB_EXPORT int cb_gemm_tcgen05(const void* A, const void* W, void* C, int M, int N, int K, int lda,
+                              int ldw, int ldc, int epi, int bn, int* status, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15))
+        return CB_ERR_UNSUPPORTED;
+    const int w_rows = epi == SWIGLU_BF16 ? 2 * N : N;
+    const int box_rows = epi == SWIGLU_BF16 ? bn / 2 : bn;
+    CUtensorMap ma, mw;
+    if (!tc::make_map_2d(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM)) return CB_ERR_UNSUPPORTED;
+    if (!tc::make_map_2d(&mw, W, (uint64_t)w_rows, (uint64_t)K, (uint64_t)ldw, box_rows))
+        return CB_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int inter = epi == SWIGLU_BF16 ? N : 0;
+    switch (bn) {
+        case 64: return launch_epi<64, 6>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
+        case 128: return launch_epi<128, 5>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
+        case 256: return launch_epi<256, 4>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
+    }
+    return CB_ERR_UNSUPPORTED;
+}

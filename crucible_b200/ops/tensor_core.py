@@ -1,16 +1,110 @@
 """The bfloat16 tensor-core kernels.  Each function returns True if it ran, or
 False if the sizes are outside what the kernel takes, in which case the caller
-runs the plain CUDA-core kernel instead (a stated rule, not a silent one: the
-conditions are listed beside each function)."""
+runs the plain CUDA-core kernel instead.  The rule is stated here and depends
+on the shapes and strides alone, never on the batch:
+
+matrix products (tcgen05 + TMA): K, the row strides of both operands and the
+row stride of a bfloat16 output must be multiples of 8 elements (TMA needs
+16-byte row pitches), and the operand bases 16-byte aligned.
+"""
 from __future__ import annotations
 
+import ctypes
 
-def linear(a, w, out, *, accumulate=False) -> bool:
-    return False
+import torch
+
+from . import build
+
+build.register_module("gemm_tcgen05", ["common.cuh", "tc_common.cuh"])
+
+_c_int, _c_void_p = ctypes.c_int, ctypes.c_void_p
+STORE_BF16, STORE_F32, ACCUM_F32, SWIGLU_BF16 = 0, 1, 2, 3
+_UNSUPPORTED = 100001
+
+_status = {}
 
 
-def linear_swiglu(h, gate_up, out) -> bool:
-    return False
+def status_word(device) -> torch.Tensor:
+    """A device int the kernels write if one of their bounded waits runs out."""
+    key = torch.device(device).index or 0
+    t = _status.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[key] = t
+    return t
+
+
+def check_status(device) -> None:
+    """Raises if a tensor-core kernel gave up a wait since the last check.
+    Synchronises; call it where the host waits anyway."""
+    key = torch.device(device).index or 0
+    t = _status.get(key)
+    if t is None:
+        return
+    code = int(t.item())
+    if code:
+        t.zero_()
+        what = {1: "a TMA producer", 2: "an MMA issuer", 3: "an epilogue"}.get(code, "a role")
+        raise RuntimeError(f"a tensor-core kernel gave up: {what} waited past its limit "
+                           f"(status {code}); the step's results are not valid")
+
+
+def _stream():
+    return _c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _tile_width(m: int, n_cols: int) -> int:
+    """Tile width in output columns.  Wider tiles reuse the A tile more; narrow
+    ones give more blocks when the problem has few tiles."""
+    m_tiles = -(-m // 128)
+    for bn in (256, 128):
+        if m_tiles * -(-n_cols // bn) >= 120:
+            return bn
+    return 64
+
+
+def _gemm(a, w, out, n, epi, bn) -> bool:
+    lib = build.load("gemm_tcgen05")
+    code = lib.cb_gemm_tcgen05(
+        _c_void_p(a.data_ptr()), _c_void_p(w.data_ptr()), _c_void_p(out.data_ptr()),
+        _c_int(a.shape[0]), _c_int(n), _c_int(a.shape[1]), _c_int(a.stride(0)),
+        _c_int(w.stride(0)), _c_int(out.stride(0)), _c_int(epi), _c_int(bn),
+        _c_void_p(status_word(a.device).data_ptr()), _stream())
+    if code == _UNSUPPORTED:
+        return False
+    if code != 0:
+        raise RuntimeError(f"tensor-core matrix product failed to launch (CUDA error {code})")
+    return True
+
+
+def _operands_ok(a, w) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.is_cuda
+            and a.stride(1) == 1 and w.stride(1) == 1 and a.shape[1] % 8 == 0
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def linear(a, w, out, *, accumulate=False, tile=None) -> bool:
+    if not _operands_ok(a, w) or out.stride(1) != 1:
+        return False
+    if out.dtype == torch.bfloat16:
+        if accumulate:
+            return False
+        epi = STORE_BF16
+    elif out.dtype == torch.float32:
+        epi = ACCUM_F32 if accumulate else STORE_F32
+    else:
+        return False
+    bn = tile or _tile_width(a.shape[0], w.shape[0])
+    return _gemm(a, w, out, w.shape[0], epi, bn)
+
+
+def linear_swiglu(h, gate_up, out, tile=None) -> bool:
+    if not _operands_ok(h, gate_up) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        return False
+    inter = gate_up.shape[0] // 2
+    bn = tile or _tile_width(h.shape[0], 2 * inter)
+    return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn)
 
 
 def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx, cache,
