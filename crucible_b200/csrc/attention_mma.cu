@@ -1,0 +1,602 @@
+// Paged causal attention in bfloat16 on tensor cores (mma.sync m16n8k16, fp32
+// accumulation, fp32 softmax), for prompts, portions of prompts and decoded
+// tokens alike.  Query rows of one request and one KV head are enumerated as
+// (position, head within the group): all query heads that share a KV head sit
+// in the same tile, so each key and value is read once per group.
+//
+// Two launch shapes over the same inner loop:
+//   tiles kernel  - a block takes 64 rows (4 warps x 16) and walks all their
+//                   keys in tiles of 64 (cp.async, double buffered); flash-style
+//                   running maximum; writes the normalised output.  For portions
+//                   of prompts.
+//   split kernel  - a block takes 16 rows and ONE chunk of 256 keys, 64 per
+//                   warp; writes an unnormalised partial (max, sum, vector) to
+//                   scratch; a second kernel merges the chunks in ascending
+//                   order.  For decoded tokens, where rows are few and keys many.
+// Chunk boundaries are multiples of 256 from key 0 whatever the batch holds, so
+// a row's result is a function of its own query and keys only.
+//
+// Head sizes: multiples of 16 up to 256.  Any head counts and group sizes, any
+// page size.  Reference counterparts: `attention_prefill_exact_*`
+// (engine/kernels/kernels.cu:2257-2275), `attention_decode_paged_f32` (:1741),
+// and the split idea of `attention_partial_f32` / `attention_combine_f32`
+// (:692-850).
+#include "common.cuh"
+
+namespace {
+
+constexpr int TILE_KEYS = 64;
+constexpr int SPLIT_KEYS = 256;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnParams {
+    const __nv_bfloat16* qkv;
+    int qkv_stride;
+    __nv_bfloat16* out;
+    int out_stride;
+    const __nv_bfloat16* k_cache;
+    const __nv_bfloat16* v_cache;
+    const int* req_row_start;
+    const int* req_first_pos;
+    const int* block_table;
+    int table_stride;
+    int n_heads, n_kv_heads, head_dim, page_tokens;
+    float scale_log2;      // softmax scale * log2(e)
+    int window;            // 0: all earlier keys
+    float* partial;        // split kernel: [rows_total * n_heads][n_chunks][head_dim + 2]
+    int n_chunks;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+    const int bytes = valid ? 16 : 0;          // 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem)), "l"(gmem),
+                 "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(smem)));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(smem)));
+}
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+        "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Loads `n_keys` (<= TILE_KEYS) keys and values starting at key `key0` of one
+// request and KV head into shared memory rows of `pitch` elements; keys at or
+// beyond `key_end` are zero-filled.  `n_threads` threads of the caller take part.
+__device__ __forceinline__ void load_kv_tile(const AttnParams& p, const int* table, int kv_head,
+                                             int key0, int n_keys, int key_end,
+                                             __nv_bfloat16* k_smem, __nv_bfloat16* v_smem,
+                                             int pitch, int tid, int n_threads) {
+    const int chunks_per_row = p.head_dim >> 3;
+    const int total = n_keys * chunks_per_row;
+    for (int i = tid; i < total; i += n_threads) {
+        const int row = i / chunks_per_row;
+        const int c = i - row * chunks_per_row;
+        const int key = key0 + row;
+        const bool valid = key < key_end;
+        size_t off = 0;
+        if (valid) {
+            const int page = table[key / p.page_tokens];
+            const int slot = key % p.page_tokens;
+            off = (((size_t)page * p.page_tokens + slot) * p.n_kv_heads + kv_head) * p.head_dim +
+                  (size_t)c * 8;
+        }
+        cp_async_16(k_smem + row * pitch + c * 8, p.k_cache + off, valid);
+        cp_async_16(v_smem + row * pitch + c * 8, p.v_cache + off, valid);
+    }
+}
+
+// One warp, 16 query rows (A fragments read from q_smem), `n_keys` keys of a
+// tile (multiple of 16, <= 64) in shared memory: scores, running-maximum
+// softmax update and the weighted sum of values.  Rows g = lane / 4 and g + 8.
+template <int HD_MAX>
+__device__ __forceinline__ void attend_tile(const AttnParams& p, const __nv_bfloat16* q_smem,
+                                            const __nv_bfloat16* k_smem,
+                                            const __nv_bfloat16* v_smem, int pitch, int n_keys,
+                                            int key0, int pos_a, int pos_b, int lo_a, int lo_b,
+                                            int key_end, float (&o)[HD_MAX / 8][4], float& m_a,
+                                            float& m_b, float& l_a, float& l_b) {
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int hd = p.head_dim;
+    float s[TILE_KEYS / 8][4];
+#pragma unroll
+    for (int j = 0; j < TILE_KEYS / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    // S = Q K^T
+#pragma unroll
+    for (int kk = 0; kk < HD_MAX / 16; ++kk) {
+        if (kk * 16 < hd) {
+            uint32_t a[4];
+            {
+                const int mat = lane >> 3;
+                const int row = (mat & 1) * 8 + (lane & 7);
+                const int col = kk * 16 + (mat >> 1) * 8;
+                ldmatrix_x4(a, q_smem + row * pitch + col);
+            }
+#pragma unroll
+            for (int j = 0; j < TILE_KEYS / 8; j += 2) {
+                if (j * 8 < n_keys) {
+                    uint32_t b[4];
+                    const int mat = lane >> 3;
+                    const int key = (j + (mat >> 1)) * 8 + (lane & 7);
+                    const int col = kk * 16 + (mat & 1) * 8;
+                    ldmatrix_x4(b, k_smem + key * pitch + col);
+                    mma_bf16(s[j], a, b[0], b[1]);
+                    mma_bf16(s[j + 1], a, b[2], b[3]);
+                }
+            }
+        }
+    }
+    // mask, scale (in log2 units), row maxima
+    float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < TILE_KEYS / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int key = key0 + j * 8 + 2 * t + e;
+            const bool in = j * 8 < n_keys && key < key_end;
+            const bool ok_a = in && key <= pos_a && key >= lo_a;
+            const bool ok_b = in && key <= pos_b && key >= lo_b;
+            s[j][e] = ok_a ? s[j][e] * p.scale_log2 : -INFINITY;
+            s[j][2 + e] = ok_b ? s[j][2 + e] * p.scale_log2 : -INFINITY;
+            mx_a = fmaxf(mx_a, s[j][e]);
+            mx_b = fmaxf(mx_b, s[j][2 + e]);
+        }
+    }
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+    const float new_a = fmaxf(m_a, mx_a), new_b = fmaxf(m_b, mx_b);
+    // a row that has seen no key yet keeps max = -inf; use 0 as its offset so
+    // that exp2(-inf - 0) = 0 instead of exp2(-inf + inf)
+    const float off_a = new_a == -INFINITY ? 0.f : new_a;
+    const float off_b = new_b == -INFINITY ? 0.f : new_b;
+    const float corr_a = exp2f(m_a - off_a), corr_b = exp2f(m_b - off_b);
+    m_a = new_a;
+    m_b = new_b;
+    float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+    for (int j = 0; j < TILE_KEYS / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            s[j][e] = exp2f(s[j][e] - off_a);
+            s[j][2 + e] = exp2f(s[j][2 + e] - off_b);
+            sum_a += s[j][e];
+            sum_b += s[j][2 + e];
+        }
+    }
+    l_a = l_a * corr_a + sum_a;      // per-thread partial sums; reduced over the quad at the end
+    l_b = l_b * corr_b + sum_b;
+#pragma unroll
+    for (int n = 0; n < HD_MAX / 8; ++n) {
+        o[n][0] *= corr_a; o[n][1] *= corr_a;
+        o[n][2] *= corr_b; o[n][3] *= corr_b;
+    }
+    // O += P V
+#pragma unroll
+    for (int kk = 0; kk < TILE_KEYS / 16; ++kk) {
+        if (kk * 16 < n_keys) {
+            uint32_t a[4];
+            a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int n = 0; n < HD_MAX / 8; n += 2) {
+                if (n * 8 < hd) {
+                    uint32_t b[4];
+                    const int mat = lane >> 3;
+                    const int key = kk * 16 + (mat & 1) * 8 + (lane & 7);
+                    const int col = (n + (mat >> 1)) * 8;
+                    ldmatrix_x4_trans(b, v_smem + key * pitch + col);
+                    mma_bf16(o[n], a, b[0], b[1]);
+                    mma_bf16(o[n + 1], a, b[2], b[3]);
+                }
+            }
+        }
+    }
+}
+
+// Copies the 16 x head_dim query rows of a warp's tile into shared memory
+// (zeros for rows past the end); row i of the request's enumeration is
+// (position i / n_rep, head kv_head * n_rep + i % n_rep).
+__device__ __forceinline__ void load_q_rows(const AttnParams& p, int row_base, int n_rows,
+                                            int first_row, int n_rep, int kv_head,
+                                            __nv_bfloat16* q_smem, int pitch, int tid, int n_threads,
+                                            int tile_rows) {
+    const int chunks_per_row = p.head_dim >> 3;
+    for (int i = tid; i < tile_rows * chunks_per_row; i += n_threads) {
+        const int r = i / chunks_per_row, c = i - r * chunks_per_row;
+        const int row = first_row + r;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < n_rows) {
+            const int tok = row_base + row / n_rep;
+            const int head = kv_head * n_rep + row % n_rep;
+            v = *reinterpret_cast<const uint4*>(p.qkv + (size_t)tok * p.qkv_stride +
+                                                (size_t)head * p.head_dim + c * 8);
+        }
+        *reinterpret_cast<uint4*>(q_smem + r * pitch + c * 8) = v;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// tiles kernel
+// ---------------------------------------------------------------------------
+template <int HD_MAX>
+__global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    const int pitch = p.head_dim + 8;
+    __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* kv_smem = q_smem + 64 * pitch;      // [2 stages][K, V][64][pitch]
+    const int req = blockIdx.z, kv_head = blockIdx.y;
+    const int n_rep = p.n_heads / p.n_kv_heads;
+    const int row_base = p.req_row_start[req];
+    const int n_new = p.req_row_start[req + 1] - row_base;
+    const int n_rows = n_new * n_rep;
+    const int q_tiles = (n_rows + 63) >> 6;
+    if ((int)blockIdx.x >= q_tiles) return;
+    const int qt = q_tiles - 1 - (int)blockIdx.x;      // heaviest tiles first
+    const int first_pos = p.req_first_pos[req];
+    const int* table = p.block_table + (size_t)req * p.table_stride;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+
+    load_q_rows(p, row_base, n_rows, qt * 64, n_rep, kv_head, q_smem, pitch, threadIdx.x, 128, 64);
+
+    const int last_row = min(n_rows - 1, qt * 64 + 63);
+    const int max_pos = first_pos + last_row / n_rep;
+    const int min_pos = first_pos + (qt * 64) / n_rep;
+    int key_lo = p.window > 0 ? max(0, min_pos - p.window + 1) : 0;
+    key_lo = key_lo / TILE_KEYS * TILE_KEYS;
+    const int key_end = max_pos + 1;
+    const int n_tiles = (key_end - key_lo + TILE_KEYS - 1) / TILE_KEYS;
+
+    // this warp's two rows
+    const int row_a = qt * 64 + warp * 16 + g, row_b = row_a + 8;
+    const int pos_a = row_a < n_rows ? first_pos + row_a / n_rep : -1;
+    const int pos_b = row_b < n_rows ? first_pos + row_b / n_rep : -1;
+    const int lo_a = p.window > 0 ? max(0, pos_a - p.window + 1) : 0;
+    const int lo_b = p.window > 0 ? max(0, pos_b - p.window + 1) : 0;
+    const int warp_last_row = min(n_rows - 1, qt * 64 + warp * 16 + 15);
+    const int warp_max_pos = qt * 64 + warp * 16 < n_rows ? first_pos + warp_last_row / n_rep : -1;
+
+    float o[HD_MAX / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD_MAX / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+
+    const int stage_elems = 2 * TILE_KEYS * pitch;
+    load_kv_tile(p, table, kv_head, key_lo, TILE_KEYS, key_end, kv_smem, kv_smem + TILE_KEYS * pitch,
+                 pitch, threadIdx.x, 128);
+    cp_async_commit();
+    for (int i = 0; i < n_tiles; ++i) {
+        const int st = i & 1;
+        if (i + 1 < n_tiles) {
+            __nv_bfloat16* nxt = kv_smem + (st ^ 1) * stage_elems;
+            load_kv_tile(p, table, kv_head, key_lo + (i + 1) * TILE_KEYS, TILE_KEYS, key_end, nxt,
+                         nxt + TILE_KEYS * pitch, pitch, threadIdx.x, 128);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int key0 = key_lo + i * TILE_KEYS;
+        if (key0 <= warp_max_pos) {
+            const __nv_bfloat16* ks = kv_smem + st * stage_elems;
+            attend_tile<HD_MAX>(p, q_smem + warp * 16 * pitch, ks, ks + TILE_KEYS * pitch, pitch,
+                                TILE_KEYS, key0, pos_a, pos_b, lo_a, lo_b, key_end, o, m_a, m_b,
+                                l_a, l_b);
+        }
+        __syncthreads();
+    }
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    const float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
+#pragma unroll
+    for (int n = 0; n < HD_MAX / 8; ++n) {
+        if (n * 8 < p.head_dim) {
+            const int col = n * 8 + 2 * t;
+            if (row_a < n_rows) {
+                const int tok = row_base + row_a / n_rep, head = kv_head * n_rep + row_a % n_rep;
+                *reinterpret_cast<uint32_t*>(p.out + (size_t)tok * p.out_stride +
+                                             (size_t)head * p.head_dim + col) =
+                    pack_bf16(o[n][0] * inv_a, o[n][1] * inv_a);
+            }
+            if (row_b < n_rows) {
+                const int tok = row_base + row_b / n_rep, head = kv_head * n_rep + row_b % n_rep;
+                *reinterpret_cast<uint32_t*>(p.out + (size_t)tok * p.out_stride +
+                                             (size_t)head * p.head_dim + col) =
+                    pack_bf16(o[n][2] * inv_b, o[n][3] * inv_b);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// split kernel: 16 rows x one chunk of 256 keys, 64 keys per warp
+// ---------------------------------------------------------------------------
+template <int HD_MAX>
+__global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    const int pitch = p.head_dim + 8;
+    __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* kv_smem = q_smem + 16 * pitch;      // [4 warps][K, V][64][pitch]
+    const int req = blockIdx.z, kv_head = blockIdx.y;
+    const int n_rep = p.n_heads / p.n_kv_heads;
+    const int row_base = p.req_row_start[req];
+    const int n_new = p.req_row_start[req + 1] - row_base;
+    const int n_rows = n_new * n_rep;
+    const int q_tiles = (n_rows + 15) >> 4;
+    const int chunk = blockIdx.x % p.n_chunks;
+    const int qt = blockIdx.x / p.n_chunks;
+    if (qt >= q_tiles) return;
+    const int first_pos = p.req_first_pos[req];
+    const int* table = p.block_table + (size_t)req * p.table_stride;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+
+    const int last_row = min(n_rows - 1, qt * 16 + 15);
+    const int max_pos = first_pos + last_row / n_rep;
+    const int min_pos = first_pos + (qt * 16) / n_rep;
+    const int key_lo = p.window > 0 ? max(0, min_pos - p.window + 1) : 0;
+    const int key_end = max_pos + 1;
+    const int c0 = chunk * SPLIT_KEYS;
+    // chunks wholly outside the tile's keys write nothing; the merge skips them
+    // by the same rule
+    if (c0 >= key_end || c0 + SPLIT_KEYS <= key_lo) return;
+
+    load_q_rows(p, row_base, n_rows, qt * 16, n_rep, kv_head, q_smem, pitch, threadIdx.x, 128, 16);
+    __nv_bfloat16* ks = kv_smem + warp * 2 * TILE_KEYS * pitch;
+    __nv_bfloat16* vs = ks + TILE_KEYS * pitch;
+    const int key0 = c0 + warp * TILE_KEYS;
+    load_kv_tile(p, table, kv_head, key0, TILE_KEYS, key_end, ks, vs, pitch, lane, 32);
+    cp_async_commit();
+
+    const int row_a = qt * 16 + g, row_b = row_a + 8;
+    const int pos_a = row_a < n_rows ? first_pos + row_a / n_rep : -1;
+    const int pos_b = row_b < n_rows ? first_pos + row_b / n_rep : -1;
+    const int lo_a = p.window > 0 ? max(0, pos_a - p.window + 1) : 0;
+    const int lo_b = p.window > 0 ? max(0, pos_b - p.window + 1) : 0;
+    float o[HD_MAX / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD_MAX / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    cp_async_wait<0>();
+    __syncthreads();             // q rows (all threads) and this warp's keys are in place
+    if (key0 < key_end)
+        attend_tile<HD_MAX>(p, q_smem, ks, vs, pitch, TILE_KEYS, key0, pos_a, pos_b, lo_a, lo_b,
+                            key_end, o, m_a, m_b, l_a, l_b);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+
+    // merge the four warps (ascending keys) through shared memory, reusing the
+    // key/value buffers: per warp 16 rows x (head_dim + 2) floats
+    __syncthreads();
+    float* merge = reinterpret_cast<float*>(kv_smem);
+    const int mp = p.head_dim + 2;
+    {
+        float* mine = merge + (size_t)warp * 16 * mp;
+#pragma unroll
+        for (int n = 0; n < HD_MAX / 8; ++n) {
+            if (n * 8 < p.head_dim) {
+                const int col = n * 8 + 2 * t;
+                mine[g * mp + col] = o[n][0];
+                mine[g * mp + col + 1] = o[n][1];
+                mine[(g + 8) * mp + col] = o[n][2];
+                mine[(g + 8) * mp + col + 1] = o[n][3];
+            }
+        }
+        if (t == 0) {
+            mine[g * mp + p.head_dim] = m_a;
+            mine[g * mp + p.head_dim + 1] = l_a;
+            mine[(g + 8) * mp + p.head_dim] = m_b;
+            mine[(g + 8) * mp + p.head_dim + 1] = l_b;
+        }
+    }
+    __syncthreads();
+    // thread -> (row, feature) pairs; write the chunk's partial
+    for (int i = threadIdx.x; i < 16 * mp; i += 128) {
+        const int r = i / mp, f = i - r * mp;
+        const int row = qt * 16 + r;
+        if (row >= n_rows) continue;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, merge[((size_t)w * 16 + r) * mp + p.head_dim]);
+        float v;
+        if (f == p.head_dim) {
+            v = m;
+        } else {
+            const int src = f == p.head_dim + 1 ? p.head_dim + 1 : f;
+            v = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float mw = merge[((size_t)w * 16 + r) * mp + p.head_dim];
+                const float scale = mw == -INFINITY ? 0.f : exp2f(mw - m);
+                v += merge[((size_t)w * 16 + r) * mp + src] * scale;
+            }
+        }
+        const int tok = row_base + row / n_rep, head = kv_head * n_rep + row % n_rep;
+        p.partial[(((size_t)tok * p.n_heads + head) * p.n_chunks + chunk) * mp + f] = v;
+    }
+}
+
+// Merges a row's chunks in ascending order.  One warp per (token, head).
+__global__ void attention_merge_kernel(const AttnParams p, const int* __restrict__ positions,
+                                       int n_tokens) {
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= n_tokens * p.n_heads) return;
+    const int lane = threadIdx.x & 31;
+    const int tok = unit / p.n_heads, head = unit - tok * p.n_heads;
+    const int pos = positions[tok];
+    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int mp = p.head_dim + 2;
+    const int c_first = lo / SPLIT_KEYS, c_last = pos / SPLIT_KEYS;
+    const float* base = p.partial + ((size_t)tok * p.n_heads + head) * p.n_chunks * mp;
+    float m = -INFINITY;
+    for (int c = c_first; c <= c_last; ++c) m = fmaxf(m, base[(size_t)c * mp + p.head_dim]);
+    float l = 0.f;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int c = c_first; c <= c_last; ++c) {
+        const float mc = base[(size_t)c * mp + p.head_dim];
+        const float w = mc == -INFINITY ? 0.f : exp2f(mc - m);
+        l += base[(size_t)c * mp + p.head_dim + 1] * w;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int f = lane + 32 * i;
+            if (f < p.head_dim) acc[i] += base[(size_t)c * mp + f] * w;
+        }
+    }
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    __nv_bfloat16* dst = p.out + (size_t)tok * p.out_stride + (size_t)head * p.head_dim;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int f = lane + 32 * i;
+        if (f < p.head_dim) dst[f] = __float2bfloat16_rn(acc[i] * inv);
+    }
+}
+
+template <int HD_MAX>
+int launch_tiles(const AttnParams& p, int n_requests, int max_q_tiles, cudaStream_t s) {
+    const int pitch = p.head_dim + 8;
+    const int smem = (64 + 4 * TILE_KEYS) * pitch * 2;
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tiles_kernel<HD_MAX>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(max_q_tiles, p.n_kv_heads, n_requests);
+    attention_tiles_kernel<HD_MAX><<<grid, 128, smem, s>>>(p);
+    return cb_last_error();
+}
+
+template <int HD_MAX>
+int launch_split(const AttnParams& p, int n_requests, int max_q_tiles, cudaStream_t s) {
+    const int pitch = p.head_dim + 8;
+    int smem = (16 + 8 * TILE_KEYS) * pitch * 2;
+    const int merge_bytes = 4 * 16 * (p.head_dim + 2) * 4;
+    if (16 * pitch * 2 + merge_bytes > smem) smem = 16 * pitch * 2 + merge_bytes;
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attention_split_kernel<HD_MAX>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(max_q_tiles * p.n_chunks, p.n_kv_heads, n_requests);
+    attention_split_kernel<HD_MAX><<<grid, 128, smem, s>>>(p);
+    return cb_last_error();
+}
+
+}  // namespace
+
+// Floats of scratch the split form needs for `n_tokens` rows and `n_chunks` chunks.
+CB_EXPORT long cb_attention_split_scratch_floats(int n_tokens, int n_heads, int head_dim,
+                                                 int n_chunks) {
+    return (long)n_tokens * n_heads * n_chunks * (head_dim + 2);
+}
+
+CB_EXPORT int cb_attention_split_keys() { return SPLIT_KEYS; }
+
+// n_chunks == 0: tiles kernel.  n_chunks > 0: split kernel over that many
+// chunks of 256 keys (it must cover the longest context) plus the merge;
+// `partial` must hold cb_attention_split_scratch_floats floats.
+// max_q_rows: the largest (new tokens x heads per group) of any request.
+CB_EXPORT int cb_attention_mma(const void* qkv, int qkv_stride, void* out, int out_stride,
+                               const void* k_cache, const void* v_cache, const int* positions,
+                               const int* req_row_start, const int* req_first_pos,
+                               const int* block_table, int table_stride, int n_tokens,
+                               int n_requests, int max_new_tokens, int n_heads, int n_kv_heads,
+                               int head_dim, int page_tokens, float scale, int window,
+                               float* partial, int n_chunks, void* stream) {
+    if (n_tokens <= 0 || n_requests <= 0) return 0;
+    if (head_dim <= 0 || head_dim > 256 || (head_dim & 15) || n_heads % n_kv_heads != 0 ||
+        (qkv_stride & 7) || (out_stride & 1) || ((uintptr_t)qkv & 15) || ((uintptr_t)k_cache & 15) ||
+        ((uintptr_t)v_cache & 15))
+        return CB_ERR_UNSUPPORTED;
+    AttnParams p;
+    p.qkv = (const __nv_bfloat16*)qkv;
+    p.qkv_stride = qkv_stride;
+    p.out = (__nv_bfloat16*)out;
+    p.out_stride = out_stride;
+    p.k_cache = (const __nv_bfloat16*)k_cache;
+    p.v_cache = (const __nv_bfloat16*)v_cache;
+    p.req_row_start = req_row_start;
+    p.req_first_pos = req_first_pos;
+    p.block_table = block_table;
+    p.table_stride = table_stride;
+    p.n_heads = n_heads;
+    p.n_kv_heads = n_kv_heads;
+    p.head_dim = head_dim;
+    p.page_tokens = page_tokens;
+    p.scale_log2 = scale * LOG2E;
+    p.window = window;
+    p.partial = partial;
+    p.n_chunks = n_chunks;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int n_rep = n_heads / n_kv_heads;
+    const int max_rows = max_new_tokens * n_rep;
+    int rc;
+    if (n_chunks == 0) {
+        const int q_tiles = (max_rows + 63) / 64;
+        if (head_dim <= 16) rc = launch_tiles<16>(p, n_requests, q_tiles, s);
+        else if (head_dim <= 32) rc = launch_tiles<32>(p, n_requests, q_tiles, s);
+        else if (head_dim <= 64) rc = launch_tiles<64>(p, n_requests, q_tiles, s);
+        else if (head_dim <= 128) rc = launch_tiles<128>(p, n_requests, q_tiles, s);
+        else rc = launch_tiles<256>(p, n_requests, q_tiles, s);
+        return rc;
+    }
+    if (partial == nullptr) return CB_ERR_UNSUPPORTED;
+    const int q_tiles = (max_rows + 15) / 16;
+    if (head_dim <= 16) rc = launch_split<16>(p, n_requests, q_tiles, s);
+    else if (head_dim <= 32) rc = launch_split<32>(p, n_requests, q_tiles, s);
+    else if (head_dim <= 64) rc = launch_split<64>(p, n_requests, q_tiles, s);
+    else if (head_dim <= 128) rc = launch_split<128>(p, n_requests, q_tiles, s);
+    else rc = launch_split<256>(p, n_requests, q_tiles, s);
+    if (rc != 0) return rc;
+    const int warps = 4;
+    const long units = (long)n_tokens * n_heads;
+    attention_merge_kernel<<<(int)((units + warps - 1) / warps), warps * 32, 0, s>>>(p, positions,
+                                                                                    n_tokens);
+    return cb_last_error();
+}

@@ -16,6 +16,7 @@ import torch
 from . import build
 
 build.register_module("gemm_tcgen05", ["common.cuh", "tc_common.cuh"])
+build.register_module("attention_mma", ["common.cuh"])
 
 _c_int, _c_void_p = ctypes.c_int, ctypes.c_void_p
 STORE_BF16, STORE_F32, ACCUM_F32, SWIGLU_BF16 = 0, 1, 2, 3
@@ -107,6 +108,49 @@ def linear_swiglu(h, gate_up, out, tile=None) -> bool:
     return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn)
 
 
+def attention_chunks(max_context_len: int) -> int:
+    """Chunks of 256 keys the split form is launched over: the smallest power
+    of two that covers the longest context of the step (a launch shape only;
+    which chunks a row reads depends on that row alone)."""
+    need = max(1, -(-max_context_len // 256))
+    n = 1
+    while n < need:
+        n *= 2
+    return n
+
+
 def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx, cache,
                     binding) -> bool:
-    return False
+    """mma.sync attention over the paged cache.  Takes head sizes that are
+    multiples of 16 up to 256 and any head counts, group sizes and page sizes;
+    refuses anything else (the plain kernel then runs).  Requests that bring at
+    most 16 query rows per KV head (decoded tokens, tiny portions) run split
+    over chunks of 256 keys; longer portions run as tiles of 64 rows."""
+    if (qkv.dtype != torch.bfloat16 or head_dim % 16 != 0 or head_dim > 256
+            or n_heads % n_kv_heads != 0 or qkv.stride(0) % 8 != 0 or out.stride(0) % 2 != 0):
+        return False
+    k_cache, v_cache = cache.keys(binding.slot), cache.values(binding.slot)
+    table = ctx.block_table(binding.group)
+    host = ctx.host
+    n_rep = n_heads // n_kv_heads
+    split = host.max_new_tokens * n_rep <= 16
+    n_chunks = attention_chunks(host.max_context_len) if split else 0
+    partial = None
+    if split:
+        floats = ctx.n_tokens * n_heads * n_chunks * (head_dim + 2)
+        partial = ctx.scratch("attn.partial", (floats,), torch.float32)
+    lib = build.load("attention_mma")
+    code = lib.cb_attention_mma(
+        _c_void_p(qkv.data_ptr()), _c_int(qkv.stride(0)), _c_void_p(out.data_ptr()),
+        _c_int(out.stride(0)), _c_void_p(k_cache.data_ptr()), _c_void_p(v_cache.data_ptr()),
+        _c_void_p(ctx.positions.data_ptr()), _c_void_p(ctx.req_row_start.data_ptr()),
+        _c_void_p(ctx.req_first_pos.data_ptr()), _c_void_p(table.data_ptr()),
+        _c_int(table.shape[1]), _c_int(ctx.n_tokens), _c_int(ctx.n_requests),
+        _c_int(host.max_new_tokens), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
+        _c_int(cache.page_tokens), ctypes.c_float(scale), _c_int(window or 0),
+        _c_void_p(partial.data_ptr() if partial is not None else 0), _c_int(n_chunks), _stream())
+    if code == _UNSUPPORTED:
+        return False
+    if code != 0:
+        raise RuntimeError(f"tensor-core attention failed to launch (CUDA error {code})")
+    return True

@@ -1,0 +1,377 @@
+"""Each kernel alone against a plain PyTorch fp32 reference of the same
+operation, at other sizes than the engine tests use."""
+import math
+import random
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _ops():
+    from crucible_b200 import ops
+    return ops
+
+
+def rel(got, ref):
+    return float((got.double() - ref.double()).abs().max()) / max(float(ref.abs().max()), 1e-6)
+
+
+# ---------------------------------------------------------------------------
+# row-wise kernels
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_rows(dtype):
+    ops = _ops()
+    table = torch.randn(301, 72, device=DEV).to(dtype)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 72, device=DEV)
+    ops.embed_rows(table, ids, out)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width,eps", [(72, 1e-5), (1000, 1e-6), (4100, 1e-3)])
+def test_rmsnorm(dtype, width, eps):
+    ops = _ops()
+    x = torch.randn(9, width, device=DEV) * 3.0
+    gain = 1.0 + 0.2 * torch.randn(width, device=DEV)
+    out = torch.empty(9, width, device=DEV, dtype=dtype)
+    ops.rmsnorm(x, gain, eps, out)
+    ref = x.double() * torch.rsqrt(x.double().pow(2).mean(-1, keepdim=True) + eps) * gain.double()
+    assert rel(out, ref) < (2e-6 if dtype == torch.float32 else 5e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(dtype):
+    ops = _ops()
+    gu = (torch.randn(11, 2 * 88, device=DEV) * 2).to(dtype)
+    out = torch.empty(11, 88, device=DEV, dtype=dtype)
+    ops.swiglu(gu, out)
+    g, u = gu[:, :88].double(), gu[:, 88:].double()
+    assert rel(out, g / (1 + torch.exp(-g)) * u) < (2e-6 if dtype == torch.float32 else 5e-3)
+
+
+def test_gather_rows():
+    ops = _ops()
+    x = torch.randn(20, 40, device=DEV)
+    rows = torch.tensor([19, 0, 7], dtype=torch.int32, device=DEV)
+    out = torch.empty(3, 40, device=DEV)
+    ops.gather_rows(x, rows, out)
+    assert torch.equal(out, x[rows.long()])
+
+
+# ---------------------------------------------------------------------------
+# matrix products
+# ---------------------------------------------------------------------------
+
+SHAPES = [(1, 64, 64), (7, 509, 96), (130, 192, 320), (300, 1280, 768), (64, 2050, 136),
+          (257, 100, 24)]
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES + [(5, 33, 7), (70, 65, 129)])
+def test_linear_plain_fp32(m, n, k):
+    ops = _ops()
+    # mantissa-dense and single-signed data, so that a dropped or doubled term shows
+    a = torch.rand(m, k, device=DEV) + 0.5
+    w = torch.rand(n, k, device=DEV) + 0.5
+    out = torch.empty(m, n, device=DEV)
+    ops.linear_plain(a, w, out)
+    ref = a.double() @ w.double().T
+    assert rel(out, ref) < 2e-6
+    base = torch.randn(m, n, device=DEV)
+    acc = base.clone()
+    ops.linear_plain(a, w, acc, accumulate=True)
+    assert rel(acc, ref + base.double()) < 2e-6
+
+
+@pytest.mark.parametrize("tile", [64, 128, 256])
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_linear_tensor_core(m, n, k, tile):
+    from crucible_b200.ops import tensor_core
+    a = (torch.rand(m, k, device=DEV) + 0.5).bfloat16()
+    w = (torch.rand(n, k, device=DEV) * 0.1 + 0.05).bfloat16()
+    ref = a.double() @ w.double().T
+    out = torch.empty(m, n, device=DEV)
+    assert tensor_core.linear(a, w, out, tile=tile)
+    assert rel(out, ref) < 1e-5
+    out16 = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    assert tensor_core.linear(a, w, out16, tile=tile)
+    assert rel(out16, ref) < 5e-3
+    base = torch.randn(m, n, device=DEV)
+    acc = base.clone()
+    assert tensor_core.linear(a, w, acc, accumulate=True, tile=tile)
+    assert rel(acc, ref + base.double()) < 1e-5
+    tensor_core.check_status(DEV)
+
+
+@pytest.mark.parametrize("tile", [64, 128, 256])
+@pytest.mark.parametrize("m,inter,k", [(1, 176, 64), (33, 320, 96), (300, 2048, 768), (130, 88, 40)])
+def test_linear_swiglu_tensor_core(m, inter, k, tile):
+    from crucible_b200.ops import tensor_core
+    h = torch.randn(m, k, device=DEV).bfloat16()
+    w = (torch.randn(2 * inter, k, device=DEV) * 0.2).bfloat16()
+    out = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
+    assert tensor_core.linear_swiglu(h, w, out, tile=tile)
+    y = h.double() @ w.double().T
+    g, u = y[:, :inter], y[:, inter:]
+    assert rel(out, g / (1 + torch.exp(-g)) * u) < 6e-3
+    tensor_core.check_status(DEV)
+
+
+def test_linear_refuses_what_tma_cannot_read():
+    from crucible_b200.ops import tensor_core
+    a = torch.randn(4, 100, device=DEV).bfloat16()      # 200-byte rows: not a multiple of 16
+    w = torch.randn(8, 100, device=DEV).bfloat16()
+    out = torch.empty(4, 8, device=DEV)
+    assert tensor_core.linear(a, w, out) is False
+    ops = _ops()
+    ops.linear(a, w, out)                                # the CUDA-core product takes over
+    assert rel(out, a.double() @ w.double().T) < 1e-5
+
+
+# ---------------------------------------------------------------------------
+# attention over a paged cache
+# ---------------------------------------------------------------------------
+
+def _paged_case(dtype, n_heads, n_kv, hd, page_tokens, requests, seed, window=None, peak=True):
+    """requests: list of (context_before, new_tokens).  Builds random q, k, v for
+    whole sequences, scatters k/v of the context into shuffled pages, and returns
+    what the kernels need plus the reference output for the new rows."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    rng = random.Random(seed)
+    total_pages = sum(-(-(c + n) // page_tokens) for c, n in requests) + 3
+    order = list(range(total_pages))
+    rng.shuffle(order)
+    kv = torch.full((1, 2, total_pages, page_tokens, n_kv, hd), float("nan"))   # poison
+    stride = max(-(-(c + n) // page_tokens) for c, n in requests) + 2
+    tables = torch.zeros(len(requests), stride, dtype=torch.int32)
+    q_rows, refs, positions, row_request, row_start, first_pos = [], [], [], [], [0], []
+    n_rep = n_heads // n_kv
+    for r, (ctx_len, n_new) in enumerate(requests):
+        length = ctx_len + n_new
+        q = torch.randn(length, n_heads, hd, generator=g)
+        k = torch.randn(length, n_kv, hd, generator=g)
+        v = torch.randn(length, n_kv, hd, generator=g)
+        if peak and length > 3:
+            # one far key stands out for the last query of every head: a kernel that
+            # loses it (a page's edge, a chunk's edge) is off by far more than rounding
+            far = rng.randrange(0, max(1, length // 3))
+            if window is not None:
+                far = max(far, length - window)
+            for h in range(n_heads):
+                k[far, h // n_rep] = q[length - 1, h] * (6.0 / math.sqrt(hd))
+        q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+        pages = [order.pop() for _ in range(-(-length // page_tokens))]
+        tables[r, :len(pages)] = torch.tensor(pages, dtype=torch.int32)
+        for pos in range(length):
+            kv[0, 0, pages[pos // page_tokens], pos % page_tokens] = k[pos].float()
+            kv[0, 1, pages[pos // page_tokens], pos % page_tokens] = v[pos].float()
+        qd, kd, vd = q.double(), k.double(), v.double()
+        out = torch.zeros(n_new, n_heads, hd, dtype=torch.float64)
+        for i, pos in enumerate(range(ctx_len, length)):
+            lo = 0 if window is None else max(0, pos - window + 1)
+            for h in range(n_heads):
+                s = (kd[lo:pos + 1, h // n_rep] @ qd[pos, h]) / math.sqrt(hd)
+                p = torch.softmax(s, dim=0)
+                out[i, h] = p @ vd[lo:pos + 1, h // n_rep]
+        refs.append(out)
+        q_rows.append(q[ctx_len:])
+        positions += list(range(ctx_len, length))
+        row_request += [r] * n_new
+        row_start.append(row_start[-1] + n_new)
+        first_pos.append(ctx_len)
+    t = len(positions)
+    qkv = torch.zeros(t, (n_heads + 2 * n_kv) * hd, dtype=dtype)
+    qkv[:, :n_heads * hd] = torch.cat(q_rows).reshape(t, n_heads * hd)
+    kv = torch.nan_to_num(kv, nan=1e4).to(dtype).to(DEV)       # unused slots hold a loud value
+
+    class Cache:
+        pass
+    cache = Cache()
+    cache.page_tokens = page_tokens
+    cache.keys = lambda slot: kv[slot, 0]
+    cache.values = lambda slot: kv[slot, 1]
+    dev = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    table_dev = tables.to(DEV)
+    scratch = {}
+
+    def get_scratch(name, shape, dt):
+        key = (name, tuple(shape), dt)
+        if key not in scratch:
+            scratch[key] = torch.empty(*shape, dtype=dt, device=DEV)
+        return scratch[key]
+    ctx = SimpleNamespace(
+        positions=dev(positions), row_request=dev(row_request), req_row_start=dev(row_start),
+        req_first_pos=dev(first_pos), n_tokens=t, n_requests=len(requests),
+        block_table=lambda group: table_dev, scratch=get_scratch,
+        host=SimpleNamespace(max_new_tokens=max(n for _, n in requests),
+                             max_context_len=max(c + n for c, n in requests)))
+    binding = SimpleNamespace(group=0, slot=0, write=True)
+    return qkv.to(DEV), ctx, cache, binding, torch.cat(refs).reshape(t, n_heads * hd)
+
+
+ATTN_CASES = [
+    # heads, kv heads, head size, page, [(context before, new tokens)], window
+    (12, 4, 64, 16, [(0, 130), (300, 1), (17, 40)], None),
+    (8, 8, 128, 32, [(0, 70), (511, 1)], None),
+    (6, 2, 48, 16, [(5, 33), (257, 2), (0, 1)], None),
+    (4, 1, 16, 8, [(1023, 1), (0, 260)], None),
+    (4, 2, 32, 16, [(100, 60), (400, 1)], 96),
+    (2, 1, 256, 16, [(40, 30)], None),
+]
+
+
+@pytest.mark.parametrize("case", ATTN_CASES)
+def test_attention_plain_fp32(case):
+    ops = _ops()
+    n_heads, n_kv, hd, page, requests, window = case
+    qkv, ctx, cache, binding, ref = _paged_case(torch.float32, n_heads, n_kv, hd, page, requests, 3,
+                                                window)
+    out = torch.zeros(qkv.shape[0], n_heads * hd, device=DEV)
+    ops.paged_attention_plain(qkv, out, n_heads, n_kv, hd, 1 / math.sqrt(hd), window, ctx, cache,
+                              binding)
+    assert rel(out.cpu(), ref) < 1e-5
+
+
+@pytest.mark.parametrize("case", ATTN_CASES)
+def test_attention_tensor_core_tiles_and_split(case):
+    from crucible_b200.ops import tensor_core
+    n_heads, n_kv, hd, page, requests, window = case
+    qkv, ctx, cache, binding, ref = _paged_case(torch.bfloat16, n_heads, n_kv, hd, page, requests,
+                                                4, window)
+    out = torch.zeros(qkv.shape[0], n_heads * hd, device=DEV, dtype=torch.bfloat16)
+    assert tensor_core.paged_attention(qkv, out, n_heads, n_kv, hd, 1 / math.sqrt(hd), window, ctx,
+                                       cache, binding)
+    assert rel(out.cpu(), ref) < 1.5e-2
+    # the split form on the decoded rows alone must agree with the tiled form
+    single = [(c + n - 1, 1) for c, n in requests]
+    qkv1, ctx1, cache1, binding1, ref1 = _paged_case(torch.bfloat16, n_heads, n_kv, hd, page, single,
+                                                     4, window)
+    out1 = torch.zeros(qkv1.shape[0], n_heads * hd, device=DEV, dtype=torch.bfloat16)
+    assert tensor_core.paged_attention(qkv1, out1, n_heads, n_kv, hd, 1 / math.sqrt(hd), window,
+                                       ctx1, cache1, binding1)
+    assert rel(out1.cpu(), ref1) < 1.5e-2
+
+
+def test_attention_odd_head_size_falls_to_plain_kernel():
+    from crucible_b200.ops import tensor_core
+    ops = _ops()
+    qkv, ctx, cache, binding, ref = _paged_case(torch.bfloat16, 4, 2, 24, 16, [(30, 5)], 5)
+    out = torch.zeros(qkv.shape[0], 4 * 24, device=DEV, dtype=torch.bfloat16)
+    assert tensor_core.paged_attention(qkv, out, 4, 2, 24, 0.2, None, ctx, cache, binding) is False
+    ops.paged_attention(qkv, out, 4, 2, 24, 1 / math.sqrt(24), None, ctx, cache, binding)
+    assert rel(out.cpu(), ref) < 1.5e-2
+
+
+# ---------------------------------------------------------------------------
+# rotary encoding + cache write
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hd,rot", [(16, 16), (64, 64), (48, 32), (32, 0)])
+def test_rope_kv_append(dtype, hd, rot):
+    ops = _ops()
+    n_heads, n_kv, page = 3, 1, 8
+    positions = [5, 6, 7, 8, 40, 0]
+    row_request = [0, 0, 0, 0, 1, 2]
+    tables = torch.tensor([[3, 1, 0, 0, 0, 0], [2, 5, 6, 7, 8, 9], [4, 0, 0, 0, 0, 0]],
+                          dtype=torch.int32, device=DEV)
+    t = len(positions)
+    qkv = torch.randn(t, (n_heads + 2 * n_kv) * hd).to(dtype)
+    before = qkv.clone()
+    kv = torch.zeros(1, 2, 10, page, n_kv, hd, dtype=dtype, device=DEV)
+    cos = sin = None
+    if rot:
+        i = torch.arange(rot // 2, dtype=torch.float64)
+        ang = torch.outer(torch.arange(64, dtype=torch.float64), 500.0 ** (-2 * i / rot))
+        cos, sin = ang.cos().float().to(DEV), ang.sin().float().to(DEV)
+
+    class Cache:
+        page_tokens = page
+        keys = staticmethod(lambda slot: kv[slot, 0])
+        values = staticmethod(lambda slot: kv[slot, 1])
+    ctx = SimpleNamespace(positions=torch.tensor(positions, dtype=torch.int32, device=DEV),
+                          row_request=torch.tensor(row_request, dtype=torch.int32, device=DEV),
+                          block_table=lambda g: tables)
+    dev_qkv = qkv.to(DEV)
+    ops.rope_kv_append(dev_qkv, n_heads, n_kv, hd, cos, sin, rot, ctx, Cache,
+                       SimpleNamespace(group=0, slot=0, write=True))
+    got = dev_qkv.cpu().double()
+    x = before.double().view(t, n_heads + 2 * n_kv, hd)
+
+    def rotate(v, pos):
+        if not rot:
+            return v
+        c, s = ang[pos].cos(), ang[pos].sin()
+        x1, x2 = v[..., :rot // 2], v[..., rot // 2:rot]
+        return torch.cat([x1 * c - x2 * s, x1 * s + x2 * c, v[..., rot:]], dim=-1)
+    tol = 1e-6 if dtype == torch.float32 else 8e-3
+    for r, pos in enumerate(positions):
+        want_q = rotate(x[r, :n_heads], pos)
+        assert rel(got[r].view(-1, hd)[:n_heads], want_q) < tol
+        page_id = int(tables[row_request[r], pos // page])
+        want_k = rotate(x[r, n_heads:n_heads + n_kv], pos)
+        assert rel(kv[0, 0, page_id, pos % page].cpu(), want_k) < tol
+        assert torch.equal(kv[0, 1, page_id, pos % page].cpu().double(), x[r, n_heads + n_kv:])
+
+
+# ---------------------------------------------------------------------------
+# token selection
+# ---------------------------------------------------------------------------
+
+def test_argmax_ties_nan_and_edges():
+    ops = _ops()
+    nan, inf = float("nan"), float("inf")
+    rows = [
+        [1.0, 3.0, 3.0, 2.0],            # tie -> lowest index
+        [nan, 1.0, 0.5, nan],            # NaN never wins
+        [-inf, -inf, -inf, -inf],        # all -inf -> 0
+        [0.0, -0.0, 0.0, -1.0],          # signed zeros tie -> 0
+        [1.0, 2.0, 3.0, inf],            # last position
+        [nan, nan, nan, nan],            # all NaN -> 0
+    ]
+    logits = torch.tensor(rows, device=DEV)
+    out = torch.empty(len(rows), dtype=torch.int32, device=DEV)
+    ops.argmax_rows(logits, out)
+    assert out.tolist() == [1, 1, 0, 0, 3, 0]
+    big = torch.randn(3, 50304, device=DEV)
+    big[1, 50303] = 100.0
+    big[2, 77] = big[2, 40000] = 50.0
+    out = torch.empty(3, dtype=torch.int32, device=DEV)
+    ops.argmax_rows(big, out)
+    assert out.tolist() == [int(big[0].argmax()), 50303, 77]
+
+
+@pytest.mark.parametrize("vocab", [509, 50304])
+def test_sample_rows_matches_plain_sampler(vocab):
+    import plain_model as pm
+    ops = _ops()
+    torch.manual_seed(1)
+    n = 6
+    logits = torch.randn(n, vocab, device=DEV) * 3
+    logits[2, 10] = logits[2, 20] = logits[2].max() + 1         # a tie among the best
+    logits[3, 5] = float("nan")
+    temps = [0.8, 0.0, 1.5, 0.3, 100.0, 0.8]
+    ks = [40, 40, 5, 1, 128, 1000]
+    seeds = [1234, 1, 7, 8, 9, 10]
+    from crucible_b200.sampling.rng import Xorshift64Star
+    for draw in range(3):
+        rngs = [Xorshift64Star(s) for s in seeds]
+        plains = [pm.PlainRng(s) for s in seeds]
+        for _ in range(draw):
+            for r, p_ in zip(rngs, plains):
+                r.next_f32(), p_.next_f32()
+        us = [r.next_f32() if t > 0 else 0.0 for r, t in zip(rngs, temps)]
+        out = torch.empty(n, dtype=torch.int32, device=DEV)
+        ops.sample_rows(logits, torch.tensor(temps, device=DEV),
+                        torch.tensor([min(k, vocab) for k in ks], dtype=torch.int32, device=DEV),
+                        torch.tensor(us, device=DEV), max(min(k, vocab) for k in ks), out)
+        want = [pm.plain_sample(logits[i].tolist(), temps[i], ks[i], plains[i]) for i in range(n)]
+        assert out.tolist() == want
