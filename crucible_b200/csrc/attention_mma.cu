@@ -128,7 +128,7 @@ __device__ __forceinline__ void attend_tile(const AttnParams& p, const __nv_bflo
                                             int key_end, float (&o)[HD_MAX / 8][4], float& m_a,
                                             float& m_b, float& l_a, float& l_b) {
     const int lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
+    const int t = lane & 3;
     const int hd = p.head_dim;
     float s[TILE_KEYS / 8][4];
 #pragma unroll
@@ -355,7 +355,7 @@ __global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int pitch = p.head_dim + 8;
     __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* kv_smem = q_smem + 16 * pitch;      // [4 warps][K, V][64][pitch]
+    __nv_bfloat16* kv_smem = q_smem + 16 * pitch;      // [4 warps][K, V][SUB][pitch]
     const int req = blockIdx.z, kv_head = blockIdx.y;
     const int n_rep = p.n_heads / p.n_kv_heads;
     const int row_base = p.req_row_start[req];
@@ -381,11 +381,12 @@ __global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p
     if (c0 >= key_end || c0 + SPLIT_KEYS <= key_lo) return;
 
     load_q_rows(p, row_base, n_rows, qt * 16, n_rep, kv_head, q_smem, pitch, threadIdx.x, 128, 16);
-    __nv_bfloat16* ks = kv_smem + warp * 2 * TILE_KEYS * pitch;
-    __nv_bfloat16* vs = ks + TILE_KEYS * pitch;
+    // each warp walks its 64 keys in passes of SUB keys (fewer for the largest
+    // head sizes, so that four warps' keys and values fit in shared memory)
+    constexpr int SUB = HD_MAX > 128 ? 32 : TILE_KEYS;
+    __nv_bfloat16* ks = kv_smem + warp * 2 * SUB * pitch;
+    __nv_bfloat16* vs = ks + SUB * pitch;
     const int key0 = c0 + warp * TILE_KEYS;
-    load_kv_tile(p, table, kv_head, key0, TILE_KEYS, key_end, ks, vs, pitch, lane, 32);
-    cp_async_commit();
 
     const int row_a = qt * 16 + g, row_b = row_a + 8;
     const int pos_a = row_a < n_rows ? first_pos + row_a / n_rep : -1;
@@ -396,11 +397,18 @@ __global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p
 #pragma unroll
     for (int n = 0; n < HD_MAX / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
-    cp_async_wait<0>();
-    __syncthreads();             // q rows (all threads) and this warp's keys are in place
-    if (key0 < key_end)
-        attend_tile<HD_MAX>(p, q_smem, ks, vs, pitch, TILE_KEYS, key0, pos_a, pos_b, lo_a, lo_b,
+    __syncthreads();             // the query rows (written by all threads) are in place
+#pragma unroll 1
+    for (int s0 = 0; s0 < TILE_KEYS; s0 += SUB) {
+        if (key0 + s0 >= key_end) break;
+        load_kv_tile(p, table, kv_head, key0 + s0, SUB, key_end, ks, vs, pitch, lane, 32);
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncwarp();
+        attend_tile<HD_MAX>(p, q_smem, ks, vs, pitch, SUB, key0 + s0, pos_a, pos_b, lo_a, lo_b,
                             key_end, o, m_a, m_b, l_a, l_b);
+        __syncwarp();
+    }
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
@@ -513,7 +521,8 @@ int launch_tiles(const AttnParams& p, int n_requests, int max_q_tiles, cudaStrea
 template <int HD_MAX>
 int launch_split(const AttnParams& p, int n_requests, int max_q_tiles, cudaStream_t s) {
     const int pitch = p.head_dim + 8;
-    int smem = (16 + 8 * TILE_KEYS) * pitch * 2;
+    const int sub = HD_MAX > 128 ? 32 : TILE_KEYS;
+    int smem = (16 + 8 * sub) * pitch * 2;
     const int merge_bytes = 4 * 16 * (p.head_dim + 2) * 4;
     if (16 * pitch * 2 + merge_bytes > smem) smem = 16 * pitch * 2 + merge_bytes;
     static bool configured = false;

@@ -92,8 +92,8 @@ class SafetensorsFile:
         nbytes = e.end - e.start
         if nbytes == 0:
             return torch.empty(e.shape, dtype=dtype)
-        view = memoryview(self._map)[self._base + e.start:self._base + e.end]
-        flat = torch.frombuffer(view, dtype=torch.uint8, count=nbytes).clone()
+        raw = bytearray(self._map[self._base + e.start:self._base + e.end])
+        flat = torch.frombuffer(raw, dtype=torch.uint8, count=nbytes)
         return flat.view(dtype).reshape(e.shape)
 
     def close(self) -> None:
