@@ -1,0 +1,310 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine on one B200: decode tokens per second (a "step" is
+one decode step) and prefill tokens per second, with roofline fractions.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Default run: the layer sizes of the 120M shape (12 layers, width 768, 12 query
+and 4 KV heads of size 64, SwiGLU 2048, vocabulary 50,304, tied head) with
+random bfloat16 weights, batch 8, 2,048-token contexts.  It prints ONE JSON
+line.  `value` is decoded tokens per second through the engine's step function
+with the chosen ids fed back on the device (K timed steps bracketed by CUDA
+events); `e2e` is the same through the Python entry point `LLM.generate`, host
+token ids in and out; `prefill` is one 2,048-token prompt in one step;
+`points` are decode at batch 1 and 64; `roofline` relates the decode step to
+the measured HBM bandwidth.  Token ids are uniform random with a fixed seed and
+the weights are N(0, 0.02) from seed 0: the data is synthetic.
+
+For --gpus N > 1 it prints one line that says so and exits with 2: this engine
+runs on one GPU.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import random
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+REFERENCE_UNAVAILABLE = ("the reference is a Rust engine with NVRTC kernels for sm_120 plus "
+                         "loose Python scripts; pip finds neither setup.py nor pyproject.toml in "
+                         "it and cargo is not in this image, so nothing of it can be installed "
+                         "or run here")
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "source": "measured"}
+    except (OSError, KeyError, ValueError):
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while work runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = None
+        self._proc = None
+
+    def start(self):
+        try:
+            self._proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self._thread = threading.Thread(target=self._read, daemon=True)
+        self._thread.start()
+
+    def _read(self):
+        for line in self._proc.stdout:
+            if self._stop.is_set():
+                break
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append((time.time(), parts))
+
+    def stop(self):
+        self._stop.set()
+        if self._proc is not None:
+            self._proc.terminate()
+            try:
+                self._proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self._proc.kill()
+
+    def summary(self, windows):
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for t, parts in self.samples:
+            if windows and not any(a <= t <= b for a, b in windows):
+                continue
+            try:
+                sm.append(int(float(parts[0])))
+                mx = max(mx, int(float(parts[1])))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            for t, parts in self.samples:
+                try:
+                    sm.append(int(float(parts[0])))
+                    mx = max(mx, int(float(parts[1])))
+                except ValueError:
+                    pass
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_numbers(cfg):
+    layer = cfg.layers[0]
+    m, f = layer.mixer, layer.feed_forward
+    d, L, V = cfg.hidden_size, len(cfg.run_order), cfg.vocab_size
+    per_layer = (d * m.n_heads * m.head_dim + 2 * d * m.n_kv_heads * m.head_dim
+                 + m.n_heads * m.head_dim * d + 3 * d * f.intermediate)
+    head = V * d
+    kv_token_bytes = 2 * m.n_kv_heads * m.head_dim * L * 2
+    return dict(per_layer=per_layer, head=head, layers=L, kv_token_bytes=kv_token_bytes,
+                q_width=m.n_heads * m.head_dim)
+
+
+def prefill_flops(nums, t):
+    gemm = 2 * t * nums["layers"] * nums["per_layer"] + 2 * nums["head"]
+    attn = nums["layers"] * 2 * 2 * nums["q_width"] * t * (t + 1) // 2
+    return gemm + attn
+
+
+def run_ours(args):
+    import torch
+    from crucible_b200 import LLM, SamplingParams, ops
+    from crucible_b200.config import parse_config, shape
+    from crucible_b200.engine import StepEntry
+    from crucible_b200.ops import tensor_core
+    from crucible_b200.weights import write_random_model
+
+    peaks = read_peaks()
+    raw = shape("120m")
+    full_layers = raw["n_layer"]
+    if args.layers:
+        raw["n_layer"] = args.layers
+    cfg = parse_config(raw)
+    nums = model_numbers(cfg)
+    ctx_len, batch, new_tokens = args.context, args.batch, args.steps
+    rng = random.Random(1)
+    vocab = cfg.vocab_size
+
+    with tempfile.TemporaryDirectory() as tmp:
+        folder = write_random_model(raw, os.path.join(tmp, "model"), seed=0)
+        max_batch = 64
+        page = 16
+        need_tokens = ctx_len + args.steps + args.warmup + 64
+        kv_pages = max_batch * (-(-need_tokens // page)) + 64
+        llm = LLM(folder, dtype="bfloat16", max_batch=max_batch, kv_pages=kv_pages,
+                  page_tokens=page, prefill_token_budget=2048)
+    engine = llm.engine
+    dev = engine.device
+    clocks = ClockSampler()
+    clocks.start()
+    windows = []
+
+    def prompt(n):
+        return [rng.randrange(vocab) for _ in range(n)]
+
+    # ---- prefill: one 2,048-token prompt, one step --------------------------------
+    t_prefill = 2048
+    pre_ms = []
+    for i in range(args.warmup + 5):
+        tokens = prompt(t_prefill)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        w0 = time.time()
+        e0.record()
+        engine.step([StepEntry("p", tokens, [t_prefill - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= args.warmup:
+            pre_ms.append(e0.elapsed_time(e1))
+            windows.append((w0, time.time()))
+        engine.finish("p")
+    pre_ms.sort()
+    prefill_ms = pre_ms[len(pre_ms) // 2]
+    prefill = {"value": round(t_prefill / (prefill_ms / 1e3), 1), "tokens": t_prefill,
+               "ms": round(prefill_ms, 4),
+               "frac": round(prefill_flops(nums, t_prefill) / (prefill_ms / 1e3)
+                             / (peaks["bf16_tflops"] * 1e12), 4)}
+
+    # ---- decode through the step function -------------------------------------------
+    def decode_run(b, steps, warmup):
+        ids = [f"d{i}" for i in range(b)]
+        for rid in ids:
+            engine.step([StepEntry(rid, prompt(ctx_len - 1), [])])
+        chosen = torch.zeros(b, dtype=torch.int32, device=dev)
+        entries = [StepEntry(rid, [0], [0]) for rid in ids]
+
+        def one():
+            logits = engine.step(entries, token_source=chosen)
+            ops.argmax_rows(logits, chosen)
+        # the first token of each request
+        chosen.copy_(torch.tensor([rng.randrange(vocab) for _ in range(b)], dtype=torch.int32))
+        for _ in range(warmup):
+            one()
+        torch.cuda.synchronize()
+        launches0 = ops.LAUNCHES[0]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0 = time.time()
+        e0.record()
+        for _ in range(steps):
+            one()
+        e1.record()
+        torch.cuda.synchronize()
+        windows.append((w0, time.time()))
+        ms = e0.elapsed_time(e1)
+        launches = ops.LAUNCHES[0] - launches0
+        tensor_core.check_status(dev)
+        first_ctx = ctx_len + warmup
+        mean_ctx = first_ctx + (steps - 1) / 2.0
+        for rid in ids:
+            engine.finish(rid)
+        return dict(tok_s=b * steps / (ms / 1e3), ms_per_step=ms / steps, launches=launches,
+                    mean_ctx=mean_ctx)
+
+    main = decode_run(batch, args.steps, args.warmup)
+    points = {}
+    for b in (1, 64):
+        r = decode_run(b, args.steps, args.warmup)
+        points[f"decode_b{b}"] = round(r["tok_s"], 1)
+        points[f"decode_b{b}_ms"] = round(r["ms_per_step"], 4)
+
+    weight_bytes = (nums["layers"] * nums["per_layer"] + nums["head"]) * 2
+    step_bytes = weight_bytes + batch * main["mean_ctx"] * nums["kv_token_bytes"]
+    achieved = step_bytes / (main["ms_per_step"] / 1e3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+                "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
+                "peaks": peaks["source"]}
+
+    # ---- end to end through the Python entry point -----------------------------------
+    prompts = [prompt(ctx_len) for _ in range(batch)]
+    llm.generate(prompts[:1], SamplingParams(max_tokens=2))          # warm the path
+    w0 = time.time()
+    outs = llm.generate(prompts, SamplingParams(max_tokens=args.steps + 1))
+    windows.append((w0, time.time()))
+    decode_steps = [s for s in llm.last_steps if s.prefill_tokens == 0 and s.decoded == batch]
+    wall = sum(s.wall_s for s in decode_steps)
+    e2e_tok_s = len(decode_steps) * batch / wall if wall > 0 else 0.0
+    assert all(len(o) == args.steps + 1 for o in outs)
+    h2d = 0
+    if decode_steps:
+        from crucible_b200.engine.context import StepLayout
+        h2d = StepLayout(batch, batch, batch, engine.table_strides).offsets()["_total"][1] * 4
+    e2e = {"value": round(e2e_tok_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": 4 * batch, "steps": len(decode_steps)}
+
+    clocks.stop()
+    line = {
+        "metric": "decode tok/s at batch 8 (120M shape, bf16, 2,048-token contexts)",
+        "value": round(main["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": "crucible-120m-shape", "layers": nums["layers"],
+                   "layers_of_shape": full_layers, "hidden": cfg.hidden_size,
+                   "q_heads": cfg.layers[0].mixer.n_heads,
+                   "kv_heads": cfg.layers[0].mixer.n_kv_heads,
+                   "head_dim": cfg.layers[0].mixer.head_dim,
+                   "intermediate": cfg.layers[0].feed_forward.intermediate,
+                   "vocab": cfg.vocab_size, "tied_head": cfg.tie_word_embeddings,
+                   "global_batch": batch, "seq_len": ctx_len, "new_tokens": args.steps,
+                   "kv_page_tokens": 16, "parallelism": "single-gpu",
+                   "l2": "inputs_exceed_l2", "weights": "random N(0,0.02) seed 0"},
+        "e2e": e2e, "gpu_launches": main["launches"], "prefill": prefill,
+        "roofline": roofline, "points": points, "clocks": clocks.summary(windows),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def main():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=256)
+    p.add_argument("--warmup", type=int, default=8)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=2048)
+    p.add_argument("--layers", type=int, default=0,
+                   help="fewer layers than the shape has (both numbers are reported)")
+    args = p.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+    if args.warmup < 3:
+        args.warmup = 3
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -153,3 +153,14 @@ class HostStep:
     @property
     def max_new_tokens(self) -> int:
         return max(self.new_tokens) if self.new_tokens else 0
+
+    @property
+    def context_bucket(self) -> int:
+        """The longest context of the step rounded up to 256 times a power of
+        two.  Launch shapes that depend on context length use this, so that a
+        captured step can be replayed for any context inside the bucket."""
+        need = max(1, -(-self.max_context_len // 256))
+        n = 1
+        while n < need:
+            n *= 2
+        return 256 * n

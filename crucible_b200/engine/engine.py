@@ -96,6 +96,10 @@ class Engine:
         self._meta_dev = None
         self._meta_host = None
         self._sampler = None
+        self._graphs = {}
+        self._graph_generation = 0
+        self._graph_failed = False
+        self._graph_error = None
 
     def _meta_buffers(self, n: int):
         if self._meta_dev is None or self._meta_dev.numel() < n:
@@ -146,10 +150,14 @@ class Engine:
 
     # -- the step ---------------------------------------------------------------
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry],
+             token_source: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs one packed batch.  Returns fp32 logits [wanted, vocab] on the
         device; the tensor is scratch of the engine and is overwritten by the
-        next step."""
+        next step.  `token_source`, if given, is a device int32 tensor whose
+        first rows replace the entries' token ids on the device (ids chosen by
+        the previous step need not visit the host; the entries' own ids are
+        then placeholders and are not validated against it)."""
         entries = list(entries)
         self._validate(entries)
         extended = []
@@ -165,7 +173,51 @@ class Engine:
                 self._shrink(e.request, len(e.tokens))
             raise
         ctx = self._make_context(entries)
+        if token_source is not None:
+            ctx.token_ids.copy_(token_source[:ctx.n_tokens])
+        if self.options.graph and not self._graph_failed and ctx.host.all_single_token:
+            return self._replay_or_capture(ctx)
         return self.model.forward(ctx)
+
+    # -- CUDA graphs for decode-only steps ----------------------------------------
+    #
+    # A step in which every request brings one token has a launch sequence that
+    # depends only on (rows, wanted rows, context bucket); the metadata it reads
+    # lies at fixed addresses and is uploaded before the replay, outside the
+    # graph (as `engine/src/gpu_model.rs:1348-1380`: graphs keyed by exact batch
+    # size, metadata H2D before the launch).  A capture that fails is remembered
+    # and the engine stays eager (`gpu_model.rs:3199-3222`).
+
+    def _replay_or_capture(self, ctx: StepContext) -> torch.Tensor:
+        from .. import ops
+        if self._graph_generation != self.scratch.generation:
+            self._graphs.clear()
+            self._graph_generation = self.scratch.generation
+        key = (ctx.n_tokens, ctx.n_logit_rows, ctx.host.context_bucket)
+        hit = self._graphs.get(key)
+        if hit is not None:
+            graph, logits, launches = hit
+            graph.replay()
+            ops.LAUNCHES[0] += launches
+            return logits
+        logits = self.model.forward(ctx)           # eager: also sizes the scratch buffers
+        if self._graph_generation != self.scratch.generation:
+            self._graphs.clear()
+            self._graph_generation = self.scratch.generation
+        try:
+            before = ops.LAUNCHES[0]
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                captured = self.model.forward(ctx)
+            launches = ops.LAUNCHES[0] - before
+            ops.LAUNCHES[0] = before
+            if self._graph_generation != self.scratch.generation:
+                raise RuntimeError("scratch buffers moved during capture")
+            self._graphs[key] = (graph, captured, launches)
+        except Exception as e:                      # stay eager from here on
+            self._graph_failed = True
+            self._graph_error = repr(e)
+        return logits
 
     def _shrink(self, request, n: int) -> None:
         r = self.cache._get(request)

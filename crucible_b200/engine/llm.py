@@ -7,6 +7,7 @@ it has them (`engine/src/main.rs:130-160`, `:476-497`): `max_batch`, `kv_pages`,
 """
 from __future__ import annotations
 
+import time
 from typing import List, Optional, Sequence, Union
 
 from ..sampling.params import SamplingParams
@@ -48,7 +49,9 @@ class LLM:
         self.last_steps = []
         done = {}
         while sched.has_work():
+            t0 = time.perf_counter()
             info = sched.step()
+            info.wall_s = time.perf_counter() - t0
             self.last_steps.append(info)
             if info.batch_tokens == 0 and info.admitted == 0 and info.finished == 0:
                 raise RuntimeError("generation made no progress")

@@ -105,6 +105,7 @@ class StepInfo:
     batch_tokens: int = 0
     free_pages: List[int] = field(default_factory=list)
     pending: int = 0
+    wall_s: float = 0.0           # host time of the iteration, filled in by the caller
 
 
 class Scheduler:

@@ -56,7 +56,11 @@ def _contig(t: torch.Tensor, what: str) -> None:
         raise KernelError(f"{what} must be contiguous")
 
 
+LAUNCHES = [0]      # kernels launched through this module (graph replays add their own)
+
+
 def _check(code: int, what: str) -> None:
+    LAUNCHES[0] += 1
     if code != 0:
         lib = build.load("elementwise")
         lib.cb_error_string.restype = ctypes.c_char_p

@@ -50,6 +50,11 @@ def check_status(device) -> None:
                            f"(status {code}); the step's results are not valid")
 
 
+def _count(n: int) -> None:
+    from . import LAUNCHES
+    LAUNCHES[0] += n
+
+
 def _stream():
     return _c_void_p(torch.cuda.current_stream().cuda_stream)
 
@@ -75,6 +80,7 @@ def _gemm(a, w, out, n, epi, bn) -> bool:
         return False
     if code != 0:
         raise RuntimeError(f"tensor-core matrix product failed to launch (CUDA error {code})")
+    _count(1)
     return True
 
 
@@ -108,17 +114,6 @@ def linear_swiglu(h, gate_up, out, tile=None) -> bool:
     return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn)
 
 
-def attention_chunks(max_context_len: int) -> int:
-    """Chunks of 256 keys the split form is launched over: the smallest power
-    of two that covers the longest context of the step (a launch shape only;
-    which chunks a row reads depends on that row alone)."""
-    need = max(1, -(-max_context_len // 256))
-    n = 1
-    while n < need:
-        n *= 2
-    return n
-
-
 def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx, cache,
                     binding) -> bool:
     """mma.sync attention over the paged cache.  Takes head sizes that are
@@ -134,7 +129,9 @@ def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx,
     host = ctx.host
     n_rep = n_heads // n_kv_heads
     split = host.max_new_tokens * n_rep <= 16
-    n_chunks = attention_chunks(host.max_context_len) if split else 0
+    # chunks of 256 keys the split form is launched over: a launch shape only;
+    # which chunks a row reads depends on that row alone
+    n_chunks = host.context_bucket // 256 if split else 0
     partial = None
     if split:
         floats = ctx.n_tokens * n_heads * n_chunks * (head_dim + 2)
@@ -153,4 +150,5 @@ def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx,
         return False
     if code != 0:
         raise RuntimeError(f"tensor-core attention failed to launch (CUDA error {code})")
+    _count(2 if split else 1)
     return True
