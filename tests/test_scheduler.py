@@ -1,0 +1,170 @@
+"""The scheduler's decisions, on the CPU with a fake executor."""
+from typing import List
+
+import pytest
+
+from crucible_b200.cache import CacheManager, GroupPolicy
+from crucible_b200.engine.scheduler import (Request, Scheduler, SchedulerError, SchedulerOptions)
+from crucible_b200.sampling import SamplingParams
+
+
+class FakeExecutor:
+    """Keeps a real cache manager; 'logits' are the list of (request, position)
+    of the wanted rows; the chosen token is a function of those."""
+    vocab_size = 1000
+    max_context = 512
+
+    def __init__(self, n_pages=16, page_tokens=16, max_requests=4):
+        self.cache = CacheManager([GroupPolicy(page_tokens)], [n_pages], max_requests)
+        self.steps: List[list] = []
+
+    def add_request(self, request, lifetime_tokens=None, max_step_tokens=None):
+        self.cache.add_request(request, lifetime_tokens, max_step_tokens)
+
+    def step(self, entries):
+        rows = []
+        self.steps.append([(e.request, len(e.tokens), list(e.want)) for e in entries])
+        for e in entries:
+            self.cache.extend(e.request, len(e.tokens))
+            start = self.cache.length(e.request) - len(e.tokens)
+            rows += [(e.request, start + w, e.tokens[w]) for w in e.want]
+        self.cache.check_invariants()
+        return rows
+
+    def sample(self, logits, rows):
+        assert len(logits) == len(rows)
+        return [(pos * 7 + tok) % self.vocab_size for (_, pos, tok) in logits]
+
+    def finish(self, request):
+        self.cache.remove_request(request)
+
+
+def greedy(n):
+    return SamplingParams(max_tokens=n)
+
+
+def test_prompts_are_cut_under_the_budget_and_decodes_ride_along():
+    ex = FakeExecutor(n_pages=64)
+    s = Scheduler(ex, SchedulerOptions(max_batch=4, prefill_token_budget=32))
+    s.submit(Request("a", list(range(50)), greedy(3)))
+    s.submit(Request("b", list(range(20)), greedy(2)))
+    i0 = s.step()
+    assert i0.admitted == 2 and ex.steps[0] == [("a", 32, [])]          # budget spent on a
+    s.step()
+    # a went to the back: b gets its 20 tokens first, then a gets the 12 left of the budget
+    assert ex.steps[1] == [("b", 20, [19]), ("a", 12, [])]
+    s.step()
+    # b decodes (1 token) beside a's last portion; the budget left is 31
+    assert ex.steps[2] == [("b", 1, [0]), ("a", 6, [5])]
+    done = s.run_to_completion()
+    by_id = {c.id: c for c in done}
+    assert len(by_id["a"].tokens) == 3 and len(by_id["b"].tokens) == 2
+    assert by_id["a"].finish_reason == "length"
+    assert ex.cache.free_pages(0) == 64 and ex.cache.slots.free_slots == 4
+    # positions used: prompt + max_tokens - 1
+    assert sum(n for step in ex.steps for (r, n, _) in step if r == "a") == 50 + 3 - 1
+
+
+def test_chunk_cap_and_request_limit():
+    ex = FakeExecutor(n_pages=64)
+    s = Scheduler(ex, SchedulerOptions(max_batch=4, prefill_token_budget=64,
+                                       prefill_chunk_tokens=10, max_prefill_requests=2))
+    for name in "abc":
+        s.submit(Request(name, list(range(25)), greedy(1)))
+    s.step()
+    assert ex.steps[0] == [("a", 10, []), ("b", 10, [])]               # two prompts per step
+    s.step()
+    assert ex.steps[1] == [("c", 10, []), ("a", 10, [])]               # round robin
+    s.run_to_completion()
+    assert ex.cache.free_pages(0) == 64
+
+
+def test_when_pages_run_out_the_request_waits_and_nobody_overtakes():
+    ex = FakeExecutor(n_pages=4, page_tokens=16)                        # 64 tokens in all
+    s = Scheduler(ex, SchedulerOptions(max_batch=4, prefill_token_budget=64))
+    s.submit(Request("big", list(range(40)), greedy(9)))                # 48 positions: 3 pages
+    s.submit(Request("next", list(range(20)), greedy(5)))               # 24 positions: 2 pages
+    s.submit(Request("small", [1, 2], greedy(2)))                       # 1 page: would fit now
+    info = s.step()
+    assert info.admitted == 1 and info.pending == 2                     # small did not overtake next
+    seen_waiting = 0
+    while any(l.request.id == "big" for l in s.active + list(s.prefilling)):
+        info = s.step()
+        ids = {r for r, _, _ in ex.steps[-1]}
+        if "next" not in ids:
+            seen_waiting += 1
+        assert ex.cache.reserved_pages(0) <= 4
+    assert seen_waiting >= 7                                            # it waited while big decoded
+    done = {c.id: c for c in s.run_to_completion()}
+    assert sorted(done) == ["next", "small"] or sorted(done) == ["big", "next", "small"]
+    assert ex.cache.free_pages(0) == 4 and ex.cache.reserved_pages(0) == 0
+
+
+def test_requests_that_can_never_run_are_refused_at_submit():
+    ex = FakeExecutor(n_pages=4, page_tokens=16)
+    s = Scheduler(ex)
+    with pytest.raises(SchedulerError, match="KV pages"):
+        s.submit(Request("x", list(range(60)), greedy(10)))             # 69 positions > 64
+    with pytest.raises(SchedulerError, match="cache positions"):
+        s.submit(Request("y", list(range(500)), greedy(20)))            # beyond the context
+    with pytest.raises(SchedulerError, match="positive"):
+        s.submit(Request("z", [], greedy(1)))
+    with pytest.raises(SchedulerError, match="vocabulary"):
+        s.submit(Request("v", [1, 1000], greedy(1)))
+    with pytest.raises(ValueError, match="temperature"):
+        s.submit(Request("t", [1], SamplingParams(temperature=float("nan"))))
+    s.submit(Request("ok", [1, 2, 3], greedy(1)))
+    with pytest.raises(SchedulerError, match="already queued"):
+        s.submit(Request("ok", [4], greedy(1)))
+    assert not ex.cache.live_requests()                                 # nothing owned pages yet
+
+
+def test_max_batch_bounds_the_residents_and_slots_are_reused():
+    ex = FakeExecutor(n_pages=64, max_requests=2)
+    s = Scheduler(ex, SchedulerOptions(max_batch=2, prefill_token_budget=64))
+    for i in range(5):
+        s.submit(Request(i, [1, 2, 3], greedy(2)))
+    most = 0
+    while s.has_work():
+        s.step()
+        most = max(most, len(s.active) + len(s.prefilling))
+    assert most == 2 and len(s.done) == 5
+    assert [c.id for c in s.done] == [0, 1, 2, 3, 4]
+
+
+def test_first_token_comes_from_the_last_prompt_row_and_eos_stops():
+    ex = FakeExecutor(n_pages=64)
+    s = Scheduler(ex)
+    s.submit(Request("a", [5, 6, 7], SamplingParams(max_tokens=50, eos_token_id=(2 * 7 + 7) % 1000)))
+    info = s.step()
+    assert ex.steps[0] == [("a", 3, [2])] and info.first_tokens == 1 and info.finished == 1
+    assert s.done[0].tokens == [21] and s.done[0].finish_reason == "eos"
+
+
+def test_greedy_requests_draw_nothing_and_sampled_ones_get_their_own_generator():
+    ex = FakeExecutor(n_pages=64)
+    seen = []
+    ex.sample = lambda logits, rows: [seen.append([(p.is_greedy, None if r is None else r.state)
+                                                   for p, r in rows]) or 1 for _ in rows][:len(rows)]
+    s = Scheduler(ex)
+    s.submit(Request("g", [1, 2], greedy(2)))
+    s.submit(Request("t", [1, 2], SamplingParams(max_tokens=2, temperature=0.8, seed=42)))
+    s.run_to_completion()
+    assert seen[0][0] == (True, None)
+    assert seen[0][1] == (False, 42 | 1)
+
+
+def test_cancel_gives_everything_back_in_every_state():
+    ex = FakeExecutor(n_pages=8)
+    s = Scheduler(ex, SchedulerOptions(max_batch=2, prefill_token_budget=16))
+    s.submit(Request("a", list(range(30)), greedy(4)))
+    s.submit(Request("b", list(range(10)), greedy(4)))
+    s.submit(Request("c", list(range(10)), greedy(4)))
+    s.step()
+    assert s.cancel("c") and s.cancel("a")                 # pending and prefilling
+    s.step(); s.step()
+    assert s.cancel("b") and not s.cancel("nobody")        # active
+    assert ex.cache.free_pages(0) == 8 and ex.cache.reserved_pages(0) == 0
+    assert {c.id: c.finish_reason for c in s.done} == {"a": "cancelled", "b": "cancelled",
+                                                        "c": "cancelled"}
+    assert not s.has_work()
