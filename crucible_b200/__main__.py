@@ -1,0 +1,5 @@
+import sys
+
+from .engine.cli import main
+
+sys.exit(main())

@@ -160,22 +160,26 @@ class Engine:
         then placeholders and are not validated against it)."""
         entries = list(entries)
         self._validate(entries)
-        extended = []
+        extended, added = [], []
         try:
             for e in entries:
                 if not self.cache.has(e.request):
                     self.add_request(e.request)
+                    added.append(e.request)
                 self.cache.extend(e.request, len(e.tokens))
                 extended.append(e)
         except Exception:
             # a step that cannot get its pages changes nothing
             for e in extended:
                 self._shrink(e.request, len(e.tokens))
+            for request in added:
+                self.cache.remove_request(request)
             raise
         ctx = self._make_context(entries)
         if token_source is not None:
             ctx.token_ids.copy_(token_source[:ctx.n_tokens])
-        if self.options.graph and not self._graph_failed and ctx.host.all_single_token:
+        if (self.options.graph and not self._graph_failed and ctx.host.all_single_token
+                and self.model.graph_safe):
             return self._replay_or_capture(ctx)
         return self.model.forward(ctx)
 

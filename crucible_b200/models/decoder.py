@@ -151,6 +151,10 @@ class DecoderModel:
         if self.config.tie_word_embeddings:
             self.head.tie(self.embedding.table)
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(part, "graph_safe", True) for _, part, _ in self._parts())
+
     # -- one step -------------------------------------------------------------
 
     def forward(self, ctx) -> torch.Tensor:

@@ -69,6 +69,12 @@ class LayerBinding:
 
 
 class Part:
+    # A part whose launches depend only on the step's shape and on device-side
+    # metadata can be replayed from a captured CUDA graph.  A part that reads
+    # per-step values on the host (other than the shape) sets this to False and
+    # the engine then runs every step eagerly.
+    graph_safe = True
+
     def tensors(self) -> List[TensorDecl]:
         return []
 
