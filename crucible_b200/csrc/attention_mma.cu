@@ -465,7 +465,9 @@ __global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p
     }
 }
 
-// Merges a row's chunks in ascending order.  One warp per (token, head).
+// Merges a row's chunks in ascending order.  One warp per (token, head): the
+// lanes first fetch the chunks' maxima and sums side by side, then every lane
+// sums its features over the chunks with the weights exp2(max_c - max).
 __global__ void attention_merge_kernel(const AttnParams p, const int* __restrict__ positions,
                                        int n_tokens) {
     const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -478,19 +480,32 @@ __global__ void attention_merge_kernel(const AttnParams p, const int* __restrict
     const int c_first = lo / SPLIT_KEYS, c_last = pos / SPLIT_KEYS;
     const float* base = p.partial + ((size_t)tok * p.n_heads + head) * p.n_chunks * mp;
     float m = -INFINITY;
-    for (int c = c_first; c <= c_last; ++c) m = fmaxf(m, base[(size_t)c * mp + p.head_dim]);
+    for (int c = c_first + lane; c <= c_last; c += 32)
+        m = fmaxf(m, base[(size_t)c * mp + p.head_dim]);
+    m = cb_warp_max(m);
     float l = 0.f;
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (int c = c_first; c <= c_last; ++c) {
-        const float mc = base[(size_t)c * mp + p.head_dim];
-        const float w = mc == -INFINITY ? 0.f : exp2f(mc - m);
-        l += base[(size_t)c * mp + p.head_dim + 1] * w;
+    for (int c0 = c_first; c0 <= c_last; c0 += 32) {
+        // this lane's chunk of the group of 32: its weight and weighted sum
+        const int mine = c0 + lane;
+        float w_mine = 0.f, l_mine = 0.f;
+        if (mine <= c_last) {
+            const float mc = base[(size_t)mine * mp + p.head_dim];
+            w_mine = mc == -INFINITY ? 0.f : exp2f(mc - m);
+            l_mine = base[(size_t)mine * mp + p.head_dim + 1] * w_mine;
+        }
+        const int n_here = min(32, c_last - c0 + 1);
+        for (int j = 0; j < n_here; ++j) {               // ascending chunks
+            const float w = __shfl_sync(0xffffffffu, w_mine, j);
+            l += __shfl_sync(0xffffffffu, l_mine, j);
+            const float* src = base + (size_t)(c0 + j) * mp;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int f = lane + 32 * i;
-            if (f < p.head_dim) acc[i] += base[(size_t)c * mp + f] * w;
+            for (int i = 0; i < 8; ++i) {
+                const int f = lane + 32 * i;
+                if (f < p.head_dim) acc[i] = fmaf(src[f], w, acc[i]);
+            }
         }
     }
     const float inv = l > 0.f ? 1.0f / l : 0.f;

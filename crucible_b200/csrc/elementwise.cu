@@ -53,16 +53,65 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
         dst[i] = cb_from_float<T>(row[i] * r * gain[i]);
 }
 
+// The same for widths that are multiples of 4: float4 loads, the row kept in
+// registers between the two passes (up to 4 vectors per thread).
+template <typename T>
+__global__ void rmsnorm_vec4_kernel(const float* __restrict__ x, const float* __restrict__ gain,
+                                    T* __restrict__ out, int width, float eps) {
+    __shared__ float scratch[32];
+    const int n4 = width >> 2;
+    const float4* row = reinterpret_cast<const float4*>(x + (size_t)blockIdx.x * width);
+    const float4* g4 = reinterpret_cast<const float4*>(gain);
+    float4 v[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        v[j] = i < n4 ? row[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss = fmaf(v[j].x, v[j].x, ss);
+        ss = fmaf(v[j].y, v[j].y, ss);
+        ss = fmaf(v[j].z, v[j].z, ss);
+        ss = fmaf(v[j].w, v[j].w, ss);
+    }
+    const float total = cb_block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(total / (float)width + eps);
+    T* dst = out + (size_t)blockIdx.x * width;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < n4) {
+            const float4 g = g4[i];
+            dst[4 * i + 0] = cb_from_float<T>(v[j].x * r * g.x);
+            dst[4 * i + 1] = cb_from_float<T>(v[j].y * r * g.y);
+            dst[4 * i + 2] = cb_from_float<T>(v[j].z * r * g.z);
+            dst[4 * i + 3] = cb_from_float<T>(v[j].w * r * g.w);
+        }
+    }
+}
+
 CB_EXPORT int cb_rmsnorm(const float* x, const float* gain, void* out, int out_dtype,
                          int n_rows, int width, float eps, void* stream) {
     if (n_rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool vec = (width & 3) == 0 && width <= 4 * 4 * 1024 && ((uintptr_t)x & 15) == 0 &&
+                     ((uintptr_t)gain & 15) == 0;
+    if (vec) {
+        int threads = ((width >> 2) + 31) / 32 * 32;
+        if (threads > 1024) threads = ((width >> 2) + 4 * 32 - 1) / (4 * 32) * 32;
+        if (threads < 32) threads = 32;
+        if (out_dtype == CB_F32)
+            rmsnorm_vec4_kernel<float><<<n_rows, threads, 0, s>>>(x, gain, (float*)out, width, eps);
+        else
+            rmsnorm_vec4_kernel<__nv_bfloat16><<<n_rows, threads, 0, s>>>(
+                x, gain, (__nv_bfloat16*)out, width, eps);
+        return cb_last_error();
+    }
     const int threads = width >= 1024 ? 256 : 128;
     if (out_dtype == CB_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, (cudaStream_t)stream>>>(
-            x, gain, (float*)out, width, eps);
+        rmsnorm_kernel<float><<<n_rows, threads, 0, s>>>(x, gain, (float*)out, width, eps);
     else
-        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, (cudaStream_t)stream>>>(
-            x, gain, (__nv_bfloat16*)out, width, eps);
+        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, s>>>(x, gain, (__nv_bfloat16*)out,
+                                                                 width, eps);
     return cb_last_error();
 }
 
@@ -132,38 +181,42 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, const float* __restri
                                       int n_heads, int n_kv_heads, int head_dim,
                                       int page_tokens, int write_cache) {
     const int t = blockIdx.x;
-    const int h = blockIdx.y;
     const int row_width = (n_heads + 2 * n_kv_heads) * head_dim;
-    T* src = qkv + (size_t)t * row_width + (size_t)h * head_dim;
+    T* row = qkv + (size_t)t * row_width;
     const int pos = positions[t];
-    const bool is_q = h < n_heads;
-    const bool is_k = !is_q && h < n_heads + n_kv_heads;
-    T* dst = nullptr;
-    if (!is_q) {
-        if (!write_cache) return;
+    const int half = rotary_dim >> 1;
+    const int pass = head_dim - rotary_dim;          // features that are not rotated
+    size_t cache_base = 0;
+    if (write_cache) {
         const int r = row_request[t];
         const int page = block_table[(size_t)r * table_stride + pos / page_tokens];
-        const int slot = pos % page_tokens;
-        const int kvh = is_k ? h - n_heads : h - n_heads - n_kv_heads;
-        T* base = is_k ? k_cache : v_cache;
-        dst = base + (((size_t)page * page_tokens + slot) * n_kv_heads + kvh) * head_dim;
+        cache_base = ((size_t)page * page_tokens + pos % page_tokens) * n_kv_heads * head_dim;
     }
-    if (is_q || is_k) {
-        const int half = rotary_dim / 2;
-        T* out = is_q ? src : dst;
-        for (int i = threadIdx.x; i < half; i += blockDim.x) {
-            const float c = cos_t[(size_t)pos * half + i];
-            const float s = sin_t[(size_t)pos * half + i];
-            const float x1 = cb_to_float(src[i]);
-            const float x2 = cb_to_float(src[i + half]);
-            out[i] = cb_from_float<T>(x1 * c - x2 * s);
-            out[i + half] = cb_from_float<T>(x1 * s + x2 * c);
+    const float* c_row = cos_t + (size_t)pos * half;
+    const float* s_row = sin_t + (size_t)pos * half;
+    // rotated pairs of q and k heads
+    const int n_rot_heads = n_heads + (write_cache ? n_kv_heads : 0);
+    for (int i = threadIdx.x; i < n_rot_heads * half; i += blockDim.x) {
+        const int h = i / half, j = i - h * half;
+        T* src = row + (size_t)h * head_dim;
+        const float c = c_row[j], s = s_row[j];
+        const float x1 = cb_to_float(src[j]);
+        const float x2 = cb_to_float(src[j + half]);
+        T* dst = h < n_heads ? src : k_cache + cache_base + (size_t)(h - n_heads) * head_dim;
+        dst[j] = cb_from_float<T>(x1 * c - x2 * s);
+        dst[j + half] = cb_from_float<T>(x1 * s + x2 * c);
+    }
+    if (!write_cache) return;
+    // unrotated tail of the k heads, and the v heads
+    if (pass > 0) {
+        for (int i = threadIdx.x; i < n_kv_heads * pass; i += blockDim.x) {
+            const int h = i / pass, j = rotary_dim + (i - h * pass);
+            k_cache[cache_base + (size_t)h * head_dim + j] = row[(size_t)(n_heads + h) * head_dim + j];
         }
-        if (is_k)
-            for (int i = rotary_dim + threadIdx.x; i < head_dim; i += blockDim.x) out[i] = src[i];
-    } else {
-        for (int i = threadIdx.x; i < head_dim; i += blockDim.x) dst[i] = src[i];
     }
+    const T* v_src = row + (size_t)(n_heads + n_kv_heads) * head_dim;
+    for (int i = threadIdx.x; i < n_kv_heads * head_dim; i += blockDim.x)
+        v_cache[cache_base + i] = v_src[i];
 }
 
 CB_EXPORT int cb_rope_kv_append(void* qkv, int dtype, const float* cos_t, const float* sin_t,
@@ -173,15 +226,17 @@ CB_EXPORT int cb_rope_kv_append(void* qkv, int dtype, const float* cos_t, const 
                                 int head_dim, int page_tokens, int write_cache, void* stream) {
     if (n_rows <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return CB_ERR_UNSUPPORTED;
-    dim3 grid(n_rows, n_heads + 2 * n_kv_heads);
-    const int threads = head_dim >= 128 ? 64 : 32;
+    const int work = (n_heads + n_kv_heads) * (rotary_dim / 2);
+    int threads = (work + 31) / 32 * 32;
+    if (threads > 512) threads = 512;
+    if (threads < 64) threads = 64;
     if (dtype == CB_F32)
-        rope_kv_append_kernel<float><<<grid, threads, 0, (cudaStream_t)stream>>>(
+        rope_kv_append_kernel<float><<<n_rows, threads, 0, (cudaStream_t)stream>>>(
             (float*)qkv, cos_t, sin_t, rotary_dim, positions, row_request, block_table,
             table_stride, (float*)k_cache, (float*)v_cache, n_heads, n_kv_heads, head_dim,
             page_tokens, write_cache);
     else
-        rope_kv_append_kernel<__nv_bfloat16><<<grid, threads, 0, (cudaStream_t)stream>>>(
+        rope_kv_append_kernel<__nv_bfloat16><<<n_rows, threads, 0, (cudaStream_t)stream>>>(
             (__nv_bfloat16*)qkv, cos_t, sin_t, rotary_dim, positions, row_request, block_table,
             table_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_heads, n_kv_heads,
             head_dim, page_tokens, write_cache);

@@ -172,14 +172,79 @@ argmax_rows_kernel(const float* __restrict__ logits, int vocab, int* __restrict_
     block_argmax(logits + (size_t)blockIdx.x * vocab, vocab, out_ids + blockIdx.x, s_val, s_idx);
 }
 
+// Two-stage argmax for wide rows: stage one reduces a slice of the row per
+// block and writes (value, index) to scratch; stage two reduces the slices.
+// The winner is the same as the one-block kernel's: highest value, lowest
+// index among equals, NaN never.
+constexpr int ARGMAX_SLICES = 32;
+
+__global__ void __launch_bounds__(256)
+argmax_slices_kernel(const float* __restrict__ logits, int vocab, float* __restrict__ part_val,
+                     int* __restrict__ part_idx) {
+    __shared__ float s_val[32];
+    __shared__ int s_idx[32];
+    const int row = blockIdx.y, slice = blockIdx.x;
+    const int per = (vocab + ARGMAX_SLICES - 1) / ARGMAX_SLICES;
+    const int lo = slice * per, hi = min(vocab, lo + per);
+    const float* r = logits + (size_t)row * vocab;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float x = r[i];
+        if (x > bv || (x == bv && i < bi)) { bv = x; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { s_val[warp] = bv; s_idx[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (s_val[w] > bv || (s_val[w] == bv && s_idx[w] < bi)) { bv = s_val[w]; bi = s_idx[w]; }
+        part_val[row * ARGMAX_SLICES + slice] = bv;
+        part_idx[row * ARGMAX_SLICES + slice] = bi;
+    }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ part_val,
+                                    const int* __restrict__ part_idx, int* __restrict__ out_ids) {
+    const int row = blockIdx.x, lane = threadIdx.x;
+    float bv = part_val[row * ARGMAX_SLICES + lane];
+    int bi = part_idx[row * ARGMAX_SLICES + lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) out_ids[row] = bi == 0x7fffffff ? 0 : bi;
+}
+
 }  // namespace
 
+// scratch: n_rows * 32 floats followed by n_rows * 32 ints (cb_argmax_scratch_bytes),
+// or null: then one block per row does the whole row.
 CB_EXPORT int cb_argmax_rows(const float* logits, int n_rows, int vocab, int* out_ids,
-                             void* stream) {
+                             void* scratch, void* stream) {
     if (n_rows <= 0) return 0;
-    argmax_rows_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>(logits, vocab, out_ids);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (scratch == nullptr || vocab < 4096) {
+        argmax_rows_kernel<<<n_rows, 256, 0, s>>>(logits, vocab, out_ids);
+        return cb_last_error();
+    }
+    float* part_val = (float*)scratch;
+    int* part_idx = (int*)(part_val + (size_t)n_rows * ARGMAX_SLICES);
+    argmax_slices_kernel<<<dim3(ARGMAX_SLICES, n_rows), 256, 0, s>>>(logits, vocab, part_val,
+                                                                     part_idx);
+    argmax_final_kernel<<<n_rows, 32, 0, s>>>(part_val, part_idx, out_ids);
     return cb_last_error();
 }
+
+CB_EXPORT long cb_argmax_scratch_bytes(int n_rows) { return (long)n_rows * ARGMAX_SLICES * 8; }
 
 // temperature[row] <= 0: greedy.  max_top_k is the largest k among the rows;
 // the launcher refuses k above the kernel's candidate capacity.

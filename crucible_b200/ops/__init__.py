@@ -56,6 +56,7 @@ def _contig(t: torch.Tensor, what: str) -> None:
         raise KernelError(f"{what} must be contiguous")
 
 
+_scratch = {}       # per-device scratch of kernels that need some beyond inputs and outputs
 LAUNCHES = [0]      # kernels launched through this module (graph replays add their own)
 
 
@@ -221,8 +222,14 @@ def argmax_rows(logits: torch.Tensor, out_ids: torch.Tensor) -> None:
         raise KernelError("argmax_rows takes float32 logits and int32 output")
     _contig(logits, "logits")
     lib = build.load("sampling")
-    _check(lib.cb_argmax_rows(_ptr(logits), _c_int(logits.shape[0]), _c_int(logits.shape[1]),
-                              _ptr(out_ids), _stream()), "argmax_rows")
+    n = logits.shape[0]
+    key = (logits.device.index, "argmax")
+    scratch = _scratch.get(key)
+    if scratch is None or scratch.numel() < n * 64:
+        scratch = torch.empty(max(n, 64) * 64, dtype=torch.int32, device=logits.device)
+        _scratch[key] = scratch
+    _check(lib.cb_argmax_rows(_ptr(logits), _c_int(n), _c_int(logits.shape[1]),
+                              _ptr(out_ids), _ptr(scratch), _stream()), "argmax_rows")
 
 
 def max_device_top_k() -> int:

@@ -64,7 +64,7 @@ def _tile_width(m: int, n_cols: int) -> int:
     ones give more blocks when the problem has few tiles."""
     m_tiles = -(-m // 128)
     for bn in (256, 128):
-        if m_tiles * -(-n_cols // bn) >= 120:
+        if m_tiles * -(-n_cols // bn) >= 90:       # enough blocks for most of the 148 SMs
             return bn
     return 64
 

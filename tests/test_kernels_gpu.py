@@ -207,12 +207,14 @@ def _paged_case(dtype, n_heads, n_kv, hd, page_tokens, requests, seed, window=No
         if key not in scratch:
             scratch[key] = torch.empty(*shape, dtype=dt, device=DEV)
         return scratch[key]
+    from crucible_b200.engine.context import HostStep
     ctx = SimpleNamespace(
         positions=dev(positions), row_request=dev(row_request), req_row_start=dev(row_start),
         req_first_pos=dev(first_pos), n_tokens=t, n_requests=len(requests),
         block_table=lambda group: table_dev, scratch=get_scratch,
-        host=SimpleNamespace(max_new_tokens=max(n for _, n in requests),
-                             max_context_len=max(c + n for c, n in requests)))
+        host=HostStep(list(range(len(requests))), [n for _, n in requests],
+                      [c for c, _ in requests], [c + n for c, n in requests],
+                      [0] * len(requests)))
     binding = SimpleNamespace(group=0, slot=0, write=True)
     return qkv.to(DEV), ctx, cache, binding, torch.cat(refs).reshape(t, n_heads * hd)
 
