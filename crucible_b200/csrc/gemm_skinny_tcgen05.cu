@@ -1,0 +1,327 @@
+// C[M,N] = A[M,K] . W[N,K]^T for few rows (M <= 64: decoded tokens), bfloat16 on
+// tcgen05 with the operands swapped: 128 rows of W are the M side of the MMA
+// and the (zero-padded) rows of A are its N side (16, 32 or 64), so no tensor
+// work is spent on padding 128 activation rows.  Such a product only streams
+// W once, so what matters is how many blocks pull on memory at a time: the K
+// range is split over `splits` blocks per 128-row tile of W.  Every block
+// writes its partial tile to scratch; the block that arrives last at the tile's
+// counter (an atomic, no block ever waits for another) sums the partials in
+// ascending split order -- so the result does not depend on which block was
+// last -- and applies the epilogue:
+//   STORE_BF16, STORE_F32, ACCUM_F32 (fp32 residual add), SWIGLU_BF16 (the tile
+//   holds 64 gate rows and the 64 matching up rows of W = [Wg; Wu]).
+// With splits == 1 nothing goes through scratch.
+//
+// Scratch: floats [n_tiles][splits][MT][128] and ints [n_tiles] that are zero
+// before the launch and zero again after it.
+// Sizes: any N, M <= 64; K and the row strides multiples of 8, bases 16-byte
+// aligned (TMA); otherwise refused.
+// Reference counterpart: the batched GEMV family `gemv_batch_i8_b*`
+// (engine/kernels/kernels.cu:1598-1607): read W once for all rows.
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace {
+
+constexpr int WM = 128;                // rows of W per block
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+
+enum Epilogue { STORE_BF16 = 0, STORE_F32 = 1, ACCUM_F32 = 2, SWIGLU_BF16 = 3 };
+
+template <int MT>
+struct SkinnyStorage {
+    alignas(1024) uint8_t w[STAGES][WM * BK * 2];
+    alignas(1024) uint8_t a[STAGES][MT * BK * 2];
+    alignas(8) uint64_t full_bar[STAGES];
+    uint64_t empty_bar[STAGES];
+    uint64_t tmem_full_bar;
+    uint32_t tmem_base;
+    int abort_flag;
+    int is_last;
+};
+
+template <int MT>
+__device__ __forceinline__ void load_acc(uint32_t taddr, float (&v)[MT]) {
+    if constexpr (MT == 16) {
+        uint32_t r[16];
+        tc::tmem_ld_32x16(taddr, r);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+    } else {
+#pragma unroll
+        for (int c = 0; c < MT; c += 32) {
+            uint32_t r[32];
+            tc::tmem_ld_32x32(taddr + c, r);
+            tc::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[c + i] = __uint_as_float(r[i]);
+        }
+    }
+}
+
+template <int MT, int EPI>
+__global__ void __launch_bounds__(192)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
+                   const __grid_constant__ CUtensorMap map_a, void* __restrict__ c_ptr, int M,
+                   int N, int K, int ldc, int inter, int splits, float* __restrict__ partial,
+                   int* __restrict__ counters, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    using Storage = SkinnyStorage<MT>;
+    Storage& s = *reinterpret_cast<Storage*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x, split = blockIdx.y;
+    const int k_blocks = (K + BK - 1) / BK;
+    const int per = (k_blocks + splits - 1) / splits;
+    const int kb0 = split * per;
+    const int kb1 = min(k_blocks, kb0 + per);
+    const int n_kb = max(0, kb1 - kb0);
+    volatile int* abort_flag = &s.abort_flag;
+    constexpr uint32_t TMEM_COLS = MT < 32 ? 32 : MT;
+    constexpr uint32_t STAGE_BYTES = (WM + MT) * BK * 2;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) {
+            tc::mbar_init(&s.full_bar[i], 1);
+            tc::mbar_init(&s.empty_bar[i], 1);
+        }
+        tc::mbar_init(&s.tmem_full_bar, 1);
+        s.abort_flag = 0;
+        s.is_last = 0;
+        tc::fence_barrier_init();
+        tc::prefetch_tensormap(&map_w);
+        tc::prefetch_tensormap(&map_a);
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(&s.tmem_base, TMEM_COLS);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem_acc = s.tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int armed = 0;
+            for (int i = 0; i < n_kb; ++i) {
+                const int st = i % STAGES;
+                const uint32_t round = i / STAGES;
+                if (round > 0 && !tc::mbar_wait(&s.empty_bar[st], (round - 1) & 1, abort_flag)) {
+                    tc::give_up(abort_flag, status, tc::ST_PRODUCER_TIMEOUT);
+                    break;
+                }
+                const int kx = (kb0 + i) * BK;
+                tc::mbar_expect_tx(&s.full_bar[st], STAGE_BYTES);
+                if (EPI == SWIGLU_BF16) {
+                    tc::tma_load_2d(s.w[st], &map_w, &s.full_bar[st], kx, tile * (WM / 2));
+                    tc::tma_load_2d(s.w[st] + (WM / 2) * BK * 2, &map_w, &s.full_bar[st], kx,
+                                    inter + tile * (WM / 2));
+                } else {
+                    tc::tma_load_2d(s.w[st], &map_w, &s.full_bar[st], kx, tile * WM);
+                }
+                tc::tma_load_2d(s.a[st], &map_a, &s.full_bar[st], kx, 0);
+                armed = i + 1;
+            }
+            if (*abort_flag) {
+                const int first = armed > STAGES ? armed - STAGES : 0;
+                for (int i = first; i < armed; ++i)
+                    for (uint32_t t = 0; t < tc::WAIT_LIMIT; ++t)
+                        if (tc::mbar_try_wait(&s.full_bar[i % STAGES], (i / STAGES) & 1)) break;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc::instr_desc_bf16(WM, MT);
+            bool ok = true;
+            for (int i = 0; i < n_kb; ++i) {
+                const int st = i % STAGES;
+                if (!tc::mbar_wait(&s.full_bar[st], (i / STAGES) & 1, abort_flag)) {
+                    tc::give_up(abort_flag, status, tc::ST_MMA_TIMEOUT);
+                    ok = false;
+                    break;
+                }
+                tc::tc_fence_after_sync();
+                const uint64_t w_desc = tc::smem_desc_sw128(tc::smem_u32(s.w[st]));
+                const uint64_t a_desc = tc::smem_desc_sw128(tc::smem_u32(s.a[st]));
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    tc::umma_bf16(tmem_acc, w_desc + 2 * k, a_desc + 2 * k, idesc,
+                                  (i > 0 || k > 0) ? 1u : 0u);
+                tc::umma_commit(&s.empty_bar[st]);
+            }
+            if (ok && n_kb > 0) tc::umma_commit(&s.tmem_full_bar);
+        }
+    }
+
+    // ---- epilogue: warps 2..5 own the four lane quarters of the accumulator --------
+    const bool epi_warp = warp >= 2;
+    const int quarter = warp & 3;
+    const int w_row = quarter * 32 + lane;              // row of the W tile = accumulator lane
+    float acc[MT];
+#pragma unroll
+    for (int i = 0; i < MT; ++i) acc[i] = 0.f;
+    bool ok = true;
+    if (epi_warp && n_kb > 0) {
+        ok = tc::mbar_wait(&s.tmem_full_bar, 0, abort_flag);
+        if (!ok && !*abort_flag) tc::give_up(abort_flag, status, tc::ST_EPILOGUE_TIMEOUT);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tc::tc_fence_after_sync();
+            load_acc<MT>(tmem_acc + ((uint32_t)(quarter * 32) << 16), acc);
+        }
+    }
+    if (splits > 1) {
+        // every block leaves its partial; the last to arrive sums them all
+        float* mine = partial + ((size_t)tile * splits + split) * MT * WM;
+        if (epi_warp) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+                if (m < M) mine[m * WM + w_row] = acc[m];
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const int prev = atomicAdd(&counters[tile], 1);
+            s.is_last = prev == splits - 1;
+        }
+        __syncthreads();
+        if (s.is_last && epi_warp) {
+            __threadfence();
+            const float* base = partial + (size_t)tile * splits * MT * WM;
+#pragma unroll
+            for (int m = 0; m < MT; ++m) acc[m] = 0.f;
+            for (int sp = 0; sp < splits; ++sp) {           // ascending: order-independent result
+                const float* src = base + (size_t)sp * MT * WM + w_row;
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+                    if (m < M) acc[m] += __ldcg(src + m * WM);
+            }
+        }
+        if (s.is_last && threadIdx.x == 0) counters[tile] = 0;    // ready for the next launch
+    }
+    const bool writer = (splits == 1 || s.is_last) && ok && !*abort_flag;
+    if (EPI == SWIGLU_BF16) {
+        // lanes 0..63 of the tile are gate rows, 64..127 the matching up rows
+        float* xch = reinterpret_cast<float*>(s.w[0]);         // [64][MT], the stages are idle now
+        __syncthreads();
+        if (writer && epi_warp && w_row >= WM / 2) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m) xch[(w_row - WM / 2) * MT + m] = acc[m];
+        }
+        __syncthreads();
+        if (writer && epi_warp && w_row < WM / 2) {
+            const int col = tile * (WM / 2) + w_row;
+            if (col < inter) {
+                __nv_bfloat16* C = (__nv_bfloat16*)c_ptr;
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    if (m < M) {
+                        const float g = acc[m], u = xch[w_row * MT + m];
+                        C[(size_t)m * ldc + col] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
+                    }
+                }
+            }
+        }
+    } else if (writer && epi_warp) {
+        const int col = tile * WM + w_row;
+        if (col < N) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                if (m < M) {
+                    if (EPI == STORE_BF16) {
+                        ((__nv_bfloat16*)c_ptr)[(size_t)m * ldc + col] = __float2bfloat16_rn(acc[m]);
+                    } else {
+                        float* dst = (float*)c_ptr + (size_t)m * ldc + col;
+                        *dst = EPI == ACCUM_F32 ? *dst + acc[m] : acc[m];
+                    }
+                }
+            }
+        }
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::tc_fence_after_sync();
+        tc::tmem_dealloc(tmem_acc, TMEM_COLS);
+    }
+}
+
+template <int MT, int EPI>
+int launch(const CUtensorMap& mw, const CUtensorMap& ma, void* C, int M, int N, int K, int ldc,
+           int inter, int n_tiles, int splits, float* partial, int* counters, int* status,
+           cudaStream_t stream) {
+    const int smem = (int)sizeof(SkinnyStorage<MT>) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, EPI>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    gemm_skinny_kernel<MT, EPI><<<dim3(n_tiles, splits), 192, smem, stream>>>(
+        mw, ma, C, M, N, K, ldc, inter, splits, partial, counters, status);
+    return cb_last_error();
+}
+
+template <int MT>
+int launch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, void* C, int M, int N, int K,
+               int ldc, int inter, int n_tiles, int splits, float* partial, int* counters,
+               int* status, cudaStream_t s) {
+    switch (epi) {
+        case STORE_BF16: return launch<MT, STORE_BF16>(mw, ma, C, M, N, K, ldc, inter, n_tiles, splits, partial, counters, status, s);
+        case STORE_F32: return launch<MT, STORE_F32>(mw, ma, C, M, N, K, ldc, inter, n_tiles, splits, partial, counters, status, s);
+        case ACCUM_F32: return launch<MT, ACCUM_F32>(mw, ma, C, M, N, K, ldc, inter, n_tiles, splits, partial, counters, status, s);
+        case SWIGLU_BF16: return launch<MT, SWIGLU_BF16>(mw, ma, C, M, N, K, ldc, inter, n_tiles, splits, partial, counters, status, s);
+    }
+    return CB_ERR_UNSUPPORTED;
+}
+
+inline int padded_rows(int m) { return m <= 16 ? 16 : (m <= 32 ? 32 : 64); }
+
+}  // namespace
+
+// Tiles of 128 rows of W for this product (for SWIGLU_BF16, N = inter and W has 2N rows).
+CB_EXPORT int cb_gemm_skinny_tiles(int N, int epi) {
+    return epi == SWIGLU_BF16 ? (N + WM / 2 - 1) / (WM / 2) : (N + WM - 1) / WM;
+}
+
+// Bytes of scratch for partial tiles (the counters, one int per tile, are separate).
+CB_EXPORT long cb_gemm_skinny_partial_bytes(int M, int N, int epi, int splits) {
+    if (splits <= 1) return 0;
+    return (long)cb_gemm_skinny_tiles(N, epi) * splits * padded_rows(M) * WM * 4;
+}
+
+CB_EXPORT int cb_gemm_skinny(const void* A, const void* W, void* C, int M, int N, int K, int lda,
+                             int ldw, int ldc, int epi, int splits, float* partial, int* counters,
+                             int* status, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 64 || K <= 0 || (K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) ||
+        ((uintptr_t)W & 15))
+        return CB_ERR_UNSUPPORTED;
+    const int k_blocks = (K + BK - 1) / BK;
+    if (splits < 1) splits = 1;
+    if (splits > k_blocks) splits = k_blocks;
+    // no split may be empty: the last block must find every partial written
+    while (splits > 1 && (splits - 1) * ((k_blocks + splits - 1) / splits) >= k_blocks) --splits;
+    if (splits > 1 && (partial == nullptr || counters == nullptr)) return CB_ERR_UNSUPPORTED;
+    const int mt = padded_rows(M);
+    const int w_rows = epi == SWIGLU_BF16 ? 2 * N : N;
+    const int box_rows = epi == SWIGLU_BF16 ? WM / 2 : WM;
+    CUtensorMap mw, ma;
+    if (!tc::make_map_2d(&mw, W, (uint64_t)w_rows, (uint64_t)K, (uint64_t)ldw, box_rows))
+        return CB_ERR_UNSUPPORTED;
+    if (!tc::make_map_2d(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, mt)) return CB_ERR_UNSUPPORTED;
+    const int inter = epi == SWIGLU_BF16 ? N : 0;
+    const int n_tiles = cb_gemm_skinny_tiles(N, epi);
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (mt) {
+        case 16: return launch_epi<16>(epi, mw, ma, C, M, N, K, ldc, inter, n_tiles, splits, partial, counters, status, s);
+        case 32: return launch_epi<32>(epi, mw, ma, C, M, N, K, ldc, inter, n_tiles, splits, partial, counters, status, s);
+        case 64: return launch_epi<64>(epi, mw, ma, C, M, N, K, ldc, inter, n_tiles, splits, partial, counters, status, s);
+    }
+    return CB_ERR_UNSUPPORTED;
+}

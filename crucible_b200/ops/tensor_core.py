@@ -17,6 +17,7 @@ from . import build
 
 build.register_module("gemm_tcgen05", ["common.cuh", "tc_common.cuh"])
 build.register_module("attention_mma", ["common.cuh"])
+build.register_module("gemm_skinny_tcgen05", ["common.cuh", "tc_common.cuh"])
 
 _c_int, _c_void_p = ctypes.c_int, ctypes.c_void_p
 STORE_BF16, STORE_F32, ACCUM_F32, SWIGLU_BF16 = 0, 1, 2, 3
@@ -84,6 +85,62 @@ def _gemm(a, w, out, n, epi, bn) -> bool:
     return True
 
 
+_buffers = {}        # (device, name) -> tensor; grown by doubling, old ones kept alive because
+_retired = []        # captured CUDA graphs may still hold their addresses
+
+
+def _buffer(device, name: str, numel: int, dtype, zero: bool = False) -> torch.Tensor:
+    key = (torch.device(device).index or 0, name)
+    t = _buffers.get(key)
+    if t is None or t.numel() < numel:
+        if t is not None:
+            _retired.append(t)
+        make = torch.zeros if zero else torch.empty
+        t = make(max(2 * numel, 1024), dtype=dtype, device=device)
+        _buffers[key] = t
+    return t
+
+
+def skinny_splits(m: int, n_tiles: int, k: int) -> int:
+    """Blocks along K per 128-row tile of W: enough blocks to cover the SMs, but
+    never so many that the partial tiles outweigh the weights they stand for."""
+    k_blocks = -(-k // 64)
+    want = -(-160 // n_tiles)
+    cap = max(1, k // (4 * m))
+    return max(1, min(want, k_blocks, cap))
+
+
+def _gemm_skinny(a, w, out, n, epi, splits=None) -> bool:
+    lib = build.load("gemm_skinny_tcgen05")
+    m, k = a.shape
+    n_tiles = int(lib.cb_gemm_skinny_tiles(_c_int(n), _c_int(epi)))
+    if splits is None:
+        splits = skinny_splits(m, n_tiles, k)
+    partial = counters = None
+    if splits > 1:
+        lib.cb_gemm_skinny_partial_bytes.restype = ctypes.c_long
+        nbytes = int(lib.cb_gemm_skinny_partial_bytes(_c_int(m), _c_int(n), _c_int(epi),
+                                                      _c_int(splits)))
+        partial = _buffer(a.device, "skinny.partial", nbytes // 4, torch.float32)
+        counters = _buffer(a.device, "skinny.counters", n_tiles, torch.int32, zero=True)
+    code = lib.cb_gemm_skinny(
+        _c_void_p(a.data_ptr()), _c_void_p(w.data_ptr()), _c_void_p(out.data_ptr()),
+        _c_int(m), _c_int(n), _c_int(k), _c_int(a.stride(0)), _c_int(w.stride(0)),
+        _c_int(out.stride(0)), _c_int(epi), _c_int(splits),
+        _c_void_p(partial.data_ptr() if partial is not None else 0),
+        _c_void_p(counters.data_ptr() if counters is not None else 0),
+        _c_void_p(status_word(a.device).data_ptr()), _stream())
+    if code == _UNSUPPORTED:
+        return False
+    if code != 0:
+        raise RuntimeError(f"tensor-core matrix product failed to launch (CUDA error {code})")
+    _count(1)
+    return True
+
+
+SKINNY_ROWS = 64     # products with at most this many rows run with W on the MMA's M side
+
+
 def _operands_ok(a, w) -> bool:
     return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.is_cuda
             and a.stride(1) == 1 and w.stride(1) == 1 and a.shape[1] % 8 == 0
@@ -102,6 +159,8 @@ def linear(a, w, out, *, accumulate=False, tile=None) -> bool:
         epi = ACCUM_F32 if accumulate else STORE_F32
     else:
         return False
+    if tile is None and a.shape[0] <= SKINNY_ROWS:
+        return _gemm_skinny(a, w, out, w.shape[0], epi)
     bn = tile or _tile_width(a.shape[0], w.shape[0])
     return _gemm(a, w, out, w.shape[0], epi, bn)
 
@@ -110,6 +169,8 @@ def linear_swiglu(h, gate_up, out, tile=None) -> bool:
     if not _operands_ok(h, gate_up) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
         return False
     inter = gate_up.shape[0] // 2
+    if tile is None and h.shape[0] <= SKINNY_ROWS:
+        return _gemm_skinny(h, gate_up, out, inter, SWIGLU_BF16)
     bn = tile or _tile_width(h.shape[0], 2 * inter)
     return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn)
 

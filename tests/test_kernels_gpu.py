@@ -125,6 +125,50 @@ def test_linear_swiglu_tensor_core(m, inter, k, tile):
     tensor_core.check_status(DEV)
 
 
+@pytest.mark.parametrize("splits", [1, 2, 5, None])
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (7, 509, 96), (16, 1280, 768), (33, 768, 2048),
+                                   (64, 200, 320), (8, 50304, 768), (3, 100, 1000)])
+def test_linear_few_rows_split_along_k(m, n, k, splits):
+    """The product for decoded tokens: W on the MMA's M side, K split over blocks,
+    the last block to arrive sums the partials in a fixed order."""
+    from crucible_b200.ops import tensor_core
+    a = (torch.rand(m, k, device=DEV) + 0.5).bfloat16()
+    w = (torch.rand(n, k, device=DEV) * 0.1 + 0.05).bfloat16()
+    ref = a.double() @ w.double().T
+    base = torch.randn(m, n, device=DEV)
+    for _ in range(2):                                   # twice: the counters must be back at zero
+        out = torch.empty(m, n, device=DEV)
+        assert tensor_core._gemm_skinny(a, w, out, n, tensor_core.STORE_F32, splits)
+        assert rel(out, ref) < 1e-5
+        out16 = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+        assert tensor_core._gemm_skinny(a, w, out16, n, tensor_core.STORE_BF16, splits)
+        assert rel(out16, ref) < 5e-3
+        acc = base.clone()
+        assert tensor_core._gemm_skinny(a, w, acc, n, tensor_core.ACCUM_F32, splits)
+        assert rel(acc, ref + base.double()) < 1e-5
+    first = torch.empty(m, n, device=DEV)
+    again = torch.empty(m, n, device=DEV)
+    tensor_core._gemm_skinny(a, w, first, n, tensor_core.STORE_F32, splits)
+    tensor_core._gemm_skinny(a, w, again, n, tensor_core.STORE_F32, splits)
+    assert torch.equal(first, again)                      # the order of the sum is fixed
+    tensor_core.check_status(DEV)
+
+
+@pytest.mark.parametrize("splits", [1, 3, None])
+@pytest.mark.parametrize("m,inter,k", [(1, 176, 64), (8, 2048, 768), (33, 320, 96), (64, 90, 136)])
+def test_linear_swiglu_few_rows(m, inter, k, splits):
+    from crucible_b200.ops import tensor_core
+    h = torch.randn(m, k, device=DEV).bfloat16()
+    w = (torch.randn(2 * inter, k, device=DEV) * 0.2).bfloat16()
+    y = h.double() @ w.double().T
+    g, u = y[:, :inter], y[:, inter:]
+    for _ in range(2):
+        out = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
+        assert tensor_core._gemm_skinny(h, w, out, inter, tensor_core.SWIGLU_BF16, splits)
+        assert rel(out, g / (1 + torch.exp(-g)) * u) < 6e-3
+    tensor_core.check_status(DEV)
+
+
 def test_linear_refuses_what_tma_cannot_read():
     from crucible_b200.ops import tensor_core
     a = torch.randn(4, 100, device=DEV).bfloat16()      # 200-byte rows: not a multiple of 16
