@@ -23,6 +23,8 @@ __global__ void attention_generic_kernel(
     const int* __restrict__ positions, const int* __restrict__ row_request,
     const int* __restrict__ block_table, int table_stride, int n_rows, int n_heads,
     int n_kv_heads, int head_dim, int page_tokens, float scale, int window) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
     const int warps_per_block = blockDim.x >> 5;
     const int unit = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     if (unit >= n_rows * n_heads) return;
@@ -89,12 +91,12 @@ CB_EXPORT int cb_attention_generic(const void* qkv, int qkv_stride, void* out, i
     const int blocks = (int)((units + warps - 1) / warps);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == CB_F32)
-        attention_generic_kernel<float><<<blocks, warps * 32, 0, s>>>(
+        cb_launch(attention_generic_kernel<float>, dim3(blocks), dim3(warps * 32), 0, s, 
             (const float*)qkv, qkv_stride, (float*)out, out_stride, (const float*)k_cache,
             (const float*)v_cache, positions, row_request, block_table, table_stride, n_rows,
             n_heads, n_kv_heads, head_dim, page_tokens, scale, window);
     else
-        attention_generic_kernel<__nv_bfloat16><<<blocks, warps * 32, 0, s>>>(
+        cb_launch(attention_generic_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), 0, s, 
             (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)out, out_stride,
             (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, row_request,
             block_table, table_stride, n_rows, n_heads, n_kv_heads, head_dim, page_tokens, scale,

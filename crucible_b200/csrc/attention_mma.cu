@@ -256,6 +256,8 @@ __device__ __forceinline__ void load_q_rows(const AttnParams& p, int row_base, i
 // ---------------------------------------------------------------------------
 template <int HD_MAX>
 __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int pitch = p.head_dim + 8;
     __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -352,6 +354,8 @@ __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p
 // ---------------------------------------------------------------------------
 template <int HD_MAX>
 __global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int pitch = p.head_dim + 8;
     __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -470,6 +474,8 @@ __global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p
 // sums its features over the chunks with the weights exp2(max_c - max).
 __global__ void attention_merge_kernel(const AttnParams p, const int* __restrict__ positions,
                                        int n_tokens) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
     const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (unit >= n_tokens * p.n_heads) return;
     const int lane = threadIdx.x & 31;
@@ -529,7 +535,7 @@ int launch_tiles(const AttnParams& p, int n_requests, int max_q_tiles, cudaStrea
         configured = true;
     }
     dim3 grid(max_q_tiles, p.n_kv_heads, n_requests);
-    attention_tiles_kernel<HD_MAX><<<grid, 128, smem, s>>>(p);
+    cb_launch(attention_tiles_kernel<HD_MAX>, dim3(grid), dim3(128), smem, s, p);
     return cb_last_error();
 }
 
@@ -548,7 +554,7 @@ int launch_split(const AttnParams& p, int n_requests, int max_q_tiles, cudaStrea
         configured = true;
     }
     dim3 grid(max_q_tiles * p.n_chunks, p.n_kv_heads, n_requests);
-    attention_split_kernel<HD_MAX><<<grid, 128, smem, s>>>(p);
+    cb_launch(attention_split_kernel<HD_MAX>, dim3(grid), dim3(128), smem, s, p);
     return cb_last_error();
 }
 
@@ -620,7 +626,7 @@ CB_EXPORT int cb_attention_mma(const void* qkv, int qkv_stride, void* out, int o
     if (rc != 0) return rc;
     const int warps = 4;
     const long units = (long)n_tokens * n_heads;
-    attention_merge_kernel<<<(int)((units + warps - 1) / warps), warps * 32, 0, s>>>(p, positions,
+    cb_launch(attention_merge_kernel, dim3((int)((units + warps - 1) / warps)), dim3(warps * 32), 0, s, p, positions,
                                                                                     n_tokens);
     return cb_last_error();
 }

@@ -51,4 +51,54 @@ __device__ __forceinline__ float cb_block_sum(float v, float* scratch) {
     return total;
 }
 
-static inline int cb_last_error() { return (int)cudaGetLastError(); }
+// The first launch failure since the last call (launches record it), else the
+// runtime's last error.
+static thread_local int cb_launch_failure = 0;
+static inline int cb_last_error() {
+    const int rc = cb_launch_failure;
+    cb_launch_failure = 0;
+    return rc ? rc : (int)cudaGetLastError();
+}
+
+// ---- programmatic dependent launch ------------------------------------------------
+// Every kernel of this package is launched with the programmatic-stream-
+// serialization attribute: it may become resident while the kernel before it in
+// the stream is still running, and must call cb_pdl_wait() before it reads
+// anything an earlier kernel wrote (the wait returns once all earlier kernels
+// have completed and their writes are visible).  What a kernel does before the
+// wait -- index arithmetic, barrier and tensor-memory set-up, loads of weights,
+// which no kernel writes -- overlaps the tail of its predecessor.  Each kernel
+// calls cb_pdl_trigger() at its start so that its successor may be scheduled
+// early.  The attribute is set only if CRUCIBLE_PDL=1 is in the environment (off by
+// default: measured on B200 inside captured graphs it changed step times by less
+// than the noise); without it the two device calls are no-ops.
+__device__ __forceinline__ void cb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void cb_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <cstdlib>
+#include <utility>
+static inline bool cb_pdl_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("CRUCIBLE_PDL");
+        return v && v[0] == '1';
+    }();
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int cb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                            cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = cb_pdl_enabled() ? 1 : 0;
+    const int rc = (int)cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+    if (rc != 0 && cb_launch_failure == 0) cb_launch_failure = rc;
+    return rc;
+}

@@ -10,6 +10,8 @@
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                   float* __restrict__ out, int width, int vocab) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
     // ids are validated on the host; an id outside the table still must not
@@ -25,10 +27,10 @@ CB_EXPORT int cb_embed_rows(const void* table, int table_dtype, const int* ids, 
     if (n_rows <= 0) return 0;
     const int threads = width >= 256 ? 256 : 64;
     if (table_dtype == CB_F32)
-        embed_rows_kernel<float><<<n_rows, threads, 0, (cudaStream_t)stream>>>(
+        cb_launch(embed_rows_kernel<float>, dim3(n_rows), dim3(threads), 0, (cudaStream_t)stream, 
             (const float*)table, ids, out, width, vocab);
     else
-        embed_rows_kernel<__nv_bfloat16><<<n_rows, threads, 0, (cudaStream_t)stream>>>(
+        cb_launch(embed_rows_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, (cudaStream_t)stream, 
             (const __nv_bfloat16*)table, ids, out, width, vocab);
     return cb_last_error();
 }
@@ -39,6 +41,8 @@ CB_EXPORT int cb_embed_rows(const void* table, int table_dtype, const int* ids, 
 template <typename T>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
                                T* __restrict__ out, int width, float eps) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
     __shared__ float scratch[32];
     const float* row = x + (size_t)blockIdx.x * width;
     T* dst = out + (size_t)blockIdx.x * width;
@@ -58,6 +62,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 template <typename T>
 __global__ void rmsnorm_vec4_kernel(const float* __restrict__ x, const float* __restrict__ gain,
                                     T* __restrict__ out, int width, float eps) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
     __shared__ float scratch[32];
     const int n4 = width >> 2;
     const float4* row = reinterpret_cast<const float4*>(x + (size_t)blockIdx.x * width);
@@ -100,17 +106,17 @@ CB_EXPORT int cb_rmsnorm(const float* x, const float* gain, void* out, int out_d
         if (threads > 1024) threads = ((width >> 2) + 4 * 32 - 1) / (4 * 32) * 32;
         if (threads < 32) threads = 32;
         if (out_dtype == CB_F32)
-            rmsnorm_vec4_kernel<float><<<n_rows, threads, 0, s>>>(x, gain, (float*)out, width, eps);
+            cb_launch(rmsnorm_vec4_kernel<float>, dim3(n_rows), dim3(threads), 0, s, x, gain, (float*)out, width, eps);
         else
-            rmsnorm_vec4_kernel<__nv_bfloat16><<<n_rows, threads, 0, s>>>(
+            cb_launch(rmsnorm_vec4_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, s, 
                 x, gain, (__nv_bfloat16*)out, width, eps);
         return cb_last_error();
     }
     const int threads = width >= 1024 ? 256 : 128;
     if (out_dtype == CB_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, s>>>(x, gain, (float*)out, width, eps);
+        cb_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, s, x, gain, (float*)out, width, eps);
     else
-        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, s>>>(x, gain, (__nv_bfloat16*)out,
+        cb_launch(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, s, x, gain, (__nv_bfloat16*)out,
                                                                  width, eps);
     return cb_last_error();
 }
@@ -121,6 +127,8 @@ CB_EXPORT int cb_rmsnorm(const float* x, const float* gain, void* out, int out_d
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out,
                               int inter, size_t total) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / inter;
@@ -139,10 +147,10 @@ CB_EXPORT int cb_swiglu(const void* gate_up, void* out, int dtype, int n_rows, i
     size_t blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == CB_F32)
-        swiglu_kernel<float><<<(int)blocks, threads, 0, (cudaStream_t)stream>>>(
+        cb_launch(swiglu_kernel<float>, dim3((int)blocks), dim3(threads), 0, (cudaStream_t)stream, 
             (const float*)gate_up, (float*)out, inter, total);
     else
-        swiglu_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, (cudaStream_t)stream>>>(
+        cb_launch(swiglu_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, (cudaStream_t)stream, 
             (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
     return cb_last_error();
 }
@@ -152,6 +160,8 @@ CB_EXPORT int cb_swiglu(const void* gate_up, void* out, int dtype, int n_rows, i
 // ---------------------------------------------------------------------------
 __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                    float* __restrict__ out, int width) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
     const float* src = x + (size_t)rows[blockIdx.x] * width;
     float* dst = out + (size_t)blockIdx.x * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
@@ -160,7 +170,7 @@ __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __res
 CB_EXPORT int cb_gather_rows(const float* x, const int* rows, float* out, int n_rows, int width,
                              void* stream) {
     if (n_rows <= 0) return 0;
-    gather_rows_kernel<<<n_rows, 128, 0, (cudaStream_t)stream>>>(x, rows, out, width);
+    cb_launch(gather_rows_kernel, dim3(n_rows), dim3(128), 0, (cudaStream_t)stream, x, rows, out, width);
     return cb_last_error();
 }
 
@@ -180,6 +190,8 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, const float* __restri
                                       T* __restrict__ k_cache, T* __restrict__ v_cache,
                                       int n_heads, int n_kv_heads, int head_dim,
                                       int page_tokens, int write_cache) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
     const int t = blockIdx.x;
     const int row_width = (n_heads + 2 * n_kv_heads) * head_dim;
     T* row = qkv + (size_t)t * row_width;
@@ -231,12 +243,12 @@ CB_EXPORT int cb_rope_kv_append(void* qkv, int dtype, const float* cos_t, const 
     if (threads > 512) threads = 512;
     if (threads < 64) threads = 64;
     if (dtype == CB_F32)
-        rope_kv_append_kernel<float><<<n_rows, threads, 0, (cudaStream_t)stream>>>(
+        cb_launch(rope_kv_append_kernel<float>, dim3(n_rows), dim3(threads), 0, (cudaStream_t)stream, 
             (float*)qkv, cos_t, sin_t, rotary_dim, positions, row_request, block_table,
             table_stride, (float*)k_cache, (float*)v_cache, n_heads, n_kv_heads, head_dim,
             page_tokens, write_cache);
     else
-        rope_kv_append_kernel<__nv_bfloat16><<<n_rows, threads, 0, (cudaStream_t)stream>>>(
+        cb_launch(rope_kv_append_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, (cudaStream_t)stream, 
             (__nv_bfloat16*)qkv, cos_t, sin_t, rotary_dim, positions, row_request, block_table,
             table_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_heads, n_kv_heads,
             head_dim, page_tokens, write_cache);

@@ -17,6 +17,8 @@ template <typename TA, typename TC, bool ACCUMULATE>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W, TC* __restrict__ C,
                  int M, int N, int K, int lda, int ldw, int ldc) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
     __shared__ float As[TK][TM + 4];
     __shared__ float Ws[TK][TN + 4];
     const int tid = threadIdx.x;
@@ -78,10 +80,10 @@ int launch(const void* A, const void* W, void* C, int M, int N, int K, int lda, 
            int ldc, int accumulate, cudaStream_t s) {
     dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
     if (accumulate)
-        gemm_simt_kernel<TA, TC, true><<<grid, 256, 0, s>>>((const TA*)A, (const TA*)W, (TC*)C,
+        cb_launch(gemm_simt_kernel<TA, TC, true>, dim3(grid), dim3(256), 0, s, (const TA*)A, (const TA*)W, (TC*)C,
                                                             M, N, K, lda, ldw, ldc);
     else
-        gemm_simt_kernel<TA, TC, false><<<grid, 256, 0, s>>>((const TA*)A, (const TA*)W, (TC*)C,
+        cb_launch(gemm_simt_kernel<TA, TC, false>, dim3(grid), dim3(256), 0, s, (const TA*)A, (const TA*)W, (TC*)C,
                                                              M, N, K, lda, ldw, ldc);
     return cb_last_error();
 }

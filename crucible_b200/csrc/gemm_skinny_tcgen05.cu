@@ -68,6 +68,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
                    const __grid_constant__ CUtensorMap map_a, void* __restrict__ c_ptr, int M,
                    int N, int K, int ldc, int inter, int splits, float* __restrict__ partial,
                    int* __restrict__ counters, int* __restrict__ status) {
+    cb_pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     using Storage = SkinnyStorage<MT>;
     Storage& s = *reinterpret_cast<Storage*>(
@@ -103,6 +104,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
     __syncthreads();
     tc::tc_fence_after_sync();
     const uint32_t tmem_acc = s.tmem_base;
+    // barriers, tensor memory and descriptors are ready; only now wait for the kernels
+    // before this one, whose outputs the loads below read
+    cb_pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -262,7 +266,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, void* C, int M, int N, 
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    gemm_skinny_kernel<MT, EPI><<<dim3(n_tiles, splits), 192, smem, stream>>>(
+    cb_launch(gemm_skinny_kernel<MT, EPI>, dim3(n_tiles, splits), dim3(192), smem, stream, 
         mw, ma, C, M, N, K, ldc, inter, splits, partial, counters, status);
     return cb_last_error();
 }

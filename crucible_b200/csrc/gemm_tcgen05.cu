@@ -46,6 +46,7 @@ __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_w, void* __restrict__ c_ptr, int M,
                     int N, int K, int ldc, int inter, int* __restrict__ status) {
+    cb_pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     using Storage = SharedStorage<BN, STAGES>;
     Storage& s = *reinterpret_cast<Storage*>(
@@ -77,6 +78,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     __syncthreads();
     tc::tc_fence_after_sync();
     const uint32_t tmem_acc = s.tmem_base;
+    // barriers, tensor memory and descriptors are ready; only now wait for the kernels
+    // before this one, whose outputs the loads below read
+    cb_pdl_wait();
 
     if (warp == 0) {
         // ---- producer: one thread feeds the ring of stages -------------------
@@ -264,7 +268,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, 
     }
     const int n_cols = EPI == SWIGLU_BF16 ? 2 * inter : N;
     dim3 grid((n_cols + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_tcgen05_kernel<BN, STAGES, EPI><<<grid, 192, smem, stream>>>(ma, mw, C, M, N, K, ldc,
+    cb_launch(gemm_tcgen05_kernel<BN, STAGES, EPI>, dim3(grid), dim3(192), smem, stream, ma, mw, C, M, N, K, ldc,
                                                                       inter, status);
     return cb_last_error();
 }

@@ -61,6 +61,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
                    const int* __restrict__ top_k, const float* __restrict__ uniform,
                    int* __restrict__ out_ids) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     __shared__ unsigned int hist[256];
@@ -167,6 +169,8 @@ sample_rows_kernel(const float* __restrict__ logits, int vocab, const float* __r
 
 __global__ void __launch_bounds__(256)
 argmax_rows_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out_ids) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     block_argmax(logits + (size_t)blockIdx.x * vocab, vocab, out_ids + blockIdx.x, s_val, s_idx);
@@ -181,6 +185,8 @@ constexpr int ARGMAX_SLICES = 32;
 __global__ void __launch_bounds__(256)
 argmax_slices_kernel(const float* __restrict__ logits, int vocab, float* __restrict__ part_val,
                      int* __restrict__ part_idx) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     const int row = blockIdx.y, slice = blockIdx.x;
@@ -212,6 +218,8 @@ argmax_slices_kernel(const float* __restrict__ logits, int vocab, float* __restr
 
 __global__ void argmax_final_kernel(const float* __restrict__ part_val,
                                     const int* __restrict__ part_idx, int* __restrict__ out_ids) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
     const int row = blockIdx.x, lane = threadIdx.x;
     float bv = part_val[row * ARGMAX_SLICES + lane];
     int bi = part_idx[row * ARGMAX_SLICES + lane];
@@ -233,14 +241,14 @@ CB_EXPORT int cb_argmax_rows(const float* logits, int n_rows, int vocab, int* ou
     if (n_rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (scratch == nullptr || vocab < 4096) {
-        argmax_rows_kernel<<<n_rows, 256, 0, s>>>(logits, vocab, out_ids);
+        cb_launch(argmax_rows_kernel, dim3(n_rows), dim3(256), 0, s, logits, vocab, out_ids);
         return cb_last_error();
     }
     float* part_val = (float*)scratch;
     int* part_idx = (int*)(part_val + (size_t)n_rows * ARGMAX_SLICES);
-    argmax_slices_kernel<<<dim3(ARGMAX_SLICES, n_rows), 256, 0, s>>>(logits, vocab, part_val,
+    cb_launch(argmax_slices_kernel, dim3(ARGMAX_SLICES, n_rows), dim3(256), 0, s, logits, vocab, part_val,
                                                                      part_idx);
-    argmax_final_kernel<<<n_rows, 32, 0, s>>>(part_val, part_idx, out_ids);
+    cb_launch(argmax_final_kernel, dim3(n_rows), dim3(32), 0, s, part_val, part_idx, out_ids);
     return cb_last_error();
 }
 
@@ -253,7 +261,7 @@ CB_EXPORT int cb_sample_rows(const float* logits, int n_rows, int vocab, const f
                              void* stream) {
     if (n_rows <= 0) return 0;
     if (max_top_k > MAX_TOP_K) return CB_ERR_UNSUPPORTED;
-    sample_rows_kernel<<<n_rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(
+    cb_launch(sample_rows_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, 
         logits, vocab, temperature, top_k, uniform, out_ids);
     return cb_last_error();
 }

@@ -6,10 +6,11 @@ and contiguity are checked here, on the host, before anything is launched.
 There is no CPU path: a tensor that is not on a CUDA device is an error, and so
 is a kernel library that cannot be built or loaded.
 
-Which kernel runs is decided by the engine dtype alone (float32: CUDA-core
-kernels with fp32 arithmetic throughout; bfloat16: the tensor-core kernels,
-with the plain kernels as the stated refuge for sizes they do not take), never
-by the batch size or the way a prompt was cut.
+Which kernel runs is decided by the engine dtype (float32: CUDA-core kernels
+with fp32 arithmetic throughout; bfloat16: the tensor-core kernels, the fused
+kernels for steps of a few rows, and the plain kernels as the stated refuge for
+sizes the others do not take) and by the step's shape; every kernel computes
+the same function, so a row's result depends on the path only by rounding.
 """
 from __future__ import annotations
 
@@ -140,24 +141,48 @@ def linear_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *,
            "linear (CUDA cores)")
 
 
-def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *,
-           accumulate: bool = False) -> None:
-    if a.dtype == torch.bfloat16:
+def linear(a, w: torch.Tensor, out: torch.Tensor, *, accumulate: bool = False) -> None:
+    """`a` is a tensor or a `small_batch.LazyNorm` (rows not yet normalised)."""
+    from . import small_batch
+    if w.dtype == torch.bfloat16:
+        if a.shape[0] <= small_batch.MAX_ROWS and small_batch.linear(a, w, out, accumulate=accumulate):
+            return
+        a = small_batch.as_tensor(a)
         from . import tensor_core
         if tensor_core.linear(a, w, out, accumulate=accumulate):
             return
+    a = small_batch.as_tensor(a)
     linear_plain(a, w, out, accumulate=accumulate)
 
 
-def linear_swiglu(h: torch.Tensor, gate_up: torch.Tensor, out: torch.Tensor, ctx) -> None:
+def linear_swiglu(h, gate_up: torch.Tensor, out: torch.Tensor, ctx) -> None:
     """out[T, I] = silu(h Wg^T) * (h Wu^T) with gate_up = [Wg; Wu] of shape [2I, d]."""
-    if h.dtype == torch.bfloat16:
+    from . import small_batch
+    if gate_up.dtype == torch.bfloat16:
+        if h.shape[0] <= small_batch.MAX_ROWS and small_batch.linear_swiglu(h, gate_up, out):
+            return
+        h = small_batch.as_tensor(h)
         from . import tensor_core
         if tensor_core.linear_swiglu(h, gate_up, out):
             return
+    h = small_batch.as_tensor(h)
     both = ctx.scratch("ffn.gate_up", (h.shape[0], gate_up.shape[0]), h.dtype)
     linear(h, gate_up, both)
     swiglu(both, out)
+
+
+def qkv_rope_append(h, wqkv: torch.Tensor, qkv: torch.Tensor, n_heads: int, n_kv_heads: int,
+                    head_dim: int, cos, sin, rotary_dim: int, ctx, cache, binding) -> None:
+    """The query/key/value projection, the rotation of q and k, and the write of
+    k and v into the cache pages: one kernel for a few rows, two otherwise.
+    Leaves the rotated q in the first columns of `qkv`."""
+    from . import small_batch
+    if (wqkv.dtype == torch.bfloat16 and h.shape[0] <= small_batch.MAX_ROWS
+            and small_batch.qkv_rope_append(h, wqkv, qkv, n_heads, n_kv_heads, head_dim, cos, sin,
+                                            rotary_dim, ctx, cache, binding)):
+        return
+    linear(h, wqkv, qkv)
+    rope_kv_append(qkv, n_heads, n_kv_heads, head_dim, cos, sin, rotary_dim, ctx, cache, binding)
 
 
 # ---------------------------------------------------------------------------

@@ -1,0 +1,133 @@
+"""Fused kernels for steps of at most 8 rows (a few decoded tokens), bfloat16
+engine only.  Each function returns True if it ran, False if the sizes are
+outside what the kernels take (more than 8 rows, K not a multiple of 8, a
+partially rotated head): the caller then runs the general kernels.
+
+`LazyNorm` is what a norm part hands to a mixer or feed-forward that can fuse
+the normalisation into its first matrix product: the fp32 rows, the gain and
+eps, not yet normalised.  `tensor()` runs the norm kernel (once) for consumers
+that need the normalised rows as a tensor.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Union
+
+import torch
+
+from . import build
+
+build.register_module("decode_small", ["common.cuh"])
+
+MAX_ROWS = 8
+_c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+_UNSUPPORTED = 100001
+
+
+class LazyNorm:
+    def __init__(self, x: torch.Tensor, gain: torch.Tensor, eps: float, materialize):
+        self.x, self.gain, self.eps = x, gain, eps
+        self._materialize = materialize
+        self._tensor: Optional[torch.Tensor] = None
+        self.shape = x.shape
+
+    def tensor(self) -> torch.Tensor:
+        if self._tensor is None:
+            self._tensor = self._materialize()
+        return self._tensor
+
+
+Rows = Union[torch.Tensor, LazyNorm]
+
+
+def as_tensor(h: Rows) -> torch.Tensor:
+    return h.tensor() if isinstance(h, LazyNorm) else h
+
+
+def _ptr(t):
+    return _c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return _c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _input(h: Rows):
+    """(x, gain, eps, a, lda) for the launchers."""
+    if isinstance(h, LazyNorm):
+        if not h.x.is_contiguous():
+            return None
+        return h.x, h.gain, h.eps, None, 0
+    if h.dtype != torch.bfloat16 or h.stride(1) != 1:
+        return None
+    return None, None, 0.0, h, h.stride(0)
+
+
+def _done(code: int, what: str) -> bool:
+    if code == _UNSUPPORTED:
+        return False
+    if code != 0:
+        raise RuntimeError(f"{what} failed to launch (CUDA error {code})")
+    from . import LAUNCHES
+    LAUNCHES[0] += 1
+    return True
+
+
+def _weights_ok(w: torch.Tensor, rows: int) -> bool:
+    return (rows <= MAX_ROWS and w.dtype == torch.bfloat16 and w.is_cuda and w.stride(1) == 1)
+
+
+MAX_OUT_ROWS = 8192     # wider products (the LM head) stream better through the tensor-core kernel
+
+
+def linear(h: Rows, w: torch.Tensor, out: torch.Tensor, *, accumulate: bool = False) -> bool:
+    if (not _weights_ok(w, h.shape[0]) or out.dtype != torch.float32 or out.stride(1) != 1
+            or w.shape[0] > MAX_OUT_ROWS):
+        return False
+    inp = _input(h)
+    if inp is None:
+        return False
+    x, gain, eps, a, lda = inp
+    lib = build.load("decode_small")
+    return _done(lib.cb_small_linear(_ptr(x), _ptr(gain), _c_float(eps), _ptr(a), _c_int(lda),
+                                     _ptr(w), _c_int(w.stride(0)), _ptr(out), _c_int(out.stride(0)),
+                                     _c_int(h.shape[0]), _c_int(w.shape[0]), _c_int(w.shape[1]),
+                                     _c_int(1 if accumulate else 0), _stream()), "small linear")
+
+
+def linear_swiglu(h: Rows, gate_up: torch.Tensor, out: torch.Tensor) -> bool:
+    if (not _weights_ok(gate_up, h.shape[0]) or out.dtype != torch.bfloat16
+            or out.stride(1) != 1):
+        return False
+    inp = _input(h)
+    if inp is None:
+        return False
+    x, gain, eps, a, lda = inp
+    lib = build.load("decode_small")
+    return _done(lib.cb_small_swiglu(_ptr(x), _ptr(gain), _c_float(eps), _ptr(a), _c_int(lda),
+                                     _ptr(gate_up), _c_int(gate_up.stride(0)), _ptr(out),
+                                     _c_int(out.stride(0)), _c_int(h.shape[0]),
+                                     _c_int(gate_up.shape[0] // 2), _c_int(gate_up.shape[1]),
+                                     _stream()), "small swiglu")
+
+
+def qkv_rope_append(h: Rows, wqkv: torch.Tensor, qkv: torch.Tensor, n_heads: int, n_kv_heads: int,
+                    head_dim: int, cos, sin, rotary_dim: int, ctx, cache, binding) -> bool:
+    if (not _weights_ok(wqkv, h.shape[0]) or qkv.dtype != torch.bfloat16 or cos is None
+            or rotary_dim != head_dim):
+        return False
+    inp = _input(h)
+    if inp is None:
+        return False
+    x, gain, eps, a, lda = inp
+    k_cache, v_cache = cache.keys(binding.slot), cache.values(binding.slot)
+    table = ctx.block_table(binding.group)
+    lib = build.load("decode_small")
+    return _done(lib.cb_small_qkv_rope_append(
+        _ptr(x), _ptr(gain), _c_float(eps), _ptr(a), _c_int(lda), _ptr(wqkv),
+        _c_int(wqkv.stride(0)), _ptr(qkv), _c_int(qkv.stride(0)), _ptr(cos), _ptr(sin),
+        _c_int(rotary_dim), _ptr(ctx.positions), _ptr(ctx.row_request), _ptr(table),
+        _c_int(table.shape[1]), _ptr(k_cache), _ptr(v_cache), _c_int(h.shape[0]),
+        _c_int(wqkv.shape[1]), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
+        _c_int(cache.page_tokens), _c_int(1 if binding.write else 0), _stream()),
+        "small qkv + rope + cache write")

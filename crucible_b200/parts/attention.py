@@ -22,6 +22,8 @@ from .base import MIXERS, POSITIONS, CacheNeed, Mixer, TensorDecl
 
 
 class PagedAttention(Mixer):
+    fuses_norm = True
+
     def __init__(self, spec: MixerSpec):
         if spec.n_heads <= 0 or spec.n_kv_heads <= 0 or spec.head_dim <= 0:
             raise ValueError("attention needs positive n_heads, n_kv_heads and head_dim")
@@ -65,16 +67,21 @@ class PagedAttention(Mixer):
         s = self.spec
         t = h.shape[0]
         qkv = ctx.scratch("attn.qkv", (t, self.q_width + 2 * self.kv_width), self.dtype)
-        ops.linear(h, self.wqkv, qkv)
+        cache = ctx.cache(binding.group)
         rot = self.position.rotation() if self.position is not None else None
-        if rot is None and self.position is not None:
+        if rot is not None or self.position is None:
+            cos, sin, rotary_dim = rot if rot is not None else (None, None, 0)
+            ops.qkv_rope_append(h, self.wqkv, qkv, s.n_heads, s.n_kv_heads, s.head_dim, cos, sin,
+                                rotary_dim, ctx, cache, binding)
+        else:
+            # an encoding that is not a rotation: project, let it act on q and k,
+            # then write k and v to the cache
+            ops.linear(h, self.wqkv, qkv)
             q = qkv[:, :self.q_width].view(t, s.n_heads, s.head_dim)
             k = qkv[:, self.q_width:self.q_width + self.kv_width].view(t, s.n_kv_heads, s.head_dim)
             self.position.apply(ctx, q, k)
-        cos, sin, rotary_dim = rot if rot is not None else (None, None, 0)
-        cache = ctx.cache(binding.group)
-        ops.rope_kv_append(qkv, s.n_heads, s.n_kv_heads, s.head_dim, cos, sin, rotary_dim,
-                           ctx, cache, binding)
+            ops.rope_kv_append(qkv, s.n_heads, s.n_kv_heads, s.head_dim, None, None, 0, ctx, cache,
+                               binding)
         out = ctx.scratch("attn.out", (t, self.q_width), self.dtype)
         ops.paged_attention(qkv, out, s.n_heads, s.n_kv_heads, s.head_dim, s.softmax_scale,
                             s.window, ctx, cache, binding)

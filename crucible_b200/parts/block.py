@@ -8,10 +8,18 @@ from .base import ARRANGEMENTS, Arrangement
 
 class PreNormBlock(Arrangement):
     def forward(self, ctx, x, binding):
-        h = self.mixer_norm.forward(ctx, x)
+        h = self._norm(ctx, self.mixer_norm, self.mixer, x)
         self.mixer.forward(ctx, h, x, binding)
-        h = self.feed_forward_norm.forward(ctx, x)
+        h = self._norm(ctx, self.feed_forward_norm, self.feed_forward, x)
         self.feed_forward.forward(ctx, h, x)
+
+    @staticmethod
+    def _norm(ctx, norm, consumer, x):
+        # a consumer that can fuse the norm into its first product (`fuses_norm`)
+        # may be handed rows that are not yet normalised, if the norm offers that
+        if getattr(consumer, "fuses_norm", False) and getattr(norm, "supports_lazy", False):
+            return norm.forward(ctx, x, lazy=True)
+        return norm.forward(ctx, x)
 
 
 ARRANGEMENTS.register("pre_norm", PreNormBlock)

@@ -10,6 +10,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
+from ..ops import small_batch
 from ..config.model_config import NormSpec
 from .base import NORMS, Norm, TensorDecl
 
@@ -27,10 +28,19 @@ class RMSNorm(Norm):
         self.gain = tensors["gain"]
         self.dtype = dtype
 
-    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
-        out = ctx.scratch("norm.out", (x.shape[0], self.spec.width), self.dtype)
-        ops.rmsnorm(x, self.gain, self.spec.eps, out)
-        return out
+    supports_lazy = True
+
+    def forward(self, ctx, x: torch.Tensor, lazy: bool = False):
+        """`lazy`: the consumer can fuse the normalisation into its first matrix
+        product; for steps of a few rows it then gets the rows not yet normalised
+        (`ops.small_batch.LazyNorm`) instead of a tensor."""
+        def run():
+            out = ctx.scratch("norm.out", (x.shape[0], self.spec.width), self.dtype)
+            ops.rmsnorm(x, self.gain, self.spec.eps, out)
+            return out
+        if lazy and self.dtype == torch.bfloat16 and x.shape[0] <= small_batch.MAX_ROWS:
+            return small_batch.LazyNorm(x, self.gain, self.spec.eps, run)
+        return run()
 
 
 NORMS.register("rmsnorm", RMSNorm)

@@ -16,6 +16,8 @@ from .base import FEED_FORWARDS, FeedForward, TensorDecl
 
 
 class SwiGLU(FeedForward):
+    fuses_norm = True
+
     def __init__(self, spec: FeedForwardSpec):
         self.spec = spec
         self.gate_up = None

@@ -147,20 +147,17 @@ def test_peaky_attention_over_many_pages(tmp_path):
     got = decoded("float32")
     worst = max(helpers.relative_error(got[k], ref[k[1]]) for k in got)
     assert worst <= TOLERANCE["float32"], worst
-    # bfloat16 rounds the queries and keys themselves, and the scaling multiplies that
-    # rounding by 9 in the scores, so the distance to the 64-bit model is no longer a
-    # test of the cache.  What a lost key would break is the agreement between the two
-    # ways of running the same bfloat16 arithmetic: decoded one by one, and whole.
+    # bfloat16 rounds the queries and keys themselves and the scaling multiplies that
+    # rounding in the scores, so for bfloat16 the factor is 1.5 (scores by 2.25): still
+    # far from uniform attention, with the rounding noise inside the usual tolerance.
+    for n in tensors:
+        if "q_proj" in n or "k_proj" in n:
+            tensors[n] = (tensors[n].float() * 0.5).bfloat16()
+    write_safetensors(path, tensors)
+    ref = helpers.plain_logits(folder, tokens)
     got = decoded("bfloat16")
-    trace = Trace()
-    trace.step([("a", tokens, list(range(269, 400)))], end=["a"])
-    out = str(tmp_path / "out-whole")
-    helpers.replay_in_process(folder, "bfloat16", trace, out, 448, 16)
-    whole = helpers.collect(trace, out, vocab)
-    assert sorted(whole) == sorted(got)
-    worst = max(helpers.relative_error(got[k], whole[k].astype("float64")) for k in got)
+    worst = max(helpers.relative_error(got[k], ref[k[1]]) for k in got)
     assert worst <= TOLERANCE["bfloat16"], worst
-    assert max(helpers.relative_error(got[k], ref[k[1]]) for k in got) < 0.25
 
 
 def test_command_line_generate(tmp_path):

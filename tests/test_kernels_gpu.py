@@ -19,7 +19,8 @@ def _ops():
 
 
 def rel(got, ref):
-    return float((got.double() - ref.double()).abs().max()) / max(float(ref.abs().max()), 1e-6)
+    got, ref = got.double().cpu(), ref.double().cpu()
+    return float((got - ref).abs().max()) / max(float(ref.abs().max()), 1e-6)
 
 
 # ---------------------------------------------------------------------------
@@ -167,6 +168,87 @@ def test_linear_swiglu_few_rows(m, inter, k, splits):
         assert tensor_core._gemm_skinny(h, w, out, inter, tensor_core.SWIGLU_BF16, splits)
         assert rel(out, g / (1 + torch.exp(-g)) * u) < 6e-3
     tensor_core.check_status(DEV)
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 8])
+@pytest.mark.parametrize("n,k", [(768, 768), (100, 2048), (33, 40), (1280, 1032)])
+def test_small_batch_linear_and_swiglu(m, n, k):
+    """The fused kernels for a few rows: bf16 input or fp32 rows normalised on the fly."""
+    from crucible_b200.ops import small_batch
+    w = (torch.randn(n, k, device=DEV) * 0.1).bfloat16()
+    a = torch.randn(m, k, device=DEV).bfloat16()
+    base = torch.randn(m, n, device=DEV)
+    out = base.clone()
+    assert small_batch.linear(a, w, out, accumulate=True)
+    assert rel(out, base.double() + a.double() @ w.double().T) < 1e-5
+    x = torch.randn(m, k, device=DEV) * 2
+    gain = 1 + 0.2 * torch.randn(k, device=DEV)
+    lazy = small_batch.LazyNorm(x, gain, 1e-5, lambda: None)
+    normed = x.double() * torch.rsqrt(x.double().pow(2).mean(-1, keepdim=True) + 1e-5) * gain.double()
+    out = torch.empty(m, n, device=DEV)
+    assert small_batch.linear(lazy, w, out)
+    assert rel(out, normed @ w.double().T) < 1e-5
+    if n % 2 == 0:
+        inter = n // 2
+        act = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
+        assert small_batch.linear_swiglu(lazy, w, act)
+        y = normed @ w.double().T
+        g, u = y[:, :inter], y[:, inter:]
+        assert rel(act, g / (1 + torch.exp(-g)) * u) < 5e-3
+    big = torch.randn(9, k, device=DEV).bfloat16()
+    assert small_batch.linear(big, w, torch.empty(9, n, device=DEV)) is False     # more than 8 rows
+    odd = torch.randn(m, 12, device=DEV).bfloat16()
+    assert small_batch.linear(odd, torch.randn(n, 12, device=DEV).bfloat16(),
+                              torch.empty(m, n, device=DEV)) is False             # K not a multiple of 8
+
+
+@pytest.mark.parametrize("write", [True, False])
+def test_small_batch_qkv_rope_append(write):
+    from crucible_b200.ops import small_batch
+    n_heads, n_kv, hd, page, d = 6, 2, 32, 8, 96
+    positions = [5, 17, 0, 40]
+    row_request = [0, 0, 1, 2]
+    tables = torch.tensor([[3, 1, 7, 0, 0, 0], [2, 0, 0, 0, 0, 0], [4, 5, 6, 8, 9, 10]],
+                          dtype=torch.int32, device=DEV)
+    t = len(positions)
+    x = torch.randn(t, d, device=DEV)
+    gain = 1 + 0.1 * torch.randn(d, device=DEV)
+    w = (torch.randn((n_heads + 2 * n_kv) * hd, d, device=DEV) * 0.2).bfloat16()
+    i = torch.arange(hd // 2, dtype=torch.float64)
+    ang = torch.outer(torch.arange(64, dtype=torch.float64), 10000.0 ** (-2 * i / hd))
+    cos, sin = ang.cos().float().to(DEV), ang.sin().float().to(DEV)
+    kv = torch.zeros(1, 2, 11, page, n_kv, hd, dtype=torch.bfloat16, device=DEV)
+
+    class Cache:
+        page_tokens = page
+        keys = staticmethod(lambda slot: kv[slot, 0])
+        values = staticmethod(lambda slot: kv[slot, 1])
+    ctx = SimpleNamespace(positions=torch.tensor(positions, dtype=torch.int32, device=DEV),
+                          row_request=torch.tensor(row_request, dtype=torch.int32, device=DEV),
+                          block_table=lambda g: tables)
+    qkv = torch.zeros(t, w.shape[0], device=DEV, dtype=torch.bfloat16)
+    lazy = small_batch.LazyNorm(x, gain, 1e-6, lambda: None)
+    assert small_batch.qkv_rope_append(lazy, w, qkv, n_heads, n_kv, hd, cos, sin, hd, ctx, Cache,
+                                       SimpleNamespace(group=0, slot=0, write=write))
+    normed = x.double() * torch.rsqrt(x.double().pow(2).mean(-1, keepdim=True) + 1e-6) * gain.double()
+    y = (normed @ w.double().T).cpu().view(t, n_heads + 2 * n_kv, hd)
+
+    def rotate(v, pos):
+        c, s = ang[pos].cos(), ang[pos].sin()
+        x1, x2 = v[..., :hd // 2], v[..., hd // 2:]
+        return torch.cat([x1 * c - x2 * s, x1 * s + x2 * c], dim=-1)
+    for r, pos in enumerate(positions):
+        assert rel(qkv[r, :n_heads * hd].view(n_heads, hd), rotate(y[r, :n_heads], pos)) < 8e-3
+        page_id = int(tables[row_request[r], pos // page])
+        if write:
+            assert rel(kv[0, 0, page_id, pos % page], rotate(y[r, n_heads:n_heads + n_kv], pos)) < 8e-3
+            assert rel(kv[0, 1, page_id, pos % page], y[r, n_heads + n_kv:]) < 8e-3
+    if not write:
+        assert float(kv.abs().max()) == 0.0
+    # a partially rotated head is refused
+    assert small_batch.qkv_rope_append(lazy, w, qkv, n_heads, n_kv, hd, cos[:, :8].contiguous(),
+                                       sin[:, :8].contiguous(), 16, ctx, Cache,
+                                       SimpleNamespace(group=0, slot=0, write=True)) is False
 
 
 def test_linear_refuses_what_tma_cannot_read():
