@@ -45,6 +45,7 @@ struct AttnParams {
     int window;            // 0: all earlier keys
     float* partial;        // split kernel: [rows_total * n_heads][n_chunks][head_dim + 2]
     int n_chunks;
+    int chunk_keys;        // split kernel: keys per chunk, a multiple of SPLIT_KEYS
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -91,36 +92,81 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Loads `n_keys` (<= TILE_KEYS) keys and values starting at key `key0` of one
-// request and KV head into shared memory rows of `pitch` elements; keys at or
-// beyond `key_end` are zero-filled.  `n_threads` threads of the caller take part.
-__device__ __forceinline__ void load_kv_tile(const AttnParams& p, const int* table, int kv_head,
-                                             int key0, int n_keys, int key_end,
-                                             __nv_bfloat16* k_smem, __nv_bfloat16* v_smem,
-                                             int pitch, int tid, int n_threads) {
-    const int chunks_per_row = p.head_dim >> 3;
-    const int total = n_keys * chunks_per_row;
-    for (int i = tid; i < total; i += n_threads) {
-        const int row = i / chunks_per_row;
-        const int c = i - row * chunks_per_row;
-        const int key = key0 + row;
-        const bool valid = key < key_end;
-        size_t off = 0;
-        if (valid) {
-            const int page = table[key / p.page_tokens];
-            const int slot = key % p.page_tokens;
-            off = (((size_t)page * p.page_tokens + slot) * p.n_kv_heads + kv_head) * p.head_dim +
-                  (size_t)c * 8;
+// Loads tiles of TILE_KEYS keys and values of one request and KV head into shared
+// memory rows of `pitch` elements, 16 bytes per cp.async, all threads of the
+// block taking part.  Which (row, 16-byte piece) a thread copies is fixed for the
+// kernel's life and worked out once; per tile only the page lookup remains (a
+// shift and a mask when the page size is a power of two).  Keys at or beyond
+// `key_end` are zero-filled.
+template <int HD_MAX, int NT>
+struct KvLoader {
+    static constexpr int ITEMS = (TILE_KEYS * (HD_MAX / 8) + NT - 1) / NT;
+    int row[ITEMS];          // key row inside the tile, or -1
+    int col[ITEMS];          // first element of the 16-byte piece
+    int page_shift;          // log2(page_tokens), or -1 if not a power of two
+
+    __device__ __forceinline__ void init(const AttnParams& p, int tid) {
+        const int chunks_per_row = p.head_dim >> 3;
+        const int total = TILE_KEYS * chunks_per_row;
+#pragma unroll
+        for (int u = 0; u < ITEMS; ++u) {
+            const int i = tid + u * NT;
+            const int r = i / chunks_per_row;
+            row[u] = i < total ? r : -1;
+            col[u] = (i - r * chunks_per_row) * 8;
         }
-        cp_async_16(k_smem + row * pitch + c * 8, p.k_cache + off, valid);
-        cp_async_16(v_smem + row * pitch + c * 8, p.v_cache + off, valid);
+        page_shift = (p.page_tokens & (p.page_tokens - 1)) == 0 ? 31 - __clz(p.page_tokens) : -1;
     }
-}
+
+    __device__ __forceinline__ void load(const AttnParams& p, const int* table, int kv_head,
+                                         int key0, int key_end, __nv_bfloat16* k_smem,
+                                         __nv_bfloat16* v_smem, int pitch) const {
+        // in batches of four pieces: first the block-table lookups (loads that may
+        // miss), then the copies, so that the lookups' latencies overlap
+#pragma unroll
+        for (int u0 = 0; u0 < ITEMS; u0 += 4) {
+            size_t off[4];
+            bool valid[4];
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const int u = u0 + v;
+                off[v] = 0;
+                valid[v] = false;
+                if (u < ITEMS && row[u] >= 0) {
+                    const int key = key0 + row[u];
+                    valid[v] = key < key_end;
+                    if (valid[v]) {
+                        int page_index, slot;
+                        if (page_shift >= 0) {
+                            page_index = key >> page_shift;
+                            slot = key & (p.page_tokens - 1);
+                        } else {
+                            page_index = key / p.page_tokens;
+                            slot = key - page_index * p.page_tokens;
+                        }
+                        const int page = table[page_index];
+                        off[v] = (((size_t)page * p.page_tokens + slot) * p.n_kv_heads + kv_head) *
+                                     p.head_dim + col[u];
+                    }
+                }
+            }
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const int u = u0 + v;
+                if (u < ITEMS && row[u] >= 0) {
+                    const int dst = row[u] * pitch + col[u];
+                    cp_async_16(k_smem + dst, p.k_cache + off[v], valid[v]);
+                    cp_async_16(v_smem + dst, p.v_cache + off[v], valid[v]);
+                }
+            }
+        }
+    }
+};
 
 // One warp, 16 query rows (A fragments read from q_smem), `n_keys` keys of a
-// tile (multiple of 16, <= 64) in shared memory: scores, running-maximum
+// tile (multiple of 16, <= NK) in shared memory: scores, running-maximum
 // softmax update and the weighted sum of values.  Rows g = lane / 4 and g + 8.
-template <int HD_MAX>
+template <int HD_MAX, int NK>
 __device__ __forceinline__ void attend_tile(const AttnParams& p, const __nv_bfloat16* q_smem,
                                             const __nv_bfloat16* k_smem,
                                             const __nv_bfloat16* v_smem, int pitch, int n_keys,
@@ -130,9 +176,9 @@ __device__ __forceinline__ void attend_tile(const AttnParams& p, const __nv_bflo
     const int lane = threadIdx.x & 31;
     const int t = lane & 3;
     const int hd = p.head_dim;
-    float s[TILE_KEYS / 8][4];
+    float s[NK / 8][4];
 #pragma unroll
-    for (int j = 0; j < TILE_KEYS / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    for (int j = 0; j < NK / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
     // S = Q K^T
 #pragma unroll
     for (int kk = 0; kk < HD_MAX / 16; ++kk) {
@@ -145,7 +191,7 @@ __device__ __forceinline__ void attend_tile(const AttnParams& p, const __nv_bflo
                 ldmatrix_x4(a, q_smem + row * pitch + col);
             }
 #pragma unroll
-            for (int j = 0; j < TILE_KEYS / 8; j += 2) {
+            for (int j = 0; j < NK / 8; j += 2) {
                 if (j * 8 < n_keys) {
                     uint32_t b[4];
                     const int mat = lane >> 3;
@@ -161,7 +207,7 @@ __device__ __forceinline__ void attend_tile(const AttnParams& p, const __nv_bflo
     // mask, scale (in log2 units), row maxima
     float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
-    for (int j = 0; j < TILE_KEYS / 8; ++j) {
+    for (int j = 0; j < NK / 8; ++j) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
             const int key = key0 + j * 8 + 2 * t + e;
@@ -188,7 +234,7 @@ __device__ __forceinline__ void attend_tile(const AttnParams& p, const __nv_bflo
     m_b = new_b;
     float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
-    for (int j = 0; j < TILE_KEYS / 8; ++j) {
+    for (int j = 0; j < NK / 8; ++j) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
             s[j][e] = exp2f(s[j][e] - off_a);
@@ -206,7 +252,7 @@ __device__ __forceinline__ void attend_tile(const AttnParams& p, const __nv_bflo
     }
     // O += P V
 #pragma unroll
-    for (int kk = 0; kk < TILE_KEYS / 16; ++kk) {
+    for (int kk = 0; kk < NK / 16; ++kk) {
         if (kk * 16 < n_keys) {
             uint32_t a[4];
             a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
@@ -300,15 +346,16 @@ __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
 
     const int stage_elems = 2 * TILE_KEYS * pitch;
-    load_kv_tile(p, table, kv_head, key_lo, TILE_KEYS, key_end, kv_smem, kv_smem + TILE_KEYS * pitch,
-                 pitch, threadIdx.x, 128);
+    KvLoader<HD_MAX, 128> loader;
+    loader.init(p, threadIdx.x);
+    loader.load(p, table, kv_head, key_lo, key_end, kv_smem, kv_smem + TILE_KEYS * pitch, pitch);
     cp_async_commit();
     for (int i = 0; i < n_tiles; ++i) {
         const int st = i & 1;
         if (i + 1 < n_tiles) {
             __nv_bfloat16* nxt = kv_smem + (st ^ 1) * stage_elems;
-            load_kv_tile(p, table, kv_head, key_lo + (i + 1) * TILE_KEYS, TILE_KEYS, key_end, nxt,
-                         nxt + TILE_KEYS * pitch, pitch, threadIdx.x, 128);
+            loader.load(p, table, kv_head, key_lo + (i + 1) * TILE_KEYS, key_end, nxt,
+                        nxt + TILE_KEYS * pitch, pitch);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -318,7 +365,7 @@ __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p
         const int key0 = key_lo + i * TILE_KEYS;
         if (key0 <= warp_max_pos) {
             const __nv_bfloat16* ks = kv_smem + st * stage_elems;
-            attend_tile<HD_MAX>(p, q_smem + warp * 16 * pitch, ks, ks + TILE_KEYS * pitch, pitch,
+            attend_tile<HD_MAX, TILE_KEYS>(p, q_smem + warp * 16 * pitch, ks, ks + TILE_KEYS * pitch, pitch,
                                 TILE_KEYS, key0, pos_a, pos_b, lo_a, lo_b, key_end, o, m_a, m_b,
                                 l_a, l_b);
         }
@@ -350,16 +397,71 @@ __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p
 }
 
 // ---------------------------------------------------------------------------
-// split kernel: 16 rows x one chunk of 256 keys, 64 keys per warp
+// split kernel: 16 rows x one chunk of 256 keys.  The block streams the chunk in
+// tiles of 64 keys through a three-stage cp.async pipeline; each warp attends
+// to 16 keys of every tile.  The warps' results are merged in warp order, the
+// chunk's partial (max, sum, vector) goes to scratch, and the block that arrives
+// last at its rows' counter merges the chunks in ascending order and writes the
+// output; no block waits for another.
 // ---------------------------------------------------------------------------
+constexpr int SPLIT_STAGES = 3;
+
+// Merges one row's chunks (ascending, with a running maximum) and writes its
+// output.  One warp; lanes own features.  The loads of up to 8 chunks are issued
+// together, so the whole merge costs about one memory round trip per 8 chunks.
+__device__ __forceinline__ void merge_row(const AttnParams& p, int tok, int head, int pos, int lane) {
+    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int mp = p.head_dim + 2;
+    const int c_first = lo / p.chunk_keys, c_last = pos / p.chunk_keys;
+    const float* base = p.partial + ((size_t)tok * p.n_heads + head) * p.n_chunks * mp;
+    float m = -INFINITY, l = 0.f;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int c0 = c_first; c0 <= c_last; c0 += 8) {
+        float mc[8], lc[8], oc[8][8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const bool in = c0 + j <= c_last;
+            const float* src = base + (size_t)(in ? c0 + j : c_first) * mp;
+            mc[j] = in ? __ldcg(src + p.head_dim) : -INFINITY;
+            lc[j] = in ? __ldcg(src + p.head_dim + 1) : 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int f = lane + 32 * i;
+                oc[j][i] = (in && f < p.head_dim) ? __ldcg(src + f) : 0.f;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {                    // ascending chunks
+            const float m_new = fmaxf(m, mc[j]);
+            const float off = m_new == -INFINITY ? 0.f : m_new;
+            const float keep = exp2f(m - off), take = exp2f(mc[j] - off);
+            l = l * keep + lc[j] * take;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = acc[i] * keep + oc[j][i] * take;
+            m = m_new;
+        }
+    }
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    __nv_bfloat16* dst = p.out + (size_t)tok * p.out_stride + (size_t)head * p.head_dim;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int f = lane + 32 * i;
+        if (f < p.head_dim) dst[f] = __float2bfloat16_rn(acc[i] * inv);
+    }
+}
+
 template <int HD_MAX>
-__global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p, int* counters,
+                                                              int max_q_tiles) {
     cb_pdl_trigger();
     cb_pdl_wait();
     extern __shared__ __align__(16) uint8_t smem_raw[];
+    __shared__ int is_last;
     const int pitch = p.head_dim + 8;
     __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* kv_smem = q_smem + 16 * pitch;      // [4 warps][K, V][SUB][pitch]
+    __nv_bfloat16* kv_smem = q_smem + 16 * pitch;      // [stages][K, V][64][pitch]
     const int req = blockIdx.z, kv_head = blockIdx.y;
     const int n_rep = p.n_heads / p.n_kv_heads;
     const int row_base = p.req_row_start[req];
@@ -379,18 +481,38 @@ __global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p
     const int min_pos = first_pos + (qt * 16) / n_rep;
     const int key_lo = p.window > 0 ? max(0, min_pos - p.window + 1) : 0;
     const int key_end = max_pos + 1;
-    const int c0 = chunk * SPLIT_KEYS;
-    // chunks wholly outside the tile's keys write nothing; the merge skips them
-    // by the same rule
-    if (c0 >= key_end || c0 + SPLIT_KEYS <= key_lo) return;
+    const int c0 = chunk * p.chunk_keys;
+    // chunks wholly outside the tile's keys take no part
+    if (c0 >= key_end || c0 + p.chunk_keys <= key_lo) return;
+    const int n_active = (key_end - 1) / p.chunk_keys - key_lo / p.chunk_keys + 1;
+    const int chunk_end = min(key_end, c0 + p.chunk_keys);
+    const int n_tiles = (chunk_end - c0 + TILE_KEYS - 1) / TILE_KEYS;
+    const int stage_elems = 2 * TILE_KEYS * pitch;
 
-    load_q_rows(p, row_base, n_rows, qt * 16, n_rep, kv_head, q_smem, pitch, threadIdx.x, 128, 16);
-    // each warp walks its 64 keys in passes of SUB keys (fewer for the largest
-    // head sizes, so that four warps' keys and values fit in shared memory)
-    constexpr int SUB = HD_MAX > 128 ? 32 : TILE_KEYS;
-    __nv_bfloat16* ks = kv_smem + warp * 2 * SUB * pitch;
-    __nv_bfloat16* vs = ks + SUB * pitch;
-    const int key0 = c0 + warp * TILE_KEYS;
+    // the query rows and the first tiles of keys and values, all in flight at once
+    {
+        const int chunks_per_row = p.head_dim >> 3;
+        for (int i = threadIdx.x; i < 16 * chunks_per_row; i += 128) {
+            const int r = i / chunks_per_row, c = i - r * chunks_per_row;
+            const int row = qt * 16 + r;
+            const bool valid = row < n_rows;
+            const int tok = row_base + (valid ? row / n_rep : 0);
+            const int head = kv_head * n_rep + (valid ? row % n_rep : 0);
+            cp_async_16(q_smem + r * pitch + c * 8,
+                        p.qkv + (size_t)tok * p.qkv_stride + (size_t)head * p.head_dim + c * 8, valid);
+        }
+    }
+    KvLoader<HD_MAX, 128> loader;
+    loader.init(p, threadIdx.x);
+#pragma unroll
+    for (int st = 0; st < SPLIT_STAGES; ++st) {
+        if (st < n_tiles) {
+            __nv_bfloat16* ks = kv_smem + st * stage_elems;
+            loader.load(p, table, kv_head, c0 + st * TILE_KEYS, key_end, ks, ks + TILE_KEYS * pitch,
+                        pitch);
+        }
+        cp_async_commit();
+    }
 
     const int row_a = qt * 16 + g, row_b = row_a + 8;
     const int pos_a = row_a < n_rows ? first_pos + row_a / n_rep : -1;
@@ -401,24 +523,31 @@ __global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p
 #pragma unroll
     for (int n = 0; n < HD_MAX / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
-    __syncthreads();             // the query rows (written by all threads) are in place
-#pragma unroll 1
-    for (int s0 = 0; s0 < TILE_KEYS; s0 += SUB) {
-        if (key0 + s0 >= key_end) break;
-        load_kv_tile(p, table, kv_head, key0 + s0, SUB, key_end, ks, vs, pitch, lane, 32);
+    for (int i = 0; i < n_tiles; ++i) {
+        cp_async_wait<SPLIT_STAGES - 1>();
+        __syncthreads();
+        const int st = i % SPLIT_STAGES;
+        const __nv_bfloat16* ks = kv_smem + st * stage_elems;
+        const int key0 = c0 + i * TILE_KEYS + warp * 16;
+        if (key0 < key_end)
+            attend_tile<HD_MAX, 16>(p, q_smem, ks + warp * 16 * pitch,
+                                ks + (TILE_KEYS + warp * 16) * pitch, pitch, 16, key0, pos_a, pos_b,
+                                lo_a, lo_b, key_end, o, m_a, m_b, l_a, l_b);
+        __syncthreads();
+        if (i + SPLIT_STAGES < n_tiles) {
+            __nv_bfloat16* nxt = kv_smem + st * stage_elems;
+            loader.load(p, table, kv_head, c0 + (i + SPLIT_STAGES) * TILE_KEYS, key_end, nxt,
+                        nxt + TILE_KEYS * pitch, pitch);
+        }
         cp_async_commit();
-        cp_async_wait<0>();
-        __syncwarp();
-        attend_tile<HD_MAX>(p, q_smem, ks, vs, pitch, SUB, key0 + s0, pos_a, pos_b, lo_a, lo_b,
-                            key_end, o, m_a, m_b, l_a, l_b);
-        __syncwarp();
     }
+    cp_async_wait<0>();
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
 
-    // merge the four warps (ascending keys) through shared memory, reusing the
+    // merge the four warps (in warp order) through shared memory, reusing the
     // key/value buffers: per warp 16 rows x (head_dim + 2) floats
     __syncthreads();
     float* merge = reinterpret_cast<float*>(kv_smem);
@@ -443,7 +572,6 @@ __global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p
         }
     }
     __syncthreads();
-    // thread -> (row, feature) pairs; write the chunk's partial
     for (int i = threadIdx.x; i < 16 * mp; i += 128) {
         const int r = i / mp, f = i - r * mp;
         const int row = qt * 16 + r;
@@ -465,61 +593,41 @@ __global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p
             }
         }
         const int tok = row_base + row / n_rep, head = kv_head * n_rep + row % n_rep;
-        p.partial[(((size_t)tok * p.n_heads + head) * p.n_chunks + chunk) * mp + f] = v;
-    }
-}
-
-// Merges a row's chunks in ascending order.  One warp per (token, head): the
-// lanes first fetch the chunks' maxima and sums side by side, then every lane
-// sums its features over the chunks with the weights exp2(max_c - max).
-__global__ void attention_merge_kernel(const AttnParams p, const int* __restrict__ positions,
-                                       int n_tokens) {
-    cb_pdl_trigger();
-    cb_pdl_wait();
-    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (unit >= n_tokens * p.n_heads) return;
-    const int lane = threadIdx.x & 31;
-    const int tok = unit / p.n_heads, head = unit - tok * p.n_heads;
-    const int pos = positions[tok];
-    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-    const int mp = p.head_dim + 2;
-    const int c_first = lo / SPLIT_KEYS, c_last = pos / SPLIT_KEYS;
-    const float* base = p.partial + ((size_t)tok * p.n_heads + head) * p.n_chunks * mp;
-    float m = -INFINITY;
-    for (int c = c_first + lane; c <= c_last; c += 32)
-        m = fmaxf(m, base[(size_t)c * mp + p.head_dim]);
-    m = cb_warp_max(m);
-    float l = 0.f;
-    float acc[8];
+        if (n_active == 1) {
+            // the only chunk of these rows: normalise and write the output at once
+            if (f < p.head_dim) {
+                float l = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (int c0 = c_first; c0 <= c_last; c0 += 32) {
-        // this lane's chunk of the group of 32: its weight and weighted sum
-        const int mine = c0 + lane;
-        float w_mine = 0.f, l_mine = 0.f;
-        if (mine <= c_last) {
-            const float mc = base[(size_t)mine * mp + p.head_dim];
-            w_mine = mc == -INFINITY ? 0.f : exp2f(mc - m);
-            l_mine = base[(size_t)mine * mp + p.head_dim + 1] * w_mine;
-        }
-        const int n_here = min(32, c_last - c0 + 1);
-        for (int j = 0; j < n_here; ++j) {               // ascending chunks
-            const float w = __shfl_sync(0xffffffffu, w_mine, j);
-            l += __shfl_sync(0xffffffffu, l_mine, j);
-            const float* src = base + (size_t)(c0 + j) * mp;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int f = lane + 32 * i;
-                if (f < p.head_dim) acc[i] = fmaf(src[f], w, acc[i]);
+                for (int w = 0; w < 4; ++w) {
+                    const float mw = merge[((size_t)w * 16 + r) * mp + p.head_dim];
+                    l += merge[((size_t)w * 16 + r) * mp + p.head_dim + 1] *
+                         (mw == -INFINITY ? 0.f : exp2f(mw - m));
+                }
+                p.out[(size_t)tok * p.out_stride + (size_t)head * p.head_dim + f] =
+                    __float2bfloat16_rn(l > 0.f ? v / l : 0.f);
             }
+        } else {
+            p.partial[(((size_t)tok * p.n_heads + head) * p.n_chunks + chunk) * mp + f] = v;
         }
     }
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
-    __nv_bfloat16* dst = p.out + (size_t)tok * p.out_stride + (size_t)head * p.head_dim;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int f = lane + 32 * i;
-        if (f < p.head_dim) dst[f] = __float2bfloat16_rn(acc[i] * inv);
+    if (n_active == 1) return;
+    // the last block to arrive for these rows merges their chunks
+    int* counter = counters + ((size_t)req * p.n_kv_heads + kv_head) * max_q_tiles + qt;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int prev = atomicAdd(counter, 1);
+        is_last = prev == n_active - 1;
+        if (is_last) *counter = 0;                      // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int r = warp; r < 16; r += 4) {
+        const int row = qt * 16 + r;
+        if (row >= n_rows) break;
+        const int tok = row_base + row / n_rep, head = kv_head * n_rep + row % n_rep;
+        merge_row(p, tok, head, first_pos + row / n_rep, lane);
     }
 }
 
@@ -540,21 +648,20 @@ int launch_tiles(const AttnParams& p, int n_requests, int max_q_tiles, cudaStrea
 }
 
 template <int HD_MAX>
-int launch_split(const AttnParams& p, int n_requests, int max_q_tiles, cudaStream_t s) {
+int launch_split(const AttnParams& p, int n_requests, int max_q_tiles, int* counters, cudaStream_t s) {
     const int pitch = p.head_dim + 8;
-    const int sub = HD_MAX > 128 ? 32 : TILE_KEYS;
-    int smem = (16 + 8 * sub) * pitch * 2;
+    int smem = (16 + SPLIT_STAGES * 2 * TILE_KEYS) * pitch * 2;
     const int merge_bytes = 4 * 16 * (p.head_dim + 2) * 4;
     if (16 * pitch * 2 + merge_bytes > smem) smem = 16 * pitch * 2 + merge_bytes;
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(attention_split_kernel<HD_MAX>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid(max_q_tiles * p.n_chunks, p.n_kv_heads, n_requests);
-    cb_launch(attention_split_kernel<HD_MAX>, dim3(grid), dim3(128), smem, s, p);
+    cb_launch(attention_split_kernel<HD_MAX>, dim3(grid), dim3(128), smem, s, p, counters, max_q_tiles);
     return cb_last_error();
 }
 
@@ -568,9 +675,19 @@ CB_EXPORT long cb_attention_split_scratch_floats(int n_tokens, int n_heads, int 
 
 CB_EXPORT int cb_attention_split_keys() { return SPLIT_KEYS; }
 
+// Counters (ints, zero before the first launch; the kernel leaves them zero) the
+// split form needs.
+CB_EXPORT long cb_attention_split_counters(int n_requests, int n_kv_heads, int max_new_tokens,
+                                           int n_heads) {
+    const int max_rows = max_new_tokens * (n_heads / n_kv_heads);
+    return (long)n_requests * n_kv_heads * ((max_rows + 15) / 16);
+}
+
 // n_chunks == 0: tiles kernel.  n_chunks > 0: split kernel over that many
-// chunks of 256 keys (it must cover the longest context) plus the merge;
-// `partial` must hold cb_attention_split_scratch_floats floats.
+// chunks of chunk_keys keys (a multiple of 256; together they must cover the
+// longest context); `partial` must hold
+// cb_attention_split_scratch_floats floats and `counters`
+// cb_attention_split_counters zeroed ints.
 // max_q_rows: the largest (new tokens x heads per group) of any request.
 CB_EXPORT int cb_attention_mma(const void* qkv, int qkv_stride, void* out, int out_stride,
                                const void* k_cache, const void* v_cache, const int* positions,
@@ -578,7 +695,8 @@ CB_EXPORT int cb_attention_mma(const void* qkv, int qkv_stride, void* out, int o
                                const int* block_table, int table_stride, int n_tokens,
                                int n_requests, int max_new_tokens, int n_heads, int n_kv_heads,
                                int head_dim, int page_tokens, float scale, int window,
-                               float* partial, int n_chunks, void* stream) {
+                               float* partial, int* counters, int n_chunks, int chunk_keys,
+                               void* stream) {
     if (n_tokens <= 0 || n_requests <= 0) return 0;
     if (head_dim <= 0 || head_dim > 256 || (head_dim & 15) || n_heads % n_kv_heads != 0 ||
         (qkv_stride & 7) || (out_stride & 1) || ((uintptr_t)qkv & 15) || ((uintptr_t)k_cache & 15) ||
@@ -603,6 +721,7 @@ CB_EXPORT int cb_attention_mma(const void* qkv, int qkv_stride, void* out, int o
     p.window = window;
     p.partial = partial;
     p.n_chunks = n_chunks;
+    p.chunk_keys = chunk_keys > 0 ? chunk_keys : SPLIT_KEYS;
     cudaStream_t s = (cudaStream_t)stream;
     const int n_rep = n_heads / n_kv_heads;
     const int max_rows = max_new_tokens * n_rep;
@@ -616,17 +735,13 @@ CB_EXPORT int cb_attention_mma(const void* qkv, int qkv_stride, void* out, int o
         else rc = launch_tiles<256>(p, n_requests, q_tiles, s);
         return rc;
     }
-    if (partial == nullptr) return CB_ERR_UNSUPPORTED;
+    if (partial == nullptr || counters == nullptr || (chunk_keys % SPLIT_KEYS) != 0)
+        return CB_ERR_UNSUPPORTED;
     const int q_tiles = (max_rows + 15) / 16;
-    if (head_dim <= 16) rc = launch_split<16>(p, n_requests, q_tiles, s);
-    else if (head_dim <= 32) rc = launch_split<32>(p, n_requests, q_tiles, s);
-    else if (head_dim <= 64) rc = launch_split<64>(p, n_requests, q_tiles, s);
-    else if (head_dim <= 128) rc = launch_split<128>(p, n_requests, q_tiles, s);
-    else rc = launch_split<256>(p, n_requests, q_tiles, s);
-    if (rc != 0) return rc;
-    const int warps = 4;
-    const long units = (long)n_tokens * n_heads;
-    cb_launch(attention_merge_kernel, dim3((int)((units + warps - 1) / warps)), dim3(warps * 32), 0, s, p, positions,
-                                                                                    n_tokens);
-    return cb_last_error();
+    if (head_dim <= 16) rc = launch_split<16>(p, n_requests, q_tiles, counters, s);
+    else if (head_dim <= 32) rc = launch_split<32>(p, n_requests, q_tiles, counters, s);
+    else if (head_dim <= 64) rc = launch_split<64>(p, n_requests, q_tiles, counters, s);
+    else if (head_dim <= 128) rc = launch_split<128>(p, n_requests, q_tiles, counters, s);
+    else rc = launch_split<256>(p, n_requests, q_tiles, counters, s);
+    return rc;
 }

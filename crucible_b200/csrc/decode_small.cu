@@ -1,26 +1,37 @@
 // Matrix products for steps of at most 8 rows (a few decoded tokens), fused
 // with what stands before and after them.  Such a step only streams the
 // weights once; what decides its time is the length of each kernel's chain of
-// dependent memory round trips and the number of kernels.  So these run on CUDA
-// cores with plain 16-byte loads (no descriptor fetch, no barrier, no tensor-
-// memory allocation in the chain) and each replaces two or three launches:
+// dependent memory round trips and the number of kernels.  So these kernels
+// read the weights with plain 16-byte loads that are issued before anything
+// else (no descriptor fetch, no barrier, no tensor-memory allocation in the
+// chain), multiply on the tensor cores with mma.sync m16n8k16 (16 rows of W
+// against the step's up to 8 rows, fp32 accumulation), and each replaces two or
+// three launches:
 //
 //   NORM_IN   the input is the fp32 residual stream; RMSNorm (fp32 statistics
 //             and gain) is applied while it is staged in shared memory, so the
-//             normalised row never goes to global memory and is not rounded;
+//             normalised rows never go to global memory;
 //   epilogues ACCUM_F32    out[m, n] += dot               (output projections)
 //             STORE_F32    out[m, n]  = dot               (logits)
 //             SWIGLU_BF16  out[m, i]  = silu(g_i) * u_i   (gate and up rows paired)
 //             ROPE_APPEND  rows (j, j + hd/2) of a head paired: q rotated and
 //                          stored, k rotated into the request's cache page,
 //                          v copied into it.
-// One warp computes two rows of W against all rows of the step; every dot
-// product is one fp32 sum whose order depends on K alone.
+// A block owns 16 rows of W: 8 "first" rows and their 8 partners (the next 8
+// rows, the matching up rows, or the other half of the rotary pairs), so that
+// both members of a pair end in the same thread.  Its four warps split K in
+// blocks of 32 elements and their partial sums are added in warp order, so a
+// dot product's summation order depends on K alone.
+//
+// Within a block of 32 elements along K, thread t of a quad loads elements
+// [8t, 8t + 8) of its two W rows and of its row of the step with one 16-byte
+// load each, and feeds them to two MMAs as "k = 2t, 2t+1, 2t+8, 2t+9": the same
+// permutation of k on both operands, which a dot product does not see.
 //
 // Sizes: at most 8 rows; K a multiple of 8 with 16-byte aligned weight rows;
 // ROPE_APPEND needs the whole head rotated (rotary_dim == head_dim).  Anything
 // else is refused and the caller runs the general kernels.
-// Reference counterparts: `gemv_f32_warp` (engine/kernels/kernels.cu:549),
+// Reference counterparts: `gemv_batch_i8_b*` (engine/kernels/kernels.cu:1598),
 // `mlp_swiglu_f32` (:637), `rope_rows_f32` (:1677), `cache_store_rows_paged_f32`
 // (:1713).
 #include "common.cuh"
@@ -38,7 +49,7 @@ struct SmallParams {
     const __nv_bfloat16* w;       // [rows, K], ldw elements between rows
     int ldw;
     int M, K, N;                  // N: output columns (SWIGLU: the intermediate width)
-    int n_tasks;
+    int n_tiles;
     void* out;                    // ACCUM/STORE: fp32 [M, ldc]; SWIGLU: bf16 [M, ldc]; ROPE: bf16 q [M, ldc]
     int ldc;
     // ROPE_APPEND
@@ -53,230 +64,244 @@ struct SmallParams {
     int n_heads, n_kv_heads, head_dim, page_tokens, write_cache;
 };
 
-__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 t = __bfloat1622float2(h[i]);
-        f[2 * i] = t.x;
-        f[2 * i + 1] = t.y;
-    }
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+        "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int MB, bool NORM_IN, int EPI, int CH>
-__global__ void __launch_bounds__(128) small_linear_kernel(const SmallParams p) {
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+constexpr int WARPS = 4;
+constexpr int BATCH = 8;          // blocks of 32 elements a warp keeps in flight per row
+
+template <bool NORM_IN, int EPI>
+__global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallParams p) {
     cb_pdl_trigger();
-    extern __shared__ __align__(16) float xs[];          // [M][K]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
     const int K = p.K;
-    const int task = blockIdx.x * n_warps + warp;
-    const bool valid = task < p.n_tasks;
-    // ---- the two rows of W this warp owns ----------------------------------------------
-    int r0 = 0, r1 = 0;
-    bool has1 = true;
-    if (valid) {
-        if (EPI == SWIGLU_BF16) {
-            r0 = task;
-            r1 = p.N + task;
-        } else if (EPI == ROPE_APPEND) {
-            const int half = p.head_dim >> 1;
-            const int head = task / half, j = task - head * half;
-            r0 = head * p.head_dim + j;
-            r1 = r0 + half;
-        } else {
-            r0 = 2 * task;
-            r1 = r0 + 1;
-            has1 = r1 < p.N;
-        }
+    const int pitch = K + 32;                             // bf16 elements; staggers the rows over the banks
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [8][pitch]
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)8 * pitch * 2);   // [WARPS][32][4]
+    const int tile = blockIdx.x;
+    // ---- this thread's two rows of W: first row g of the tile, and its partner ------------
+    int rf, rs;
+    bool ok_f, ok_s;
+    if (EPI == SWIGLU_BF16) {
+        rf = tile * 8 + g;
+        ok_f = ok_s = rf < p.N;
+        rs = p.N + rf;
+    } else if (EPI == ROPE_APPEND) {
+        const int half = p.head_dim >> 1;
+        const int pair = tile * 8 + g;
+        const int head = pair / half, j = pair - head * half;
+        const int heads = p.write_cache ? p.n_heads + 2 * p.n_kv_heads : p.n_heads;
+        ok_f = ok_s = head < heads;
+        rf = head * p.head_dim + j;
+        rs = rf + half;
+    } else {
+        rf = tile * 16 + g;
+        rs = rf + 8;
+        ok_f = rf < p.N;
+        ok_s = rs < p.N;
     }
-    const __nv_bfloat16* w0 = p.w + (size_t)r0 * p.ldw;
-    const __nv_bfloat16* w1 = p.w + (size_t)(has1 ? r1 : r0) * p.ldw;
-    const int n_chunks = (K + 255) >> 8;                 // 256 elements per warp and chunk
+    const __nv_bfloat16* wf = p.w + (size_t)(ok_f ? rf : 0) * p.ldw + t * 8;
+    const __nv_bfloat16* ws = p.w + (size_t)(ok_s ? rs : 0) * p.ldw + t * 8;
+    const int k_blocks = (K + 31) >> 5;
     // The first batch of weight loads goes out before anything else: it depends on
     // nothing, and the staging of the step's rows below hides under its latency.
-    uint4 v0[CH], v1[CH];
+    uint4 vf[BATCH], vs[BATCH];
 #pragma unroll
-    for (int c = 0; c < CH; ++c) {
-        const int k = (c * 32 + lane) * 8;
-        if (valid && c < n_chunks && k < K) {
-            v0[c] = __ldg(reinterpret_cast<const uint4*>(w0 + k));
-            v1[c] = __ldg(reinterpret_cast<const uint4*>(w1 + k));
-        } else {
-            v0[c] = v1[c] = make_uint4(0, 0, 0, 0);
-        }
+    for (int i = 0; i < BATCH; ++i) {
+        const int kb = warp + i * WARPS;
+        const bool in = kb < k_blocks && kb * 32 + t * 8 < K;
+        vf[i] = in ? __ldg(reinterpret_cast<const uint4*>(wf + kb * 32)) : make_uint4(0, 0, 0, 0);
+        vs[i] = in ? __ldg(reinterpret_cast<const uint4*>(ws + kb * 32)) : make_uint4(0, 0, 0, 0);
     }
     // the weights above are written by no kernel; everything below reads what earlier
     // kernels of the stream produced
     cb_pdl_wait();
-    float old0 = 0.f, old1 = 0.f;                        // ACCUM: the residual values, fetched early
-    if (EPI == ACCUM_F32 && valid && lane < p.M) {
-        const float* out = (const float*)p.out + (size_t)lane * p.ldc;
-        old0 = out[r0];
-        if (has1) old1 = out[r1];
-    }
-    // ---- stage the step's rows in shared memory (normalised if asked) -------------------
-    // 16-byte loads, unrolled so that a row's loads are in flight together: these few
-    // round trips are the whole prologue of the kernel.
+    // ---- stage the step's rows in shared memory as bf16 (normalised if asked) -------------
     if (NORM_IN) {
+        // each warp normalises rows `warp` and `warp + 4` side by side, so that both
+        // rows' loads are in flight together
         const int n4 = K >> 2;
         const float4* g4 = reinterpret_cast<const float4*>(p.gain);
-        for (int m = warp; m < p.M; m += n_warps) {
-            const float4* row4 = reinterpret_cast<const float4*>(p.x + (size_t)m * K);
-            float ss = 0.f;
-#pragma unroll 8
+        const int ma = warp, mb = warp + WARPS;
+        const bool has_a = ma < p.M, has_b = mb < p.M;
+        const float4* row_a = reinterpret_cast<const float4*>(p.x + (size_t)(has_a ? ma : 0) * K);
+        const float4* row_b = reinterpret_cast<const float4*>(p.x + (size_t)(has_b ? mb : 0) * K);
+        uint2* dst_a = reinterpret_cast<uint2*>(xs + (size_t)ma * pitch);
+        uint2* dst_b = reinterpret_cast<uint2*>(xs + (size_t)mb * pitch);
+        float ss_a = 0.f, ss_b = 0.f;
+        if (has_a) {
+#pragma unroll 4
             for (int j = lane; j < n4; j += 32) {
-                const float4 v = row4[j];
-                ss = fmaf(v.x, v.x, ss);
-                ss = fmaf(v.y, v.y, ss);
-                ss = fmaf(v.z, v.z, ss);
-                ss = fmaf(v.w, v.w, ss);
+                const float4 va = row_a[j];
+                const float4 vb = has_b ? row_b[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+                ss_a = fmaf(va.x, va.x, ss_a); ss_a = fmaf(va.y, va.y, ss_a);
+                ss_a = fmaf(va.z, va.z, ss_a); ss_a = fmaf(va.w, va.w, ss_a);
+                ss_b = fmaf(vb.x, vb.x, ss_b); ss_b = fmaf(vb.y, vb.y, ss_b);
+                ss_b = fmaf(vb.z, vb.z, ss_b); ss_b = fmaf(vb.w, vb.w, ss_b);
             }
-            ss = cb_warp_sum(ss);
-            const float r = 1.0f / sqrtf(ss / (float)K + p.eps);
-            float4* dst4 = reinterpret_cast<float4*>(xs + m * K);
-#pragma unroll 8
-            for (int j = lane; j < n4; j += 32) {
-                const float4 v = row4[j];
-                const float4 g = g4[j];
-                dst4[j] = make_float4(v.x * r * g.x, v.y * r * g.y, v.z * r * g.z, v.w * r * g.w);
+        }
+        ss_a = cb_warp_sum(ss_a);
+        ss_b = cb_warp_sum(ss_b);
+        const float r_a = 1.0f / sqrtf(ss_a / (float)K + p.eps);
+        const float r_b = 1.0f / sqrtf(ss_b / (float)K + p.eps);
+#pragma unroll 4
+        for (int j = lane; j < n4; j += 32) {
+            uint2 oa = make_uint2(0, 0), ob = make_uint2(0, 0);
+            if (has_a) {
+                const float4 gn = g4[j];
+                const float4 va = row_a[j];
+                oa = make_uint2(pack2(va.x * r_a * gn.x, va.y * r_a * gn.y),
+                                pack2(va.z * r_a * gn.z, va.w * r_a * gn.w));
+                if (has_b) {
+                    const float4 vb = row_b[j];
+                    ob = make_uint2(pack2(vb.x * r_b * gn.x, vb.y * r_b * gn.y),
+                                    pack2(vb.z * r_b * gn.z, vb.w * r_b * gn.w));
+                }
             }
+            dst_a[j] = oa;
+            dst_b[j] = ob;
         }
     } else {
         const int n8 = K >> 3;
-        const int total = p.M * n8;
 #pragma unroll 4
-        for (int i = threadIdx.x; i < total; i += blockDim.x) {
+        for (int i = threadIdx.x; i < 8 * n8; i += blockDim.x) {
             const int m = i / n8, c = i - m * n8;
-            const uint4 v = *reinterpret_cast<const uint4*>(p.a + (size_t)m * p.lda + c * 8);
-            float f[8];
-            unpack8(v, f);
-            float4* dst4 = reinterpret_cast<float4*>(xs + m * K + c * 8);
-            dst4[0] = make_float4(f[0], f[1], f[2], f[3]);
-            dst4[1] = make_float4(f[4], f[5], f[6], f[7]);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (m < p.M) v = *reinterpret_cast<const uint4*>(p.a + (size_t)m * p.lda + c * 8);
+            *reinterpret_cast<uint4*>(xs + (size_t)m * pitch + c * 8) = v;
+        }
+    }
+    // ACCUM: the residual values this block will add to, fetched while the rows settle
+    float old[4] = {0.f, 0.f, 0.f, 0.f};
+    const int m0 = 2 * t, m1 = 2 * t + 1;
+    if (EPI == ACCUM_F32 && warp == 0) {
+        const float* out = (const float*)p.out;
+        if (m0 < p.M && ok_f) old[0] = out[(size_t)m0 * p.ldc + rf];
+        if (m1 < p.M && ok_f) old[1] = out[(size_t)m1 * p.ldc + rf];
+        if (m0 < p.M && ok_s) old[2] = out[(size_t)m0 * p.ldc + rs];
+        if (m1 < p.M && ok_s) old[3] = out[(size_t)m1 * p.ldc + rs];
+    }
+    // ROPE_APPEND: positions, rotation factors and cache pages of the two step rows this
+    // thread will finish, fetched now so that their round trips overlap the multiply
+    int pos2[2] = {0, 0}, page2[2] = {0, 0};
+    float cs2[2] = {1.f, 1.f}, sn2[2] = {0.f, 0.f};
+    if (EPI == ROPE_APPEND && warp == 0 && ok_f) {
+        const int half = p.head_dim >> 1;
+        const int pair = tile * 8 + g;
+        const int head = pair / half, j = pair - head * half;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int m = 2 * t + e;
+            if (m < p.M) {
+                pos2[e] = p.positions[m];
+                if (head >= p.n_heads)
+                    page2[e] = p.block_table[(size_t)p.row_request[m] * p.table_stride +
+                                             pos2[e] / p.page_tokens];
+                if (head < p.n_heads + p.n_kv_heads) {
+                    cs2[e] = p.cos_t[(size_t)pos2[e] * half + j];
+                    sn2[e] = p.sin_t[(size_t)pos2[e] * half + j];
+                }
+            }
         }
     }
     __syncthreads();
-    if (!valid) return;
-    float acc0[MB], acc1[MB];
+    // ---- multiply: this warp's blocks of K -------------------------------------------------
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    const __nv_bfloat16* xrow = xs + (size_t)g * pitch + t * 8;
+    for (int kb0 = 0; kb0 < k_blocks; kb0 += BATCH * WARPS) {
+        if (kb0 > 0) {
 #pragma unroll
-    for (int m = 0; m < MB; ++m) acc0[m] = acc1[m] = 0.f;
-    for (int c0 = 0; c0 < n_chunks; c0 += CH) {
-        if (c0 > 0) {
-#pragma unroll
-            for (int c = 0; c < CH; ++c) {
-                const int k = ((c0 + c) * 32 + lane) * 8;
-                if (c0 + c < n_chunks && k < K) {
-                    v0[c] = __ldg(reinterpret_cast<const uint4*>(w0 + k));
-                    v1[c] = __ldg(reinterpret_cast<const uint4*>(w1 + k));
-                } else {
-                    v0[c] = v1[c] = make_uint4(0, 0, 0, 0);
-                }
+            for (int i = 0; i < BATCH; ++i) {
+                const int kb = kb0 + warp + i * WARPS;
+                const bool in = kb < k_blocks && kb * 32 + t * 8 < K;
+                vf[i] = in ? __ldg(reinterpret_cast<const uint4*>(wf + kb * 32)) : make_uint4(0, 0, 0, 0);
+                vs[i] = in ? __ldg(reinterpret_cast<const uint4*>(ws + kb * 32)) : make_uint4(0, 0, 0, 0);
             }
         }
 #pragma unroll
-        for (int c = 0; c < CH; ++c) {
-            const int k = ((c0 + c) * 32 + lane) * 8;
-            if (c0 + c < n_chunks && k < K) {
-                float f0[8], f1[8];
-                unpack8(v0[c], f0);
-                unpack8(v1[c], f1);
-#pragma unroll
-                for (int m = 0; m < MB; ++m) {
-                    if (m < p.M) {
-                        const float4 xa = *reinterpret_cast<const float4*>(xs + m * K + k);
-                        const float4 xb = *reinterpret_cast<const float4*>(xs + m * K + k + 4);
-                        acc0[m] = fmaf(f0[0], xa.x, acc0[m]); acc1[m] = fmaf(f1[0], xa.x, acc1[m]);
-                        acc0[m] = fmaf(f0[1], xa.y, acc0[m]); acc1[m] = fmaf(f1[1], xa.y, acc1[m]);
-                        acc0[m] = fmaf(f0[2], xa.z, acc0[m]); acc1[m] = fmaf(f1[2], xa.z, acc1[m]);
-                        acc0[m] = fmaf(f0[3], xa.w, acc0[m]); acc1[m] = fmaf(f1[3], xa.w, acc1[m]);
-                        acc0[m] = fmaf(f0[4], xb.x, acc0[m]); acc1[m] = fmaf(f1[4], xb.x, acc1[m]);
-                        acc0[m] = fmaf(f0[5], xb.y, acc0[m]); acc1[m] = fmaf(f1[5], xb.y, acc1[m]);
-                        acc0[m] = fmaf(f0[6], xb.z, acc0[m]); acc1[m] = fmaf(f1[6], xb.z, acc1[m]);
-                        acc0[m] = fmaf(f0[7], xb.w, acc0[m]); acc1[m] = fmaf(f1[7], xb.w, acc1[m]);
-                    }
-                }
+        for (int i = 0; i < BATCH; ++i) {
+            const int kb = kb0 + warp + i * WARPS;
+            if (kb < k_blocks) {                          // warp-uniform
+                uint4 xb = make_uint4(0, 0, 0, 0);
+                if (kb * 32 + t * 8 < K) xb = *reinterpret_cast<const uint4*>(xrow + kb * 32);
+                mma_bf16(c, vf[i].x, vs[i].x, vf[i].y, vs[i].y, xb.x, xb.y);
+                mma_bf16(c, vf[i].z, vs[i].z, vf[i].w, vs[i].w, xb.z, xb.w);
             }
         }
     }
-    // ---- reduce over the warp; lane m keeps row m's two sums -------------------------
-    float d0 = 0.f, d1 = 0.f;
+    // ---- add the warps' partial sums in warp order; warp 0 finishes ------------------------
+    float4* mine = reinterpret_cast<float4*>(red) + warp * 32 + lane;
+    *mine = make_float4(c[0], c[1], c[2], c[3]);
+    __syncthreads();
+    if (warp != 0) return;
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int m = 0; m < MB; ++m) {
-        const float s0 = cb_warp_sum(acc0[m]);
-        const float s1 = cb_warp_sum(acc1[m]);
-        if (lane == m) { d0 = s0; d1 = s1; }
+    for (int w = 0; w < WARPS; ++w) {
+        const float4 v = reinterpret_cast<const float4*>(red)[w * 32 + lane];
+        d[0] += v.x; d[1] += v.y; d[2] += v.z; d[3] += v.w;
     }
-    if (lane >= p.M) return;
-    const int m = lane;
-    if (EPI == ACCUM_F32 || EPI == STORE_F32) {
-        float* out = (float*)p.out + (size_t)m * p.ldc;
-        if (EPI == ACCUM_F32) {
-            out[r0] = old0 + d0;
-            if (has1) out[r1] = old1 + d1;
-        } else {
-            out[r0] = d0;
-            if (has1) out[r1] = d1;
-        }
-    } else if (EPI == SWIGLU_BF16) {
-        ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + task] =
-            __float2bfloat16_rn(d0 / (1.0f + expf(-d0)) * d1);
-    } else {
-        const int half = p.head_dim >> 1;
-        const int head = task / half, j = task - head * half;
-        const int pos = p.positions[m];
-        if (head < p.n_heads + p.n_kv_heads) {           // q or k: rotate
-            const float c = p.cos_t[(size_t)pos * half + j], s = p.sin_t[(size_t)pos * half + j];
-            const float y0 = d0 * c - d1 * s, y1 = d0 * s + d1 * c;
-            d0 = y0;
-            d1 = y1;
-        }
-        if (head < p.n_heads) {
-            __nv_bfloat16* q = (__nv_bfloat16*)p.out + (size_t)m * p.ldc + (size_t)head * p.head_dim;
-            q[j] = __float2bfloat16_rn(d0);
-            q[j + half] = __float2bfloat16_rn(d1);
-        } else if (p.write_cache) {
-            const int page = p.block_table[(size_t)p.row_request[m] * p.table_stride + pos / p.page_tokens];
-            const bool is_k = head < p.n_heads + p.n_kv_heads;
-            const int kvh = is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
-            __nv_bfloat16* dst = (is_k ? p.k_cache : p.v_cache) +
-                (((size_t)page * p.page_tokens + pos % p.page_tokens) * p.n_kv_heads + kvh) * p.head_dim;
-            dst[j] = __float2bfloat16_rn(d0);
-            dst[j + half] = __float2bfloat16_rn(d1);
+    // d[0], d[1]: first row x step rows 2t, 2t+1;  d[2], d[3]: partner row x the same
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int m = e == 0 ? m0 : m1;
+        if (m >= p.M) continue;
+        const float df = d[e], ds = d[2 + e];
+        if (EPI == ACCUM_F32 || EPI == STORE_F32) {
+            float* out = (float*)p.out + (size_t)m * p.ldc;
+            if (ok_f) out[rf] = EPI == ACCUM_F32 ? old[e] + df : df;
+            if (ok_s) out[rs] = EPI == ACCUM_F32 ? old[2 + e] + ds : ds;
+        } else if (EPI == SWIGLU_BF16) {
+            if (ok_f)
+                ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + rf] =
+                    __float2bfloat16_rn(df / (1.0f + expf(-df)) * ds);
+        } else if (ok_f) {
+            const int half = p.head_dim >> 1;
+            const int pair = tile * 8 + g;
+            const int head = pair / half, j = pair - head * half;
+            const int pos = pos2[e];
+            const float y0 = df * cs2[e] - ds * sn2[e];   // v heads keep cos 1, sin 0
+            const float y1 = df * sn2[e] + ds * cs2[e];
+            if (head < p.n_heads) {
+                __nv_bfloat16* q = (__nv_bfloat16*)p.out + (size_t)m * p.ldc + (size_t)head * p.head_dim;
+                q[j] = __float2bfloat16_rn(y0);
+                q[j + half] = __float2bfloat16_rn(y1);
+            } else {
+                const bool is_k = head < p.n_heads + p.n_kv_heads;
+                const int kvh = is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
+                __nv_bfloat16* dst = (is_k ? p.k_cache : p.v_cache) +
+                    (((size_t)page2[e] * p.page_tokens + pos % p.page_tokens) * p.n_kv_heads + kvh) * p.head_dim;
+                dst[j] = __float2bfloat16_rn(y0);
+                dst[j + half] = __float2bfloat16_rn(y1);
+            }
         }
     }
-}
-
-template <int MB, bool NORM_IN, int EPI, int CH>
-int launch_ch(const SmallParams& p, cudaStream_t s) {
-    // two warps per block while the tasks are few, so that enough blocks pull on memory
-    const int warps = p.n_tasks < 148 * 4 ? 2 : 4;
-    const int smem = p.M * p.K * 4;
-    static int configured = 0;
-    if (smem > 48 * 1024 && smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(small_linear_kernel<MB, NORM_IN, EPI, CH>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = smem;
-    }
-    const int blocks = (p.n_tasks + warps - 1) / warps;
-    cb_launch(small_linear_kernel<MB, NORM_IN, EPI, CH>, dim3(blocks), dim3(warps * 32), smem, s, p);
-    return cb_last_error();
-}
-
-// Weight loads kept in flight per lane: 4 chunks of 256 elements cover K <= 1024
-// in one batch, 8 cover K <= 2048.
-template <int MB, bool NORM_IN, int EPI>
-int launch(const SmallParams& p, cudaStream_t s) {
-    if (p.K <= 1024) return launch_ch<MB, NORM_IN, EPI, 4>(p, s);
-    return launch_ch<MB, NORM_IN, EPI, 8>(p, s);
 }
 
 template <bool NORM_IN, int EPI>
 int launch_rows(const SmallParams& p, cudaStream_t s) {
-    if (p.M <= 1) return launch<1, NORM_IN, EPI>(p, s);
-    if (p.M <= 2) return launch<2, NORM_IN, EPI>(p, s);
-    if (p.M <= 4) return launch<4, NORM_IN, EPI>(p, s);
-    return launch<8, NORM_IN, EPI>(p, s);
+    const int smem = 8 * (p.K + 32) * 2 + WARPS * 32 * 16;
+    static int configured = 0;
+    if (smem > 48 * 1024 && smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(small_linear_kernel<NORM_IN, EPI>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = smem;
+    }
+    cb_launch(small_linear_kernel<NORM_IN, EPI>, dim3(p.n_tiles), dim3(WARPS * 32), smem, s, p);
+    return cb_last_error();
 }
 
 bool sizes_ok(const float* x, const float* gain, const void* a, int lda, int M, int K, int ldw,
@@ -284,7 +309,7 @@ bool sizes_ok(const float* x, const float* gain, const void* a, int lda, int M, 
     if (x ? (((uintptr_t)x & 15) || ((uintptr_t)gain & 15)) : (((uintptr_t)a & 15) || (lda & 7)))
         return false;
     return M >= 1 && M <= 8 && K > 0 && (K & 7) == 0 && (ldw & 7) == 0 && ((uintptr_t)w & 15) == 0 &&
-           (size_t)M * K * 4 <= 200 * 1024;
+           (size_t)8 * (K + 32) * 2 <= 200 * 1024;
 }
 
 }  // namespace
@@ -299,7 +324,7 @@ CB_EXPORT int cb_small_linear(const float* x, const float* gain, float eps, cons
     SmallParams p = {};
     p.x = x; p.gain = gain; p.eps = eps; p.a = (const __nv_bfloat16*)a; p.lda = lda;
     p.w = (const __nv_bfloat16*)w; p.ldw = ldw; p.M = M; p.K = K; p.N = N;
-    p.n_tasks = (N + 1) / 2; p.out = out; p.ldc = ldc;
+    p.n_tiles = (N + 15) / 16; p.out = out; p.ldc = ldc;
     cudaStream_t s = (cudaStream_t)stream;
     if (x) return accumulate ? launch_rows<true, ACCUM_F32>(p, s) : launch_rows<true, STORE_F32>(p, s);
     return accumulate ? launch_rows<false, ACCUM_F32>(p, s) : launch_rows<false, STORE_F32>(p, s);
@@ -314,7 +339,7 @@ CB_EXPORT int cb_small_swiglu(const float* x, const float* gain, float eps, cons
     SmallParams p = {};
     p.x = x; p.gain = gain; p.eps = eps; p.a = (const __nv_bfloat16*)a; p.lda = lda;
     p.w = (const __nv_bfloat16*)w; p.ldw = ldw; p.M = M; p.K = K; p.N = inter;
-    p.n_tasks = inter; p.out = out; p.ldc = ldc;
+    p.n_tiles = (inter + 7) / 8; p.out = out; p.ldc = ldc;
     cudaStream_t s = (cudaStream_t)stream;
     return x ? launch_rows<true, SWIGLU_BF16>(p, s) : launch_rows<false, SWIGLU_BF16>(p, s);
 }
@@ -337,7 +362,7 @@ CB_EXPORT int cb_small_qkv_rope_append(const float* x, const float* gain, float 
     p.w = (const __nv_bfloat16*)w; p.ldw = ldw; p.M = M; p.K = K;
     p.N = (n_heads + 2 * n_kv_heads) * head_dim;
     const int heads = write_cache ? n_heads + 2 * n_kv_heads : n_heads;
-    p.n_tasks = heads * (head_dim / 2);
+    p.n_tiles = (heads * (head_dim / 2) + 7) / 8;
     p.out = q_out; p.ldc = ldq;
     p.cos_t = cos_t; p.sin_t = sin_t; p.positions = positions; p.row_request = row_request;
     p.block_table = block_table; p.table_stride = table_stride;

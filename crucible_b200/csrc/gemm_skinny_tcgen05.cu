@@ -233,15 +233,20 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
     } else if (writer && epi_warp) {
         const int col = tile * WM + w_row;
         if (col < N) {
+            if (EPI == ACCUM_F32) {
+                // all residual values first (independent loads), then the sums
+                const float* src = (const float*)c_ptr + col;
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+                    if (m < M) acc[m] += __ldcg(src + (size_t)m * ldc);
+            }
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
                 if (m < M) {
-                    if (EPI == STORE_BF16) {
+                    if (EPI == STORE_BF16)
                         ((__nv_bfloat16*)c_ptr)[(size_t)m * ldc + col] = __float2bfloat16_rn(acc[m]);
-                    } else {
-                        float* dst = (float*)c_ptr + (size_t)m * ldc + col;
-                        *dst = EPI == ACCUM_F32 ? *dst + acc[m] : acc[m];
-                    }
+                    else
+                        ((float*)c_ptr)[(size_t)m * ldc + col] = acc[m];
                 }
             }
         }

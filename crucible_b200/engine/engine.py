@@ -100,6 +100,7 @@ class Engine:
         self._graph_generation = 0
         self._graph_failed = False
         self._graph_error = None
+        self._table_rows = {}
 
     def _meta_buffers(self, n: int):
         if self._meta_dev is None or self._meta_dev.numel() < n:
@@ -144,6 +145,8 @@ class Engine:
     def finish(self, request) -> None:
         """Gives back everything the request holds.  Call between steps only."""
         self.cache.remove_request(request)
+        for g in range(len(self.table_strides)):
+            self._table_rows.pop((request, g), None)
 
     def held_tokens(self, request) -> int:
         return self.cache.length(request)
@@ -234,8 +237,11 @@ class Engine:
     def _validate(self, entries: List[StepEntry]) -> None:
         if not entries:
             raise StepError("a step needs at least one entry")
+        cache = self.cache
         seen = set()
         new_requests = 0
+        max_context = self.config.max_context
+        vocab = self.config.vocab_size
         for e in entries:
             if e.request in seen:
                 raise StepError(f"request {e.request!r} appears twice in one step")
@@ -243,33 +249,70 @@ class Engine:
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"request {e.request!r} brings no tokens")
-            held = self.cache.length(e.request) if self.cache.has(e.request) else 0
-            if not self.cache.has(e.request):
+            if min(e.tokens) < 0 or max(e.tokens) >= vocab:
+                bad = next(t for t in e.tokens if not 0 <= t < vocab)
+                raise StepError(f"request {e.request!r}: token {bad} is outside the "
+                                f"vocabulary of {vocab}")
+            if cache.has(e.request):
+                held = cache.length(e.request)
+            else:
+                held = 0
                 new_requests += 1
-            if held + n > self.config.max_context:
+            if held + n > max_context:
                 raise StepError(f"request {e.request!r} would hold {held + n} tokens; the "
-                                f"model's context is {self.config.max_context}")
-            for tok in e.tokens:
-                if not 0 <= int(tok) < self.config.vocab_size:
-                    raise StepError(f"request {e.request!r}: token {tok} is outside the "
-                                    f"vocabulary of {self.config.vocab_size}")
-            last = -1
-            for w in e.want:
-                if not 0 <= int(w) < n:
-                    raise StepError(f"request {e.request!r}: wanted place {w} is outside its "
-                                    f"{n} tokens")
-                if int(w) <= last:
-                    raise StepError(f"request {e.request!r}: wanted places must ascend")
-                last = int(w)
-        if new_requests > self.cache.slots.free_slots:
+                                f"model's context is {max_context}")
+            want = e.want
+            if len(want) == 1:
+                if not 0 <= int(want[0]) < n:
+                    raise StepError(f"request {e.request!r}: wanted place {want[0]} is outside "
+                                    f"its {n} tokens")
+            elif want:
+                last = -1
+                for w in want:
+                    if not 0 <= int(w) < n:
+                        raise StepError(f"request {e.request!r}: wanted place {w} is outside its "
+                                        f"{n} tokens")
+                    if int(w) <= last:
+                        raise StepError(f"request {e.request!r}: wanted places must ascend")
+                    last = int(w)
+        if new_requests > cache.slots.free_slots:
             raise StepError(f"{new_requests} new requests but only "
-                            f"{self.cache.slots.free_slots} of {self.options.max_requests} "
+                            f"{cache.slots.free_slots} of {self.options.max_requests} "
                             f"request slots are free")
 
+    def _table_row(self, request, group: int) -> np.ndarray:
+        """The request's block table of `group`, padded to the table stride, kept as a
+        numpy row that is only touched when the table changed."""
+        table = self.cache.block_table(request, group)
+        key = (request, group)
+        row, known = self._table_rows.get(key, (None, 0))
+        n_pages = self.cache.pools[group].n_pages
+        if row is None:
+            row = np.zeros(self.table_strides[group], dtype=np.int32)
+            known = 0
+        windowed = self.cache.policies[group].window is not None
+        if windowed or len(table) < known:
+            row[:len(table)] = table          # early releases rewrite entries: copy it all
+            row[len(table):] = 0
+            fresh = table
+        elif len(table) > known:
+            fresh = table[known:]
+            row[known:len(table)] = fresh
+        else:
+            fresh = ()
+        for page in fresh:
+            if page != RELEASED and not 0 <= page < n_pages:
+                raise StepError(f"page {page} of request {request!r} is out of range")
+        self._table_rows[key] = (row, len(table))
+        return row
+
     def _make_context(self, entries: List[StepEntry]) -> StepContext:
-        n_tokens = sum(len(e.tokens) for e in entries)
+        cache = self.cache
+        counts = [len(e.tokens) for e in entries]
+        n_tokens = sum(counts)
         n_want = sum(len(e.want) for e in entries)
-        layout = StepLayout(n_tokens, len(entries), n_want, self.table_strides)
+        n_req = len(entries)
+        layout = StepLayout(n_tokens, n_req, n_want, self.table_strides)
         off = layout.offsets()
         total = off["_total"][1]
         host_t, dev_t = self._meta_buffers(total)
@@ -279,45 +322,41 @@ class Engine:
             a, n = off[name]
             return host[a:a + n]
 
-        token_ids, positions = piece("token_ids"), piece("positions")
-        row_request, logit_rows = piece("row_request"), piece("logit_rows")
-        row_start, ctx_len = piece("req_row_start"), piece("req_context_len")
-        first_pos, state_slot = piece("req_first_pos"), piece("req_state_slot")
-        hs = HostStep([], [], [], [], [])
-        row = 0
-        w_at = 0
-        for r, e in enumerate(entries):
-            n = len(e.tokens)
-            held_after = self.cache.length(e.request)
-            start = held_after - n
-            token_ids[row:row + n] = np.asarray(e.tokens, dtype=np.int32)
-            positions[row:row + n] = np.arange(start, held_after, dtype=np.int32)
-            row_request[row:row + n] = r
-            for w in e.want:
-                logit_rows[w_at] = row + int(w)
-                w_at += 1
-            row_start[r] = row
-            ctx_len[r] = held_after
-            first_pos[r] = start
-            slot = self.cache.state_slot(e.request)
-            state_slot[r] = slot
-            hs.request_ids.append(e.request)
-            hs.new_tokens.append(n)
-            hs.first_pos.append(start)
-            hs.context_len.append(held_after)
-            hs.state_slots.append(slot)
-            for g, stride in enumerate(self.table_strides):
-                table = self.cache.block_table(e.request, g)
-                a, _ = off[f"table{g}"]
-                dst = host[a + r * stride:a + (r + 1) * stride]
-                dst[:len(table)] = table
-                dst[len(table):] = 0
-                n_pages = self.cache.pools[g].n_pages
-                for p in table:
-                    if p != RELEASED and not 0 <= p < n_pages:
-                        raise StepError(f"page {p} of request {e.request!r} is out of range")
-            row += n
-        row_start[len(entries)] = row
+        held_after = [cache.length(e.request) for e in entries]
+        slots = [cache.state_slot(e.request) for e in entries]
+        starts = [h - n for h, n in zip(held_after, counts)]
+        row_starts = [0] * (n_req + 1)
+        for r, n in enumerate(counts):
+            row_starts[r + 1] = row_starts[r] + n
+        if n_tokens == n_req:                                  # every request brings one token
+            tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=n_req)
+            piece("positions")[:] = starts
+            piece("row_request")[:] = np.arange(n_req, dtype=np.int32)
+        else:
+            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+            counts_np = np.asarray(counts)
+            owner = np.repeat(np.arange(n_req, dtype=np.int32), counts_np)
+            piece("row_request")[:] = owner
+            shift = np.asarray(starts) - np.asarray(row_starts[:-1])
+            piece("positions")[:] = np.arange(n_tokens) + shift[owner]
+        piece("token_ids")[:] = tokens
+        if n_want:
+            if all(len(e.want) == 1 for e in entries):
+                piece("logit_rows")[:] = [row_starts[r] + int(e.want[0])
+                                          for r, e in enumerate(entries)]
+            else:
+                piece("logit_rows")[:] = [row_starts[r] + int(w) for r, e in enumerate(entries)
+                                          for w in e.want]
+        piece("req_row_start")[:] = row_starts
+        piece("req_context_len")[:] = held_after
+        piece("req_first_pos")[:] = starts
+        piece("req_state_slot")[:] = slots
+        for g, stride in enumerate(self.table_strides):
+            a, _ = off[f"table{g}"]
+            block = host[a:a + n_req * stride].reshape(n_req, stride)
+            for r, e in enumerate(entries):
+                block[r] = self._table_row(e.request, g)
+        hs = HostStep([e.request for e in entries], counts, starts, held_after, slots)
         dev_t[:total].copy_(host_t[:total], non_blocking=True)
         return StepContext(layout=layout, meta=dev_t, caches=self.storages, state=self.state,
                            scratch=self.scratch, dtype=self.dtype, host=hs)

@@ -138,7 +138,8 @@ def _gemm_skinny(a, w, out, n, epi, splits=None) -> bool:
     return True
 
 
-SKINNY_ROWS = 64     # products with at most this many rows run with W on the MMA's M side
+SKINNY_ROWS = 32     # products with at most this many rows run with W on the MMA's M side
+SKINNY_WIDE_N = 8192 # ... and up to 64 rows if W has at least this many rows (the LM head)
 
 
 def _operands_ok(a, w) -> bool:
@@ -159,7 +160,8 @@ def linear(a, w, out, *, accumulate=False, tile=None) -> bool:
         epi = ACCUM_F32 if accumulate else STORE_F32
     else:
         return False
-    if tile is None and a.shape[0] <= SKINNY_ROWS:
+    if tile is None and (a.shape[0] <= SKINNY_ROWS
+                         or (a.shape[0] <= 64 and w.shape[0] >= SKINNY_WIDE_N)):
         return _gemm_skinny(a, w, out, w.shape[0], epi)
     bn = tile or _tile_width(a.shape[0], w.shape[0])
     return _gemm(a, w, out, w.shape[0], epi, bn)
@@ -190,13 +192,22 @@ def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx,
     host = ctx.host
     n_rep = n_heads // n_kv_heads
     split = host.max_new_tokens * n_rep <= 16
-    # chunks of 256 keys the split form is launched over: a launch shape only;
-    # which chunks a row reads depends on that row alone
-    n_chunks = host.context_bucket // 256 if split else 0
-    partial = None
+    # The split form is launched over chunks of 256 * 2^k keys that cover the step's
+    # context bucket; the chunk is the largest that still gives about two waves of
+    # blocks (a function of the step's shape alone, so a captured step replays).
+    chunk_keys = 256
+    if split:
+        blocks_per_chunk = ctx.n_requests * n_kv_heads * (-(-host.max_new_tokens * n_rep // 16))
+        while (chunk_keys * 2 <= host.context_bucket
+               and blocks_per_chunk * (host.context_bucket // (chunk_keys * 2)) >= 2 * 148):
+            chunk_keys *= 2
+    n_chunks = host.context_bucket // chunk_keys if split else 0
+    partial = counters = None
     if split:
         floats = ctx.n_tokens * n_heads * n_chunks * (head_dim + 2)
         partial = ctx.scratch("attn.partial", (floats,), torch.float32)
+        n_counters = ctx.n_requests * n_kv_heads * (-(-host.max_new_tokens * n_rep // 16))
+        counters = _buffer(qkv.device, "attn.counters", n_counters, torch.int32, zero=True)
     lib = build.load("attention_mma")
     code = lib.cb_attention_mma(
         _c_void_p(qkv.data_ptr()), _c_int(qkv.stride(0)), _c_void_p(out.data_ptr()),
@@ -206,10 +217,12 @@ def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx,
         _c_int(table.shape[1]), _c_int(ctx.n_tokens), _c_int(ctx.n_requests),
         _c_int(host.max_new_tokens), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
         _c_int(cache.page_tokens), ctypes.c_float(scale), _c_int(window or 0),
-        _c_void_p(partial.data_ptr() if partial is not None else 0), _c_int(n_chunks), _stream())
+        _c_void_p(partial.data_ptr() if partial is not None else 0),
+        _c_void_p(counters.data_ptr() if counters is not None else 0), _c_int(n_chunks),
+        _c_int(chunk_keys), _stream())
     if code == _UNSUPPORTED:
         return False
     if code != 0:
         raise RuntimeError(f"tensor-core attention failed to launch (CUDA error {code})")
-    _count(2 if split else 1)
+    _count(1)
     return True

@@ -187,7 +187,7 @@ def test_small_batch_linear_and_swiglu(m, n, k):
     normed = x.double() * torch.rsqrt(x.double().pow(2).mean(-1, keepdim=True) + 1e-5) * gain.double()
     out = torch.empty(m, n, device=DEV)
     assert small_batch.linear(lazy, w, out)
-    assert rel(out, normed @ w.double().T) < 1e-5
+    assert rel(out, normed @ w.double().T) < 5e-3        # the normalised rows are rounded to bfloat16
     if n % 2 == 0:
         inter = n // 2
         act = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
