@@ -48,7 +48,7 @@ __global__ void attention_generic_kernel(
     for (int j = lo; j <= pos; ++j) {
         const int page = table[j / page_tokens];
         const size_t base =
-            (((size_t)page * page_tokens + (j % page_tokens)) * n_kv_heads + kvh) * head_dim;
+            (((size_t)page * n_kv_heads + kvh) * page_tokens + (j % page_tokens)) * head_dim;
         float part = 0.f;
 #pragma unroll
         for (int i = 0; i < MAX_PER_LANE; ++i) {

@@ -92,35 +92,41 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Loads tiles of TILE_KEYS keys and values of one request and KV head into shared
-// memory rows of `pitch` elements, 16 bytes per cp.async, all threads of the
-// block taking part.  Which (row, 16-byte piece) a thread copies is fixed for the
+// Loads tiles of TILE keys and values of one request and KV head into shared
+// memory rows of `pitch` elements, 16 bytes per cp.async, NT threads (a block or
+// a warp) taking part.  Which (row, 16-byte piece) a thread copies is fixed for the
 // kernel's life and worked out once; per tile only the page lookup remains (a
 // shift and a mask when the page size is a power of two).  Keys at or beyond
 // `key_end` are zero-filled.
-template <int HD_MAX, int NT>
+template <int HD_MAX, int NT, int TILE>
 struct KvLoader {
-    static constexpr int ITEMS = (TILE_KEYS * (HD_MAX / 8) + NT - 1) / NT;
+    static constexpr int ITEMS = (TILE * (HD_MAX / 8) + NT - 1) / NT;
     int row[ITEMS];          // key row inside the tile, or -1
-    int col[ITEMS];          // first element of the 16-byte piece
+    int base[ITEMS];         // element offset inside a page: kv_head's block + the piece's column
+    int sdst[ITEMS];         // byte offset of the piece inside a shared-memory tile
+    size_t page_elems;       // elements of one page (all KV heads)
     int page_shift;          // log2(page_tokens), or -1 if not a power of two
 
-    __device__ __forceinline__ void init(const AttnParams& p, int tid) {
+    __device__ __forceinline__ void init(const AttnParams& p, int kv_head, int pitch, int tid) {
         const int chunks_per_row = p.head_dim >> 3;
-        const int total = TILE_KEYS * chunks_per_row;
+        const int total = TILE * chunks_per_row;
 #pragma unroll
         for (int u = 0; u < ITEMS; ++u) {
             const int i = tid + u * NT;
             const int r = i / chunks_per_row;
+            const int col = (i - r * chunks_per_row) * 8;
             row[u] = i < total ? r : -1;
-            col[u] = (i - r * chunks_per_row) * 8;
+            base[u] = kv_head * p.page_tokens * p.head_dim + col;
+            sdst[u] = (r * pitch + col) * 2;
         }
+        page_elems = (size_t)p.n_kv_heads * p.page_tokens * p.head_dim;
         page_shift = (p.page_tokens & (p.page_tokens - 1)) == 0 ? 31 - __clz(p.page_tokens) : -1;
     }
 
-    __device__ __forceinline__ void load(const AttnParams& p, const int* table, int kv_head,
-                                         int key0, int key_end, __nv_bfloat16* k_smem,
-                                         __nv_bfloat16* v_smem, int pitch) const {
+    __device__ __forceinline__ void load(const AttnParams& p, const int* table, int key0,
+                                         int key_end, __nv_bfloat16* k_smem,
+                                         __nv_bfloat16* v_smem) const {
+        const uint32_t ks = smem_u32(k_smem), vs = smem_u32(v_smem);
         // in batches of four pieces: first the block-table lookups (loads that may
         // miss), then the copies, so that the lookups' latencies overlap
 #pragma unroll
@@ -144,9 +150,8 @@ struct KvLoader {
                             page_index = key / p.page_tokens;
                             slot = key - page_index * p.page_tokens;
                         }
-                        const int page = table[page_index];
-                        off[v] = (((size_t)page * p.page_tokens + slot) * p.n_kv_heads + kv_head) *
-                                     p.head_dim + col[u];
+                        off[v] = (size_t)table[page_index] * page_elems +
+                                 (size_t)(base[u] + slot * p.head_dim);
                     }
                 }
             }
@@ -154,68 +159,108 @@ struct KvLoader {
             for (int v = 0; v < 4; ++v) {
                 const int u = u0 + v;
                 if (u < ITEMS && row[u] >= 0) {
-                    const int dst = row[u] * pitch + col[u];
-                    cp_async_16(k_smem + dst, p.k_cache + off[v], valid[v]);
-                    cp_async_16(v_smem + dst, p.v_cache + off[v], valid[v]);
+                    const int bytes = valid[v] ? 16 : 0;     // 0: zero-filled
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ks + sdst[u]),
+                                 "l"(p.k_cache + off[v]), "r"(bytes) : "memory");
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vs + sdst[u]),
+                                 "l"(p.v_cache + off[v]), "r"(bytes) : "memory");
                 }
             }
         }
     }
 };
 
-// One warp, 16 query rows (A fragments read from q_smem), `n_keys` keys of a
-// tile (multiple of 16, <= NK) in shared memory: scores, running-maximum
-// softmax update and the weighted sum of values.  Rows g = lane / 4 and g + 8.
-template <int HD_MAX, int NK>
-__device__ __forceinline__ void attend_tile(const AttnParams& p, const __nv_bfloat16* q_smem,
+// The query fragments of one warp's 16 rows, for all of head_dim: kept in
+// registers for head sizes up to 128, re-read from shared memory beyond that.
+template <int HD_MAX>
+struct QFrags {
+    static constexpr bool IN_REGS = HD_MAX <= 128;
+    uint32_t a[IN_REGS ? HD_MAX / 16 : 1][4];
+    const __nv_bfloat16* smem;
+    int pitch;
+
+    __device__ __forceinline__ void init(const __nv_bfloat16* q_smem, int pitch_, int head_dim) {
+        smem = q_smem;
+        pitch = pitch_;
+        if (IN_REGS) {
+#pragma unroll
+            for (int kk = 0; kk < HD_MAX / 16; ++kk)
+                if (kk * 16 < head_dim) fetch(kk, a[kk]);
+        }
+    }
+    __device__ __forceinline__ void fetch(int kk, uint32_t (&out)[4]) const {
+        const int lane = threadIdx.x & 31;
+        const int mat = lane >> 3;
+        const int row = (mat & 1) * 8 + (lane & 7);
+        const int col = kk * 16 + (mat >> 1) * 8;
+        ldmatrix_x4(out, smem + row * pitch + col);
+    }
+    __device__ __forceinline__ void get(int kk, uint32_t (&out)[4]) const {
+        if (IN_REGS) {
+            out[0] = a[kk][0]; out[1] = a[kk][1]; out[2] = a[kk][2]; out[3] = a[kk][3];
+        } else {
+            fetch(kk, out);
+        }
+    }
+};
+
+// One warp, 16 query rows, NK keys of a tile in shared memory (NK a multiple of
+// 16): scores, running-maximum softmax update and the weighted sum of values.
+// Rows g = lane / 4 and g + 8.  `masked`: some key of the tile may lie outside a
+// row's range (after its position, before its window, or past the end); when
+// the caller knows that none does, the per-element tests are skipped.
+template <int HD_MAX, int NK, bool EXACT>
+__device__ __forceinline__ void attend_tile(const AttnParams& p, const QFrags<HD_MAX>& q,
                                             const __nv_bfloat16* k_smem,
-                                            const __nv_bfloat16* v_smem, int pitch, int n_keys,
-                                            int key0, int pos_a, int pos_b, int lo_a, int lo_b,
-                                            int key_end, float (&o)[HD_MAX / 8][4], float& m_a,
-                                            float& m_b, float& l_a, float& l_b) {
+                                            const __nv_bfloat16* v_smem, int pitch_, bool masked,
+                                            int key0,
+                                            int pos_a, int pos_b, int lo_a, int lo_b, int key_end,
+                                            float (&o)[HD_MAX / 8][4], float& m_a, float& m_b,
+                                            float& l_a, float& l_b) {
     const int lane = threadIdx.x & 31;
     const int t = lane & 3;
-    const int hd = p.head_dim;
+    // EXACT: the head size is HD_MAX itself, so the loop bounds and the row pitch are
+    // constants and the address arithmetic folds away
+    const int hd = EXACT ? HD_MAX : p.head_dim;
+    const int pitch = EXACT ? HD_MAX + 8 : pitch_;
+    const int mat = lane >> 3;
     float s[NK / 8][4];
 #pragma unroll
     for (int j = 0; j < NK / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
     // S = Q K^T
+    const __nv_bfloat16* k_lane = k_smem + ((mat >> 1) * 8 + (lane & 7)) * pitch + (mat & 1) * 8;
 #pragma unroll
     for (int kk = 0; kk < HD_MAX / 16; ++kk) {
         if (kk * 16 < hd) {
             uint32_t a[4];
-            {
-                const int mat = lane >> 3;
-                const int row = (mat & 1) * 8 + (lane & 7);
-                const int col = kk * 16 + (mat >> 1) * 8;
-                ldmatrix_x4(a, q_smem + row * pitch + col);
-            }
+            q.get(kk, a);
 #pragma unroll
             for (int j = 0; j < NK / 8; j += 2) {
-                if (j * 8 < n_keys) {
-                    uint32_t b[4];
-                    const int mat = lane >> 3;
-                    const int key = (j + (mat >> 1)) * 8 + (lane & 7);
-                    const int col = kk * 16 + (mat & 1) * 8;
-                    ldmatrix_x4(b, k_smem + key * pitch + col);
-                    mma_bf16(s[j], a, b[0], b[1]);
-                    mma_bf16(s[j + 1], a, b[2], b[3]);
-                }
+                uint32_t b[4];
+                ldmatrix_x4(b, k_lane + j * 8 * pitch + kk * 16);
+                mma_bf16(s[j], a, b[0], b[1]);
+                mma_bf16(s[j + 1], a, b[2], b[3]);
             }
         }
     }
-    // mask, scale (in log2 units), row maxima
+    // mask and row maxima (raw scores; the scale is positive and applied below)
     float mx_a = -INFINITY, mx_b = -INFINITY;
+    if (masked) {                    // warp-uniform
+        const int hi_a = min(pos_a, key_end - 1), hi_b = min(pos_b, key_end - 1);
+#pragma unroll
+        for (int j = 0; j < NK / 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = key0 + j * 8 + 2 * t + e;
+                if (key > hi_a || key < lo_a) s[j][e] = -INFINITY;
+                if (key > hi_b || key < lo_b) s[j][2 + e] = -INFINITY;
+            }
+        }
+    }
 #pragma unroll
     for (int j = 0; j < NK / 8; ++j) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-            const int key = key0 + j * 8 + 2 * t + e;
-            const bool in = j * 8 < n_keys && key < key_end;
-            const bool ok_a = in && key <= pos_a && key >= lo_a;
-            const bool ok_b = in && key <= pos_b && key >= lo_b;
-            s[j][e] = ok_a ? s[j][e] * p.scale_log2 : -INFINITY;
-            s[j][2 + e] = ok_b ? s[j][2 + e] * p.scale_log2 : -INFINITY;
             mx_a = fmaxf(mx_a, s[j][e]);
             mx_b = fmaxf(mx_b, s[j][2 + e]);
         }
@@ -224,52 +269,53 @@ __device__ __forceinline__ void attend_tile(const AttnParams& p, const __nv_bflo
     mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-    const float new_a = fmaxf(m_a, mx_a), new_b = fmaxf(m_b, mx_b);
+    const float new_a = fmaxf(m_a, mx_a * p.scale_log2), new_b = fmaxf(m_b, mx_b * p.scale_log2);
     // a row that has seen no key yet keeps max = -inf; use 0 as its offset so
     // that exp2(-inf - 0) = 0 instead of exp2(-inf + inf)
     const float off_a = new_a == -INFINITY ? 0.f : new_a;
     const float off_b = new_b == -INFINITY ? 0.f : new_b;
-    const float corr_a = exp2f(m_a - off_a), corr_b = exp2f(m_b - off_b);
-    m_a = new_a;
-    m_b = new_b;
+    const bool moved = new_a != m_a || new_b != m_b;
+    if (__any_sync(0xffffffffu, moved)) {            // the running maxima rarely move late in a row
+        const float corr_a = exp2f(m_a - off_a), corr_b = exp2f(m_b - off_b);
+        l_a *= corr_a;
+        l_b *= corr_b;
+#pragma unroll
+        for (int n = 0; n < HD_MAX / 8; ++n) {
+            o[n][0] *= corr_a; o[n][1] *= corr_a;
+            o[n][2] *= corr_b; o[n][3] *= corr_b;
+        }
+        m_a = new_a;
+        m_b = new_b;
+    }
     float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
     for (int j = 0; j < NK / 8; ++j) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-            s[j][e] = exp2f(s[j][e] - off_a);
-            s[j][2 + e] = exp2f(s[j][2 + e] - off_b);
+            s[j][e] = exp2f(fmaf(s[j][e], p.scale_log2, -off_a));
+            s[j][2 + e] = exp2f(fmaf(s[j][2 + e], p.scale_log2, -off_b));
             sum_a += s[j][e];
             sum_b += s[j][2 + e];
         }
     }
-    l_a = l_a * corr_a + sum_a;      // per-thread partial sums; reduced over the quad at the end
-    l_b = l_b * corr_b + sum_b;
-#pragma unroll
-    for (int n = 0; n < HD_MAX / 8; ++n) {
-        o[n][0] *= corr_a; o[n][1] *= corr_a;
-        o[n][2] *= corr_b; o[n][3] *= corr_b;
-    }
+    l_a += sum_a;                    // per-thread partial sums; reduced over the quad at the end
+    l_b += sum_b;
     // O += P V
+    const __nv_bfloat16* v_lane = v_smem + ((mat & 1) * 8 + (lane & 7)) * pitch + (mat >> 1) * 8;
 #pragma unroll
     for (int kk = 0; kk < NK / 16; ++kk) {
-        if (kk * 16 < n_keys) {
-            uint32_t a[4];
-            a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-            a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-            a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-            a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
-            for (int n = 0; n < HD_MAX / 8; n += 2) {
-                if (n * 8 < hd) {
-                    uint32_t b[4];
-                    const int mat = lane >> 3;
-                    const int key = kk * 16 + (mat & 1) * 8 + (lane & 7);
-                    const int col = (n + (mat >> 1)) * 8;
-                    ldmatrix_x4_trans(b, v_smem + key * pitch + col);
-                    mma_bf16(o[n], a, b[0], b[1]);
-                    mma_bf16(o[n + 1], a, b[2], b[3]);
-                }
+        for (int n = 0; n < HD_MAX / 8; n += 2) {
+            if (n * 8 < hd) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, v_lane + kk * 16 * pitch + n * 8);
+                mma_bf16(o[n], a, b[0], b[1]);
+                mma_bf16(o[n + 1], a, b[2], b[3]);
             }
         }
     }
@@ -300,12 +346,12 @@ __device__ __forceinline__ void load_q_rows(const AttnParams& p, int row_base, i
 // ---------------------------------------------------------------------------
 // tiles kernel
 // ---------------------------------------------------------------------------
-template <int HD_MAX>
+template <int HD_MAX, bool EXACT>
 __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p) {
     cb_pdl_trigger();
     cb_pdl_wait();
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    const int pitch = p.head_dim + 8;
+    const int pitch = EXACT ? HD_MAX + 8 : p.head_dim + 8;
     __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __nv_bfloat16* kv_smem = q_smem + 64 * pitch;      // [2 stages][K, V][64][pitch]
     const int req = blockIdx.z, kv_head = blockIdx.y;
@@ -339,6 +385,12 @@ __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p
     const int lo_b = p.window > 0 ? max(0, pos_b - p.window + 1) : 0;
     const int warp_last_row = min(n_rows - 1, qt * 64 + warp * 16 + 15);
     const int warp_max_pos = qt * 64 + warp * 16 < n_rows ? first_pos + warp_last_row / n_rep : -1;
+    // interior tiles: all 16 rows of the warp exist, and the tile lies before the
+    // lowest position and inside the latest window of the warp's rows
+    const bool warp_full = qt * 64 + warp * 16 + 15 < n_rows;
+    const int warp_min_pos = warp_full ? first_pos + (qt * 64 + warp * 16) / n_rep : -1;
+    const int warp_max_lo = p.window > 0 ? max(0, warp_max_pos - p.window + 1) : 0;
+    QFrags<HD_MAX> qf;
 
     float o[HD_MAX / 8][4];
 #pragma unroll
@@ -346,28 +398,30 @@ __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
 
     const int stage_elems = 2 * TILE_KEYS * pitch;
-    KvLoader<HD_MAX, 128> loader;
-    loader.init(p, threadIdx.x);
-    loader.load(p, table, kv_head, key_lo, key_end, kv_smem, kv_smem + TILE_KEYS * pitch, pitch);
+    KvLoader<HD_MAX, 128, TILE_KEYS> loader;
+    loader.init(p, kv_head, pitch, threadIdx.x);
+    loader.load(p, table, key_lo, key_end, kv_smem, kv_smem + TILE_KEYS * pitch);
     cp_async_commit();
     for (int i = 0; i < n_tiles; ++i) {
         const int st = i & 1;
         if (i + 1 < n_tiles) {
             __nv_bfloat16* nxt = kv_smem + (st ^ 1) * stage_elems;
-            loader.load(p, table, kv_head, key_lo + (i + 1) * TILE_KEYS, key_end, nxt,
-                        nxt + TILE_KEYS * pitch, pitch);
+            loader.load(p, table, key_lo + (i + 1) * TILE_KEYS, key_end, nxt, nxt + TILE_KEYS * pitch);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
         }
         __syncthreads();
+        if (i == 0) qf.init(q_smem + warp * 16 * pitch, pitch, p.head_dim);   // the rows are in place now
         const int key0 = key_lo + i * TILE_KEYS;
         if (key0 <= warp_max_pos) {
             const __nv_bfloat16* ks = kv_smem + st * stage_elems;
-            attend_tile<HD_MAX, TILE_KEYS>(p, q_smem + warp * 16 * pitch, ks, ks + TILE_KEYS * pitch, pitch,
-                                TILE_KEYS, key0, pos_a, pos_b, lo_a, lo_b, key_end, o, m_a, m_b,
-                                l_a, l_b);
+            // no test per element if every key of the tile is inside every row's range
+            const bool interior = key0 + TILE_KEYS - 1 <= warp_min_pos && key0 >= warp_max_lo;
+            attend_tile<HD_MAX, TILE_KEYS, EXACT>(p, qf, ks, ks + TILE_KEYS * pitch, pitch, !interior,
+                                                  key0, pos_a, pos_b, lo_a, lo_b, key_end, o, m_a,
+                                                  m_b, l_a, l_b);
         }
         __syncthreads();
     }
@@ -397,14 +451,23 @@ __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p
 }
 
 // ---------------------------------------------------------------------------
-// split kernel: 16 rows x one chunk of 256 keys.  The block streams the chunk in
-// tiles of 64 keys through a three-stage cp.async pipeline; each warp attends
-// to 16 keys of every tile.  The warps' results are merged in warp order, the
-// chunk's partial (max, sum, vector) goes to scratch, and the block that arrives
-// last at its rows' counter merges the chunks in ascending order and writes the
-// output; no block waits for another.
+// split kernel: 16 rows x one chunk of keys (a multiple of 256).  The chunk is
+// cut into sub-tiles that are dealt to the four warps in turn; each warp streams
+// its sub-tiles through a ring of its own in shared memory (cp.async, several
+// in flight, no block-wide barrier in the loop) and attends to them with a
+// running maximum.  The warps' results are merged in warp order; if the rows
+// have a single chunk the output is written at once, else the chunk's partial
+// (max, sum, vector) goes to scratch and the block that arrives last at the rows'
+// counter merges the chunks in ascending order.  No block waits for another.
 // ---------------------------------------------------------------------------
-constexpr int SPLIT_STAGES = 3;
+template <int HD_MAX>
+struct SplitShape {
+    // keys per sub-tile and ring depth per warp, sized so that two blocks fit an SM
+    // for head sizes up to 64 and one beyond
+    static constexpr int SUB = HD_MAX <= 128 ? 32 : 16;
+    static constexpr int RING = HD_MAX <= 64 ? 3 : 2;
+};
+
 
 // Merges one row's chunks (ascending, with a running maximum) and writes its
 // output.  One warp; lanes own features.  The loads of up to 8 chunks are issued
@@ -452,16 +515,18 @@ __device__ __forceinline__ void merge_row(const AttnParams& p, int tok, int head
     }
 }
 
-template <int HD_MAX>
+template <int HD_MAX, bool EXACT>
 __global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p, int* counters,
                                                               int max_q_tiles) {
     cb_pdl_trigger();
     cb_pdl_wait();
+    constexpr int SUB = SplitShape<HD_MAX>::SUB;
+    constexpr int RING = SplitShape<HD_MAX>::RING;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __shared__ int is_last;
-    const int pitch = p.head_dim + 8;
+    const int pitch = EXACT ? HD_MAX + 8 : p.head_dim + 8;
     __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* kv_smem = q_smem + 16 * pitch;      // [stages][K, V][64][pitch]
+    __nv_bfloat16* kv_smem = q_smem + 16 * pitch;      // [warp][RING][K, V][SUB][pitch]
     const int req = blockIdx.z, kv_head = blockIdx.y;
     const int n_rep = p.n_heads / p.n_kv_heads;
     const int row_base = p.req_row_start[req];
@@ -486,10 +551,12 @@ __global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p
     if (c0 >= key_end || c0 + p.chunk_keys <= key_lo) return;
     const int n_active = (key_end - 1) / p.chunk_keys - key_lo / p.chunk_keys + 1;
     const int chunk_end = min(key_end, c0 + p.chunk_keys);
-    const int n_tiles = (chunk_end - c0 + TILE_KEYS - 1) / TILE_KEYS;
-    const int stage_elems = 2 * TILE_KEYS * pitch;
+    const int n_sub = (chunk_end - c0 + SUB - 1) / SUB;          // sub-tiles of the chunk
+    const int mine = warp < n_sub ? (n_sub - warp + 3) / 4 : 0;  // ... of which this warp takes
+    const int stage_elems = 2 * SUB * pitch;
+    __nv_bfloat16* ring = kv_smem + (size_t)warp * RING * stage_elems;
 
-    // the query rows and the first tiles of keys and values, all in flight at once
+    // the query rows (all threads), then this warp's first sub-tiles, all in flight at once
     {
         const int chunks_per_row = p.head_dim >> 3;
         for (int i = threadIdx.x; i < 16 * chunks_per_row; i += 128) {
@@ -501,15 +568,15 @@ __global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p
             cp_async_16(q_smem + r * pitch + c * 8,
                         p.qkv + (size_t)tok * p.qkv_stride + (size_t)head * p.head_dim + c * 8, valid);
         }
+        cp_async_commit();
     }
-    KvLoader<HD_MAX, 128> loader;
-    loader.init(p, threadIdx.x);
+    KvLoader<HD_MAX, 32, SUB> loader;
+    loader.init(p, kv_head, pitch, lane);
 #pragma unroll
-    for (int st = 0; st < SPLIT_STAGES; ++st) {
-        if (st < n_tiles) {
-            __nv_bfloat16* ks = kv_smem + st * stage_elems;
-            loader.load(p, table, kv_head, c0 + st * TILE_KEYS, key_end, ks, ks + TILE_KEYS * pitch,
-                        pitch);
+    for (int st = 0; st < RING; ++st) {
+        if (st < mine) {
+            __nv_bfloat16* ks = ring + st * stage_elems;
+            loader.load(p, table, c0 + (warp + 4 * st) * SUB, key_end, ks, ks + SUB * pitch);
         }
         cp_async_commit();
     }
@@ -523,21 +590,27 @@ __global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p
 #pragma unroll
     for (int n = 0; n < HD_MAX / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
-    for (int i = 0; i < n_tiles; ++i) {
-        cp_async_wait<SPLIT_STAGES - 1>();
-        __syncthreads();
-        const int st = i % SPLIT_STAGES;
-        const __nv_bfloat16* ks = kv_smem + st * stage_elems;
-        const int key0 = c0 + i * TILE_KEYS + warp * 16;
-        if (key0 < key_end)
-            attend_tile<HD_MAX, 16>(p, q_smem, ks + warp * 16 * pitch,
-                                ks + (TILE_KEYS + warp * 16) * pitch, pitch, 16, key0, pos_a, pos_b,
-                                lo_a, lo_b, key_end, o, m_a, m_b, l_a, l_b);
-        __syncthreads();
-        if (i + SPLIT_STAGES < n_tiles) {
-            __nv_bfloat16* nxt = kv_smem + st * stage_elems;
-            loader.load(p, table, kv_head, c0 + (i + SPLIT_STAGES) * TILE_KEYS, key_end, nxt,
-                        nxt + TILE_KEYS * pitch, pitch);
+    // interior sub-tiles need no per-element test: all 16 rows exist, the keys lie at
+    // or before the lowest position and inside the latest window
+    const bool all_rows = qt * 16 + 15 < n_rows;
+    const int max_lo = p.window > 0 ? max(0, max_pos - p.window + 1) : 0;
+    cp_async_wait<RING>();              // this thread's piece of the query rows has landed
+    __syncthreads();                    // ... and everybody else's
+    QFrags<HD_MAX> qf;
+    qf.init(q_smem, pitch, p.head_dim);
+    for (int i = 0; i < mine; ++i) {
+        cp_async_wait<RING - 1>();
+        __syncwarp();
+        const int st = i % RING;
+        const __nv_bfloat16* ks = ring + st * stage_elems;
+        const int key0 = c0 + (warp + 4 * i) * SUB;
+        const bool interior = all_rows && key0 + SUB - 1 <= min_pos && key0 >= max_lo;
+        attend_tile<HD_MAX, SUB, EXACT>(p, qf, ks, ks + SUB * pitch, pitch, !interior, key0, pos_a,
+                                        pos_b, lo_a, lo_b, key_end, o, m_a, m_b, l_a, l_b);
+        __syncwarp();
+        if (i + RING < mine) {
+            __nv_bfloat16* nxt = ring + st * stage_elems;
+            loader.load(p, table, c0 + (warp + 4 * (i + RING)) * SUB, key_end, nxt, nxt + SUB * pitch);
         }
         cp_async_commit();
     }
@@ -547,8 +620,9 @@ __global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
 
-    // merge the four warps (in warp order) through shared memory, reusing the
-    // key/value buffers: per warp 16 rows x (head_dim + 2) floats
+    // merge the four warps through shared memory, reusing the key/value rings: per
+    // warp 16 rows x (head_dim + 2) floats.  Warp w holds sub-tiles w, w+4, ...; the
+    // merge takes the warps in a fixed order, so the result does not vary
     __syncthreads();
     float* merge = reinterpret_cast<float*>(kv_smem);
     const int mp = p.head_dim + 2;
@@ -631,38 +705,53 @@ __global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p
     }
 }
 
-template <int HD_MAX>
-int launch_tiles(const AttnParams& p, int n_requests, int max_q_tiles, cudaStream_t s) {
+template <int HD_MAX, bool EXACT>
+int launch_tiles_as(const AttnParams& p, int n_requests, int max_q_tiles, cudaStream_t s) {
     const int pitch = p.head_dim + 8;
     const int smem = (64 + 4 * TILE_KEYS) * pitch * 2;
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tiles_kernel<HD_MAX>,
+        cudaError_t e = cudaFuncSetAttribute(attention_tiles_kernel<HD_MAX, EXACT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid(max_q_tiles, p.n_kv_heads, n_requests);
-    cb_launch(attention_tiles_kernel<HD_MAX>, dim3(grid), dim3(128), smem, s, p);
+    cb_launch(attention_tiles_kernel<HD_MAX, EXACT>, dim3(grid), dim3(128), smem, s, p);
     return cb_last_error();
 }
 
 template <int HD_MAX>
-int launch_split(const AttnParams& p, int n_requests, int max_q_tiles, int* counters, cudaStream_t s) {
+int launch_tiles(const AttnParams& p, int n_requests, int max_q_tiles, cudaStream_t s) {
+    return p.head_dim == HD_MAX ? launch_tiles_as<HD_MAX, true>(p, n_requests, max_q_tiles, s)
+                                : launch_tiles_as<HD_MAX, false>(p, n_requests, max_q_tiles, s);
+}
+
+template <int HD_MAX, bool EXACT>
+int launch_split_as(const AttnParams& p, int n_requests, int max_q_tiles, int* counters,
+                    cudaStream_t s) {
     const int pitch = p.head_dim + 8;
-    int smem = (16 + SPLIT_STAGES * 2 * TILE_KEYS) * pitch * 2;
+    int smem = (16 + 4 * SplitShape<HD_MAX>::RING * 2 * SplitShape<HD_MAX>::SUB) * pitch * 2;
     const int merge_bytes = 4 * 16 * (p.head_dim + 2) * 4;
     if (16 * pitch * 2 + merge_bytes > smem) smem = 16 * pitch * 2 + merge_bytes;
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attention_split_kernel<HD_MAX>,
+        cudaError_t e = cudaFuncSetAttribute(attention_split_kernel<HD_MAX, EXACT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid(max_q_tiles * p.n_chunks, p.n_kv_heads, n_requests);
-    cb_launch(attention_split_kernel<HD_MAX>, dim3(grid), dim3(128), smem, s, p, counters, max_q_tiles);
+    cb_launch(attention_split_kernel<HD_MAX, EXACT>, dim3(grid), dim3(128), smem, s, p, counters,
+              max_q_tiles);
     return cb_last_error();
+}
+
+template <int HD_MAX>
+int launch_split(const AttnParams& p, int n_requests, int max_q_tiles, int* counters, cudaStream_t s) {
+    return p.head_dim == HD_MAX
+               ? launch_split_as<HD_MAX, true>(p, n_requests, max_q_tiles, counters, s)
+               : launch_split_as<HD_MAX, false>(p, n_requests, max_q_tiles, counters, s);
 }
 
 }  // namespace

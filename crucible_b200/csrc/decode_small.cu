@@ -282,7 +282,7 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
                 const bool is_k = head < p.n_heads + p.n_kv_heads;
                 const int kvh = is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
                 __nv_bfloat16* dst = (is_k ? p.k_cache : p.v_cache) +
-                    (((size_t)page2[e] * p.page_tokens + pos % p.page_tokens) * p.n_kv_heads + kvh) * p.head_dim;
+                    (((size_t)page2[e] * p.n_kv_heads + kvh) * p.page_tokens + pos % p.page_tokens) * p.head_dim;
                 dst[j] = __float2bfloat16_rn(y0);
                 dst[j + half] = __float2bfloat16_rn(y1);
             }

@@ -177,7 +177,7 @@ CB_EXPORT int cb_gather_rows(const float* x, const int* rows, float* out, int n_
 // ---------------------------------------------------------------------------
 // Rotary encoding of q and k (half-split pairing) fused with the cache write.
 // qkv: [T, (Hq + 2 Hkv) * hd]; q is rotated in place; rotated k and plain v go
-// to the token's page: cache[page][slot][kv_head][feature].
+// to the token's page: cache[page][kv_head][slot][feature].
 // One block per (token, head); heads 0..Hq-1 are q, then Hkv k heads, then
 // Hkv v heads.
 // ---------------------------------------------------------------------------
@@ -198,11 +198,14 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, const float* __restri
     const int pos = positions[t];
     const int half = rotary_dim >> 1;
     const int pass = head_dim - rotary_dim;          // features that are not rotated
+    // cache[page][kv_head][slot][feature]: the token's row of KV head h starts at
+    // cache_base + h * head_stride
     size_t cache_base = 0;
+    const size_t head_stride = (size_t)page_tokens * head_dim;
     if (write_cache) {
         const int r = row_request[t];
         const int page = block_table[(size_t)r * table_stride + pos / page_tokens];
-        cache_base = ((size_t)page * page_tokens + pos % page_tokens) * n_kv_heads * head_dim;
+        cache_base = (size_t)page * n_kv_heads * head_stride + (size_t)(pos % page_tokens) * head_dim;
     }
     const float* c_row = cos_t + (size_t)pos * half;
     const float* s_row = sin_t + (size_t)pos * half;
@@ -214,7 +217,7 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, const float* __restri
         const float c = c_row[j], s = s_row[j];
         const float x1 = cb_to_float(src[j]);
         const float x2 = cb_to_float(src[j + half]);
-        T* dst = h < n_heads ? src : k_cache + cache_base + (size_t)(h - n_heads) * head_dim;
+        T* dst = h < n_heads ? src : k_cache + cache_base + (size_t)(h - n_heads) * head_stride;
         dst[j] = cb_from_float<T>(x1 * c - x2 * s);
         dst[j + half] = cb_from_float<T>(x1 * s + x2 * c);
     }
@@ -223,12 +226,14 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, const float* __restri
     if (pass > 0) {
         for (int i = threadIdx.x; i < n_kv_heads * pass; i += blockDim.x) {
             const int h = i / pass, j = rotary_dim + (i - h * pass);
-            k_cache[cache_base + (size_t)h * head_dim + j] = row[(size_t)(n_heads + h) * head_dim + j];
+            k_cache[cache_base + (size_t)h * head_stride + j] = row[(size_t)(n_heads + h) * head_dim + j];
         }
     }
     const T* v_src = row + (size_t)(n_heads + n_kv_heads) * head_dim;
-    for (int i = threadIdx.x; i < n_kv_heads * head_dim; i += blockDim.x)
-        v_cache[cache_base + i] = v_src[i];
+    for (int i = threadIdx.x; i < n_kv_heads * head_dim; i += blockDim.x) {
+        const int h = i / head_dim;
+        v_cache[cache_base + (size_t)h * head_stride + (i - h * head_dim)] = v_src[i];
+    }
 }
 
 CB_EXPORT int cb_rope_kv_append(void* qkv, int dtype, const float* cos_t, const float* sin_t,

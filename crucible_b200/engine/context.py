@@ -41,7 +41,9 @@ class StepLayout:
 
 
 class CacheStorage:
-    """Device pages of one cache group: [slot, K|V, page, token, kv_head, feature]."""
+    """Device pages of one cache group: [slot, K|V, page, kv_head, token, feature].
+    Inside a page each KV head's tokens are contiguous (page_tokens * head_dim
+    elements in a row), so a head's keys are read in long runs."""
 
     def __init__(self, n_slots: int, n_pages: int, page_tokens: int, kv_heads: int,
                  head_dim: int, dtype: torch.dtype, device):
@@ -49,7 +51,7 @@ class CacheStorage:
         self.n_pages = n_pages
         self.kv_heads = kv_heads
         self.head_dim = head_dim
-        self.kv = torch.zeros((n_slots, 2, n_pages, page_tokens, kv_heads, head_dim),
+        self.kv = torch.zeros((n_slots, 2, n_pages, kv_heads, page_tokens, head_dim),
                               dtype=dtype, device=device)
 
     def keys(self, slot: int) -> torch.Tensor:

@@ -193,13 +193,14 @@ def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx,
     n_rep = n_heads // n_kv_heads
     split = host.max_new_tokens * n_rep <= 16
     # The split form is launched over chunks of 256 * 2^k keys that cover the step's
-    # context bucket; the chunk is the largest that still gives about two waves of
-    # blocks (a function of the step's shape alone, so a captured step replays).
+    # context bucket; the chunk is the largest that still gives a few waves of blocks
+    # over the 148 SMs (a function of the step's shape alone, so a captured step
+    # replays; contexts fill about half of their bucket on average).
     chunk_keys = 256
     if split:
         blocks_per_chunk = ctx.n_requests * n_kv_heads * (-(-host.max_new_tokens * n_rep // 16))
         while (chunk_keys * 2 <= host.context_bucket
-               and blocks_per_chunk * (host.context_bucket // (chunk_keys * 2)) >= 2 * 148):
+               and blocks_per_chunk * (host.context_bucket // (chunk_keys * 2)) >= 4 * 148):
             chunk_keys *= 2
     n_chunks = host.context_bucket // chunk_keys if split else 0
     partial = counters = None

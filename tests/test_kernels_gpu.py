@@ -217,7 +217,7 @@ def test_small_batch_qkv_rope_append(write):
     i = torch.arange(hd // 2, dtype=torch.float64)
     ang = torch.outer(torch.arange(64, dtype=torch.float64), 10000.0 ** (-2 * i / hd))
     cos, sin = ang.cos().float().to(DEV), ang.sin().float().to(DEV)
-    kv = torch.zeros(1, 2, 11, page, n_kv, hd, dtype=torch.bfloat16, device=DEV)
+    kv = torch.zeros(1, 2, 11, n_kv, page, hd, dtype=torch.bfloat16, device=DEV)
 
     class Cache:
         page_tokens = page
@@ -241,8 +241,8 @@ def test_small_batch_qkv_rope_append(write):
         assert rel(qkv[r, :n_heads * hd].view(n_heads, hd), rotate(y[r, :n_heads], pos)) < 8e-3
         page_id = int(tables[row_request[r], pos // page])
         if write:
-            assert rel(kv[0, 0, page_id, pos % page], rotate(y[r, n_heads:n_heads + n_kv], pos)) < 8e-3
-            assert rel(kv[0, 1, page_id, pos % page], y[r, n_heads + n_kv:]) < 8e-3
+            assert rel(kv[0, 0, page_id, :, pos % page], rotate(y[r, n_heads:n_heads + n_kv], pos)) < 8e-3
+            assert rel(kv[0, 1, page_id, :, pos % page], y[r, n_heads + n_kv:]) < 8e-3
     if not write:
         assert float(kv.abs().max()) == 0.0
     # a partially rotated head is refused
@@ -275,7 +275,7 @@ def _paged_case(dtype, n_heads, n_kv, hd, page_tokens, requests, seed, window=No
     total_pages = sum(-(-(c + n) // page_tokens) for c, n in requests) + 3
     order = list(range(total_pages))
     rng.shuffle(order)
-    kv = torch.full((1, 2, total_pages, page_tokens, n_kv, hd), float("nan"))   # poison
+    kv = torch.full((1, 2, total_pages, n_kv, page_tokens, hd), float("nan"))   # poison
     stride = max(-(-(c + n) // page_tokens) for c, n in requests) + 2
     tables = torch.zeros(len(requests), stride, dtype=torch.int32)
     q_rows, refs, positions, row_request, row_start, first_pos = [], [], [], [], [0], []
@@ -297,8 +297,8 @@ def _paged_case(dtype, n_heads, n_kv, hd, page_tokens, requests, seed, window=No
         pages = [order.pop() for _ in range(-(-length // page_tokens))]
         tables[r, :len(pages)] = torch.tensor(pages, dtype=torch.int32)
         for pos in range(length):
-            kv[0, 0, pages[pos // page_tokens], pos % page_tokens] = k[pos].float()
-            kv[0, 1, pages[pos // page_tokens], pos % page_tokens] = v[pos].float()
+            kv[0, 0, pages[pos // page_tokens], :, pos % page_tokens] = k[pos].float()
+            kv[0, 1, pages[pos // page_tokens], :, pos % page_tokens] = v[pos].float()
         qd, kd, vd = q.double(), k.double(), v.double()
         out = torch.zeros(n_new, n_heads, hd, dtype=torch.float64)
         for i, pos in enumerate(range(ctx_len, length)):
@@ -414,7 +414,7 @@ def test_rope_kv_append(dtype, hd, rot):
     t = len(positions)
     qkv = torch.randn(t, (n_heads + 2 * n_kv) * hd).to(dtype)
     before = qkv.clone()
-    kv = torch.zeros(1, 2, 10, page, n_kv, hd, dtype=dtype, device=DEV)
+    kv = torch.zeros(1, 2, 10, n_kv, page, hd, dtype=dtype, device=DEV)
     cos = sin = None
     if rot:
         i = torch.arange(rot // 2, dtype=torch.float64)
@@ -446,8 +446,8 @@ def test_rope_kv_append(dtype, hd, rot):
         assert rel(got[r].view(-1, hd)[:n_heads], want_q) < tol
         page_id = int(tables[row_request[r], pos // page])
         want_k = rotate(x[r, n_heads:n_heads + n_kv], pos)
-        assert rel(kv[0, 0, page_id, pos % page].cpu(), want_k) < tol
-        assert torch.equal(kv[0, 1, page_id, pos % page].cpu().double(), x[r, n_heads + n_kv:])
+        assert rel(kv[0, 0, page_id, :, pos % page].cpu(), want_k) < tol
+        assert torch.equal(kv[0, 1, page_id, :, pos % page].cpu().double(), x[r, n_heads + n_kv:])
 
 
 # ---------------------------------------------------------------------------
