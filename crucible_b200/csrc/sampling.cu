@@ -13,6 +13,7 @@
 //    generator, so a request's sequence does not depend on its neighbours.
 //  * temperature <= 0 means greedy and uses no randomness (:290-298).
 #include "common.cuh"
+#include "no_alloc_argmax.h"
 
 namespace {
 
@@ -267,3 +268,39 @@ CB_EXPORT int cb_sample_rows(const float* logits, int n_rows, int vocab, const f
 }
 
 CB_EXPORT int cb_sample_max_top_k() { return MAX_TOP_K; }
+
+// ---------------------------------------------------------------------------
+// The same two-stage argmax with its scratch inside the library, for callers
+// that cannot allocate (see no_alloc_argmax.h).  The array's name is a host-side
+// stand-in in host code, not a device address: the address is looked up once per
+// device with cudaGetSymbolAddress and that pointer is what the kernels get.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char
+    cb_argmax_static_scratch[CB_ARGMAX_STATIC_MAX_ROWS * ARGMAX_SLICES * 8];
+
+CB_EXPORT int cb_argmax_rows_static(const float* logits, int n_rows, int vocab, int* out_ids,
+                                    void* stream) {
+    if (n_rows <= 0) return 0;
+    if (n_rows > CB_ARGMAX_STATIC_MAX_ROWS) return CB_ERR_STATIC_TOO_LARGE;
+    constexpr int MAX_DEVICES = 64;
+    static void* scratch_of_device[MAX_DEVICES] = {};
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= MAX_DEVICES) return (int)cudaErrorInvalidDevice;
+    if (scratch_of_device[device] == nullptr) {
+        // set-up, once per device, with that device current
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, cb_argmax_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        scratch_of_device[device] = ptr;
+    }
+    float* part_val = (float*)scratch_of_device[device];
+    int* part_idx = (int*)(part_val + (size_t)n_rows * ARGMAX_SLICES);
+    cudaStream_t s = (cudaStream_t)stream;
+    cb_launch(argmax_slices_kernel, dim3(ARGMAX_SLICES, n_rows), dim3(256), 0, s, logits, vocab,
+              part_val, part_idx);
+    cb_launch(argmax_final_kernel, dim3(n_rows), dim3(32), 0, s, (const float*)part_val,
+              (const int*)part_idx, out_ids);
+    return cb_last_error();
+}

@@ -35,7 +35,7 @@ MODULES: Dict[str, List[str]] = {
     "elementwise": ["common.cuh"],
     "gemm_simt": ["common.cuh"],
     "attention_generic": ["common.cuh"],
-    "sampling": ["common.cuh"],
+    "sampling": ["common.cuh", "no_alloc_argmax.h"],
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}
