@@ -56,7 +56,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     const int n_tile = blockIdx.x;
     const int k_blocks = (K + BK - 1) / BK;
     volatile int* abort_flag = &s.abort_flag;
-    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    // tensor-memory columns are allocated in powers of two
+    constexpr uint32_t TMEM_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
     constexpr uint32_t STAGE_BYTES = (BM + BN) * BK * 2;
 
     if (threadIdx.x == 0) {
@@ -288,7 +289,7 @@ int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, void* C, i
 }  // namespace
 
 // W is [N, K] (for SWIGLU_BF16: [2 * inter, K], N = inter and C is [M, inter]).
-// bn: tile width, 64, 128 or 256.  status: device int, stays 0 unless a wait ran out.
+// bn: tile width: 64, 96, 128, 160, 192 or 256.  status: device int, stays 0 unless a wait ran out.
 CB_EXPORT int cb_gemm_tcgen05(const void* A, const void* W, void* C, int M, int N, int K, int lda,
                               int ldw, int ldc, int epi, int bn, int* status, void* stream) {
     if (M <= 0 || N <= 0) return 0;
@@ -304,7 +305,10 @@ CB_EXPORT int cb_gemm_tcgen05(const void* A, const void* W, void* C, int M, int 
     const int inter = epi == SWIGLU_BF16 ? N : 0;
     switch (bn) {
         case 64: return launch_epi<64, 6>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
+        case 96: return launch_epi<96, 6>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
         case 128: return launch_epi<128, 5>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
+        case 160: return launch_epi<160, 5>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
+        case 192: return launch_epi<192, 5>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
         case 256: return launch_epi<256, 4>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
     }
     return CB_ERR_UNSUPPORTED;

@@ -94,21 +94,41 @@ class Engine:
                                      dtype=torch.uint8, device=self.device)
         self.scratch = Scratch(self.device)
         self._meta_dev = None
-        self._meta_host = None
+        self._meta_ring = []
         self._sampler = None
         self._graphs = {}
         self._graph_generation = 0
         self._graph_failed = False
         self._graph_error = None
+        self._shapes_seen = {}
         self._table_rows = {}
 
+    META_RING = 4
+
     def _meta_buffers(self, n: int):
+        """The device metadata buffer (one, at a fixed address) and a pinned host
+        buffer to fill for this step.  The upload is asynchronous, so the host may
+        run ahead of the device by several steps: the pinned buffers form a ring,
+        and one is reused only after the copy that last read it has finished."""
         if self._meta_dev is None or self._meta_dev.numel() < n:
             cap = max(n, 1024)
+            torch.cuda.current_stream().synchronize()
             self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
-            self._meta_host = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+            self._meta_ring = [(torch.empty(cap, dtype=torch.int32, pin_memory=True),
+                                torch.cuda.Event()) for _ in range(self.META_RING)]
+            self._meta_used = [False] * self.META_RING
+            self._meta_at = 0
             self.scratch.generation += 1
-        return self._meta_host, self._meta_dev
+        self._meta_at = (self._meta_at + 1) % self.META_RING
+        host, event = self._meta_ring[self._meta_at]
+        if self._meta_used[self._meta_at]:
+            event.synchronize()
+        return host, self._meta_dev
+
+    def _upload_meta(self, host_t: torch.Tensor, total: int) -> None:
+        self._meta_dev[:total].copy_(host_t[:total], non_blocking=True)
+        self._meta_ring[self._meta_at][1].record()
+        self._meta_used[self._meta_at] = True
 
     # -- what the scheduler needs of an executor ----------------------------------
 
@@ -181,26 +201,36 @@ class Engine:
         ctx = self._make_context(entries)
         if token_source is not None:
             ctx.token_ids.copy_(token_source[:ctx.n_tokens])
-        if (self.options.graph and not self._graph_failed and ctx.host.all_single_token
-                and self.model.graph_safe):
-            return self._replay_or_capture(ctx)
+        if self.options.graph and not self._graph_failed:
+            if ctx.host.all_single_token:
+                if self.model.graph_safe:
+                    return self._replay_or_capture(ctx, at_once=True)
+            elif self.model.graph_safe_prompt_steps:
+                return self._replay_or_capture(ctx, at_once=False)
         return self.model.forward(ctx)
 
-    # -- CUDA graphs for decode-only steps ----------------------------------------
+    # -- CUDA graphs ----------------------------------------------------------------
     #
-    # A step in which every request brings one token has a launch sequence that
-    # depends only on (rows, wanted rows, context bucket); the metadata it reads
-    # lies at fixed addresses and is uploaded before the replay, outside the
-    # graph (as `engine/src/gpu_model.rs:1348-1380`: graphs keyed by exact batch
-    # size, metadata H2D before the launch).  A capture that fails is remembered
-    # and the engine stays eager (`gpu_model.rs:3199-3222`).
+    # The launch sequence of a step depends only on its shape: (rows, requests,
+    # wanted rows, most new tokens of a request, context bucket); everything else
+    # the kernels read from metadata at fixed addresses, uploaded before the replay
+    # and outside the graph (as `engine/src/gpu_model.rs:1348-1380`: decode graphs
+    # keyed by exact batch size, metadata H2D before the launch; and `:3193-3229`:
+    # prefill graphs keyed by length, at most 64 of them).  A decode-only shape is
+    # captured the first time it is seen, any other shape the second time.  A
+    # capture that fails is remembered and the engine stays eager
+    # (`gpu_model.rs:3199-3222`).
 
-    def _replay_or_capture(self, ctx: StepContext) -> torch.Tensor:
+    MAX_GRAPHS = 64
+
+    def _replay_or_capture(self, ctx: StepContext, at_once: bool) -> torch.Tensor:
         from .. import ops
         if self._graph_generation != self.scratch.generation:
             self._graphs.clear()
             self._graph_generation = self.scratch.generation
-        key = (ctx.n_tokens, ctx.n_logit_rows, ctx.host.context_bucket)
+        host = ctx.host
+        key = (ctx.n_tokens, ctx.n_requests, ctx.n_logit_rows, host.max_new_tokens,
+               host.context_bucket)
         hit = self._graphs.get(key)
         if hit is not None:
             graph, logits, launches = hit
@@ -211,6 +241,13 @@ class Engine:
         if self._graph_generation != self.scratch.generation:
             self._graphs.clear()
             self._graph_generation = self.scratch.generation
+        if not at_once:
+            seen = self._shapes_seen.get(key, 0) + 1
+            self._shapes_seen[key] = seen
+            if seen < 2:
+                return logits
+            if len(self._shapes_seen) > 4096:
+                self._shapes_seen.clear()
         try:
             before = ops.LAUNCHES[0]
             graph = torch.cuda.CUDAGraph()
@@ -220,6 +257,8 @@ class Engine:
             ops.LAUNCHES[0] = before
             if self._graph_generation != self.scratch.generation:
                 raise RuntimeError("scratch buffers moved during capture")
+            while len(self._graphs) >= self.MAX_GRAPHS:
+                self._graphs.pop(next(iter(self._graphs)))
             self._graphs[key] = (graph, captured, launches)
         except Exception as e:                      # stay eager from here on
             self._graph_failed = True
@@ -357,6 +396,6 @@ class Engine:
             for r, e in enumerate(entries):
                 block[r] = self._table_row(e.request, g)
         hs = HostStep([e.request for e in entries], counts, starts, held_after, slots)
-        dev_t[:total].copy_(host_t[:total], non_blocking=True)
+        self._upload_meta(host_t, total)
         return StepContext(layout=layout, meta=dev_t, caches=self.storages, state=self.state,
                            scratch=self.scratch, dtype=self.dtype, host=hs)

@@ -155,6 +155,13 @@ class DecoderModel:
     def graph_safe(self) -> bool:
         return all(getattr(part, "graph_safe", True) for _, part, _ in self._parts())
 
+    @property
+    def graph_safe_prompt_steps(self) -> bool:
+        def ok(part):
+            flag = getattr(part, "graph_safe_prompt_steps", None)
+            return getattr(part, "graph_safe", True) if flag is None else flag
+        return all(ok(part) for _, part, _ in self._parts())
+
     # -- one step -------------------------------------------------------------
 
     def forward(self, ctx) -> torch.Tensor:

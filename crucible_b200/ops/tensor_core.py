@@ -60,14 +60,22 @@ def _stream():
     return _c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+TILE_WIDTHS = (64, 96, 128, 160, 192, 256)
+N_SMS = 148
+
+
 def _tile_width(m: int, n_cols: int) -> int:
-    """Tile width in output columns.  Wider tiles reuse the A tile more; narrow
-    ones give more blocks when the problem has few tiles."""
+    """Tile width in output columns: the one that needs the least time if every
+    block costs (width + a fixed part) and blocks run in waves over the SMs.  A
+    wide tile reuses the A tile more; a narrow one fills the last wave better."""
     m_tiles = -(-m // 128)
-    for bn in (256, 128):
-        if m_tiles * -(-n_cols // bn) >= 90:       # enough blocks for most of the 148 SMs
-            return bn
-    return 64
+    best, best_cost = 64, None
+    for bn in TILE_WIDTHS:
+        blocks = m_tiles * -(-n_cols // bn)
+        cost = -(-blocks // N_SMS) * (bn + 48)
+        if best_cost is None or cost < best_cost or (cost == best_cost and bn > best):
+            best, best_cost = bn, cost
+    return best
 
 
 def _gemm(a, w, out, n, epi, bn) -> bool:

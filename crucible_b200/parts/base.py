@@ -72,8 +72,12 @@ class Part:
     # A part whose launches depend only on the step's shape and on device-side
     # metadata can be replayed from a captured CUDA graph.  A part that reads
     # per-step values on the host (other than the shape) sets this to False and
-    # the engine then runs every step eagerly.
+    # the engine then runs every step eagerly.  `graph_safe_prompt_steps` says the same
+    # for steps in which some request brings more than one token (a part may, for
+    # instance, walk such portions in a host loop but run decode steps from device
+    # metadata alone); None means "as graph_safe".
     graph_safe = True
+    graph_safe_prompt_steps = None
 
     def tensors(self) -> List[TensorDecl]:
         return []

@@ -92,7 +92,7 @@ def test_linear_plain_fp32(m, n, k):
     assert rel(acc, ref + base.double()) < 2e-6
 
 
-@pytest.mark.parametrize("tile", [64, 128, 256])
+@pytest.mark.parametrize("tile", [64, 96, 128, 160, 192, 256])
 @pytest.mark.parametrize("m,n,k", SHAPES)
 def test_linear_tensor_core(m, n, k, tile):
     from crucible_b200.ops import tensor_core
@@ -112,7 +112,7 @@ def test_linear_tensor_core(m, n, k, tile):
     tensor_core.check_status(DEV)
 
 
-@pytest.mark.parametrize("tile", [64, 128, 256])
+@pytest.mark.parametrize("tile", [64, 96, 128, 160, 192, 256])
 @pytest.mark.parametrize("m,inter,k", [(1, 176, 64), (33, 320, 96), (300, 2048, 768), (130, 88, 40)])
 def test_linear_swiglu_tensor_core(m, inter, k, tile):
     from crucible_b200.ops import tensor_core

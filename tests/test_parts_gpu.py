@@ -112,6 +112,8 @@ def _register_toys():
 
     class EmaMixer(Mixer):
         """State of fixed size per request: s = decay * s + (1 - decay) * h, y = s W^T."""
+        graph_safe_prompt_steps = False      # portions are walked in a host loop below
+
         def __init__(self, spec):
             self.spec = spec
             self.decay = float(spec.option("decay"))
