@@ -284,6 +284,57 @@ def run_ours(args):
     return 0
 
 
+def run_profile_case(args):
+    """A small workload for a profiler (ncu): builds the 120M shape with
+    `--layers` layers, fills `--batch` requests to `--context` tokens, then runs
+    `--steps` eager steps of the named kind between cudaProfilerStart and
+    cudaProfilerStop, so that `ncu --profile-from-start off` sees only those."""
+    import torch
+    from crucible_b200 import LLM, ops
+    from crucible_b200.config import shape
+    from crucible_b200.engine import StepEntry
+    from crucible_b200.weights import write_random_model
+    raw = shape("120m")
+    if args.layers:
+        raw["n_layer"] = args.layers
+    rng = random.Random(1)
+    with tempfile.TemporaryDirectory() as tmp:
+        folder = write_random_model(raw, os.path.join(tmp, "model"), seed=0)
+        pages = 64 * (-(-(args.context + args.steps + 64) // 16)) + 64
+        llm = LLM(folder, dtype="bfloat16", max_batch=64, kv_pages=pages, prefill_token_budget=2048,
+                  graph=False)
+    engine = llm.engine
+    vocab = engine.config.vocab_size
+    if args.profile_case == "prefill":
+        tokens = [rng.randrange(vocab) for _ in range(2048)]
+        engine.step([StepEntry("w", tokens, [2047])])
+        engine.finish("w")
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        for i in range(args.steps):
+            engine.step([StepEntry("p", tokens, [2047])])
+            engine.finish("p")
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    else:
+        ids = [f"d{i}" for i in range(args.batch)]
+        for rid in ids:
+            engine.step([StepEntry(rid, [rng.randrange(vocab) for _ in range(args.context - 1)], [])])
+        chosen = torch.zeros(args.batch, dtype=torch.int32, device=engine.device)
+        entries = [StepEntry(rid, [0], [0]) for rid in ids]
+        for _ in range(2):
+            ops.argmax_rows(engine.step(entries, token_source=chosen), chosen)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        for _ in range(args.steps):
+            ops.argmax_rows(engine.step(entries, token_source=chosen), chosen)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    print(f"profile case {args.profile_case}: {args.steps} steps, batch {args.batch}, "
+          f"{engine.config.n_layers} layers")
+    return 0
+
+
 def main():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
@@ -294,7 +345,11 @@ def main():
     p.add_argument("--context", type=int, default=2048)
     p.add_argument("--layers", type=int, default=0,
                    help="fewer layers than the shape has (both numbers are reported)")
+    p.add_argument("--profile-case", default=None, choices=["prefill", "decode"],
+                   help="run a small eager workload for a profiler instead of the benchmark")
     args = p.parse_args()
+    if args.profile_case:
+        return run_profile_case(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

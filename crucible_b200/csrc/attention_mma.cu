@@ -465,7 +465,7 @@ struct SplitShape {
     // keys per sub-tile and ring depth per warp, sized so that two blocks fit an SM
     // for head sizes up to 64 and one beyond
     static constexpr int SUB = HD_MAX <= 128 ? 32 : 16;
-    static constexpr int RING = HD_MAX <= 64 ? 3 : 2;
+    static constexpr int RING = 2;
 };
 
 
