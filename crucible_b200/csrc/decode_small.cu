@@ -129,62 +129,9 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
     // the weights above are written by no kernel; everything below reads what earlier
     // kernels of the stream produced
     cb_pdl_wait();
-    // ---- stage the step's rows in shared memory as bf16 (normalised if asked) -------------
-    if (NORM_IN) {
-        // each warp normalises rows `warp` and `warp + 4` side by side, so that both
-        // rows' loads are in flight together
-        const int n4 = K >> 2;
-        const float4* g4 = reinterpret_cast<const float4*>(p.gain);
-        const int ma = warp, mb = warp + WARPS;
-        const bool has_a = ma < p.M, has_b = mb < p.M;
-        const float4* row_a = reinterpret_cast<const float4*>(p.x + (size_t)(has_a ? ma : 0) * K);
-        const float4* row_b = reinterpret_cast<const float4*>(p.x + (size_t)(has_b ? mb : 0) * K);
-        uint2* dst_a = reinterpret_cast<uint2*>(xs + (size_t)ma * pitch);
-        uint2* dst_b = reinterpret_cast<uint2*>(xs + (size_t)mb * pitch);
-        float ss_a = 0.f, ss_b = 0.f;
-        if (has_a) {
-#pragma unroll 4
-            for (int j = lane; j < n4; j += 32) {
-                const float4 va = row_a[j];
-                const float4 vb = has_b ? row_b[j] : make_float4(0.f, 0.f, 0.f, 0.f);
-                ss_a = fmaf(va.x, va.x, ss_a); ss_a = fmaf(va.y, va.y, ss_a);
-                ss_a = fmaf(va.z, va.z, ss_a); ss_a = fmaf(va.w, va.w, ss_a);
-                ss_b = fmaf(vb.x, vb.x, ss_b); ss_b = fmaf(vb.y, vb.y, ss_b);
-                ss_b = fmaf(vb.z, vb.z, ss_b); ss_b = fmaf(vb.w, vb.w, ss_b);
-            }
-        }
-        ss_a = cb_warp_sum(ss_a);
-        ss_b = cb_warp_sum(ss_b);
-        const float r_a = 1.0f / sqrtf(ss_a / (float)K + p.eps);
-        const float r_b = 1.0f / sqrtf(ss_b / (float)K + p.eps);
-#pragma unroll 4
-        for (int j = lane; j < n4; j += 32) {
-            uint2 oa = make_uint2(0, 0), ob = make_uint2(0, 0);
-            if (has_a) {
-                const float4 gn = g4[j];
-                const float4 va = row_a[j];
-                oa = make_uint2(pack2(va.x * r_a * gn.x, va.y * r_a * gn.y),
-                                pack2(va.z * r_a * gn.z, va.w * r_a * gn.w));
-                if (has_b) {
-                    const float4 vb = row_b[j];
-                    ob = make_uint2(pack2(vb.x * r_b * gn.x, vb.y * r_b * gn.y),
-                                    pack2(vb.z * r_b * gn.z, vb.w * r_b * gn.w));
-                }
-            }
-            dst_a[j] = oa;
-            dst_b[j] = ob;
-        }
-    } else {
-        const int n8 = K >> 3;
-#pragma unroll 4
-        for (int i = threadIdx.x; i < 8 * n8; i += blockDim.x) {
-            const int m = i / n8, c = i - m * n8;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (m < p.M) v = *reinterpret_cast<const uint4*>(p.a + (size_t)m * p.lda + c * 8);
-            *reinterpret_cast<uint4*>(xs + (size_t)m * pitch + c * 8) = v;
-        }
-    }
-    // ACCUM: the residual values this block will add to, fetched while the rows settle
+    // What the epilogue will need from memory is asked for now, before the staging, so
+    // that every round trip of this kernel's prologue is in flight at the same time.
+    // ACCUM: the residual values this block will add to.
     float old[4] = {0.f, 0.f, 0.f, 0.f};
     const int m0 = 2 * t, m1 = 2 * t + 1;
     if (EPI == ACCUM_F32 && warp == 0) {
@@ -195,7 +142,7 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
         if (m1 < p.M && ok_s) old[3] = out[(size_t)m1 * p.ldc + rs];
     }
     // ROPE_APPEND: positions, rotation factors and cache pages of the two step rows this
-    // thread will finish, fetched now so that their round trips overlap the multiply
+    // thread will finish.
     int pos2[2] = {0, 0}, page2[2] = {0, 0};
     float cs2[2] = {1.f, 1.f}, sn2[2] = {0.f, 0.f};
     if (EPI == ROPE_APPEND && warp == 0 && ok_f) {
@@ -216,6 +163,104 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
                 }
             }
         }
+    }
+    // ---- stage the step's rows in shared memory as bf16 (normalised if asked) -------------
+    if (NORM_IN) {
+        // each warp normalises rows `warp` and `warp + 4` side by side; for widths up to
+        // 1024 both rows and the gain stay in registers between the two passes, so the
+        // whole staging is one round trip
+        const int n4 = K >> 2;
+        const float4* g4 = reinterpret_cast<const float4*>(p.gain);
+        const int ma = warp, mb = warp + WARPS;
+        const bool has_a = ma < p.M, has_b = mb < p.M;
+        const float4* row_a = reinterpret_cast<const float4*>(p.x + (size_t)(has_a ? ma : 0) * K);
+        const float4* row_b = reinterpret_cast<const float4*>(p.x + (size_t)(has_b ? mb : 0) * K);
+        uint2* dst_a = reinterpret_cast<uint2*>(xs + (size_t)ma * pitch);
+        uint2* dst_b = reinterpret_cast<uint2*>(xs + (size_t)mb * pitch);
+        constexpr int J = 8;
+        const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (n4 <= 32 * J) {
+            float4 va[J], vb[J], gn[J];
+#pragma unroll
+            for (int j = 0; j < J; ++j) {
+                const int i = lane + 32 * j;
+                const bool in = i < n4;
+                va[j] = (in && has_a) ? row_a[i] : zero4;
+                vb[j] = (in && has_b) ? row_b[i] : zero4;
+                gn[j] = in ? g4[i] : zero4;
+            }
+            float ss_a = 0.f, ss_b = 0.f;
+#pragma unroll
+            for (int j = 0; j < J; ++j) {
+                ss_a = fmaf(va[j].x, va[j].x, ss_a); ss_a = fmaf(va[j].y, va[j].y, ss_a);
+                ss_a = fmaf(va[j].z, va[j].z, ss_a); ss_a = fmaf(va[j].w, va[j].w, ss_a);
+                ss_b = fmaf(vb[j].x, vb[j].x, ss_b); ss_b = fmaf(vb[j].y, vb[j].y, ss_b);
+                ss_b = fmaf(vb[j].z, vb[j].z, ss_b); ss_b = fmaf(vb[j].w, vb[j].w, ss_b);
+            }
+            ss_a = cb_warp_sum(ss_a);
+            ss_b = cb_warp_sum(ss_b);
+            const float r_a = 1.0f / sqrtf(ss_a / (float)K + p.eps);
+            const float r_b = 1.0f / sqrtf(ss_b / (float)K + p.eps);
+#pragma unroll
+            for (int j = 0; j < J; ++j) {
+                const int i = lane + 32 * j;
+                if (i < n4) {
+                    dst_a[i] = make_uint2(pack2(va[j].x * r_a * gn[j].x, va[j].y * r_a * gn[j].y),
+                                          pack2(va[j].z * r_a * gn[j].z, va[j].w * r_a * gn[j].w));
+                    dst_b[i] = make_uint2(pack2(vb[j].x * r_b * gn[j].x, vb[j].y * r_b * gn[j].y),
+                                          pack2(vb[j].z * r_b * gn[j].z, vb[j].w * r_b * gn[j].w));
+                }
+            }
+        } else {
+            float ss_a = 0.f, ss_b = 0.f;
+            if (has_a) {
+#pragma unroll 4
+                for (int j = lane; j < n4; j += 32) {
+                    const float4 va = row_a[j];
+                    const float4 vb = has_b ? row_b[j] : zero4;
+                    ss_a = fmaf(va.x, va.x, ss_a); ss_a = fmaf(va.y, va.y, ss_a);
+                    ss_a = fmaf(va.z, va.z, ss_a); ss_a = fmaf(va.w, va.w, ss_a);
+                    ss_b = fmaf(vb.x, vb.x, ss_b); ss_b = fmaf(vb.y, vb.y, ss_b);
+                    ss_b = fmaf(vb.z, vb.z, ss_b); ss_b = fmaf(vb.w, vb.w, ss_b);
+                }
+            }
+            ss_a = cb_warp_sum(ss_a);
+            ss_b = cb_warp_sum(ss_b);
+            const float r_a = 1.0f / sqrtf(ss_a / (float)K + p.eps);
+            const float r_b = 1.0f / sqrtf(ss_b / (float)K + p.eps);
+#pragma unroll 4
+            for (int j = lane; j < n4; j += 32) {
+                uint2 oa = make_uint2(0, 0), ob = make_uint2(0, 0);
+                if (has_a) {
+                    const float4 gn = g4[j];
+                    const float4 va = row_a[j];
+                    oa = make_uint2(pack2(va.x * r_a * gn.x, va.y * r_a * gn.y),
+                                    pack2(va.z * r_a * gn.z, va.w * r_a * gn.w));
+                    if (has_b) {
+                        const float4 vb = row_b[j];
+                        ob = make_uint2(pack2(vb.x * r_b * gn.x, vb.y * r_b * gn.y),
+                                        pack2(vb.z * r_b * gn.z, vb.w * r_b * gn.w));
+                    }
+                }
+                dst_a[j] = oa;
+                dst_b[j] = ob;
+            }
+        }
+    } else {
+        // bf16 rows go to shared memory as they are: asynchronous 16-byte copies, all in
+        // flight at once; rows past the step's last are zero-filled
+        const int n8 = K >> 3;
+        for (int i = threadIdx.x; i < 8 * n8; i += blockDim.x) {
+            const int m = i / n8, c = i - m * n8;
+            const bool in = m < p.M;
+            const __nv_bfloat16* src = p.a + (size_t)(in ? m : 0) * p.lda + c * 8;
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(xs + (size_t)m * pitch + c * 8);
+            const int bytes = in ? 16 : 0;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
+                         "r"(bytes) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
     // ---- multiply: this warp's blocks of K -------------------------------------------------
