@@ -5,15 +5,19 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------
-// embedding: out[t, :] = float(table[ids[t], :])
+// embedding: out[t, :] = float(table[ids[t], :]).  A negative id -(s + 1) means
+// "the token the engine last chose for state slot s", read from device_tokens[s]:
+// a decoded token then never has to visit the host before it is run.
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                  float* __restrict__ out, int width, int vocab) {
+                                  float* __restrict__ out, int width, int vocab,
+                                  const int* __restrict__ device_tokens) {
     cb_pdl_trigger();
     cb_pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
+    if (id < 0 && device_tokens != nullptr) id = device_tokens[-id - 1];
     // ids are validated on the host; an id outside the table still must not
     // read outside it
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
@@ -23,15 +27,16 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __rest
 }
 
 CB_EXPORT int cb_embed_rows(const void* table, int table_dtype, const int* ids, float* out,
-                            int n_rows, int width, int vocab, void* stream) {
+                            int n_rows, int width, int vocab, const int* device_tokens,
+                            void* stream) {
     if (n_rows <= 0) return 0;
     const int threads = width >= 256 ? 256 : 64;
     if (table_dtype == CB_F32)
         cb_launch(embed_rows_kernel<float>, dim3(n_rows), dim3(threads), 0, (cudaStream_t)stream, 
-            (const float*)table, ids, out, width, vocab);
+            (const float*)table, ids, out, width, vocab, device_tokens);
     else
         cb_launch(embed_rows_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, (cudaStream_t)stream, 
-            (const __nv_bfloat16*)table, ids, out, width, vocab);
+            (const __nv_bfloat16*)table, ids, out, width, vocab, device_tokens);
     return cb_last_error();
 }
 

@@ -33,6 +33,15 @@ __device__ __forceinline__ unsigned long long sort_key(float v, int id) {
     return ((unsigned long long)value_key(v) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)id);
 }
 
+// If `scatter_index` is given, the chosen id of row r is also written to
+// scatter_out[scatter_index[r]]: the engine keeps each request's latest token
+// on the device that way, so that the next step can read it without the host.
+__device__ __forceinline__ void publish(int row, int id, int* out_ids, const int* scatter_index,
+                                        int* scatter_out) {
+    out_ids[row] = id;
+    if (scatter_index != nullptr) scatter_out[scatter_index[row]] = id;
+}
+
 __device__ void block_argmax(const float* row, int vocab, int* out_id, float* s_val, int* s_idx) {
     float bv = -INFINITY;
     int bi = 0x7fffffff;
@@ -61,7 +70,8 @@ __device__ void block_argmax(const float* row, int vocab, int* out_id, float* s_
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
                    const int* __restrict__ top_k, const float* __restrict__ uniform,
-                   int* __restrict__ out_ids) {
+                   int* __restrict__ out_ids, const int* __restrict__ scatter_index,
+                   int* __restrict__ scatter_out) {
     cb_pdl_trigger();
     cb_pdl_wait();
     __shared__ float s_val[32];
@@ -76,7 +86,9 @@ sample_rows_kernel(const float* __restrict__ logits, int vocab, const float* __r
     const float* row = logits + (size_t)row_i * vocab;
     const float temp = temperature ? temperature[row_i] : 0.f;
     if (!(temp > 0.f)) {
-        block_argmax(row, vocab, out_ids + row_i, s_val, s_idx);
+        __shared__ int greedy_id;
+        block_argmax(row, vocab, &greedy_id, s_val, s_idx);
+        if (threadIdx.x == 0) publish(row_i, greedy_id, out_ids, scatter_index, scatter_out);
         return;
     }
     int k = top_k[row_i];
@@ -164,17 +176,20 @@ sample_rows_kernel(const float* __restrict__ logits, int vocab, const float* __r
                 if (acc >= threshold) { chosen = id; break; }
             }
         }
-        out_ids[row_i] = chosen;
+        publish(row_i, chosen, out_ids, scatter_index, scatter_out);
     }
 }
 
 __global__ void __launch_bounds__(256)
-argmax_rows_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out_ids) {
+argmax_rows_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out_ids,
+                   const int* __restrict__ scatter_index, int* __restrict__ scatter_out) {
     cb_pdl_trigger();
     cb_pdl_wait();
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
-    block_argmax(logits + (size_t)blockIdx.x * vocab, vocab, out_ids + blockIdx.x, s_val, s_idx);
+    __shared__ int id;
+    block_argmax(logits + (size_t)blockIdx.x * vocab, vocab, &id, s_val, s_idx);
+    if (threadIdx.x == 0) publish(blockIdx.x, id, out_ids, scatter_index, scatter_out);
 }
 
 // Two-stage argmax for wide rows: stage one reduces a slice of the row per
@@ -218,7 +233,9 @@ argmax_slices_kernel(const float* __restrict__ logits, int vocab, float* __restr
 }
 
 __global__ void argmax_final_kernel(const float* __restrict__ part_val,
-                                    const int* __restrict__ part_idx, int* __restrict__ out_ids) {
+                                    const int* __restrict__ part_idx, int* __restrict__ out_ids,
+                                    const int* __restrict__ scatter_index,
+                                    int* __restrict__ scatter_out) {
     cb_pdl_trigger();
     cb_pdl_wait();
     const int row = blockIdx.x, lane = threadIdx.x;
@@ -230,7 +247,7 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_val,
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
         if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
-    if (lane == 0) out_ids[row] = bi == 0x7fffffff ? 0 : bi;
+    if (lane == 0) publish(row, bi == 0x7fffffff ? 0 : bi, out_ids, scatter_index, scatter_out);
 }
 
 }  // namespace
@@ -238,18 +255,21 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_val,
 // scratch: n_rows * 32 floats followed by n_rows * 32 ints (cb_argmax_scratch_bytes),
 // or null: then one block per row does the whole row.
 CB_EXPORT int cb_argmax_rows(const float* logits, int n_rows, int vocab, int* out_ids,
-                             void* scratch, void* stream) {
+                             void* scratch, const int* scatter_index, int* scatter_out,
+                             void* stream) {
     if (n_rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (scratch == nullptr || vocab < 4096) {
-        cb_launch(argmax_rows_kernel, dim3(n_rows), dim3(256), 0, s, logits, vocab, out_ids);
+        cb_launch(argmax_rows_kernel, dim3(n_rows), dim3(256), 0, s, logits, vocab, out_ids,
+                  scatter_index, scatter_out);
         return cb_last_error();
     }
     float* part_val = (float*)scratch;
     int* part_idx = (int*)(part_val + (size_t)n_rows * ARGMAX_SLICES);
     cb_launch(argmax_slices_kernel, dim3(ARGMAX_SLICES, n_rows), dim3(256), 0, s, logits, vocab, part_val,
                                                                      part_idx);
-    cb_launch(argmax_final_kernel, dim3(n_rows), dim3(32), 0, s, part_val, part_idx, out_ids);
+    cb_launch(argmax_final_kernel, dim3(n_rows), dim3(32), 0, s, (const float*)part_val,
+              (const int*)part_idx, out_ids, scatter_index, scatter_out);
     return cb_last_error();
 }
 
@@ -259,11 +279,11 @@ CB_EXPORT long cb_argmax_scratch_bytes(int n_rows) { return (long)n_rows * ARGMA
 // the launcher refuses k above the kernel's candidate capacity.
 CB_EXPORT int cb_sample_rows(const float* logits, int n_rows, int vocab, const float* temperature,
                              const int* top_k, const float* uniform, int max_top_k, int* out_ids,
-                             void* stream) {
+                             const int* scatter_index, int* scatter_out, void* stream) {
     if (n_rows <= 0) return 0;
     if (max_top_k > MAX_TOP_K) return CB_ERR_UNSUPPORTED;
     cb_launch(sample_rows_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, 
-        logits, vocab, temperature, top_k, uniform, out_ids);
+        logits, vocab, temperature, top_k, uniform, out_ids, scatter_index, scatter_out);
     return cb_last_error();
 }
 
@@ -301,6 +321,6 @@ CB_EXPORT int cb_argmax_rows_static(const float* logits, int n_rows, int vocab, 
     cb_launch(argmax_slices_kernel, dim3(ARGMAX_SLICES, n_rows), dim3(256), 0, s, logits, vocab,
               part_val, part_idx);
     cb_launch(argmax_final_kernel, dim3(n_rows), dim3(32), 0, s, (const float*)part_val,
-              (const int*)part_idx, out_ids);
+              (const int*)part_idx, out_ids, (const int*)nullptr, (int*)nullptr);
     return cb_last_error();
 }

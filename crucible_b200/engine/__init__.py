@@ -1,2 +1,2 @@
 from .context import CacheStorage, HostStep, Scratch, StepContext, StepLayout
-from .engine import Engine, EngineOptions, StepEntry, StepError, parse_dtype
+from .engine import DEVICE_TOKEN, Engine, EngineOptions, StepEntry, StepError, parse_dtype

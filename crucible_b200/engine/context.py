@@ -91,7 +91,7 @@ class StepContext:
 
     def __init__(self, *, layout: StepLayout, meta: torch.Tensor, caches: List[CacheStorage],
                  state: Optional[torch.Tensor], scratch: Scratch, dtype: torch.dtype,
-                 host: "HostStep"):
+                 host: "HostStep", device_tokens: Optional[torch.Tensor] = None):
         self.layout = layout
         self.dtype = dtype
         self.n_tokens = layout.n_tokens
@@ -101,6 +101,7 @@ class StepContext:
         self._state = state
         self._scratch = scratch
         self.host = host
+        self.device_tokens = device_tokens     # int32 per state slot: the token last chosen
         off = layout.offsets()
 
         def view(name):

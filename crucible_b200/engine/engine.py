@@ -49,6 +49,11 @@ class StepError(ValueError):
     pass
 
 
+# As the only token of an entry: "the token the engine last chose for this request",
+# which it kept on the device (see `Engine.sample`); the host need not know it yet.
+DEVICE_TOKEN = -1
+
+
 @dataclass
 class EngineOptions:
     dtype: object = "bfloat16"
@@ -93,6 +98,7 @@ class Engine:
             self.state = torch.zeros((o.max_requests, self.model.state_bytes),
                                      dtype=torch.uint8, device=self.device)
         self.scratch = Scratch(self.device)
+        self.device_tokens = torch.zeros(o.max_requests, dtype=torch.int32, device=self.device)
         self._meta_dev = None
         self._meta_ring = []
         self._sampler = None
@@ -145,11 +151,24 @@ class Engine:
         from .. import ops
         return ops.max_device_top_k()
 
-    def sample(self, logits: torch.Tensor, rows) -> List[int]:
+    def _get_sampler(self):
         if self._sampler is None:
             from ..sampling.sampler import Sampler
             self._sampler = Sampler(self.device, self.config.vocab_size)
-        return self._sampler.sample(logits, rows)
+        return self._sampler
+
+    def sample(self, logits: torch.Tensor, rows) -> List[int]:
+        """Chooses a token for every row of `logits`; returns the ids."""
+        return self._get_sampler().sample(logits, rows)
+
+    def sample_deferred(self, logits: torch.Tensor, rows, requests):
+        """Chooses a token for every row and keeps it on the device as the latest
+        token of `requests[i]` (an entry with tokens [DEVICE_TOKEN] runs it).  The
+        ids travel to the host asynchronously; the returned object's `get()` waits
+        for them."""
+        slots = [self.cache.state_slot(r) for r in requests]
+        return self._get_sampler().sample(logits, rows, slots=slots,
+                                          scatter_out=self.device_tokens, defer=True)
 
     # -- requests ---------------------------------------------------------------
 
@@ -288,7 +307,10 @@ class Engine:
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"request {e.request!r} brings no tokens")
-            if min(e.tokens) < 0 or max(e.tokens) >= vocab:
+            if n == 1 and e.tokens[0] == DEVICE_TOKEN:
+                if not cache.has(e.request):
+                    raise StepError(f"request {e.request!r} has no token on the device yet")
+            elif min(e.tokens) < 0 or max(e.tokens) >= vocab:
                 bad = next(t for t in e.tokens if not 0 <= t < vocab)
                 raise StepError(f"request {e.request!r}: token {bad} is outside the "
                                 f"vocabulary of {vocab}")
@@ -368,11 +390,14 @@ class Engine:
         for r, n in enumerate(counts):
             row_starts[r + 1] = row_starts[r] + n
         if n_tokens == n_req:                                  # every request brings one token
-            tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=n_req)
+            tokens = np.fromiter((e.tokens[0] if e.tokens[0] != DEVICE_TOKEN else -(s + 1)
+                                  for e, s in zip(entries, slots)), dtype=np.int64, count=n_req)
             piece("positions")[:] = starts
             piece("row_request")[:] = np.arange(n_req, dtype=np.int32)
         else:
-            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+            tokens = np.concatenate([
+                np.asarray(e.tokens if e.tokens[0] != DEVICE_TOKEN or len(e.tokens) > 1
+                           else [-(s + 1)], dtype=np.int64) for e, s in zip(entries, slots)])
             counts_np = np.asarray(counts)
             owner = np.repeat(np.arange(n_req, dtype=np.int32), counts_np)
             piece("row_request")[:] = owner
@@ -398,4 +423,5 @@ class Engine:
         hs = HostStep([e.request for e in entries], counts, starts, held_after, slots)
         self._upload_meta(host_t, total)
         return StepContext(layout=layout, meta=dev_t, caches=self.storages, state=self.state,
-                           scratch=self.scratch, dtype=self.dtype, host=hs)
+                           scratch=self.scratch, dtype=self.dtype, host=hs,
+                           device_tokens=self.device_tokens)

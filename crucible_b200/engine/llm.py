@@ -58,4 +58,7 @@ class LLM:
             for c in sched.done:
                 done[c.id] = c
             sched.done = []
+        sched.flush()
+        for c in sched.done:
+            done[c.id] = c
         return [done[i].tokens for i in range(len(prompts))]

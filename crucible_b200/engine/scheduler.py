@@ -39,7 +39,7 @@ from typing import Deque, Dict, Hashable, List, Optional, Sequence
 
 from ..sampling.params import SamplingParams
 from ..sampling.rng import Xorshift64Star
-from .engine import StepEntry
+from .engine import DEVICE_TOKEN, StepEntry
 
 DEFAULT_PREFILL_TOKEN_BUDGET = 1024     # runtime.rs:208
 DEFAULT_PREFILL_CHUNK = 128             # runtime.rs:205 (a cap; off unless asked for)
@@ -89,7 +89,8 @@ class _Live:
     done: int = 0                                  # prompt tokens already run
     generated: List[int] = field(default_factory=list)
     rng: Optional[Xorshift64Star] = None
-    next_token: Optional[int] = None               # chosen, not yet run
+    next_token: Optional[int] = None               # chosen, not yet run; None: still on the device
+    n_chosen: int = 0                              # tokens chosen so far (known before their values)
 
 
 @dataclass
@@ -118,6 +119,13 @@ class Scheduler:
         self.active: List[_Live] = []
         self.done: List[Completion] = []
         self.step_no = 0
+        # Tokens chosen by the last step whose values have not reached the host yet:
+        # (ids on their way, [(live, is_first_token), ...]).  With an executor that can
+        # keep a request's latest token on the device (`sample_deferred`), a step is
+        # queued before the previous step's ids are read, so the device never waits for
+        # the host between steps; values are needed earlier only for eos_token_id.
+        self._in_flight = None
+        self._finishing: List[tuple] = []          # (live, reason) waiting for their last values
 
     # -- submission ---------------------------------------------------------------
 
@@ -152,6 +160,8 @@ class Scheduler:
     # -- one iteration ------------------------------------------------------------
 
     def has_work(self) -> bool:
+        """Requests still to be run.  When this turns false, `flush()` brings in the
+        last token values."""
         return bool(self.pending or self.prefilling or self.active)
 
     def step(self) -> StepInfo:
@@ -161,7 +171,8 @@ class Scheduler:
         entries: List[StepEntry] = []
         sample_rows = []                     # (live, is_first_token)
         for live in self.active:
-            entries.append(StepEntry(live.request.id, [live.next_token], [0]))
+            token = live.next_token if live.next_token is not None else DEVICE_TOKEN
+            entries.append(StepEntry(live.request.id, [token], [0]))
             sample_rows.append((live, False))
         info.decoded = len(self.active)
         plan = self._plan_prefill(budget=self.options.prefill_token_budget - len(self.active))
@@ -181,11 +192,26 @@ class Scheduler:
                 if first and not live.request.params.is_greedy:
                     live.rng = Xorshift64Star(live.request.params.seed)
                 rows.append((live.request.params, live.rng))
-            chosen = self.executor.sample(logits, rows)
-            for (live, first), tok in zip(sample_rows, chosen):
-                live.generated.append(int(tok))
-                live.next_token = int(tok)
-                info.first_tokens += int(first)
+            defer = (rows and hasattr(self.executor, "sample_deferred")
+                     and all(p.eos_token_id is None for p, _ in rows))
+            previous, self._in_flight = self._in_flight, None
+            if defer:
+                ids = self.executor.sample_deferred(logits, rows,
+                                                    [live.request.id for live, _ in sample_rows])
+                for live, first in sample_rows:
+                    live.n_chosen += 1
+                    live.next_token = None
+                    info.first_tokens += int(first)
+                self._in_flight = (ids, list(sample_rows))
+                self._resolve(previous)            # the step before: its ids have long arrived
+            else:
+                self._resolve(previous)
+                chosen = self.executor.sample(logits, rows)
+                for (live, first), tok in zip(sample_rows, chosen):
+                    live.generated.append(int(tok))
+                    live.next_token = int(tok)
+                    live.n_chosen += 1
+                    info.first_tokens += int(first)
         # bookkeeping of the prefill queue: finished prompts start decoding,
         # unfinished ones go to the back
         for live, n in plan:
@@ -233,6 +259,29 @@ class Scheduler:
             used += n
         return plan
 
+    def _resolve(self, in_flight) -> None:
+        """Reads the values of tokens chosen earlier and files them."""
+        if in_flight is None:
+            return
+        ids, rows = in_flight
+        for (live, _), tok in zip(rows, ids.get()):
+            live.generated.append(int(tok))
+            if len(live.generated) == live.n_chosen:
+                live.next_token = int(tok)
+        still = []
+        for live, reason in self._finishing:
+            if len(live.generated) == live.n_chosen:
+                self.done.append(Completion(live.request.id, len(live.request.prompt),
+                                            live.generated, reason))
+            else:
+                still.append((live, reason))
+        self._finishing = still
+
+    def flush(self) -> None:
+        """Waits for every token value still on its way."""
+        previous, self._in_flight = self._in_flight, None
+        self._resolve(previous)
+
     def _retire(self) -> int:
         n = 0
         i = 0
@@ -240,7 +289,7 @@ class Scheduler:
             live = self.active[i]
             p = live.request.params
             reason = None
-            if len(live.generated) >= p.max_tokens:
+            if live.n_chosen >= p.max_tokens:
                 reason = "length"
             elif (p.eos_token_id is not None and live.generated
                   and live.generated[-1] == p.eos_token_id):
@@ -252,8 +301,11 @@ class Scheduler:
             self.active[i] = self.active[-1]
             self.active.pop()
             self.executor.finish(live.request.id)
-            self.done.append(Completion(live.request.id, len(live.request.prompt),
-                                        live.generated, reason))
+            if len(live.generated) == live.n_chosen:
+                self.done.append(Completion(live.request.id, len(live.request.prompt),
+                                            live.generated, reason))
+            else:
+                self._finishing.append((live, reason))     # its last value is still on its way
             n += 1
         return n
 
@@ -264,6 +316,7 @@ class Scheduler:
                 del self.pending[i]
                 self.done.append(Completion(request_id, len(r.prompt), [], "cancelled"))
                 return True
+        self.flush()
         for queue in (self.prefilling, self.active):
             for live in list(queue):
                 if live.request.id == request_id:
@@ -284,5 +337,6 @@ class Scheduler:
                                      "cannot be admitted and nothing is running")
             if max_steps is not None and steps >= max_steps:
                 break
+        self.flush()
         out, self.done = self.done, []
         return out

@@ -74,15 +74,17 @@ def _check(code: int, what: str) -> None:
 # row-wise kernels
 # ---------------------------------------------------------------------------
 
-def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
-    _need_cuda(table, ids, out)
+def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor,
+               device_tokens: Optional[torch.Tensor] = None) -> None:
+    """`device_tokens`: int32 per state slot; an id -(s + 1) reads device_tokens[s]."""
+    _need_cuda(table, ids, out, device_tokens)
     if ids.dtype != torch.int32 or out.dtype != torch.float32:
         raise KernelError("embed_rows takes int32 ids and a float32 output")
     _contig(table, "embedding table"); _contig(out, "embed_rows output")
     lib = build.load("elementwise")
     _check(lib.cb_embed_rows(_ptr(table), _c_int(_code(table.dtype)), _ptr(ids), _ptr(out),
                              _c_int(ids.shape[0]), _c_int(table.shape[1]),
-                             _c_int(table.shape[0]), _stream()), "embed_rows")
+                             _c_int(table.shape[0]), _ptr(device_tokens), _stream()), "embed_rows")
 
 
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor) -> None:
@@ -241,8 +243,12 @@ def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx,
 # token selection
 # ---------------------------------------------------------------------------
 
-def argmax_rows(logits: torch.Tensor, out_ids: torch.Tensor) -> None:
-    _need_cuda(logits, out_ids)
+def argmax_rows(logits: torch.Tensor, out_ids: torch.Tensor,
+                scatter_index: Optional[torch.Tensor] = None,
+                scatter_out: Optional[torch.Tensor] = None) -> None:
+    """`scatter_index`, `scatter_out` (int32): also write row r's id to
+    scatter_out[scatter_index[r]]."""
+    _need_cuda(logits, out_ids, scatter_index, scatter_out)
     if logits.dtype != torch.float32 or out_ids.dtype != torch.int32:
         raise KernelError("argmax_rows takes float32 logits and int32 output")
     _contig(logits, "logits")
@@ -254,7 +260,8 @@ def argmax_rows(logits: torch.Tensor, out_ids: torch.Tensor) -> None:
         scratch = torch.empty(max(n, 64) * 64, dtype=torch.int32, device=logits.device)
         _scratch[key] = scratch
     _check(lib.cb_argmax_rows(_ptr(logits), _c_int(n), _c_int(logits.shape[1]),
-                              _ptr(out_ids), _ptr(scratch), _stream()), "argmax_rows")
+                              _ptr(out_ids), _ptr(scratch), _ptr(scatter_index), _ptr(scatter_out),
+                              _stream()), "argmax_rows")
 
 
 def max_device_top_k() -> int:
@@ -262,8 +269,10 @@ def max_device_top_k() -> int:
 
 
 def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
-                uniform: torch.Tensor, max_top_k: int, out_ids: torch.Tensor) -> None:
-    _need_cuda(logits, temperature, top_k, uniform, out_ids)
+                uniform: torch.Tensor, max_top_k: int, out_ids: torch.Tensor,
+                scatter_index: Optional[torch.Tensor] = None,
+                scatter_out: Optional[torch.Tensor] = None) -> None:
+    _need_cuda(logits, temperature, top_k, uniform, out_ids, scatter_index, scatter_out)
     if (logits.dtype != torch.float32 or temperature.dtype != torch.float32
             or uniform.dtype != torch.float32 or top_k.dtype != torch.int32
             or out_ids.dtype != torch.int32):
@@ -272,7 +281,7 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Te
     lib = build.load("sampling")
     code = lib.cb_sample_rows(_ptr(logits), _c_int(logits.shape[0]), _c_int(logits.shape[1]),
                               _ptr(temperature), _ptr(top_k), _ptr(uniform), _c_int(max_top_k),
-                              _ptr(out_ids), _stream())
+                              _ptr(out_ids), _ptr(scatter_index), _ptr(scatter_out), _stream())
     if code == 100001:
         raise KernelError(f"top_k {max_top_k} exceeds what the sampling kernel holds "
                           f"({max_device_top_k()} candidates)")

@@ -2,7 +2,8 @@
 
 Embedding: x[t, :] = table[token[t], :], no scaling (`model.py:347`,
 `engine/kernels/kernels.cu:1049-1059`); the gathered row is widened into the
-fp32 residual stream.  Head: logits = norm(x[rows]) W^T at the wanted rows only,
+fp32 residual stream; an id -(s + 1) stands for the token the engine last chose for
+state slot s and is read on the device (`ctx.device_tokens`).  Head: logits = norm(x[rows]) W^T at the wanted rows only,
 never [T, V] (`engine/src/gpu_model.rs:3590-3613`); W is the embedding table
 when the model ties them (`model.py:289`), else its own matrix.  Logits are fp32.
 """
@@ -28,7 +29,7 @@ class TokenEmbedding(Part):
 
     def forward(self, ctx, token_ids: torch.Tensor) -> torch.Tensor:
         x = ctx.scratch("residual", (token_ids.shape[0], self.width), torch.float32)
-        ops.embed_rows(self.table, token_ids, x)
+        ops.embed_rows(self.table, token_ids, x, getattr(ctx, "device_tokens", None))
         return x
 
 

@@ -1,9 +1,11 @@
 """Token selection for the rows of a step, on the device.
 
-All rows greedy: one argmax kernel.  Otherwise one kernel that handles greedy
+All rows greedy: the argmax kernels.  Otherwise one kernel that handles greedy
 and sampled rows side by side; the host draws one uniform number per sampled
 row from that request's own generator and uploads it with the row's
-temperature and top-k.  Only the chosen ids come back to the host.
+temperature and top-k.  Only the chosen ids come back to the host, either at
+once or, deferred, through a ring of pinned buffers while the next step already
+runs (the ids then also stay on the device, per state slot, for that next step).
 """
 from __future__ import annotations
 
@@ -17,40 +19,70 @@ from .params import SamplingParams
 from .rng import Xorshift64Star
 
 
+class PendingIds:
+    """Ids on their way to the host."""
+
+    def __init__(self, host: torch.Tensor, n: int, event: torch.cuda.Event):
+        self._host, self._n, self._event = host, n, event
+        self._ids: Optional[List[int]] = None
+
+    def get(self) -> List[int]:
+        if self._ids is None:
+            self._event.synchronize()
+            self._ids = self._host[:self._n].tolist()
+        return self._ids
+
+
 class Sampler:
+    RING = 4
+
     def __init__(self, device, vocab: int):
         self.device = device
         self.vocab = vocab
         self._cap = 0
-        self._host = None
-        self._dev = None
-        self._ids = None
-        self._ids_host = None
+        self._at = 0
 
     def _buffers(self, n: int):
         if n > self._cap:
             cap = max(n, 64)
-            self._host = torch.empty((3, cap), dtype=torch.float32, pin_memory=True)
-            self._dev = torch.empty((3, cap), dtype=torch.float32, device=self.device)
-            self._ids = torch.empty(cap, dtype=torch.int32, device=self.device)
-            self._ids_host = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+            torch.cuda.current_stream().synchronize()
+            # per ring entry: pinned parameters [4, cap] (temperature, top-k bits, uniform,
+            # slot bits), their device copy, device ids, pinned ids, and an event
+            self._ring = [dict(host=torch.empty((4, cap), dtype=torch.float32, pin_memory=True),
+                               dev=torch.empty((4, cap), dtype=torch.float32, device=self.device),
+                               ids=torch.empty(cap, dtype=torch.int32, device=self.device),
+                               ids_host=torch.empty(cap, dtype=torch.int32, pin_memory=True),
+                               event=torch.cuda.Event(), used=False) for _ in range(self.RING)]
             self._cap = cap
+        self._at = (self._at + 1) % self.RING
+        slot = self._ring[self._at]
+        if slot["used"]:
+            slot["event"].synchronize()         # the copy that last read these buffers is done
+        return slot
 
     def sample(self, logits: torch.Tensor,
-               rows: Sequence[Tuple[SamplingParams, Optional[Xorshift64Star]]]) -> List[int]:
-        """`logits`: fp32 [n, vocab] on the device; `rows[i]` = (params, generator)."""
+               rows: Sequence[Tuple[SamplingParams, Optional[Xorshift64Star]]],
+               slots: Optional[Sequence[int]] = None,
+               scatter_out: Optional[torch.Tensor] = None, defer: bool = False):
+        """`logits`: fp32 [n, vocab] on the device; `rows[i]` = (params, generator).
+        `slots`, `scatter_out`: also leave row i's id in scatter_out[slots[i]].
+        Returns the ids, or with `defer` a `PendingIds`."""
         n = len(rows)
         if n == 0:
-            return []
+            return PendingIds(torch.empty(0, dtype=torch.int32), 0, torch.cuda.Event()) if defer else []
         if logits.shape[0] != n:
             raise ValueError(f"{n} rows to sample but logits has {logits.shape[0]}")
-        self._buffers(n)
-        ids = self._ids[:n]
-        if all(p.is_greedy for p, _ in rows):
-            ops.argmax_rows(logits, ids)
-        else:
-            host = self._host.numpy()
-            max_k = 1
+        buf = self._buffers(n)
+        ids = buf["ids"][:n]
+        host = buf["host"].numpy()
+        greedy = all(p.is_greedy for p, _ in rows)
+        upload = not greedy or slots is not None
+        scatter_index = None
+        if slots is not None:
+            host[3, :n] = np.asarray(slots, dtype=np.int32).view(np.float32)
+            scatter_index = buf["dev"][3, :n].view(torch.int32)
+        max_k = 1
+        if not greedy:
             topk_bits = np.zeros(n, dtype=np.int32)
             for i, (p, rng) in enumerate(rows):
                 if p.is_greedy:
@@ -60,9 +92,16 @@ class Sampler:
                     max_k = max(max_k, k)
                     host[0, i], topk_bits[i], host[2, i] = p.temperature, k, rng.next_f32()
             host[1, :n] = topk_bits.view(np.float32)
-            self._dev[:, :n].copy_(self._host[:, :n], non_blocking=True)
-            ops.sample_rows(logits, self._dev[0, :n], self._dev[1, :n].view(torch.int32),
-                            self._dev[2, :n], max_k, ids)
-        self._ids_host[:n].copy_(ids, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self._ids_host[:n].tolist()
+        if upload:
+            buf["dev"][:, :n].copy_(buf["host"][:, :n], non_blocking=True)
+        out = scatter_out if slots is not None else None
+        if greedy:
+            ops.argmax_rows(logits, ids, scatter_index, out)
+        else:
+            ops.sample_rows(logits, buf["dev"][0, :n], buf["dev"][1, :n].view(torch.int32),
+                            buf["dev"][2, :n], max_k, ids, scatter_index, out)
+        buf["ids_host"][:n].copy_(ids, non_blocking=True)
+        buf["event"].record()
+        buf["used"] = True
+        pending = PendingIds(buf["ids_host"], n, buf["event"])
+        return pending if defer else pending.get()

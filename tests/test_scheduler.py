@@ -168,3 +168,57 @@ def test_cancel_gives_everything_back_in_every_state():
     assert {c.id: c.finish_reason for c in s.done} == {"a": "cancelled", "b": "cancelled",
                                                         "c": "cancelled"}
     assert not s.has_work()
+
+
+class LaggedExecutor(FakeExecutor):
+    """An executor that keeps the latest token of each request 'on the device' and
+    hands the values over one call later, like the engine's `sample_deferred`."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.device_tokens = {}
+        self.reads = 0
+
+    def step(self, entries):
+        from crucible_b200.engine import DEVICE_TOKEN
+        fixed = []
+        for e in entries:
+            tokens = list(e.tokens)
+            if tokens == [DEVICE_TOKEN]:
+                tokens = [self.device_tokens[e.request]]
+            fixed.append(type(e)(e.request, tokens, e.want))
+        return super().step(fixed)
+
+    def sample_deferred(self, logits, rows, requests):
+        ids = FakeExecutor.sample(self, logits, rows)
+        for r, tok in zip(requests, ids):
+            self.device_tokens[r] = tok
+        outer = self
+
+        class Pending:
+            def get(self_inner):
+                outer.reads += 1
+                return ids
+        return Pending()
+
+
+def test_token_values_may_lag_one_step_without_changing_the_result():
+    prompts = {"a": list(range(50)), "b": list(range(20)), "c": [7, 8, 9]}
+
+    def run(executor):
+        s = Scheduler(executor, SchedulerOptions(max_batch=4, prefill_token_budget=32))
+        for name, prompt in prompts.items():
+            s.submit(Request(name, prompt, greedy(5 if name != "c" else 1)))
+        return {c.id: c.tokens for c in s.run_to_completion()}, executor.steps
+
+    want, steps_sync = run(FakeExecutor(n_pages=64))
+    lagged = LaggedExecutor(n_pages=64)
+    got, steps_lagged = run(lagged)
+    assert got == want and all(len(v) == (1 if k == "c" else 5) for k, v in got.items())
+    shape = lambda steps: [[(r, n) for r, n, _ in step] for step in steps]
+    assert shape(steps_lagged) == shape(steps_sync)
+    assert lagged.cache.free_pages(0) == 64 and lagged.reads > 0
+    # a request that stops on a token value is run with its values at hand
+    s = Scheduler(LaggedExecutor(n_pages=64))
+    s.submit(Request("e", [5, 6, 7], SamplingParams(max_tokens=50, eos_token_id=(2 * 7 + 7) % 1000)))
+    assert [c.finish_reason for c in s.run_to_completion()] == ["eos"]
