@@ -1,0 +1,398 @@
+// Paged causal attention for portions of prompts on the 5th-generation tensor
+// cores (head size 64, bfloat16): S = Q K^T and O += P V are tcgen05.mma with
+// the scores and the output accumulator in tensor memory; K and V pages come in
+// by TMA; the softmax runs on four warps, one thread per query row, reading S
+// from tensor memory and writing P (bf16) to shared memory for the second MMA.
+//
+// A block takes 128 query rows of one request and one KV head; rows are
+// (position, head within the group) pairs, so every query head that shares the
+// KV head uses the same K and V tiles.  It walks the keys in tiles of 128.
+// Roles: warp 0 loads (one thread: block-table lookups, one TMA box per page),
+// warp 1 owns tensor memory and issues the MMAs, warps 2-5 are the softmax.
+//
+// Running maximum: a row keeps a reference maximum that is only raised when the
+// tile's maximum exceeds it by more than 2^8 (in the base-2 exponent), so P
+// stays <= 256 and the accumulator in tensor memory is rescaled rarely; the row
+// sum uses the same reference, and the final division makes the result the
+// exact softmax-weighted mean whatever the reference was.
+//
+// Sizes: head size 64 exactly; page size a power of two from 8 to 128; any head
+// counts and group sizes; window.  Anything else is refused and the mma.sync
+// kernel runs.  Every wait is bounded (tc_common.cuh).
+// Reference counterpart: `attention_prefill_exact_*`
+// (engine/kernels/kernels.cu:2257-2275).
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace {
+
+constexpr int HD = 64;
+constexpr int ROWS = 128;            // query rows per block = tensor-memory lanes
+constexpr int KEYS = 128;            // keys per tile
+constexpr int STAGES = 2;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float RAISE = 8.0f;        // raise the reference maximum when exceeded by 2^8
+
+struct TcAttnParams {
+    const __nv_bfloat16* qkv;
+    int qkv_stride;
+    __nv_bfloat16* out;
+    int out_stride;
+    const int* req_row_start;
+    const int* req_first_pos;
+    const int* block_table;
+    int table_stride;
+    int n_heads, n_kv_heads, page_tokens, page_shift;
+    float scale_log2;
+    int window;
+    int* status;
+};
+
+struct Storage {
+    alignas(1024) uint8_t q[ROWS * HD * 2];
+    alignas(1024) uint8_t k[STAGES][KEYS * HD * 2];
+    alignas(1024) uint8_t v[STAGES][KEYS * HD * 2];
+    alignas(1024) uint8_t p[2][ROWS * 64 * 2];      // P: two halves of 64 keys
+    alignas(8) uint64_t kv_full[STAGES];
+    uint64_t kv_empty[STAGES];
+    uint64_t s_full, p_full, pv_done;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(192)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, const TcAttnParams p) {
+    cb_pdl_trigger();
+    // 1024-byte alignment (the swizzled tiles need it) is asked of the declaration, not
+    // bought with slack: two blocks of 112 KB then fit one SM
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    Storage& s = *reinterpret_cast<Storage*>(smem_raw);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int req = blockIdx.z, kv_head = blockIdx.y;
+    volatile int* abort_flag = &s.abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) {
+            tc::mbar_init(&s.kv_full[i], 1);
+            tc::mbar_init(&s.kv_empty[i], 1);
+        }
+        tc::mbar_init(&s.s_full, 1);
+        tc::mbar_init(&s.p_full, 128);
+        tc::mbar_init(&s.pv_done, 1);
+        s.abort_flag = 0;
+        tc::fence_barrier_init();
+        tc::prefetch_tensormap(&map_k);
+        tc::prefetch_tensormap(&map_v);
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(&s.tmem_base, 256);            // S: columns 0..127, O: 128..191
+        tc::tmem_relinquish();
+    }
+    cb_pdl_wait();
+
+    const int n_rep = p.n_heads / p.n_kv_heads;
+    const int row_base = p.req_row_start[req];
+    const int n_new = p.req_row_start[req + 1] - row_base;
+    const int n_rows = n_new * n_rep;
+    const int q_tiles = (n_rows + ROWS - 1) / ROWS;
+    const bool active = (int)blockIdx.x < q_tiles;
+    const int qt = active ? q_tiles - 1 - (int)blockIdx.x : 0;     // heaviest tiles first
+    const int first_pos = p.req_first_pos[req];
+    const int* table = p.block_table + (size_t)req * p.table_stride;
+
+    // the block's keys: from the first key any of its rows may read to its last position
+    const int last_row = min(n_rows - 1, qt * ROWS + ROWS - 1);
+    const int max_pos = first_pos + last_row / n_rep;
+    const int min_pos = first_pos + (qt * ROWS) / n_rep;
+    int key_lo = p.window > 0 ? max(0, min_pos - p.window + 1) : 0;
+    key_lo = key_lo / KEYS * KEYS;
+    const int key_end = max_pos + 1;
+    const int n_tiles = active ? (key_end - key_lo + KEYS - 1) / KEYS : 0;
+
+    // ---- the query rows, by all threads: 16-byte pieces into the 128-byte swizzle -------
+    if (active) {
+        for (int i = threadIdx.x; i < ROWS * 8; i += blockDim.x) {
+            const int r = i >> 3, c = i & 7;
+            const int row = qt * ROWS + r;
+            uint4 val = make_uint4(0, 0, 0, 0);
+            if (row < n_rows) {
+                const int tok = row_base + row / n_rep, head = kv_head * n_rep + row % n_rep;
+                val = *reinterpret_cast<const uint4*>(p.qkv + (size_t)tok * p.qkv_stride +
+                                                      (size_t)head * HD + c * 8);
+            }
+            *reinterpret_cast<uint4*>(s.q + r * 128 + ((c ^ (r & 7)) << 4)) = val;
+        }
+    }
+    tc::fence_proxy_async();                // generic-proxy writes of Q, before the MMAs read them
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem_s = s.tmem_base;
+    const uint32_t tmem_o = s.tmem_base + 128;
+
+    if (warp == 0) {
+        // ---- loader ---------------------------------------------------------------------
+        if (lane == 0 && n_tiles > 0) {
+            const int pages_per_tile = KEYS >> p.page_shift;
+            int armed = 0;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int st = j % STAGES;
+                const uint32_t round = j / STAGES;
+                if (round > 0 && !tc::mbar_wait(&s.kv_empty[st], (round - 1) & 1, abort_flag)) {
+                    tc::give_up(abort_flag, p.status, tc::ST_PRODUCER_TIMEOUT);
+                    break;
+                }
+                tc::mbar_expect_tx(&s.kv_full[st], 2 * KEYS * HD * 2);
+                const int key0 = key_lo + j * KEYS;
+                for (int i = 0; i < pages_per_tile; ++i) {
+                    int index = (key0 >> p.page_shift) + i;
+                    index = index < p.table_stride ? index : p.table_stride - 1;
+                    int page = table[index];
+                    page = page < 0 ? 0 : page;               // an entry given back early: never read
+                    const int y = (page * p.n_kv_heads + kv_head) << p.page_shift;
+                    const int dst = (i << p.page_shift) * HD * 2;
+                    tc::tma_load_2d(s.k[st] + dst, &map_k, &s.kv_full[st], 0, y);
+                    tc::tma_load_2d(s.v[st] + dst, &map_v, &s.kv_full[st], 0, y);
+                }
+                armed = j + 1;
+            }
+            if (*abort_flag) {
+                const int first = armed > STAGES ? armed - STAGES : 0;
+                for (int j = first; j < armed; ++j)
+                    for (uint32_t t = 0; t < tc::WAIT_LIMIT; ++t)
+                        if (tc::mbar_try_wait(&s.kv_full[j % STAGES], (j / STAGES) & 1)) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer -------------------------------------------------------------------
+        if (lane == 0 && n_tiles > 0) {
+            constexpr uint32_t idesc_qk = tc::instr_desc_bf16(ROWS, KEYS);
+            constexpr uint32_t idesc_pv = tc::instr_desc_bf16_b_mn(ROWS, HD);
+            const uint64_t q_desc = tc::smem_desc_sw128(tc::smem_u32(s.q));
+            for (int j = 0; j < n_tiles; ++j) {
+                const int st = j % STAGES;
+                if (!tc::mbar_wait(&s.kv_full[st], (j / STAGES) & 1, abort_flag)) {
+                    tc::give_up(abort_flag, p.status, tc::ST_MMA_TIMEOUT);
+                    break;
+                }
+                tc::tc_fence_after_sync();
+                // S = Q K^T: K = 64 in four steps of 16
+                const uint64_t k_desc = tc::smem_desc_sw128(tc::smem_u32(s.k[st]));
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k)
+                    tc::umma_bf16(tmem_s, q_desc + 2 * k, k_desc + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
+                tc::umma_commit(&s.s_full);
+                // O += P V once the softmax has written P: K = 128 keys in eight steps of 16
+                if (!tc::mbar_wait(&s.p_full, j & 1, abort_flag)) {
+                    tc::give_up(abort_flag, p.status, tc::ST_MMA_TIMEOUT);
+                    break;
+                }
+                tc::tc_fence_after_sync();
+                const uint64_t v_desc = tc::smem_desc_sw128(tc::smem_u32(s.v[st]));
+#pragma unroll
+                for (int k = 0; k < KEYS / 16; ++k) {
+                    const uint64_t p_desc =
+                        tc::smem_desc_sw128(tc::smem_u32(s.p[k >> 2])) + 2 * (k & 3);
+                    // 16 keys further down V: 16 rows of 128 bytes = 128 descriptor units
+                    tc::umma_bf16(tmem_o, p_desc, v_desc + 128 * k, idesc_pv,
+                                  (j > 0 || k > 0) ? 1u : 0u);
+                }
+                tc::umma_commit(&s.kv_empty[st]);
+                tc::umma_commit(&s.pv_done);
+            }
+        }
+    } else {
+        // ---- softmax: warps 2..5, one thread per row = tensor-memory lane -------------------
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const int row = qt * ROWS + r;
+        const bool real = active && row < n_rows;
+        const int pos = real ? first_pos + row / n_rep : -1;
+        const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int key0 = key_lo + j * KEYS;
+            ok = tc::mbar_wait(&s.s_full, j & 1, abort_flag);
+            if (!ok && !*abort_flag) tc::give_up(abort_flag, p.status, tc::ST_EPILOGUE_TIMEOUT);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc::tc_fence_after_sync();
+            // pass 1: the row's maximum over the tile's keys it may read
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c0 = 0; c0 < KEYS; c0 += 32) {
+                uint32_t v[32];
+                tc::tmem_ld_32x32(tmem_s + lane_bits + c0, v);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int key = key0 + c0 + i;
+                    if (key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(v[i]));
+                }
+            }
+            mx *= p.scale_log2;
+            // raise the reference maximum only when it is exceeded by far; the accumulator
+            // in tensor memory is rescaled then, by the whole warp at once
+            float corr = 1.0f;
+            if (mx > m_ref + RAISE || (m_ref == -INFINITY && mx > -INFINITY)) {
+                corr = m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx);
+                m_ref = mx;
+            }
+            // P's buffer and O are free only when the previous tile's second MMA is done
+            if (j > 0) {
+                ok = tc::mbar_wait(&s.pv_done, (j - 1) & 1, abort_flag);
+                if (!ok && !*abort_flag) tc::give_up(abort_flag, p.status, tc::ST_EPILOGUE_TIMEOUT);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc::tc_fence_after_sync();
+                if (__any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < HD; c0 += 32) {
+                        uint32_t v[32];
+                        tc::tmem_ld_32x32(tmem_o + lane_bits + c0, v);
+                        tc::tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                        tc::tmem_st_32x32(tmem_o + lane_bits + c0, v);
+                    }
+                    tc::tmem_st_wait();
+                }
+            }
+            l *= corr;
+            // pass 2: P = exp2(s * scale - reference), to shared memory in the layout the
+            // second MMA reads (rows of 128 bytes per half of 64 keys, 128-byte swizzle)
+            const float off = m_ref == -INFINITY ? 0.f : m_ref;
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < KEYS; c0 += 32) {
+                uint32_t v[32];
+                tc::tmem_ld_32x32(tmem_s + lane_bits + c0, v);
+                tc::tmem_ld_wait();
+                float e[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int key = key0 + c0 + i;
+                    const bool in = key <= pos && key >= lo;
+                    e[i] = in ? exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2, -off)) : 0.f;
+                    sum += e[i];
+                }
+                uint8_t* half = s.p[c0 >> 6] + r * 128;
+#pragma unroll
+                for (int piece = 0; piece < 4; ++piece) {
+                    const int c = ((c0 & 63) >> 3) + piece;          // 16-byte piece inside the row
+                    uint4 w;
+                    w.x = pack_bf16(e[8 * piece + 0], e[8 * piece + 1]);
+                    w.y = pack_bf16(e[8 * piece + 2], e[8 * piece + 3]);
+                    w.z = pack_bf16(e[8 * piece + 4], e[8 * piece + 5]);
+                    w.w = pack_bf16(e[8 * piece + 6], e[8 * piece + 7]);
+                    *reinterpret_cast<uint4*>(half + ((c ^ (r & 7)) << 4)) = w;
+                }
+            }
+            l += sum;
+            tc::tc_fence_before_sync();          // our reads of S are done before S is overwritten
+            tc::fence_proxy_async();             // P is written by the generic proxy, read by the MMA
+            tc::mbar_arrive(&s.p_full);
+        }
+        // ---- the output: O / l ------------------------------------------------------------
+        if (ok && n_tiles > 0) {
+            ok = tc::mbar_wait(&s.pv_done, (n_tiles - 1) & 1, abort_flag);
+            if (!ok && !*abort_flag) tc::give_up(abort_flag, p.status, tc::ST_EPILOGUE_TIMEOUT);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok && n_tiles > 0) {
+            tc::tc_fence_after_sync();
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            __nv_bfloat16* dst = nullptr;
+            if (real) {
+                const int tok = row_base + row / n_rep, head = kv_head * n_rep + row % n_rep;
+                dst = p.out + (size_t)tok * p.out_stride + (size_t)head * HD;
+            }
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t v[32];
+                tc::tmem_ld_32x32(tmem_o + lane_bits + c0, v);
+                tc::tmem_ld_wait();
+                if (real) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 w;
+                        w.x = pack_bf16(__uint_as_float(v[8 * q4 + 0]) * inv, __uint_as_float(v[8 * q4 + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(v[8 * q4 + 2]) * inv, __uint_as_float(v[8 * q4 + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(v[8 * q4 + 4]) * inv, __uint_as_float(v[8 * q4 + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(v[8 * q4 + 6]) * inv, __uint_as_float(v[8 * q4 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + 8 * q4) = w;
+                    }
+                }
+            }
+        }
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::tc_fence_after_sync();
+        tc::tmem_dealloc(s.tmem_base, 256);
+    }
+}
+
+}  // namespace
+
+// Attention for the rows of a step whose requests bring portions of prompts.
+// k_cache / v_cache: [n_pages][n_kv_heads][page_tokens][64] bf16.
+CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, int out_stride,
+                                   const void* k_cache, const void* v_cache, int n_pages,
+                                   const int* req_row_start, const int* req_first_pos,
+                                   const int* block_table, int table_stride, int n_requests,
+                                   int max_new_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                   int page_tokens, float scale, int window, int* status,
+                                   void* stream) {
+    if (n_requests <= 0 || max_new_tokens <= 0) return 0;
+    if (head_dim != HD || n_heads % n_kv_heads != 0 || page_tokens < 8 || page_tokens > KEYS ||
+        (page_tokens & (page_tokens - 1)) || (qkv_stride & 7) || (out_stride & 7) ||
+        ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) || ((uintptr_t)k_cache & 15) ||
+        ((uintptr_t)v_cache & 15))
+        return CB_ERR_UNSUPPORTED;
+    int shift = 0;
+    while ((1 << shift) < page_tokens) ++shift;
+    CUtensorMap mk, mv;
+    const uint64_t rows = (uint64_t)n_pages * n_kv_heads * page_tokens;
+    if (!tc::make_map_2d(&mk, k_cache, rows, HD, HD, page_tokens)) return CB_ERR_UNSUPPORTED;
+    if (!tc::make_map_2d(&mv, v_cache, rows, HD, HD, page_tokens)) return CB_ERR_UNSUPPORTED;
+    TcAttnParams p;
+    p.qkv = (const __nv_bfloat16*)qkv;
+    p.qkv_stride = qkv_stride;
+    p.out = (__nv_bfloat16*)out;
+    p.out_stride = out_stride;
+    p.req_row_start = req_row_start;
+    p.req_first_pos = req_first_pos;
+    p.block_table = block_table;
+    p.table_stride = table_stride;
+    p.n_heads = n_heads;
+    p.n_kv_heads = n_kv_heads;
+    p.page_tokens = page_tokens;
+    p.page_shift = shift;
+    p.scale_log2 = scale * LOG2E;
+    p.window = window;
+    p.status = status;
+    const int smem = (int)sizeof(Storage);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int n_rep = n_heads / n_kv_heads;
+    const int q_tiles = (max_new_tokens * n_rep + ROWS - 1) / ROWS;
+    cb_launch(attention_tcgen05_kernel, dim3(q_tiles, n_kv_heads, n_requests), dim3(192), smem,
+              (cudaStream_t)stream, mk, mv, p);
+    return cb_last_error();
+}

@@ -18,6 +18,11 @@ from . import build
 build.register_module("gemm_tcgen05", ["common.cuh", "tc_common.cuh"])
 build.register_module("attention_mma", ["common.cuh"])
 build.register_module("gemm_skinny_tcgen05", ["common.cuh", "tc_common.cuh"])
+build.register_module("attention_tcgen05", ["common.cuh", "tc_common.cuh"])
+
+# Portions of prompts with head size 64 run on the tcgen05 attention kernel; False sends
+# them to the mma.sync kernel instead (the tests compare the two).
+USE_TCGEN05_ATTENTION = True
 
 _c_int, _c_void_p = ctypes.c_int, ctypes.c_void_p
 STORE_BF16, STORE_F32, ACCUM_F32, SWIGLU_BF16 = 0, 1, 2, 3
@@ -185,6 +190,31 @@ def linear_swiglu(h, gate_up, out, tile=None) -> bool:
     return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn)
 
 
+def _attention_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads, head_dim, scale,
+                       window, ctx, cache) -> bool:
+    """tcgen05 attention for portions of prompts: head size 64, page size a power of
+    two from 8 to 128.  Returns False for anything else."""
+    pt = cache.page_tokens
+    if pt < 8 or pt > 128 or pt & (pt - 1):
+        return False
+    lib = build.load("attention_tcgen05")
+    code = lib.cb_attention_tcgen05(
+        _c_void_p(qkv.data_ptr()), _c_int(qkv.stride(0)), _c_void_p(out.data_ptr()),
+        _c_int(out.stride(0)), _c_void_p(k_cache.data_ptr()), _c_void_p(v_cache.data_ptr()),
+        _c_int(k_cache.shape[0]), _c_void_p(ctx.req_row_start.data_ptr()),
+        _c_void_p(ctx.req_first_pos.data_ptr()), _c_void_p(table.data_ptr()),
+        _c_int(table.shape[1]), _c_int(ctx.n_requests), _c_int(ctx.host.max_new_tokens),
+        _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim), _c_int(pt),
+        ctypes.c_float(scale), _c_int(window or 0),
+        _c_void_p(status_word(qkv.device).data_ptr()), _stream())
+    if code == _UNSUPPORTED:
+        return False
+    if code != 0:
+        raise RuntimeError(f"tcgen05 attention failed to launch (CUDA error {code})")
+    _count(1)
+    return True
+
+
 def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx, cache,
                     binding) -> bool:
     """mma.sync attention over the paged cache.  Takes head sizes that are
@@ -217,6 +247,11 @@ def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx,
         partial = ctx.scratch("attn.partial", (floats,), torch.float32)
         n_counters = ctx.n_requests * n_kv_heads * (-(-host.max_new_tokens * n_rep // 16))
         counters = _buffer(qkv.device, "attn.counters", n_counters, torch.int32, zero=True)
+    if (USE_TCGEN05_ATTENTION and not split and head_dim == 64
+            and host.max_new_tokens * n_rep >= 64 and out.stride(0) % 8 == 0
+            and _attention_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads,
+                                   head_dim, scale, window, ctx, cache)):
+        return True
     lib = build.load("attention_mma")
     code = lib.cb_attention_mma(
         _c_void_p(qkv.data_ptr()), _c_int(qkv.stride(0)), _c_void_p(out.data_ptr()),

@@ -388,6 +388,37 @@ def test_attention_tensor_core_tiles_and_split(case):
     assert rel(out1.cpu(), ref1) < 1.5e-2
 
 
+@pytest.mark.parametrize("case", [
+    (12, 4, 64, 16, [(0, 130), (300, 1), (17, 40)], None),
+    (4, 4, 64, 32, [(0, 700)], None),
+    (6, 1, 64, 8, [(513, 300), (0, 129)], None),
+    (8, 2, 64, 128, [(100, 260)], 200),
+])
+def test_attention_tcgen05_matches_reference_and_mma(case):
+    """Prompt portions with head size 64: S and O in tensor memory, K and V by TMA."""
+    from crucible_b200.ops import tensor_core
+    n_heads, n_kv, hd, page, requests, window = case
+    qkv, ctx, cache, binding, ref = _paged_case(torch.bfloat16, n_heads, n_kv, hd, page, requests,
+                                                6, window)
+    k_cache = cache.keys(0)
+    cache.n_pages = k_cache.shape[0]
+    out = torch.zeros(qkv.shape[0], n_heads * hd, device=DEV, dtype=torch.bfloat16)
+    assert tensor_core.USE_TCGEN05_ATTENTION
+    assert tensor_core._attention_tcgen05(qkv, out, k_cache, cache.values(0), ctx.block_table(0),
+                                          n_heads, n_kv, hd, 1 / math.sqrt(hd), window, ctx, cache)
+    torch.cuda.synchronize()
+    tensor_core.check_status(DEV)
+    assert rel(out, ref) < 1.5e-2
+    try:
+        tensor_core.USE_TCGEN05_ATTENTION = False
+        other = torch.zeros_like(out)
+        assert tensor_core.paged_attention(qkv, other, n_heads, n_kv, hd, 1 / math.sqrt(hd), window,
+                                           ctx, cache, binding)
+    finally:
+        tensor_core.USE_TCGEN05_ATTENTION = True
+    assert rel(out, other.float()) < 1.5e-2
+
+
 def test_attention_odd_head_size_falls_to_plain_kernel():
     from crucible_b200.ops import tensor_core
     ops = _ops()
