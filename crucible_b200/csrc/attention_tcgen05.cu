@@ -9,6 +9,9 @@
 // KV head uses the same K and V tiles.  It walks the keys in tiles of 128.
 // Roles: warp 0 loads (one thread: block-table lookups, one TMA box per page),
 // warp 1 owns tensor memory and issues the MMAs, warps 2-5 are the softmax.
+// S and P are double-buffered: while the softmax works on tile j, the first MMA
+// of tile j+1 and the second MMA of tile j-1 run, so a block's time per tile is
+// the softmax's alone.
 //
 // Running maximum: a row keeps a reference maximum that is only raised when the
 // tile's maximum exceeds it by more than 2^8 (in the base-2 exponent), so P
@@ -29,7 +32,7 @@ namespace {
 constexpr int HD = 64;
 constexpr int ROWS = 128;            // query rows per block = tensor-memory lanes
 constexpr int KEYS = 128;            // keys per tile
-constexpr int STAGES = 2;
+constexpr int STAGES = 3;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RAISE = 8.0f;        // raise the reference maximum when exceeded by 2^8
 
@@ -52,10 +55,10 @@ struct Storage {
     alignas(1024) uint8_t q[ROWS * HD * 2];
     alignas(1024) uint8_t k[STAGES][KEYS * HD * 2];
     alignas(1024) uint8_t v[STAGES][KEYS * HD * 2];
-    alignas(1024) uint8_t p[2][ROWS * 64 * 2];      // P: two halves of 64 keys
+    alignas(1024) uint8_t p[2][2][ROWS * 64 * 2];   // P: two buffers of two halves of 64 keys
     alignas(8) uint64_t kv_full[STAGES];
     uint64_t kv_empty[STAGES];
-    uint64_t s_full, p_full, pv_done;
+    uint64_t s_full[2], p_full[2], pv_done[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -63,6 +66,34 @@ struct Storage {
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// 2^x by the special-function unit, flushing denormals: the argument is a score
+// minus a maximum, so a result below 2^-126 counts as nothing in the row's sum.
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// (x0, x1) * a + b in one instruction on the pair
+__device__ __forceinline__ void fma_pair(float& x0, float& x1, float a, float b) {
+    asm("{\n\t"
+        ".reg .b64 x, s, o;\n\t"
+        "mov.b64 x, {%0, %1};\n\t"
+        "mov.b64 s, {%2, %2};\n\t"
+        "mov.b64 o, {%3, %3};\n\t"
+        "fma.rn.f32x2 x, x, s, o;\n\t"
+        "mov.b64 {%0, %1}, x;\n\t"
+        "}"
+        : "+f"(x0), "+f"(x1)
+        : "f"(a), "f"(b));
 }
 
 __global__ void __launch_bounds__(192)
@@ -82,16 +113,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             tc::mbar_init(&s.kv_full[i], 1);
             tc::mbar_init(&s.kv_empty[i], 1);
         }
-        tc::mbar_init(&s.s_full, 1);
-        tc::mbar_init(&s.p_full, 128);
-        tc::mbar_init(&s.pv_done, 1);
+        for (int b = 0; b < 2; ++b) {
+            tc::mbar_init(&s.s_full[b], 1);
+            tc::mbar_init(&s.p_full[b], 128);
+            tc::mbar_init(&s.pv_done[b], 1);
+        }
         s.abort_flag = 0;
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&map_k);
         tc::prefetch_tensormap(&map_v);
     }
     if (warp == 1) {
-        tc::tmem_alloc(&s.tmem_base, 256);            // S: columns 0..127, O: 128..191
+        tc::tmem_alloc(&s.tmem_base, 512);            // S: columns 0..127 and 128..255, O: 256..319
         tc::tmem_relinquish();
     }
     cb_pdl_wait();
@@ -133,8 +166,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     tc::tc_fence_before_sync();
     __syncthreads();
     tc::tc_fence_after_sync();
-    const uint32_t tmem_s = s.tmem_base;
-    const uint32_t tmem_o = s.tmem_base + 128;
+    const uint32_t tmem_s = s.tmem_base;          // + 128 for the second buffer
+    const uint32_t tmem_o = s.tmem_base + 256;
 
     if (warp == 0) {
         // ---- loader ---------------------------------------------------------------------
@@ -144,21 +177,30 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             for (int j = 0; j < n_tiles; ++j) {
                 const int st = j % STAGES;
                 const uint32_t round = j / STAGES;
+                // the tile's table entries first, all in flight at once: the copies below
+                // are ordered against memory and would take the lookups one by one
+                const int key0 = key_lo + j * KEYS;
+                int rows_y[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    int index = (key0 >> p.page_shift) + (i < pages_per_tile ? i : 0);
+                    index = index < p.table_stride ? index : p.table_stride - 1;
+                    int page = table[index];
+                    page = page < 0 ? 0 : page;               // an entry given back early: never read
+                    rows_y[i] = (page * p.n_kv_heads + kv_head) << p.page_shift;
+                }
                 if (round > 0 && !tc::mbar_wait(&s.kv_empty[st], (round - 1) & 1, abort_flag)) {
                     tc::give_up(abort_flag, p.status, tc::ST_PRODUCER_TIMEOUT);
                     break;
                 }
                 tc::mbar_expect_tx(&s.kv_full[st], 2 * KEYS * HD * 2);
-                const int key0 = key_lo + j * KEYS;
-                for (int i = 0; i < pages_per_tile; ++i) {
-                    int index = (key0 >> p.page_shift) + i;
-                    index = index < p.table_stride ? index : p.table_stride - 1;
-                    int page = table[index];
-                    page = page < 0 ? 0 : page;               // an entry given back early: never read
-                    const int y = (page * p.n_kv_heads + kv_head) << p.page_shift;
-                    const int dst = (i << p.page_shift) * HD * 2;
-                    tc::tma_load_2d(s.k[st] + dst, &map_k, &s.kv_full[st], 0, y);
-                    tc::tma_load_2d(s.v[st] + dst, &map_v, &s.kv_full[st], 0, y);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    if (i < pages_per_tile) {
+                        const int dst = (i << p.page_shift) * HD * 2;
+                        tc::tma_load_2d(s.k[st] + dst, &map_k, &s.kv_full[st], 0, rows_y[i]);
+                        tc::tma_load_2d(s.v[st] + dst, &map_v, &s.kv_full[st], 0, rows_y[i]);
+                    }
                 }
                 armed = j + 1;
             }
@@ -175,37 +217,46 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             constexpr uint32_t idesc_qk = tc::instr_desc_bf16(ROWS, KEYS);
             constexpr uint32_t idesc_pv = tc::instr_desc_bf16_b_mn(ROWS, HD);
             const uint64_t q_desc = tc::smem_desc_sw128(tc::smem_u32(s.q));
-            for (int j = 0; j < n_tiles; ++j) {
+            bool ok = true;
+            // S_j = Q K_j^T into buffer j & 1: K = 64 in four steps of 16
+            auto issue_qk = [&](int j) -> bool {
                 const int st = j % STAGES;
-                if (!tc::mbar_wait(&s.kv_full[st], (j / STAGES) & 1, abort_flag)) {
-                    tc::give_up(abort_flag, p.status, tc::ST_MMA_TIMEOUT);
-                    break;
-                }
+                if (!tc::mbar_wait(&s.kv_full[st], (j / STAGES) & 1, abort_flag)) return false;
                 tc::tc_fence_after_sync();
-                // S = Q K^T: K = 64 in four steps of 16
                 const uint64_t k_desc = tc::smem_desc_sw128(tc::smem_u32(s.k[st]));
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k)
-                    tc::umma_bf16(tmem_s, q_desc + 2 * k, k_desc + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
-                tc::umma_commit(&s.s_full);
-                // O += P V once the softmax has written P: K = 128 keys in eight steps of 16
-                if (!tc::mbar_wait(&s.p_full, j & 1, abort_flag)) {
-                    tc::give_up(abort_flag, p.status, tc::ST_MMA_TIMEOUT);
+                    tc::umma_bf16(tmem_s + (j & 1) * 128, q_desc + 2 * k, k_desc + 2 * k, idesc_qk,
+                                  k > 0 ? 1u : 0u);
+                tc::umma_commit(&s.s_full[j & 1]);
+                return true;
+            };
+            ok = issue_qk(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                // the next tile's scores go out first: their buffer was last read by the
+                // softmax of tile j - 1, whose P this thread has already waited for
+                if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+                if (!ok) break;
+                // O += P_j V_j once the softmax has written P_j: 128 keys in eight steps of 16
+                if (!tc::mbar_wait(&s.p_full[j & 1], (j >> 1) & 1, abort_flag)) {
+                    ok = false;
                     break;
                 }
                 tc::tc_fence_after_sync();
+                const int st = j % STAGES;
                 const uint64_t v_desc = tc::smem_desc_sw128(tc::smem_u32(s.v[st]));
 #pragma unroll
                 for (int k = 0; k < KEYS / 16; ++k) {
                     const uint64_t p_desc =
-                        tc::smem_desc_sw128(tc::smem_u32(s.p[k >> 2])) + 2 * (k & 3);
+                        tc::smem_desc_sw128(tc::smem_u32(s.p[j & 1][k >> 2])) + 2 * (k & 3);
                     // 16 keys further down V: 16 rows of 128 bytes = 128 descriptor units
                     tc::umma_bf16(tmem_o, p_desc, v_desc + 128 * k, idesc_pv,
                                   (j > 0 || k > 0) ? 1u : 0u);
                 }
                 tc::umma_commit(&s.kv_empty[st]);
-                tc::umma_commit(&s.pv_done);
+                tc::umma_commit(&s.pv_done[j & 1]);
             }
+            if (!ok) tc::give_up(abort_flag, p.status, tc::ST_MMA_TIMEOUT);
         }
     } else {
         // ---- softmax: warps 2..5, one thread per row = tensor-memory lane -------------------
@@ -213,101 +264,117 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         const int r = quarter * 32 + lane;
         const int row = qt * ROWS + r;
         const bool real = active && row < n_rows;
-        const int pos = real ? first_pos + row / n_rep : -1;
-        const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        // rows past the request's last are computed like rows that may read every key (their
+        // queries are zero) and are not stored: they keep a tile's fast path open
+        const int pos = real ? first_pos + row / n_rep : (1 << 30);
+        const int lo = real && p.window > 0 ? max(0, pos - p.window + 1) : 0;
         const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
+        auto wait_all = [&](uint64_t* bar, uint32_t parity) -> bool {
+            bool got = tc::mbar_wait(bar, parity, abort_flag);
+            if (!got && !*abort_flag) tc::give_up(abort_flag, p.status, tc::ST_EPILOGUE_TIMEOUT);
+            return __all_sync(0xffffffffu, got);
+        };
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int key0 = key_lo + j * KEYS;
-            ok = tc::mbar_wait(&s.s_full, j & 1, abort_flag);
-            if (!ok && !*abort_flag) tc::give_up(abort_flag, p.status, tc::ST_EPILOGUE_TIMEOUT);
-            ok = __all_sync(0xffffffffu, ok);
+            const int b = j & 1;
+            ok = wait_all(&s.s_full[b], (j >> 1) & 1);
             if (!ok) break;
             tc::tc_fence_after_sync();
-            // pass 1: the row's maximum over the tile's keys it may read
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c0 = 0; c0 < KEYS; c0 += 32) {
-                uint32_t v[32];
-                tc::tmem_ld_32x32(tmem_s + lane_bits + c0, v);
-                tc::tmem_ld_wait();
+            // the row's 128 scores, once, into registers
+            uint32_t sv[4][32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = key0 + c0 + i;
-                    if (key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(v[i]));
-                }
+            for (int c = 0; c < 4; ++c) tc::tmem_ld_32x32(tmem_s + b * 128 + lane_bits + c * 32, sv[c]);
+            tc::tmem_ld_wait();
+            tc::tc_fence_before_sync();
+            // keys of this tile the row may read: [first, last] relative to key0.  Most tiles
+            // lie wholly inside every row's range and skip the test.
+            const int last = min(pos - key0, KEYS - 1);
+            const int first = max(lo - key0, 0);
+            if (!__all_sync(0xffffffffu, last == KEYS - 1 && first == 0)) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int kk = c * 32 + i;
+                        if (kk > last || kk < first) sv[c][i] = __float_as_uint(-INFINITY);
+                    }
             }
+            float mc[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                mc[c] = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 32; i += 2)
+                    mc[c] = max3(mc[c], __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
+            }
+            float mx = fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3]));
             mx *= p.scale_log2;
             // raise the reference maximum only when it is exceeded by far; the accumulator
-            // in tensor memory is rescaled then, by the whole warp at once
+            // in tensor memory is rescaled then, by the whole warp at once, after the
+            // second MMA of the tile before has finished
             float corr = 1.0f;
             if (mx > m_ref + RAISE || (m_ref == -INFINITY && mx > -INFINITY)) {
                 corr = m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx);
                 m_ref = mx;
             }
-            // P's buffer and O are free only when the previous tile's second MMA is done
-            if (j > 0) {
-                ok = tc::mbar_wait(&s.pv_done, (j - 1) & 1, abort_flag);
-                if (!ok && !*abort_flag) tc::give_up(abort_flag, p.status, tc::ST_EPILOGUE_TIMEOUT);
-                ok = __all_sync(0xffffffffu, ok);
+            if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+                ok = wait_all(&s.pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1);
                 if (!ok) break;
                 tc::tc_fence_after_sync();
-                if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
-                    for (int c0 = 0; c0 < HD; c0 += 32) {
-                        uint32_t v[32];
-                        tc::tmem_ld_32x32(tmem_o + lane_bits + c0, v);
-                        tc::tmem_ld_wait();
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t v[32];
+                    tc::tmem_ld_32x32(tmem_o + lane_bits + c0, v);
+                    tc::tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-                        tc::tmem_st_32x32(tmem_o + lane_bits + c0, v);
-                    }
-                    tc::tmem_st_wait();
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                    tc::tmem_st_32x32(tmem_o + lane_bits + c0, v);
                 }
+                tc::tmem_st_wait();
+                tc::tc_fence_before_sync();
             }
             l *= corr;
-            // pass 2: P = exp2(s * scale - reference), to shared memory in the layout the
-            // second MMA reads (rows of 128 bytes per half of 64 keys, 128-byte swizzle)
-            const float off = m_ref == -INFINITY ? 0.f : m_ref;
-            float sum = 0.f;
-#pragma unroll 1
-            for (int c0 = 0; c0 < KEYS; c0 += 32) {
-                uint32_t v[32];
-                tc::tmem_ld_32x32(tmem_s + lane_bits + c0, v);
-                tc::tmem_ld_wait();
-                float e[32];
+            // P's buffer was last read by the second MMA of tile j - 2
+            if (j >= 2) {
+                ok = wait_all(&s.pv_done[b], ((j - 2) >> 1) & 1);
+                if (!ok) break;
+            }
+            // P = exp2(s * scale - reference), to shared memory in the layout the second MMA
+            // reads (rows of 128 bytes per half of 64 keys, 128-byte swizzle)
+            const float off = m_ref == -INFINITY ? 0.f : -m_ref;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = key0 + c0 + i;
-                    const bool in = key <= pos && key >= lo;
-                    e[i] = in ? exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2, -off)) : 0.f;
-                    sum += e[i];
-                }
-                uint8_t* half = s.p[c0 >> 6] + r * 128;
+            for (int c = 0; c < 4; ++c) {
+                uint8_t* half = s.p[b][c >> 1] + r * 128;
 #pragma unroll
                 for (int piece = 0; piece < 4; ++piece) {
-                    const int c = ((c0 & 63) >> 3) + piece;          // 16-byte piece inside the row
+                    float e[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i += 2) {
+                        e[i] = __uint_as_float(sv[c][8 * piece + i]);
+                        e[i + 1] = __uint_as_float(sv[c][8 * piece + i + 1]);
+                        fma_pair(e[i], e[i + 1], p.scale_log2, off);
+                        e[i] = ex2_fast(e[i]);
+                        e[i + 1] = ex2_fast(e[i + 1]);
+                        sum[i >> 1] += e[i] + e[i + 1];
+                    }
                     uint4 w;
-                    w.x = pack_bf16(e[8 * piece + 0], e[8 * piece + 1]);
-                    w.y = pack_bf16(e[8 * piece + 2], e[8 * piece + 3]);
-                    w.z = pack_bf16(e[8 * piece + 4], e[8 * piece + 5]);
-                    w.w = pack_bf16(e[8 * piece + 6], e[8 * piece + 7]);
-                    *reinterpret_cast<uint4*>(half + ((c ^ (r & 7)) << 4)) = w;
+                    w.x = pack_bf16(e[0], e[1]);
+                    w.y = pack_bf16(e[2], e[3]);
+                    w.z = pack_bf16(e[4], e[5]);
+                    w.w = pack_bf16(e[6], e[7]);
+                    const int pc = (c & 1) * 4 + piece;              // 16-byte piece inside the row
+                    *reinterpret_cast<uint4*>(half + ((pc ^ (r & 7)) << 4)) = w;
                 }
             }
-            l += sum;
-            tc::tc_fence_before_sync();          // our reads of S are done before S is overwritten
+            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             tc::fence_proxy_async();             // P is written by the generic proxy, read by the MMA
-            tc::mbar_arrive(&s.p_full);
+            tc::mbar_arrive(&s.p_full[b]);
         }
         // ---- the output: O / l ------------------------------------------------------------
-        if (ok && n_tiles > 0) {
-            ok = tc::mbar_wait(&s.pv_done, (n_tiles - 1) & 1, abort_flag);
-            if (!ok && !*abort_flag) tc::give_up(abort_flag, p.status, tc::ST_EPILOGUE_TIMEOUT);
-            ok = __all_sync(0xffffffffu, ok);
-        }
+        if (ok && n_tiles > 0) ok = wait_all(&s.pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
         if (ok && n_tiles > 0) {
             tc::tc_fence_after_sync();
             const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -339,7 +406,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     __syncthreads();
     if (warp == 1) {
         tc::tc_fence_after_sync();
-        tc::tmem_dealloc(s.tmem_base, 256);
+        tc::tmem_dealloc(s.tmem_base, 512);
     }
 }
 
