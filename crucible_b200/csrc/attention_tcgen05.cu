@@ -45,7 +45,7 @@ struct TcAttnParams {
     const int* req_first_pos;
     const int* block_table;
     int table_stride;
-    int n_heads, n_kv_heads, page_tokens, page_shift;
+    int n_heads, n_kv_heads, n_requests, page_tokens, page_shift;
     float scale_log2;
     int window;
     int* status;
@@ -100,12 +100,15 @@ __global__ void __launch_bounds__(192)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const TcAttnParams p) {
     cb_pdl_trigger();
-    // 1024-byte alignment (the swizzled tiles need it) is asked of the declaration, not
-    // bought with slack: two blocks of 112 KB then fit one SM
+    // 1024-byte alignment (the swizzled tiles need it) is asked of the declaration
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     Storage& s = *reinterpret_cast<Storage*>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int req = blockIdx.z, kv_head = blockIdx.y;
+    // one index over (tile rank, request, head) with the tile rank slowest: blocks start in
+    // order of weight over the whole launch, the longest rows first
+    const int kv_head = blockIdx.x % p.n_kv_heads;
+    const int req = (blockIdx.x / p.n_kv_heads) % p.n_requests;
+    const int rank = blockIdx.x / (p.n_kv_heads * p.n_requests);
     volatile int* abort_flag = &s.abort_flag;
 
     if (threadIdx.x == 0) {
@@ -115,7 +118,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         }
         for (int b = 0; b < 2; ++b) {
             tc::mbar_init(&s.s_full[b], 1);
-            tc::mbar_init(&s.p_full[b], 128);
+            tc::mbar_init(&s.p_full[b], 4);               // one arrival per softmax warp
             tc::mbar_init(&s.pv_done[b], 1);
         }
         s.abort_flag = 0;
@@ -134,8 +137,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     const int n_new = p.req_row_start[req + 1] - row_base;
     const int n_rows = n_new * n_rep;
     const int q_tiles = (n_rows + ROWS - 1) / ROWS;
-    const bool active = (int)blockIdx.x < q_tiles;
-    const int qt = active ? q_tiles - 1 - (int)blockIdx.x : 0;     // heaviest tiles first
+    const bool active = rank < q_tiles;
+    const int qt = active ? q_tiles - 1 - rank : 0;               // heaviest tiles first
     const int first_pos = p.req_first_pos[req];
     const int* table = p.block_table + (size_t)req * p.table_stride;
 
@@ -148,9 +151,47 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     const int key_end = max_pos + 1;
     const int n_tiles = active ? (key_end - key_lo + KEYS - 1) / KEYS : 0;
 
-    // ---- the query rows, by all threads: 16-byte pieces into the 128-byte swizzle -------
-    if (active) {
-        for (int i = threadIdx.x; i < ROWS * 8; i += blockDim.x) {
+    // ---- the loader's thread: one tile of K and V pages into a stage --------------------------
+    const int pages_per_tile = KEYS >> p.page_shift;
+    auto load_tile = [&](int j) -> bool {
+        const int st = j % STAGES;
+        const uint32_t round = j / STAGES;
+        // the tile's table entries first, all in flight at once: the copies below
+        // are ordered against memory and would take the lookups one by one
+        const int key0 = key_lo + j * KEYS;
+        int rows_y[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            int index = (key0 >> p.page_shift) + (i < pages_per_tile ? i : 0);
+            index = index < p.table_stride ? index : p.table_stride - 1;
+            int page = table[index];
+            page = page < 0 ? 0 : page;               // an entry given back early: never read
+            rows_y[i] = (page * p.n_kv_heads + kv_head) << p.page_shift;
+        }
+        if (round > 0 && !tc::mbar_wait(&s.kv_empty[st], (round - 1) & 1, abort_flag)) {
+            tc::give_up(abort_flag, p.status, tc::ST_PRODUCER_TIMEOUT);
+            return false;
+        }
+        tc::mbar_expect_tx(&s.kv_full[st], 2 * KEYS * HD * 2);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if (i < pages_per_tile) {
+                const int dst = (i << p.page_shift) * HD * 2;
+                tc::tma_load_2d(s.k[st] + dst, &map_k, &s.kv_full[st], 0, rows_y[i]);
+                tc::tma_load_2d(s.v[st] + dst, &map_v, &s.kv_full[st], 0, rows_y[i]);
+            }
+        }
+        return true;
+    };
+    const int early = n_tiles < STAGES ? n_tiles : STAGES;
+
+    // ---- the query rows, by warps 1..5: 16-byte pieces into the 128-byte swizzle; warp 0's
+    // thread meanwhile starts the first tiles' copies, which wait for nothing -----------------
+    if (warp == 0) {
+        if (lane == 0)
+            for (int j = 0; j < early; ++j) load_tile(j);
+    } else if (active) {
+        for (int i = threadIdx.x - 32; i < ROWS * 8; i += blockDim.x - 32) {
             const int r = i >> 3, c = i & 7;
             const int row = qt * ROWS + r;
             uint4 val = make_uint4(0, 0, 0, 0);
@@ -170,38 +211,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     const uint32_t tmem_o = s.tmem_base + 256;
 
     if (warp == 0) {
-        // ---- loader ---------------------------------------------------------------------
+        // ---- loader: the remaining tiles, each once its stage has been read ------------------
         if (lane == 0 && n_tiles > 0) {
-            const int pages_per_tile = KEYS >> p.page_shift;
-            int armed = 0;
-            for (int j = 0; j < n_tiles; ++j) {
-                const int st = j % STAGES;
-                const uint32_t round = j / STAGES;
-                // the tile's table entries first, all in flight at once: the copies below
-                // are ordered against memory and would take the lookups one by one
-                const int key0 = key_lo + j * KEYS;
-                int rows_y[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    int index = (key0 >> p.page_shift) + (i < pages_per_tile ? i : 0);
-                    index = index < p.table_stride ? index : p.table_stride - 1;
-                    int page = table[index];
-                    page = page < 0 ? 0 : page;               // an entry given back early: never read
-                    rows_y[i] = (page * p.n_kv_heads + kv_head) << p.page_shift;
-                }
-                if (round > 0 && !tc::mbar_wait(&s.kv_empty[st], (round - 1) & 1, abort_flag)) {
-                    tc::give_up(abort_flag, p.status, tc::ST_PRODUCER_TIMEOUT);
-                    break;
-                }
-                tc::mbar_expect_tx(&s.kv_full[st], 2 * KEYS * HD * 2);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    if (i < pages_per_tile) {
-                        const int dst = (i << p.page_shift) * HD * 2;
-                        tc::tma_load_2d(s.k[st] + dst, &map_k, &s.kv_full[st], 0, rows_y[i]);
-                        tc::tma_load_2d(s.v[st] + dst, &map_v, &s.kv_full[st], 0, rows_y[i]);
-                    }
-                }
+            int armed = early;
+            for (int j = early; j < n_tiles; ++j) {
+                if (!load_tile(j)) break;
                 armed = j + 1;
             }
             if (*abort_flag) {
@@ -284,6 +298,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             tc::tc_fence_after_sync();
             // the row's 128 scores, once, into registers
             uint32_t sv[4][32];
+#pragma unroll
 #pragma unroll
             for (int c = 0; c < 4; ++c) tc::tmem_ld_32x32(tmem_s + b * 128 + lane_bits + c * 32, sv[c]);
             tc::tmem_ld_wait();
@@ -371,7 +386,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             }
             l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             tc::fence_proxy_async();             // P is written by the generic proxy, read by the MMA
-            tc::mbar_arrive(&s.p_full[b]);
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&s.p_full[b]);
         }
         // ---- the output: O / l ------------------------------------------------------------
         if (ok && n_tiles > 0) ok = wait_all(&s.pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
@@ -444,6 +460,7 @@ CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, i
     p.table_stride = table_stride;
     p.n_heads = n_heads;
     p.n_kv_heads = n_kv_heads;
+    p.n_requests = n_requests;
     p.page_tokens = page_tokens;
     p.page_shift = shift;
     p.scale_log2 = scale * LOG2E;
@@ -459,7 +476,7 @@ CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, i
     }
     const int n_rep = n_heads / n_kv_heads;
     const int q_tiles = (max_new_tokens * n_rep + ROWS - 1) / ROWS;
-    cb_launch(attention_tcgen05_kernel, dim3(q_tiles, n_kv_heads, n_requests), dim3(192), smem,
+    cb_launch(attention_tcgen05_kernel, dim3(q_tiles * n_kv_heads * n_requests), dim3(192), smem,
               (cudaStream_t)stream, mk, mv, p);
     return cb_last_error();
 }
