@@ -9,12 +9,15 @@
 //                   keys in tiles of 64 (cp.async, double buffered); flash-style
 //                   running maximum; writes the normalised output.  For portions
 //                   of prompts.
-//   split kernel  - a block takes 16 rows and ONE chunk of 256 keys, 64 per
-//                   warp; writes an unnormalised partial (max, sum, vector) to
-//                   scratch; a second kernel merges the chunks in ascending
-//                   order.  For decoded tokens, where rows are few and keys many.
-// Chunk boundaries are multiples of 256 from key 0 whatever the batch holds, so
-// a row's result is a function of its own query and keys only.
+//   split kernel  - a block takes 16 rows and ONE chunk of 256 * 2^k keys, a
+//                   quarter per warp; writes an unnormalised partial (max, sum,
+//                   vector) to scratch; the last block of a row group to arrive
+//                   (an atomic counter: no block waits for another) merges the
+//                   chunks in ascending order.  For decoded tokens, where rows
+//                   are few and keys many.
+// Chunk boundaries are multiples of the chunk from key 0 whatever the batch
+// holds, and the chunk is chosen from the launch's shape, so a row's result is
+// a function of its own query and keys only.
 //
 // Head sizes: multiples of 16 up to 256.  Any head counts and group sizes, any
 // page size.  Reference counterparts: `attention_prefill_exact_*`

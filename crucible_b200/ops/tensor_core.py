@@ -217,11 +217,12 @@ def _attention_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads, h
 
 def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx, cache,
                     binding) -> bool:
-    """mma.sync attention over the paged cache.  Takes head sizes that are
+    """Tensor-core attention over the paged cache.  Takes head sizes that are
     multiples of 16 up to 256 and any head counts, group sizes and page sizes;
-    refuses anything else (the plain kernel then runs).  Requests that bring at
-    most 16 query rows per KV head (decoded tokens, tiny portions) run split
-    over chunks of 256 keys; longer portions run as tiles of 64 rows."""
+    refuses anything else (the plain kernel then runs).  Steps whose requests
+    bring at most 16 query rows per KV head (decoded tokens, tiny portions) run
+    split over chunks of 256 * 2^k keys; longer portions run as tiles: the
+    tcgen05 kernel for head size 64, the mma.sync kernel of 64-row tiles else."""
     if (qkv.dtype != torch.bfloat16 or head_dim % 16 != 0 or head_dim > 256
             or n_heads % n_kv_heads != 0 or qkv.stride(0) % 8 != 0 or out.stride(0) % 2 != 0):
         return False
