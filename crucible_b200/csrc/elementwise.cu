@@ -241,6 +241,89 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, const float* __restri
     }
 }
 
+// The same for bfloat16 rows whose head size, rotated half and unrotated tail are
+// multiples of 8: a thread takes 8 features (16 bytes) of a head - for rotated
+// features the 8 of the first half and their 8 partners - so a token's row is
+// read and written once in 16-byte pieces.  Items are spread over the grid
+// whatever the number of tokens.
+__global__ void rope_kv_append_vec8_kernel(__nv_bfloat16* __restrict__ qkv,
+                                           const float* __restrict__ cos_t,
+                                           const float* __restrict__ sin_t, int rotary_dim,
+                                           const int* __restrict__ positions,
+                                           const int* __restrict__ row_request,
+                                           const int* __restrict__ block_table, int table_stride,
+                                           __nv_bfloat16* __restrict__ k_cache,
+                                           __nv_bfloat16* __restrict__ v_cache, int n_rows,
+                                           int n_heads, int n_kv_heads, int head_dim,
+                                           int page_tokens, int write_cache) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    const int half = rotary_dim >> 1;
+    const int pass = head_dim - rotary_dim;
+    const int n_rot_heads = n_heads + (write_cache ? n_kv_heads : 0);
+    const int rot_items = n_rot_heads * (half >> 3);
+    const int tail_items = write_cache ? n_kv_heads * (pass >> 3) : 0;
+    const int v_items = write_cache ? n_kv_heads * (head_dim >> 3) : 0;
+    const int per_token = rot_items + tail_items + v_items;
+    const int row_width = (n_heads + 2 * n_kv_heads) * head_dim;
+    const size_t head_stride = (size_t)page_tokens * head_dim;
+    const long total = (long)n_rows * per_token;
+    for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long)gridDim.x * blockDim.x) {
+        const int t = (int)(idx / per_token);
+        int item = (int)(idx - (long)t * per_token);
+        __nv_bfloat16* row = qkv + (size_t)t * row_width;
+        const int pos = positions[t];
+        size_t cache_base = 0;
+        if (write_cache) {
+            const int page = block_table[(size_t)row_request[t] * table_stride + pos / page_tokens];
+            cache_base = (size_t)page * n_kv_heads * head_stride + (size_t)(pos % page_tokens) * head_dim;
+        }
+        if (item < rot_items) {
+            const int per_head = half >> 3;
+            const int h = item / per_head, j = (item - h * per_head) << 3;
+            const __nv_bfloat16* src = row + (size_t)h * head_dim;
+            const uint4 lo = *reinterpret_cast<const uint4*>(src + j);
+            const uint4 hi = *reinterpret_cast<const uint4*>(src + j + half);
+            const float4 c0 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + j);
+            const float4 c1 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + j + 4);
+            const float4 s0 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + j);
+            const float4 s1 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + j + 4);
+            const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            const __nv_bfloat16* x1 = reinterpret_cast<const __nv_bfloat16*>(&lo);
+            const __nv_bfloat16* x2 = reinterpret_cast<const __nv_bfloat16*>(&hi);
+            uint4 out_lo, out_hi;
+            __nv_bfloat16* y1 = reinterpret_cast<__nv_bfloat16*>(&out_lo);
+            __nv_bfloat16* y2 = reinterpret_cast<__nv_bfloat16*>(&out_hi);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float a = __bfloat162float(x1[i]), b = __bfloat162float(x2[i]);
+                y1[i] = __float2bfloat16_rn(a * c[i] - b * sn[i]);
+                y2[i] = __float2bfloat16_rn(a * sn[i] + b * c[i]);
+            }
+            __nv_bfloat16* dst = h < n_heads ? row + (size_t)h * head_dim
+                                             : k_cache + cache_base + (size_t)(h - n_heads) * head_stride;
+            *reinterpret_cast<uint4*>(dst + j) = out_lo;
+            *reinterpret_cast<uint4*>(dst + j + half) = out_hi;
+            continue;
+        }
+        item -= rot_items;
+        if (item < tail_items) {
+            const int per_head = pass >> 3;
+            const int h = item / per_head, j = rotary_dim + ((item - h * per_head) << 3);
+            *reinterpret_cast<uint4*>(k_cache + cache_base + (size_t)h * head_stride + j) =
+                *reinterpret_cast<const uint4*>(row + (size_t)(n_heads + h) * head_dim + j);
+            continue;
+        }
+        item -= tail_items;
+        const int per_head = head_dim >> 3;
+        const int h = item / per_head, j = (item - h * per_head) << 3;
+        *reinterpret_cast<uint4*>(v_cache + cache_base + (size_t)h * head_stride + j) =
+            *reinterpret_cast<const uint4*>(row + (size_t)(n_heads + n_kv_heads + h) * head_dim + j);
+    }
+}
+
 CB_EXPORT int cb_rope_kv_append(void* qkv, int dtype, const float* cos_t, const float* sin_t,
                                 int rotary_dim, const int* positions, const int* row_request,
                                 const int* block_table, int table_stride, void* k_cache,
@@ -252,6 +335,22 @@ CB_EXPORT int cb_rope_kv_append(void* qkv, int dtype, const float* cos_t, const 
     int threads = (work + 31) / 32 * 32;
     if (threads > 512) threads = 512;
     if (threads < 64) threads = 64;
+    if (dtype != CB_F32 && (head_dim & 7) == 0 && (rotary_dim & 15) == 0 &&
+        ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 &&
+        (rotary_dim == 0 || (((uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0)) {
+        const int half8 = rotary_dim >> 4;
+        const long per_token = (long)(n_heads + (write_cache ? n_kv_heads : 0)) * half8 +
+                               (write_cache ? (long)n_kv_heads * (((head_dim - rotary_dim) >> 3) + (head_dim >> 3)) : 0);
+        const long total = (long)n_rows * per_token;
+        if (total == 0) return 0;
+        long blocks = (total + 255) / 256;
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        cb_launch(rope_kv_append_vec8_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream,
+                  (__nv_bfloat16*)qkv, cos_t, sin_t, rotary_dim, positions, row_request, block_table,
+                  table_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_rows, n_heads,
+                  n_kv_heads, head_dim, page_tokens, write_cache);
+        return cb_last_error();
+    }
     if (dtype == CB_F32)
         cb_launch(rope_kv_append_kernel<float>, dim3(n_rows), dim3(threads), 0, (cudaStream_t)stream, 
             (float*)qkv, cos_t, sin_t, rotary_dim, positions, row_request, block_table,

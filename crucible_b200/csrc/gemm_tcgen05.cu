@@ -145,6 +145,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         // ---- epilogue: warps 2..5, lane quarter = warp % 4 -----------------------
         const int quarter = warp & 3;
         const int row = m0 + quarter * 32 + lane;
+        // ACCUM_F32: the values to add to are asked for now, while the products run; the
+        // thread's whole row of the tile stays in registers (tiles up to 128 wide)
+        constexpr bool EARLY = EPI == ACCUM_F32 && BN <= 128;
+        constexpr int NQ = EARLY ? BN / 4 : 1;
+        float4 early[NQ];
+        if (EARLY) {
+            const bool vec = (ldc & 3) == 0 && row < M;
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) {
+                const int col = n_tile * BN + (q >> 3) * 32;          // the chunk of 32 columns
+                early[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (vec && col + 32 <= N)
+                    early[q] = __ldcg(reinterpret_cast<const float4*>((const float*)c_ptr +
+                                                                      (size_t)row * ldc + col) + (q & 7));
+            }
+        }
         bool ok = tc::mbar_wait(&s.tmem_full_bar, 0, abort_flag);
         if (!ok && !*abort_flag) tc::give_up(abort_flag, status, tc::ST_EPILOGUE_TIMEOUT);
         ok = __all_sync(0xffffffffu, ok);
@@ -187,6 +203,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                 }
                             }
                         }
+                    }
+                }
+            } else if (EARLY) {
+#pragma unroll
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t r[32];
+                    tc::tmem_ld_32x32(lane_addr + c0, r);
+                    tc::tmem_ld_wait();
+                    const int col0 = n_tile * BN + c0;
+                    if (row >= M || col0 >= N) continue;
+                    float* dst = (float*)c_ptr + (size_t)row * ldc + col0;
+                    if (col0 + 32 <= N && (ldc & 3) == 0) {
+                        float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            const float4 o = early[(c0 >> 2) + q];
+                            d4[q] = make_float4(o.x + __uint_as_float(r[4 * q]),
+                                                o.y + __uint_as_float(r[4 * q + 1]),
+                                                o.z + __uint_as_float(r[4 * q + 2]),
+                                                o.w + __uint_as_float(r[4 * q + 3]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < N) dst[j] += __uint_as_float(r[j]);
                     }
                 }
             } else {
