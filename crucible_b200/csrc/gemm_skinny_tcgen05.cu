@@ -225,7 +225,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
                 for (int m = 0; m < MT; ++m) {
                     if (m < M) {
                         const float g = acc[m], u = xch[w_row * MT + m];
-                        C[(size_t)m * ldc + col] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
+                        C[(size_t)m * ldc + col] = __float2bfloat16_rn(tc::silu_fast(g) * u);
                     }
                 }
             }

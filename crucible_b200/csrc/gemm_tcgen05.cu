@@ -42,7 +42,7 @@ struct SharedStorage {
 };
 
 template <int BN, int STAGES, int EPI>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, STAGES <= 3 ? 2 : 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_w, void* __restrict__ c_ptr, int M,
                     int N, int K, int ldc, int inter, int* __restrict__ status) {
@@ -185,8 +185,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                             for (int j = 0; j < 8; ++j) {
                                 const float g0 = __uint_as_float(g[2 * j]);
                                 const float g1 = __uint_as_float(g[2 * j + 1]);
-                                const float h0 = g0 / (1.0f + __expf(-g0)) * __uint_as_float(u[2 * j]);
-                                const float h1 = g1 / (1.0f + __expf(-g1)) * __uint_as_float(u[2 * j + 1]);
+                                const float h0 = tc::silu_fast(g0) * __uint_as_float(u[2 * j]);
+                                const float h1 = tc::silu_fast(g1) * __uint_as_float(u[2 * j + 1]);
                                 __nv_bfloat162 v = __floats2bfloat162_rn(h0, h1);
                                 packed[j] = *reinterpret_cast<uint32_t*>(&v);
                             }
@@ -198,7 +198,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                             for (int j = 0; j < 16; ++j) {
                                 if (col0 + j < inter) {
                                     const float gv = __uint_as_float(g[j]);
-                                    dst[j] = __float2bfloat16_rn(gv / (1.0f + __expf(-gv)) *
+                                    dst[j] = __float2bfloat16_rn(tc::silu_fast(gv) *
                                                                  __uint_as_float(u[j]));
                                 }
                             }
@@ -330,9 +330,13 @@ int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, void* C, i
 }  // namespace
 
 // W is [N, K] (for SWIGLU_BF16: [2 * inter, K], N = inter and C is [M, inter]).
-// bn: tile width: 64, 96, 128, 160, 192 or 256.  status: device int, stays 0 unless a wait ran out.
+// bn: tile width: 64, 96, 128, 160, 192 or 256.  per_sm: 1 = a deep ring of stages, one
+// block per SM; 2 = three stages, so that two blocks share an SM and one's prologue and
+// epilogue run beside the other's products (tile widths up to 128).
+// status: device int, stays 0 unless a wait ran out.
 CB_EXPORT int cb_gemm_tcgen05(const void* A, const void* W, void* C, int M, int N, int K, int lda,
-                              int ldw, int ldc, int epi, int bn, int* status, void* stream) {
+                              int ldw, int ldc, int epi, int bn, int per_sm, int* status,
+                              void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15))
         return CB_ERR_UNSUPPORTED;
@@ -344,6 +348,14 @@ CB_EXPORT int cb_gemm_tcgen05(const void* A, const void* W, void* C, int M, int 
         return CB_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const int inter = epi == SWIGLU_BF16 ? N : 0;
+    if (per_sm == 2) {
+        switch (bn) {
+            case 64: return launch_epi<64, 3>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
+            case 96: return launch_epi<96, 3>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
+            case 128: return launch_epi<128, 3>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
+        }
+        return CB_ERR_UNSUPPORTED;
+    }
     switch (bn) {
         case 64: return launch_epi<64, 6>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
         case 96: return launch_epi<96, 6>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);

@@ -69,7 +69,12 @@ TILE_WIDTHS = (64, 96, 128, 160, 192, 256)
 N_SMS = 148
 
 
-def _tile_width(m: int, n_cols: int) -> int:
+def _tile_of(tile):
+    """`tile` as callers may give it: a width, or (width, blocks per SM)."""
+    return (tile, 1) if isinstance(tile, int) else tuple(tile)
+
+
+def _tile_width(m: int, n_cols: int):
     """Tile width in output columns: the one that needs the least time if every
     block costs (width + a fixed part) and blocks run in waves over the SMs.  A
     wide tile reuses the A tile more; a narrow one fills the last wave better."""
@@ -80,15 +85,15 @@ def _tile_width(m: int, n_cols: int) -> int:
         cost = -(-blocks // N_SMS) * (bn + 48)
         if best_cost is None or cost < best_cost or (cost == best_cost and bn > best):
             best, best_cost = bn, cost
-    return best
+    return best, 1
 
 
-def _gemm(a, w, out, n, epi, bn) -> bool:
+def _gemm(a, w, out, n, epi, bn, per_sm=1) -> bool:
     lib = build.load("gemm_tcgen05")
     code = lib.cb_gemm_tcgen05(
         _c_void_p(a.data_ptr()), _c_void_p(w.data_ptr()), _c_void_p(out.data_ptr()),
         _c_int(a.shape[0]), _c_int(n), _c_int(a.shape[1]), _c_int(a.stride(0)),
-        _c_int(w.stride(0)), _c_int(out.stride(0)), _c_int(epi), _c_int(bn),
+        _c_int(w.stride(0)), _c_int(out.stride(0)), _c_int(epi), _c_int(bn), _c_int(per_sm),
         _c_void_p(status_word(a.device).data_ptr()), _stream())
     if code == _UNSUPPORTED:
         return False
@@ -176,8 +181,8 @@ def linear(a, w, out, *, accumulate=False, tile=None) -> bool:
     if tile is None and (a.shape[0] <= SKINNY_ROWS
                          or (a.shape[0] <= 64 and w.shape[0] >= SKINNY_WIDE_N)):
         return _gemm_skinny(a, w, out, w.shape[0], epi)
-    bn = tile or _tile_width(a.shape[0], w.shape[0])
-    return _gemm(a, w, out, w.shape[0], epi, bn)
+    bn, per_sm = _tile_of(tile) if tile else _tile_width(a.shape[0], w.shape[0])
+    return _gemm(a, w, out, w.shape[0], epi, bn, per_sm)
 
 
 def linear_swiglu(h, gate_up, out, tile=None) -> bool:
@@ -186,8 +191,8 @@ def linear_swiglu(h, gate_up, out, tile=None) -> bool:
     inter = gate_up.shape[0] // 2
     if tile is None and h.shape[0] <= SKINNY_ROWS:
         return _gemm_skinny(h, gate_up, out, inter, SWIGLU_BF16)
-    bn = tile or _tile_width(h.shape[0], 2 * inter)
-    return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn)
+    bn, per_sm = _tile_of(tile) if tile else _tile_width(h.shape[0], 2 * inter)
+    return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn, per_sm)
 
 
 def _attention_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads, head_dim, scale,
