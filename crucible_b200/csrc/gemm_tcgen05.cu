@@ -44,8 +44,10 @@ struct SharedStorage {
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(192, STAGES <= 3 ? 2 : 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
-                    const __grid_constant__ CUtensorMap map_w, void* __restrict__ c_ptr, int M,
-                    int N, int K, int ldc, int inter, int* __restrict__ status) {
+                    const __grid_constant__ CUtensorMap map_w,
+                    const __grid_constant__ CUtensorMap map_c, int tma_out,
+                    void* __restrict__ c_ptr, int M, int N, int K, int ldc, int inter,
+                    int* __restrict__ status) {
     cb_pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     using Storage = SharedStorage<BN, STAGES>;
@@ -70,6 +72,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&map_a);
         tc::prefetch_tensormap(&map_w);
+        if (tma_out) tc::prefetch_tensormap(&map_c);
     }
     if (warp == 1) {
         tc::tmem_alloc(&s.tmem_base, TMEM_COLS);
@@ -150,7 +153,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         constexpr bool EARLY = EPI == ACCUM_F32 && BN <= 128;
         constexpr int NQ = EARLY ? BN / 4 : 1;
         float4 early[NQ];
-        if (EARLY) {
+        if (EARLY && !tma_out) {
             const bool vec = (ldc & 3) == 0 && row < M;
 #pragma unroll
             for (int q = 0; q < NQ; ++q) {
@@ -167,7 +170,71 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         if (ok) {
             tc::tc_fence_after_sync();
             const uint32_t lane_addr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
-            if (EPI == SWIGLU_BF16) {
+            if (tma_out) {
+                // Through shared memory and out by TMA: the ring of stages is free by now.
+                // Chunks of [128 rows][128 bytes] in the 128-byte swizzle; a thread writes
+                // its row's eight 16-byte pieces, then one thread sends the box: a store, or
+                // for ACCUM_F32 an fp32 add at the memory side (no read of C at all).
+                const int r = quarter * 32 + lane;
+                uint8_t* ring = s.a[0];
+                constexpr int OUT_COLS = EPI == SWIGLU_BF16 ? BN / 2 : BN;     // columns of C per tile
+                constexpr int CHUNK = (EPI == STORE_F32 || EPI == ACCUM_F32) ? 32 : 64;
+                const int n_out = EPI == SWIGLU_BF16 ? inter : N;
+#pragma unroll 1
+                for (int c = 0; c < OUT_COLS / CHUNK; ++c) {
+                    uint8_t* buf = ring + c * (BM * 128);
+                    uint8_t* mine = buf + r * 128;
+                    if (EPI == STORE_F32 || EPI == ACCUM_F32) {
+                        uint32_t v[32];
+                        tc::tmem_ld_32x32(lane_addr + c * 32, v);
+                        tc::tmem_ld_wait();
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            *reinterpret_cast<uint4*>(mine + ((q ^ (r & 7)) << 4)) =
+                                make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            uint32_t v[32];
+                            tc::tmem_ld_32x32(lane_addr + c * 64 + h * 32, v);
+                            if (EPI == SWIGLU_BF16) {
+                                uint32_t u[32];
+                                tc::tmem_ld_32x32(lane_addr + BN / 2 + c * 64 + h * 32, u);
+                                tc::tmem_ld_wait();
+#pragma unroll
+                                for (int j = 0; j < 32; ++j)
+                                    v[j] = __float_as_uint(tc::silu_fast(__uint_as_float(v[j])) *
+                                                           __uint_as_float(u[j]));
+                            } else {
+                                tc::tmem_ld_wait();
+                            }
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                uint32_t pk[4];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(
+                                        __uint_as_float(v[q * 8 + 2 * j]), __uint_as_float(v[q * 8 + 2 * j + 1]));
+                                    pk[j] = *reinterpret_cast<uint32_t*>(&b2);
+                                }
+                                *reinterpret_cast<uint4*>(mine + (((h * 4 + q) ^ (r & 7)) << 4)) =
+                                    make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                            }
+                        }
+                    }
+                    tc::fence_proxy_async();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (warp == 2 && lane == 0) {
+                        const int x = n_tile * OUT_COLS + c * CHUNK;
+                        if (x < n_out) {
+                            if (EPI == ACCUM_F32) tc::tma_reduce_add_2d(&map_c, buf, x, m0);
+                            else tc::tma_store_2d(&map_c, buf, x, m0);
+                            tc::tma_store_commit();
+                        }
+                    }
+                }
+                if (warp == 2 && lane == 0) tc::tma_store_wait_all();
+            } else if (EPI == SWIGLU_BF16) {
                 constexpr int HALF = BN / 2;
                 __nv_bfloat16* C = (__nv_bfloat16*)c_ptr;
 #pragma unroll 1
@@ -299,6 +366,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 template <int BN, int STAGES, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, int K, int ldc,
            int inter, int* status, cudaStream_t stream) {
+    // the output goes through shared memory and TMA where its rows allow it
+    const bool f32 = EPI == STORE_F32 || EPI == ACCUM_F32;
+    const int esize = f32 ? 4 : 2;
+    const int out_cols = EPI == SWIGLU_BF16 ? inter : N;
+    int tma_out = ((uintptr_t)C & 15) == 0 && ((size_t)ldc * esize) % 16 == 0 &&
+                  (f32 || (EPI == SWIGLU_BF16 ? BN % 128 == 0 : BN % 64 == 0));
+    CUtensorMap mc = ma;
+    if (tma_out && !tc::make_out_map_2d(&mc, C, f32, (uint64_t)M, (uint64_t)out_cols, (uint64_t)ldc, BM))
+        tma_out = 0;
     using Storage = SharedStorage<BN, STAGES>;
     const int smem = (int)sizeof(Storage) + 1024;
     static bool configured = false;
@@ -310,8 +386,8 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, 
     }
     const int n_cols = EPI == SWIGLU_BF16 ? 2 * inter : N;
     dim3 grid((n_cols + BN - 1) / BN, (M + BM - 1) / BM);
-    cb_launch(gemm_tcgen05_kernel<BN, STAGES, EPI>, dim3(grid), dim3(192), smem, stream, ma, mw, C, M, N, K, ldc,
-                                                                      inter, status);
+    cb_launch(gemm_tcgen05_kernel<BN, STAGES, EPI>, dim3(grid), dim3(192), smem, stream, ma, mw, mc, tma_out,
+              C, M, N, K, ldc, inter, status);
     return cb_last_error();
 }
 

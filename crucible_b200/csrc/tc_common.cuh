@@ -281,6 +281,56 @@ inline bool make_map_2d(CUtensorMap* out, const void* base, uint64_t rows, uint6
     return true;
 }
 
+// An output matrix [rows, cols] (bf16 or fp32) with `ld` elements between rows,
+// written in boxes of [box_rows, 128 bytes] with the 128-byte swizzle.
+inline bool make_out_map_2d(CUtensorMap* out, const void* base, bool f32, uint64_t rows,
+                            uint64_t cols, uint64_t ld, uint32_t box_rows) {
+    typedef std::tuple<const void*, bool, uint64_t, uint64_t, uint64_t, uint32_t> Key;
+    static std::map<Key, CUtensorMap> cache;
+    static std::mutex mu;
+    Key key(base, f32, rows, cols, ld, box_rows);
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return true;
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const uint64_t esize = f32 ? 4 : 2;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * esize};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / esize), box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+    if (cache.size() > 8192) cache.clear();
+    cache[key] = *out;
+    return true;
+}
+
+// 2-D tiled TMA store shared -> global of one box; elements outside the tensor are
+// not written.  x * element size must be a multiple of 16; never negative.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"((uint64_t)map), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+                 : "memory");
+}
+
+// The same box added to global memory (fp32 add at the memory side).
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"((uint64_t)map), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until every committed store of this thread has been written
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // silu(g) = g / (1 + e^-g) in fp32 with the hardware's exponential and reciprocal
 // (a few ulp; the result is then rounded to bfloat16).  The IEEE division costs a
 // hundred dependent cycles per element in an epilogue whose threads have no other work.

@@ -74,15 +74,18 @@ def _tile_of(tile):
     return (tile, 1) if isinstance(tile, int) else tuple(tile)
 
 
-def _tile_width(m: int, n_cols: int):
+def _tile_width(m: int, n_cols: int, epi: int = 1):
     """Tile width in output columns: the one that needs the least time if every
     block costs (width + a fixed part) and blocks run in waves over the SMs.  A
-    wide tile reuses the A tile more; a narrow one fills the last wave better."""
+    wide tile reuses the A tile more; a narrow one fills the last wave better.
+    Widths whose output cannot leave through shared memory and TMA (bfloat16 rows
+    that are no multiple of 128 bytes per tile) pay for their strided stores."""
     m_tiles = -(-m // 128)
     best, best_cost = 64, None
     for bn in TILE_WIDTHS:
         blocks = m_tiles * -(-n_cols // bn)
-        cost = -(-blocks // N_SMS) * (bn + 48)
+        direct = (epi == STORE_BF16 and bn % 64) or (epi == SWIGLU_BF16 and bn % 128)
+        cost = -(-blocks // N_SMS) * (bn + 48 + (40 if direct else 0))
         if best_cost is None or cost < best_cost or (cost == best_cost and bn > best):
             best, best_cost = bn, cost
     return best, 1
@@ -181,7 +184,7 @@ def linear(a, w, out, *, accumulate=False, tile=None) -> bool:
     if tile is None and (a.shape[0] <= SKINNY_ROWS
                          or (a.shape[0] <= 64 and w.shape[0] >= SKINNY_WIDE_N)):
         return _gemm_skinny(a, w, out, w.shape[0], epi)
-    bn, per_sm = _tile_of(tile) if tile else _tile_width(a.shape[0], w.shape[0])
+    bn, per_sm = _tile_of(tile) if tile else _tile_width(a.shape[0], w.shape[0], epi)
     return _gemm(a, w, out, w.shape[0], epi, bn, per_sm)
 
 
@@ -191,7 +194,7 @@ def linear_swiglu(h, gate_up, out, tile=None) -> bool:
     inter = gate_up.shape[0] // 2
     if tile is None and h.shape[0] <= SKINNY_ROWS:
         return _gemm_skinny(h, gate_up, out, inter, SWIGLU_BF16)
-    bn, per_sm = _tile_of(tile) if tile else _tile_width(h.shape[0], 2 * inter)
+    bn, per_sm = _tile_of(tile) if tile else _tile_width(h.shape[0], 2 * inter, SWIGLU_BF16)
     return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn, per_sm)
 
 
