@@ -19,10 +19,13 @@ build.register_module("gemm_tcgen05", ["common.cuh", "tc_common.cuh"])
 build.register_module("attention_mma", ["common.cuh"])
 build.register_module("gemm_skinny_tcgen05", ["common.cuh", "tc_common.cuh"])
 build.register_module("attention_tcgen05", ["common.cuh", "tc_common.cuh"])
+build.register_module("attention_decode_tcgen05", ["common.cuh", "tc_common.cuh"])
 
 # Portions of prompts with head size 64 run on the tcgen05 attention kernel; False sends
 # them to the mma.sync kernel instead (the tests compare the two).
 USE_TCGEN05_ATTENTION = True
+USE_TCGEN05_DECODE = True
+DECODE_TC_BLOCKS = 148      # chunks are doubled while the launch would still have this many blocks
 
 _c_int, _c_void_p = ctypes.c_int, ctypes.c_void_p
 STORE_BF16, STORE_F32, ACCUM_F32, SWIGLU_BF16 = 0, 1, 2, 3
@@ -223,6 +226,34 @@ def _attention_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads, h
     return True
 
 
+def _attention_decode_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads, head_dim,
+                              scale, window, ctx, cache, partial, counters, n_chunks,
+                              chunk_keys) -> bool:
+    """tcgen05 attention for decoded tokens (at most 16 packed rows per request and
+    KV head): head size 64, page size a power of two from 8 to 128.  Returns False
+    for anything else."""
+    pt = cache.page_tokens
+    if pt < 8 or pt > 128 or pt & (pt - 1):
+        return False
+    lib = build.load("attention_decode_tcgen05")
+    code = lib.cb_attention_decode_tcgen05(
+        _c_void_p(qkv.data_ptr()), _c_int(qkv.stride(0)), _c_void_p(out.data_ptr()),
+        _c_int(out.stride(0)), _c_void_p(k_cache.data_ptr()), _c_void_p(v_cache.data_ptr()),
+        _c_int(k_cache.shape[0]), _c_void_p(ctx.req_row_start.data_ptr()),
+        _c_void_p(ctx.req_first_pos.data_ptr()), _c_void_p(table.data_ptr()),
+        _c_int(table.shape[1]), _c_int(ctx.n_requests), _c_int(ctx.host.max_new_tokens),
+        _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim), _c_int(pt),
+        ctypes.c_float(scale), _c_int(window or 0), _c_void_p(partial.data_ptr()),
+        _c_void_p(counters.data_ptr()), _c_int(n_chunks), _c_int(chunk_keys),
+        _c_void_p(status_word(qkv.device).data_ptr()), _stream())
+    if code == _UNSUPPORTED:
+        return False
+    if code != 0:
+        raise RuntimeError(f"tcgen05 decode attention failed to launch (CUDA error {code})")
+    _count(1)
+    return True
+
+
 def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx, cache,
                     binding) -> bool:
     """Tensor-core attention over the paged cache.  Takes head sizes that are
@@ -244,10 +275,16 @@ def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx,
     # over the 148 SMs (a function of the step's shape alone, so a captured step
     # replays; contexts fill about half of their bucket on average).
     chunk_keys = 256
+    pt = cache.page_tokens
+    decode_tc = (USE_TCGEN05_DECODE and split and head_dim == 64 and out.stride(0) % 2 == 0
+                 and 8 <= pt <= 128 and pt & (pt - 1) == 0)
     if split:
+        # the tcgen05 form keeps two blocks per SM busy with far fewer instructions per
+        # key, so it wants fewer, longer chunks than the mma.sync form
+        enough = DECODE_TC_BLOCKS if decode_tc else 4 * N_SMS
         blocks_per_chunk = ctx.n_requests * n_kv_heads * (-(-host.max_new_tokens * n_rep // 16))
         while (chunk_keys * 2 <= host.context_bucket
-               and blocks_per_chunk * (host.context_bucket // (chunk_keys * 2)) >= 4 * 148):
+               and blocks_per_chunk * (host.context_bucket // (chunk_keys * 2)) >= enough):
             chunk_keys *= 2
     n_chunks = host.context_bucket // chunk_keys if split else 0
     partial = counters = None
@@ -256,6 +293,11 @@ def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx,
         partial = ctx.scratch("attn.partial", (floats,), torch.float32)
         n_counters = ctx.n_requests * n_kv_heads * (-(-host.max_new_tokens * n_rep // 16))
         counters = _buffer(qkv.device, "attn.counters", n_counters, torch.int32, zero=True)
+    if (decode_tc
+            and _attention_decode_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads,
+                                          head_dim, scale, window, ctx, cache, partial, counters,
+                                          n_chunks, chunk_keys)):
+        return True
     if (USE_TCGEN05_ATTENTION and not split and head_dim == 64
             and host.max_new_tokens * n_rep >= 64 and out.stride(0) % 8 == 0
             and _attention_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads,

@@ -419,6 +419,43 @@ def test_attention_tcgen05_matches_reference_and_mma(case):
     assert rel(out, other.float()) < 1.5e-2
 
 
+@pytest.mark.parametrize("case", [
+    # heads, kv heads, head size, page, [(context before, new tokens)], window
+    (12, 4, 64, 16, [(2047, 1), (300, 1), (0, 1), (127, 1), (128, 1)], None),
+    (8, 1, 64, 32, [(1500, 2), (40, 1)], None),              # 8 heads on one KV head: 16 packed rows
+    (6, 2, 64, 8, [(700, 3), (255, 1), (256, 5)], None),     # a few tokens per request
+    (4, 4, 64, 128, [(900, 1), (3000, 1)], 400),             # window: leading chunks take no part
+    (12, 4, 64, 16, [(5000, 1), (64, 1)], None),             # several chunks merged
+])
+def test_attention_decode_tcgen05_matches_reference_and_mma(case):
+    """Decoded tokens with head size 64: the keys on the tensor-memory lanes."""
+    from crucible_b200.ops import tensor_core
+    n_heads, n_kv, hd, page, requests, window = case
+    qkv, ctx, cache, binding, ref = _paged_case(torch.bfloat16, n_heads, n_kv, hd, page, requests,
+                                                8, window)
+    outs = {}
+    for use in (True, False):
+        try:
+            tensor_core.USE_TCGEN05_DECODE = use
+            before = tensor_core.build._loaded.get("attention_decode_tcgen05")
+            out = torch.zeros(qkv.shape[0], n_heads * hd, device=DEV, dtype=torch.bfloat16)
+            assert tensor_core.paged_attention(qkv, out, n_heads, n_kv, hd, 1 / math.sqrt(hd), window,
+                                               ctx, cache, binding)
+            torch.cuda.synchronize()
+            tensor_core.check_status(DEV)
+            outs[use] = out
+        finally:
+            tensor_core.USE_TCGEN05_DECODE = True
+    assert "attention_decode_tcgen05" in tensor_core.build._loaded
+    assert rel(outs[True].cpu(), ref) < 1.5e-2
+    assert rel(outs[True], outs[False].float()) < 1.5e-2
+    # twice in a row: the counters were left zero
+    again = torch.zeros_like(outs[True])
+    assert tensor_core.paged_attention(qkv, again, n_heads, n_kv, hd, 1 / math.sqrt(hd), window, ctx,
+                                       cache, binding)
+    assert torch.equal(again, outs[True])
+
+
 def test_attention_odd_head_size_falls_to_plain_kernel():
     from crucible_b200.ops import tensor_core
     ops = _ops()
