@@ -81,7 +81,9 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 constexpr int WARPS = 4;
 constexpr int BATCH = 8;          // blocks of 32 elements a warp keeps in flight per row
 
-template <bool NORM_IN, int EPI>
+// DEEP: K spans more than one batch of weight loads per warp; the next batch is then in
+// flight while the current one is multiplied (costs registers, so short K keeps the plain form).
+template <bool NORM_IN, int EPI, bool DEEP>
 __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallParams p) {
     cb_pdl_trigger();
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -267,7 +269,19 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
     float c[4] = {0.f, 0.f, 0.f, 0.f};
     const __nv_bfloat16* xrow = xs + (size_t)g * pitch + t * 8;
     for (int kb0 = 0; kb0 < k_blocks; kb0 += BATCH * WARPS) {
-        if (kb0 > 0) {
+        const bool more = DEEP && kb0 + BATCH * WARPS < k_blocks;    // block-uniform
+        uint4 nf[DEEP ? BATCH : 1], ns[DEEP ? BATCH : 1];
+        if (DEEP) {
+            if (more) {
+#pragma unroll
+                for (int i = 0; i < BATCH; ++i) {
+                    const int kb = kb0 + BATCH * WARPS + warp + i * WARPS;
+                    const bool in = kb < k_blocks && kb * 32 + t * 8 < K;
+                    nf[i] = in ? __ldg(reinterpret_cast<const uint4*>(wf + kb * 32)) : make_uint4(0, 0, 0, 0);
+                    ns[i] = in ? __ldg(reinterpret_cast<const uint4*>(ws + kb * 32)) : make_uint4(0, 0, 0, 0);
+                }
+            }
+        } else if (kb0 > 0) {
 #pragma unroll
             for (int i = 0; i < BATCH; ++i) {
                 const int kb = kb0 + warp + i * WARPS;
@@ -284,6 +298,13 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
                 if (kb * 32 + t * 8 < K) xb = *reinterpret_cast<const uint4*>(xrow + kb * 32);
                 mma_bf16(c, vf[i].x, vs[i].x, vf[i].y, vs[i].y, xb.x, xb.y);
                 mma_bf16(c, vf[i].z, vs[i].z, vf[i].w, vs[i].w, xb.z, xb.w);
+            }
+        }
+        if (DEEP && more) {
+#pragma unroll
+            for (int i = 0; i < BATCH; ++i) {
+                vf[i] = nf[i];
+                vs[i] = ns[i];
             }
         }
     }
@@ -335,18 +356,25 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
     }
 }
 
-template <bool NORM_IN, int EPI>
-int launch_rows(const SmallParams& p, cudaStream_t s) {
+template <bool NORM_IN, int EPI, bool DEEP>
+int launch_rows_as(const SmallParams& p, cudaStream_t s) {
     const int smem = 8 * (p.K + 32) * 2 + WARPS * 32 * 16;
     static int configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(small_linear_kernel<NORM_IN, EPI>,
+        cudaError_t e = cudaFuncSetAttribute(small_linear_kernel<NORM_IN, EPI, DEEP>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    cb_launch(small_linear_kernel<NORM_IN, EPI>, dim3(p.n_tiles), dim3(WARPS * 32), smem, s, p);
+    cb_launch(small_linear_kernel<NORM_IN, EPI, DEEP>, dim3(p.n_tiles), dim3(WARPS * 32), smem, s, p);
     return cb_last_error();
+}
+
+template <bool NORM_IN, int EPI>
+int launch_rows(const SmallParams& p, cudaStream_t s) {
+    // more than one batch of 32-element blocks per warp: keep two batches in flight
+    return p.K > BATCH * WARPS * 32 ? launch_rows_as<NORM_IN, EPI, true>(p, s)
+                                    : launch_rows_as<NORM_IN, EPI, false>(p, s);
 }
 
 bool sizes_ok(const float* x, const float* gain, const void* a, int lda, int M, int K, int ldw,

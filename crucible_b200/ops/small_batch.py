@@ -52,8 +52,10 @@ def _stream():
     return _c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _input(h: Rows):
+def _input(h: Rows, w: torch.Tensor):
     """(x, gain, eps, a, lda) for the launchers."""
+    if isinstance(h, LazyNorm) and w.numel() * 2 > NORM_FUSE_MAX_BYTES:
+        h = h.tensor()
     if isinstance(h, LazyNorm):
         if not h.x.is_contiguous():
             return None
@@ -73,8 +75,20 @@ def _done(code: int, what: str) -> bool:
     return True
 
 
+# These kernels are built for latency (a few megabytes of weights per launch).  They
+# stream at about 1.7 TB/s; the TMA-fed tensor-core kernel for few rows reaches the
+# memory's bandwidth but costs a norm kernel and a split-K reduction more, so beyond
+# this size the caller's general path is faster.
+MAX_WEIGHT_BYTES = 64 << 20
+# Every block of a product normalises the step's rows for itself.  That is free while the
+# blocks are few; with thousands of blocks it costs as much as the weights, and one norm
+# kernel for all of them is cheaper.
+NORM_FUSE_MAX_BYTES = 8 << 20
+
+
 def _weights_ok(w: torch.Tensor, rows: int) -> bool:
-    return (rows <= MAX_ROWS and w.dtype == torch.bfloat16 and w.is_cuda and w.stride(1) == 1)
+    return (rows <= MAX_ROWS and w.dtype == torch.bfloat16 and w.is_cuda and w.stride(1) == 1
+            and w.numel() * 2 <= MAX_WEIGHT_BYTES)
 
 
 MAX_OUT_ROWS = 8192     # wider products (the LM head) stream better through the tensor-core kernel
@@ -84,7 +98,7 @@ def linear(h: Rows, w: torch.Tensor, out: torch.Tensor, *, accumulate: bool = Fa
     if (not _weights_ok(w, h.shape[0]) or out.dtype != torch.float32 or out.stride(1) != 1
             or w.shape[0] > MAX_OUT_ROWS):
         return False
-    inp = _input(h)
+    inp = _input(h, w)
     if inp is None:
         return False
     x, gain, eps, a, lda = inp
@@ -99,7 +113,7 @@ def linear_swiglu(h: Rows, gate_up: torch.Tensor, out: torch.Tensor) -> bool:
     if (not _weights_ok(gate_up, h.shape[0]) or out.dtype != torch.bfloat16
             or out.stride(1) != 1):
         return False
-    inp = _input(h)
+    inp = _input(h, gate_up)
     if inp is None:
         return False
     x, gain, eps, a, lda = inp
@@ -116,7 +130,7 @@ def qkv_rope_append(h: Rows, wqkv: torch.Tensor, qkv: torch.Tensor, n_heads: int
     if (not _weights_ok(wqkv, h.shape[0]) or qkv.dtype != torch.bfloat16 or cos is None
             or rotary_dim != head_dim):
         return False
-    inp = _input(h)
+    inp = _input(h, wqkv)
     if inp is None:
         return False
     x, gain, eps, a, lda = inp

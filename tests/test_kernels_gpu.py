@@ -171,7 +171,7 @@ def test_linear_swiglu_few_rows(m, inter, k, splits):
 
 
 @pytest.mark.parametrize("m", [1, 2, 3, 8])
-@pytest.mark.parametrize("n,k", [(768, 768), (100, 2048), (33, 40), (1280, 1032)])
+@pytest.mark.parametrize("n,k", [(768, 768), (100, 2048), (33, 40), (1280, 1032), (64, 4104)])
 def test_small_batch_linear_and_swiglu(m, n, k):
     """The fused kernels for a few rows: bf16 input or fp32 rows normalised on the fly."""
     from crucible_b200.ops import small_batch
@@ -200,6 +200,33 @@ def test_small_batch_linear_and_swiglu(m, n, k):
     odd = torch.randn(m, 12, device=DEV).bfloat16()
     assert small_batch.linear(odd, torch.randn(n, 12, device=DEV).bfloat16(),
                               torch.empty(m, n, device=DEV)) is False             # K not a multiple of 8
+
+
+def test_small_batch_large_weights_take_other_paths():
+    """Beyond a few megabytes the norm is run once instead of in every block; beyond
+    tens of megabytes the kernels refuse and the caller's tensor-core kernel streams."""
+    from crucible_b200.ops import small_batch
+    ops = _ops()
+    m, n, k = 5, 2560, 2048                                    # 10.5 MB
+    assert n * k * 2 > small_batch.NORM_FUSE_MAX_BYTES
+    w = (torch.randn(n, k, device=DEV) * 0.05).bfloat16()
+    x = torch.randn(m, k, device=DEV) * 2
+    gain = 1 + 0.2 * torch.randn(k, device=DEV)
+    ran = []
+
+    def materialize():
+        ran.append(1)
+        out = torch.empty(m, k, device=DEV, dtype=torch.bfloat16)
+        ops.rmsnorm(x, gain, 1e-5, out)
+        return out
+    lazy = small_batch.LazyNorm(x, gain, 1e-5, materialize)
+    out = torch.empty(m, n, device=DEV)
+    assert small_batch.linear(lazy, w, out)
+    assert ran == [1]
+    normed = x.double() * torch.rsqrt(x.double().pow(2).mean(-1, keepdim=True) + 1e-5) * gain.double()
+    assert rel(out, normed @ w.double().T) < 5e-3
+    huge = torch.empty(small_batch.MAX_WEIGHT_BYTES // (2 * k) + 8, k, device=DEV, dtype=torch.bfloat16)
+    assert small_batch.linear(lazy, huge, torch.empty(m, huge.shape[0], device=DEV)) is False
 
 
 @pytest.mark.parametrize("write", [True, False])
