@@ -10,7 +10,8 @@
 //            exponentials per thread - and writes P (bf16) to shared memory
 //   O[16 rows, 64] += P V_tile               tcgen05.mma, M = 128 (rows 16.. unused), N = 64, K = 128
 //
-// K and V pages come in by TMA, one box per page, in a ring of three stages.  A
+// K and V pages come in by TMA in a ring of three stages: one box per page, or one
+// box for a whole tile when its pages follow one another in the pool.  A
 // block takes the up to 16 (token, head of the group) rows of one request and
 // one KV head against ONE chunk of keys and writes an unnormalised partial
 // (vector, maximum, sum); the last block of a row group to arrive (an atomic
@@ -64,6 +65,8 @@ struct DecodeParams {
     float* partial;          // [rows_total * n_heads][n_chunks][HD + 2]
     int* counters;           // [n_requests * n_kv_heads], zero between launches
     int n_chunks, chunk_keys;
+    int n_pages;             // of the pool
+    int runs;                // 1: the 4-D maps may be used for tiles whose pages are consecutive
     int* status;
 };
 
@@ -152,7 +155,9 @@ __device__ __forceinline__ void merge_row(const DecodeParams& p, int tok, int he
 template <int RMAX>
 __global__ void __launch_bounds__(192, 2)
 attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
-                                const __grid_constant__ CUtensorMap map_v, const DecodeParams p) {
+                                const __grid_constant__ CUtensorMap map_v,
+                                const __grid_constant__ CUtensorMap run_k,
+                                const __grid_constant__ CUtensorMap run_v, const DecodeParams p) {
     cb_pdl_trigger();
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     Storage& s = *reinterpret_cast<Storage*>(smem_raw);
@@ -195,6 +200,10 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&map_k);
         tc::prefetch_tensormap(&map_v);
+        if (p.runs) {
+            tc::prefetch_tensormap(&run_k);
+            tc::prefetch_tensormap(&run_v);
+        }
     }
     if (warp == 1) {
         tc::tmem_alloc(&s.tmem_base, 128);        // S^T: columns 0..15 and 16..31, O: 64..127
@@ -204,7 +213,7 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
 
     // ---- the loader's thread: one tile of K and V pages into a stage -----------------------
     const int pages_per_tile = KEYS >> p.page_shift;
-    auto lookup = [&](int j, int (&rows_y)[16]) {
+    auto lookup = [&](int j, int (&pages)[16]) {
         // the tile's table entries, all in flight at once: the copies are ordered against
         // memory and would take the lookups one by one
         const int key0 = tile0 + j * KEYS;
@@ -212,25 +221,35 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         for (int i = 0; i < 16; ++i) {
             int index = (key0 >> p.page_shift) + (i < pages_per_tile ? i : 0);
             index = index < p.table_stride ? index : p.table_stride - 1;
-            int page = table[index];
-            page = page < 0 ? 0 : page;               // an entry given back early: never read
-            rows_y[i] = (page * p.n_kv_heads + kv_head) << p.page_shift;
+            const int page = table[index];
+            pages[i] = page < 0 ? 0 : page;           // an entry given back early: never read
         }
     };
-    auto issue = [&](int j, const int (&rows_y)[16]) -> bool {
+    auto issue = [&](int j, const int (&pages)[16]) -> bool {
         const int st = j % STAGES;
         const uint32_t round = j / STAGES;
+        // pages that follow one another in the pool come in with one copy per tile
+        bool run = p.runs != 0 && pages[0] + pages_per_tile <= p.n_pages;
+#pragma unroll
+        for (int i = 1; i < 16; ++i)
+            if (i < pages_per_tile && pages[i] != pages[0] + i) run = false;
         if (round > 0 && !tc::mbar_wait(&s.kv_empty[st], (round - 1) & 1, abort_flag)) {
             tc::give_up(abort_flag, p.status, tc::ST_PRODUCER_TIMEOUT);
             return false;
         }
         tc::mbar_expect_tx(&s.kv_full[st], 2 * KEYS * HD * 2);
+        if (run) {
+            tc::tma_load_4d(s.k[st], &run_k, &s.kv_full[st], 0, 0, kv_head, pages[0]);
+            tc::tma_load_4d(s.v[st], &run_v, &s.kv_full[st], 0, 0, kv_head, pages[0]);
+            return true;
+        }
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             if (i < pages_per_tile) {
                 const int dst = (i << p.page_shift) * HD * 2;
-                tc::tma_load_2d(s.k[st] + dst, &map_k, &s.kv_full[st], 0, rows_y[i]);
-                tc::tma_load_2d(s.v[st] + dst, &map_v, &s.kv_full[st], 0, rows_y[i]);
+                const int y = (pages[i] * p.n_kv_heads + kv_head) << p.page_shift;
+                tc::tma_load_2d(s.k[st] + dst, &map_k, &s.kv_full[st], 0, y);
+                tc::tma_load_2d(s.v[st] + dst, &map_v, &s.kv_full[st], 0, y);
             }
         }
         return true;
@@ -543,7 +562,15 @@ CB_EXPORT int cb_attention_decode_tcgen05(const void* qkv, int qkv_stride, void*
     const uint64_t rows = (uint64_t)n_pages * n_kv_heads * page_tokens;
     if (!tc::make_map_2d(&mk, k_cache, rows, HD, HD, page_tokens)) return CB_ERR_UNSUPPORTED;
     if (!tc::make_map_2d(&mv, v_cache, rows, HD, HD, page_tokens)) return CB_ERR_UNSUPPORTED;
+    // tiles of several pages: a second pair of maps that takes a run of pages at once
+    CUtensorMap rk = mk, rv = mv;
+    const int pages_per_tile = KEYS / page_tokens;
+    const bool runs = pages_per_tile > 1 &&
+                      tc::make_map_pages(&rk, k_cache, n_pages, n_kv_heads, page_tokens, pages_per_tile) &&
+                      tc::make_map_pages(&rv, v_cache, n_pages, n_kv_heads, page_tokens, pages_per_tile);
     DecodeParams p;
+    p.n_pages = n_pages;
+    p.runs = runs ? 1 : 0;
     p.qkv = (const __nv_bfloat16*)qkv;
     p.qkv_stride = qkv_stride;
     p.out = (__nv_bfloat16*)out;
@@ -580,8 +607,8 @@ CB_EXPORT int cb_attention_decode_tcgen05(const void* qkv, int qkv_stride, void*
     const int most_rows = max_new_tokens * (n_heads / n_kv_heads);
     const dim3 grid(n_chunks * n_kv_heads * n_requests);
     cudaStream_t st = (cudaStream_t)stream;
-    if (most_rows <= 4) cb_launch(attention_decode_tcgen05_kernel<4>, grid, dim3(192), smem, st, mk, mv, p);
-    else if (most_rows <= 8) cb_launch(attention_decode_tcgen05_kernel<8>, grid, dim3(192), smem, st, mk, mv, p);
-    else cb_launch(attention_decode_tcgen05_kernel<16>, grid, dim3(192), smem, st, mk, mv, p);
+    if (most_rows <= 4) cb_launch(attention_decode_tcgen05_kernel<4>, grid, dim3(192), smem, st, mk, mv, rk, rv, p);
+    else if (most_rows <= 8) cb_launch(attention_decode_tcgen05_kernel<8>, grid, dim3(192), smem, st, mk, mv, rk, rv, p);
+    else cb_launch(attention_decode_tcgen05_kernel<16>, grid, dim3(192), smem, st, mk, mv, rk, rv, p);
     return cb_last_error();
 }

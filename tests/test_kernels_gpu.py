@@ -293,7 +293,8 @@ def test_linear_refuses_what_tma_cannot_read():
 # attention over a paged cache
 # ---------------------------------------------------------------------------
 
-def _paged_case(dtype, n_heads, n_kv, hd, page_tokens, requests, seed, window=None, peak=True):
+def _paged_case(dtype, n_heads, n_kv, hd, page_tokens, requests, seed, window=None, peak=True,
+                shuffle=True):
     """requests: list of (context_before, new_tokens).  Builds random q, k, v for
     whole sequences, scatters k/v of the context into shuffled pages, and returns
     what the kernels need plus the reference output for the new rows."""
@@ -301,7 +302,10 @@ def _paged_case(dtype, n_heads, n_kv, hd, page_tokens, requests, seed, window=No
     rng = random.Random(seed)
     total_pages = sum(-(-(c + n) // page_tokens) for c, n in requests) + 3
     order = list(range(total_pages))
-    rng.shuffle(order)
+    if shuffle:
+        rng.shuffle(order)
+    else:
+        order.reverse()              # pages are handed out in ascending order: runs of pages
     kv = torch.full((1, 2, total_pages, n_kv, page_tokens, hd), float("nan"))   # poison
     stride = max(-(-(c + n) // page_tokens) for c, n in requests) + 2
     tables = torch.zeros(len(requests), stride, dtype=torch.int32)
@@ -454,12 +458,14 @@ def test_attention_tcgen05_matches_reference_and_mma(case):
     (4, 4, 64, 128, [(900, 1), (3000, 1)], 400),             # window: leading chunks take no part
     (12, 4, 64, 16, [(5000, 1), (64, 1)], None),             # several chunks merged
 ])
-def test_attention_decode_tcgen05_matches_reference_and_mma(case):
-    """Decoded tokens with head size 64: the keys on the tensor-memory lanes."""
+@pytest.mark.parametrize("shuffle", [True, False])
+def test_attention_decode_tcgen05_matches_reference_and_mma(case, shuffle):
+    """Decoded tokens with head size 64: the keys on the tensor-memory lanes.  With
+    pages in ascending order a tile's pages come in with one copy."""
     from crucible_b200.ops import tensor_core
     n_heads, n_kv, hd, page, requests, window = case
     qkv, ctx, cache, binding, ref = _paged_case(torch.bfloat16, n_heads, n_kv, hd, page, requests,
-                                                8, window)
+                                                8, window, shuffle=shuffle)
     outs = {}
     for use in (True, False):
         try:
