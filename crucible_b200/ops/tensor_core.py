@@ -162,7 +162,9 @@ def _gemm_skinny(a, w, out, n, epi, splits=None) -> bool:
     return True
 
 
-SKINNY_ROWS = 32     # products with at most this many rows run with W on the MMA's M side
+SKINNY_ROWS = 32     # products with at most this many rows run with W on the MMA's M side ...
+SKINNY_MIN_BYTES = 16 << 20   # ... if W is at least this large (it streams; smaller ones are
+                              # latency-bound and the 128-row tiles are quicker to start and end)
 SKINNY_WIDE_N = 8192 # ... and up to 64 rows if W has at least this many rows (the LM head)
 
 
@@ -184,7 +186,7 @@ def linear(a, w, out, *, accumulate=False, tile=None) -> bool:
         epi = ACCUM_F32 if accumulate else STORE_F32
     else:
         return False
-    if tile is None and (a.shape[0] <= SKINNY_ROWS
+    if tile is None and ((a.shape[0] <= SKINNY_ROWS and w.numel() * 2 >= SKINNY_MIN_BYTES)
                          or (a.shape[0] <= 64 and w.shape[0] >= SKINNY_WIDE_N)):
         return _gemm_skinny(a, w, out, w.shape[0], epi)
     bn, per_sm = _tile_of(tile) if tile else _tile_width(a.shape[0], w.shape[0], epi)
@@ -195,7 +197,7 @@ def linear_swiglu(h, gate_up, out, tile=None) -> bool:
     if not _operands_ok(h, gate_up) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
         return False
     inter = gate_up.shape[0] // 2
-    if tile is None and h.shape[0] <= SKINNY_ROWS:
+    if tile is None and h.shape[0] <= SKINNY_ROWS and gate_up.numel() * 2 >= SKINNY_MIN_BYTES:
         return _gemm_skinny(h, gate_up, out, inter, SWIGLU_BF16)
     bn, per_sm = _tile_of(tile) if tile else _tile_width(h.shape[0], 2 * inter, SWIGLU_BF16)
     return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn, per_sm)
