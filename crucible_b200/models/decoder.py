@@ -153,14 +153,25 @@ class DecoderModel:
 
     @property
     def graph_safe(self) -> bool:
-        return all(getattr(part, "graph_safe", True) for _, part, _ in self._parts())
+        return self._graph_flags()[0]
 
     @property
     def graph_safe_prompt_steps(self) -> bool:
-        def ok(part):
-            flag = getattr(part, "graph_safe_prompt_steps", None)
-            return getattr(part, "graph_safe", True) if flag is None else flag
-        return all(ok(part) for _, part, _ in self._parts())
+        return self._graph_flags()[1]
+
+    def _graph_flags(self):
+        """(decode steps may be captured, steps with prompt portions may be captured): what
+        the parts say about themselves, asked once."""
+        flags = self.__dict__.get("_graph_flags_cache")
+        if flags is None:
+            def prompt_ok(part):
+                flag = getattr(part, "graph_safe_prompt_steps", None)
+                return getattr(part, "graph_safe", True) if flag is None else flag
+            parts = [part for _, part, _ in self._parts()]
+            flags = (all(getattr(part, "graph_safe", True) for part in parts),
+                     all(prompt_ok(part) for part in parts))
+            self._graph_flags_cache = flags
+        return flags
 
     # -- one step -------------------------------------------------------------
 
