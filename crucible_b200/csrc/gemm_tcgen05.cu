@@ -28,7 +28,22 @@ constexpr int BM = 128;
 constexpr int BK = 64;                 // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 
-enum Epilogue { STORE_BF16 = 0, STORE_F32 = 1, ACCUM_F32 = 2, SWIGLU_BF16 = 3 };
+enum Epilogue { STORE_BF16 = 0, STORE_F32 = 1, ACCUM_F32 = 2, SWIGLU_BF16 = 3, ROPE_APPEND = 4 };
+
+// ROPE_APPEND: W = [Wq; Wk; Wv]; a tile covers whole heads.  The q heads are rotated
+// and stored (bf16) to C[M, ldc]; the k heads are rotated and the v heads copied into
+// the rows' cache pages [page][kv_head][slot][head_dim].
+struct RopeArgs {
+    const float* cos_t;           // [positions][head_dim / 2]
+    const float* sin_t;
+    const int* positions;         // per row
+    const int* row_request;
+    const int* block_table;
+    int table_stride;
+    __nv_bfloat16* k_cache;
+    __nv_bfloat16* v_cache;
+    int n_heads, n_kv_heads, head_dim, page_tokens, write_cache;
+};
 
 template <int BN, int STAGES>
 struct SharedStorage {
@@ -37,6 +52,7 @@ struct SharedStorage {
     alignas(8) uint64_t full_bar[STAGES];
     uint64_t empty_bar[STAGES];
     uint64_t tmem_full_bar;
+    long row_base[BM];          // ROPE_APPEND: a row's first element in a cache page / head_dim, or -1
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -47,7 +63,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_c, int tma_out,
                     void* __restrict__ c_ptr, int M, int N, int K, int ldc, int inter,
-                    int* __restrict__ status) {
+                    int* __restrict__ status, const RopeArgs ra) {
     cb_pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     using Storage = SharedStorage<BN, STAGES>;
@@ -164,13 +180,130 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                       (size_t)row * ldc + col) + (q & 7));
             }
         }
+        // ROPE_APPEND: the row's position and its place in the cache pages, asked for while
+        // the products run; every epilogue thread publishes its row's place
+        int row_pos = 0;
+        if (EPI == ROPE_APPEND) {
+            long base = -1;
+            if (row < M) {
+                row_pos = ra.positions[row];
+                if (ra.write_cache) {
+                    const int page = ra.block_table[(size_t)ra.row_request[row] * ra.table_stride +
+                                                    row_pos / ra.page_tokens];
+                    base = (long)page * ra.n_kv_heads * ra.page_tokens + row_pos % ra.page_tokens;
+                }
+            }
+            s.row_base[quarter * 32 + lane] = base;
+        }
+        // ... and for head size 64 its 32 rotation factors, kept in registers for every head
+        float4 cs_reg[8], sn_reg[8];
+        if (EPI == ROPE_APPEND) {
+            if (ra.head_dim == 64) {
+                const float4* cp = reinterpret_cast<const float4*>(ra.cos_t + (size_t)row_pos * 32);
+                const float4* sp = reinterpret_cast<const float4*>(ra.sin_t + (size_t)row_pos * 32);
+#pragma unroll
+                for (int q4 = 0; q4 < 8; ++q4) {
+                    cs_reg[q4] = __ldg(cp + q4);
+                    sn_reg[q4] = __ldg(sp + q4);
+                }
+            }
+        }
         bool ok = tc::mbar_wait(&s.tmem_full_bar, 0, abort_flag);
         if (!ok && !*abort_flag) tc::give_up(abort_flag, status, tc::ST_EPILOGUE_TIMEOUT);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             tc::tc_fence_after_sync();
             const uint32_t lane_addr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
-            if (tma_out) {
+            if (EPI == ROPE_APPEND) {
+                // A thread owns one token's row of the tile: whole heads of head_dim columns,
+                // taken in pairs of 32-column chunks (j, j + head_dim / 2), rotated in
+                // registers and staged in shared memory as [128 rows][128 bytes] per 64
+                // columns (the ring of stages is free by now).  A q head then leaves by TMA;
+                // a k or v head is copied to the rows' cache pages by all threads, a row's
+                // 128 bytes as eight 16-byte pieces of neighbouring lanes.
+                const int hd = ra.head_dim, half = hd >> 1;
+                const int r = quarter * 32 + lane;
+                const int heads_all = ra.n_heads + 2 * ra.n_kv_heads;
+                const int chunks = hd >> 6;                         // 64-column chunks per head
+                uint8_t* ring = s.a[0];
+                const float* cs_row = ra.cos_t + (size_t)row_pos * half;
+                const float* sn_row = ra.sin_t + (size_t)row_pos * half;
+#pragma unroll 1
+                for (int hc = 0; hc < BN; hc += hd) {
+                    const int head = (n_tile * BN + hc) / hd;
+                    if (head >= heads_all) break;
+                    const bool is_q = head < ra.n_heads, is_k = !is_q && head < ra.n_heads + ra.n_kv_heads;
+                    uint8_t* buf = ring + (hc >> 6) * (BM * 128);
+#pragma unroll 1
+                    for (int c = 0; c < half; c += 32) {
+                        uint32_t lo[32], hi[32];
+                        tc::tmem_ld_32x32(lane_addr + hc + c, lo);
+                        tc::tmem_ld_32x32(lane_addr + hc + half + c, hi);
+                        tc::tmem_ld_wait();
+                        if (is_q || is_k) {
+#pragma unroll
+                            for (int q4 = 0; q4 < 8; ++q4) {
+                                const float4 cs = hd == 64 ? cs_reg[q4]
+                                                           : __ldg(reinterpret_cast<const float4*>(cs_row + c) + q4);
+                                const float4 sn = hd == 64 ? sn_reg[q4]
+                                                           : __ldg(reinterpret_cast<const float4*>(sn_row + c) + q4);
+                                const float cc[4] = {cs.x, cs.y, cs.z, cs.w};
+                                const float ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const float x1 = __uint_as_float(lo[4 * q4 + i]);
+                                    const float x2 = __uint_as_float(hi[4 * q4 + i]);
+                                    lo[4 * q4 + i] = __float_as_uint(x1 * cc[i] - x2 * ss[i]);
+                                    hi[4 * q4 + i] = __float_as_uint(x1 * ss[i] + x2 * cc[i]);
+                                }
+                            }
+                        }
+                        // columns c.. and half + c.. of the head: which 64-column chunk, which pieces
+                        uint8_t* lo_row = buf + (c >> 6) * (BM * 128) + r * 128;
+                        uint8_t* hi_row = buf + ((half + c) >> 6) * (BM * 128) + r * 128;
+                        const int lo_piece = (c & 63) >> 3, hi_piece = ((half + c) & 63) >> 3;
+#pragma unroll
+                        for (int q8 = 0; q8 < 4; ++q8) {
+                            uint32_t pl[4], ph[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(lo[q8 * 8 + 2 * j]),
+                                                                          __uint_as_float(lo[q8 * 8 + 2 * j + 1]));
+                                __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(hi[q8 * 8 + 2 * j]),
+                                                                          __uint_as_float(hi[q8 * 8 + 2 * j + 1]));
+                                pl[j] = *reinterpret_cast<uint32_t*>(&a2);
+                                ph[j] = *reinterpret_cast<uint32_t*>(&b2);
+                            }
+                            *reinterpret_cast<uint4*>(lo_row + (((lo_piece + q8) ^ (r & 7)) << 4)) =
+                                make_uint4(pl[0], pl[1], pl[2], pl[3]);
+                            *reinterpret_cast<uint4*>(hi_row + (((hi_piece + q8) ^ (r & 7)) << 4)) =
+                                make_uint4(ph[0], ph[1], ph[2], ph[3]);
+                        }
+                    }
+                    tc::fence_proxy_async();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (is_q) {
+                        if (warp == 2 && lane == 0) {
+                            for (int ch = 0; ch < chunks; ++ch)
+                                tc::tma_store_2d(&map_c, buf + ch * (BM * 128), head * hd + ch * 64, m0);
+                            tc::tma_store_commit();
+                        }
+                    } else if (ra.write_cache) {
+                        const int kvh = is_k ? head - ra.n_heads : head - ra.n_heads - ra.n_kv_heads;
+                        __nv_bfloat16* cache = is_k ? ra.k_cache : ra.v_cache;
+                        for (int i = r; i < BM * 8 * chunks; i += 128) {
+                            const int ch = i / (BM * 8), rr = (i >> 3) & (BM - 1), piece = i & 7;
+                            const long base = s.row_base[rr];
+                            if (base < 0) continue;
+                            const uint4 v = *reinterpret_cast<const uint4*>(
+                                buf + ch * (BM * 128) + rr * 128 + ((piece ^ (rr & 7)) << 4));
+                            *reinterpret_cast<uint4*>(cache + ((size_t)base + (size_t)kvh * ra.page_tokens) * hd +
+                                                      ch * 64 + piece * 8) = v;
+                        }
+                    }
+                }
+                if (warp == 2 && lane == 0) tc::tma_store_wait_all();
+            } else if (tma_out) {
                 // Through shared memory and out by TMA: the ring of stages is free by now.
                 // Chunks of [128 rows][128 bytes] in the 128-byte swizzle; a thread writes
                 // its row's eight 16-byte pieces, then one thread sends the box: a store, or
@@ -365,7 +498,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 
 template <int BN, int STAGES, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, int K, int ldc,
-           int inter, int* status, cudaStream_t stream) {
+           int inter, int* status, cudaStream_t stream, const RopeArgs& ra = RopeArgs{}) {
     // the output goes through shared memory and TMA where its rows allow it
     const bool f32 = EPI == STORE_F32 || EPI == ACCUM_F32;
     const int esize = f32 ? 4 : 2;
@@ -373,8 +506,11 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, 
     int tma_out = ((uintptr_t)C & 15) == 0 && ((size_t)ldc * esize) % 16 == 0 &&
                   (f32 || (EPI == SWIGLU_BF16 ? BN % 128 == 0 : BN % 64 == 0));
     CUtensorMap mc = ma;
-    if (tma_out && !tc::make_out_map_2d(&mc, C, f32, (uint64_t)M, (uint64_t)out_cols, (uint64_t)ldc, BM))
+    // ROPE_APPEND: only the q heads' columns of C are written
+    const uint64_t map_cols = EPI == ROPE_APPEND ? (uint64_t)ra.n_heads * ra.head_dim : (uint64_t)out_cols;
+    if (tma_out && !tc::make_out_map_2d(&mc, C, f32, (uint64_t)M, map_cols, (uint64_t)ldc, BM))
         tma_out = 0;
+    if (EPI == ROPE_APPEND && !tma_out) return CB_ERR_UNSUPPORTED;
     using Storage = SharedStorage<BN, STAGES>;
     const int smem = (int)sizeof(Storage) + 1024;
     static bool configured = false;
@@ -387,7 +523,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, 
     const int n_cols = EPI == SWIGLU_BF16 ? 2 * inter : N;
     dim3 grid((n_cols + BN - 1) / BN, (M + BM - 1) / BM);
     cb_launch(gemm_tcgen05_kernel<BN, STAGES, EPI>, dim3(grid), dim3(192), smem, stream, ma, mw, mc, tma_out,
-              C, M, N, K, ldc, inter, status);
+              C, M, N, K, ldc, inter, status, ra);
     return cb_last_error();
 }
 
@@ -439,6 +575,42 @@ CB_EXPORT int cb_gemm_tcgen05(const void* A, const void* W, void* C, int M, int 
         case 160: return launch_epi<160, 5>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
         case 192: return launch_epi<192, 5>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
         case 256: return launch_epi<256, 4>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
+    }
+    return CB_ERR_UNSUPPORTED;
+}
+
+// The query/key/value projection with the rotation of q and k and the write of k and v
+// into the rows' cache pages in the epilogue.  W = [Wq; Wk; Wv] ([(Hq + 2 Hkv) * head_dim, K]);
+// rotated q goes to q_out[M, ldq] (bf16).  The whole head is rotated (pairs j, j + head_dim / 2);
+// head_dim is a multiple of 64 and divides the tile width bn.
+CB_EXPORT int cb_gemm_tcgen05_rope(const void* A, const void* W, void* q_out, int M, int K, int lda,
+                                   int ldw, int ldq, int bn, const float* cos_t, const float* sin_t,
+                                   const int* positions, const int* row_request,
+                                   const int* block_table, int table_stride, void* k_cache,
+                                   void* v_cache, int n_heads, int n_kv_heads, int head_dim,
+                                   int page_tokens, int write_cache, int* status, void* stream) {
+    if (M <= 0) return 0;
+    if (K <= 0 || (K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) ||
+        head_dim <= 0 || (head_dim & 63) || bn % head_dim != 0 || (ldq & 7) || ((uintptr_t)q_out & 15) ||
+        ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)cos_t & 15) ||
+        ((uintptr_t)sin_t & 15))
+        return CB_ERR_UNSUPPORTED;
+    const int N = (n_heads + 2 * n_kv_heads) * head_dim;
+    CUtensorMap ma, mw;
+    if (!tc::make_map_2d(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM)) return CB_ERR_UNSUPPORTED;
+    if (!tc::make_map_2d(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, bn)) return CB_ERR_UNSUPPORTED;
+    RopeArgs ra;
+    ra.cos_t = cos_t; ra.sin_t = sin_t; ra.positions = positions; ra.row_request = row_request;
+    ra.block_table = block_table; ra.table_stride = table_stride;
+    ra.k_cache = (__nv_bfloat16*)k_cache; ra.v_cache = (__nv_bfloat16*)v_cache;
+    ra.n_heads = n_heads; ra.n_kv_heads = n_kv_heads; ra.head_dim = head_dim;
+    ra.page_tokens = page_tokens; ra.write_cache = write_cache;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (bn) {
+        case 64: return launch<64, 6, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, status, s, ra);
+        case 128: return launch<128, 5, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, status, s, ra);
+        case 192: return launch<192, 5, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, status, s, ra);
+        case 256: return launch<256, 4, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, status, s, ra);
     }
     return CB_ERR_UNSUPPORTED;
 }

@@ -176,13 +176,20 @@ def linear_swiglu(h, gate_up: torch.Tensor, out: torch.Tensor, ctx) -> None:
 def qkv_rope_append(h, wqkv: torch.Tensor, qkv: torch.Tensor, n_heads: int, n_kv_heads: int,
                     head_dim: int, cos, sin, rotary_dim: int, ctx, cache, binding) -> None:
     """The query/key/value projection, the rotation of q and k, and the write of
-    k and v into the cache pages: one kernel for a few rows, two otherwise.
-    Leaves the rotated q in the first columns of `qkv`."""
+    k and v into the cache pages: one kernel for a few rows (mma.sync) and for many
+    (tcgen05, rotation and cache write in the epilogue), two otherwise.  Leaves the
+    rotated q in the first columns of `qkv`; the k and v columns of `qkv` are not
+    defined afterwards (attention reads keys and values from the cache)."""
     from . import small_batch
     if (wqkv.dtype == torch.bfloat16 and h.shape[0] <= small_batch.MAX_ROWS
             and small_batch.qkv_rope_append(h, wqkv, qkv, n_heads, n_kv_heads, head_dim, cos, sin,
                                             rotary_dim, ctx, cache, binding)):
         return
+    if wqkv.dtype == torch.bfloat16 and h.shape[0] > small_batch.MAX_ROWS:
+        from . import tensor_core
+        if tensor_core.linear_rope_append(small_batch.as_tensor(h), wqkv, qkv, n_heads, n_kv_heads,
+                                          head_dim, cos, sin, rotary_dim, ctx, cache, binding):
+            return
     linear(h, wqkv, qkv)
     rope_kv_append(qkv, n_heads, n_kv_heads, head_dim, cos, sin, rotary_dim, ctx, cache, binding)
 

@@ -28,7 +28,7 @@ USE_TCGEN05_DECODE = True
 DECODE_TC_BLOCKS = 148      # chunks are doubled while the launch would still have this many blocks
 
 _c_int, _c_void_p = ctypes.c_int, ctypes.c_void_p
-STORE_BF16, STORE_F32, ACCUM_F32, SWIGLU_BF16 = 0, 1, 2, 3
+STORE_BF16, STORE_F32, ACCUM_F32, SWIGLU_BF16, ROPE_APPEND = 0, 1, 2, 3, 4
 _UNSUPPORTED = 100001
 
 _status = {}
@@ -77,7 +77,7 @@ def _tile_of(tile):
     return (tile, 1) if isinstance(tile, int) else tuple(tile)
 
 
-def _tile_width(m: int, n_cols: int, epi: int = 1):
+def _tile_width(m: int, n_cols: int, epi: int = 1, multiple_of: int = 1):
     """Tile width in output columns: the one that needs the least time if every
     block costs (width + a fixed part) and blocks run in waves over the SMs.  A
     wide tile reuses the A tile more; a narrow one fills the last wave better.
@@ -86,6 +86,8 @@ def _tile_width(m: int, n_cols: int, epi: int = 1):
     m_tiles = -(-m // 128)
     best, best_cost = 64, None
     for bn in TILE_WIDTHS:
+        if bn % multiple_of:
+            continue
         blocks = m_tiles * -(-n_cols // bn)
         direct = (epi == STORE_BF16 and bn % 64) or (epi == SWIGLU_BF16 and bn % 128)
         cost = -(-blocks // N_SMS) * (bn + 48 + (40 if direct else 0))
@@ -201,6 +203,40 @@ def linear_swiglu(h, gate_up, out, tile=None) -> bool:
         return _gemm_skinny(h, gate_up, out, inter, SWIGLU_BF16)
     bn, per_sm = _tile_of(tile) if tile else _tile_width(h.shape[0], 2 * inter, SWIGLU_BF16)
     return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn, per_sm)
+
+
+def linear_rope_append(h, wqkv, qkv, n_heads, n_kv_heads, head_dim, cos, sin, rotary_dim, ctx, cache,
+                       binding) -> bool:
+    """The q/k/v projection with the rotation and the cache write in the product's
+    epilogue (whole head rotated, head size a multiple of 64).  Rotated q lands in the
+    first columns of `qkv`; k and v only in the cache.  False: not taken."""
+    if (not _operands_ok(h, wqkv) or qkv.dtype != torch.bfloat16 or qkv.stride(1) != 1
+            or cos is None or rotary_dim != head_dim or head_dim % 64 or head_dim > 256
+            or h.shape[0] <= SKINNY_ROWS):
+        return False
+    k_cache, v_cache = cache.keys(binding.slot), cache.values(binding.slot)
+    if k_cache.dtype != torch.bfloat16:
+        return False
+    table = ctx.block_table(binding.group)
+    bn, _ = _tile_width(h.shape[0], wqkv.shape[0], ROPE_APPEND, multiple_of=head_dim)
+    if bn % head_dim:
+        return False
+    lib = build.load("gemm_tcgen05")
+    code = lib.cb_gemm_tcgen05_rope(
+        _c_void_p(h.data_ptr()), _c_void_p(wqkv.data_ptr()), _c_void_p(qkv.data_ptr()),
+        _c_int(h.shape[0]), _c_int(h.shape[1]), _c_int(h.stride(0)), _c_int(wqkv.stride(0)),
+        _c_int(qkv.stride(0)), _c_int(bn), _c_void_p(cos.data_ptr()), _c_void_p(sin.data_ptr()),
+        _c_void_p(ctx.positions.data_ptr()), _c_void_p(ctx.row_request.data_ptr()),
+        _c_void_p(table.data_ptr()), _c_int(table.shape[1]), _c_void_p(k_cache.data_ptr()),
+        _c_void_p(v_cache.data_ptr()), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
+        _c_int(cache.page_tokens), _c_int(1 if binding.write else 0),
+        _c_void_p(status_word(h.device).data_ptr()), _stream())
+    if code == _UNSUPPORTED:
+        return False
+    if code != 0:
+        raise RuntimeError(f"tensor-core q/k/v product failed to launch (CUDA error {code})")
+    _count(1)
+    return True
 
 
 def _attention_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads, head_dim, scale,

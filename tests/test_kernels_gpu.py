@@ -229,6 +229,70 @@ def test_small_batch_large_weights_take_other_paths():
     assert small_batch.linear(lazy, huge, torch.empty(m, huge.shape[0], device=DEV)) is False
 
 
+@pytest.mark.parametrize("hd,n_heads,n_kv,rows", [(64, 6, 2, 300), (64, 5, 1, 40), (128, 3, 1, 150)])
+@pytest.mark.parametrize("write", [True, False])
+def test_linear_rope_append_tensor_core(hd, n_heads, n_kv, rows, write):
+    """The q/k/v product for many rows with rotation and cache write in its epilogue."""
+    from crucible_b200.ops import tensor_core
+    d, page = 256, 16
+    torch.manual_seed(rows)
+    n_req = 3
+    # rows of three requests, each at its own positions; pages shuffled
+    per = [rows // 3, rows // 3, rows - 2 * (rows // 3)]
+    starts = [7, 0, 33]
+    positions, row_request = [], []
+    for r in range(n_req):
+        positions += list(range(starts[r], starts[r] + per[r]))
+        row_request += [r] * per[r]
+    pages_per = [-(-(starts[r] + per[r]) // page) for r in range(n_req)]
+    ids = list(range(sum(pages_per) + 2))
+    random.Random(1).shuffle(ids)
+    tables = torch.zeros(n_req, max(pages_per) + 1, dtype=torch.int32)
+    for r in range(n_req):
+        for i in range(pages_per[r]):
+            tables[r, i] = ids.pop()
+    tables = tables.to(DEV)
+    h = torch.randn(rows, d, device=DEV).bfloat16()
+    w = (torch.randn((n_heads + 2 * n_kv) * hd, d, device=DEV) * 0.2).bfloat16()
+    i = torch.arange(hd // 2, dtype=torch.float64)
+    ang = torch.outer(torch.arange(max(positions) + 1, dtype=torch.float64), 10000.0 ** (-2 * i / hd))
+    cos, sin = ang.cos().float().to(DEV), ang.sin().float().to(DEV)
+    n_pages = sum(pages_per) + 2
+    kv = torch.zeros(1, 2, n_pages, n_kv, page, hd, dtype=torch.bfloat16, device=DEV)
+
+    class Cache:
+        page_tokens = page
+        keys = staticmethod(lambda slot: kv[slot, 0])
+        values = staticmethod(lambda slot: kv[slot, 1])
+    ctx = SimpleNamespace(positions=torch.tensor(positions, dtype=torch.int32, device=DEV),
+                          row_request=torch.tensor(row_request, dtype=torch.int32, device=DEV),
+                          block_table=lambda g: tables)
+    qkv = torch.zeros(rows, w.shape[0], device=DEV, dtype=torch.bfloat16)
+    assert tensor_core.linear_rope_append(h, w, qkv, n_heads, n_kv, hd, cos, sin, hd, ctx, Cache,
+                                          SimpleNamespace(group=0, slot=0, write=write))
+    torch.cuda.synchronize()
+    tensor_core.check_status(DEV)
+    y = (h.double() @ w.double().T).cpu().view(rows, n_heads + 2 * n_kv, hd)
+    pos_t = torch.tensor(positions)
+    c, s = ang[pos_t].cos()[:, None, :], ang[pos_t].sin()[:, None, :]
+
+    def rotate(v):
+        x1, x2 = v[..., :hd // 2], v[..., hd // 2:]
+        return torch.cat([x1 * c - x2 * s, x1 * s + x2 * c], dim=-1)
+    assert rel(qkv[:, :n_heads * hd].view(rows, n_heads, hd), rotate(y[:, :n_heads])) < 6e-3
+    page_of = tables.cpu()[torch.tensor(row_request), pos_t // page].long()
+    got_k = kv[0, 0].cpu()[page_of, :, pos_t % page]
+    got_v = kv[0, 1].cpu()[page_of, :, pos_t % page]
+    if write:
+        assert rel(got_k, rotate(y[:, n_heads:n_heads + n_kv])) < 6e-3
+        assert rel(got_v, y[:, n_heads + n_kv:]) < 6e-3
+        written = torch.zeros(n_pages, page, dtype=torch.bool)
+        written[page_of, pos_t % page] = True
+        assert kv[0, 0].cpu().float().abs().sum(dim=(1, 3))[~written].sum() == 0     # nothing else touched
+    else:
+        assert kv.abs().sum() == 0
+
+
 @pytest.mark.parametrize("write", [True, False])
 def test_small_batch_qkv_rope_append(write):
     from crucible_b200.ops import small_batch
