@@ -100,12 +100,82 @@ __global__ void rmsnorm_vec4_kernel(const float* __restrict__ x, const float* __
     }
 }
 
+// One warp per row (widths up to 32 * 4 * V floats): the row stays in registers between
+// the two passes, no block barrier, several rows per block; the result leaves in 8- or
+// 16-byte stores.  For many rows this keeps far more bytes in flight than a block per row.
+template <typename T, int V>
+__global__ void __launch_bounds__(128) rmsnorm_warp_kernel(const float* __restrict__ x,
+                                                           const float* __restrict__ gain,
+                                                           T* __restrict__ out, int n_rows, int width,
+                                                           float eps) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const int n4 = width >> 2;
+    const float4* row = reinterpret_cast<const float4*>(x + (size_t)r * width);
+    const float4* g4 = reinterpret_cast<const float4*>(gain);
+    float4 v[V];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        const int i = lane + 32 * j;
+        v[j] = i < n4 ? row[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        ss = fmaf(v[j].x, v[j].x, ss);
+        ss = fmaf(v[j].y, v[j].y, ss);
+        ss = fmaf(v[j].z, v[j].z, ss);
+        ss = fmaf(v[j].w, v[j].w, ss);
+    }
+    ss = cb_warp_sum(ss);
+    const float rs = 1.0f / sqrtf(ss / (float)width + eps);
+    T* dst = out + (size_t)r * width;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        const int i = lane + 32 * j;
+        if (i < n4) {
+            const float4 g = __ldg(g4 + i);
+            const float y0 = v[j].x * rs * g.x, y1 = v[j].y * rs * g.y;
+            const float y2 = v[j].z * rs * g.z, y3 = v[j].w * rs * g.w;
+            if (sizeof(T) == 2) {
+                __nv_bfloat162 a = __floats2bfloat162_rn(y0, y1), b = __floats2bfloat162_rn(y2, y3);
+                uint2 w;
+                w.x = *reinterpret_cast<uint32_t*>(&a);
+                w.y = *reinterpret_cast<uint32_t*>(&b);
+                reinterpret_cast<uint2*>(dst)[i] = w;
+            } else {
+                reinterpret_cast<float4*>(dst)[i] = make_float4(y0, y1, y2, y3);
+            }
+        }
+    }
+}
+
+template <typename T>
+static void launch_rmsnorm_warp(const float* x, const float* gain, T* out, int n_rows, int width,
+                                float eps, cudaStream_t s) {
+    const int blocks = (n_rows + 3) / 4;
+    if ((width >> 2) <= 32 * 8)
+        cb_launch(rmsnorm_warp_kernel<T, 8>, dim3(blocks), dim3(128), 0, s, x, gain, out, n_rows, width, eps);
+    else
+        cb_launch(rmsnorm_warp_kernel<T, 32>, dim3(blocks), dim3(128), 0, s, x, gain, out, n_rows, width, eps);
+}
+
 CB_EXPORT int cb_rmsnorm(const float* x, const float* gain, void* out, int out_dtype,
                          int n_rows, int width, float eps, void* stream) {
     if (n_rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const bool vec = (width & 3) == 0 && width <= 4 * 4 * 1024 && ((uintptr_t)x & 15) == 0 &&
                      ((uintptr_t)gain & 15) == 0;
+    // many rows: a warp per row; the output's rows must allow the vector stores
+    const bool out_vec = out_dtype == CB_F32 ? ((uintptr_t)out & 15) == 0 : ((uintptr_t)out & 7) == 0;
+    if (vec && out_vec && n_rows >= 64 && (width >> 2) <= 32 * 32) {
+        if (out_dtype == CB_F32) launch_rmsnorm_warp<float>(x, gain, (float*)out, n_rows, width, eps, s);
+        else launch_rmsnorm_warp<__nv_bfloat16>(x, gain, (__nv_bfloat16*)out, n_rows, width, eps, s);
+        return cb_last_error();
+    }
     if (vec) {
         int threads = ((width >> 2) + 31) / 32 * 32;
         if (threads > 1024) threads = ((width >> 2) + 4 * 32 - 1) / (4 * 32) * 32;

@@ -38,12 +38,13 @@ def test_embed_rows(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width,eps", [(72, 1e-5), (1000, 1e-6), (4100, 1e-3)])
-def test_rmsnorm(dtype, width, eps):
+@pytest.mark.parametrize("width,eps", [(72, 1e-5), (1000, 1e-6), (4100, 1e-3), (768, 1e-5), (4096, 1e-6)])
+@pytest.mark.parametrize("rows", [9, 203])                 # few rows: a block per row; many: a warp per row
+def test_rmsnorm(dtype, width, eps, rows):
     ops = _ops()
-    x = torch.randn(9, width, device=DEV) * 3.0
+    x = torch.randn(rows, width, device=DEV) * 3.0
     gain = 1.0 + 0.2 * torch.randn(width, device=DEV)
-    out = torch.empty(9, width, device=DEV, dtype=dtype)
+    out = torch.empty(rows, width, device=DEV, dtype=dtype)
     ops.rmsnorm(x, gain, eps, out)
     ref = x.double() * torch.rsqrt(x.double().pow(2).mean(-1, keepdim=True) + eps) * gain.double()
     assert rel(out, ref) < (2e-6 if dtype == torch.float32 else 5e-3)
