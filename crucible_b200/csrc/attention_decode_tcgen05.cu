@@ -1,14 +1,14 @@
 // Paged attention for decoded tokens (a few query rows per request, many keys)
-// on the 5th-generation tensor cores, head size 64, bfloat16.  Such a step only
+// on the 5th-generation tensor cores, head size 64 or 128, bfloat16.  Such a step only
 // has to read the keys and values once; what the mma.sync kernel spends per key
 // in instructions keeps it at a third of the memory bandwidth.  Here the KEYS sit
 // on the tensor-memory lanes:
 //
-//   S^T[128 keys, 16 rows] = K_tile Q^T      tcgen05.mma, M = 128 keys, N = 16, K = 64
+//   S^T[128 keys, 16 rows] = K_tile Q^T      tcgen05.mma, M = 128 keys, N = 16, K = head size
 //   softmax: one thread per key reads its row of S^T from tensor memory and
 //            computes p for the block's (at most 16) query rows - a handful of
 //            exponentials per thread - and writes P (bf16) to shared memory
-//   O[16 rows, 64] += P V_tile               tcgen05.mma, M = 128 (rows 16.. unused), N = 64, K = 128
+//   O[16 rows, hd] += P V_tile               tcgen05.mma, M = 128 (rows 16.. unused), N = 64 per half of hd, K = 128
 //
 // K and V pages come in by TMA in a ring of three stages: one box per page, or one
 // box for a whole tile when its pages follow one another in the pool.  A
@@ -33,7 +33,7 @@
 // are the softmax (128 threads = 128 keys).  Every wait on an mbarrier is bounded;
 // the softmax warps' block barriers are passed by all of them whatever happened.
 //
-// Sizes: head size 64; page size a power of two from 8 to 128; at most 16 packed
+// Sizes: head size 64 or 128; page size a power of two from 8 to 128; at most 16 packed
 // rows per request and KV head; chunk a multiple of 128 keys.  Anything else is
 // refused and the mma.sync kernel runs.
 // Reference counterparts: `attention_decode_paged_f32` (engine/kernels/kernels.cu:1741)
@@ -43,7 +43,6 @@
 
 namespace {
 
-constexpr int HD = 64;
 constexpr int KEYS = 128;            // keys per tile = tensor-memory lanes of S^T
 constexpr int ROWS = 16;             // query rows per block (N of the first MMA)
 constexpr int STAGES = 3;            // the loader's first copies are written out for three
@@ -62,7 +61,7 @@ struct DecodeParams {
     int n_heads, n_kv_heads, n_requests, page_shift;
     float scale_log2;
     int window;
-    float* partial;          // [rows_total * n_heads][n_chunks][HD + 2]
+    float* partial;          // [rows_total * n_heads][n_chunks][head size + 2]
     int* counters;           // [n_requests * n_kv_heads], zero between launches
     int n_chunks, chunk_keys;
     int n_pages;             // of the pool
@@ -70,11 +69,14 @@ struct DecodeParams {
     int* status;
 };
 
+// HD: the head size, 64 or 128.  Operands whose contracted or free dimension is the head
+// size lie in shared memory as HD / 64 halves of [rows][128 bytes] (one swizzle atom wide).
+template <int HD>
 struct Storage {
-    alignas(1024) uint8_t q[ROWS * HD * 2];          // [16 rows][128 B], swizzled
-    alignas(1024) uint8_t p[2][2][ROWS * 64 * 2];    // P: two buffers of two halves of 64 keys
-    alignas(1024) uint8_t k[STAGES][KEYS * HD * 2];  // directly after P (see above)
-    alignas(1024) uint8_t v[STAGES][KEYS * HD * 2];
+    alignas(1024) uint8_t q[HD / 64][ROWS * 64 * 2];         // [16 rows][128 B] per half, swizzled
+    alignas(1024) uint8_t p[2][2][ROWS * 64 * 2];            // P: two buffers of two halves of 64 keys
+    alignas(1024) uint8_t k[STAGES][HD / 64][KEYS * 64 * 2]; // directly after P (see above)
+    alignas(1024) uint8_t v[STAGES][HD / 64][KEYS * 64 * 2];
     alignas(8) uint64_t kv_full[STAGES];
     uint64_t kv_empty[STAGES];
     uint64_t s_full[2], p_full[2], pv_done[2];
@@ -115,24 +117,32 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // Merges one row's chunks (ascending, with a running maximum) and writes its
-// output.  One warp; lanes own features 2 * lane, 2 * lane + 1.
+// output.  One warp; a lane owns HD / 32 neighbouring features.
+template <int HD>
 __device__ __forceinline__ void merge_row(const DecodeParams& p, int tok, int head, int pos, int lane) {
     const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     constexpr int MP = HD + 2;
+    constexpr int F = HD / 32;
     const int c_first = lo / p.chunk_keys, c_last = pos / p.chunk_keys;
     const float* base = p.partial + ((size_t)tok * p.n_heads + head) * p.n_chunks * MP;
-    float m = -INFINITY, l = 0.f, a0 = 0.f, a1 = 0.f;
+    float m = -INFINITY, l = 0.f, acc[F];
+#pragma unroll
+    for (int f = 0; f < F; ++f) acc[f] = 0.f;
     for (int c0 = c_first; c0 <= c_last; c0 += 8) {
-        float mc[8], lc[8], o0[8], o1[8];
+        float mc[8], lc[8], o[8][F];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const bool in = c0 + j <= c_last;
             const float* src = base + (size_t)(in ? c0 + j : c_first) * MP;
             mc[j] = in ? __ldcg(src + HD) : -INFINITY;
             lc[j] = in ? __ldcg(src + HD + 1) : 0.f;
-            const float2 o = in ? __ldcg(reinterpret_cast<const float2*>(src) + lane) : make_float2(0.f, 0.f);
-            o0[j] = o.x;
-            o1[j] = o.y;
+#pragma unroll
+            for (int f = 0; f < F; f += 2) {
+                const float2 v = in ? __ldcg(reinterpret_cast<const float2*>(src + lane * F + f))
+                                    : make_float2(0.f, 0.f);
+                o[j][f] = v.x;
+                o[j][f + 1] = v.y;
+            }
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {                    // ascending chunks
@@ -140,27 +150,32 @@ __device__ __forceinline__ void merge_row(const DecodeParams& p, int tok, int he
             const float off = m_new == -INFINITY ? 0.f : m_new;
             const float keep = exp2f(m - off), take = exp2f(mc[j] - off);
             l = l * keep + lc[j] * take;
-            a0 = a0 * keep + o0[j] * take;
-            a1 = a1 * keep + o1[j] * take;
+#pragma unroll
+            for (int f = 0; f < F; ++f) acc[f] = acc[f] * keep + o[j][f] * take;
             m = m_new;
         }
     }
     const float inv = l > 0.f ? 1.0f / l : 0.f;
-    __nv_bfloat162 v = __floats2bfloat162_rn(a0 * inv, a1 * inv);
-    *reinterpret_cast<__nv_bfloat162*>(p.out + (size_t)tok * p.out_stride + (size_t)head * HD + 2 * lane) = v;
+    __nv_bfloat16* dst = p.out + (size_t)tok * p.out_stride + (size_t)head * HD + lane * F;
+#pragma unroll
+    for (int f = 0; f < F; f += 2)
+        *reinterpret_cast<__nv_bfloat162*>(dst + f) = __floats2bfloat162_rn(acc[f] * inv, acc[f + 1] * inv);
 }
 
 // RMAX: the most packed rows a block of this instantiation takes (4, 8 or 16): the
 // softmax's per-row loops are unrolled that far and no further.
-template <int RMAX>
-__global__ void __launch_bounds__(192, 2)
+template <int HD, int RMAX>
+__global__ void __launch_bounds__(192, HD == 64 ? 2 : 1)
 attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                                 const __grid_constant__ CUtensorMap map_v,
                                 const __grid_constant__ CUtensorMap run_k,
                                 const __grid_constant__ CUtensorMap run_v, const DecodeParams p) {
     cb_pdl_trigger();
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    Storage& s = *reinterpret_cast<Storage*>(smem_raw);
+    using Store = Storage<HD>;
+    constexpr int NH = HD / 64;                       // halves of the head size
+    constexpr uint32_t TMEM_COLS = HD == 64 ? 128 : 256;
+    Store& s = *reinterpret_cast<Store*>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int chunk = blockIdx.x % p.n_chunks;
     const int grp = blockIdx.x / p.n_chunks;
@@ -206,7 +221,7 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         }
     }
     if (warp == 1) {
-        tc::tmem_alloc(&s.tmem_base, 128);        // S^T: columns 0..15 and 16..31, O: 64..127
+        tc::tmem_alloc(&s.tmem_base, TMEM_COLS);  // S^T: columns 0..15 and 16..31, O: from 64
         tc::tmem_relinquish();
     }
     cb_pdl_wait();
@@ -239,17 +254,23 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         }
         tc::mbar_expect_tx(&s.kv_full[st], 2 * KEYS * HD * 2);
         if (run) {
-            tc::tma_load_4d(s.k[st], &run_k, &s.kv_full[st], 0, 0, kv_head, pages[0]);
-            tc::tma_load_4d(s.v[st], &run_v, &s.kv_full[st], 0, 0, kv_head, pages[0]);
+#pragma unroll
+            for (int h = 0; h < NH; ++h) {
+                tc::tma_load_4d(s.k[st][h], &run_k, &s.kv_full[st], h * 64, 0, kv_head, pages[0]);
+                tc::tma_load_4d(s.v[st][h], &run_v, &s.kv_full[st], h * 64, 0, kv_head, pages[0]);
+            }
             return true;
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             if (i < pages_per_tile) {
-                const int dst = (i << p.page_shift) * HD * 2;
+                const int dst = (i << p.page_shift) * 128;
                 const int y = (pages[i] * p.n_kv_heads + kv_head) << p.page_shift;
-                tc::tma_load_2d(s.k[st] + dst, &map_k, &s.kv_full[st], 0, y);
-                tc::tma_load_2d(s.v[st] + dst, &map_v, &s.kv_full[st], 0, y);
+#pragma unroll
+                for (int h = 0; h < NH; ++h) {
+                    tc::tma_load_2d(s.k[st][h] + dst, &map_k, &s.kv_full[st], h * 64, y);
+                    tc::tma_load_2d(s.v[st][h] + dst, &map_v, &s.kv_full[st], h * 64, y);
+                }
             }
         }
         return true;
@@ -271,15 +292,15 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         }
     } else {
         const int tid = threadIdx.x - 32;
-        if (tid < ROWS * 8) {
-            const int r = tid >> 3, c = tid & 7;
+        for (int i = tid; i < ROWS * 8 * NH; i += 160) {
+            const int r = i / (8 * NH), c = i % (8 * NH);        // row, 16-byte piece of the row
             uint4 val = make_uint4(0, 0, 0, 0);
             if (r < n_rows) {
                 const int tok = row_base + r / n_rep, head = kv_head * n_rep + r % n_rep;
                 val = *reinterpret_cast<const uint4*>(p.qkv + (size_t)tok * p.qkv_stride +
                                                       (size_t)head * HD + c * 8);
             }
-            *reinterpret_cast<uint4*>(s.q + r * 128 + ((c ^ (r & 7)) << 4)) = val;
+            *reinterpret_cast<uint4*>(s.q[c >> 3] + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = val;
         }
         for (int i = tid; i < (int)sizeof(s.p) / 16; i += 160)
             reinterpret_cast<uint4*>(&s.p[0][0][0])[i] = make_uint4(0, 0, 0, 0);
@@ -317,8 +338,7 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         // ---- MMA issuer -------------------------------------------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc_qk = tc::instr_desc_bf16(KEYS, ROWS);
-            constexpr uint32_t idesc_pv = tc::instr_desc_bf16_b_mn(128, HD);
-            const uint64_t q_desc = tc::smem_desc_sw128(tc::smem_u32(s.q));
+            constexpr uint32_t idesc_pv = tc::instr_desc_bf16_b_mn(128, 64);
             bool ok = true;
             // S^T_j = K_j Q^T into buffer j & 1: K = 64 in four steps of 16
             // `block`: wait for the tile; else only take it if it has landed (true: issued)
@@ -330,11 +350,12 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                     return false;
                 }
                 tc::tc_fence_after_sync();
-                const uint64_t k_desc = tc::smem_desc_sw128(tc::smem_u32(s.k[st]));
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k)
-                    tc::umma_bf16(tmem_s + (j & 1) * 16, k_desc + 2 * k, q_desc + 2 * k, idesc_qk,
-                                  k > 0 ? 1u : 0u);
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint64_t k_desc = tc::smem_desc_sw128(tc::smem_u32(s.k[st][k >> 2])) + 2 * (k & 3);
+                    const uint64_t q_desc = tc::smem_desc_sw128(tc::smem_u32(s.q[k >> 2])) + 2 * (k & 3);
+                    tc::umma_bf16(tmem_s + (j & 1) * 16, k_desc, q_desc, idesc_qk, k > 0 ? 1u : 0u);
+                }
                 tc::umma_commit(&s.s_full[j & 1]);
                 return true;
             };
@@ -350,13 +371,16 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                 }
                 tc::tc_fence_after_sync();
                 const int st = j % STAGES;
-                const uint64_t v_desc = tc::smem_desc_sw128(tc::smem_u32(s.v[st]));
 #pragma unroll
-                for (int k = 0; k < KEYS / 16; ++k) {
-                    const uint64_t p_desc =
-                        tc::smem_desc_sw128(tc::smem_u32(s.p[j & 1][k >> 2])) + 2 * (k & 3);
-                    tc::umma_bf16(tmem_o, p_desc, v_desc + 128 * k, idesc_pv,
-                                  (j > 0 || k > 0) ? 1u : 0u);
+                for (int h = 0; h < NH; ++h) {                       // 64 output features at a time
+                    const uint64_t v_desc = tc::smem_desc_sw128(tc::smem_u32(s.v[st][h]));
+#pragma unroll
+                    for (int k = 0; k < KEYS / 16; ++k) {
+                        const uint64_t p_desc =
+                            tc::smem_desc_sw128(tc::smem_u32(s.p[j & 1][k >> 2])) + 2 * (k & 3);
+                        tc::umma_bf16(tmem_o + h * 64, p_desc, v_desc + 128 * k, idesc_pv,
+                                      (j > 0 || k > 0) ? 1u : 0u);
+                    }
                 }
                 tc::umma_commit(&s.kv_empty[st]);
                 tc::umma_commit(&s.pv_done[j & 1]);
@@ -516,7 +540,7 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     __syncthreads();
     if (warp == 1) {
         tc::tc_fence_after_sync();
-        tc::tmem_dealloc(s.tmem_base, 128);
+        tc::tmem_dealloc(s.tmem_base, TMEM_COLS);
     }
     if (n_active == 1 || *abort_flag) return;
     // ---- the last block to arrive for these rows merges their chunks ------------------------
@@ -531,15 +555,30 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     __threadfence();
     for (int r = warp; r < n_rows; r += 6) {
         const int tok = row_base + r / n_rep, head = kv_head * n_rep + r % n_rep;
-        merge_row(p, tok, head, first_pos + r / n_rep, lane);
+        merge_row<HD>(p, tok, head, first_pos + r / n_rep, lane);
     }
+}
+
+template <int HD, int RMAX>
+int launch_as(dim3 grid, cudaStream_t st, const CUtensorMap& mk, const CUtensorMap& mv,
+              const CUtensorMap& rk, const CUtensorMap& rv, const DecodeParams& p) {
+    const int smem = (int)sizeof(Storage<HD>);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_tcgen05_kernel<HD, RMAX>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cb_launch(attention_decode_tcgen05_kernel<HD, RMAX>, grid, dim3(192), smem, st, mk, mv, rk, rv, p);
+    return cb_last_error();
 }
 
 }  // namespace
 
 // Attention for a step whose requests bring at most 16 (token, head of a group)
-// rows each.  k_cache / v_cache: [n_pages][n_kv_heads][page_tokens][64] bf16.
-// partial: n_tokens * n_heads * n_chunks * 66 floats; counters: n_requests *
+// rows each.  k_cache / v_cache: [n_pages][n_kv_heads][page_tokens][head_dim] bf16.
+// partial: n_tokens * n_heads * n_chunks * (head_dim + 2) floats; counters: n_requests *
 // n_kv_heads ints, zero before the first launch (the kernel leaves them zero).
 CB_EXPORT int cb_attention_decode_tcgen05(const void* qkv, int qkv_stride, void* out, int out_stride,
                                           const void* k_cache, const void* v_cache, int n_pages,
@@ -550,7 +589,7 @@ CB_EXPORT int cb_attention_decode_tcgen05(const void* qkv, int qkv_stride, void*
                                           float* partial, int* counters, int n_chunks,
                                           int chunk_keys, int* status, void* stream) {
     if (n_requests <= 0 || max_new_tokens <= 0) return 0;
-    if (head_dim != HD || n_heads % n_kv_heads != 0 || page_tokens < 8 || page_tokens > KEYS ||
+    if ((head_dim != 64 && head_dim != 128) || n_heads % n_kv_heads != 0 || page_tokens < 8 || page_tokens > KEYS ||
         (page_tokens & (page_tokens - 1)) || (qkv_stride & 7) || (out_stride & 1) ||
         ((uintptr_t)qkv & 15) || ((uintptr_t)out & 3) || ((uintptr_t)k_cache & 15) ||
         ((uintptr_t)v_cache & 15) || max_new_tokens * (n_heads / n_kv_heads) > ROWS ||
@@ -560,14 +599,14 @@ CB_EXPORT int cb_attention_decode_tcgen05(const void* qkv, int qkv_stride, void*
     while ((1 << shift) < page_tokens) ++shift;
     CUtensorMap mk, mv;
     const uint64_t rows = (uint64_t)n_pages * n_kv_heads * page_tokens;
-    if (!tc::make_map_2d(&mk, k_cache, rows, HD, HD, page_tokens)) return CB_ERR_UNSUPPORTED;
-    if (!tc::make_map_2d(&mv, v_cache, rows, HD, HD, page_tokens)) return CB_ERR_UNSUPPORTED;
+    if (!tc::make_map_2d(&mk, k_cache, rows, head_dim, head_dim, page_tokens)) return CB_ERR_UNSUPPORTED;
+    if (!tc::make_map_2d(&mv, v_cache, rows, head_dim, head_dim, page_tokens)) return CB_ERR_UNSUPPORTED;
     // tiles of several pages: a second pair of maps that takes a run of pages at once
     CUtensorMap rk = mk, rv = mv;
     const int pages_per_tile = KEYS / page_tokens;
     const bool runs = pages_per_tile > 1 &&
-                      tc::make_map_pages(&rk, k_cache, n_pages, n_kv_heads, page_tokens, pages_per_tile) &&
-                      tc::make_map_pages(&rv, v_cache, n_pages, n_kv_heads, page_tokens, pages_per_tile);
+                      tc::make_map_pages(&rk, k_cache, n_pages, n_kv_heads, page_tokens, head_dim, pages_per_tile) &&
+                      tc::make_map_pages(&rv, v_cache, n_pages, n_kv_heads, page_tokens, head_dim, pages_per_tile);
     DecodeParams p;
     p.n_pages = n_pages;
     p.runs = runs ? 1 : 0;
@@ -590,25 +629,15 @@ CB_EXPORT int cb_attention_decode_tcgen05(const void* qkv, int qkv_stride, void*
     p.n_chunks = n_chunks;
     p.chunk_keys = chunk_keys;
     p.status = status;
-    const int smem = (int)sizeof(Storage);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_tcgen05_kernel<4>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(attention_decode_tcgen05_kernel<8>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(attention_decode_tcgen05_kernel<16>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
     const int most_rows = max_new_tokens * (n_heads / n_kv_heads);
     const dim3 grid(n_chunks * n_kv_heads * n_requests);
     cudaStream_t st = (cudaStream_t)stream;
-    if (most_rows <= 4) cb_launch(attention_decode_tcgen05_kernel<4>, grid, dim3(192), smem, st, mk, mv, rk, rv, p);
-    else if (most_rows <= 8) cb_launch(attention_decode_tcgen05_kernel<8>, grid, dim3(192), smem, st, mk, mv, rk, rv, p);
-    else cb_launch(attention_decode_tcgen05_kernel<16>, grid, dim3(192), smem, st, mk, mv, rk, rv, p);
-    return cb_last_error();
+    if (head_dim == 64) {
+        if (most_rows <= 4) return launch_as<64, 4>(grid, st, mk, mv, rk, rv, p);
+        if (most_rows <= 8) return launch_as<64, 8>(grid, st, mk, mv, rk, rv, p);
+        return launch_as<64, 16>(grid, st, mk, mv, rk, rv, p);
+    }
+    if (most_rows <= 4) return launch_as<128, 4>(grid, st, mk, mv, rk, rv, p);
+    if (most_rows <= 8) return launch_as<128, 8>(grid, st, mk, mv, rk, rv, p);
+    return launch_as<128, 16>(grid, st, mk, mv, rk, rv, p);
 }

@@ -281,15 +281,15 @@ inline bool make_map_2d(CUtensorMap* out, const void* base, uint64_t rows, uint6
     return true;
 }
 
-// K or V pages [n_pages][n_kv_heads][page_tokens][64] bf16 as a 4-D tensor, read in boxes of
-// `box_pages` consecutive pages of one KV head (128-byte swizzle): a tile of keys whose pages
+// K or V pages [n_pages][n_kv_heads][page_tokens][head_dim] bf16 as a 4-D tensor, read in boxes
+// of 64 features of `box_pages` consecutive pages of one KV head (128-byte swizzle): a tile of keys whose pages
 // follow one another in the pool comes in with one copy instead of one per page.
 inline bool make_map_pages(CUtensorMap* out, const void* base, uint64_t n_pages, uint64_t n_kv_heads,
-                           uint32_t page_tokens, uint32_t box_pages) {
-    typedef std::tuple<const void*, uint64_t, uint64_t, uint32_t, uint32_t> Key;
+                           uint32_t page_tokens, uint32_t head_dim, uint32_t box_pages) {
+    typedef std::tuple<const void*, uint64_t, uint64_t, uint32_t, uint32_t, uint32_t> Key;
     static std::map<Key, CUtensorMap> cache;
     static std::mutex mu;
-    Key key(base, n_pages, n_kv_heads, page_tokens, box_pages);
+    Key key(base, n_pages, n_kv_heads, page_tokens, head_dim, box_pages);
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
     if (it != cache.end()) {
@@ -298,8 +298,9 @@ inline bool make_map_pages(CUtensorMap* out, const void* base, uint64_t n_pages,
     }
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
-    cuuint64_t dims[4] = {64, page_tokens, n_kv_heads, n_pages};
-    cuuint64_t strides[3] = {128, (cuuint64_t)page_tokens * 128, n_kv_heads * page_tokens * 128};
+    const cuuint64_t row = (cuuint64_t)head_dim * 2;          // bytes of one token's features
+    cuuint64_t dims[4] = {head_dim, page_tokens, n_kv_heads, n_pages};
+    cuuint64_t strides[3] = {row, page_tokens * row, n_kv_heads * page_tokens * row};
     cuuint32_t box[4] = {64, page_tokens, 1, box_pages};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides,

@@ -314,7 +314,7 @@ def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx,
     # replays; contexts fill about half of their bucket on average).
     chunk_keys = 256
     pt = cache.page_tokens
-    decode_tc = (USE_TCGEN05_DECODE and split and head_dim == 64 and out.stride(0) % 2 == 0
+    decode_tc = (USE_TCGEN05_DECODE and split and head_dim in (64, 128) and out.stride(0) % 2 == 0
                  and 8 <= pt <= 128 and pt & (pt - 1) == 0)
     if split:
         # the tcgen05 form keeps two blocks per SM busy with far fewer instructions per

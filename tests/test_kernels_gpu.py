@@ -522,6 +522,8 @@ def test_attention_tcgen05_matches_reference_and_mma(case):
     (6, 2, 64, 8, [(700, 3), (255, 1), (256, 5)], None),     # a few tokens per request
     (4, 4, 64, 128, [(900, 1), (3000, 1)], 400),             # window: leading chunks take no part
     (12, 4, 64, 16, [(5000, 1), (64, 1)], None),             # several chunks merged
+    (8, 2, 128, 16, [(2047, 1), (300, 2), (0, 1)], None),    # head size 128
+    (4, 4, 128, 64, [(700, 1), (1500, 1)], 512),
 ])
 @pytest.mark.parametrize("shuffle", [True, False])
 def test_attention_decode_tcgen05_matches_reference_and_mma(case, shuffle):
