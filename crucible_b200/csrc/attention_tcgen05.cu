@@ -1,5 +1,5 @@
 // Paged causal attention for portions of prompts on the 5th-generation tensor
-// cores (head size 64, bfloat16): S = Q K^T and O += P V are tcgen05.mma with
+// cores (head size 64 or 128, bfloat16): S = Q K^T and O += P V are tcgen05.mma with
 // the scores and the output accumulator in tensor memory; K and V pages come in
 // by TMA; the softmax runs on four warps, one thread per query row, reading S
 // from tensor memory and writing P (bf16) to shared memory for the second MMA.
@@ -19,7 +19,7 @@
 // sum uses the same reference, and the final division makes the result the
 // exact softmax-weighted mean whatever the reference was.
 //
-// Sizes: head size 64 exactly; page size a power of two from 8 to 128; any head
+// Sizes: head size 64 or 128; page size a power of two from 8 to 128; any head
 // counts and group sizes; window.  Anything else is refused and the mma.sync
 // kernel runs.  Every wait is bounded (tc_common.cuh).
 // Reference counterpart: `attention_prefill_exact_*`
@@ -29,10 +29,8 @@
 
 namespace {
 
-constexpr int HD = 64;
 constexpr int ROWS = 128;            // query rows per block = tensor-memory lanes
 constexpr int KEYS = 128;            // keys per tile
-constexpr int STAGES = 3;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RAISE = 8.0f;        // raise the reference maximum when exceeded by 2^8
 
@@ -51,11 +49,18 @@ struct TcAttnParams {
     int* status;
 };
 
+// HD: the head size, 64 or 128.  Operands whose contracted or free dimension is the head
+// size lie in shared memory as HD / 64 halves of [rows][128 bytes] (one swizzle atom wide).
+// Head size 64: three K/V stages and two P buffers; 128: two stages and one P buffer (what
+// 227 KB hold), so the softmax of a tile then waits for the second MMA of the tile before.
+template <int HD>
 struct Storage {
-    alignas(1024) uint8_t q[ROWS * HD * 2];
-    alignas(1024) uint8_t k[STAGES][KEYS * HD * 2];
-    alignas(1024) uint8_t v[STAGES][KEYS * HD * 2];
-    alignas(1024) uint8_t p[2][2][ROWS * 64 * 2];   // P: two buffers of two halves of 64 keys
+    static constexpr int STAGES = HD == 64 ? 3 : 2;
+    static constexpr int PB = HD == 64 ? 2 : 1;
+    alignas(1024) uint8_t q[HD / 64][ROWS * 64 * 2];
+    alignas(1024) uint8_t k[STAGES][HD / 64][KEYS * 64 * 2];
+    alignas(1024) uint8_t v[STAGES][HD / 64][KEYS * 64 * 2];
+    alignas(1024) uint8_t p[PB][2][ROWS * 64 * 2];  // P: buffers of two halves of 64 keys
     alignas(8) uint64_t kv_full[STAGES];
     uint64_t kv_empty[STAGES];
     uint64_t s_full[2], p_full[2], pv_done[2];
@@ -96,13 +101,16 @@ __device__ __forceinline__ void fma_pair(float& x0, float& x1, float a, float b)
         : "f"(a), "f"(b));
 }
 
+template <int HD>
 __global__ void __launch_bounds__(192)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const TcAttnParams p) {
     cb_pdl_trigger();
     // 1024-byte alignment (the swizzled tiles need it) is asked of the declaration
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    Storage& s = *reinterpret_cast<Storage*>(smem_raw);
+    using Store = Storage<HD>;
+    constexpr int STAGES = Store::STAGES, PB = Store::PB, NH = HD / 64;
+    Store& s = *reinterpret_cast<Store*>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // one index over (tile rank, request, head) with the tile rank slowest: blocks start in
     // order of weight over the whole launch, the longest rows first
@@ -127,7 +135,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         tc::prefetch_tensormap(&map_v);
     }
     if (warp == 1) {
-        tc::tmem_alloc(&s.tmem_base, 512);            // S: columns 0..127 and 128..255, O: 256..319
+        tc::tmem_alloc(&s.tmem_base, 512);            // S: columns 0..127 and 128..255, O: from 256
         tc::tmem_relinquish();
     }
     cb_pdl_wait();
@@ -176,9 +184,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             if (i < pages_per_tile) {
-                const int dst = (i << p.page_shift) * HD * 2;
-                tc::tma_load_2d(s.k[st] + dst, &map_k, &s.kv_full[st], 0, rows_y[i]);
-                tc::tma_load_2d(s.v[st] + dst, &map_v, &s.kv_full[st], 0, rows_y[i]);
+                const int dst = (i << p.page_shift) * 128;
+#pragma unroll
+                for (int h = 0; h < NH; ++h) {
+                    tc::tma_load_2d(s.k[st][h] + dst, &map_k, &s.kv_full[st], h * 64, rows_y[i]);
+                    tc::tma_load_2d(s.v[st][h] + dst, &map_v, &s.kv_full[st], h * 64, rows_y[i]);
+                }
             }
         }
         return true;
@@ -191,8 +202,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         if (lane == 0)
             for (int j = 0; j < early; ++j) load_tile(j);
     } else if (active) {
-        for (int i = threadIdx.x - 32; i < ROWS * 8; i += blockDim.x - 32) {
-            const int r = i >> 3, c = i & 7;
+        for (int i = threadIdx.x - 32; i < ROWS * 8 * NH; i += blockDim.x - 32) {
+            const int r = i / (8 * NH), c = i % (8 * NH);         // row, 16-byte piece of the row
             const int row = qt * ROWS + r;
             uint4 val = make_uint4(0, 0, 0, 0);
             if (row < n_rows) {
@@ -200,7 +211,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                 val = *reinterpret_cast<const uint4*>(p.qkv + (size_t)tok * p.qkv_stride +
                                                       (size_t)head * HD + c * 8);
             }
-            *reinterpret_cast<uint4*>(s.q + r * 128 + ((c ^ (r & 7)) << 4)) = val;
+            *reinterpret_cast<uint4*>(s.q[c >> 3] + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = val;
         }
     }
     tc::fence_proxy_async();                // generic-proxy writes of Q, before the MMAs read them
@@ -229,46 +240,57 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         // ---- MMA issuer -------------------------------------------------------------------
         if (lane == 0 && n_tiles > 0) {
             constexpr uint32_t idesc_qk = tc::instr_desc_bf16(ROWS, KEYS);
-            constexpr uint32_t idesc_pv = tc::instr_desc_bf16_b_mn(ROWS, HD);
-            const uint64_t q_desc = tc::smem_desc_sw128(tc::smem_u32(s.q));
+            constexpr uint32_t idesc_pv = tc::instr_desc_bf16_b_mn(ROWS, 64);
             bool ok = true;
-            // S_j = Q K_j^T into buffer j & 1: K = 64 in four steps of 16
-            auto issue_qk = [&](int j) -> bool {
+            // S_j = Q K_j^T into buffer j & 1: the head size in steps of 16.  `block`: wait for
+            // the tile; else only take it if it has landed (true: issued)
+            auto issue_qk = [&](int j, bool block) -> bool {
                 const int st = j % STAGES;
-                if (!tc::mbar_wait(&s.kv_full[st], (j / STAGES) & 1, abort_flag)) return false;
+                if (block) {
+                    if (!tc::mbar_wait(&s.kv_full[st], (j / STAGES) & 1, abort_flag)) return false;
+                } else if (!tc::mbar_try_wait(&s.kv_full[st], (j / STAGES) & 1)) {
+                    return false;
+                }
                 tc::tc_fence_after_sync();
-                const uint64_t k_desc = tc::smem_desc_sw128(tc::smem_u32(s.k[st]));
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k)
-                    tc::umma_bf16(tmem_s + (j & 1) * 128, q_desc + 2 * k, k_desc + 2 * k, idesc_qk,
-                                  k > 0 ? 1u : 0u);
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint64_t q_desc = tc::smem_desc_sw128(tc::smem_u32(s.q[k >> 2])) + 2 * (k & 3);
+                    const uint64_t k_desc = tc::smem_desc_sw128(tc::smem_u32(s.k[st][k >> 2])) + 2 * (k & 3);
+                    tc::umma_bf16(tmem_s + (j & 1) * 128, q_desc, k_desc, idesc_qk, k > 0 ? 1u : 0u);
+                }
                 tc::umma_commit(&s.s_full[j & 1]);
                 return true;
             };
-            ok = issue_qk(0);
+            ok = issue_qk(0, true);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                // the next tile's scores go out first: their buffer was last read by the
-                // softmax of tile j - 1, whose P this thread has already waited for
-                if (j + 1 < n_tiles) ok = issue_qk(j + 1);
-                if (!ok) break;
-                // O += P_j V_j once the softmax has written P_j: 128 keys in eight steps of 16
-                if (!tc::mbar_wait(&s.p_full[j & 1], (j >> 1) & 1, abort_flag)) {
+                // the next tile's scores go out first if its keys have landed (their buffer was
+                // last read by the softmax of tile j - 1, whose P this thread has waited for);
+                // else after this tile's second product, which must not wait for a copy
+                const bool ahead = j + 1 < n_tiles && issue_qk(j + 1, false);
+                // O += P_j V_j once the softmax has written P_j: 128 keys in eight steps of 16,
+                // 64 output features at a time
+                const int pb = j % PB;
+                if (!tc::mbar_wait(&s.p_full[pb], (j / PB) & 1, abort_flag)) {
                     ok = false;
                     break;
                 }
                 tc::tc_fence_after_sync();
                 const int st = j % STAGES;
-                const uint64_t v_desc = tc::smem_desc_sw128(tc::smem_u32(s.v[st]));
 #pragma unroll
-                for (int k = 0; k < KEYS / 16; ++k) {
-                    const uint64_t p_desc =
-                        tc::smem_desc_sw128(tc::smem_u32(s.p[j & 1][k >> 2])) + 2 * (k & 3);
-                    // 16 keys further down V: 16 rows of 128 bytes = 128 descriptor units
-                    tc::umma_bf16(tmem_o, p_desc, v_desc + 128 * k, idesc_pv,
-                                  (j > 0 || k > 0) ? 1u : 0u);
+                for (int h = 0; h < NH; ++h) {
+                    const uint64_t v_desc = tc::smem_desc_sw128(tc::smem_u32(s.v[st][h]));
+#pragma unroll
+                    for (int k = 0; k < KEYS / 16; ++k) {
+                        const uint64_t p_desc =
+                            tc::smem_desc_sw128(tc::smem_u32(s.p[pb][k >> 2])) + 2 * (k & 3);
+                        // 16 keys further down V: 16 rows of 128 bytes = 128 descriptor units
+                        tc::umma_bf16(tmem_o + h * 64, p_desc, v_desc + 128 * k, idesc_pv,
+                                      (j > 0 || k > 0) ? 1u : 0u);
+                    }
                 }
                 tc::umma_commit(&s.kv_empty[st]);
-                tc::umma_commit(&s.pv_done[j & 1]);
+                tc::umma_commit(&s.pv_done[pb]);
+                if (j + 1 < n_tiles && !ahead) ok = issue_qk(j + 1, true);
             }
             if (!ok) tc::give_up(abort_flag, p.status, tc::ST_MMA_TIMEOUT);
         }
@@ -292,7 +314,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         };
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int key0 = key_lo + j * KEYS;
-            const int b = j & 1;
+            const int b = j & 1;                      // the scores' buffer
+            const int pb = j % PB;                    // P's buffer
             ok = wait_all(&s.s_full[b], (j >> 1) & 1);
             if (!ok) break;
             tc::tc_fence_after_sync();
@@ -335,7 +358,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                 m_ref = mx;
             }
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-                ok = wait_all(&s.pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1);
+                ok = wait_all(&s.pv_done[(j - 1) % PB], ((j - 1) / PB) & 1);
                 if (!ok) break;
                 tc::tc_fence_after_sync();
 #pragma unroll 1
@@ -351,9 +374,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                 tc::tc_fence_before_sync();
             }
             l *= corr;
-            // P's buffer was last read by the second MMA of tile j - 2
-            if (j >= 2) {
-                ok = wait_all(&s.pv_done[b], ((j - 2) >> 1) & 1);
+            // P's buffer was last read by the second MMA of tile j - PB
+            if (j >= PB) {
+                ok = wait_all(&s.pv_done[pb], ((j - PB) / PB) & 1);
                 if (!ok) break;
             }
             // P = exp2(s * scale - reference), to shared memory in the layout the second MMA
@@ -362,7 +385,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                uint8_t* half = s.p[b][c >> 1] + r * 128;
+                uint8_t* half = s.p[pb][c >> 1] + r * 128;
 #pragma unroll
                 for (int piece = 0; piece < 4; ++piece) {
                     float e[8];
@@ -387,10 +410,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             tc::fence_proxy_async();             // P is written by the generic proxy, read by the MMA
             __syncwarp();
-            if (lane == 0) tc::mbar_arrive(&s.p_full[b]);
+            if (lane == 0) tc::mbar_arrive(&s.p_full[pb]);
         }
         // ---- the output: O / l ------------------------------------------------------------
-        if (ok && n_tiles > 0) ok = wait_all(&s.pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
+        if (ok && n_tiles > 0) ok = wait_all(&s.pv_done[(n_tiles - 1) % PB], ((n_tiles - 1) / PB) & 1);
         if (ok && n_tiles > 0) {
             tc::tc_fence_after_sync();
             const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -426,10 +449,25 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     }
 }
 
+template <int HD>
+int launch_as(dim3 grid, cudaStream_t st, const CUtensorMap& mk, const CUtensorMap& mv,
+              const TcAttnParams& p) {
+    const int smem = (int)sizeof(Storage<HD>);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cb_launch(attention_tcgen05_kernel<HD>, grid, dim3(192), smem, st, mk, mv, p);
+    return cb_last_error();
+}
+
 }  // namespace
 
 // Attention for the rows of a step whose requests bring portions of prompts.
-// k_cache / v_cache: [n_pages][n_kv_heads][page_tokens][64] bf16.
+// k_cache / v_cache: [n_pages][n_kv_heads][page_tokens][head_dim] bf16; head_dim 64 or 128.
 CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, int out_stride,
                                    const void* k_cache, const void* v_cache, int n_pages,
                                    const int* req_row_start, const int* req_first_pos,
@@ -438,7 +476,7 @@ CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, i
                                    int page_tokens, float scale, int window, int* status,
                                    void* stream) {
     if (n_requests <= 0 || max_new_tokens <= 0) return 0;
-    if (head_dim != HD || n_heads % n_kv_heads != 0 || page_tokens < 8 || page_tokens > KEYS ||
+    if ((head_dim != 64 && head_dim != 128) || n_heads % n_kv_heads != 0 || page_tokens < 8 || page_tokens > KEYS ||
         (page_tokens & (page_tokens - 1)) || (qkv_stride & 7) || (out_stride & 7) ||
         ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) || ((uintptr_t)k_cache & 15) ||
         ((uintptr_t)v_cache & 15))
@@ -447,8 +485,8 @@ CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, i
     while ((1 << shift) < page_tokens) ++shift;
     CUtensorMap mk, mv;
     const uint64_t rows = (uint64_t)n_pages * n_kv_heads * page_tokens;
-    if (!tc::make_map_2d(&mk, k_cache, rows, HD, HD, page_tokens)) return CB_ERR_UNSUPPORTED;
-    if (!tc::make_map_2d(&mv, v_cache, rows, HD, HD, page_tokens)) return CB_ERR_UNSUPPORTED;
+    if (!tc::make_map_2d(&mk, k_cache, rows, head_dim, head_dim, page_tokens)) return CB_ERR_UNSUPPORTED;
+    if (!tc::make_map_2d(&mv, v_cache, rows, head_dim, head_dim, page_tokens)) return CB_ERR_UNSUPPORTED;
     TcAttnParams p;
     p.qkv = (const __nv_bfloat16*)qkv;
     p.qkv_stride = qkv_stride;
@@ -466,17 +504,9 @@ CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, i
     p.scale_log2 = scale * LOG2E;
     p.window = window;
     p.status = status;
-    const int smem = (int)sizeof(Storage);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
     const int n_rep = n_heads / n_kv_heads;
     const int q_tiles = (max_new_tokens * n_rep + ROWS - 1) / ROWS;
-    cb_launch(attention_tcgen05_kernel, dim3(q_tiles * n_kv_heads * n_requests), dim3(192), smem,
-              (cudaStream_t)stream, mk, mv, p);
-    return cb_last_error();
+    const dim3 grid(q_tiles * n_kv_heads * n_requests);
+    return head_dim == 64 ? launch_as<64>(grid, (cudaStream_t)stream, mk, mv, p)
+                          : launch_as<128>(grid, (cudaStream_t)stream, mk, mv, p);
 }

@@ -241,8 +241,8 @@ def linear_rope_append(h, wqkv, qkv, n_heads, n_kv_heads, head_dim, cos, sin, ro
 
 def _attention_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads, head_dim, scale,
                        window, ctx, cache) -> bool:
-    """tcgen05 attention for portions of prompts: head size 64, page size a power of
-    two from 8 to 128.  Returns False for anything else."""
+    """tcgen05 attention for portions of prompts: head size 64 or 128, page size a
+    power of two from 8 to 128.  Returns False for anything else."""
     pt = cache.page_tokens
     if pt < 8 or pt > 128 or pt & (pt - 1):
         return False
@@ -336,7 +336,7 @@ def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx,
                                           head_dim, scale, window, ctx, cache, partial, counters,
                                           n_chunks, chunk_keys)):
         return True
-    if (USE_TCGEN05_ATTENTION and not split and head_dim == 64
+    if (USE_TCGEN05_ATTENTION and not split and head_dim in (64, 128)
             and host.max_new_tokens * n_rep >= 64 and out.stride(0) % 8 == 0
             and _attention_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads,
                                    head_dim, scale, window, ctx, cache)):

@@ -489,6 +489,8 @@ def test_attention_tensor_core_tiles_and_split(case):
     (4, 4, 64, 32, [(0, 700)], None),
     (6, 1, 64, 8, [(513, 300), (0, 129)], None),
     (8, 2, 64, 128, [(100, 260)], 200),
+    (4, 2, 128, 16, [(0, 600), (40, 70)], None),            # head size 128: two stages, one P buffer
+    (2, 1, 128, 64, [(300, 420)], 256),
 ])
 def test_attention_tcgen05_matches_reference_and_mma(case):
     """Prompt portions with head size 64: S and O in tensor memory, K and V by TMA."""
