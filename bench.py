@@ -134,6 +134,9 @@ def prefill_flops(nums, t):
     return gemm + attn
 
 
+SHAPE_LABEL = {"120m": "120M", "llama-1b": "Llama-3.2-1B", "llama-8b": "Llama-3-8B"}
+
+
 def run_ours(args):
     import torch
     from crucible_b200 import LLM, SamplingParams, ops
@@ -143,10 +146,11 @@ def run_ours(args):
     from crucible_b200.weights import write_random_model
 
     peaks = read_peaks()
-    raw = shape("120m")
-    full_layers = raw["n_layer"]
+    raw = shape(args.shape)
+    layer_key = "n_layer" if "n_layer" in raw else "num_hidden_layers"
+    full_layers = raw[layer_key]
     if args.layers:
-        raw["n_layer"] = args.layers
+        raw[layer_key] = args.layers
     cfg = parse_config(raw)
     nums = model_numbers(cfg)
     ctx_len, batch, new_tokens = args.context, args.batch, args.steps
@@ -261,13 +265,14 @@ def run_ours(args):
 
     clocks.stop()
     line = {
-        "metric": "decode tok/s at batch 8 (120M shape, bf16, 2,048-token contexts)",
+        "metric": f"decode tok/s at batch {batch} ({SHAPE_LABEL[args.shape]} shape, bf16, "
+                  f"{ctx_len:,}-token contexts)",
         "value": round(main["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
-        "config": {"model": "crucible-120m-shape", "layers": nums["layers"],
+        "config": {"model": f"crucible-{args.shape}-shape", "layers": nums["layers"],
                    "layers_of_shape": full_layers, "hidden": cfg.hidden_size,
                    "q_heads": cfg.layers[0].mixer.n_heads,
                    "kv_heads": cfg.layers[0].mixer.n_kv_heads,
@@ -343,6 +348,8 @@ def main():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=2048)
+    p.add_argument("--shape", default="120m", choices=sorted(SHAPE_LABEL),
+                   help="a named shape; the default is the benchmark's")
     p.add_argument("--layers", type=int, default=0,
                    help="fewer layers than the shape has (both numbers are reported)")
     p.add_argument("--profile-case", default=None, choices=["prefill", "decode"],
