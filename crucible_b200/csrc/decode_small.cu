@@ -78,12 +78,12 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-constexpr int WARPS = 4;
 constexpr int BATCH = 8;          // blocks of 32 elements a warp keeps in flight per row
 
 // DEEP: K spans more than one batch of weight loads per warp; the next batch is then in
 // flight while the current one is multiplied (costs registers, so short K keeps the plain form).
-template <bool NORM_IN, int EPI, bool DEEP>
+// WARPS: 4, or 8 for long K (each warp's share of K is then short enough for one batch).
+template <bool NORM_IN, int EPI, bool DEEP, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallParams p) {
     cb_pdl_trigger();
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -168,7 +168,8 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
     }
     // ---- stage the step's rows in shared memory as bf16 (normalised if asked) -------------
     if (NORM_IN) {
-        // each warp normalises rows `warp` and `warp + 4` side by side; for widths up to
+        // each of four warps normalises rows `warp` and `warp + 4` side by side (of eight
+        // warps each takes one row); for widths up to
         // 1024 both rows and the gain stay in registers between the two passes, so the
         // whole staging is one round trip
         const int n4 = K >> 2;
@@ -209,8 +210,9 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
                 if (i < n4) {
                     dst_a[i] = make_uint2(pack2(va[j].x * r_a * gn[j].x, va[j].y * r_a * gn[j].y),
                                           pack2(va[j].z * r_a * gn[j].z, va[j].w * r_a * gn[j].w));
-                    dst_b[i] = make_uint2(pack2(vb[j].x * r_b * gn[j].x, vb[j].y * r_b * gn[j].y),
-                                          pack2(vb[j].z * r_b * gn[j].z, vb[j].w * r_b * gn[j].w));
+                    if (WARPS == 4)                     // with eight warps a warp has one row
+                        dst_b[i] = make_uint2(pack2(vb[j].x * r_b * gn[j].x, vb[j].y * r_b * gn[j].y),
+                                              pack2(vb[j].z * r_b * gn[j].z, vb[j].w * r_b * gn[j].w));
                 }
             }
         } else {
@@ -245,7 +247,7 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
                     }
                 }
                 dst_a[j] = oa;
-                dst_b[j] = ob;
+                if (WARPS == 4) dst_b[j] = ob;
             }
         }
     } else {
@@ -356,25 +358,28 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
     }
 }
 
-template <bool NORM_IN, int EPI, bool DEEP>
+template <bool NORM_IN, int EPI, bool DEEP, int WARPS>
 int launch_rows_as(const SmallParams& p, cudaStream_t s) {
     const int smem = 8 * (p.K + 32) * 2 + WARPS * 32 * 16;
     static int configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(small_linear_kernel<NORM_IN, EPI, DEEP>,
+        cudaError_t e = cudaFuncSetAttribute(small_linear_kernel<NORM_IN, EPI, DEEP, WARPS>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    cb_launch(small_linear_kernel<NORM_IN, EPI, DEEP>, dim3(p.n_tiles), dim3(WARPS * 32), smem, s, p);
+    cb_launch(small_linear_kernel<NORM_IN, EPI, DEEP, WARPS>, dim3(p.n_tiles), dim3(WARPS * 32), smem, s, p);
     return cb_last_error();
 }
 
 template <bool NORM_IN, int EPI>
 int launch_rows(const SmallParams& p, cudaStream_t s) {
-    // more than one batch of 32-element blocks per warp: keep two batches in flight
-    return p.K > BATCH * WARPS * 32 ? launch_rows_as<NORM_IN, EPI, true>(p, s)
-                                    : launch_rows_as<NORM_IN, EPI, false>(p, s);
+    // A warp takes one batch of 8 blocks of 32 elements at a time.  K up to 1024: four warps,
+    // one batch each.  Up to 2048: eight warps, still one batch each (the chain of round trips
+    // stays as short).  Beyond: eight warps with two batches in flight.
+    if (p.K <= BATCH * 4 * 32) return launch_rows_as<NORM_IN, EPI, false, 4>(p, s);
+    if (p.K <= BATCH * 8 * 32) return launch_rows_as<NORM_IN, EPI, false, 8>(p, s);
+    return launch_rows_as<NORM_IN, EPI, true, 8>(p, s);
 }
 
 bool sizes_ok(const float* x, const float* gain, const void* a, int lda, int M, int K, int ldw,
