@@ -28,7 +28,9 @@
 // load each, and feeds them to two MMAs as "k = 2t, 2t+1, 2t+8, 2t+9": the same
 // permutation of k on both operands, which a dot product does not see.
 //
-// Sizes: at most 8 rows; K a multiple of 8 with 16-byte aligned weight rows;
+// Sizes: at most 8 rows of fp32 input (normalised on the way in), or up to 32 rows of bf16
+// input (in groups of 8: each weight fragment then meets two or four MMAs); K a multiple of
+// 8 with 16-byte aligned weight rows;
 // ROPE_APPEND needs the whole head rotated (rotary_dim == head_dim).  Anything
 // else is refused and the caller runs the general kernels.
 // Reference counterparts: `gemv_batch_i8_b*` (engine/kernels/kernels.cu:1598),
@@ -83,7 +85,9 @@ constexpr int BATCH = 8;          // blocks of 32 elements a warp keeps in fligh
 // DEEP: K spans more than one batch of weight loads per warp; the next batch is then in
 // flight while the current one is multiplied (costs registers, so short K keeps the plain form).
 // WARPS: 4, or 8 for long K (each warp's share of K is then short enough for one batch).
-template <bool NORM_IN, int EPI, bool DEEP, int WARPS>
+// MT: groups of 8 rows of the step (1, 2 or 4: up to 8, 16 or 32 rows); more than one group
+// only with bf16 rows (the norm has then run as a kernel of its own).
+template <bool NORM_IN, int EPI, bool DEEP, int WARPS, int MT>
 __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallParams p) {
     cb_pdl_trigger();
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -91,8 +95,8 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
     const int g = lane >> 2, t = lane & 3;
     const int K = p.K;
     const int pitch = K + 32;                             // bf16 elements; staggers the rows over the banks
-    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [8][pitch]
-    float* red = reinterpret_cast<float*>(smem_raw + (size_t)8 * pitch * 2);   // [WARPS][32][4]
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                    // [8 * MT][pitch]
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)8 * MT * pitch * 2);      // [WARPS][MT][32][4]
     const int tile = blockIdx.x;
     // ---- this thread's two rows of W: first row g of the tile, and its partner ------------
     int rf, rs;
@@ -134,26 +138,36 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
     // What the epilogue will need from memory is asked for now, before the staging, so
     // that every round trip of this kernel's prologue is in flight at the same time.
     // ACCUM: the residual values this block will add to.
-    float old[4] = {0.f, 0.f, 0.f, 0.f};
-    const int m0 = 2 * t, m1 = 2 * t + 1;
-    if (EPI == ACCUM_F32 && warp == 0) {
-        const float* out = (const float*)p.out;
-        if (m0 < p.M && ok_f) old[0] = out[(size_t)m0 * p.ldc + rf];
-        if (m1 < p.M && ok_f) old[1] = out[(size_t)m1 * p.ldc + rf];
-        if (m0 < p.M && ok_s) old[2] = out[(size_t)m0 * p.ldc + rs];
-        if (m1 < p.M && ok_s) old[3] = out[(size_t)m1 * p.ldc + rs];
+    float old[MT][4];
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt) {
+        old[nt][0] = old[nt][1] = old[nt][2] = old[nt][3] = 0.f;
+        if (EPI == ACCUM_F32 && warp == 0) {
+            const float* out = (const float*)p.out;
+            const int m0 = nt * 8 + 2 * t, m1 = m0 + 1;
+            if (m0 < p.M && ok_f) old[nt][0] = out[(size_t)m0 * p.ldc + rf];
+            if (m1 < p.M && ok_f) old[nt][1] = out[(size_t)m1 * p.ldc + rf];
+            if (m0 < p.M && ok_s) old[nt][2] = out[(size_t)m0 * p.ldc + rs];
+            if (m1 < p.M && ok_s) old[nt][3] = out[(size_t)m1 * p.ldc + rs];
+        }
     }
     // ROPE_APPEND: positions, rotation factors and cache pages of the two step rows this
     // thread will finish.
-    int pos2[2] = {0, 0}, page2[2] = {0, 0};
-    float cs2[2] = {1.f, 1.f}, sn2[2] = {0.f, 0.f};
+    int pos2[2 * MT], page2[2 * MT];
+    float cs2[2 * MT], sn2[2 * MT];
+#pragma unroll
+    for (int e = 0; e < 2 * MT; ++e) {
+        pos2[e] = page2[e] = 0;
+        cs2[e] = 1.f;
+        sn2[e] = 0.f;
+    }
     if (EPI == ROPE_APPEND && warp == 0 && ok_f) {
         const int half = p.head_dim >> 1;
         const int pair = tile * 8 + g;
         const int head = pair / half, j = pair - head * half;
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            const int m = 2 * t + e;
+        for (int e = 0; e < 2 * MT; ++e) {
+            const int m = (e >> 1) * 8 + 2 * t + (e & 1);
             if (m < p.M) {
                 pos2[e] = p.positions[m];
                 if (head >= p.n_heads)
@@ -254,7 +268,7 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
         // bf16 rows go to shared memory as they are: asynchronous 16-byte copies, all in
         // flight at once; rows past the step's last are zero-filled
         const int n8 = K >> 3;
-        for (int i = threadIdx.x; i < 8 * n8; i += blockDim.x) {
+        for (int i = threadIdx.x; i < 8 * MT * n8; i += blockDim.x) {
             const int m = i / n8, c = i - m * n8;
             const bool in = m < p.M;
             const __nv_bfloat16* src = p.a + (size_t)(in ? m : 0) * p.lda + c * 8;
@@ -268,7 +282,9 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
     }
     __syncthreads();
     // ---- multiply: this warp's blocks of K -------------------------------------------------
-    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    float c[MT][4];
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt) c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.f;
     const __nv_bfloat16* xrow = xs + (size_t)g * pitch + t * 8;
     for (int kb0 = 0; kb0 < k_blocks; kb0 += BATCH * WARPS) {
         const bool more = DEEP && kb0 + BATCH * WARPS < k_blocks;    // block-uniform
@@ -296,10 +312,14 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
         for (int i = 0; i < BATCH; ++i) {
             const int kb = kb0 + warp + i * WARPS;
             if (kb < k_blocks) {                          // warp-uniform
-                uint4 xb = make_uint4(0, 0, 0, 0);
-                if (kb * 32 + t * 8 < K) xb = *reinterpret_cast<const uint4*>(xrow + kb * 32);
-                mma_bf16(c, vf[i].x, vs[i].x, vf[i].y, vs[i].y, xb.x, xb.y);
-                mma_bf16(c, vf[i].z, vs[i].z, vf[i].w, vs[i].w, xb.z, xb.w);
+#pragma unroll
+                for (int nt = 0; nt < MT; ++nt) {
+                    uint4 xb = make_uint4(0, 0, 0, 0);
+                    if (kb * 32 + t * 8 < K)
+                        xb = *reinterpret_cast<const uint4*>(xrow + (size_t)nt * 8 * pitch + kb * 32);
+                    mma_bf16(c[nt], vf[i].x, vs[i].x, vf[i].y, vs[i].y, xb.x, xb.y);
+                    mma_bf16(c[nt], vf[i].z, vs[i].z, vf[i].w, vs[i].w, xb.z, xb.w);
+                }
             }
         }
         if (DEEP && more) {
@@ -311,83 +331,100 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
         }
     }
     // ---- add the warps' partial sums in warp order; warp 0 finishes ------------------------
-    float4* mine = reinterpret_cast<float4*>(red) + warp * 32 + lane;
-    *mine = make_float4(c[0], c[1], c[2], c[3]);
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt)
+        reinterpret_cast<float4*>(red)[(warp * MT + nt) * 32 + lane] =
+            make_float4(c[nt][0], c[nt][1], c[nt][2], c[nt][3]);
     __syncthreads();
     if (warp != 0) return;
-    float d[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int w = 0; w < WARPS; ++w) {
-        const float4 v = reinterpret_cast<const float4*>(red)[w * 32 + lane];
-        d[0] += v.x; d[1] += v.y; d[2] += v.z; d[3] += v.w;
-    }
-    // d[0], d[1]: first row x step rows 2t, 2t+1;  d[2], d[3]: partner row x the same
+    for (int nt = 0; nt < MT; ++nt) {
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-        const int m = e == 0 ? m0 : m1;
-        if (m >= p.M) continue;
-        const float df = d[e], ds = d[2 + e];
-        if (EPI == ACCUM_F32 || EPI == STORE_F32) {
-            float* out = (float*)p.out + (size_t)m * p.ldc;
-            if (ok_f) out[rf] = EPI == ACCUM_F32 ? old[e] + df : df;
-            if (ok_s) out[rs] = EPI == ACCUM_F32 ? old[2 + e] + ds : ds;
-        } else if (EPI == SWIGLU_BF16) {
-            if (ok_f)
-                ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + rf] =
-                    __float2bfloat16_rn(df / (1.0f + expf(-df)) * ds);
-        } else if (ok_f) {
-            const int half = p.head_dim >> 1;
-            const int pair = tile * 8 + g;
-            const int head = pair / half, j = pair - head * half;
-            const int pos = pos2[e];
-            const float y0 = df * cs2[e] - ds * sn2[e];   // v heads keep cos 1, sin 0
-            const float y1 = df * sn2[e] + ds * cs2[e];
-            if (head < p.n_heads) {
-                __nv_bfloat16* q = (__nv_bfloat16*)p.out + (size_t)m * p.ldc + (size_t)head * p.head_dim;
-                q[j] = __float2bfloat16_rn(y0);
-                q[j + half] = __float2bfloat16_rn(y1);
-            } else {
-                const bool is_k = head < p.n_heads + p.n_kv_heads;
-                const int kvh = is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
-                __nv_bfloat16* dst = (is_k ? p.k_cache : p.v_cache) +
-                    (((size_t)page2[e] * p.n_kv_heads + kvh) * p.page_tokens + pos % p.page_tokens) * p.head_dim;
-                dst[j] = __float2bfloat16_rn(y0);
-                dst[j + half] = __float2bfloat16_rn(y1);
+        for (int w = 0; w < WARPS; ++w) {
+            const float4 v = reinterpret_cast<const float4*>(red)[(w * MT + nt) * 32 + lane];
+            d[0] += v.x; d[1] += v.y; d[2] += v.z; d[3] += v.w;
+        }
+        // d[0], d[1]: first row x step rows 8 nt + 2t, + 1;  d[2], d[3]: partner row x the same
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int m = nt * 8 + 2 * t + e;
+            if (m >= p.M) continue;
+            const float df = d[e], ds = d[2 + e];
+            if (EPI == ACCUM_F32 || EPI == STORE_F32) {
+                float* out = (float*)p.out + (size_t)m * p.ldc;
+                if (ok_f) out[rf] = EPI == ACCUM_F32 ? old[nt][e] + df : df;
+                if (ok_s) out[rs] = EPI == ACCUM_F32 ? old[nt][2 + e] + ds : ds;
+            } else if (EPI == SWIGLU_BF16) {
+                if (ok_f)
+                    ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + rf] =
+                        __float2bfloat16_rn(df / (1.0f + expf(-df)) * ds);
+            } else if (ok_f) {
+                const int half = p.head_dim >> 1;
+                const int pair = tile * 8 + g;
+                const int head = pair / half, j = pair - head * half;
+                const int pos = pos2[2 * nt + e];
+                const float y0 = df * cs2[2 * nt + e] - ds * sn2[2 * nt + e];   // v heads keep cos 1, sin 0
+                const float y1 = df * sn2[2 * nt + e] + ds * cs2[2 * nt + e];
+                if (head < p.n_heads) {
+                    __nv_bfloat16* q = (__nv_bfloat16*)p.out + (size_t)m * p.ldc + (size_t)head * p.head_dim;
+                    q[j] = __float2bfloat16_rn(y0);
+                    q[j + half] = __float2bfloat16_rn(y1);
+                } else {
+                    const bool is_k = head < p.n_heads + p.n_kv_heads;
+                    const int kvh = is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
+                    __nv_bfloat16* dst = (is_k ? p.k_cache : p.v_cache) +
+                        (((size_t)page2[2 * nt + e] * p.n_kv_heads + kvh) * p.page_tokens + pos % p.page_tokens) *
+                            p.head_dim;
+                    dst[j] = __float2bfloat16_rn(y0);
+                    dst[j + half] = __float2bfloat16_rn(y1);
+                }
             }
         }
     }
 }
 
-template <bool NORM_IN, int EPI, bool DEEP, int WARPS>
+template <bool NORM_IN, int EPI, bool DEEP, int WARPS, int MT>
 int launch_rows_as(const SmallParams& p, cudaStream_t s) {
-    const int smem = 8 * (p.K + 32) * 2 + WARPS * 32 * 16;
+    const int smem = 8 * MT * (p.K + 32) * 2 + WARPS * MT * 32 * 16;
     static int configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(small_linear_kernel<NORM_IN, EPI, DEEP, WARPS>,
+        cudaError_t e = cudaFuncSetAttribute(small_linear_kernel<NORM_IN, EPI, DEEP, WARPS, MT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    cb_launch(small_linear_kernel<NORM_IN, EPI, DEEP, WARPS>, dim3(p.n_tiles), dim3(WARPS * 32), smem, s, p);
+    cb_launch(small_linear_kernel<NORM_IN, EPI, DEEP, WARPS, MT>, dim3(p.n_tiles), dim3(WARPS * 32), smem,
+              s, p);
     return cb_last_error();
 }
 
-template <bool NORM_IN, int EPI>
-int launch_rows(const SmallParams& p, cudaStream_t s) {
+template <bool NORM_IN, int EPI, int MT>
+int launch_rows_mt(const SmallParams& p, cudaStream_t s) {
     // A warp takes one batch of 8 blocks of 32 elements at a time.  K up to 1024: four warps,
     // one batch each.  Up to 2048: eight warps, still one batch each (the chain of round trips
     // stays as short).  Beyond: eight warps with two batches in flight.
-    if (p.K <= BATCH * 4 * 32) return launch_rows_as<NORM_IN, EPI, false, 4>(p, s);
-    if (p.K <= BATCH * 8 * 32) return launch_rows_as<NORM_IN, EPI, false, 8>(p, s);
-    return launch_rows_as<NORM_IN, EPI, true, 8>(p, s);
+    if (p.K <= BATCH * 4 * 32) return launch_rows_as<NORM_IN, EPI, false, 4, MT>(p, s);
+    if (p.K <= BATCH * 8 * 32) return launch_rows_as<NORM_IN, EPI, false, 8, MT>(p, s);
+    return launch_rows_as<NORM_IN, EPI, true, 8, MT>(p, s);
+}
+
+// More than 8 rows: bf16 rows only, in two or four groups of 8.
+template <bool NORM_IN, int EPI>
+int launch_rows(const SmallParams& p, cudaStream_t s) {
+    if (p.M <= 8) return launch_rows_mt<NORM_IN, EPI, 1>(p, s);
+    if (NORM_IN) return CB_ERR_UNSUPPORTED;
+    if (p.M <= 16) return launch_rows_mt<false, EPI, 2>(p, s);
+    return launch_rows_mt<false, EPI, 4>(p, s);
 }
 
 bool sizes_ok(const float* x, const float* gain, const void* a, int lda, int M, int K, int ldw,
               const void* w) {
     if (x ? (((uintptr_t)x & 15) || ((uintptr_t)gain & 15)) : (((uintptr_t)a & 15) || (lda & 7)))
         return false;
-    return M >= 1 && M <= 8 && K > 0 && (K & 7) == 0 && (ldw & 7) == 0 && ((uintptr_t)w & 15) == 0 &&
-           (size_t)8 * (K + 32) * 2 <= 200 * 1024;
+    const int groups = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
+    return M >= 1 && M <= (x ? 8 : 32) && K > 0 && (K & 7) == 0 && (ldw & 7) == 0 &&
+           ((uintptr_t)w & 15) == 0 && (size_t)8 * groups * (K + 32) * 2 <= 200 * 1024;
 }
 
 }  // namespace

@@ -196,11 +196,38 @@ def test_small_batch_linear_and_swiglu(m, n, k):
         y = normed @ w.double().T
         g, u = y[:, :inter], y[:, inter:]
         assert rel(act, g / (1 + torch.exp(-g)) * u) < 5e-3
-    big = torch.randn(9, k, device=DEV).bfloat16()
-    assert small_batch.linear(big, w, torch.empty(9, n, device=DEV)) is False     # more than 8 rows
+    too_many = small_batch.MAX_ROWS_BF16 + 1
+    big = torch.randn(too_many, k, device=DEV).bfloat16()
+    assert small_batch.linear(big, w, torch.empty(too_many, n, device=DEV)) is False
     odd = torch.randn(m, 12, device=DEV).bfloat16()
     assert small_batch.linear(odd, torch.randn(n, 12, device=DEV).bfloat16(),
                               torch.empty(m, n, device=DEV)) is False             # K not a multiple of 8
+
+
+@pytest.mark.parametrize("m", [9, 13, 16, 17, 27, 32])
+@pytest.mark.parametrize("n,k", [(768, 768), (100, 2048), (1280, 1032), (64, 4104)])
+def test_small_batch_row_groups(m, n, k):
+    """9 to 32 rows of bf16 input: two or four groups of 8 rows share each weight fragment."""
+    from crucible_b200.ops import small_batch
+    w = (torch.randn(n, k, device=DEV) * 0.1).bfloat16()
+    a = torch.randn(m, k, device=DEV).bfloat16()
+    base = torch.randn(m, n, device=DEV)
+    out = base.clone()
+    groups = 2 if m <= 16 else 4
+    if 8 * groups * (k + 32) * 2 > 200 * 1024:           # the staged rows do not fit: refused
+        assert small_batch.linear(a, w, out, accumulate=True) is False
+        return
+    assert small_batch.linear(a, w, out, accumulate=True)
+    assert rel(out, base.double() + a.double() @ w.double().T) < 1e-5
+    out2 = torch.empty(m, n, device=DEV)
+    assert small_batch.linear(a, w, out2)
+    assert rel(out2, a.double() @ w.double().T) < 1e-5
+    inter = n // 2
+    act = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
+    assert small_batch.linear_swiglu(a, w, act)
+    y = a.double() @ w.double().T
+    g, u = y[:, :inter], y[:, inter:]
+    assert rel(act, g / (1 + torch.exp(-g)) * u) < 5e-3
 
 
 def test_small_batch_large_weights_take_other_paths():
@@ -295,11 +322,13 @@ def test_linear_rope_append_tensor_core(hd, n_heads, n_kv, rows, write):
 
 
 @pytest.mark.parametrize("write", [True, False])
-def test_small_batch_qkv_rope_append(write):
+@pytest.mark.parametrize("many", [False, True])
+def test_small_batch_qkv_rope_append(write, many):
+    """A few rows not yet normalised (the norm runs inside), or up to 32 normalised bf16 rows."""
     from crucible_b200.ops import small_batch
     n_heads, n_kv, hd, page, d = 6, 2, 32, 8, 96
-    positions = [5, 17, 0, 40]
-    row_request = [0, 0, 1, 2]
+    positions = [5, 17, 0, 40] + ([41, 42, 43, 44, 18, 19, 1, 2, 3, 4, 5, 6, 7, 20, 21, 22, 23, 45] if many else [])
+    row_request = [0, 0, 1, 2] + ([2, 2, 2, 2, 0, 0, 1, 1, 1, 1, 1, 1, 1, 0, 0, 0, 0, 2] if many else [])
     tables = torch.tensor([[3, 1, 7, 0, 0, 0], [2, 0, 0, 0, 0, 0], [4, 5, 6, 8, 9, 10]],
                           dtype=torch.int32, device=DEV)
     t = len(positions)
@@ -319,10 +348,10 @@ def test_small_batch_qkv_rope_append(write):
                           row_request=torch.tensor(row_request, dtype=torch.int32, device=DEV),
                           block_table=lambda g: tables)
     qkv = torch.zeros(t, w.shape[0], device=DEV, dtype=torch.bfloat16)
-    lazy = small_batch.LazyNorm(x, gain, 1e-6, lambda: None)
+    normed = x.double() * torch.rsqrt(x.double().pow(2).mean(-1, keepdim=True) + 1e-6) * gain.double()
+    lazy = small_batch.LazyNorm(x, gain, 1e-6, lambda: normed.to(torch.bfloat16))
     assert small_batch.qkv_rope_append(lazy, w, qkv, n_heads, n_kv, hd, cos, sin, hd, ctx, Cache,
                                        SimpleNamespace(group=0, slot=0, write=write))
-    normed = x.double() * torch.rsqrt(x.double().pow(2).mean(-1, keepdim=True) + 1e-6) * gain.double()
     y = (normed @ w.double().T).cpu().view(t, n_heads + 2 * n_kv, hd)
 
     def rotate(v, pos):
