@@ -28,8 +28,8 @@
 // load each, and feeds them to two MMAs as "k = 2t, 2t+1, 2t+8, 2t+9": the same
 // permutation of k on both operands, which a dot product does not see.
 //
-// Sizes: at most 8 rows of fp32 input (normalised on the way in), or up to 32 rows of bf16
-// input (in groups of 8: each weight fragment then meets two or four MMAs); K a multiple of
+// Sizes: at most 32 rows (in groups of 8: each weight fragment then meets one, two or four
+// pairs of MMAs); K a multiple of
 // 8 with 16-byte aligned weight rows;
 // ROPE_APPEND needs the whole head rotated (rotary_dim == head_dim).  Anything
 // else is refused and the caller runs the general kernels.
@@ -85,8 +85,8 @@ constexpr int BATCH = 8;          // blocks of 32 elements a warp keeps in fligh
 // DEEP: K spans more than one batch of weight loads per warp; the next batch is then in
 // flight while the current one is multiplied (costs registers, so short K keeps the plain form).
 // WARPS: 4, or 8 for long K (each warp's share of K is then short enough for one batch).
-// MT: groups of 8 rows of the step (1, 2 or 4: up to 8, 16 or 32 rows); more than one group
-// only with bf16 rows (the norm has then run as a kernel of its own).
+// MT: groups of 8 rows of the step (1, 2 or 4: up to 8, 16 or 32 rows); each weight fragment
+// then meets MT pairs of MMAs, and the rows are staged one group after the other.
 template <bool NORM_IN, int EPI, bool DEEP, int WARPS, int MT>
 __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallParams p) {
     cb_pdl_trigger();
@@ -188,80 +188,84 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
         // whole staging is one round trip
         const int n4 = K >> 2;
         const float4* g4 = reinterpret_cast<const float4*>(p.gain);
-        const int ma = warp, mb = warp + WARPS;
-        const bool has_a = ma < p.M, has_b = mb < p.M;
-        const float4* row_a = reinterpret_cast<const float4*>(p.x + (size_t)(has_a ? ma : 0) * K);
-        const float4* row_b = reinterpret_cast<const float4*>(p.x + (size_t)(has_b ? mb : 0) * K);
-        uint2* dst_a = reinterpret_cast<uint2*>(xs + (size_t)ma * pitch);
-        uint2* dst_b = reinterpret_cast<uint2*>(xs + (size_t)mb * pitch);
-        constexpr int J = 8;
-        const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (n4 <= 32 * J) {
-            float4 va[J], vb[J], gn[J];
-#pragma unroll
-            for (int j = 0; j < J; ++j) {
-                const int i = lane + 32 * j;
-                const bool in = i < n4;
-                va[j] = (in && has_a) ? row_a[i] : zero4;
-                vb[j] = (in && has_b) ? row_b[i] : zero4;
-                gn[j] = in ? g4[i] : zero4;
-            }
-            float ss_a = 0.f, ss_b = 0.f;
-#pragma unroll
-            for (int j = 0; j < J; ++j) {
-                ss_a = fmaf(va[j].x, va[j].x, ss_a); ss_a = fmaf(va[j].y, va[j].y, ss_a);
-                ss_a = fmaf(va[j].z, va[j].z, ss_a); ss_a = fmaf(va[j].w, va[j].w, ss_a);
-                ss_b = fmaf(vb[j].x, vb[j].x, ss_b); ss_b = fmaf(vb[j].y, vb[j].y, ss_b);
-                ss_b = fmaf(vb[j].z, vb[j].z, ss_b); ss_b = fmaf(vb[j].w, vb[j].w, ss_b);
-            }
-            ss_a = cb_warp_sum(ss_a);
-            ss_b = cb_warp_sum(ss_b);
-            const float r_a = 1.0f / sqrtf(ss_a / (float)K + p.eps);
-            const float r_b = 1.0f / sqrtf(ss_b / (float)K + p.eps);
-#pragma unroll
-            for (int j = 0; j < J; ++j) {
-                const int i = lane + 32 * j;
-                if (i < n4) {
-                    dst_a[i] = make_uint2(pack2(va[j].x * r_a * gn[j].x, va[j].y * r_a * gn[j].y),
-                                          pack2(va[j].z * r_a * gn[j].z, va[j].w * r_a * gn[j].w));
-                    if (WARPS == 4)                     // with eight warps a warp has one row
-                        dst_b[i] = make_uint2(pack2(vb[j].x * r_b * gn[j].x, vb[j].y * r_b * gn[j].y),
-                                              pack2(vb[j].z * r_b * gn[j].z, vb[j].w * r_b * gn[j].w));
+        // one group of 8 rows after the other
+#pragma unroll 1
+        for (int grp = 0; grp < MT; ++grp) {
+            const int ma = grp * 8 + warp, mb = ma + WARPS;
+            const bool has_a = ma < p.M, has_b = WARPS == 4 && mb < p.M;
+            const float4* row_a = reinterpret_cast<const float4*>(p.x + (size_t)(has_a ? ma : 0) * K);
+            const float4* row_b = reinterpret_cast<const float4*>(p.x + (size_t)(has_b ? mb : 0) * K);
+            uint2* dst_a = reinterpret_cast<uint2*>(xs + (size_t)ma * pitch);
+            uint2* dst_b = reinterpret_cast<uint2*>(xs + (size_t)mb * pitch);
+            constexpr int J = 8;
+            const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (n4 <= 32 * J) {
+                float4 va[J], vb[J], gn[J];
+    #pragma unroll
+                for (int j = 0; j < J; ++j) {
+                    const int i = lane + 32 * j;
+                    const bool in = i < n4;
+                    va[j] = (in && has_a) ? row_a[i] : zero4;
+                    vb[j] = (in && has_b) ? row_b[i] : zero4;
+                    gn[j] = in ? g4[i] : zero4;
                 }
-            }
-        } else {
-            float ss_a = 0.f, ss_b = 0.f;
-            if (has_a) {
-#pragma unroll 4
-                for (int j = lane; j < n4; j += 32) {
-                    const float4 va = row_a[j];
-                    const float4 vb = has_b ? row_b[j] : zero4;
-                    ss_a = fmaf(va.x, va.x, ss_a); ss_a = fmaf(va.y, va.y, ss_a);
-                    ss_a = fmaf(va.z, va.z, ss_a); ss_a = fmaf(va.w, va.w, ss_a);
-                    ss_b = fmaf(vb.x, vb.x, ss_b); ss_b = fmaf(vb.y, vb.y, ss_b);
-                    ss_b = fmaf(vb.z, vb.z, ss_b); ss_b = fmaf(vb.w, vb.w, ss_b);
+                float ss_a = 0.f, ss_b = 0.f;
+    #pragma unroll
+                for (int j = 0; j < J; ++j) {
+                    ss_a = fmaf(va[j].x, va[j].x, ss_a); ss_a = fmaf(va[j].y, va[j].y, ss_a);
+                    ss_a = fmaf(va[j].z, va[j].z, ss_a); ss_a = fmaf(va[j].w, va[j].w, ss_a);
+                    ss_b = fmaf(vb[j].x, vb[j].x, ss_b); ss_b = fmaf(vb[j].y, vb[j].y, ss_b);
+                    ss_b = fmaf(vb[j].z, vb[j].z, ss_b); ss_b = fmaf(vb[j].w, vb[j].w, ss_b);
                 }
-            }
-            ss_a = cb_warp_sum(ss_a);
-            ss_b = cb_warp_sum(ss_b);
-            const float r_a = 1.0f / sqrtf(ss_a / (float)K + p.eps);
-            const float r_b = 1.0f / sqrtf(ss_b / (float)K + p.eps);
-#pragma unroll 4
-            for (int j = lane; j < n4; j += 32) {
-                uint2 oa = make_uint2(0, 0), ob = make_uint2(0, 0);
-                if (has_a) {
-                    const float4 gn = g4[j];
-                    const float4 va = row_a[j];
-                    oa = make_uint2(pack2(va.x * r_a * gn.x, va.y * r_a * gn.y),
-                                    pack2(va.z * r_a * gn.z, va.w * r_a * gn.w));
-                    if (has_b) {
-                        const float4 vb = row_b[j];
-                        ob = make_uint2(pack2(vb.x * r_b * gn.x, vb.y * r_b * gn.y),
-                                        pack2(vb.z * r_b * gn.z, vb.w * r_b * gn.w));
+                ss_a = cb_warp_sum(ss_a);
+                ss_b = cb_warp_sum(ss_b);
+                const float r_a = 1.0f / sqrtf(ss_a / (float)K + p.eps);
+                const float r_b = 1.0f / sqrtf(ss_b / (float)K + p.eps);
+    #pragma unroll
+                for (int j = 0; j < J; ++j) {
+                    const int i = lane + 32 * j;
+                    if (i < n4) {
+                        dst_a[i] = make_uint2(pack2(va[j].x * r_a * gn[j].x, va[j].y * r_a * gn[j].y),
+                                              pack2(va[j].z * r_a * gn[j].z, va[j].w * r_a * gn[j].w));
+                        if (WARPS == 4)                     // with eight warps a warp has one row
+                            dst_b[i] = make_uint2(pack2(vb[j].x * r_b * gn[j].x, vb[j].y * r_b * gn[j].y),
+                                                  pack2(vb[j].z * r_b * gn[j].z, vb[j].w * r_b * gn[j].w));
                     }
                 }
-                dst_a[j] = oa;
-                if (WARPS == 4) dst_b[j] = ob;
+            } else {
+                float ss_a = 0.f, ss_b = 0.f;
+                if (has_a) {
+    #pragma unroll 4
+                    for (int j = lane; j < n4; j += 32) {
+                        const float4 va = row_a[j];
+                        const float4 vb = has_b ? row_b[j] : zero4;
+                        ss_a = fmaf(va.x, va.x, ss_a); ss_a = fmaf(va.y, va.y, ss_a);
+                        ss_a = fmaf(va.z, va.z, ss_a); ss_a = fmaf(va.w, va.w, ss_a);
+                        ss_b = fmaf(vb.x, vb.x, ss_b); ss_b = fmaf(vb.y, vb.y, ss_b);
+                        ss_b = fmaf(vb.z, vb.z, ss_b); ss_b = fmaf(vb.w, vb.w, ss_b);
+                    }
+                }
+                ss_a = cb_warp_sum(ss_a);
+                ss_b = cb_warp_sum(ss_b);
+                const float r_a = 1.0f / sqrtf(ss_a / (float)K + p.eps);
+                const float r_b = 1.0f / sqrtf(ss_b / (float)K + p.eps);
+    #pragma unroll 4
+                for (int j = lane; j < n4; j += 32) {
+                    uint2 oa = make_uint2(0, 0), ob = make_uint2(0, 0);
+                    if (has_a) {
+                        const float4 gn = g4[j];
+                        const float4 va = row_a[j];
+                        oa = make_uint2(pack2(va.x * r_a * gn.x, va.y * r_a * gn.y),
+                                        pack2(va.z * r_a * gn.z, va.w * r_a * gn.w));
+                        if (has_b) {
+                            const float4 vb = row_b[j];
+                            ob = make_uint2(pack2(vb.x * r_b * gn.x, vb.y * r_b * gn.y),
+                                            pack2(vb.z * r_b * gn.z, vb.w * r_b * gn.w));
+                        }
+                    }
+                    dst_a[j] = oa;
+                    if (WARPS == 4) dst_b[j] = ob;
+                }
             }
         }
     } else {
@@ -409,13 +413,12 @@ int launch_rows_mt(const SmallParams& p, cudaStream_t s) {
     return launch_rows_as<NORM_IN, EPI, true, 8, MT>(p, s);
 }
 
-// More than 8 rows: bf16 rows only, in two or four groups of 8.
+// More than 8 rows: in two or four groups of 8.
 template <bool NORM_IN, int EPI>
 int launch_rows(const SmallParams& p, cudaStream_t s) {
     if (p.M <= 8) return launch_rows_mt<NORM_IN, EPI, 1>(p, s);
-    if (NORM_IN) return CB_ERR_UNSUPPORTED;
-    if (p.M <= 16) return launch_rows_mt<false, EPI, 2>(p, s);
-    return launch_rows_mt<false, EPI, 4>(p, s);
+    if (p.M <= 16) return launch_rows_mt<NORM_IN, EPI, 2>(p, s);
+    return launch_rows_mt<NORM_IN, EPI, 4>(p, s);
 }
 
 bool sizes_ok(const float* x, const float* gain, const void* a, int lda, int M, int K, int ldw,
@@ -423,7 +426,7 @@ bool sizes_ok(const float* x, const float* gain, const void* a, int lda, int M, 
     if (x ? (((uintptr_t)x & 15) || ((uintptr_t)gain & 15)) : (((uintptr_t)a & 15) || (lda & 7)))
         return false;
     const int groups = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
-    return M >= 1 && M <= (x ? 8 : 32) && K > 0 && (K & 7) == 0 && (ldw & 7) == 0 &&
+    return M >= 1 && M <= 32 && K > 0 && (K & 7) == 0 && (ldw & 7) == 0 &&
            ((uintptr_t)w & 15) == 0 && (size_t)8 * groups * (K + 32) * 2 <= 200 * 1024;
 }
 

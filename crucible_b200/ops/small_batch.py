@@ -1,5 +1,5 @@
 """Fused kernels for steps of a few rows (decoded tokens), bfloat16 engine only: up
-to 8 rows with the norm inside, up to 32 rows of normalised bf16 input.  Each
+to 32 rows, normalised bf16 input or fp32 rows with the norm inside.  Each
 function returns True if it ran, False if the sizes are outside what the kernels
 take (more rows, K not a multiple of 8, a partially rotated head, weights too
 large to be worth it): the caller then runs the general kernels.
@@ -20,8 +20,9 @@ from . import build
 
 build.register_module("decode_small", ["common.cuh"])
 
-MAX_ROWS = 8            # rows a norm may hand over not yet normalised (fused into the product)
-MAX_ROWS_BF16 = 32      # rows of bf16 input these kernels take (in groups of 8)
+MAX_ROWS = 32           # rows these kernels take (in groups of 8)
+MAX_LAZY_ROWS = 16      # rows a norm hands over not yet normalised: every block then normalises
+                        # them for itself, which beyond 16 rows costs more than a norm kernel
 _c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 _UNSUPPORTED = 100001
 
@@ -56,7 +57,7 @@ def _stream():
 
 def _input(h: Rows, w: torch.Tensor):
     """(x, gain, eps, a, lda) for the launchers."""
-    if isinstance(h, LazyNorm) and (w.numel() * 2 > NORM_FUSE_MAX_BYTES or h.shape[0] > MAX_ROWS):
+    if isinstance(h, LazyNorm) and (w.numel() * 2 > NORM_FUSE_MAX_BYTES or h.shape[0] > MAX_LAZY_ROWS):
         h = h.tensor()
     if isinstance(h, LazyNorm):
         if not h.x.is_contiguous():
@@ -89,7 +90,7 @@ NORM_FUSE_MAX_BYTES = 8 << 20
 
 
 def _weights_ok(w: torch.Tensor, rows: int) -> bool:
-    return (rows <= MAX_ROWS_BF16 and w.dtype == torch.bfloat16 and w.is_cuda and w.stride(1) == 1
+    return (rows <= MAX_ROWS and w.dtype == torch.bfloat16 and w.is_cuda and w.stride(1) == 1
             and w.numel() * 2 <= MAX_WEIGHT_BYTES)
 
 

@@ -38,7 +38,7 @@ class RMSNorm(Norm):
             out = ctx.scratch("norm.out", (x.shape[0], self.spec.width), self.dtype)
             ops.rmsnorm(x, self.gain, self.spec.eps, out)
             return out
-        if lazy and self.dtype == torch.bfloat16 and x.shape[0] <= small_batch.MAX_ROWS:
+        if lazy and self.dtype == torch.bfloat16 and x.shape[0] <= small_batch.MAX_LAZY_ROWS:
             return small_batch.LazyNorm(x, self.gain, self.spec.eps, run)
         return run()
 

@@ -171,7 +171,7 @@ def test_linear_swiglu_few_rows(m, inter, k, splits):
     tensor_core.check_status(DEV)
 
 
-@pytest.mark.parametrize("m", [1, 2, 3, 8])
+@pytest.mark.parametrize("m", [1, 2, 3, 8, 11, 16])
 @pytest.mark.parametrize("n,k", [(768, 768), (100, 2048), (33, 40), (1280, 1032), (64, 4104)])
 def test_small_batch_linear_and_swiglu(m, n, k):
     """The fused kernels for a few rows: bf16 input or fp32 rows normalised on the fly."""
@@ -196,7 +196,7 @@ def test_small_batch_linear_and_swiglu(m, n, k):
         y = normed @ w.double().T
         g, u = y[:, :inter], y[:, inter:]
         assert rel(act, g / (1 + torch.exp(-g)) * u) < 5e-3
-    too_many = small_batch.MAX_ROWS_BF16 + 1
+    too_many = small_batch.MAX_ROWS + 1
     big = torch.randn(too_many, k, device=DEV).bfloat16()
     assert small_batch.linear(big, w, torch.empty(too_many, n, device=DEV)) is False
     odd = torch.randn(m, 12, device=DEV).bfloat16()
