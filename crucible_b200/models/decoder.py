@@ -182,8 +182,13 @@ class DecoderModel:
             self.layers[entry.layer].forward(ctx, x, binding)
         if ctx.n_logit_rows == 0:
             return ctx.scratch("logits", (0, self.config.vocab_size), torch.float32)
-        rows = ctx.scratch("head.rows", (ctx.n_logit_rows, self.config.hidden_size),
-                           torch.float32)
-        ops.gather_rows(x, ctx.logit_rows, rows)
+        if ctx.host.all_single_token and ctx.n_logit_rows == ctx.n_tokens:
+            # every request brings one token and wants its logits: the wanted rows are the
+            # step's rows in order (a fact of the step's shape, so a captured step replays)
+            rows = x
+        else:
+            rows = ctx.scratch("head.rows", (ctx.n_logit_rows, self.config.hidden_size),
+                               torch.float32)
+            ops.gather_rows(x, ctx.logit_rows, rows)
         h = self.final_norm.forward(ctx, rows)
         return self.head.forward(ctx, h)
