@@ -10,9 +10,9 @@ from typing import Dict, List, Sequence, Tuple
 import numpy as np
 import torch
 
-# Two tiny configurations that differ in every size and option: layers, width,
+# Tiny configurations (the first two differ in every size and option: layers, width,
 # head counts and group size, head size, feed-forward width, vocabulary, rotary
-# base, norm epsilon, tied or untied head, context, and (below) the page size.
+# base, norm epsilon, tied or untied head, context, and (below) the page size).
 TINY = {
     "tiny-a": dict(config={
         "architectures": ["CrucibleGPT"], "vocab_size": 256, "n_layer": 2, "n_head": 4,
@@ -26,6 +26,14 @@ TINY = {
         "intermediate_size": 320, "max_position_embeddings": 448, "hidden_act": "silu",
         "rope_theta": 500000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False},
         seed=2, page_tokens=32),
+    # head size 64: the bfloat16 engine then runs its tcgen05 attention kernels and the
+    # q/k/v product with the rotation in its epilogue; the q width differs from the model's
+    "tiny-c": dict(config={
+        "architectures": ["LlamaForCausalLM"], "vocab_size": 300, "num_hidden_layers": 2,
+        "num_attention_heads": 4, "num_key_value_heads": 2, "hidden_size": 128, "head_dim": 64,
+        "intermediate_size": 208, "max_position_embeddings": 512, "hidden_act": "silu",
+        "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True},
+        seed=5, page_tokens=16),
 }
 
 # Larger than the reference's 0.02 so that attention is not nearly uniform and

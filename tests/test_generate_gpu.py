@@ -44,7 +44,7 @@ def test_greedy_generation_float32_is_token_identical(tmp_path, name):
     assert llm2.generate(prompts, SamplingParams(max_tokens=n_new)) == want
 
 
-@pytest.mark.parametrize("name", ["tiny-a", "tiny-b"])
+@pytest.mark.parametrize("name", ["tiny-a", "tiny-b", "tiny-c"])
 def test_greedy_generation_bfloat16_follows_the_plain_model(tmp_path, name):
     """bfloat16 rounds, so a token may differ where the two best logits are
     close; every token must be the plain model's choice or within the rounding

@@ -15,7 +15,12 @@ from helpers import TINY, TOLERANCE, Trace
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"tiny-a": [7, 33, 64, 150], "tiny-b": [1, 17, 50, 95, 130]}
+LENGTHS = {"tiny-a": [7, 33, 64, 150], "tiny-b": [1, 17, 50, 95, 130], "tiny-c": [70, 150, 201]}
+
+
+def _one_at_a_time(name):
+    """--max-tokens when one request is live at a time: the longest, rounded up to 64."""
+    return max(192, -(-max(LENGTHS[name]) // 64) * 64)
 
 
 def _vocab(name):
@@ -52,18 +57,18 @@ def _check(name, dtype, model_dir, trace, out_dir, requests, max_tokens):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny-a", "tiny-b"])
+@pytest.mark.parametrize("name", ["tiny-a", "tiny-b", "tiny-c"])
 def test_each_request_alone_and_whole(tmp_path, name, dtype):
     model_dir = helpers.make_folder(tmp_path, name)
     requests = _requests(name)
     trace = Trace()
     for rid, tokens in requests.items():
         trace.step([(rid, tokens, list(range(len(tokens))))], end=[rid])
-    _check(name, dtype, model_dir, trace, str(tmp_path / "out"), requests, 192)
+    _check(name, dtype, model_dir, trace, str(tmp_path / "out"), requests, _one_at_a_time(name))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny-a", "tiny-b"])
+@pytest.mark.parametrize("name", ["tiny-a", "tiny-b", "tiny-c"])
 def test_prompt_then_last_32_one_by_one(tmp_path, name, dtype):
     model_dir = helpers.make_folder(tmp_path, name)
     requests = {k: v for k, v in _requests(name).items() if len(v) > 40}
@@ -73,11 +78,11 @@ def test_prompt_then_last_32_one_by_one(tmp_path, name, dtype):
         trace.step([(rid, tokens[:head], [head - 1])])
         for i in range(head, len(tokens)):
             trace.step([(rid, [tokens[i]], [0])], end=[rid] if i == len(tokens) - 1 else [])
-    _check(name, dtype, model_dir, trace, str(tmp_path / "out"), requests, 192)
+    _check(name, dtype, model_dir, trace, str(tmp_path / "out"), requests, _one_at_a_time(name))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny-a", "tiny-b"])
+@pytest.mark.parametrize("name", ["tiny-a", "tiny-b", "tiny-c"])
 def test_portions_of_changing_size(tmp_path, name, dtype):
     model_dir = helpers.make_folder(tmp_path, name)
     requests = {k: v for k, v in _requests(name).items() if len(v) >= 33}
@@ -93,7 +98,7 @@ def test_portions_of_changing_size(tmp_path, name, dtype):
             trace.step([(rid, tokens[at:at + n], list(range(n)))], end=[rid] if last else [])
             at += n
             i += 1
-    _check(name, dtype, model_dir, trace, str(tmp_path / "out"), requests, 192)
+    _check(name, dtype, model_dir, trace, str(tmp_path / "out"), requests, _one_at_a_time(name))
 
 
 def _mixed_trace(requests, chunk, seed):
@@ -135,7 +140,7 @@ def _mixed_trace(requests, chunk, seed):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny-a", "tiny-b"])
+@pytest.mark.parametrize("name", ["tiny-a", "tiny-b", "tiny-c"])
 def test_mixed_requests_with_pages_used_again(tmp_path, name, dtype):
     model_dir = helpers.make_folder(tmp_path, name)
     base = _requests(name)
