@@ -85,20 +85,38 @@ static inline bool cb_pdl_enabled() {
     return on;
 }
 
+// cluster_z > 1: the blocks (x, y, 0..cluster_z-1) form a thread-block cluster.
 template <typename... KArgs, typename... Args>
-static inline int cb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                            cudaStream_t stream, Args&&... args) {
+static inline int cb_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, int cluster_z, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (cb_pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_z > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = (unsigned)cluster_z;
+        ++n;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = cb_pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = n;
     const int rc = (int)cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
     if (rc != 0 && cb_launch_failure == 0) cb_launch_failure = rc;
     return rc;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int cb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                            cudaStream_t stream, Args&&... args) {
+    return cb_launch_cluster(kernel, grid, block, smem, stream, 1, std::forward<Args>(args)...);
 }

@@ -12,6 +12,12 @@
 //   SWIGLU_BF16 W = [Wg; Wu] ([2I, K]); the tile holds BN/2 gate rows and the
 //               BN/2 matching up rows; C[M, I] bf16 = silu(g) * u in fp32
 //
+// Few tiles and a long K (a step of 33 to a few hundred rows): the blocks (x, y, 0..S-1)
+// form a cluster that splits K.  Each multiplies its share into its own accumulator; the
+// others then leave theirs in their shared memory, and block 0 of the cluster adds them
+// to its own in the order of the shares (over distributed shared memory, so the order
+// of the sum is fixed), writes the sums back to tensor memory and runs the epilogue.
+//
 // Sizes: any M, N; K a multiple of 8 (a TMA row stride must be a multiple of
 // 16 bytes) with lda, ldw multiples of 8 and 16-byte aligned bases; tails in
 // M, N and K are zero-filled by TMA and masked at the store.  Anything else is
@@ -63,7 +69,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_c, int tma_out,
                     void* __restrict__ c_ptr, int M, int N, int K, int ldc, int inter,
-                    int* __restrict__ status, const RopeArgs ra) {
+                    int k_splits, int* __restrict__ status, const RopeArgs ra) {
     cb_pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     using Storage = SharedStorage<BN, STAGES>;
@@ -72,7 +78,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * BM;
     const int n_tile = blockIdx.x;
-    const int k_blocks = (K + BK - 1) / BK;
+    // this block's share of K: blocks of 64 elements [kb_first, kb_first + k_blocks)
+    const uint32_t split = k_splits > 1 ? tc::cluster_rank() : 0u;
+    const int k_blocks_all = (K + BK - 1) / BK;
+    const int per_split = (k_blocks_all + k_splits - 1) / k_splits;
+    const int kb_first = (int)split * per_split;
+    const int k_blocks = min(per_split, k_blocks_all - kb_first);      // the launcher keeps it positive
     volatile int* abort_flag = &s.abort_flag;
     // tensor-memory columns are allocated in powers of two
     constexpr uint32_t TMEM_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
@@ -114,14 +125,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     break;
                 }
                 tc::mbar_expect_tx(&s.full_bar[st], STAGE_BYTES);
-                tc::tma_load_2d(s.a[st], &map_a, &s.full_bar[st], kb * BK, m0);
+                tc::tma_load_2d(s.a[st], &map_a, &s.full_bar[st], (kb_first + kb) * BK, m0);
                 if (EPI == SWIGLU_BF16) {
                     const int half = BN / 2;
-                    tc::tma_load_2d(s.b[st], &map_w, &s.full_bar[st], kb * BK, n_tile * half);
-                    tc::tma_load_2d(s.b[st] + half * BK * 2, &map_w, &s.full_bar[st], kb * BK,
+                    tc::tma_load_2d(s.b[st], &map_w, &s.full_bar[st], (kb_first + kb) * BK, n_tile * half);
+                    tc::tma_load_2d(s.b[st] + half * BK * 2, &map_w, &s.full_bar[st], (kb_first + kb) * BK,
                                     inter + n_tile * half);
                 } else {
-                    tc::tma_load_2d(s.b[st], &map_w, &s.full_bar[st], kb * BK, n_tile * BN);
+                    tc::tma_load_2d(s.b[st], &map_w, &s.full_bar[st], (kb_first + kb) * BK, n_tile * BN);
                 }
                 armed = kb + 1;
             }
@@ -134,6 +145,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                         if (tc::mbar_try_wait(&s.full_bar[st], (kb / STAGES) & 1)) break;
                 }
             }
+        }
+        if (k_splits > 1) {                 // the two barriers of the epilogue warps
+            __syncwarp();
+            tc::cluster_sync_all();
+            tc::cluster_sync_all();
         }
     } else if (warp == 1) {
         // ---- MMA issuer --------------------------------------------------------
@@ -159,6 +175,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                 tc::umma_commit(&s.empty_bar[st]);      // stage free once these MMAs are done
             }
             if (ok) tc::umma_commit(&s.tmem_full_bar);   // accumulator complete
+        }
+        if (k_splits > 1) {
+            __syncwarp();
+            tc::cluster_sync_all();
+            tc::cluster_sync_all();
         }
     } else {
         // ---- epilogue: warps 2..5, lane quarter = warp % 4 -----------------------
@@ -211,9 +232,74 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         bool ok = tc::mbar_wait(&s.tmem_full_bar, 0, abort_flag);
         if (!ok && !*abort_flag) tc::give_up(abort_flag, status, tc::ST_EPILOGUE_TIMEOUT);
         ok = __all_sync(0xffffffffu, ok);
+        const uint32_t lane_addr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
+        if (k_splits > 1) {
+            // Shares of K: a block other than the cluster's first leaves its accumulator in
+            // its shared memory (the ring of stages is free by now) as [4 columns][row], so
+            // that neighbouring threads touch neighbouring 16 bytes; the first block adds
+            // the shares in their order and puts the sums back into tensor memory.
+            float4* part = reinterpret_cast<float4*>(s.a[0]);
+            const int r = quarter * 32 + lane;
+            if (split != 0 && ok) {
+                tc::tc_fence_after_sync();
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t v[32];
+                    tc::tmem_ld_32x32(lane_addr + c0, v);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        part[((c0 >> 2) + q) * BM + r] =
+                            make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                        __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+                }
+            }
+            tc::cluster_sync_all();
+            if (split == 0 && ok) {
+                // 16 columns at a time, and the loads from up to four other blocks go out together
+                // (a round trip over the cluster's network per four blocks, not per block)
+                tc::tc_fence_after_sync();
+                const uint32_t mine = tc::smem_u32(part);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    uint32_t v[16];
+                    tc::tmem_ld_32x16(lane_addr + c0, v);
+                    tc::tmem_ld_wait();
+#pragma unroll 1
+                    for (int sp0 = 1; sp0 < k_splits; sp0 += 4) {          // four blocks' loads at a time
+                        float4 o[4][4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            if (sp0 + i < k_splits) {
+                                const uint32_t theirs = tc::cluster_map(mine, (uint32_t)(sp0 + i)) +
+                                                        (uint32_t)(((c0 >> 2) * BM + r) * 16);
+#pragma unroll
+                                for (int q = 0; q < 4; ++q)
+                                    o[i][q] = tc::cluster_ld_f4(theirs + (uint32_t)(q * BM * 16));
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            if (sp0 + i < k_splits) {
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    v[4 * q] = __float_as_uint(__uint_as_float(v[4 * q]) + o[i][q].x);
+                                    v[4 * q + 1] = __float_as_uint(__uint_as_float(v[4 * q + 1]) + o[i][q].y);
+                                    v[4 * q + 2] = __float_as_uint(__uint_as_float(v[4 * q + 2]) + o[i][q].z);
+                                    v[4 * q + 3] = __float_as_uint(__uint_as_float(v[4 * q + 3]) + o[i][q].w);
+                                }
+                            }
+                        }
+                    }
+                    tc::tmem_st_32x16(lane_addr + c0, v);
+                }
+                tc::tmem_st_wait();
+            }
+            tc::cluster_sync_all();          // the others' shared memory may go now
+            if (split != 0) ok = false;      // the first block alone has the epilogue
+        }
         if (ok) {
             tc::tc_fence_after_sync();
-            const uint32_t lane_addr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
             if (EPI == ROPE_APPEND) {
                 // A thread owns one token's row of the tile: whole heads of head_dim columns,
                 // taken in pairs of 32-column chunks (j, j + head_dim / 2), rotated in
@@ -498,7 +584,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 
 template <int BN, int STAGES, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, int K, int ldc,
-           int inter, int* status, cudaStream_t stream, const RopeArgs& ra = RopeArgs{}) {
+           int inter, int k_splits, int* status, cudaStream_t stream, const RopeArgs& ra = RopeArgs{}) {
+    // shares of K: at most 8 blocks in a cluster, every share at least one block of 64
+    // elements, and a block's accumulator (128 x BN fp32) has to fit in the ring of stages
+    if (k_splits < 1) k_splits = 1;
+    if (k_splits > 1) {
+        const int kb = (K + BK - 1) / BK, per = (kb + k_splits - 1) / k_splits;
+        if (k_splits > 8 || (k_splits - 1) * per >= kb || (size_t)BM * BN * 4 > (size_t)STAGES * (BM + BN) * BK * 2)
+            return CB_ERR_UNSUPPORTED;
+    }
     // the output goes through shared memory and TMA where its rows allow it
     const bool f32 = EPI == STORE_F32 || EPI == ACCUM_F32;
     const int esize = f32 ? 4 : 2;
@@ -521,20 +615,20 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, 
         configured = true;
     }
     const int n_cols = EPI == SWIGLU_BF16 ? 2 * inter : N;
-    dim3 grid((n_cols + BN - 1) / BN, (M + BM - 1) / BM);
-    cb_launch(gemm_tcgen05_kernel<BN, STAGES, EPI>, dim3(grid), dim3(192), smem, stream, ma, mw, mc, tma_out,
-              C, M, N, K, ldc, inter, status, ra);
+    dim3 grid((n_cols + BN - 1) / BN, (M + BM - 1) / BM, k_splits);
+    cb_launch_cluster(gemm_tcgen05_kernel<BN, STAGES, EPI>, dim3(grid), dim3(192), smem, stream, k_splits,
+                      ma, mw, mc, tma_out, C, M, N, K, ldc, inter, k_splits, status, ra);
     return cb_last_error();
 }
 
 template <int BN, int STAGES>
 int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N,
-               int K, int ldc, int inter, int* status, cudaStream_t stream) {
+               int K, int ldc, int inter, int ks, int* status, cudaStream_t stream) {
     switch (epi) {
-        case STORE_BF16: return launch<BN, STAGES, STORE_BF16>(ma, mw, C, M, N, K, ldc, inter, status, stream);
-        case STORE_F32: return launch<BN, STAGES, STORE_F32>(ma, mw, C, M, N, K, ldc, inter, status, stream);
-        case ACCUM_F32: return launch<BN, STAGES, ACCUM_F32>(ma, mw, C, M, N, K, ldc, inter, status, stream);
-        case SWIGLU_BF16: return launch<BN, STAGES, SWIGLU_BF16>(ma, mw, C, M, N, K, ldc, inter, status, stream);
+        case STORE_BF16: return launch<BN, STAGES, STORE_BF16>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream);
+        case STORE_F32: return launch<BN, STAGES, STORE_F32>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream);
+        case ACCUM_F32: return launch<BN, STAGES, ACCUM_F32>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream);
+        case SWIGLU_BF16: return launch<BN, STAGES, SWIGLU_BF16>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream);
     }
     return CB_ERR_UNSUPPORTED;
 }
@@ -546,8 +640,9 @@ int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, void* C, i
 // block per SM; 2 = three stages, so that two blocks share an SM and one's prologue and
 // epilogue run beside the other's products (tile widths up to 128).
 // status: device int, stays 0 unless a wait ran out.
+// k_splits: 1, or the number of blocks (at most 8) that share a tile's K as a cluster.
 CB_EXPORT int cb_gemm_tcgen05(const void* A, const void* W, void* C, int M, int N, int K, int lda,
-                              int ldw, int ldc, int epi, int bn, int per_sm, int* status,
+                              int ldw, int ldc, int epi, int bn, int per_sm, int k_splits, int* status,
                               void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15))
@@ -562,19 +657,19 @@ CB_EXPORT int cb_gemm_tcgen05(const void* A, const void* W, void* C, int M, int 
     const int inter = epi == SWIGLU_BF16 ? N : 0;
     if (per_sm == 2) {
         switch (bn) {
-            case 64: return launch_epi<64, 3>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
-            case 96: return launch_epi<96, 3>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
-            case 128: return launch_epi<128, 3>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
+            case 64: return launch_epi<64, 3>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
+            case 96: return launch_epi<96, 3>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
+            case 128: return launch_epi<128, 3>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
         }
         return CB_ERR_UNSUPPORTED;
     }
     switch (bn) {
-        case 64: return launch_epi<64, 6>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
-        case 96: return launch_epi<96, 6>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
-        case 128: return launch_epi<128, 5>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
-        case 160: return launch_epi<160, 5>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
-        case 192: return launch_epi<192, 5>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
-        case 256: return launch_epi<256, 4>(epi, ma, mw, C, M, N, K, ldc, inter, status, s);
+        case 64: return launch_epi<64, 6>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
+        case 96: return launch_epi<96, 6>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
+        case 128: return launch_epi<128, 5>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
+        case 160: return launch_epi<160, 5>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
+        case 192: return launch_epi<192, 5>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
+        case 256: return launch_epi<256, 4>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
     }
     return CB_ERR_UNSUPPORTED;
 }
@@ -588,7 +683,8 @@ CB_EXPORT int cb_gemm_tcgen05_rope(const void* A, const void* W, void* q_out, in
                                    const int* positions, const int* row_request,
                                    const int* block_table, int table_stride, void* k_cache,
                                    void* v_cache, int n_heads, int n_kv_heads, int head_dim,
-                                   int page_tokens, int write_cache, int* status, void* stream) {
+                                   int page_tokens, int write_cache, int k_splits, int* status,
+                                   void* stream) {
     if (M <= 0) return 0;
     if (K <= 0 || (K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) ||
         head_dim <= 0 || (head_dim & 63) || bn % head_dim != 0 || (ldq & 7) || ((uintptr_t)q_out & 15) ||
@@ -607,10 +703,10 @@ CB_EXPORT int cb_gemm_tcgen05_rope(const void* A, const void* W, void* q_out, in
     ra.page_tokens = page_tokens; ra.write_cache = write_cache;
     cudaStream_t s = (cudaStream_t)stream;
     switch (bn) {
-        case 64: return launch<64, 6, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, status, s, ra);
-        case 128: return launch<128, 5, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, status, s, ra);
-        case 192: return launch<192, 5, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, status, s, ra);
-        case 256: return launch<256, 4, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, status, s, ra);
+        case 64: return launch<64, 6, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, k_splits, status, s, ra);
+        case 128: return launch<128, 5, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, k_splits, status, s, ra);
+        case 192: return launch<192, 5, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, k_splits, status, s, ra);
+        case 256: return launch<256, 4, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, k_splits, status, s, ra);
     }
     return CB_ERR_UNSUPPORTED;
 }

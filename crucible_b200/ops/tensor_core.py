@@ -73,8 +73,40 @@ N_SMS = 148
 
 
 def _tile_of(tile):
-    """`tile` as callers may give it: a width, or (width, blocks per SM)."""
+    """`tile` as callers may give it: a width, (width, blocks per SM), or
+    (width, blocks per SM, shares of K)."""
     return (tile, 1) if isinstance(tile, int) else tuple(tile)
+
+
+# Shares of K, measured on B200 at 33 to 512 rows: a block's chain costs about 0.32 us per
+# block of 64 elements of K (0.43 us for tiles wider than 128 columns: the ring of stages
+# in flight over the latency of a load, not the tile's bytes, sets it), a cluster costs
+# about 2 us more than a lone block, and the first block of a cluster takes about 0.5 us
+# to pull 32 KB of another block's sums.  Clusters of 3 and 4 need room to be placed inside
+# one GPC, so they may not fill the SMs to the last one.
+K_SPLIT_STEP_US = (0.32, 0.43)
+K_SPLIT_CLUSTER_US = 2.0
+K_SPLIT_PULL_US = 0.5
+K_SPLIT_BLOCK_LIMIT = {2: 148, 3: 120, 4: 128}
+K_SPLIT_MIN_GAIN_US = 1.0
+
+
+def k_splits(m: int, n_cols: int, k: int, bn: int) -> int:
+    """Blocks that share one tile's K as a cluster (1: none).  A step of 33 to a few
+    hundred rows has few tiles, each a chain of K / 64 loads and products on one SM while
+    most SMs idle; shares of K spread the chain over the idle SMs."""
+    tiles = -(-m // 128) * -(-n_cols // bn)
+    k_blocks = -(-k // 64)
+    step = K_SPLIT_STEP_US[1 if bn > 128 else 0]
+    best, best_cost = 1, k_blocks * step - K_SPLIT_MIN_GAIN_US
+    for s, limit in K_SPLIT_BLOCK_LIMIT.items():
+        per = -(-k_blocks // s)
+        if tiles * s > limit or (s - 1) * per >= k_blocks:
+            continue
+        cost = per * step + K_SPLIT_CLUSTER_US + K_SPLIT_PULL_US * (s - 1) * bn / 64
+        if cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 def _tile_width(m: int, n_cols: int, epi: int = 1, multiple_of: int = 1):
@@ -96,13 +128,15 @@ def _tile_width(m: int, n_cols: int, epi: int = 1, multiple_of: int = 1):
     return best, 1
 
 
-def _gemm(a, w, out, n, epi, bn, per_sm=1) -> bool:
+def _gemm(a, w, out, n, epi, bn, per_sm=1, splits=None) -> bool:
     lib = build.load("gemm_tcgen05")
+    if splits is None:
+        splits = k_splits(a.shape[0], 2 * n if epi == SWIGLU_BF16 else n, a.shape[1], bn)
     code = lib.cb_gemm_tcgen05(
         _c_void_p(a.data_ptr()), _c_void_p(w.data_ptr()), _c_void_p(out.data_ptr()),
         _c_int(a.shape[0]), _c_int(n), _c_int(a.shape[1]), _c_int(a.stride(0)),
         _c_int(w.stride(0)), _c_int(out.stride(0)), _c_int(epi), _c_int(bn), _c_int(per_sm),
-        _c_void_p(status_word(a.device).data_ptr()), _stream())
+        _c_int(splits), _c_void_p(status_word(a.device).data_ptr()), _stream())
     if code == _UNSUPPORTED:
         return False
     if code != 0:
@@ -191,8 +225,8 @@ def linear(a, w, out, *, accumulate=False, tile=None) -> bool:
     if tile is None and ((a.shape[0] <= SKINNY_ROWS and w.numel() * 2 >= SKINNY_MIN_BYTES)
                          or (a.shape[0] <= 64 and w.shape[0] >= SKINNY_WIDE_N)):
         return _gemm_skinny(a, w, out, w.shape[0], epi)
-    bn, per_sm = _tile_of(tile) if tile else _tile_width(a.shape[0], w.shape[0], epi)
-    return _gemm(a, w, out, w.shape[0], epi, bn, per_sm)
+    bn, per_sm, *splits = _tile_of(tile) if tile else _tile_width(a.shape[0], w.shape[0], epi)
+    return _gemm(a, w, out, w.shape[0], epi, bn, per_sm, splits[0] if splits else None)
 
 
 def linear_swiglu(h, gate_up, out, tile=None) -> bool:
@@ -201,8 +235,8 @@ def linear_swiglu(h, gate_up, out, tile=None) -> bool:
     inter = gate_up.shape[0] // 2
     if tile is None and h.shape[0] <= SKINNY_ROWS and gate_up.numel() * 2 >= SKINNY_MIN_BYTES:
         return _gemm_skinny(h, gate_up, out, inter, SWIGLU_BF16)
-    bn, per_sm = _tile_of(tile) if tile else _tile_width(h.shape[0], 2 * inter, SWIGLU_BF16)
-    return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn, per_sm)
+    bn, per_sm, *splits = _tile_of(tile) if tile else _tile_width(h.shape[0], 2 * inter, SWIGLU_BF16)
+    return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn, per_sm, splits[0] if splits else None)
 
 
 def linear_rope_append(h, wqkv, qkv, n_heads, n_kv_heads, head_dim, cos, sin, rotary_dim, ctx, cache,
@@ -230,6 +264,7 @@ def linear_rope_append(h, wqkv, qkv, n_heads, n_kv_heads, head_dim, cos, sin, ro
         _c_void_p(table.data_ptr()), _c_int(table.shape[1]), _c_void_p(k_cache.data_ptr()),
         _c_void_p(v_cache.data_ptr()), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
         _c_int(cache.page_tokens), _c_int(1 if binding.write else 0),
+        _c_int(k_splits(h.shape[0], wqkv.shape[0], h.shape[1], bn)),
         _c_void_p(status_word(h.device).data_ptr()), _stream())
     if code == _UNSUPPORTED:
         return False

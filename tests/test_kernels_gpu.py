@@ -127,6 +127,57 @@ def test_linear_swiglu_tensor_core(m, inter, k, tile):
     tensor_core.check_status(DEV)
 
 
+@pytest.mark.parametrize("tile", [64, 128, 256])
+@pytest.mark.parametrize("splits", [2, 3, 8])
+@pytest.mark.parametrize("m,n,k", [(40, 768, 2048), (64, 100, 520), (130, 192, 1000), (300, 96, 4096)])
+def test_linear_tensor_core_shares_of_k(m, n, k, splits, tile):
+    """A cluster of blocks shares one tile's K and sums over distributed shared memory;
+    a number of shares that would leave one empty is refused."""
+    from crucible_b200.ops import tensor_core
+    a = (torch.rand(m, k, device=DEV) + 0.5).bfloat16()
+    w = (torch.rand(n, k, device=DEV) * 0.1 + 0.05).bfloat16()
+    k_blocks = -(-k // 64)
+    fits = (splits - 1) * -(-k_blocks // splits) < k_blocks
+    out = torch.empty(m, n, device=DEV)
+    assert tensor_core.linear(a, w, out, tile=(tile, 1, splits)) is fits
+    if not fits:
+        return
+    ref = a.double() @ w.double().T
+    assert rel(out, ref) < 1e-5
+    again = torch.empty(m, n, device=DEV)
+    assert tensor_core.linear(a, w, again, tile=(tile, 1, splits))
+    assert torch.equal(out, again)                     # the order of the sum is fixed
+    out16 = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    assert tensor_core.linear(a, w, out16, tile=(tile, 1, splits))
+    assert rel(out16, ref) < 5e-3
+    base = torch.randn(m, n, device=DEV)
+    acc = base.clone()
+    assert tensor_core.linear(a, w, acc, accumulate=True, tile=(tile, 1, splits))
+    assert rel(acc, ref + base.double()) < 1e-5
+    inter = n // 2
+    h = torch.randn(m, k, device=DEV).bfloat16()
+    w2 = (torch.randn(2 * inter, k, device=DEV) * 0.05).bfloat16()
+    act = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
+    assert tensor_core.linear_swiglu(h, w2, act, tile=(tile, 1, splits))
+    y = h.double() @ w2.double().T
+    g, u = y[:, :inter], y[:, inter:]
+    assert rel(act, g / (1 + torch.exp(-g)) * u) < 6e-3
+    tensor_core.check_status(DEV)
+
+
+def test_linear_tensor_core_takes_shares_of_k_by_itself():
+    from crucible_b200.ops import tensor_core
+    m, n, k = 64, 768, 2048
+    assert tensor_core.k_splits(m, n, k, 64) == 4
+    a = (torch.rand(m, k, device=DEV) + 0.5).bfloat16()
+    w = (torch.rand(n, k, device=DEV) * 0.1 + 0.05).bfloat16()
+    base = torch.randn(m, n, device=DEV)
+    acc = base.clone()
+    assert tensor_core.linear(a, w, acc, accumulate=True)
+    assert rel(acc, a.double() @ w.double().T + base.double()) < 1e-5
+    tensor_core.check_status(DEV)
+
+
 @pytest.mark.parametrize("splits", [1, 2, 5, None])
 @pytest.mark.parametrize("m,n,k", [(1, 64, 64), (7, 509, 96), (16, 1280, 768), (33, 768, 2048),
                                    (64, 200, 320), (8, 50304, 768), (3, 100, 1000)])
@@ -257,12 +308,14 @@ def test_small_batch_large_weights_take_other_paths():
     assert small_batch.linear(lazy, huge, torch.empty(m, huge.shape[0], device=DEV)) is False
 
 
-@pytest.mark.parametrize("hd,n_heads,n_kv,rows", [(64, 6, 2, 300), (64, 5, 1, 40), (128, 3, 1, 150)])
+@pytest.mark.parametrize("hd,n_heads,n_kv,rows,d", [(64, 6, 2, 300, 256), (64, 5, 1, 40, 256),
+                                                    (128, 3, 1, 150, 256), (64, 6, 2, 60, 1024)])
 @pytest.mark.parametrize("write", [True, False])
-def test_linear_rope_append_tensor_core(hd, n_heads, n_kv, rows, write):
-    """The q/k/v product for many rows with rotation and cache write in its epilogue."""
+def test_linear_rope_append_tensor_core(hd, n_heads, n_kv, rows, d, write):
+    """The q/k/v product for many rows with rotation and cache write in its epilogue (the
+    last case: few tiles and a long K, so clusters share K)."""
     from crucible_b200.ops import tensor_core
-    d, page = 256, 16
+    page = 16
     torch.manual_seed(rows)
     n_req = 3
     # rows of three requests, each at its own positions; pages shuffled
