@@ -10,6 +10,7 @@
 // Reference counterparts: `attention_decode_paged_f32`
 // (engine/kernels/kernels.cu:1741-1839) and `attention_prefill_paged_impl`
 // (:1844-1925): scores scaled by hd^-1/2, max, exp(s - max), sum, one division.
+#define CB_PDL_BIT 8      // this file's bit in CRUCIBLE_PDL
 #include "common.cuh"
 
 namespace {

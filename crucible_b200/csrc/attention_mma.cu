@@ -24,6 +24,7 @@
 // (engine/kernels/kernels.cu:2257-2275), `attention_decode_paged_f32` (:1741),
 // and the split idea of `attention_partial_f32` / `attention_combine_f32`
 // (:692-850).
+#define CB_PDL_BIT 7      // this file's bit in CRUCIBLE_PDL
 #include "common.cuh"
 
 namespace {

@@ -24,6 +24,7 @@
 // kernel runs.  Every wait is bounded (tc_common.cuh).
 // Reference counterpart: `attention_prefill_exact_*`
 // (engine/kernels/kernels.cu:2257-2275).
+#define CB_PDL_BIT 1      // this file's bit in CRUCIBLE_PDL
 #include "common.cuh"
 #include "tc_common.cuh"
 

@@ -69,26 +69,48 @@ static inline int cb_last_error() {
 // wait -- index arithmetic, barrier and tensor-memory set-up, loads of weights,
 // which no kernel writes -- overlaps the tail of its predecessor.  Each kernel
 // calls cb_pdl_trigger() at its start so that its successor may be scheduled
-// early.  The attribute is set only if CRUCIBLE_PDL=1 is in the environment (off by
-// default: measured on B200 inside captured graphs it changed step times by less
-// than the noise); without it the two device calls are no-ops.
+// early.  Which kernels get the attribute was measured on B200 inside captured graphs,
+// source file by source file (CB_PDL_BIT, defined before this header is included, is the
+// file's bit): the tensor-core products for more than 32 rows gain most (their barriers,
+// tensor memory and descriptors are set up under the kernel before: 1.09 -> 1.02 ms per
+// 2,048-token prefill, 0.93 -> 0.88 ms per batch-64 decode step); the prompt attention a
+// little; the split decode attention gains beside the few-row kernels (0.42 -> 0.41 ms at
+// batch 8) and loses beside the tensor-core products (0.87 -> 0.92 ms at batch 64), so its
+// launcher allows it for steps of at most 32 rows; norms and the like gain in small
+// launches and lose in large ones (CB_PDL_MAX_BLOCKS); the few-row products lose (0.41 ->
+// 0.44 ms).  Hence the default below.  CRUCIBLE_PDL in the environment overrides it: a
+// number is taken as the files' bits, "all" sets every bit.  Without the attribute the
+// two device calls are no-ops.
 __device__ __forceinline__ void cb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void cb_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 #include <cstdlib>
+#include <cstring>
 #include <utility>
+#ifndef CB_PDL_BIT
+#define CB_PDL_BIT 31
+#endif
+#ifndef CB_PDL_MAX_BLOCKS
+#define CB_PDL_MAX_BLOCKS 0          // 0: launches of any size
+#endif
+// bits: 0 gemm_tcgen05, 1 attention_tcgen05, 2 attention_decode_tcgen05, 3 elementwise
+#define CB_PDL_DEFAULT_MASK 0xFul
 static inline bool cb_pdl_enabled() {
     static const bool on = [] {
         const char* v = std::getenv("CRUCIBLE_PDL");
-        return v && v[0] == '1';
+        unsigned long mask = CB_PDL_DEFAULT_MASK;
+        if (v && std::strcmp(v, "all") == 0) mask = ~0ul;
+        else if (v && v[0]) mask = std::strtoul(v, nullptr, 0);
+        return ((mask >> CB_PDL_BIT) & 1ul) != 0;
     }();
     return on;
 }
 
 // cluster_z > 1: the blocks (x, y, 0..cluster_z-1) form a thread-block cluster.
+// allow_early: the launcher's own word on the programmatic launch (false: never).
 template <typename... KArgs, typename... Args>
-static inline int cb_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                    cudaStream_t stream, int cluster_z, Args&&... args) {
+static inline int cb_launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                               cudaStream_t stream, int cluster_z, bool allow_early, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -96,7 +118,8 @@ static inline int cb_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     int n = 0;
-    if (cb_pdl_enabled()) {
+    const size_t blocks = (size_t)grid.x * grid.y * grid.z;
+    if (allow_early && cb_pdl_enabled() && (CB_PDL_MAX_BLOCKS == 0 || blocks <= CB_PDL_MAX_BLOCKS)) {
         attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         ++n;
@@ -116,7 +139,13 @@ static inline int cb_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 bl
 }
 
 template <typename... KArgs, typename... Args>
+static inline int cb_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, int cluster_z, Args&&... args) {
+    return cb_launch_ex(kernel, grid, block, smem, stream, cluster_z, true, std::forward<Args>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
 static inline int cb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                             cudaStream_t stream, Args&&... args) {
-    return cb_launch_cluster(kernel, grid, block, smem, stream, 1, std::forward<Args>(args)...);
+    return cb_launch_ex(kernel, grid, block, smem, stream, 1, true, std::forward<Args>(args)...);
 }

@@ -36,6 +36,7 @@
 // Reference counterparts: `gemv_batch_i8_b*` (engine/kernels/kernels.cu:1598),
 // `mlp_swiglu_f32` (:637), `rope_rows_f32` (:1677), `cache_store_rows_paged_f32`
 // (:1713).
+#define CB_PDL_BIT 4      // this file's bit in CRUCIBLE_PDL
 #include "common.cuh"
 
 namespace {

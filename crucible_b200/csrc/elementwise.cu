@@ -2,6 +2,8 @@
 // and rotary encoding fused with the write of keys and values into the paged
 // cache.  All arithmetic is fp32; T is the storage type of activations
 // (float for the 32-bit engine, __nv_bfloat16 for the bfloat16 engine).
+#define CB_PDL_BIT 3      // this file's bit in CRUCIBLE_PDL
+#define CB_PDL_MAX_BLOCKS 148
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------

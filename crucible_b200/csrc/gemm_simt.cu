@@ -7,6 +7,7 @@
 //
 // Reference counterpart: `gemm_f32` (engine/kernels/kernels.cu:922), 16x16
 // scalar tiles; this one uses 64x64 tiles with a 4x4 micro-tile per thread.
+#define CB_PDL_BIT 9      // this file's bit in CRUCIBLE_PDL
 #include "common.cuh"
 
 namespace {

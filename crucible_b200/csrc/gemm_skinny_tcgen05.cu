@@ -18,6 +18,7 @@
 // aligned (TMA); otherwise refused.
 // Reference counterpart: the batched GEMV family `gemv_batch_i8_b*`
 // (engine/kernels/kernels.cu:1598-1607): read W once for all rows.
+#define CB_PDL_BIT 5      // this file's bit in CRUCIBLE_PDL
 #include "common.cuh"
 #include "tc_common.cuh"
 

@@ -25,6 +25,7 @@
 //
 // Reference counterpart: `gemm_f32_wmma` (engine/kernels/kernels.cu:2420-2520),
 // fp16 wmma tiles 16x64 / 64x64.
+#define CB_PDL_BIT 0      // this file's bit in CRUCIBLE_PDL
 #include "common.cuh"
 #include "tc_common.cuh"
 

@@ -12,6 +12,7 @@
 //    number per sampled token, drawn by the host from the request's own
 //    generator, so a request's sequence does not depend on its neighbours.
 //  * temperature <= 0 means greedy and uses no randomness (:290-298).
+#define CB_PDL_BIT 6      // this file's bit in CRUCIBLE_PDL
 #include "common.cuh"
 #include "no_alloc_argmax.h"
 
