@@ -172,7 +172,6 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                                 const __grid_constant__ CUtensorMap map_v,
                                 const __grid_constant__ CUtensorMap run_k,
                                 const __grid_constant__ CUtensorMap run_v, const DecodeParams p) {
-    cb_pdl_trigger();
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     using Store = Storage<HD>;
     constexpr int NH = HD / 64;                       // halves of the head size
@@ -311,6 +310,9 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     tc::tc_fence_before_sync();
     __syncthreads();
     tc::tc_fence_after_sync();
+    // the query rows are staged and the first tiles' copies are on their way: the kernel
+    // after this one may start (its first loads then do not get in the way of these)
+    cb_pdl_trigger();
     const uint32_t tmem_s = s.tmem_base;          // + 16 for the second buffer
     const uint32_t tmem_o = s.tmem_base + 64;
 

@@ -77,8 +77,11 @@ static inline int cb_last_error() {
 // little; the split decode attention gains beside the few-row kernels (0.42 -> 0.41 ms at
 // batch 8) and loses beside the tensor-core products (0.87 -> 0.92 ms at batch 64), so its
 // launcher allows it for steps of at most 32 rows; norms and the like gain in small
-// launches and lose in large ones (CB_PDL_MAX_BLOCKS); the few-row products lose (0.41 ->
-// 0.44 ms).  Hence the default below.  CRUCIBLE_PDL in the environment overrides it: a
+// launches and lose in large ones (CB_PDL_MAX_BLOCKS); the few-row products lose if they
+// let their successor start at once (0.41 -> 0.44 ms: its loads of weights get in the way of
+// the loads this kernel waits for) and gain if they do so once their own rows are staged
+// (0.41 -> 0.385 ms at batch 8, 0.37 -> 0.35 ms at batch 1), for up to 16 rows.  Hence the
+// default below.  CRUCIBLE_PDL in the environment overrides it: a
 // number is taken as the files' bits, "all" sets every bit.  Without the attribute the
 // two device calls are no-ops.
 __device__ __forceinline__ void cb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -93,8 +96,8 @@ __device__ __forceinline__ void cb_pdl_trigger() { asm volatile("griddepcontrol.
 #ifndef CB_PDL_MAX_BLOCKS
 #define CB_PDL_MAX_BLOCKS 0          // 0: launches of any size
 #endif
-// bits: 0 gemm_tcgen05, 1 attention_tcgen05, 2 attention_decode_tcgen05, 3 elementwise
-#define CB_PDL_DEFAULT_MASK 0xFul
+// bits: 0 gemm_tcgen05, 1 attention_tcgen05, 2 attention_decode_tcgen05, 3 elementwise, 4 decode_small
+#define CB_PDL_DEFAULT_MASK 0x1Ful
 static inline bool cb_pdl_enabled() {
     static const bool on = [] {
         const char* v = std::getenv("CRUCIBLE_PDL");

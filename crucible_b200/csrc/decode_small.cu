@@ -90,7 +90,6 @@ constexpr int BATCH = 8;          // blocks of 32 elements a warp keeps in fligh
 // then meets MT pairs of MMAs, and the rows are staged one group after the other.
 template <bool NORM_IN, int EPI, bool DEEP, int WARPS, int MT>
 __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallParams p) {
-    cb_pdl_trigger();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -286,6 +285,9 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
         asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
+    // the step's rows are staged and this block's weights are on their way: the kernel after
+    // this one may start and ask for its own
+    cb_pdl_trigger();
     // ---- multiply: this warp's blocks of K -------------------------------------------------
     float c[MT][4];
 #pragma unroll
@@ -399,8 +401,9 @@ int launch_rows_as(const SmallParams& p, cudaStream_t s) {
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    cb_launch(small_linear_kernel<NORM_IN, EPI, DEEP, WARPS, MT>, dim3(p.n_tiles), dim3(WARPS * 32), smem,
-              s, p);
+    // started under the kernel before it for up to 16 rows (measured: beyond, it loses)
+    cb_launch_ex(small_linear_kernel<NORM_IN, EPI, DEEP, WARPS, MT>, dim3(p.n_tiles), dim3(WARPS * 32), smem,
+                 s, 1, MT <= 2, p);
     return cb_last_error();
 }
 
