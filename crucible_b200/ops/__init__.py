@@ -147,7 +147,7 @@ def linear(a, w: torch.Tensor, out: torch.Tensor, *, accumulate: bool = False) -
     """`a` is a tensor or a `small_batch.LazyNorm` (rows not yet normalised)."""
     from . import small_batch
     if w.dtype == torch.bfloat16:
-        if a.shape[0] <= small_batch.MAX_ROWS and small_batch.linear(a, w, out, accumulate=accumulate):
+        if a.shape[0] <= small_batch.PREFERRED_ROWS and small_batch.linear(a, w, out, accumulate=accumulate):
             return
         a = small_batch.as_tensor(a)
         from . import tensor_core
@@ -161,7 +161,7 @@ def linear_swiglu(h, gate_up: torch.Tensor, out: torch.Tensor, ctx) -> None:
     """out[T, I] = silu(h Wg^T) * (h Wu^T) with gate_up = [Wg; Wu] of shape [2I, d]."""
     from . import small_batch
     if gate_up.dtype == torch.bfloat16:
-        if h.shape[0] <= small_batch.MAX_ROWS and small_batch.linear_swiglu(h, gate_up, out):
+        if h.shape[0] <= small_batch.PREFERRED_ROWS and small_batch.linear_swiglu(h, gate_up, out):
             return
         h = small_batch.as_tensor(h)
         from . import tensor_core
@@ -181,11 +181,11 @@ def qkv_rope_append(h, wqkv: torch.Tensor, qkv: torch.Tensor, n_heads: int, n_kv
     rotated q in the first columns of `qkv`; the k and v columns of `qkv` are not
     defined afterwards (attention reads keys and values from the cache)."""
     from . import small_batch
-    if (wqkv.dtype == torch.bfloat16 and h.shape[0] <= small_batch.MAX_ROWS
+    if (wqkv.dtype == torch.bfloat16 and h.shape[0] <= small_batch.PREFERRED_ROWS
             and small_batch.qkv_rope_append(h, wqkv, qkv, n_heads, n_kv_heads, head_dim, cos, sin,
                                             rotary_dim, ctx, cache, binding)):
         return
-    if wqkv.dtype == torch.bfloat16 and h.shape[0] > small_batch.MAX_ROWS:
+    if wqkv.dtype == torch.bfloat16 and h.shape[0] > small_batch.PREFERRED_ROWS:
         from . import tensor_core
         if tensor_core.linear_rope_append(small_batch.as_tensor(h), wqkv, qkv, n_heads, n_kv_heads,
                                           head_dim, cos, sin, rotary_dim, ctx, cache, binding):

@@ -21,6 +21,10 @@ from . import build
 build.register_module("decode_small", ["common.cuh"])
 
 MAX_ROWS = 32           # rows these kernels take (in groups of 8)
+PREFERRED_ROWS = 16     # rows up to which the callers choose them: measured on B200, a step of 17
+                        # to 32 rows is as fast or faster through the 128-row tensor-core tiles
+                        # (Llama-3.2-1B sizes at 32 rows: 9.7 against 13.1 us for q/k/v, 15.8
+                        # against 48.5 us for gate/up)
 MAX_LAZY_ROWS = 16      # rows a norm hands over not yet normalised: every block then normalises
                         # them for itself, which beyond 16 rows costs more than a norm kernel
 _c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
@@ -78,11 +82,14 @@ def _done(code: int, what: str) -> bool:
     return True
 
 
-# These kernels are built for latency (a few megabytes of weights per launch).  They
-# stream at about 1.7 TB/s; the TMA-fed tensor-core kernel for few rows reaches the
-# memory's bandwidth but costs a norm kernel and a split-K reduction more, so beyond
-# this size the caller's general path is faster.
+# These kernels are built for latency (a few megabytes of weights per launch): 2.6-3.9 us
+# for the 120M shape's matrices at 8 rows, where the 128-row tiles need 5.4-8.0 us.  They
+# stream at 1.7 to 3.7 TB/s; the TMA-fed tensor-core kernel for few rows reaches 3.5 to
+# 5.5 TB/s but costs a norm kernel and a reduction over K more.  Measured on B200: up to 8
+# rows these kernels hold out to 64 MB (67 MB: 18.1 us with the norm inside against 18.5 us
+# and a norm kernel); with 9 to 16 rows to about 40 MB (50 MB: 24.2 against 17.7 us).
 MAX_WEIGHT_BYTES = 64 << 20
+MAX_WEIGHT_BYTES_TWO_GROUPS = 40 << 20
 # Every block of a product normalises the step's rows for itself.  That is free while the
 # blocks are few; with thousands of blocks it costs as much as the weights, and one norm
 # kernel for all of them is cheaper.
@@ -90,8 +97,9 @@ NORM_FUSE_MAX_BYTES = 8 << 20
 
 
 def _weights_ok(w: torch.Tensor, rows: int) -> bool:
+    limit = MAX_WEIGHT_BYTES if rows <= 8 else MAX_WEIGHT_BYTES_TWO_GROUPS
     return (rows <= MAX_ROWS and w.dtype == torch.bfloat16 and w.is_cuda and w.stride(1) == 1
-            and w.numel() * 2 <= MAX_WEIGHT_BYTES)
+            and w.numel() * 2 <= limit)
 
 
 MAX_OUT_ROWS = 8192     # wider products (the LM head) stream better through the tensor-core kernel

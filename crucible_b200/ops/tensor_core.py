@@ -198,9 +198,11 @@ def _gemm_skinny(a, w, out, n, epi, splits=None) -> bool:
     return True
 
 
-SKINNY_ROWS = 32     # products with at most this many rows run with W on the MMA's M side ...
-SKINNY_MIN_BYTES = 16 << 20   # ... if W is at least this large (it streams; smaller ones are
-                              # latency-bound and the 128-row tiles are quicker to start and end)
+SKINNY_ROWS = 16     # products with at most this many rows run with W on the MMA's M side ...
+SKINNY_MIN_BYTES = 40 << 20   # ... if W is at least this large (it streams: 3.5-5.5 TB/s; smaller
+                              # ones are latency-bound and the 128-row tiles, with K shared by
+                              # clusters, are quicker: 33 MB at 16 rows 16.0 against 23.4 us).  From
+                              # 17 rows on the 128-row tiles are as fast or faster at every size.
 SKINNY_WIDE_N = 8192 # ... and up to 64 rows if W has at least this many rows (the LM head)
 
 
