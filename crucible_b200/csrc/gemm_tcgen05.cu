@@ -110,14 +110,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     __syncthreads();
     tc::tc_fence_after_sync();
     const uint32_t tmem_acc = s.tmem_base;
-    // barriers, tensor memory and descriptors are ready; only now wait for the kernels
-    // before this one, whose outputs the loads below read
+    auto load_w = [&](int kb) {
+        const int st = kb % STAGES;
+        if (EPI == SWIGLU_BF16) {
+            const int half = BN / 2;
+            tc::tma_load_2d(s.b[st], &map_w, &s.full_bar[st], (kb_first + kb) * BK, n_tile * half);
+            tc::tma_load_2d(s.b[st] + half * BK * 2, &map_w, &s.full_bar[st], (kb_first + kb) * BK,
+                            inter + n_tile * half);
+        } else {
+            tc::tma_load_2d(s.b[st], &map_w, &s.full_bar[st], (kb_first + kb) * BK, n_tile * BN);
+        }
+    };
+    // Barriers, tensor memory and descriptors are ready.  The first stages' tiles of W go out
+    // now: W is a weight matrix, which no kernel of the stream writes, so these copies need
+    // not wait for the kernels before this one; A is their output and does.
+    const int w_ahead = k_blocks < STAGES ? k_blocks : STAGES;
+    if (warp == 0 && lane == 0) {
+        for (int kb = 0; kb < w_ahead; ++kb) {
+            tc::mbar_expect_tx(&s.full_bar[kb], STAGE_BYTES);
+            load_w(kb);
+        }
+    }
     cb_pdl_wait();
 
     if (warp == 0) {
         // ---- producer: one thread feeds the ring of stages -------------------
         if (lane == 0) {
-            int armed = 0;
+            int armed = w_ahead;
             for (int kb = 0; kb < k_blocks; ++kb) {
                 const int st = kb % STAGES;
                 const uint32_t round = kb / STAGES;
@@ -125,17 +144,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     tc::give_up(abort_flag, status, tc::ST_PRODUCER_TIMEOUT);
                     break;
                 }
-                tc::mbar_expect_tx(&s.full_bar[st], STAGE_BYTES);
-                tc::tma_load_2d(s.a[st], &map_a, &s.full_bar[st], (kb_first + kb) * BK, m0);
-                if (EPI == SWIGLU_BF16) {
-                    const int half = BN / 2;
-                    tc::tma_load_2d(s.b[st], &map_w, &s.full_bar[st], (kb_first + kb) * BK, n_tile * half);
-                    tc::tma_load_2d(s.b[st] + half * BK * 2, &map_w, &s.full_bar[st], (kb_first + kb) * BK,
-                                    inter + n_tile * half);
-                } else {
-                    tc::tma_load_2d(s.b[st], &map_w, &s.full_bar[st], (kb_first + kb) * BK, n_tile * BN);
+                if (kb >= w_ahead) {
+                    tc::mbar_expect_tx(&s.full_bar[st], STAGE_BYTES);
+                    load_w(kb);
                 }
-                armed = kb + 1;
+                tc::tma_load_2d(s.a[st], &map_a, &s.full_bar[st], (kb_first + kb) * BK, m0);
+                if (kb + 1 > armed) armed = kb + 1;
             }
             if (*abort_flag) {
                 // let our own copies land before the block's shared memory goes away

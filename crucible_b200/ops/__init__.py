@@ -144,7 +144,10 @@ def linear_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *,
 
 
 def linear(a, w: torch.Tensor, out: torch.Tensor, *, accumulate: bool = False) -> None:
-    """`a` is a tensor or a `small_batch.LazyNorm` (rows not yet normalised)."""
+    """`a` is a tensor or a `small_batch.LazyNorm` (rows not yet normalised).  `w` is a weight
+    matrix: something no kernel of the step writes.  The bfloat16 kernels ask for it before the
+    kernels ahead of them in the stream have finished (only `a` and `out` wait for those); a
+    matrix computed during the step belongs in `linear_plain`."""
     from . import small_batch
     if w.dtype == torch.bfloat16:
         if a.shape[0] <= small_batch.PREFERRED_ROWS and small_batch.linear(a, w, out, accumulate=accumulate):
