@@ -71,7 +71,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_c, int tma_out,
                     void* __restrict__ c_ptr, int M, int N, int K, int ldc, int inter,
                     int k_splits, int* __restrict__ status, const RopeArgs ra) {
-    cb_pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     using Storage = SharedStorage<BN, STAGES>;
     Storage& s = *reinterpret_cast<Storage*>(
@@ -132,6 +131,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         }
     }
     cb_pdl_wait();
+    cb_pdl_trigger();
 
     if (warp == 0) {
         // ---- producer: one thread feeds the ring of stages -------------------
