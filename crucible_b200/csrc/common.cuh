@@ -96,8 +96,9 @@ __device__ __forceinline__ void cb_pdl_trigger() { asm volatile("griddepcontrol.
 #ifndef CB_PDL_MAX_BLOCKS
 #define CB_PDL_MAX_BLOCKS 0          // 0: launches of any size
 #endif
-// bits: 0 gemm_tcgen05, 1 attention_tcgen05, 2 attention_decode_tcgen05, 3 elementwise, 4 decode_small
-#define CB_PDL_DEFAULT_MASK 0x1Ful
+// bits: 0 gemm_tcgen05, 1 attention_tcgen05, 2 attention_decode_tcgen05, 3 elementwise, 4 decode_small,
+// 5 gemm_skinny_tcgen05
+#define CB_PDL_DEFAULT_MASK 0x3Ful
 static inline bool cb_pdl_enabled() {
     static const bool on = [] {
         const char* v = std::getenv("CRUCIBLE_PDL");

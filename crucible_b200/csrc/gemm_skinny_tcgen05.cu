@@ -69,7 +69,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
                    const __grid_constant__ CUtensorMap map_a, void* __restrict__ c_ptr, int M,
                    int N, int K, int ldc, int inter, int splits, float* __restrict__ partial,
                    int* __restrict__ counters, int* __restrict__ status) {
-    cb_pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     using Storage = SkinnyStorage<MT>;
     Storage& s = *reinterpret_cast<Storage*>(
@@ -105,13 +104,33 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
     __syncthreads();
     tc::tc_fence_after_sync();
     const uint32_t tmem_acc = s.tmem_base;
-    // barriers, tensor memory and descriptors are ready; only now wait for the kernels
-    // before this one, whose outputs the loads below read
+    auto load_w = [&](int i) {
+        const int st = i % STAGES;
+        const int kx = (kb0 + i) * BK;
+        if (EPI == SWIGLU_BF16) {
+            tc::tma_load_2d(s.w[st], &map_w, &s.full_bar[st], kx, tile * (WM / 2));
+            tc::tma_load_2d(s.w[st] + (WM / 2) * BK * 2, &map_w, &s.full_bar[st], kx,
+                            inter + tile * (WM / 2));
+        } else {
+            tc::tma_load_2d(s.w[st], &map_w, &s.full_bar[st], kx, tile * WM);
+        }
+    };
+    // Barriers, tensor memory and descriptors are ready.  The first stages' tiles of W go out
+    // now (a weight matrix, which no kernel of the stream writes); the step's rows are the
+    // output of the kernels before this one and wait for them.
+    const int w_ahead = n_kb < STAGES ? n_kb : STAGES;
+    if (warp == 0 && lane == 0) {
+        for (int i = 0; i < w_ahead; ++i) {
+            tc::mbar_expect_tx(&s.full_bar[i], STAGE_BYTES);
+            load_w(i);
+        }
+    }
     cb_pdl_wait();
+    cb_pdl_trigger();
 
     if (warp == 0) {
         if (lane == 0) {
-            int armed = 0;
+            int armed = w_ahead;
             for (int i = 0; i < n_kb; ++i) {
                 const int st = i % STAGES;
                 const uint32_t round = i / STAGES;
@@ -119,17 +138,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
                     tc::give_up(abort_flag, status, tc::ST_PRODUCER_TIMEOUT);
                     break;
                 }
-                const int kx = (kb0 + i) * BK;
-                tc::mbar_expect_tx(&s.full_bar[st], STAGE_BYTES);
-                if (EPI == SWIGLU_BF16) {
-                    tc::tma_load_2d(s.w[st], &map_w, &s.full_bar[st], kx, tile * (WM / 2));
-                    tc::tma_load_2d(s.w[st] + (WM / 2) * BK * 2, &map_w, &s.full_bar[st], kx,
-                                    inter + tile * (WM / 2));
-                } else {
-                    tc::tma_load_2d(s.w[st], &map_w, &s.full_bar[st], kx, tile * WM);
+                if (i >= w_ahead) {
+                    tc::mbar_expect_tx(&s.full_bar[st], STAGE_BYTES);
+                    load_w(i);
                 }
-                tc::tma_load_2d(s.a[st], &map_a, &s.full_bar[st], kx, 0);
-                armed = i + 1;
+                tc::tma_load_2d(s.a[st], &map_a, &s.full_bar[st], (kb0 + i) * BK, 0);
+                if (i + 1 > armed) armed = i + 1;
             }
             if (*abort_flag) {
                 const int first = armed > STAGES ? armed - STAGES : 0;
