@@ -52,12 +52,21 @@ struct TcAttnParams {
 
 // HD: the head size, 64 or 128.  Operands whose contracted or free dimension is the head
 // size lie in shared memory as HD / 64 halves of [rows][128 bytes] (one swizzle atom wide).
-// Head size 64: three K/V stages and two P buffers; 128: two stages and one P buffer (what
-// 227 KB hold), so the softmax of a tile then waits for the second MMA of the tile before.
-template <int HD>
+// Head size 64 has two forms.  The roomy one: three K/V stages, two P buffers, two buffers of
+// scores, an SM to itself (176 KB, all 512 columns of tensor memory); it is the quicker block,
+// and the right one while all blocks of a launch find a place at once.  The lean one: two
+// stages, one P buffer, one buffer of scores (112 KB, 256 columns), so that two blocks share
+// an SM and one's waits (for a copy, an MMA, the scores' way out of tensor memory) are filled
+// by the other's exponentials; its one buffer of scores is handed back to the MMA thread as
+// soon as the softmax has the scores in registers, so the next tile's first MMA still runs
+// beside this tile's softmax.  It is the right one when the launch has more blocks than places
+// (measured on B200: 4,096-token prompt of the 120M shape 1.84 against 2.01 ms, 2,048 tokens
+// 1.13 against 1.02 ms).  Head size 128: two stages and one P buffer (what 227 KB hold).
+template <int HD, bool LEAN>
 struct Storage {
-    static constexpr int STAGES = HD == 64 ? 3 : 2;
-    static constexpr int PB = HD == 64 ? 2 : 1;
+    static constexpr int STAGES = (HD == 64 && !LEAN) ? 3 : 2;
+    static constexpr int PB = (HD == 64 && !LEAN) ? 2 : 1;
+    static constexpr int S_BUFS = LEAN ? 1 : 2;
     alignas(1024) uint8_t q[HD / 64][ROWS * 64 * 2];
     alignas(1024) uint8_t k[STAGES][HD / 64][KEYS * 64 * 2];
     alignas(1024) uint8_t v[STAGES][HD / 64][KEYS * 64 * 2];
@@ -65,6 +74,7 @@ struct Storage {
     alignas(8) uint64_t kv_full[STAGES];
     uint64_t kv_empty[STAGES];
     uint64_t s_full[2], p_full[2], pv_done[2];
+    uint64_t s_free;                                // lean form: a tile's scores are in registers
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -102,15 +112,16 @@ __device__ __forceinline__ void fma_pair(float& x0, float& x1, float a, float b)
         : "f"(a), "f"(b));
 }
 
-template <int HD>
-__global__ void __launch_bounds__(192)
+template <int HD, bool LEAN>
+__global__ void __launch_bounds__(192, LEAN ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const TcAttnParams p) {
     cb_pdl_trigger();
     // 1024-byte alignment (the swizzled tiles need it) is asked of the declaration
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    using Store = Storage<HD>;
-    constexpr int STAGES = Store::STAGES, PB = Store::PB, NH = HD / 64;
+    using Store = Storage<HD, LEAN>;
+    constexpr int STAGES = Store::STAGES, PB = Store::PB, NH = HD / 64, S_BUFS = Store::S_BUFS;
+    constexpr uint32_t TMEM_COLS = LEAN ? 256 : 512;     // scores: 128 columns a buffer, then O
     Store& s = *reinterpret_cast<Store*>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // one index over (tile rank, request, head) with the tile rank slowest: blocks start in
@@ -130,13 +141,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             tc::mbar_init(&s.p_full[b], 4);               // one arrival per softmax warp
             tc::mbar_init(&s.pv_done[b], 1);
         }
+        tc::mbar_init(&s.s_free, 4);
         s.abort_flag = 0;
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&map_k);
         tc::prefetch_tensormap(&map_v);
     }
     if (warp == 1) {
-        tc::tmem_alloc(&s.tmem_base, 512);            // S: columns 0..127 and 128..255, O: from 256
+        tc::tmem_alloc(&s.tmem_base, TMEM_COLS);
         tc::tmem_relinquish();
     }
     cb_pdl_wait();
@@ -220,7 +232,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     __syncthreads();
     tc::tc_fence_after_sync();
     const uint32_t tmem_s = s.tmem_base;          // + 128 for the second buffer
-    const uint32_t tmem_o = s.tmem_base + 256;
+    const uint32_t tmem_o = s.tmem_base + S_BUFS * 128;
 
     if (warp == 0) {
         // ---- loader: the remaining tiles, each once its stage has been read ------------------
@@ -247,9 +259,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             // the tile; else only take it if it has landed (true: issued)
             auto issue_qk = [&](int j, bool block) -> bool {
                 const int st = j % STAGES;
+                // one buffer of scores: the softmax of tile j - 1 must have them in registers
+                const bool hand_back = S_BUFS == 1 && j > 0;
                 if (block) {
                     if (!tc::mbar_wait(&s.kv_full[st], (j / STAGES) & 1, abort_flag)) return false;
-                } else if (!tc::mbar_try_wait(&s.kv_full[st], (j / STAGES) & 1)) {
+                    if (hand_back && !tc::mbar_wait(&s.s_free, (j - 1) & 1, abort_flag)) return false;
+                } else if (!tc::mbar_try_wait(&s.kv_full[st], (j / STAGES) & 1) ||
+                           (hand_back && !tc::mbar_try_wait(&s.s_free, (j - 1) & 1))) {
                     return false;
                 }
                 tc::tc_fence_after_sync();
@@ -257,9 +273,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                 for (int k = 0; k < HD / 16; ++k) {
                     const uint64_t q_desc = tc::smem_desc_sw128(tc::smem_u32(s.q[k >> 2])) + 2 * (k & 3);
                     const uint64_t k_desc = tc::smem_desc_sw128(tc::smem_u32(s.k[st][k >> 2])) + 2 * (k & 3);
-                    tc::umma_bf16(tmem_s + (j & 1) * 128, q_desc, k_desc, idesc_qk, k > 0 ? 1u : 0u);
+                    tc::umma_bf16(tmem_s + (j % S_BUFS) * 128, q_desc, k_desc, idesc_qk, k > 0 ? 1u : 0u);
                 }
-                tc::umma_commit(&s.s_full[j & 1]);
+                tc::umma_commit(&s.s_full[j % S_BUFS]);
                 return true;
             };
             ok = issue_qk(0, true);
@@ -267,11 +283,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                 // the next tile's scores go out first if its keys have landed (their buffer was
                 // last read by the softmax of tile j - 1, whose P this thread has waited for);
                 // else after this tile's second product, which must not wait for a copy
-                const bool ahead = j + 1 < n_tiles && issue_qk(j + 1, false);
+                bool ahead = j + 1 < n_tiles && issue_qk(j + 1, false);
                 // O += P_j V_j once the softmax has written P_j: 128 keys in eight steps of 16,
-                // 64 output features at a time
+                // 64 output features at a time.  With one buffer of scores the next tile's first
+                // MMA may go as soon as this tile's softmax has the scores in registers, which
+                // happens during this wait.
                 const int pb = j % PB;
-                if (!tc::mbar_wait(&s.p_full[pb], (j / PB) & 1, abort_flag)) {
+                bool got = false;
+                for (uint32_t i = 0; i < tc::WAIT_LIMIT && !got; ++i) {
+                    got = tc::mbar_try_wait(&s.p_full[pb], (j / PB) & 1);
+                    if (S_BUFS == 1 && !got && !ahead && j + 1 < n_tiles) ahead = issue_qk(j + 1, false);
+                    if ((i & 1023u) == 1023u && *abort_flag) break;
+                }
+                if (!got) {
                     ok = false;
                     break;
                 }
@@ -315,9 +339,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         };
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int key0 = key_lo + j * KEYS;
-            const int b = j & 1;                      // the scores' buffer
+            const int b = j % S_BUFS;                 // the scores' buffer
             const int pb = j % PB;                    // P's buffer
-            ok = wait_all(&s.s_full[b], (j >> 1) & 1);
+            ok = wait_all(&s.s_full[b], (j / S_BUFS) & 1);
             if (!ok) break;
             tc::tc_fence_after_sync();
             // the row's 128 scores, once, into registers
@@ -327,6 +351,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             for (int c = 0; c < 4; ++c) tc::tmem_ld_32x32(tmem_s + b * 128 + lane_bits + c * 32, sv[c]);
             tc::tmem_ld_wait();
             tc::tc_fence_before_sync();
+            if (S_BUFS == 1) {                        // the buffer may take the next tile's scores
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(&s.s_free);
+            }
             // keys of this tile the row may read: [first, last] relative to key0.  Most tiles
             // lie wholly inside every row's range and skip the test.
             const int last = min(pos - key0, KEYS - 1);
@@ -446,22 +474,22 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     __syncthreads();
     if (warp == 1) {
         tc::tc_fence_after_sync();
-        tc::tmem_dealloc(s.tmem_base, 512);
+        tc::tmem_dealloc(s.tmem_base, TMEM_COLS);
     }
 }
 
-template <int HD>
+template <int HD, bool LEAN>
 int launch_as(dim3 grid, cudaStream_t st, const CUtensorMap& mk, const CUtensorMap& mv,
               const TcAttnParams& p) {
-    const int smem = (int)sizeof(Storage<HD>);
+    const int smem = (int)sizeof(Storage<HD, LEAN>);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD>,
+        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD, LEAN>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    cb_launch(attention_tcgen05_kernel<HD>, grid, dim3(192), smem, st, mk, mv, p);
+    cb_launch(attention_tcgen05_kernel<HD, LEAN>, grid, dim3(192), smem, st, mk, mv, p);
     return cb_last_error();
 }
 
@@ -474,7 +502,7 @@ CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, i
                                    const int* req_row_start, const int* req_first_pos,
                                    const int* block_table, int table_stride, int n_requests,
                                    int max_new_tokens, int n_heads, int n_kv_heads, int head_dim,
-                                   int page_tokens, float scale, int window, int* status,
+                                   int page_tokens, float scale, int window, int lean, int* status,
                                    void* stream) {
     if (n_requests <= 0 || max_new_tokens <= 0) return 0;
     if ((head_dim != 64 && head_dim != 128) || n_heads % n_kv_heads != 0 || page_tokens < 8 || page_tokens > KEYS ||
@@ -508,6 +536,19 @@ CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, i
     const int n_rep = n_heads / n_kv_heads;
     const int q_tiles = (max_new_tokens * n_rep + ROWS - 1) / ROWS;
     const dim3 grid(q_tiles * n_kv_heads * n_requests);
-    return head_dim == 64 ? launch_as<64>(grid, (cudaStream_t)stream, mk, mv, p)
-                          : launch_as<128>(grid, (cudaStream_t)stream, mk, mv, p);
+    // lean: -1 lets the launch decide (the lean form of head size 64 when there are more blocks
+    // than places for them: two to each of the SMs), 0 and 1 fix the form
+    if (lean < 0) {
+        static const int n_sms = [] {
+            int device = 0, n = 148;
+            if (cudaGetDevice(&device) == cudaSuccess)
+                cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
+            return n;
+        }();
+        lean = head_dim == 64 && (int)grid.x > 2 * n_sms;
+    }
+    if (head_dim == 64)
+        return lean ? launch_as<64, true>(grid, (cudaStream_t)stream, mk, mv, p)
+                    : launch_as<64, false>(grid, (cudaStream_t)stream, mk, mv, p);
+    return launch_as<128, false>(grid, (cudaStream_t)stream, mk, mv, p);
 }

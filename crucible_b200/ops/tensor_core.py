@@ -276,6 +276,10 @@ def linear_rope_append(h, wqkv, qkv, n_heads, n_kv_heads, head_dim, cos, sin, ro
     return True
 
 
+ATTENTION_LEAN = -1      # the form of the head-size-64 prompt attention: -1 by the number of
+                         # blocks (see the kernel's header), 0 roomy, 1 lean (tests fix it)
+
+
 def _attention_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads, head_dim, scale,
                        window, ctx, cache) -> bool:
     """tcgen05 attention for portions of prompts: head size 64 or 128, page size a
@@ -291,7 +295,7 @@ def _attention_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads, h
         _c_void_p(ctx.req_first_pos.data_ptr()), _c_void_p(table.data_ptr()),
         _c_int(table.shape[1]), _c_int(ctx.n_requests), _c_int(ctx.host.max_new_tokens),
         _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim), _c_int(pt),
-        ctypes.c_float(scale), _c_int(window or 0),
+        ctypes.c_float(scale), _c_int(window or 0), _c_int(ATTENTION_LEAN),
         _c_void_p(status_word(qkv.device).data_ptr()), _stream())
     if code == _UNSUPPORTED:
         return False

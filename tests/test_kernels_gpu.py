@@ -574,8 +574,10 @@ def test_attention_tensor_core_tiles_and_split(case):
     (4, 2, 128, 16, [(0, 600), (40, 70)], None),            # head size 128: two stages, one P buffer
     (2, 1, 128, 64, [(300, 420)], 256),
 ])
-def test_attention_tcgen05_matches_reference_and_mma(case):
-    """Prompt portions with head size 64: S and O in tensor memory, K and V by TMA."""
+@pytest.mark.parametrize("lean", [0, 1])
+def test_attention_tcgen05_matches_reference_and_mma(case, lean):
+    """Prompt portions with head size 64 or 128: S and O in tensor memory, K and V by TMA; for
+    head size 64 both forms of the kernel (an SM to a block, or two lean blocks to an SM)."""
     from crucible_b200.ops import tensor_core
     n_heads, n_kv, hd, page, requests, window = case
     qkv, ctx, cache, binding, ref = _paged_case(torch.bfloat16, n_heads, n_kv, hd, page, requests,
@@ -584,8 +586,12 @@ def test_attention_tcgen05_matches_reference_and_mma(case):
     cache.n_pages = k_cache.shape[0]
     out = torch.zeros(qkv.shape[0], n_heads * hd, device=DEV, dtype=torch.bfloat16)
     assert tensor_core.USE_TCGEN05_ATTENTION
-    assert tensor_core._attention_tcgen05(qkv, out, k_cache, cache.values(0), ctx.block_table(0),
-                                          n_heads, n_kv, hd, 1 / math.sqrt(hd), window, ctx, cache)
+    try:
+        tensor_core.ATTENTION_LEAN = lean
+        assert tensor_core._attention_tcgen05(qkv, out, k_cache, cache.values(0), ctx.block_table(0),
+                                              n_heads, n_kv, hd, 1 / math.sqrt(hd), window, ctx, cache)
+    finally:
+        tensor_core.ATTENTION_LEAN = -1
     torch.cuda.synchronize()
     tensor_core.check_status(DEV)
     assert rel(out, ref) < 1.5e-2
