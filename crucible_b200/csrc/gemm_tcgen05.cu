@@ -12,6 +12,13 @@
 //   SWIGLU_BF16 W = [Wg; Wu] ([2I, K]); the tile holds BN/2 gate rows and the
 //               BN/2 matching up rows; C[M, I] bf16 = silu(g) * u in fp32
 //
+// Many tiles and a long K (prompts at the larger layer sizes): 148 blocks of 128 x 256 ask
+// the L2 for more operand bytes than it delivers (384 rows of operands per 128 x 256 of
+// output).  MH = 2 gives a block two accumulators, 256 x 256 of output from 512 rows of
+// operands: the W tile in shared memory meets two A tiles.  Three stages of 64 KB then, and
+// all 512 columns of tensor memory; the output leaves through shared memory and TMA, half
+// after half.
+//
 // Few tiles and a long K (a step of 33 to a few hundred rows): the blocks (x, y, 0..S-1)
 // form a cluster that splits K.  Each multiplies its share into its own accumulator; the
 // others then leave theirs in their shared memory, and block 0 of the cluster adds them
@@ -52,9 +59,9 @@ struct RopeArgs {
     int n_heads, n_kv_heads, head_dim, page_tokens, write_cache;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MH>
 struct SharedStorage {
-    alignas(1024) uint8_t a[STAGES][BM * BK * 2];
+    alignas(1024) uint8_t a[STAGES][MH * BM * BK * 2];
     alignas(1024) uint8_t b[STAGES][BN * BK * 2];
     alignas(8) uint64_t full_bar[STAGES];
     uint64_t empty_bar[STAGES];
@@ -64,19 +71,19 @@ struct SharedStorage {
     int abort_flag;
 };
 
-template <int BN, int STAGES, int EPI>
-__global__ void __launch_bounds__(192, STAGES <= 3 ? 2 : 1)
+template <int BN, int STAGES, int EPI, int MH>
+__global__ void __launch_bounds__(192, (STAGES <= 3 && MH == 1) ? 2 : 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_c, int tma_out,
                     void* __restrict__ c_ptr, int M, int N, int K, int ldc, int inter,
                     int k_splits, int* __restrict__ status, const RopeArgs ra) {
     extern __shared__ uint8_t smem_raw[];
-    using Storage = SharedStorage<BN, STAGES>;
+    using Storage = SharedStorage<BN, STAGES, MH>;
     Storage& s = *reinterpret_cast<Storage*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM;
+    const int m0 = blockIdx.y * BM * MH;
     const int n_tile = blockIdx.x;
     // this block's share of K: blocks of 64 elements [kb_first, kb_first + k_blocks)
     const uint32_t split = k_splits > 1 ? tc::cluster_rank() : 0u;
@@ -86,8 +93,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     const int k_blocks = min(per_split, k_blocks_all - kb_first);      // the launcher keeps it positive
     volatile int* abort_flag = &s.abort_flag;
     // tensor-memory columns are allocated in powers of two
-    constexpr uint32_t TMEM_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
-    constexpr uint32_t STAGE_BYTES = (BM + BN) * BK * 2;
+    constexpr uint32_t TMEM_COLS = MH * BN <= 32 ? 32 : (MH * BN <= 64 ? 64 : (MH * BN <= 128 ? 128 : (MH * BN <= 256 ? 256 : 512)));
+    constexpr uint32_t STAGE_BYTES = (MH * BM + BN) * BK * 2;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) {
@@ -148,7 +155,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     tc::mbar_expect_tx(&s.full_bar[st], STAGE_BYTES);
                     load_w(kb);
                 }
-                tc::tma_load_2d(s.a[st], &map_a, &s.full_bar[st], (kb_first + kb) * BK, m0);
+#pragma unroll
+                for (int mh = 0; mh < MH; ++mh)
+                    tc::tma_load_2d(s.a[st] + mh * (BM * BK * 2), &map_a, &s.full_bar[st], (kb_first + kb) * BK,
+                                    m0 + mh * BM);
                 if (kb + 1 > armed) armed = kb + 1;
             }
             if (*abort_flag) {
@@ -179,13 +189,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     break;
                 }
                 tc::tc_fence_after_sync();
-                const uint64_t a_desc = tc::smem_desc_sw128(tc::smem_u32(s.a[st]));
                 const uint64_t b_desc = tc::smem_desc_sw128(tc::smem_u32(s.b[st]));
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // advancing 16 elements along K = 32 bytes = 2 descriptor units
-                    tc::umma_bf16(tmem_acc, a_desc + 2 * k, b_desc + 2 * k, idesc,
-                                  (kb > 0 || k > 0) ? 1u : 0u);
+                for (int mh = 0; mh < MH; ++mh) {
+                    const uint64_t a_desc = tc::smem_desc_sw128(tc::smem_u32(s.a[st] + mh * (BM * BK * 2)));
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // advancing 16 elements along K = 32 bytes = 2 descriptor units
+                        tc::umma_bf16(tmem_acc + mh * BN, a_desc + 2 * k, b_desc + 2 * k, idesc,
+                                      (kb > 0 || k > 0) ? 1u : 0u);
+                    }
                 }
                 tc::umma_commit(&s.empty_bar[st]);      // stage free once these MMAs are done
             }
@@ -202,7 +215,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         const int row = m0 + quarter * 32 + lane;
         // ACCUM_F32: the values to add to are asked for now, while the products run; the
         // thread's whole row of the tile stays in registers (tiles up to 128 wide)
-        constexpr bool EARLY = EPI == ACCUM_F32 && BN <= 128;
+        constexpr bool EARLY = EPI == ACCUM_F32 && BN <= 128 && MH == 1;
         constexpr int NQ = EARLY ? BN / 4 : 1;
         float4 early[NQ];
         if (EARLY && !tma_out) {
@@ -415,12 +428,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                 constexpr int CHUNK = (EPI == STORE_F32 || EPI == ACCUM_F32) ? 32 : 64;
                 const int n_out = EPI == SWIGLU_BF16 ? inter : N;
 #pragma unroll 1
+                for (int mh = 0; mh < MH; ++mh) {                   // one accumulator after the other
+                const uint32_t lane_addr_h = lane_addr + mh * BN;
+                if (mh > 0) {
+                    // the staging buffers are used again: the first half's stores must have read them
+                    if (warp == 2 && lane == 0) tc::tma_store_wait_read();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                }
+#pragma unroll 1
                 for (int c = 0; c < OUT_COLS / CHUNK; ++c) {
                     uint8_t* buf = ring + c * (BM * 128);
                     uint8_t* mine = buf + r * 128;
                     if (EPI == STORE_F32 || EPI == ACCUM_F32) {
                         uint32_t v[32];
-                        tc::tmem_ld_32x32(lane_addr + c * 32, v);
+                        tc::tmem_ld_32x32(lane_addr_h + c * 32, v);
                         tc::tmem_ld_wait();
 #pragma unroll
                         for (int q = 0; q < 8; ++q)
@@ -430,10 +451,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
                             uint32_t v[32];
-                            tc::tmem_ld_32x32(lane_addr + c * 64 + h * 32, v);
+                            tc::tmem_ld_32x32(lane_addr_h + c * 64 + h * 32, v);
                             if (EPI == SWIGLU_BF16) {
                                 uint32_t u[32];
-                                tc::tmem_ld_32x32(lane_addr + BN / 2 + c * 64 + h * 32, u);
+                                tc::tmem_ld_32x32(lane_addr_h + BN / 2 + c * 64 + h * 32, u);
                                 tc::tmem_ld_wait();
 #pragma unroll
                                 for (int j = 0; j < 32; ++j)
@@ -461,11 +482,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     if (warp == 2 && lane == 0) {
                         const int x = n_tile * OUT_COLS + c * CHUNK;
                         if (x < n_out) {
-                            if (EPI == ACCUM_F32) tc::tma_reduce_add_2d(&map_c, buf, x, m0);
-                            else tc::tma_store_2d(&map_c, buf, x, m0);
+                            if (EPI == ACCUM_F32) tc::tma_reduce_add_2d(&map_c, buf, x, m0 + mh * BM);
+                            else tc::tma_store_2d(&map_c, buf, x, m0 + mh * BM);
                             tc::tma_store_commit();
                         }
                     }
+                }
                 }
                 if (warp == 2 && lane == 0) tc::tma_store_wait_all();
             } else if (EPI == SWIGLU_BF16) {
@@ -597,9 +619,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     }
 }
 
-template <int BN, int STAGES, int EPI>
+template <int BN, int STAGES, int EPI, int MH = 1>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, int K, int ldc,
            int inter, int k_splits, int* status, cudaStream_t stream, const RopeArgs& ra = RopeArgs{}) {
+    if (MH > 1 && k_splits > 1) return CB_ERR_UNSUPPORTED;
     // shares of K: at most 8 blocks in a cluster, every share at least one block of 64
     // elements, and a block's accumulator (128 x BN fp32) has to fit in the ring of stages
     if (k_splits < 1) k_splits = 1;
@@ -619,31 +642,31 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, 
     const uint64_t map_cols = EPI == ROPE_APPEND ? (uint64_t)ra.n_heads * ra.head_dim : (uint64_t)out_cols;
     if (tma_out && !tc::make_out_map_2d(&mc, C, f32, (uint64_t)M, map_cols, (uint64_t)ldc, BM))
         tma_out = 0;
-    if (EPI == ROPE_APPEND && !tma_out) return CB_ERR_UNSUPPORTED;
-    using Storage = SharedStorage<BN, STAGES>;
+    if ((EPI == ROPE_APPEND || MH > 1) && !tma_out) return CB_ERR_UNSUPPORTED;
+    using Storage = SharedStorage<BN, STAGES, MH>;
     const int smem = (int)sizeof(Storage) + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, EPI>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, EPI, MH>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const int n_cols = EPI == SWIGLU_BF16 ? 2 * inter : N;
-    dim3 grid((n_cols + BN - 1) / BN, (M + BM - 1) / BM, k_splits);
-    cb_launch_cluster(gemm_tcgen05_kernel<BN, STAGES, EPI>, dim3(grid), dim3(192), smem, stream, k_splits,
+    dim3 grid((n_cols + BN - 1) / BN, (M + BM * MH - 1) / (BM * MH), k_splits);
+    cb_launch_cluster(gemm_tcgen05_kernel<BN, STAGES, EPI, MH>, dim3(grid), dim3(192), smem, stream, k_splits,
                       ma, mw, mc, tma_out, C, M, N, K, ldc, inter, k_splits, status, ra);
     return cb_last_error();
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MH = 1>
 int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N,
                int K, int ldc, int inter, int ks, int* status, cudaStream_t stream) {
     switch (epi) {
-        case STORE_BF16: return launch<BN, STAGES, STORE_BF16>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream);
-        case STORE_F32: return launch<BN, STAGES, STORE_F32>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream);
-        case ACCUM_F32: return launch<BN, STAGES, ACCUM_F32>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream);
-        case SWIGLU_BF16: return launch<BN, STAGES, SWIGLU_BF16>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream);
+        case STORE_BF16: return launch<BN, STAGES, STORE_BF16, MH>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream);
+        case STORE_F32: return launch<BN, STAGES, STORE_F32, MH>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream);
+        case ACCUM_F32: return launch<BN, STAGES, ACCUM_F32, MH>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream);
+        case SWIGLU_BF16: return launch<BN, STAGES, SWIGLU_BF16, MH>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream);
     }
     return CB_ERR_UNSUPPORTED;
 }
@@ -651,7 +674,8 @@ int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, void* C, i
 }  // namespace
 
 // W is [N, K] (for SWIGLU_BF16: [2 * inter, K], N = inter and C is [M, inter]).
-// bn: tile width: 64, 96, 128, 160, 192 or 256.  per_sm: 1 = a deep ring of stages, one
+// bn: tile width: 64, 96, 128, 160, 192 or 256.  per_sm: 0 = two accumulators (256 rows of
+// output per block, bn 256 only, no shares of K); 1 = a deep ring of stages, one
 // block per SM; 2 = three stages, so that two blocks share an SM and one's prologue and
 // epilogue run beside the other's products (tile widths up to 128).
 // status: device int, stays 0 unless a wait ran out.
@@ -670,6 +694,10 @@ CB_EXPORT int cb_gemm_tcgen05(const void* A, const void* W, void* C, int M, int 
         return CB_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const int inter = epi == SWIGLU_BF16 ? N : 0;
+    if (per_sm == 0) {            // two accumulators: 256 x 256 of output per block
+        if (bn == 256) return launch_epi<256, 3, 2>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
+        return CB_ERR_UNSUPPORTED;
+    }
     if (per_sm == 2) {
         switch (bn) {
             case 64: return launch_epi<64, 3>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);

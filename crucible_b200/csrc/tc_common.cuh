@@ -394,6 +394,8 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const 
 
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // waits until every committed store of this thread has been written
+// waits until the stores sent so far have read their shared memory (it may be written again)
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // silu(g) = g / (1 + e^-g) in fp32 with the hardware's exponential and reciprocal

@@ -128,8 +128,31 @@ def _tile_width(m: int, n_cols: int, epi: int = 1, multiple_of: int = 1):
     return best, 1
 
 
+TALL_MIN_ROWS = 1024        # two accumulators per block (256 x 256 of output) ...
+TALL_MIN_K = 2048           # ... pay where the products are bound by the operands' way from L2 to
+TALL_MIN_FILL = 0.8         # the SMs: many rows, a long K, and enough 256 x 256 tiles to fill the SMs
+
+
+def _tall_tiles(m: int, n_cols: int, k: int) -> bool:
+    """Whether a product should run as 256 x 256 tiles (two accumulators per block).  At the
+    Llama-3-8B layer sizes 148 blocks of 128 x 256 ask the L2 for 384 rows of operands per
+    tile and run at half the tensor cores' rate; 256 x 256 needs 512 rows for twice the output."""
+    if m < TALL_MIN_ROWS or k < TALL_MIN_K:
+        return False
+    blocks = -(-m // 256) * -(-n_cols // 256)
+    waves = -(-blocks // N_SMS)
+    return blocks / (waves * N_SMS) >= TALL_MIN_FILL
+
+
 def _gemm(a, w, out, n, epi, bn, per_sm=1, splits=None) -> bool:
     lib = build.load("gemm_tcgen05")
+    if per_sm == 0:
+        # 256 x 256 tiles; an output that cannot leave by TMA is refused, and the 128-row tiles run
+        if _gemm(a, w, out, n, epi, 256, -1, 1):
+            return True
+        per_sm = 1
+    if per_sm == -1:
+        per_sm, splits = 0, 1
     if splits is None:
         splits = k_splits(a.shape[0], 2 * n if epi == SWIGLU_BF16 else n, a.shape[1], bn)
     code = lib.cb_gemm_tcgen05(
@@ -227,6 +250,8 @@ def linear(a, w, out, *, accumulate=False, tile=None) -> bool:
     if tile is None and ((a.shape[0] <= SKINNY_ROWS and w.numel() * 2 >= SKINNY_MIN_BYTES)
                          or (a.shape[0] <= 64 and w.shape[0] >= SKINNY_WIDE_N)):
         return _gemm_skinny(a, w, out, w.shape[0], epi)
+    if tile is None and _tall_tiles(a.shape[0], w.shape[0], a.shape[1]):
+        tile = (256, 0)
     bn, per_sm, *splits = _tile_of(tile) if tile else _tile_width(a.shape[0], w.shape[0], epi)
     return _gemm(a, w, out, w.shape[0], epi, bn, per_sm, splits[0] if splits else None)
 
@@ -237,6 +262,8 @@ def linear_swiglu(h, gate_up, out, tile=None) -> bool:
     inter = gate_up.shape[0] // 2
     if tile is None and h.shape[0] <= SKINNY_ROWS and gate_up.numel() * 2 >= SKINNY_MIN_BYTES:
         return _gemm_skinny(h, gate_up, out, inter, SWIGLU_BF16)
+    if tile is None and _tall_tiles(h.shape[0], 2 * inter, h.shape[1]):
+        tile = (256, 0)
     bn, per_sm, *splits = _tile_of(tile) if tile else _tile_width(h.shape[0], 2 * inter, SWIGLU_BF16)
     return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn, per_sm, splits[0] if splits else None)
 

@@ -27,3 +27,11 @@ def test_large_products_are_not_split():
     assert tensor_core.k_splits(64, 768, 2048, 64) == 4
     assert tensor_core.k_splits(64, 2048, 8192, 64) == 4
     assert tensor_core.k_splits(512, 768, 2048, 64) == 2
+
+
+def test_tall_tiles_only_where_they_fill_the_sms():
+    assert tensor_core._tall_tiles(2048, 28672, 4096)          # Llama-3-8B gate/up
+    assert tensor_core._tall_tiles(2048, 4096, 14336)          # ... down: 128 tiles of 256 x 256
+    assert not tensor_core._tall_tiles(2048, 2048, 8192)       # Llama-3.2-1B down: 64 tiles
+    assert not tensor_core._tall_tiles(2048, 4096, 768)        # the 120M shape: K too short
+    assert not tensor_core._tall_tiles(512, 28672, 4096)

@@ -113,6 +113,34 @@ def test_linear_tensor_core(m, n, k, tile):
     tensor_core.check_status(DEV)
 
 
+@pytest.mark.parametrize("m,n,k", [(300, 1280, 768), (1000, 512, 320), (257, 100, 24), (130, 192, 1096)])
+def test_linear_tensor_core_two_accumulators(m, n, k):
+    """256 x 256 of output per block: two accumulators in tensor memory, the W tile shared."""
+    from crucible_b200.ops import tensor_core
+    a = (torch.rand(m, k, device=DEV) + 0.5).bfloat16()
+    w = (torch.rand(n, k, device=DEV) * 0.1 + 0.05).bfloat16()
+    ref = a.double() @ w.double().T
+    out = torch.empty(m, n, device=DEV)
+    assert tensor_core.linear(a, w, out, tile=(256, 0))
+    assert rel(out, ref) < 1e-5
+    out16 = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    assert tensor_core.linear(a, w, out16, tile=(256, 0))      # rows of 200 bytes: the 128-row tiles step in
+    assert rel(out16, ref) < 5e-3
+    base = torch.randn(m, n, device=DEV)
+    acc = base.clone()
+    assert tensor_core.linear(a, w, acc, accumulate=True, tile=(256, 0))
+    assert rel(acc, ref + base.double()) < 1e-5
+    inter = n // 2 // 8 * 8
+    h = torch.randn(m, k, device=DEV).bfloat16()
+    w2 = (torch.randn(2 * inter, k, device=DEV) * 0.05).bfloat16()
+    act = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
+    assert tensor_core.linear_swiglu(h, w2, act, tile=(256, 0))
+    y = h.double() @ w2.double().T
+    g, u = y[:, :inter], y[:, inter:]
+    assert rel(act, g / (1 + torch.exp(-g)) * u) < 6e-3
+    tensor_core.check_status(DEV)
+
+
 @pytest.mark.parametrize("tile", [64, 96, 128, 160, 192, 256])
 @pytest.mark.parametrize("m,inter,k", [(1, 176, 64), (33, 320, 96), (300, 2048, 768), (130, 88, 40)])
 def test_linear_swiglu_tensor_core(m, inter, k, tile):
