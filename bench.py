@@ -303,9 +303,9 @@ def run_profile_case(args):
     from crucible_b200.config import shape
     from crucible_b200.engine import StepEntry
     from crucible_b200.weights import write_random_model
-    raw = shape("120m")
+    raw = shape(args.shape)
     if args.layers:
-        raw["n_layer"] = args.layers
+        raw["n_layer" if "n_layer" in raw else "num_hidden_layers"] = args.layers
     rng = random.Random(1)
     with tempfile.TemporaryDirectory() as tmp:
         folder = write_random_model(raw, os.path.join(tmp, "model"), seed=0)
