@@ -230,23 +230,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             }
         }
         // ROPE_APPEND: the row's position and its place in the cache pages, asked for while
-        // the products run; every epilogue thread publishes its row's place
+        // the products run; every epilogue thread publishes its row's place.  For head size 64
+        // also its 32 rotation factors, kept in registers for every head.  (Per 128 rows: a
+        // block with two accumulators does this again for its second half.)
         int row_pos = 0;
-        if (EPI == ROPE_APPEND) {
+        float4 cs_reg[8], sn_reg[8];
+        auto rope_rows = [&](int at_row) {
             long base = -1;
-            if (row < M) {
-                row_pos = ra.positions[row];
+            row_pos = 0;
+            if (at_row < M) {
+                row_pos = ra.positions[at_row];
                 if (ra.write_cache) {
-                    const int page = ra.block_table[(size_t)ra.row_request[row] * ra.table_stride +
+                    const int page = ra.block_table[(size_t)ra.row_request[at_row] * ra.table_stride +
                                                     row_pos / ra.page_tokens];
                     base = (long)page * ra.n_kv_heads * ra.page_tokens + row_pos % ra.page_tokens;
                 }
             }
             s.row_base[quarter * 32 + lane] = base;
-        }
-        // ... and for head size 64 its 32 rotation factors, kept in registers for every head
-        float4 cs_reg[8], sn_reg[8];
-        if (EPI == ROPE_APPEND) {
             if (ra.head_dim == 64) {
                 const float4* cp = reinterpret_cast<const float4*>(ra.cos_t + (size_t)row_pos * 32);
                 const float4* sp = reinterpret_cast<const float4*>(ra.sin_t + (size_t)row_pos * 32);
@@ -256,7 +256,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     sn_reg[q4] = __ldg(sp + q4);
                 }
             }
-        }
+        };
+        if (EPI == ROPE_APPEND) rope_rows(row);
         bool ok = tc::mbar_wait(&s.tmem_full_bar, 0, abort_flag);
         if (!ok && !*abort_flag) tc::give_up(abort_flag, status, tc::ST_EPILOGUE_TIMEOUT);
         ok = __all_sync(0xffffffffu, ok);
@@ -340,6 +341,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                 const int heads_all = ra.n_heads + 2 * ra.n_kv_heads;
                 const int chunks = hd >> 6;                         // 64-column chunks per head
                 uint8_t* ring = s.a[0];
+#pragma unroll 1
+                for (int mh = 0; mh < MH; ++mh) {                   // one accumulator after the other
+                if (mh > 0) {
+                    // the staging buffers and the rows' places are used again: the first half's
+                    // stores and copies must be done with them
+                    if (warp == 2 && lane == 0) tc::tma_store_wait_read();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    rope_rows(row + mh * BM);
+                }
+                const uint32_t lane_addr_h = lane_addr + mh * BN;
+                const int m0_h = m0 + mh * BM;
                 const float* cs_row = ra.cos_t + (size_t)row_pos * half;
                 const float* sn_row = ra.sin_t + (size_t)row_pos * half;
 #pragma unroll 1
@@ -351,8 +363,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll 1
                     for (int c = 0; c < half; c += 32) {
                         uint32_t lo[32], hi[32];
-                        tc::tmem_ld_32x32(lane_addr + hc + c, lo);
-                        tc::tmem_ld_32x32(lane_addr + hc + half + c, hi);
+                        tc::tmem_ld_32x32(lane_addr_h + hc + c, lo);
+                        tc::tmem_ld_32x32(lane_addr_h + hc + half + c, hi);
                         tc::tmem_ld_wait();
                         if (is_q || is_k) {
 #pragma unroll
@@ -399,7 +411,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     if (is_q) {
                         if (warp == 2 && lane == 0) {
                             for (int ch = 0; ch < chunks; ++ch)
-                                tc::tma_store_2d(&map_c, buf + ch * (BM * 128), head * hd + ch * 64, m0);
+                                tc::tma_store_2d(&map_c, buf + ch * (BM * 128), head * hd + ch * 64, m0_h);
                             tc::tma_store_commit();
                         }
                     } else if (ra.write_cache) {
@@ -415,6 +427,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                       ch * 64 + piece * 8) = v;
                         }
                     }
+                }
                 }
                 if (warp == 2 && lane == 0) tc::tma_store_wait_all();
             } else if (tma_out) {
@@ -726,7 +739,7 @@ CB_EXPORT int cb_gemm_tcgen05_rope(const void* A, const void* W, void* q_out, in
                                    const int* positions, const int* row_request,
                                    const int* block_table, int table_stride, void* k_cache,
                                    void* v_cache, int n_heads, int n_kv_heads, int head_dim,
-                                   int page_tokens, int write_cache, int k_splits, int* status,
+                                   int page_tokens, int write_cache, int k_splits, int tall, int* status,
                                    void* stream) {
     if (M <= 0) return 0;
     if (K <= 0 || (K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) ||
@@ -745,6 +758,10 @@ CB_EXPORT int cb_gemm_tcgen05_rope(const void* A, const void* W, void* q_out, in
     ra.n_heads = n_heads; ra.n_kv_heads = n_kv_heads; ra.head_dim = head_dim;
     ra.page_tokens = page_tokens; ra.write_cache = write_cache;
     cudaStream_t s = (cudaStream_t)stream;
+    if (tall) {           // two accumulators: 256 rows of output per block
+        if (bn == 256) return launch<256, 3, ROPE_APPEND, 2>(ma, mw, q_out, M, N, K, ldq, 0, 1, status, s, ra);
+        return CB_ERR_UNSUPPORTED;
+    }
     switch (bn) {
         case 64: return launch<64, 6, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, k_splits, status, s, ra);
         case 128: return launch<128, 5, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, k_splits, status, s, ra);

@@ -268,6 +268,9 @@ def linear_swiglu(h, gate_up, out, tile=None) -> bool:
     return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn, per_sm, splits[0] if splits else None)
 
 
+ROPE_TALL = None     # tests may fix the form of the q/k/v product (True: 256 x 256 tiles)
+
+
 def linear_rope_append(h, wqkv, qkv, n_heads, n_kv_heads, head_dim, cos, sin, rotary_dim, ctx, cache,
                        binding) -> bool:
     """The q/k/v projection with the rotation and the cache write in the product's
@@ -282,6 +285,11 @@ def linear_rope_append(h, wqkv, qkv, n_heads, n_kv_heads, head_dim, cos, sin, ro
         return False
     table = ctx.block_table(binding.group)
     bn, _ = _tile_width(h.shape[0], wqkv.shape[0], ROPE_APPEND, multiple_of=head_dim)
+    tall = 256 % head_dim == 0 and _tall_tiles(h.shape[0], wqkv.shape[0], h.shape[1])
+    if ROPE_TALL is not None:
+        tall = ROPE_TALL
+    if tall:
+        bn = 256
     if bn % head_dim:
         return False
     lib = build.load("gemm_tcgen05")
@@ -293,7 +301,7 @@ def linear_rope_append(h, wqkv, qkv, n_heads, n_kv_heads, head_dim, cos, sin, ro
         _c_void_p(table.data_ptr()), _c_int(table.shape[1]), _c_void_p(k_cache.data_ptr()),
         _c_void_p(v_cache.data_ptr()), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
         _c_int(cache.page_tokens), _c_int(1 if binding.write else 0),
-        _c_int(k_splits(h.shape[0], wqkv.shape[0], h.shape[1], bn)),
+        _c_int(1 if tall else k_splits(h.shape[0], wqkv.shape[0], h.shape[1], bn)), _c_int(1 if tall else 0),
         _c_void_p(status_word(h.device).data_ptr()), _stream())
     if code == _UNSUPPORTED:
         return False

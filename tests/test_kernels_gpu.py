@@ -339,9 +339,10 @@ def test_small_batch_large_weights_take_other_paths():
 @pytest.mark.parametrize("hd,n_heads,n_kv,rows,d", [(64, 6, 2, 300, 256), (64, 5, 1, 40, 256),
                                                     (128, 3, 1, 150, 256), (64, 6, 2, 60, 1024)])
 @pytest.mark.parametrize("write", [True, False])
-def test_linear_rope_append_tensor_core(hd, n_heads, n_kv, rows, d, write):
+@pytest.mark.parametrize("tall", [False, True])
+def test_linear_rope_append_tensor_core(hd, n_heads, n_kv, rows, d, write, tall):
     """The q/k/v product for many rows with rotation and cache write in its epilogue (the
-    last case: few tiles and a long K, so clusters share K)."""
+    last case: few tiles and a long K, so clusters share K); `tall`: 256 x 256 tiles."""
     from crucible_b200.ops import tensor_core
     page = 16
     torch.manual_seed(rows)
@@ -377,8 +378,12 @@ def test_linear_rope_append_tensor_core(hd, n_heads, n_kv, rows, d, write):
                           row_request=torch.tensor(row_request, dtype=torch.int32, device=DEV),
                           block_table=lambda g: tables)
     qkv = torch.zeros(rows, w.shape[0], device=DEV, dtype=torch.bfloat16)
-    assert tensor_core.linear_rope_append(h, w, qkv, n_heads, n_kv, hd, cos, sin, hd, ctx, Cache,
-                                          SimpleNamespace(group=0, slot=0, write=write))
+    try:
+        tensor_core.ROPE_TALL = tall
+        assert tensor_core.linear_rope_append(h, w, qkv, n_heads, n_kv, hd, cos, sin, hd, ctx, Cache,
+                                              SimpleNamespace(group=0, slot=0, write=write))
+    finally:
+        tensor_core.ROPE_TALL = None
     torch.cuda.synchronize()
     tensor_core.check_status(DEV)
     y = (h.double() @ w.double().T).cpu().view(rows, n_heads + 2 * n_kv, hd)
