@@ -129,8 +129,8 @@ def _tile_width(m: int, n_cols: int, epi: int = 1, multiple_of: int = 1):
 
 
 TALL_MIN_ROWS = 1024        # two accumulators per block (256 x 256 of output) ...
-TALL_MIN_K = 2048           # ... pay where the products are bound by the operands' way from L2 to
-TALL_MIN_FILL = 0.8         # the SMs: many rows, a long K, and enough 256 x 256 tiles to fill the SMs
+TALL_MIN_K = 512            # ... pay where many rows meet enough 256 x 256 tiles to fill the SMs: at
+TALL_MIN_FILL = 0.8         # long K they halve the operand bytes per flop, at short K the blocks' starts and ends
 
 
 def _tall_tiles(m: int, n_cols: int, k: int) -> bool:

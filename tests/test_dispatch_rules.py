@@ -33,5 +33,6 @@ def test_tall_tiles_only_where_they_fill_the_sms():
     assert tensor_core._tall_tiles(2048, 28672, 4096)          # Llama-3-8B gate/up
     assert tensor_core._tall_tiles(2048, 4096, 14336)          # ... down: 128 tiles of 256 x 256
     assert not tensor_core._tall_tiles(2048, 2048, 8192)       # Llama-3.2-1B down: 64 tiles
-    assert not tensor_core._tall_tiles(2048, 4096, 768)        # the 120M shape: K too short
+    assert tensor_core._tall_tiles(2048, 4096, 768)            # the 120M shape's gate/up: 128 tiles
+    assert not tensor_core._tall_tiles(2048, 768, 2048)        # ... its down projection: 24 tiles
     assert not tensor_core._tall_tiles(512, 28672, 4096)
