@@ -116,7 +116,6 @@ template <int HD, bool LEAN>
 __global__ void __launch_bounds__(192, LEAN ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const TcAttnParams p) {
-    cb_pdl_trigger();
     // 1024-byte alignment (the swizzled tiles need it) is asked of the declaration
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     using Store = Storage<HD, LEAN>;
@@ -231,6 +230,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     tc::tc_fence_before_sync();
     __syncthreads();
     tc::tc_fence_after_sync();
+    // only now may the kernel after this one start: every block of this one holds its tensor
+    // memory by now, so a successor that asks for tensor memory queues behind it
+    cb_pdl_trigger();
     const uint32_t tmem_s = s.tmem_base;          // + 128 for the second buffer
     const uint32_t tmem_o = s.tmem_base + S_BUFS * 128;
 

@@ -68,8 +68,11 @@ static inline int cb_last_error() {
 // have completed and their writes are visible).  What a kernel does before the
 // wait -- index arithmetic, barrier and tensor-memory set-up, loads of weights,
 // which no kernel writes -- overlaps the tail of its predecessor.  Each kernel
-// calls cb_pdl_trigger() at its start so that its successor may be scheduled
-// early.  Which kernels get the attribute was measured on B200 inside captured graphs,
+// calls cb_pdl_trigger() so that its successor may be scheduled early: kernels that hold
+// tensor memory only after they have allocated it and passed their own wait (a successor
+// that started earlier could take the tensor memory of an SM first and then wait for this
+// kernel, which waits for that tensor memory), the others at their start or once their own
+// loads are on their way.  Which kernels get the attribute was measured on B200 inside captured graphs,
 // source file by source file (CB_PDL_BIT, defined before this header is included, is the
 // file's bit): the tensor-core products for more than 32 rows gain most (their barriers,
 // tensor memory and descriptors are set up under the kernel before: 1.09 -> 1.02 ms per
