@@ -1,0 +1,78 @@
+"""The engine at the benchmark's layer sizes (two layers of the 120M shape): steps whose
+shapes reach the kernels and rules that the tiny configurations cannot (256 x 256 tiles,
+clusters that share K, the products' hand-over at 17 rows, replayed graphs of 64 rows).
+The plain implementation would take minutes at this width, so the bfloat16 engine is
+compared with the float32 engine, which the other tests hold against the plain
+implementation, and the float32 engine with itself across ways of cutting."""
+import random
+
+import pytest
+import torch
+
+from helpers import TOLERANCE
+
+pytestmark = pytest.mark.gpu
+
+
+def _plan(vocab):
+    rng = random.Random(3)
+    long_prompt = [rng.randrange(vocab) for _ in range(2048)]
+    others = {f"r{i}": [rng.randrange(vocab) for _ in range(40 + i)] for i in range(63)}
+    plan = [[("a", long_prompt, [0, 2047])],                               # whole
+            [("b", long_prompt[:1500], [])], [("b", long_prompt[1500:2000], [])],
+            [("b", long_prompt[2000:2046], [])], [("b", long_prompt[2046:], [1])], "end b",
+            # 63 short prompts beside a decoded token: thousands of rows in one step
+            [("a", [7], [0])] + [(rid, toks, [len(toks) - 1]) for rid, toks in others.items()]]
+    for _ in range(2):                                                     # 64 rows; the second replays
+        plan.append([("a", [9], [0])] + [(rid, [11], [0]) for rid in others])
+    for n in (24, 17, 8):                                                  # the products' hand-overs
+        for _ in range(2):
+            plan.append([("a", [5], [0])] + [(f"r{i}", [6], [0]) for i in range(n - 1)])
+    return plan
+
+
+def _run(folder, dtype, plan):
+    from crucible_b200 import LLM
+    from crucible_b200.engine import StepEntry
+    from crucible_b200.ops import tensor_core
+    llm = LLM(folder, dtype=dtype, max_batch=66, kv_pages=66 * 40 + 300, prefill_token_budget=4096)
+    engine = llm.engine
+    rows = []
+    for step in plan:
+        if step == "end b":
+            engine.finish("b")
+            continue
+        logits = engine.step([StepEntry(rid, toks, want) for rid, toks, want in step])
+        rows.extend(logits.float().cpu())
+    tensor_core.check_status(engine.device)
+    assert not engine._graph_failed
+    engine.cache.check_invariants()
+    return rows
+
+
+def _config(which):
+    from crucible_b200.config import shape
+    if which == "120m":
+        raw = shape("120m")
+        raw["n_layer"] = 2
+        return raw
+    # the Llama spelling with heads of 128 and a long K: a quarter of the Llama-3-8B widths
+    raw = shape("llama-8b")
+    raw.update(num_hidden_layers=1, hidden_size=1024, num_attention_heads=8, num_key_value_heads=2,
+               intermediate_size=3584, vocab_size=32000, max_position_embeddings=4096)
+    return raw
+
+
+@pytest.mark.parametrize("which", ["120m", "heads-of-128"])
+def test_bfloat16_follows_float32_at_the_benchmark_widths(tmp_path, which):
+    from crucible_b200.weights import write_random_model
+    raw = _config(which)
+    folder = write_random_model(raw, str(tmp_path / "model"), seed=0)
+    plan = _plan(raw["vocab_size"])
+    ref = _run(folder, "float32", plan)
+    got = _run(folder, "bfloat16", plan)
+    assert len(ref) == len(got) > 200
+    # the prompt whole and in portions: the same logits at its last position
+    assert float((ref[1] - ref[2]).abs().max() / ref[1].abs().max()) < TOLERANCE["float32"]
+    worst = max(float((r - g).abs().max() / r.abs().max()) for r, g in zip(ref, got))
+    assert worst < TOLERANCE["bfloat16"], worst
