@@ -60,7 +60,6 @@ struct DecodeParams {
     const int* block_table;
     int table_stride;
     int n_heads, n_kv_heads, n_requests, page_shift;
-    int max_new_tokens;      // most new tokens of a request in the step (the launcher's use)
     float scale_log2;
     int window;
     float* partial;          // [rows_total * n_heads][n_chunks][head size + 2]
@@ -574,11 +573,7 @@ int launch_as(dim3 grid, cudaStream_t st, const CUtensorMap& mk, const CUtensorM
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    // started under the kernel before it only in steps of at most 32 rows, whose other kernels
-    // are the few-row products; beside the tensor-core products it lost by it (measured)
-    const bool few_rows = p.n_requests * p.max_new_tokens <= 32;
-    cb_launch_ex(attention_decode_tcgen05_kernel<HD, RMAX>, grid, dim3(192), smem, st, 1, few_rows, mk, mv,
-                 rk, rv, p);
+    cb_launch(attention_decode_tcgen05_kernel<HD, RMAX>, grid, dim3(192), smem, st, mk, mv, rk, rv, p);
     return cb_last_error();
 }
 
@@ -629,7 +624,6 @@ CB_EXPORT int cb_attention_decode_tcgen05(const void* qkv, int qkv_stride, void*
     p.n_heads = n_heads;
     p.n_kv_heads = n_kv_heads;
     p.n_requests = n_requests;
-    p.max_new_tokens = max_new_tokens;
     p.page_shift = shift;
     p.scale_log2 = scale * LOG2E;
     p.window = window;

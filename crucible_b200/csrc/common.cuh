@@ -77,9 +77,8 @@ static inline int cb_last_error() {
 // file's bit): the tensor-core products for more than 32 rows gain most (their barriers,
 // tensor memory and descriptors are set up under the kernel before: 1.09 -> 1.02 ms per
 // 2,048-token prefill, 0.93 -> 0.88 ms per batch-64 decode step); the prompt attention a
-// little; the split decode attention gains beside the few-row kernels (0.42 -> 0.41 ms at
-// batch 8) and loses beside the tensor-core products (0.87 -> 0.92 ms at batch 64), so its
-// launcher allows it for steps of at most 32 rows; norms and the like gain in small
+// little; the split decode attention gains once it lets its own successor start only after
+// its query rows are staged (0.42 -> 0.41 ms at batch 8, 0.85 -> 0.84 ms at batch 64); norms and the like gain in small
 // launches and lose in large ones (CB_PDL_MAX_BLOCKS); the few-row products lose if they
 // let their successor start at once (0.41 -> 0.44 ms: its loads of weights get in the way of
 // the loads this kernel waits for) and gain if they do so once their own rows are staged
