@@ -315,13 +315,14 @@ def run_profile_case(args):
     engine = llm.engine
     vocab = engine.config.vocab_size
     if args.profile_case == "prefill":
-        tokens = [rng.randrange(vocab) for _ in range(2048)]
-        engine.step([StepEntry("w", tokens, [2047])])
+        n = args.context                                    # one prompt of this many tokens
+        tokens = [rng.randrange(vocab) for _ in range(n)]
+        engine.step([StepEntry("w", tokens, [n - 1])])
         engine.finish("w")
         torch.cuda.synchronize()
         torch.cuda.profiler.start()
         for i in range(args.steps):
-            engine.step([StepEntry("p", tokens, [2047])])
+            engine.step([StepEntry("p", tokens, [n - 1])])
             engine.finish("p")
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
