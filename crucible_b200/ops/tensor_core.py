@@ -368,6 +368,25 @@ def _attention_decode_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_h
     return True
 
 
+def decode_chunk_keys(blocks_per_chunk: int, context_bucket: int, tcgen05: bool) -> int:
+    """Keys per block of the split attention for decoded tokens: 256 * 2^k, a function of the
+    step's shape alone (so a captured step replays).  `blocks_per_chunk`: blocks that one chunk
+    of every request takes (requests x KV heads x groups of 16 packed rows)."""
+    # the tcgen05 form keeps two blocks per SM busy with far fewer instructions per key, so it
+    # wants fewer, longer chunks than the mma.sync form
+    enough = DECODE_TC_BLOCKS if tcgen05 else 4 * N_SMS
+    chunk = 256
+    while chunk * 2 <= context_bucket and blocks_per_chunk * (context_bucket // (chunk * 2)) >= enough:
+        chunk *= 2
+    if tcgen05 and chunk >= 512 and chunk * 2 == context_bucket:
+        # Half the bucket is the worst chunk: a context lies in the bucket's upper half, so every
+        # request would bring one full chunk and a scrap of a second.  Quarters while they stay
+        # two waves of blocks (two to an SM), else the whole bucket as one chunk (measured on
+        # B200, 24 requests x 4 KV heads at 2,100 tokens: 0.64 against 0.75 ms per step).
+        chunk = chunk // 2 if blocks_per_chunk * 4 <= 4 * N_SMS else context_bucket
+    return chunk
+
+
 def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx, cache,
                     binding) -> bool:
     """Tensor-core attention over the paged cache.  Takes head sizes that are
@@ -388,24 +407,13 @@ def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx,
     # context bucket; the chunk is the largest that still gives a few waves of blocks
     # over the 148 SMs (a function of the step's shape alone, so a captured step
     # replays; contexts fill about half of their bucket on average).
-    chunk_keys = 256
     pt = cache.page_tokens
     decode_tc = (USE_TCGEN05_DECODE and split and head_dim in (64, 128) and out.stride(0) % 2 == 0
                  and 8 <= pt <= 128 and pt & (pt - 1) == 0)
+    chunk_keys = 256
     if split:
-        # the tcgen05 form keeps two blocks per SM busy with far fewer instructions per
-        # key, so it wants fewer, longer chunks than the mma.sync form
-        enough = DECODE_TC_BLOCKS if decode_tc else 4 * N_SMS
         blocks_per_chunk = ctx.n_requests * n_kv_heads * (-(-host.max_new_tokens * n_rep // 16))
-        while (chunk_keys * 2 <= host.context_bucket
-               and blocks_per_chunk * (host.context_bucket // (chunk_keys * 2)) >= enough):
-            chunk_keys *= 2
-        if decode_tc and chunk_keys >= 512 and chunk_keys * 2 == host.context_bucket:
-            # Half the bucket is the worst chunk: a context lies in the bucket's upper half, so
-            # every request would bring one full chunk and a scrap of a second.  Quarters while
-            # they stay two waves of blocks (two to an SM), else the whole bucket as one chunk (measured on
-            # B200, 24 requests x 4 KV heads at 2,100 tokens: 0.64 against 0.75 ms per step).
-            chunk_keys = chunk_keys // 2 if blocks_per_chunk * 4 <= 4 * N_SMS else host.context_bucket
+        chunk_keys = decode_chunk_keys(blocks_per_chunk, host.context_bucket, decode_tc)
     n_chunks = host.context_bucket // chunk_keys if split else 0
     partial = counters = None
     if split:

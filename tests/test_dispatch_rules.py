@@ -36,3 +36,22 @@ def test_tall_tiles_only_where_they_fill_the_sms():
     assert tensor_core._tall_tiles(2048, 4096, 768)            # the 120M shape's gate/up: 128 tiles
     assert not tensor_core._tall_tiles(2048, 768, 2048)        # ... its down projection: 24 tiles
     assert not tensor_core._tall_tiles(512, 28672, 4096)
+
+
+@pytest.mark.parametrize("bucket", [256, 512, 1024, 4096, 8192])
+@pytest.mark.parametrize("blocks", [1, 4, 32, 48, 96, 128, 160, 256, 1000])
+@pytest.mark.parametrize("tcgen05", [True, False])
+def test_decode_chunks_divide_the_bucket(blocks, bucket, tcgen05):
+    chunk = tensor_core.decode_chunk_keys(blocks, bucket, tcgen05)
+    assert 256 <= chunk <= bucket and bucket % chunk == 0
+    if tcgen05 and chunk >= 512:
+        assert chunk * 2 != bucket                  # never one full chunk and a scrap
+
+
+def test_decode_chunks_of_the_benchmark_points():
+    # 4 KV heads, contexts of 2,048 to 2,304 tokens (bucket 4,096)
+    assert tensor_core.decode_chunk_keys(1 * 4, 4096, True) == 256
+    assert tensor_core.decode_chunk_keys(8 * 4, 4096, True) == 512
+    assert tensor_core.decode_chunk_keys(24 * 4, 4096, True) == 1024
+    assert tensor_core.decode_chunk_keys(32 * 4, 4096, True) == 1024
+    assert tensor_core.decode_chunk_keys(64 * 4, 4096, True) == 4096
