@@ -34,10 +34,10 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-REFERENCE_UNAVAILABLE = ("the reference is a Rust engine with NVRTC kernels for sm_120 plus "
-                         "loose Python scripts; pip finds neither setup.py nor pyproject.toml in "
-                         "it and cargo is not in this image, so nothing of it can be installed "
-                         "or run here")
+REFERENCE_DIR = os.path.join(ROOT, "baseline", "_ref")
+REFERENCE_NOTE = ("the reference's engine is Rust with NVRTC kernels for sm_120 (no cargo in this "
+                  "image, not installable by pip); this arm runs the reference's own PyTorch model, "
+                  "an unmodified copy of its model.py, through its GPT.forward / GPT.generate")
 
 
 def read_peaks():
@@ -293,6 +293,123 @@ def run_ours(args):
     return 0
 
 
+def run_reference(args):
+    """The reference arm: the reference's own PyTorch model (`model.py`, copied unmodified
+    to baseline/_ref/) at the same shape, batch and context, through its stock code path:
+    `GPT.generate` (`model.py:371-383`, which runs the whole sequence again for every new
+    token: it keeps no cache) for decoding and `GPT.forward` (`model.py:343-365`) for the
+    prefill.  Nothing of crucible_b200 is imported here and none of its libraries is
+    loaded."""
+    path = os.path.join(REFERENCE_DIR, "model.py")
+    if not os.path.exists(path):
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "baseline/_ref/model.py is absent (copy the reference's model.py "
+                          "there); " + REFERENCE_NOTE}))
+        return 0
+    import importlib.util
+    import torch
+    spec = importlib.util.spec_from_file_location("crucible_reference_model", path)
+    ref = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = ref
+    spec.loader.exec_module(ref)
+    if args.shape != "120m":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          f"the reference arm runs the 120M shape only, not {args.shape}"}))
+        return 0
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    layers = args.layers or 12
+    cfg = ref.GPTConfig(vocab_size=50304, n_layer=layers, n_head=12, n_kv_head=4, n_embd=768,
+                        block_size=4096, attention="gqa")
+    model = ref.GPT(cfg).to(dev).to(torch.bfloat16).eval()
+    batch, ctx_len, steps, warmup = args.batch, args.context, args.steps, max(3, args.warmup)
+    gen = torch.Generator().manual_seed(1)
+    peaks = read_peaks()
+    clocks = ClockSampler()
+    clocks.start()
+    windows = []
+
+    def ids(b, n):
+        return torch.randint(0, cfg.vocab_size, (b, n), generator=gen, dtype=torch.long)
+
+    def timed(fn):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        w0 = time.time()
+        e0.record()
+        out = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        windows.append((w0, time.time()))
+        return e0.elapsed_time(e1), out
+
+    with torch.no_grad():
+        # prefill: one 2,048-token forward (logits at the last position only)
+        t_prefill, n_prefill = 2048, 8
+        prompts = [ids(1, t_prefill).to(dev) for _ in range(warmup + n_prefill)]
+        for x in prompts[:warmup]:
+            model(x)
+        ms, _ = timed(lambda: [model(x) for x in prompts[warmup:]])
+        prefill_ms = ms / n_prefill
+        d, inter = 768, 64 * ((int(2 * (4 * 768) / 3) + 63) // 64)
+        per_layer = d * 768 + 2 * d * 256 + 768 * d + 3 * d * inter
+        flops = (2 * t_prefill * layers * per_layer + 2 * 50304 * d
+                 + layers * 2 * 2 * 768 * t_prefill * (t_prefill + 1) // 2)
+        prefill = {"value": round(t_prefill / (prefill_ms / 1e3), 1), "tokens": t_prefill,
+                   "ms": round(prefill_ms, 4), "steps": n_prefill,
+                   "frac": round(flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}
+
+        def decode(b, k):
+            start = ids(b, ctx_len).to(dev)
+            model.generate(start, warmup, temperature=1.0, top_k=1)
+            ms, _ = timed(lambda: model.generate(start, k, temperature=1.0, top_k=1))
+            return b * k / (ms / 1e3), ms / k
+
+        tok_s, ms_per_step = decode(batch, steps)
+        points = {}
+        for b in (1, 64):
+            k = min(steps, 16)              # a step of the reference costs b x 2,048 tokens
+            r = decode(b, k)
+            points[f"decode_b{b}"] = round(r[0], 1)
+            points[f"decode_b{b}_ms"] = round(r[1], 4)
+        # end to end: host ids in (pinned), host ids out, around the same generate call
+        host = ids(batch, ctx_len).pin_memory()
+        t0 = time.time()
+        out = model.generate(host.to(dev, non_blocking=True), steps, temperature=1.0, top_k=1).cpu()
+        wall = time.time() - t0
+        windows.append((t0, time.time()))
+        assert out.shape == (batch, ctx_len + steps)
+    clocks.stop()
+    weight_bytes = (layers * per_layer + 50304 * d) * 2
+    kv_token_bytes = 2 * 256 * layers * 2
+    achieved = (weight_bytes + batch * (ctx_len + warmup + (steps - 1) / 2.0) * kv_token_bytes) \
+        / (ms_per_step / 1e3) / 1e9
+    line = {
+        "metric": f"decode tok/s at batch {batch} (120M shape, bf16, {ctx_len:,}-token contexts)",
+        "value": round(tok_s, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "reference", "note": REFERENCE_NOTE + "; weights cast to bfloat16, greedy "
+                                     "(top_k=1), no KV cache in its generate",
+        "config": {"model": "crucible-120m-shape", "layers": layers, "layers_of_shape": 12,
+                   "hidden": 768, "q_heads": 12, "kv_heads": 4, "head_dim": 64,
+                   "intermediate": inter, "vocab": 50304, "tied_head": True,
+                   "global_batch": batch, "seq_len": ctx_len, "new_tokens": steps,
+                   "kv_page_tokens": 0, "parallelism": "single-gpu", "l2": "inputs_exceed_l2",
+                   "weights": "random N(0,0.02) seed 0 (its own init)"},
+        "e2e": {"value": round(batch * steps / wall, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": batch * ctx_len * 8 // steps,
+                "d2h_bytes_per_step": batch * (ctx_len + steps) * 8 // steps, "steps": steps},
+        "gpu_launches": 0, "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
+                     "peaks": peaks["source"]},
+        "points": points, "clocks": clocks.summary(windows),
+    }
+    print(json.dumps(line))
+    return 0
+
+
 def run_profile_case(args):
     """A small workload for a profiler (ncu): builds the 120M shape with
     `--layers` layers, fills `--batch` requests to `--context` tokens, then runs
@@ -366,8 +483,7 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
-        return 0
+        return run_reference(args)
     if args.warmup < 3:
         args.warmup = 3
     return run_ours(args)

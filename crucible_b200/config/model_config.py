@@ -68,11 +68,47 @@ class FeedForwardSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
+    """One stored layer.  `norms` are the arrangement's norms by name, as many as it
+    asks for: two for `pre_norm` ("mixer_norm", "feed_forward_norm"); an arrangement
+    with sandwich norms or with one norm for parallel branches names others.  The names
+    are also the parts' paths ("layer.<name>.gain") in the architecture's tensor names."""
     arrangement: str       # registered block arrangement, e.g. "pre_norm"
     mixer: MixerSpec
-    mixer_norm: NormSpec
     feed_forward: FeedForwardSpec
-    feed_forward_norm: NormSpec
+    norms: Tuple[Tuple[str, NormSpec], ...]
+
+    def norm(self, name: str) -> NormSpec:
+        for key, spec in self.norms:
+            if key == name:
+                return spec
+        raise ConfigError(f"the layer has no norm named {name!r} "
+                          f"(it has {[k for k, _ in self.norms]})")
+
+    @property
+    def mixer_norm(self) -> NormSpec:
+        return self.norm("mixer_norm")
+
+    @property
+    def feed_forward_norm(self) -> NormSpec:
+        return self.norm("feed_forward_norm")
+
+
+def pre_norm_layer(mixer: MixerSpec, mixer_norm: NormSpec, feed_forward: FeedForwardSpec,
+                   feed_forward_norm: NormSpec) -> LayerSpec:
+    """x += mixer(norm(x)); x += feed_forward(norm(x))."""
+    return LayerSpec(arrangement="pre_norm", mixer=mixer, feed_forward=feed_forward,
+                     norms=(("mixer_norm", mixer_norm), ("feed_forward_norm", feed_forward_norm)))
+
+
+@dataclass(frozen=True)
+class EndSpec:
+    """The token embedding or the LM head: a registered kind and free-form options
+    (an embedding scale, a soft cap of the logits, a bias: whatever that kind reads)."""
+    kind: str
+    extra: Tuple[Tuple[str, Any], ...] = ()
+
+    def option(self, key: str, default: Any = None) -> Any:
+        return dict(self.extra).get(key, default)
 
 
 @dataclass(frozen=True)
@@ -93,6 +129,8 @@ class ModelConfig:
     layers: Tuple[LayerSpec, ...]
     run_order: Tuple[RunEntry, ...]
     final_norm: NormSpec
+    embedding: EndSpec = EndSpec("token")
+    head: EndSpec = EndSpec("linear")
     tensor_names: Mapping[str, str] = field(default_factory=dict, compare=False)
     raw: Mapping[str, Any] = field(default_factory=dict, compare=False)
 
@@ -114,10 +152,12 @@ class ModelConfig:
                 raise ConfigError(f"run_order[{i}] reads the cache of layer "
                                   f"{entry.cache_of}, which does not exist")
         for i, layer in enumerate(self.layers):
-            for what, width in (("mixer", layer.mixer.width),
-                                ("mixer_norm", layer.mixer_norm.width),
-                                ("feed_forward", layer.feed_forward.width),
-                                ("feed_forward_norm", layer.feed_forward_norm.width)):
+            names = [name for name, _ in layer.norms]
+            if len(set(names)) != len(names):
+                raise ConfigError(f"layer {i} names a norm twice: {names}")
+            for what, width in ([("mixer", layer.mixer.width),
+                                 ("feed_forward", layer.feed_forward.width)]
+                                + [(name, spec.width) for name, spec in layer.norms]):
                 if width != self.hidden_size:
                     raise ConfigError(f"layer {i} {what} width {width} differs from "
                                       f"hidden_size {self.hidden_size}")

@@ -154,8 +154,14 @@ struct KvLoader {
                             page_index = key / p.page_tokens;
                             slot = key - page_index * p.page_tokens;
                         }
-                        off[v] = (size_t)table[page_index] * page_elems +
-                                 (size_t)(base[u] + slot * p.head_dim);
+                        // A page that the window has passed was given back and its table
+                        // entry is negative: every key in it is masked for every row, so it
+                        // is zero-filled like a key past the end instead of being read.
+                        const int page = table[page_index];
+                        valid[v] = page >= 0;
+                        if (valid[v])
+                            off[v] = (size_t)page * page_elems +
+                                     (size_t)(base[u] + slot * p.head_dim);
                     }
                 }
             }

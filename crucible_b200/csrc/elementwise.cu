@@ -171,11 +171,15 @@ CB_EXPORT int cb_rmsnorm(const float* x, const float* gain, void* out, int out_d
     cudaStream_t s = (cudaStream_t)stream;
     const bool vec = (width & 3) == 0 && width <= 4 * 4 * 1024 && ((uintptr_t)x & 15) == 0 &&
                      ((uintptr_t)gain & 15) == 0;
-    // many rows: a warp per row; the output's rows must allow the vector stores
-    const bool out_vec = out_dtype == CB_F32 ? ((uintptr_t)out & 15) == 0 : ((uintptr_t)out & 7) == 0;
-    if (vec && out_vec && n_rows >= 64 && (width >> 2) <= 32 * 32) {
-        if (out_dtype == CB_F32) launch_rmsnorm_warp<float>(x, gain, (float*)out, n_rows, width, eps, s);
-        else launch_rmsnorm_warp<__nv_bfloat16>(x, gain, (__nv_bfloat16*)out, n_rows, width, eps, s);
+    // Many rows with a bfloat16 result: a warp per row; the output's rows must allow the
+    // vector stores.  A float32 result (the 32-bit engine) never takes this form: the warp
+    // kernel adds a row's squares in another order than the block kernels below, and the
+    // 32-bit path's sums must be the same whatever the number of rows in the step, so that
+    // a token's values do not depend on how its prompt was cut.  Below, the kernel and its
+    // block size are functions of the width and of the pointers' alignment alone.
+    const bool out_vec = ((uintptr_t)out & 7) == 0;
+    if (vec && out_vec && out_dtype != CB_F32 && n_rows >= 64 && (width >> 2) <= 32 * 32) {
+        launch_rmsnorm_warp<__nv_bfloat16>(x, gain, (__nv_bfloat16*)out, n_rows, width, eps, s);
         return cb_last_error();
     }
     if (vec) {

@@ -770,3 +770,30 @@ CB_EXPORT int cb_gemm_tcgen05_rope(const void* A, const void* W, void* q_out, in
     }
     return CB_ERR_UNSUPPORTED;
 }
+
+// ---------------------------------------------------------------------------
+// A wait that runs out, for tests of the failure path: one thread waits, with
+// the kernels' own bounded wait and a short limit given by the caller, on an
+// mbarrier at which nothing ever arrives; when the limit is reached it records
+// ST_PROBE_TIMEOUT in the status word exactly as a real role does, and the
+// kernel returns.  Nothing faults, traps or hangs; the context stays usable.
+// ---------------------------------------------------------------------------
+namespace {
+__global__ void wait_probe_kernel(int* status, uint32_t limit) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        tc::mbar_init(&bar, 1);
+        tc::fence_barrier_init();
+        if (!tc::mbar_wait(&bar, 0, &abort_flag, limit))
+            tc::give_up(&abort_flag, status, tc::ST_PROBE_TIMEOUT);
+    }
+}
+}  // namespace
+
+CB_EXPORT int cb_tc_wait_probe(int* status, int limit, void* stream) {
+    if (limit <= 0 || limit > (1 << 20)) return CB_ERR_UNSUPPORTED;
+    wait_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, (uint32_t)limit);
+    return (int)cudaGetLastError();
+}

@@ -10,8 +10,9 @@
  * scratch with the library instead.
  *
  * It computes, for each of n_rows rows of fp32 logits [n_rows, vocab], the index
- * of the highest value (lowest index among equals, NaN never wins; a row of
- * NaNs gives 0), exactly as cb_argmax_rows does, in two kernels: per-slice
+ * of the highest value (lowest index among equals; a NaN displaces nothing and a
+ * NaN in column 0 is never displaced, so such a row gives 0), exactly as
+ * cb_argmax_rows does, in two kernels: per-slice
  * maxima into scratch, then the maximum over the slices.
  *
  * Scratch: a file-scope device array inside the library, 64 KiB, enough for
@@ -22,7 +23,9 @@
  * Nothing in the array has to start at zero: each call overwrites every entry it
  * later reads, so stale contents of an earlier call are harmless.
  *
- * The first call on a device looks up the array's device address (one
+ * Every call, not only the first, must be made with the logits' device current:
+ * the scratch address is chosen by cudaGetDevice at each call.  The first call
+ * on a device also looks up the array's device address (one
  * cudaGetSymbolAddress with that device current); make that first call before
  * any stream capture begins.  No call allocates or frees anything: no
  * cudaMalloc, cudaFree, or library routine that allocates.

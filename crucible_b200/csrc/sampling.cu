@@ -2,8 +2,10 @@
 // the top-k candidates, one block per logits row.
 //
 // Rules, from the reference's sampler (engine/src/sampling.rs):
-//  * greedy: the highest logit, ties to the lowest index, NaN never wins
-//    (:141-149; kernel engine/kernels/kernels.cu:1201-1212);
+//  * greedy: `best = 0; for i: if v[i] > v[best]: best = i` (:141-149): the highest
+//    logit, ties to the lowest index; a NaN never displaces anything, and a NaN at
+//    index 0 is never displaced (nothing compares greater than it), so such a row
+//    gives 0;
 //  * sampled: candidates are the k best in canonical order (logit descending,
 //    token id ascending; :161-163) found by radix selection on a 64-bit key
 //    (value key << 32 | ~id; :178-202); weights exp((v - max) / T) in fp32,
@@ -43,6 +45,13 @@ __device__ __forceinline__ void publish(int row, int id, int* out_ids, const int
     if (scatter_index != nullptr) scatter_out[scatter_index[row]] = id;
 }
 
+// The step's status word rides to the host with the chosen ids: one thread of the
+// launch copies it behind them, so that the host, which reads the ids anyway, learns
+// of a kernel that gave up a bounded wait without a transfer or a wait of its own.
+__device__ __forceinline__ void relay_status(const int* status_src, int* status_dst) {
+    if (status_src != nullptr && status_dst != nullptr) *status_dst = *status_src;
+}
+
 __device__ void block_argmax(const float* row, int vocab, int* out_id, float* s_val, int* s_idx) {
     float bv = -INFINITY;
     int bi = 0x7fffffff;
@@ -63,7 +72,8 @@ __device__ void block_argmax(const float* row, int vocab, int* out_id, float* s_
         const int nw = (blockDim.x + 31) >> 5;
         for (int w = 1; w < nw; ++w)
             if (s_val[w] > bv || (s_val[w] == bv && s_idx[w] < bi)) { bv = s_val[w]; bi = s_idx[w]; }
-        *out_id = bi == 0x7fffffff ? 0 : bi;   // every logit NaN: token 0
+        // every logit NaN: token 0; a NaN at index 0 is never displaced
+        *out_id = (bi == 0x7fffffff || row[0] != row[0]) ? 0 : bi;
     }
     __syncthreads();
 }
@@ -72,9 +82,11 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
                    const int* __restrict__ top_k, const float* __restrict__ uniform,
                    int* __restrict__ out_ids, const int* __restrict__ scatter_index,
-                   int* __restrict__ scatter_out) {
+                   int* __restrict__ scatter_out, const int* __restrict__ status_src,
+                   int* __restrict__ status_dst) {
     cb_pdl_trigger();
     cb_pdl_wait();
+    if (blockIdx.x == 0 && threadIdx.x == 0) relay_status(status_src, status_dst);
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     __shared__ unsigned int hist[256];
@@ -183,9 +195,11 @@ sample_rows_kernel(const float* __restrict__ logits, int vocab, const float* __r
 
 __global__ void __launch_bounds__(256)
 argmax_rows_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out_ids,
-                   const int* __restrict__ scatter_index, int* __restrict__ scatter_out) {
+                   const int* __restrict__ scatter_index, int* __restrict__ scatter_out,
+                   const int* __restrict__ status_src, int* __restrict__ status_dst) {
     cb_pdl_trigger();
     cb_pdl_wait();
+    if (blockIdx.x == 0 && threadIdx.x == 0) relay_status(status_src, status_dst);
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     __shared__ int id;
@@ -228,6 +242,9 @@ argmax_slices_kernel(const float* __restrict__ logits, int vocab, float* __restr
     if (threadIdx.x == 0) {
         for (int w = 1; w < 8; ++w)
             if (s_val[w] > bv || (s_val[w] == bv && s_idx[w] < bi)) { bv = s_val[w]; bi = s_idx[w]; }
+        // a NaN at index 0 is never displaced: it enters the second stage as the
+        // highest value at the lowest index, which wins there against everything
+        if (slice == 0 && r[0] != r[0]) { bv = INFINITY; bi = 0; }
         part_val[row * ARGMAX_SLICES + slice] = bv;
         part_idx[row * ARGMAX_SLICES + slice] = bi;
     }
@@ -236,9 +253,12 @@ argmax_slices_kernel(const float* __restrict__ logits, int vocab, float* __restr
 __global__ void argmax_final_kernel(const float* __restrict__ part_val,
                                     const int* __restrict__ part_idx, int* __restrict__ out_ids,
                                     const int* __restrict__ scatter_index,
-                                    int* __restrict__ scatter_out) {
+                                    int* __restrict__ scatter_out,
+                                    const int* __restrict__ status_src,
+                                    int* __restrict__ status_dst) {
     cb_pdl_trigger();
     cb_pdl_wait();
+    if (blockIdx.x == 0 && threadIdx.x == 0) relay_status(status_src, status_dst);
     const int row = blockIdx.x, lane = threadIdx.x;
     float bv = part_val[row * ARGMAX_SLICES + lane];
     int bi = part_idx[row * ARGMAX_SLICES + lane];
@@ -255,14 +275,16 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_val,
 
 // scratch: n_rows * 32 floats followed by n_rows * 32 ints (cb_argmax_scratch_bytes),
 // or null: then one block per row does the whole row.
+// status_src, status_dst (both or neither): *status_dst = *status_src, by the launch
+// that writes the ids.
 CB_EXPORT int cb_argmax_rows(const float* logits, int n_rows, int vocab, int* out_ids,
                              void* scratch, const int* scatter_index, int* scatter_out,
-                             void* stream) {
+                             const int* status_src, int* status_dst, void* stream) {
     if (n_rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (scratch == nullptr || vocab < 4096) {
         cb_launch(argmax_rows_kernel, dim3(n_rows), dim3(256), 0, s, logits, vocab, out_ids,
-                  scatter_index, scatter_out);
+                  scatter_index, scatter_out, status_src, status_dst);
         return cb_last_error();
     }
     float* part_val = (float*)scratch;
@@ -270,7 +292,7 @@ CB_EXPORT int cb_argmax_rows(const float* logits, int n_rows, int vocab, int* ou
     cb_launch(argmax_slices_kernel, dim3(ARGMAX_SLICES, n_rows), dim3(256), 0, s, logits, vocab, part_val,
                                                                      part_idx);
     cb_launch(argmax_final_kernel, dim3(n_rows), dim3(32), 0, s, (const float*)part_val,
-              (const int*)part_idx, out_ids, scatter_index, scatter_out);
+              (const int*)part_idx, out_ids, scatter_index, scatter_out, status_src, status_dst);
     return cb_last_error();
 }
 
@@ -280,11 +302,13 @@ CB_EXPORT long cb_argmax_scratch_bytes(int n_rows) { return (long)n_rows * ARGMA
 // the launcher refuses k above the kernel's candidate capacity.
 CB_EXPORT int cb_sample_rows(const float* logits, int n_rows, int vocab, const float* temperature,
                              const int* top_k, const float* uniform, int max_top_k, int* out_ids,
-                             const int* scatter_index, int* scatter_out, void* stream) {
+                             const int* scatter_index, int* scatter_out, const int* status_src,
+                             int* status_dst, void* stream) {
     if (n_rows <= 0) return 0;
     if (max_top_k > MAX_TOP_K) return CB_ERR_UNSUPPORTED;
-    cb_launch(sample_rows_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, 
-        logits, vocab, temperature, top_k, uniform, out_ids, scatter_index, scatter_out);
+    cb_launch(sample_rows_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream,
+              logits, vocab, temperature, top_k, uniform, out_ids, scatter_index, scatter_out,
+              status_src, status_dst);
     return cb_last_error();
 }
 
@@ -322,6 +346,7 @@ CB_EXPORT int cb_argmax_rows_static(const float* logits, int n_rows, int vocab, 
     cb_launch(argmax_slices_kernel, dim3(ARGMAX_SLICES, n_rows), dim3(256), 0, s, logits, vocab,
               part_val, part_idx);
     cb_launch(argmax_final_kernel, dim3(n_rows), dim3(32), 0, s, (const float*)part_val,
-              (const int*)part_idx, out_ids, (const int*)nullptr, (int*)nullptr);
+              (const int*)part_idx, out_ids, (const int*)nullptr, (int*)nullptr,
+              (const int*)nullptr, (int*)nullptr);
     return cb_last_error();
 }

@@ -21,6 +21,7 @@ constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr int ST_PRODUCER_TIMEOUT = 1;
 constexpr int ST_MMA_TIMEOUT = 2;
 constexpr int ST_EPILOGUE_TIMEOUT = 3;
+constexpr int ST_PROBE_TIMEOUT = 4;     // the wait probe of the tests (see cb_tc_wait_probe)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -61,8 +62,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait.  Returns false if the limit ran out or the block is aborting.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          uint32_t limit = WAIT_LIMIT) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 1023u) == 1023u && *abort_flag) return false;
     }

@@ -90,8 +90,17 @@ class Engine:
         self.cache = CacheManager(
             [GroupPolicy(o.page_tokens, g.need.window) for g in groups],
             [n_pages] * len(groups), o.max_requests)
-        self.storages = [CacheStorage(len(g.layers), n_pages, o.page_tokens, g.need.kv_heads,
+        # One page more than the pool hands out: the null page, never written, all zeros.
+        # A table entry whose page the window has passed and given back names it, so a
+        # kernel that loads whole tiles of keys reads zeros there (every such key is masked)
+        # and never another request's data.
+        self.storages = [CacheStorage(len(g.layers), n_pages + 1, o.page_tokens, g.need.kv_heads,
                                       g.need.head_dim, self.dtype, self.device) for g in groups]
+        self.null_page = n_pages
+        # which live request (by state slot) each page belongs to, as the tables that went to
+        # the device say: the check that no two requests of a step name the same page
+        self._page_owner = [np.full(n_pages, -1, dtype=np.int32) for _ in groups]
+        self._has_device_token = set()      # state slots whose latest token is on the device
         self.table_strides = tuple(ctx_pages for _ in groups)
         self.state = None
         if self.model.state_bytes:
@@ -106,6 +115,10 @@ class Engine:
         self._graph_generation = 0
         self._graph_failed = False
         self._graph_error = None
+        self._graph_replays = 0          # steps run by replaying a captured graph ...
+        self._prompt_graph_replays = 0   # ... of which steps that held a prompt portion
+        from ..ops import tensor_core
+        self._failures_seen = tensor_core.FAILURES[0]
         self._shapes_seen = {}
         self._table_rows = {}
 
@@ -167,6 +180,7 @@ class Engine:
         ids travel to the host asynchronously; the returned object's `get()` waits
         for them."""
         slots = [self.cache.state_slot(r) for r in requests]
+        self._has_device_token.update(slots)
         return self._get_sampler().sample(logits, rows, slots=slots,
                                           scatter_out=self.device_tokens, defer=True)
 
@@ -175,6 +189,7 @@ class Engine:
     def add_request(self, request, lifetime_tokens: Optional[int] = None,
                     max_step_tokens: Optional[int] = None) -> None:
         slot = self.cache.add_request(request, lifetime_tokens, max_step_tokens)
+        self._has_device_token.discard(slot)   # the slot's last owner's token is not this one's
         if self.state is not None:
             self.state[slot].zero_()      # a slot is handed out clean
 
@@ -183,9 +198,21 @@ class Engine:
 
     def finish(self, request) -> None:
         """Gives back everything the request holds.  Call between steps only."""
+        self._forget(request)
         self.cache.remove_request(request)
+
+    def _forget(self, request) -> None:
+        """Drops what the engine itself remembers of a request that is about to go."""
+        slot = self.cache.state_slot(request)
+        self._has_device_token.discard(slot)
         for g in range(len(self.table_strides)):
-            self._table_rows.pop((request, g), None)
+            hit = self._table_rows.pop((request, g), None)
+            if hit is not None:
+                row, known = hit
+                mine = row[:known]
+                mine = mine[mine != self.null_page]
+                owner = self._page_owner[g]
+                owner[mine[owner[mine] == slot]] = -1
 
     def held_tokens(self, request) -> int:
         return self.cache.length(request)
@@ -210,14 +237,19 @@ class Engine:
                     added.append(e.request)
                 self.cache.extend(e.request, len(e.tokens))
                 extended.append(e)
+            # the tables that will go to the device: every page in range and no page named
+            # by two requests (`engine/src/gpu_model.rs:2809-2934` refuses such a batch)
+            rows = [[self._table_row(e.request, g) for e in entries]
+                    for g in range(len(self.table_strides))]
         except Exception:
-            # a step that cannot get its pages changes nothing
+            # a step that cannot get its pages, or whose tables are not sound, changes nothing
             for e in extended:
                 self._shrink(e.request, len(e.tokens))
             for request in added:
+                self._forget(request)
                 self.cache.remove_request(request)
             raise
-        ctx = self._make_context(entries)
+        ctx = self._make_context(entries, rows)
         if token_source is not None:
             ctx.token_ids.copy_(token_source[:ctx.n_tokens])
         if self.options.graph and not self._graph_failed:
@@ -244,6 +276,12 @@ class Engine:
 
     def _replay_or_capture(self, ctx: StepContext, at_once: bool) -> torch.Tensor:
         from .. import ops
+        from ..ops import tensor_core
+        if self._failures_seen != tensor_core.FAILURES[0]:
+            # a kernel gave up since the last step: what was captured is kept no longer
+            self._failures_seen = tensor_core.FAILURES[0]
+            self._graphs.clear()
+            self._shapes_seen.clear()
         if self._graph_generation != self.scratch.generation:
             self._graphs.clear()
             self._graph_generation = self.scratch.generation
@@ -255,6 +293,8 @@ class Engine:
             graph, logits, launches = hit
             graph.replay()
             ops.LAUNCHES[0] += launches
+            self._graph_replays += 1
+            self._prompt_graph_replays += 0 if at_once else 1
             return logits
         logits = self.model.forward(ctx)           # eager: also sizes the scratch buffers
         if self._graph_generation != self.scratch.generation:
@@ -290,7 +330,14 @@ class Engine:
         for g, pool in enumerate(self.cache.pools):
             needed = -(-r.length // pool.page_tokens)
             while len(r.tables[g]) > needed:
-                pool.release(r.tables[g].pop())
+                page = r.tables[g].pop()
+                pool.release(page)
+                if 0 <= page < pool.n_pages and self._page_owner[g][page] == r.slot:
+                    self._page_owner[g][page] = -1
+            hit = self._table_rows.get((request, g))
+            if hit is not None and hit[1] > needed:
+                hit[0][needed:] = 0
+                self._table_rows[(request, g)] = (hit[0], needed)
 
     def _validate(self, entries: List[StepEntry]) -> None:
         if not entries:
@@ -308,7 +355,8 @@ class Engine:
             if n == 0:
                 raise StepError(f"request {e.request!r} brings no tokens")
             if n == 1 and e.tokens[0] == DEVICE_TOKEN:
-                if not cache.has(e.request):
+                if (not cache.has(e.request)
+                        or cache.state_slot(e.request) not in self._has_device_token):
                     raise StepError(f"request {e.request!r} has no token on the device yet")
             elif min(e.tokens) < 0 or max(e.tokens) >= vocab:
                 bad = next(t for t in e.tokens if not 0 <= t < vocab)
@@ -342,8 +390,10 @@ class Engine:
                             f"request slots are free")
 
     def _table_row(self, request, group: int) -> np.ndarray:
-        """The request's block table of `group`, padded to the table stride, kept as a
-        numpy row that is only touched when the table changed."""
+        """The request's block table of `group` as it goes to the device, padded to the
+        table stride: a numpy row that is only touched when the table changed.  Entries
+        given back early name the null page.  Every page that is new to the row is
+        checked: inside the pool, and not in the row of another live request."""
         table = self.cache.block_table(request, group)
         key = (request, group)
         row, known = self._table_rows.get(key, (None, 0))
@@ -351,23 +401,59 @@ class Engine:
         if row is None:
             row = np.zeros(self.table_strides[group], dtype=np.int32)
             known = 0
-        windowed = self.cache.policies[group].window is not None
-        if windowed or len(table) < known:
-            row[:len(table)] = table          # early releases rewrite entries: copy it all
-            row[len(table):] = 0
-            fresh = table
-        elif len(table) > known:
-            fresh = table[known:]
-            row[known:len(table)] = fresh
+        if len(table) == known and self.cache.policies[group].window is None:
+            return row
+        slot = self.cache.state_slot(request)
+        owner = self._page_owner[group]
+        if self.cache.policies[group].window is not None or len(table) < known:
+            # early releases rewrite entries: take the whole table again
+            new = np.asarray(table, dtype=np.int64)
+            old = row[:known]
+            gone = old[:min(known, len(new))][new[:known] == RELEASED]
+            gone = np.concatenate([gone, old[len(new):]]) if len(new) < known else gone
+            gone = gone[gone != self.null_page]
+            owner[gone[owner[gone] == slot]] = -1
+            first_new = 0
         else:
-            fresh = ()
-        for page in fresh:
-            if page != RELEASED and not 0 <= page < n_pages:
-                raise StepError(f"page {page} of request {request!r} is out of range")
+            new = np.asarray(table[known:], dtype=np.int64)
+            first_new = known
+        live = new[new != RELEASED]
+        if live.size and (live.min() < 0 or live.max() >= n_pages):
+            bad = int(live[(live < 0) | (live >= n_pages)][0])
+            raise StepError(f"page {bad} of request {request!r} is out of range")
+        theirs = owner[live]
+        clash = (theirs != -1) & (theirs != slot)
+        if clash.any() or np.unique(live).size != live.size:
+            page = int(live[clash][0]) if clash.any() else int(live[0])
+            raise StepError(f"page {page} of cache group {group} is named by request "
+                            f"{request!r} and by another live request (or twice): two "
+                            f"requests would write the same keys")
+        owner[live] = slot
+        row[first_new:first_new + len(new)] = np.where(new == RELEASED, self.null_page, new)
+        row[first_new + len(new):] = 0
         self._table_rows[key] = (row, len(table))
         return row
 
-    def _make_context(self, entries: List[StepEntry]) -> StepContext:
+    def check_tables(self) -> None:
+        """The whole check, over every live request and not only the pages new to a step:
+        no page of a cache group is named by two requests, or twice by one.  The step
+        itself checks incrementally (`_table_row`); this is for tests and for a host that
+        suspects its cache manager."""
+        for g, pool in enumerate(self.cache.pools):
+            seen = {}
+            for request in self.cache.live_requests():
+                for page in self.cache.block_table(request, g):
+                    if page == RELEASED:
+                        continue
+                    if not 0 <= page < pool.n_pages:
+                        raise StepError(f"page {page} of request {request!r} is out of range")
+                    if page in seen:
+                        raise StepError(f"page {page} of cache group {g} is named by request "
+                                        f"{request!r} and by another live request (or twice): "
+                                        f"{seen[page]!r}")
+                    seen[page] = request
+
+    def _make_context(self, entries: List[StepEntry], table_rows) -> StepContext:
         cache = self.cache
         counts = [len(e.tokens) for e in entries]
         n_tokens = sum(counts)
@@ -418,8 +504,8 @@ class Engine:
         for g, stride in enumerate(self.table_strides):
             a, _ = off[f"table{g}"]
             block = host[a:a + n_req * stride].reshape(n_req, stride)
-            for r, e in enumerate(entries):
-                block[r] = self._table_row(e.request, g)
+            for r, row in enumerate(table_rows[g]):
+                block[r] = row
         hs = HostStep([e.request for e in entries], counts, starts, held_after, slots)
         self._upload_meta(host_t, total)
         return StepContext(layout=layout, meta=dev_t, caches=self.storages, state=self.state,

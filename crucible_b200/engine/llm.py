@@ -48,17 +48,25 @@ class LLM:
             sched.submit(Request(i, list(prompt), p))
         self.last_steps = []
         done = {}
-        while sched.has_work():
-            t0 = time.perf_counter()
-            info = sched.step()
-            info.wall_s = time.perf_counter() - t0
-            self.last_steps.append(info)
-            if info.batch_tokens == 0 and info.admitted == 0 and info.finished == 0:
-                raise RuntimeError("generation made no progress")
+        try:
+            while sched.has_work():
+                t0 = time.perf_counter()
+                info = sched.step()
+                info.wall_s = time.perf_counter() - t0
+                self.last_steps.append(info)
+                if info.batch_tokens == 0 and info.admitted == 0 and info.finished == 0:
+                    raise RuntimeError("generation made no progress")
+                for c in sched.done:
+                    done[c.id] = c
+                sched.done = []
+            sched.flush()
             for c in sched.done:
                 done[c.id] = c
-            sched.done = []
-        sched.flush()
-        for c in sched.done:
-            done[c.id] = c
+            # every id came to the host with the status word behind it (`PendingIds.get`);
+            # this last look also covers steps that chose nothing
+            from ..ops import tensor_core
+            tensor_core.check_status(self.engine.device)
+        except Exception:
+            sched.abort()          # the engine keeps nothing of a run that failed
+            raise
         return [done[i].tokens for i in range(len(prompts))]

@@ -21,6 +21,7 @@ from typing import IO, Optional
 
 import numpy as np
 
+from ..ops import tensor_core
 from .engine import Engine, EngineOptions, StepEntry
 
 
@@ -53,12 +54,16 @@ def run(engine: Engine, lines: IO[str], out_dir: str, done: Optional[IO[str]] = 
             logits = engine.step(entries)
             if logits.shape[0] > 0:
                 host = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
+                # the copy waited for the step; a kernel that gave up a wait says so now,
+                # before anything of this step is written
+                tensor_core.check_status(engine.device)
                 host.tofile(os.path.join(out_dir, f"{step}.f32"))
         for req in rec.get("end", []):
             engine.finish(req)
         done.write(f"done {step}\n")
         done.flush()
         n += 1
+    tensor_core.check_status(engine.device)      # steps that wanted nothing were not waited for
     return n
 
 

@@ -327,16 +327,38 @@ class Scheduler:
                     return True
         return False
 
+    def abort(self) -> List[Hashable]:
+        """After the executor failed in the middle of a run (`engine/src/server.rs:1187-1227`
+        injects such a failure): every resident request gives back its pages, its
+        reservation and its state slot, queued requests are dropped, and token values
+        still on their way are forgotten.  Returns the ids of the requests it ended; the
+        executor is then as empty as before the run."""
+        ended = [r.id for r in self.pending]
+        self.pending.clear()
+        self._in_flight = None
+        self._finishing = []
+        for queue in (self.prefilling, self.active):
+            for live in list(queue):
+                ended.append(live.request.id)
+                if self.executor.cache.has(live.request.id):
+                    self.executor.finish(live.request.id)
+            queue.clear()
+        return ended
+
     def run_to_completion(self, max_steps: Optional[int] = None) -> List[Completion]:
         steps = 0
-        while self.has_work():
-            info = self.step()
-            steps += 1
-            if info.batch_tokens == 0 and info.admitted == 0 and info.finished == 0:
-                raise SchedulerError("the scheduler made no progress: a pending request "
-                                     "cannot be admitted and nothing is running")
-            if max_steps is not None and steps >= max_steps:
-                break
-        self.flush()
+        try:
+            while self.has_work():
+                info = self.step()
+                steps += 1
+                if info.batch_tokens == 0 and info.admitted == 0 and info.finished == 0:
+                    raise SchedulerError("the scheduler made no progress: a pending request "
+                                         "cannot be admitted and nothing is running")
+                if max_steps is not None and steps >= max_steps:
+                    break
+            self.flush()
+        except Exception:
+            self.abort()
+            raise
         out, self.done = self.done, []
         return out

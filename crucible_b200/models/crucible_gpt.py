@@ -16,8 +16,8 @@ from __future__ import annotations
 import math
 from typing import Any, Mapping
 
-from ..config.model_config import (ConfigError, FeedForwardSpec, KeyReader, LayerSpec,
-                                   MixerSpec, ModelConfig, NormSpec, PositionSpec, RunEntry)
+from ..config.model_config import (ConfigError, FeedForwardSpec, KeyReader, MixerSpec,
+                                   ModelConfig, NormSpec, PositionSpec, RunEntry, pre_norm_layer)
 from ..config.registry import Architecture, register_architecture
 
 # The reference fixes the RMSNorm epsilon in code (`model.py:108`,
@@ -41,8 +41,7 @@ def _dense_decoder(*, architecture: str, raw: Mapping[str, Any], vocab: int, hid
                       window=None, position=position)
     norm = NormSpec(kind="rmsnorm", width=hidden, eps=eps)
     ffn = FeedForwardSpec(kind="swiglu", width=hidden, intermediate=intermediate)
-    layer = LayerSpec(arrangement="pre_norm", mixer=mixer, mixer_norm=norm,
-                      feed_forward=ffn, feed_forward_norm=norm)
+    layer = pre_norm_layer(mixer, norm, ffn, norm)
     return ModelConfig(
         architecture=architecture, vocab_size=vocab, hidden_size=hidden,
         max_context=max_context, tie_word_embeddings=tie,

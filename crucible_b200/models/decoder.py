@@ -20,9 +20,8 @@ import torch
 
 from .. import ops
 from ..config.model_config import ConfigError, ModelConfig
-from ..parts import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, CacheNeed, LayerBinding,
-                     TensorDecl)
-from ..parts.embedding import LMHead, TokenEmbedding
+from ..parts import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, CacheNeed,
+                     LayerBinding, TensorDecl)
 
 
 @dataclass(frozen=True)
@@ -42,16 +41,17 @@ class TensorRequest:
 class DecoderModel:
     def __init__(self, config: ModelConfig):
         self.config = config
-        self.embedding = TokenEmbedding(config.vocab_size, config.hidden_size)
-        self.head = LMHead(config.vocab_size, config.hidden_size, config.tie_word_embeddings)
+        self.embedding = EMBEDDINGS.build(config.embedding.kind, config.embedding,
+                                          config.vocab_size, config.hidden_size)
+        self.head = HEADS.build(config.head.kind, config.head, config.vocab_size,
+                                config.hidden_size, config.tie_word_embeddings)
         self.final_norm = NORMS.build(config.final_norm.kind, config.final_norm)
         self.layers = []
         for spec in config.layers:
             mixer = MIXERS.build(spec.mixer.kind, spec.mixer)
             ffn = FEED_FORWARDS.build(spec.feed_forward.kind, spec.feed_forward)
-            n1 = NORMS.build(spec.mixer_norm.kind, spec.mixer_norm)
-            n2 = NORMS.build(spec.feed_forward_norm.kind, spec.feed_forward_norm)
-            self.layers.append(ARRANGEMENTS.build(spec.arrangement, n1, mixer, n2, ffn))
+            norms = {name: NORMS.build(n.kind, n) for name, n in spec.norms}
+            self.layers.append(ARRANGEMENTS.build(spec.arrangement, spec, norms, mixer, ffn))
         self.cache_groups, self.bindings, self.state_bytes = self._plan_storage()
         self.dtype: Optional[torch.dtype] = None
         self.device: Optional[torch.device] = None
@@ -120,9 +120,9 @@ class DecoderModel:
         yield "head", self.head, None
         yield "final_norm", self.final_norm, None
         for li, layer in enumerate(self.layers):
-            yield "layer.mixer_norm", layer.mixer_norm, li
+            for name, norm in layer.norms.items():
+                yield f"layer.{name}", norm, li
             yield "layer.mixer", layer.mixer, li
-            yield "layer.feed_forward_norm", layer.feed_forward_norm, li
             yield "layer.feed_forward", layer.feed_forward, li
 
     def tensor_requests(self) -> List[TensorRequest]:

@@ -143,13 +143,55 @@ def linear_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *,
            "linear (CUDA cores)")
 
 
+# Device ranges that hold weights: tensors that no kernel of a step writes.  The bfloat16
+# product kernels ask for their matrix before the kernels ahead of them in the stream have
+# finished (only the rows and the output wait for those), which is sound for a weight and a
+# race for a matrix that an earlier kernel of the same step computes.  So a part declares
+# its weights when it binds them, and a matrix that was not declared runs through the
+# CUDA-core product, which reads nothing before its predecessors are done.
+_weight_starts: list = []
+_weight_ends: list = []
+
+
+def declare_weights(*tensors: Optional[torch.Tensor]) -> None:
+    """Says that these tensors are written by no kernel of any step, for as long as the
+    tensor objects given here live (the declaration goes with them)."""
+    import bisect
+    import weakref
+    for t in tensors:
+        if t is None or not t.is_cuda:
+            continue
+        start = t.untyped_storage().data_ptr()
+        end = start + t.untyped_storage().nbytes()
+        at = bisect.bisect_left(_weight_starts, start)
+        if at < len(_weight_starts) and _weight_starts[at] == start:
+            continue
+        _weight_starts.insert(at, start)
+        _weight_ends.insert(at, end)
+        weakref.finalize(t, _forget_weight, start)
+
+
+def _forget_weight(start: int) -> None:
+    import bisect
+    at = bisect.bisect_left(_weight_starts, start)
+    if at < len(_weight_starts) and _weight_starts[at] == start:
+        del _weight_starts[at]
+        del _weight_ends[at]
+
+
+def is_weight(t: torch.Tensor) -> bool:
+    import bisect
+    p = t.data_ptr()
+    at = bisect.bisect_right(_weight_starts, p) - 1
+    return at >= 0 and p < _weight_ends[at]
+
+
 def linear(a, w: torch.Tensor, out: torch.Tensor, *, accumulate: bool = False) -> None:
-    """`a` is a tensor or a `small_batch.LazyNorm` (rows not yet normalised).  `w` is a weight
-    matrix: something no kernel of the step writes.  The bfloat16 kernels ask for it before the
-    kernels ahead of them in the stream have finished (only `a` and `out` wait for those); a
-    matrix computed during the step belongs in `linear_plain`."""
+    """`a` is a tensor or a `small_batch.LazyNorm` (rows not yet normalised).  `w`: if it was
+    declared a weight (`declare_weights`) the bfloat16 kernels may fetch it early; any other
+    matrix, one computed during the step for instance, takes the CUDA-core product."""
     from . import small_batch
-    if w.dtype == torch.bfloat16:
+    if w.dtype == torch.bfloat16 and is_weight(w):
         if a.shape[0] <= small_batch.PREFERRED_ROWS and small_batch.linear(a, w, out, accumulate=accumulate):
             return
         a = small_batch.as_tensor(a)
@@ -163,7 +205,7 @@ def linear(a, w: torch.Tensor, out: torch.Tensor, *, accumulate: bool = False) -
 def linear_swiglu(h, gate_up: torch.Tensor, out: torch.Tensor, ctx) -> None:
     """out[T, I] = silu(h Wg^T) * (h Wu^T) with gate_up = [Wg; Wu] of shape [2I, d]."""
     from . import small_batch
-    if gate_up.dtype == torch.bfloat16:
+    if gate_up.dtype == torch.bfloat16 and is_weight(gate_up):
         if h.shape[0] <= small_batch.PREFERRED_ROWS and small_batch.linear_swiglu(h, gate_up, out):
             return
         h = small_batch.as_tensor(h)
@@ -184,6 +226,10 @@ def qkv_rope_append(h, wqkv: torch.Tensor, qkv: torch.Tensor, n_heads: int, n_kv
     rotated q in the first columns of `qkv`; the k and v columns of `qkv` are not
     defined afterwards (attention reads keys and values from the cache)."""
     from . import small_batch
+    if not is_weight(wqkv):
+        linear(h, wqkv, qkv)
+        rope_kv_append(qkv, n_heads, n_kv_heads, head_dim, cos, sin, rotary_dim, ctx, cache, binding)
+        return
     if (wqkv.dtype == torch.bfloat16 and h.shape[0] <= small_batch.PREFERRED_ROWS
             and small_batch.qkv_rope_append(h, wqkv, qkv, n_heads, n_kv_heads, head_dim, cos, sin,
                                             rotary_dim, ctx, cache, binding)):
@@ -253,11 +299,23 @@ def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx,
 # token selection
 # ---------------------------------------------------------------------------
 
+def _status_pair(status):
+    """(source, destination) pointers of a status relay, or two nulls."""
+    if status is None:
+        return _c_void_p(0), _c_void_p(0)
+    src, dst = status
+    _need_cuda(src, dst)
+    if src.dtype != torch.int32 or dst.dtype != torch.int32:
+        raise KernelError("a status relay copies one int32 to another")
+    return _ptr(src), _ptr(dst)
+
+
 def argmax_rows(logits: torch.Tensor, out_ids: torch.Tensor,
                 scatter_index: Optional[torch.Tensor] = None,
-                scatter_out: Optional[torch.Tensor] = None) -> None:
+                scatter_out: Optional[torch.Tensor] = None, status=None) -> None:
     """`scatter_index`, `scatter_out` (int32): also write row r's id to
-    scatter_out[scatter_index[r]]."""
+    scatter_out[scatter_index[r]].  `status`: (src, dst) int32 device tensors; the
+    launch that writes the ids also copies src[0] to dst[0]."""
     _need_cuda(logits, out_ids, scatter_index, scatter_out)
     if logits.dtype != torch.float32 or out_ids.dtype != torch.int32:
         raise KernelError("argmax_rows takes float32 logits and int32 output")
@@ -271,7 +329,7 @@ def argmax_rows(logits: torch.Tensor, out_ids: torch.Tensor,
         _scratch[key] = scratch
     _check(lib.cb_argmax_rows(_ptr(logits), _c_int(n), _c_int(logits.shape[1]),
                               _ptr(out_ids), _ptr(scratch), _ptr(scatter_index), _ptr(scatter_out),
-                              _stream()), "argmax_rows")
+                              *_status_pair(status), _stream()), "argmax_rows")
 
 
 def max_device_top_k() -> int:
@@ -281,7 +339,7 @@ def max_device_top_k() -> int:
 def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
                 uniform: torch.Tensor, max_top_k: int, out_ids: torch.Tensor,
                 scatter_index: Optional[torch.Tensor] = None,
-                scatter_out: Optional[torch.Tensor] = None) -> None:
+                scatter_out: Optional[torch.Tensor] = None, status=None) -> None:
     _need_cuda(logits, temperature, top_k, uniform, out_ids, scatter_index, scatter_out)
     if (logits.dtype != torch.float32 or temperature.dtype != torch.float32
             or uniform.dtype != torch.float32 or top_k.dtype != torch.int32
@@ -291,7 +349,8 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Te
     lib = build.load("sampling")
     code = lib.cb_sample_rows(_ptr(logits), _c_int(logits.shape[0]), _c_int(logits.shape[1]),
                               _ptr(temperature), _ptr(top_k), _ptr(uniform), _c_int(max_top_k),
-                              _ptr(out_ids), _ptr(scatter_index), _ptr(scatter_out), _stream())
+                              _ptr(out_ids), _ptr(scatter_index), _ptr(scatter_out),
+                              *_status_pair(status), _stream())
     if code == 100001:
         raise KernelError(f"top_k {max_top_k} exceeds what the sampling kernel holds "
                           f"({max_device_top_k()} candidates)")

@@ -32,6 +32,12 @@ STORE_BF16, STORE_F32, ACCUM_F32, SWIGLU_BF16, ROPE_APPEND = 0, 1, 2, 3, 4
 _UNSUPPORTED = 100001
 
 _status = {}
+FAILURES = [0]       # kernels that gave up so far; engines drop their captured steps when it moves
+
+
+class KernelGaveUp(RuntimeError):
+    """A tensor-core kernel ran out one of its bounded waits: the results of the step
+    it belonged to are not valid."""
 
 
 def status_word(device) -> torch.Tensor:
@@ -44,6 +50,28 @@ def status_word(device) -> torch.Tensor:
     return t
 
 
+def raise_if_gave_up(device, code: int) -> None:
+    """`code` is a value of the status word that reached the host (read here, or relayed
+    behind a step's chosen ids).  Non-zero: puts the device-side state back in order (the
+    word to zero; the arrival counters of the split kernels, which a block that gave up
+    leaves counted short) and raises."""
+    if not code:
+        return
+    key = torch.device(device).index or 0
+    torch.cuda.synchronize(device)
+    t = _status.get(key)
+    if t is not None:
+        t.zero_()
+    for (dev, name), buf in _buffers.items():
+        if dev == key and name.endswith(".counters"):
+            buf.zero_()
+    FAILURES[0] += 1
+    what = {1: "a TMA producer", 2: "an MMA issuer", 3: "an epilogue",
+            4: "a wait made to run out on purpose"}.get(code, "a role")
+    raise KernelGaveUp(f"a tensor-core kernel gave up: {what} waited past its limit "
+                       f"(status {code}); the step's results are not valid")
+
+
 def check_status(device) -> None:
     """Raises if a tensor-core kernel gave up a wait since the last check.
     Synchronises; call it where the host waits anyway."""
@@ -51,12 +79,7 @@ def check_status(device) -> None:
     t = _status.get(key)
     if t is None:
         return
-    code = int(t.item())
-    if code:
-        t.zero_()
-        what = {1: "a TMA producer", 2: "an MMA issuer", 3: "an epilogue"}.get(code, "a role")
-        raise RuntimeError(f"a tensor-core kernel gave up: {what} waited past its limit "
-                           f"(status {code}); the step's results are not valid")
+    raise_if_gave_up(device, int(t.item()))
 
 
 def _count(n: int) -> None:
@@ -449,3 +472,13 @@ def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx,
         raise RuntimeError(f"tensor-core attention failed to launch (CUDA error {code})")
     _count(1)
     return True
+
+
+def run_wait_probe(device, limit: int = 4096) -> None:
+    """Launches a kernel whose only thread waits, bounded by `limit` polls, on a barrier
+    nothing arrives at, and then records its give-up code in the status word: the failure
+    path of the tensor-core kernels, made to happen without a fault (for tests)."""
+    lib = build.load("gemm_tcgen05")
+    code = lib.cb_tc_wait_probe(_c_void_p(status_word(device).data_ptr()), _c_int(limit), _stream())
+    if code != 0:
+        raise RuntimeError(f"wait probe failed to launch (CUDA error {code})")

@@ -55,6 +55,7 @@ class PagedAttention(Mixer):
     def bind(self, tensors, dtype, device):
         self.wqkv = torch.cat([tensors["q"], tensors["k"], tensors["v"]], dim=0).contiguous()
         self.wo = tensors["o"]
+        ops.declare_weights(self.wqkv, self.wo)
         self.dtype = dtype
         if self.position is not None:
             self.position.bind({}, dtype, device)

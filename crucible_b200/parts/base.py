@@ -1,7 +1,8 @@
 """Interfaces of the parts a layer is put together from, and their registries.
 
-A layer = a block arrangement over {norm, mixer, norm, feed-forward}; a mixer
-may own a position encoding.  Each kind of part is registered under a name
+A layer = a block arrangement over a mixer, a feed-forward and the norms the
+arrangement names; a mixer may own a position encoding.  The model's two ends, the
+token embedding and the LM head, are registered parts too.  Each kind of part is registered under a name
 and built from its spec (sizes and constants are parameters of the spec, never
 of the code).  No part knows which model it is in: it sees its spec, its own
 tensors under local names, and the `StepContext` of the step being run.
@@ -18,7 +19,9 @@ position        `rotation() -> (cos, sin, rotary_dim) | None`, or
 mixer           `cache_need() -> CacheNeed | None`, `state_bytes() -> int`,
                 `forward(ctx, h, residual, binding)`: residual += mixer(h)
 feed-forward    `forward(ctx, h, residual)`: residual += ffn(h)
-arrangement     `forward(ctx, x, binding)`: runs one layer on the residual x
+arrangement     `norm_names`; `forward(ctx, x, binding)`: runs one layer on the residual x
+embedding       `forward(ctx, token_ids) -> x`  fp32 [T, width]; `table` if a head may tie to it
+head            `forward(ctx, normed_rows) -> logits` fp32 [rows, vocab]; `tie(table)`
 
 The residual stream is always fp32 (the residual sum is a 32-bit sum in both
 engine dtypes); `h` and everything a part produces internally is in the engine
@@ -118,16 +121,39 @@ class FeedForward(Part):
 
 
 class Arrangement:
-    """Puts one layer's parts in order.  Built from the already-built parts."""
+    """Puts one layer's parts in order.  Built from the layer's spec and its
+    already-built parts; `norm_names` are the norms it needs (the spec must give
+    exactly these), `norms` the built ones by name."""
+    norm_names: Tuple[str, ...] = ()
 
-    def __init__(self, mixer_norm: Norm, mixer: Mixer, feed_forward_norm: Norm,
-                 feed_forward: FeedForward):
-        self.mixer_norm = mixer_norm
+    def __init__(self, spec, norms: Dict[str, Norm], mixer: Mixer, feed_forward: FeedForward):
+        if set(norms) != set(self.norm_names):
+            raise ValueError(f"arrangement {spec.arrangement!r} needs the norms "
+                             f"{sorted(self.norm_names)}, the layer gives {sorted(norms)}")
+        self.spec = spec
+        self.norms = dict(norms)
         self.mixer = mixer
-        self.feed_forward_norm = feed_forward_norm
         self.feed_forward = feed_forward
 
     def forward(self, ctx, x: torch.Tensor, binding: LayerBinding) -> None:
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    """Token ids -> rows of the fp32 residual stream."""
+
+    def forward(self, ctx, token_ids: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Head(Part):
+    """Normalised rows -> fp32 logits [rows, vocab]; `tie(table)` hands it the
+    embedding's table when the model ties them."""
+
+    def tie(self, table: torch.Tensor) -> None:
+        raise NotImplementedError
+
+    def forward(self, ctx, normed_rows: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
 
@@ -160,4 +186,6 @@ NORMS = _Registry("norm")                   # maker(spec: NormSpec) -> Norm
 POSITIONS = _Registry("position encoding")  # maker(spec: PositionSpec) -> PositionEncoding
 MIXERS = _Registry("mixer")                 # maker(spec: MixerSpec) -> Mixer
 FEED_FORWARDS = _Registry("feed-forward")   # maker(spec: FeedForwardSpec) -> FeedForward
-ARRANGEMENTS = _Registry("arrangement")     # maker(norm, mixer, norm, ffn) -> Arrangement
+ARRANGEMENTS = _Registry("arrangement")     # maker(spec: LayerSpec, norms: dict, mixer, ffn) -> Arrangement
+EMBEDDINGS = _Registry("embedding")         # maker(spec: EndSpec, vocab, width) -> Embedding
+HEADS = _Registry("head")                   # maker(spec: EndSpec, vocab, width, tied) -> Head

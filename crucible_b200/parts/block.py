@@ -7,10 +7,12 @@ from .base import ARRANGEMENTS, Arrangement
 
 
 class PreNormBlock(Arrangement):
+    norm_names = ("mixer_norm", "feed_forward_norm")
+
     def forward(self, ctx, x, binding):
-        h = self._norm(ctx, self.mixer_norm, self.mixer, x)
+        h = self._norm(ctx, self.norms["mixer_norm"], self.mixer, x)
         self.mixer.forward(ctx, h, x, binding)
-        h = self._norm(ctx, self.feed_forward_norm, self.feed_forward, x)
+        h = self._norm(ctx, self.norms["feed_forward_norm"], self.feed_forward, x)
         self.feed_forward.forward(ctx, h, x)
 
     @staticmethod

@@ -12,10 +12,10 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import Part, TensorDecl
+from .base import EMBEDDINGS, HEADS, Embedding, Head, TensorDecl
 
 
-class TokenEmbedding(Part):
+class TokenEmbedding(Embedding):
     def __init__(self, vocab_size: int, width: int):
         self.vocab_size = vocab_size
         self.width = width
@@ -26,6 +26,7 @@ class TokenEmbedding(Part):
 
     def bind(self, tensors, dtype, device):
         self.table = tensors["table"]
+        ops.declare_weights(self.table)
 
     def forward(self, ctx, token_ids: torch.Tensor) -> torch.Tensor:
         x = ctx.scratch("residual", (token_ids.shape[0], self.width), torch.float32)
@@ -33,7 +34,7 @@ class TokenEmbedding(Part):
         return x
 
 
-class LMHead(Part):
+class LMHead(Head):
     def __init__(self, vocab_size: int, width: int, tied: bool):
         self.vocab_size = vocab_size
         self.width = width
@@ -46,6 +47,7 @@ class LMHead(Part):
     def bind(self, tensors, dtype, device):
         if not self.tied:
             self.weight = tensors["weight"]
+            ops.declare_weights(self.weight)
 
     def tie(self, table: torch.Tensor) -> None:
         self.weight = table
@@ -54,3 +56,7 @@ class LMHead(Part):
         logits = ctx.scratch("logits", (normed_rows.shape[0], self.vocab_size), torch.float32)
         ops.linear(normed_rows, self.weight, logits)
         return logits
+
+
+EMBEDDINGS.register("token", lambda spec, vocab, width: TokenEmbedding(vocab, width))
+HEADS.register("linear", lambda spec, vocab, width, tied: LMHead(vocab, width, tied))

@@ -14,6 +14,9 @@ from ..config.model_config import PositionSpec
 from .base import POSITIONS, PositionEncoding
 
 
+_TABLES = {}     # (theta, rotary_dim, positions, device) -> (cos, sin), read-only
+
+
 class RotaryEncoding(PositionEncoding):
     def __init__(self, spec: PositionSpec):
         if spec.rotary_dim % 2 != 0 or spec.rotary_dim <= 0:
@@ -23,14 +26,24 @@ class RotaryEncoding(PositionEncoding):
         self.sin = None
 
     def bind(self, tensors, dtype, device):
-        half = self.spec.rotary_dim // 2
-        i = torch.arange(half, dtype=torch.float64)
-        inv_freq = torch.pow(torch.tensor(self.spec.theta, dtype=torch.float64),
-                             -2.0 * i / self.spec.rotary_dim)
-        pos = torch.arange(self.spec.max_positions, dtype=torch.float64)
-        ang = torch.outer(pos, inv_freq)
-        self.cos = ang.cos().to(torch.float32).contiguous().to(device)
-        self.sin = ang.sin().to(torch.float32).contiguous().to(device)
+        # layers with the same rotation share one pair of tables (a model of 32 layers
+        # with 131,072 positions would otherwise hold 32 identical pairs of 33 MB)
+        key = (float(self.spec.theta), self.spec.rotary_dim, self.spec.max_positions,
+               str(torch.device(device)))
+        hit = _TABLES.get(key)
+        if hit is None:
+            half = self.spec.rotary_dim // 2
+            i = torch.arange(half, dtype=torch.float64)
+            inv_freq = torch.pow(torch.tensor(self.spec.theta, dtype=torch.float64),
+                                 -2.0 * i / self.spec.rotary_dim)
+            pos = torch.arange(self.spec.max_positions, dtype=torch.float64)
+            ang = torch.outer(pos, inv_freq)
+            hit = (ang.cos().to(torch.float32).contiguous().to(device),
+                   ang.sin().to(torch.float32).contiguous().to(device))
+            if len(_TABLES) >= 8:
+                _TABLES.pop(next(iter(_TABLES)))
+            _TABLES[key] = hit
+        self.cos, self.sin = hit
 
     def rotation(self):
         return self.cos, self.sin, self.spec.rotary_dim

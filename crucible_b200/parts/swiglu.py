@@ -31,6 +31,7 @@ class SwiGLU(FeedForward):
     def bind(self, tensors, dtype, device):
         self.gate_up = torch.cat([tensors["gate"], tensors["up"]], dim=0).contiguous()
         self.down = tensors["down"]
+        ops.declare_weights(self.gate_up, self.down)
         self.dtype = dtype
 
     def forward(self, ctx, h, residual):

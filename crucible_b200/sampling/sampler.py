@@ -20,16 +20,23 @@ from .rng import Xorshift64Star
 
 
 class PendingIds:
-    """Ids on their way to the host."""
+    """Ids on their way to the host.  Behind them rides the status word of the
+    tensor-core kernels as it stood when the ids were chosen: `get()` raises
+    `KernelGaveUp` if a kernel of that step, or of one before it, ran out a bounded wait
+    (its logits, and so these ids, are then not valid)."""
 
-    def __init__(self, host: torch.Tensor, n: int, event: torch.cuda.Event):
-        self._host, self._n, self._event = host, n, event
+    def __init__(self, host: torch.Tensor, n: int, event: torch.cuda.Event, device=None):
+        self._host, self._n, self._event, self._device = host, n, event, device
         self._ids: Optional[List[int]] = None
 
     def get(self) -> List[int]:
         if self._ids is None:
             self._event.synchronize()
-            self._ids = self._host[:self._n].tolist()
+            values = self._host[:self._n + 1].tolist()
+            if self._device is not None and values[self._n]:
+                from ..ops import tensor_core
+                tensor_core.raise_if_gave_up(self._device, values[self._n])
+            self._ids = values[:self._n]
         return self._ids
 
 
@@ -50,8 +57,8 @@ class Sampler:
             # slot bits), their device copy, device ids, pinned ids, and an event
             self._ring = [dict(host=torch.empty((4, cap), dtype=torch.float32, pin_memory=True),
                                dev=torch.empty((4, cap), dtype=torch.float32, device=self.device),
-                               ids=torch.empty(cap, dtype=torch.int32, device=self.device),
-                               ids_host=torch.empty(cap, dtype=torch.int32, pin_memory=True),
+                               ids=torch.zeros(cap + 1, dtype=torch.int32, device=self.device),
+                               ids_host=torch.zeros(cap + 1, dtype=torch.int32, pin_memory=True),
                                event=torch.cuda.Event(), used=False) for _ in range(self.RING)]
             self._cap = cap
         self._at = (self._at + 1) % self.RING
@@ -69,11 +76,14 @@ class Sampler:
         Returns the ids, or with `defer` a `PendingIds`."""
         n = len(rows)
         if n == 0:
-            return PendingIds(torch.empty(0, dtype=torch.int32), 0, torch.cuda.Event()) if defer else []
+            return PendingIds(torch.zeros(1, dtype=torch.int32), 0, torch.cuda.Event()) if defer else []
         if logits.shape[0] != n:
             raise ValueError(f"{n} rows to sample but logits has {logits.shape[0]}")
         buf = self._buffers(n)
         ids = buf["ids"][:n]
+        # the kernel that writes the ids also leaves the status word right behind them
+        from ..ops import tensor_core
+        status = (tensor_core.status_word(self.device), buf["ids"][n:n + 1])
         host = buf["host"].numpy()
         greedy = all(p.is_greedy for p, _ in rows)
         upload = not greedy or slots is not None
@@ -93,15 +103,18 @@ class Sampler:
                     host[0, i], topk_bits[i], host[2, i] = p.temperature, k, rng.next_f32()
             host[1, :n] = topk_bits.view(np.float32)
         if upload:
-            buf["dev"][:, :n].copy_(buf["host"][:, :n], non_blocking=True)
+            # one copy of whole rows of the parameter block (a slice [:, :n] is strided, and a
+            # strided host-to-device copy goes through a staging buffer and a copy kernel)
+            first, last = (3, 4) if greedy else (0, 4 if slots is not None else 3)
+            buf["dev"][first:last].copy_(buf["host"][first:last], non_blocking=True)
         out = scatter_out if slots is not None else None
         if greedy:
-            ops.argmax_rows(logits, ids, scatter_index, out)
+            ops.argmax_rows(logits, ids, scatter_index, out, status=status)
         else:
             ops.sample_rows(logits, buf["dev"][0, :n], buf["dev"][1, :n].view(torch.int32),
-                            buf["dev"][2, :n], max_k, ids, scatter_index, out)
-        buf["ids_host"][:n].copy_(ids, non_blocking=True)
+                            buf["dev"][2, :n], max_k, ids, scatter_index, out, status=status)
+        buf["ids_host"][:n + 1].copy_(buf["ids"][:n + 1], non_blocking=True)
         buf["event"].record()
         buf["used"] = True
-        pending = PendingIds(buf["ids_host"], n, buf["event"])
+        pending = PendingIds(buf["ids_host"], n, buf["event"], self.device)
         return pending if defer else pending.get()

@@ -116,5 +116,4 @@ def replay_in_process(model_dir: str, dtype: str, trace: Trace, out_dir: str, ma
     replay.run(engine, io.StringIO(trace.text()), out_dir, done)
     assert done.getvalue().split() == [x for i in range(len(trace.steps)) for x in ("done", str(i))]
     engine.cache.check_invariants()
-    assert not engine.cache.live_requests() or True
     return engine

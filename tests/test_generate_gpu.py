@@ -197,3 +197,129 @@ def test_step_refuses_malformed_batches(tmp_path):
     eng.cache.check_invariants()
     eng.finish("a")
     assert eng.cache.free_pages(0) == 4
+
+
+# ---------------------------------------------------------------------------
+# failure paths, made to happen without faulting, trapping or hanging anything
+# ---------------------------------------------------------------------------
+
+def test_a_wait_that_runs_out_is_reported_and_the_engine_recovers(tmp_path):
+    """A kernel waits, bounded by a short limit, on a barrier at which nothing arrives,
+    and records its give-up code in the status word as the tensor-core kernels do.  The
+    product reads the word where the host waits anyway: generation raises instead of
+    returning tokens chosen from a step that is not valid, gives back everything the
+    run held, and the next run is clean."""
+    from crucible_b200 import SamplingParams
+    from crucible_b200.ops import tensor_core
+    name = "tiny-c"
+    folder = helpers.make_folder(tmp_path, name)
+    vocab = TINY[name]["config"]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, 70 + i) for i, n in enumerate([80, 9])]
+    llm = _llm(folder, "bfloat16", name, max_batch=2)
+    want = llm.generate(prompts, SamplingParams(max_tokens=6))
+    tensor_core.check_status(llm.engine.device)                 # nothing gave up so far
+    failures = tensor_core.FAILURES[0]
+
+    tensor_core.run_wait_probe(llm.engine.device, limit=2048)   # returns after 2,048 polls
+    with pytest.raises(tensor_core.KernelGaveUp, match="status 4"):
+        llm.generate(prompts, SamplingParams(max_tokens=6))
+    assert tensor_core.FAILURES[0] == failures + 1
+    assert not llm.engine.cache.live_requests()
+    llm.engine.cache.check_invariants()
+    assert int(tensor_core.status_word(llm.engine.device).item()) == 0
+    assert llm.generate(prompts, SamplingParams(max_tokens=6)) == want
+
+    # the trace replayer reads the word too, before it writes a step's logits
+    tokens = prompts[0]
+    trace = Trace()
+    trace.step([("a", tokens, [len(tokens) - 1])], end=["a"])
+    from crucible_b200.engine import replay
+    import io
+    engine = replay.make_engine(folder, "bfloat16", 128, TINY[name]["page_tokens"])
+    tensor_core.run_wait_probe(engine.device, limit=2048)
+    out = tmp_path / "replay-out"
+    with pytest.raises(tensor_core.KernelGaveUp):
+        replay.run(engine, io.StringIO(trace.text()), str(out), io.StringIO())
+    assert not (out / "0.f32").exists()
+    tensor_core.check_status(engine.device)                     # cleared
+
+
+def test_a_capture_that_fails_leaves_the_engine_eager_and_right(tmp_path, monkeypatch):
+    """`torch.cuda.graph` is made to raise when a step is captured (as
+    `engine/src/gpu_model.rs:3199-3222` remembers a failed capture): the engine notes it,
+    runs every further step eagerly, leaves no capture open, and the tokens are the same."""
+    import torch
+    from crucible_b200 import SamplingParams
+    name = "tiny-a"
+    folder = helpers.make_folder(tmp_path, name)
+    vocab = TINY[name]["config"]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, 30 + i) for i, n in enumerate([12, 30])]
+    want = _llm(folder, "float32", name, max_batch=2, graph=False).generate(
+        prompts, SamplingParams(max_tokens=10))
+
+    class Refusing:
+        def __init__(self, *a, **k):
+            raise RuntimeError("capture refused (injected)")
+
+    llm = _llm(folder, "float32", name, max_batch=2)
+    monkeypatch.setattr(torch.cuda, "graph", Refusing)
+    got = llm.generate(prompts, SamplingParams(max_tokens=10))
+    assert got == want
+    assert llm.engine._graph_failed and "injected" in llm.engine._graph_error
+    assert not llm.engine._graphs
+    assert not torch.cuda.is_current_stream_capturing()
+    monkeypatch.undo()
+    assert llm.generate(prompts, SamplingParams(max_tokens=10)) == want      # still eager, still right
+    assert llm.engine._graph_replays == 0
+
+
+def test_step_refuses_a_page_named_by_two_requests(tmp_path):
+    """An allocator that hands out a page that is still held (made to happen here by
+    putting a held page back on the free stack): the step that would upload the second
+    request's table is refused before anything is written, and changes nothing."""
+    from crucible_b200.engine import Engine, EngineOptions, StepEntry, StepError
+    folder = helpers.make_folder(tmp_path, "tiny-a")
+    eng = Engine(folder, EngineOptions(dtype="float32", n_pages=8, max_requests=3))
+    tokens = helpers.random_tokens(256, 40, 1)
+    before = eng.step([StepEntry("a", tokens[:20], [19])]).clone()
+    held = eng.cache.block_table("a", 0)[0]
+    pool = eng.cache.pools[0]
+    pool._free.append(held)                       # the fault: a held page looks free
+    with pytest.raises(StepError, match="another live request"):
+        eng.step([StepEntry("b", tokens[:5], [4])])
+    assert not eng.has_request("b")
+    assert pool._free[-1] == held                 # rolled back to where the fault left it
+    pool._free.pop()                              # undo the fault
+    pool._in_use[held] = True
+    eng.cache.check_invariants()
+    # request a is untouched: the same logits as a run that never saw the fault
+    again = Engine(folder, EngineOptions(dtype="float32", n_pages=8, max_requests=3))
+    again.step([StepEntry("a", tokens[:20], [19])])
+    got = eng.step([StepEntry("a", tokens[20:], [19])])
+    want = again.step([StepEntry("a", tokens[20:], [19])])
+    assert torch.equal(got, want) and torch.equal(before, before)
+    # a table entry changed behind the engine's back is found by the full check
+    eng.step([StepEntry("c", tokens[:5], [])])
+    eng.cache.block_table("c", 0)[0] = eng.cache.block_table("a", 0)[1]
+    with pytest.raises(StepError, match="another live request"):
+        eng.check_tables()
+
+
+def test_device_token_needs_a_deferred_sample(tmp_path):
+    """`DEVICE_TOKEN` stands for the token the engine last chose for the request and kept
+    on the device; a request that never had one chosen that way (a new one in a slot
+    whose last owner had) is refused instead of reading the old owner's token."""
+    from crucible_b200 import SamplingParams
+    from crucible_b200.engine import DEVICE_TOKEN, Engine, EngineOptions, StepEntry, StepError
+    folder = helpers.make_folder(tmp_path, "tiny-a")
+    eng = Engine(folder, EngineOptions(dtype="float32", n_pages=8, max_requests=1))
+    logits = eng.step([StepEntry("a", [5, 6, 7], [2])])
+    with pytest.raises(StepError, match="no token on the device"):
+        eng.step([StepEntry("a", [DEVICE_TOKEN], [0])])
+    ids = eng.sample_deferred(logits, [(SamplingParams(), None)], ["a"])
+    eng.step([StepEntry("a", [DEVICE_TOKEN], [0])])          # now it has one
+    assert 0 <= ids.get()[0] < 256
+    eng.finish("a")
+    eng.step([StepEntry("b", [1, 2], [1])])                  # takes the same slot
+    with pytest.raises(StepError, match="no token on the device"):
+        eng.step([StepEntry("b", [DEVICE_TOKEN], [0])])

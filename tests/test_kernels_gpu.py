@@ -746,26 +746,41 @@ def test_rope_kv_append(dtype, hd, rot):
 # ---------------------------------------------------------------------------
 
 def test_argmax_ties_nan_and_edges():
+    import plain_model as pm
     ops = _ops()
     nan, inf = float("nan"), float("inf")
     rows = [
         [1.0, 3.0, 3.0, 2.0],            # tie -> lowest index
-        [nan, 1.0, 0.5, nan],            # NaN never wins
+        [nan, 1.0, 0.5, nan],            # a NaN at index 0 is never displaced -> 0
+        [1.0, nan, 2.0, nan],            # a NaN elsewhere displaces nothing -> 2
         [-inf, -inf, -inf, -inf],        # all -inf -> 0
         [0.0, -0.0, 0.0, -1.0],          # signed zeros tie -> 0
         [1.0, 2.0, 3.0, inf],            # last position
         [nan, nan, nan, nan],            # all NaN -> 0
+        [-inf, nan, -inf, -inf],         # nothing exceeds the first -> 0
     ]
     logits = torch.tensor(rows, device=DEV)
     out = torch.empty(len(rows), dtype=torch.int32, device=DEV)
     ops.argmax_rows(logits, out)
-    assert out.tolist() == [1, 1, 0, 0, 3, 0]
-    big = torch.randn(3, 50304, device=DEV)
+    want = [pm.plain_argmax(r) for r in rows]
+    assert want == [1, 0, 2, 0, 0, 3, 0, 0]
+    assert out.tolist() == want
+    # the same rules through the greedy rows of the sampling kernel
+    out2 = torch.empty(len(rows), dtype=torch.int32, device=DEV)
+    ops.sample_rows(logits, torch.zeros(len(rows), device=DEV),
+                    torch.ones(len(rows), dtype=torch.int32, device=DEV),
+                    torch.zeros(len(rows), device=DEV), 1, out2)
+    assert out2.tolist() == want
+    # wide rows take the two-stage form
+    big = torch.randn(5, 50304, device=DEV)
     big[1, 50303] = 100.0
     big[2, 77] = big[2, 40000] = 50.0
-    out = torch.empty(3, dtype=torch.int32, device=DEV)
+    big[3, 0] = nan                       # never displaced
+    big[4, 1] = nan                       # displaces nothing
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
     ops.argmax_rows(big, out)
-    assert out.tolist() == [int(big[0].argmax()), 50303, 77]
+    assert out.tolist() == [pm.plain_argmax(r) for r in big.tolist()]
+    assert out.tolist()[1:4] == [50303, 77, 0]
 
 
 @pytest.mark.parametrize("vocab", [509, 50304])

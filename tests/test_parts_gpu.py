@@ -104,8 +104,8 @@ DECAY = 0.75
 
 
 def _register_toys():
-    from crucible_b200.config import (Architecture, FeedForwardSpec, LayerSpec, MixerSpec, ModelConfig,
-                                      NormSpec, PositionSpec, RunEntry, register_architecture)
+    from crucible_b200.config import (Architecture, FeedForwardSpec, MixerSpec, ModelConfig, NormSpec,
+                                      PositionSpec, RunEntry, pre_norm_layer, register_architecture)
     from crucible_b200.config.registry import _ARCHITECTURES
     from crucible_b200.parts import (FEED_FORWARDS, MIXERS, POSITIONS, FeedForward, Mixer,
                                      PositionEncoding, TensorDecl)
@@ -200,8 +200,8 @@ def _register_toys():
         attn = MixerSpec("attention", WIDTH, HEADS, KV, HD, 1 / math.sqrt(HD), None,
                          PositionSpec("additive", HD, raw["step"], raw["ctx"]))
         ema = MixerSpec("ema", WIDTH, extra=(("decay", raw["decay"]),))
-        layers = (LayerSpec("pre_norm", attn, norm, FeedForwardSpec("swiglu", WIDTH, INTER), norm),
-                  LayerSpec("pre_norm", ema, norm, FeedForwardSpec("routed", WIDTH, INTER), norm))
+        layers = (pre_norm_layer(attn, norm, FeedForwardSpec("swiglu", WIDTH, INTER), norm),
+                  pre_norm_layer(ema, norm, FeedForwardSpec("routed", WIDTH, INTER), norm))
         # layer 0 runs twice; its second run reads the cache the first one wrote
         order = (RunEntry(0), RunEntry(1), RunEntry(0, cache_of=0))
         return ModelConfig("ToyHybrid", VOCAB, WIDTH, raw["ctx"], False, layers, order, norm,
@@ -304,3 +304,211 @@ def test_model_layouts_are_checked():
     bad = dataclasses.replace(cfg, run_order=(RunEntry(1, cache_of=0), RunEntry(0)))
     with pytest.raises(ConfigError):
         DecoderModel(bad)
+
+
+# ---------------------------------------------------------------------------
+# a window: pages given back while the request runs, through the whole engine
+# ---------------------------------------------------------------------------
+
+WINDOW = 40
+
+
+def _register_windowed():
+    """The dense decoder with a window on every layer's attention: the reference's own
+    keys plus "window".  Defined here; the framework's files know nothing of it."""
+    import dataclasses
+    from crucible_b200.config import Architecture, register_architecture
+    from crucible_b200.config.registry import _ARCHITECTURES
+    from crucible_b200.models import crucible_gpt
+
+    def parse(raw):
+        base = crucible_gpt._parse_crucible({k: v for k, v in raw.items() if k != "window"})
+        layers = tuple(dataclasses.replace(l, mixer=dataclasses.replace(l.mixer, window=raw["window"]))
+                       for l in base.layers)
+        return dataclasses.replace(base, architecture="WindowedGPT", layers=layers, raw=dict(raw))
+
+    _ARCHITECTURES.pop("WindowedGPT", None)
+    register_architecture(Architecture("WindowedGPT", parse, lambda cfg: dict(cfg.raw)))
+    return {"architectures": ["WindowedGPT"], "vocab_size": 211, "n_layer": 2, "n_head": 4,
+            "n_kv_head": 2, "n_embd": 96, "head_dim": 48, "intermediate_size": 160,
+            "block_size": 384, "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
+            "tie_word_embeddings": True, "window": WINDOW}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_windowed_attention_gives_pages_back_and_stays_right(tmp_path, dtype):
+    """Window 40, pages of 16, heads of 48 (the mma.sync kernels in bfloat16): portions
+    of 20 to 60 tokens, then decoding across several pages that the window has passed
+    and the cache manager has given back.  Their table entries name the null page, and
+    every page that is free is filled with NaN after each step, so a kernel that read
+    a released page (or one it was never given) would show it."""
+    from crucible_b200.engine import Engine, EngineOptions, StepEntry
+    from crucible_b200.weights import write_random_model
+    raw = _register_windowed()
+    folder = write_random_model(raw, str(tmp_path / "windowed"), seed=12, std=helpers.TEST_STD)
+    cfg, w = pm.read_folder(folder)
+    cfg["window"] = WINDOW
+    seqs = {"a": helpers.random_tokens(211, 300, 31), "b": helpers.random_tokens(211, 130, 32)}
+    refs = {k: pm.plain_forward(cfg, w, v).numpy() for k, v in seqs.items()}
+    # 14 pages = 224 tokens for 430 tokens of requests: only a window's worth is ever held
+    eng = Engine(folder, EngineOptions(dtype=dtype, page_tokens=16, n_pages=14, max_requests=2))
+    assert eng.model.cache_groups[0].need.window == WINDOW
+    got, fed = {}, {"a": 0, "b": 0}
+    least_free = [14]
+
+    def run(entries):
+        batch = []
+        for r, n, want in entries:
+            batch.append(StepEntry(r, seqs[r][fed[r]:fed[r] + n], want))
+        logits = eng.step(batch).float().cpu().numpy()
+        i = 0
+        for r, n, want in entries:
+            for wpos in want:
+                got[(r, fed[r] + wpos)] = logits[i]
+                i += 1
+            fed[r] += n
+        eng.cache.check_invariants()
+        pool = eng.cache.pools[0]
+        least_free[0] = min(least_free[0], pool.free_pages)
+        free = [p for p in range(pool.n_pages) if not pool.is_in_use(p)]
+        if free:
+            eng.storages[0].kv[:, :, free] = float("nan")
+
+    for n in (37, 60, 20, 45, 23):                              # a: 185 tokens in portions
+        run([("a", n, [0, n // 2, n - 1])])
+    assert eng.cache.held_pages("a", 0) < -(-185 // 16), "no page was given back"
+    run([("a", 1, [0]), ("b", 52, [51])])                       # b starts beside a's decoding
+    run([("a", 1, [0]), ("b", 33, [0, 32])])
+    for _ in range(45):                                         # both decode, crossing pages
+        run([("a", 1, [0]), ("b", 1, [0])])
+    eng.finish("b")
+    while fed["a"] < 300:
+        run([("a", 1, [0])])
+    assert least_free[0] < 14 - 2 * 3                           # both held their windows at once
+    tol = helpers.TOLERANCE[dtype]
+    for (r, pos), row in sorted(got.items()):
+        assert np.isfinite(row).all(), (r, pos)
+        err = helpers.relative_error(row, refs[r][pos])
+        assert err <= tol, f"{r} position {pos}: relative error {err:.3g}"
+    assert len(got) > 150
+
+
+# ---------------------------------------------------------------------------
+# another arrangement and other ends, defined here
+# ---------------------------------------------------------------------------
+
+def test_sandwich_norms_scaled_embedding_and_capped_head_without_framework_edits(tmp_path):
+    """An arrangement with four norms (before and after each branch), an embedding that
+    scales its rows and a head that soft-caps its logits: registered here, named by a toy
+    architecture's config, built and stepped by the unchanged framework."""
+    from crucible_b200 import ops
+    from crucible_b200.config import (Architecture, EndSpec, FeedForwardSpec, LayerSpec, MixerSpec,
+                                      ModelConfig, NormSpec, PositionSpec, RunEntry,
+                                      register_architecture)
+    from crucible_b200.config.registry import _ARCHITECTURES
+    from crucible_b200.engine import Engine, EngineOptions, StepEntry
+    from crucible_b200.parts import (ARRANGEMENTS, EMBEDDINGS, HEADS, Arrangement, Embedding, Head,
+                                     TensorDecl)
+    from crucible_b200.weights import write_random_model
+    from safetensors import safe_open
+    width, heads, kv, hd, inter, vocab, eps, cap, scale = 48, 3, 1, 16, 80, 97, 1e-5, 3.0, 1.7
+
+    class Sandwich(Arrangement):
+        norm_names = ("pre_mixer", "post_mixer", "pre_ffn", "post_ffn")
+
+        def forward(self, ctx, x, binding):
+            for pre, post, branch, extra in (("pre_mixer", "post_mixer", self.mixer, (binding,)),
+                                             ("pre_ffn", "post_ffn", self.feed_forward, ())):
+                h = self.norms[pre].forward(ctx, x)
+                y = torch.zeros_like(x)                      # the branch's output alone
+                branch.forward(ctx, h, y, *extra)
+                x.add_(self.norms[post].forward(ctx, y).float())
+
+    class ScaledEmbedding(Embedding):
+        def __init__(self, spec, vocab_size, w):
+            self.vocab_size, self.width, self.scale = vocab_size, w, float(spec.option("scale"))
+
+        def tensors(self):
+            return [TensorDecl("table", (self.vocab_size, self.width))]
+
+        def bind(self, tensors, dtype, device):
+            self.table = tensors["table"]
+
+        def forward(self, ctx, token_ids):
+            x = ctx.scratch("residual", (token_ids.shape[0], self.width), torch.float32)
+            ops.embed_rows(self.table, token_ids, x, ctx.device_tokens)
+            return x.mul_(self.scale)
+
+    class CappedHead(Head):
+        def __init__(self, spec, vocab_size, w, tied):
+            self.vocab_size, self.cap = vocab_size, float(spec.option("cap"))
+
+        def tie(self, table):
+            self.weight = table
+
+        def forward(self, ctx, rows):
+            logits = ctx.scratch("logits", (rows.shape[0], self.vocab_size), torch.float32)
+            ops.linear(rows, self.weight, logits)
+            return logits.copy_(torch.tanh(logits / self.cap) * self.cap)
+
+    ARRANGEMENTS.register("sandwich", Sandwich, replace=True)
+    EMBEDDINGS.register("scaled", ScaledEmbedding, replace=True)
+    HEADS.register("capped", CappedHead, replace=True)
+    names = {"embedding.table": "emb", "final_norm.gain": "norm",
+             "layer.pre_mixer.gain": "l{layer}.n0", "layer.post_mixer.gain": "l{layer}.n1",
+             "layer.pre_ffn.gain": "l{layer}.n2", "layer.post_ffn.gain": "l{layer}.n3",
+             "layer.mixer.q": "l{layer}.q", "layer.mixer.k": "l{layer}.k", "layer.mixer.v": "l{layer}.v",
+             "layer.mixer.o": "l{layer}.o", "layer.feed_forward.gate": "l{layer}.gate",
+             "layer.feed_forward.up": "l{layer}.up", "layer.feed_forward.down": "l{layer}.down"}
+
+    def parse(raw):
+        norm = NormSpec("rmsnorm", width, eps)
+        attn = MixerSpec("attention", width, heads, kv, hd, 1 / math.sqrt(hd), None,
+                         PositionSpec("rope", hd, 10000.0, raw["ctx"]))
+        layer = LayerSpec("sandwich", attn, FeedForwardSpec("swiglu", width, inter),
+                          tuple((n, norm) for n in Sandwich.norm_names))
+        return ModelConfig("ToySandwich", vocab, width, raw["ctx"], True, (layer, layer),
+                           (RunEntry(0), RunEntry(1)), norm,
+                           embedding=EndSpec("scaled", (("scale", raw["scale"]),)),
+                           head=EndSpec("capped", (("cap", raw["cap"]),)),
+                           tensor_names=names, raw=dict(raw))
+
+    _ARCHITECTURES.pop("ToySandwich", None)
+    register_architecture(Architecture("ToySandwich", parse, lambda cfg: dict(cfg.raw)))
+    raw = {"architectures": ["ToySandwich"], "ctx": 64, "scale": scale, "cap": cap}
+    folder = write_random_model(raw, str(tmp_path / "sandwich"), seed=3, std=0.2)
+    with safe_open(os.path.join(folder, "model.safetensors"), framework="pt") as f:
+        w = {k: f.get_tensor(k).double() for k in f.keys()}
+    # a layer that asks for norms the arrangement does not have is refused when built
+    from crucible_b200.models.decoder import DecoderModel
+    import dataclasses
+    cfg = parse(raw)
+    bad = dataclasses.replace(cfg, layers=(dataclasses.replace(cfg.layers[0], arrangement="pre_norm"),) * 2)
+    with pytest.raises(ValueError, match="needs the norms"):
+        DecoderModel(bad)
+
+    tokens = helpers.random_tokens(vocab, 40, 8)
+    t = len(tokens)
+    cos, sin = pm.plain_rope_tables(hd, t, 10000.0)
+    x = pm.plain_embedding(w["emb"], tokens) * scale
+    for l in range(2):
+        n = pm.plain_rmsnorm(x, w[f"l{l}.n0"], eps)
+        q = pm.plain_rope((n @ w[f"l{l}.q"].T).view(t, heads, hd), cos, sin)
+        k = pm.plain_rope((n @ w[f"l{l}.k"].T).view(t, kv, hd), cos, sin)
+        v = (n @ w[f"l{l}.v"].T).view(t, kv, hd)
+        y = pm.plain_attention(q, k, v).reshape(t, heads * hd) @ w[f"l{l}.o"].T
+        x = x + pm.plain_rmsnorm(y, w[f"l{l}.n1"], eps)
+        n = pm.plain_rmsnorm(x, w[f"l{l}.n2"], eps)
+        y = pm.plain_swiglu(n, w[f"l{l}.gate"], w[f"l{l}.up"], w[f"l{l}.down"])
+        x = x + pm.plain_rmsnorm(y, w[f"l{l}.n3"], eps)
+    want = pm.plain_rmsnorm(x, w["norm"], eps) @ w["emb"].T
+    want = (torch.tanh(want / cap) * cap).numpy()
+
+    eng = Engine(folder, EngineOptions(dtype="float32", page_tokens=16, n_pages=6, max_requests=1))
+    first = eng.step([StepEntry("a", tokens[:23], [0, 22])]).cpu().numpy()
+    assert helpers.relative_error(first[0], want[0]) < 3e-5
+    assert helpers.relative_error(first[1], want[22]) < 3e-5
+    for i in range(23, t):
+        row = eng.step([StepEntry("a", [tokens[i]], [0])]).cpu().numpy()[0]
+        assert helpers.relative_error(row, want[i]) < 3e-5, i
+    assert eng._graph_replays > 0 and not eng._graph_failed, eng._graph_error

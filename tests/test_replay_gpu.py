@@ -174,3 +174,95 @@ def test_trace_run_program(tmp_path):
     ref = helpers.plain_logits(model_dir, tokens)
     for (rid, pos), row in got.items():
         assert helpers.relative_error(row, ref[pos]) <= TOLERANCE["float32"]
+
+
+# ---------------------------------------------------------------------------
+# float32: the four ways of cutting give the same bits
+# ---------------------------------------------------------------------------
+
+def _wide_folder(tmp_path):
+    """Two layers at the 120M shape's widths (768 wide, 12 query and 4 KV heads of 64,
+    feed-forward 2,048) with a small vocabulary that is no power of two.  At this width
+    a row of the residual stream is several float4 per lane and several warps per block,
+    so two norm kernels that add in different orders give different bits; at the tiny
+    widths they would agree by accident."""
+    from crucible_b200.config import shape
+    from crucible_b200.weights import write_random_model
+    raw = shape("120m")
+    raw.update(n_layer=2, vocab_size=1003, block_size=512)
+    return write_random_model(raw, str(tmp_path / "wide"), seed=4, std=helpers.TEST_STD), 1003, 16
+
+
+def _bit_equal_case(tmp_path, which):
+    if which == "wide":
+        return _wide_folder(tmp_path)
+    return (helpers.make_folder(tmp_path, which), _vocab(which), TINY[which]["page_tokens"])
+
+
+@pytest.mark.parametrize("which", ["wide", "tiny-b"])
+def test_float32_cuts_are_bit_equal(tmp_path, which):
+    """One request of more than 200 tokens run whole, token by token, in portions of
+    changing size and mixed beside three other requests: in float32 every sum's order is
+    a function of the problem alone (never of how many rows a step holds), so the logits
+    at a position are the same bits in all four (the reference met the opposite three
+    times: `README.md:2806-2814`, `docs/paged-attention-design.md:109-130`,
+    `engine/kernels/kernels.cu:2100-2108`)."""
+    model_dir, vocab, page = _bit_equal_case(tmp_path, which)
+    n = 230
+    main = helpers.random_tokens(vocab, n, 900)
+    others = {f"o{i}": helpers.random_tokens(vocab, m, 910 + i) for i, m in enumerate([75, 140, 190])}
+    places = list(range(0, n, 9)) + [n - 1]
+
+    def collect_main(trace, sub):
+        out = str(tmp_path / sub)
+        helpers.replay_in_process(model_dir, "float32", trace, out, 4 * 256, page)
+        got = helpers.collect(trace, out, vocab)
+        return {pos: row for (rid, pos), row in got.items() if rid == "m"}
+
+    whole = Trace()
+    whole.step([("m", main, places)], end=["m"])
+    one_by_one = Trace()
+    for i, tok in enumerate(main):
+        one_by_one.step([("m", [tok], [0] if i in places else [])], end=["m"] if i == n - 1 else [])
+    portions = Trace()
+    sizes, at, i = [24, 7, 2, 13, 2, 31, 5, 17, 3, 70, 40], 0, 0
+    while at < n:
+        m = min(sizes[i % len(sizes)], n - at)
+        portions.step([("m", main[at:at + m], [p - at for p in places if at <= p < at + m])],
+                      end=["m"] if at + m == n else [])
+        at, i = at + m, i + 1
+    # mixed: the main request in portions beside the others, which are fed in portions of
+    # their own and then token by token; more than 64 rows in some steps, fewer in others
+    mixed = Trace()
+    fed = {rid: 0 for rid in others}
+    at, i = 0, 0
+    main_sizes = [40, 3, 66, 1, 1, 25, 90, 2, 1, 1]
+    while at < n or any(fed[r] < len(t) for r, t in others.items()):
+        entries, ended = [], []
+        if at < n:
+            m = min(main_sizes[i % len(main_sizes)], n - at)
+            entries.append(("m", main[at:at + m], [p - at for p in places if at <= p < at + m]))
+            at += m
+            if at == n:
+                ended.append("m")
+        for j, (rid, toks) in enumerate(others.items()):
+            if fed[rid] >= len(toks) or (i + j) % 4 == 3:
+                continue
+            m = 1 if fed[rid] >= len(toks) - 20 else min(30 + 7 * j, len(toks) - 20 - fed[rid])
+            entries.append((rid, toks[fed[rid]:fed[rid] + m], [m - 1]))
+            fed[rid] += m
+            if fed[rid] == len(toks):
+                ended.append(rid)
+        if entries:
+            mixed.step(entries, end=ended)
+        i += 1
+
+    ref = collect_main(whole, "whole")
+    assert sorted(ref) == sorted(set(places))
+    for name, trace in (("one by one", one_by_one), ("portions", portions), ("mixed", mixed)):
+        got = collect_main(trace, name.replace(" ", "_"))
+        assert sorted(got) == sorted(ref), name
+        for pos in sorted(ref):
+            assert np.array_equal(got[pos], ref[pos]), (
+                f"{which}: {name} differs from the whole prompt at position {pos} "
+                f"(largest difference {np.abs(got[pos] - ref[pos]).max():.3g})")

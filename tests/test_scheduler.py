@@ -222,3 +222,32 @@ def test_token_values_may_lag_one_step_without_changing_the_result():
     s = Scheduler(LaggedExecutor(n_pages=64))
     s.submit(Request("e", [5, 6, 7], SamplingParams(max_tokens=50, eos_token_id=(2 * 7 + 7) % 1000)))
     assert [c.finish_reason for c in s.run_to_completion()] == ["eos"]
+
+
+def test_an_executor_that_fails_mid_run_leaves_nothing_behind():
+    """The executor raises in the middle of a run (the reference injects a device
+    failure the same way, `engine/src/server.rs:1187-1227`): every live request's
+    pages, reservation and state slot are returned, and the queue is empty."""
+    class Failing(FakeExecutor):
+        def step(self, entries):
+            if len(self.steps) == 3:
+                raise RuntimeError("injected device failure")
+            return super().step(entries)
+
+    ex = Failing(n_pages=32, max_requests=3)
+    s = Scheduler(ex, SchedulerOptions(max_batch=3, prefill_token_budget=24))
+    for i, n in enumerate([40, 10, 30, 12]):
+        s.submit(Request(f"r{i}", list(range(n)), greedy(6)))
+    with pytest.raises(RuntimeError, match="injected"):
+        s.run_to_completion()
+    assert len(ex.steps) == 3
+    assert not ex.cache.live_requests()
+    assert ex.cache.free_pages(0) == 32 and ex.cache.reserved_pages(0) == 0
+    assert ex.cache.slots.free_slots == 3
+    assert not s.has_work() and not s.pending
+    ex.cache.check_invariants()
+    # the same executor serves a new run afterwards
+    ex.steps.append("recovered")
+    s2 = Scheduler(ex, SchedulerOptions(max_batch=3, prefill_token_budget=24))
+    s2.submit(Request("again", list(range(9)), greedy(3)))
+    assert len(s2.run_to_completion()[0].tokens) == 3

@@ -31,16 +31,22 @@ def test_static_scratch_argmax_matches_the_usual_one_twice_in_a_row():
     first[3, 100] = first[3, 40000] = 50.0              # a tie: the lower index wins
     first[4, 5] = float("nan")                          # NaN never wins
     second = torch.randn(64, 9001, device=dev) * 3      # other rows, other width: the scratch is reused
+    # one call first: it also looks up the scratch array's address, once for this device
+    warm = torch.empty(7, dtype=torch.int32, device=dev)
+    assert _static_argmax(lib, first, warm) == 0
+    torch.cuda.synchronize()
     for logits in (first, second):
         want = torch.empty(logits.shape[0], dtype=torch.int32, device=dev)
         ops.argmax_rows(logits, want)
         got = torch.full((logits.shape[0],), -1, dtype=torch.int32, device=dev)
-        allocated = torch.cuda.memory_allocated(dev)
+        torch.cuda.synchronize()
+        # free bytes as the driver counts them: a cudaMalloc inside the library would show
+        # here, which a counter of torch's own allocator would not
+        free_before = torch.cuda.mem_get_info(dev)[0]
         assert _static_argmax(lib, logits, got) == 0
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated(dev) == allocated
+        assert torch.cuda.mem_get_info(dev)[0] == free_before
         assert torch.equal(got, want)
-    assert first[3].argmax().item() in (100, 40000) and int(got.shape[0]) == 64
     ids = torch.empty(7, dtype=torch.int32, device=dev)
     assert _static_argmax(lib, first, ids) == 0
     torch.cuda.synchronize()
