@@ -46,9 +46,11 @@ def read_peaks():
         with open(path) as f:
             p = json.load(f)
         return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
                 "source": "measured"}
     except (OSError, KeyError, ValueError):
-        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+                "source": "fallback"}
 
 
 class ClockSampler:
@@ -196,10 +198,12 @@ def run_ours(args):
     torch.cuda.synchronize()
     windows.append((w0, time.time()))
     prefill_ms = e0.elapsed_time(e1) / n_prefill
+    prefill_tflops = prefill_flops(nums, t_prefill) / (prefill_ms / 1e3) / 1e12
     prefill = {"value": round(t_prefill / (prefill_ms / 1e3), 1), "tokens": t_prefill,
                "ms": round(prefill_ms, 4), "steps": n_prefill,
-               "frac": round(prefill_flops(nums, t_prefill) / (prefill_ms / 1e3)
-                             / (peaks["bf16_tflops"] * 1e12), 4)}
+               "frac": round(prefill_tflops / peaks["bf16_tflops"], 4),
+               "frac_of_sustained": round(prefill_tflops / peaks["bf16_tflops_sustained"], 4),
+               "tflops": round(prefill_tflops, 1)}
 
     # ---- decode through the step function -------------------------------------------
     def decode_run(b, steps, warmup):
@@ -236,16 +240,53 @@ def run_ours(args):
         return dict(tok_s=b * steps / (ms / 1e3), ms_per_step=ms / steps, launches=launches,
                     mean_ctx=mean_ctx)
 
+    weight_bytes = (nums["layers"] * nums["per_layer"] + nums["head"]) * 2
+
+    def hbm_gbs(r, b):
+        """Bytes a decode step has to read (every weight once, the live requests' cache
+        at the run's mean context) over its time."""
+        return (weight_bytes + b * r["mean_ctx"] * nums["kv_token_bytes"]) / (r["ms_per_step"] / 1e3) / 1e9
+
     main = decode_run(batch, args.steps, args.warmup)
     points = {}
     for b in (1, 64):
         r = decode_run(b, args.steps, args.warmup)
         points[f"decode_b{b}"] = round(r["tok_s"], 1)
         points[f"decode_b{b}_ms"] = round(r["ms_per_step"], 4)
+        points[f"decode_b{b}_frac"] = round(hbm_gbs(r, b) / peaks["hbm_gbs"], 4)
 
-    weight_bytes = (nums["layers"] * nums["per_layer"] + nums["head"]) * 2
-    step_bytes = weight_bytes + batch * main["mean_ctx"] * nums["kv_token_bytes"]
-    achieved = step_bytes / (main["ms_per_step"] / 1e3) / 1e9
+    # ---- a mixed step: 63 requests decoding beside one 512-token portion ----------------
+    # (the decoded tokens go through the split attention kernel, the portion through the
+    # tile kernel, in one step); beside it, for comparison, the 512-token portion alone.
+    def mixed_run(n_decoding, portion, steps, warmup):
+        ids = [f"m{i}" for i in range(n_decoding)]
+        for rid in ids:
+            engine.step([StepEntry(rid, prompt(ctx_len - 1), [])])
+        decoding = [StepEntry(rid, [rng.randrange(vocab)], [0]) for rid in ids]
+        portions = [prompt(portion) for _ in range(warmup + steps)]
+
+        def one(tokens):
+            engine.step(decoding + [StepEntry("fresh", tokens, [portion - 1])])
+            engine.finish("fresh")
+        for tokens in portions[:warmup]:
+            one(tokens)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        w0 = time.time()
+        e0.record()
+        for tokens in portions[warmup:]:
+            one(tokens)
+        e1.record()
+        torch.cuda.synchronize()
+        windows.append((w0, time.time()))
+        for rid in ids:
+            engine.finish(rid)
+        return e0.elapsed_time(e1) / steps
+
+    points["mixed_63_decoding_plus_512_ms"] = round(mixed_run(63, 512, 16, args.warmup), 4)
+    points["portion_512_alone_ms"] = round(mixed_run(0, 512, 16, args.warmup), 4)
+
+    achieved = hbm_gbs(main, batch)
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
                 "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
                 "peaks": peaks["source"]}

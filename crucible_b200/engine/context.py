@@ -13,6 +13,7 @@ final rows) extended so that a decoded token is simply a portion of length one.
 from __future__ import annotations
 
 from dataclasses import dataclass
+from functools import cached_property
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -145,25 +146,55 @@ class HostStep:
     context_len: List[int]           # per request: tokens held after this step
     state_slots: List[int]
 
-    @property
+    @cached_property
     def all_single_token(self) -> bool:
         return all(n == 1 for n in self.new_tokens)
 
-    @property
+    @cached_property
     def max_context_len(self) -> int:
         return max(self.context_len) if self.context_len else 0
 
-    @property
+    @cached_property
     def max_new_tokens(self) -> int:
         return max(self.new_tokens) if self.new_tokens else 0
 
-    @property
+    @staticmethod
+    def _bucket(longest: int) -> int:
+        return 256 * max(1, -(-longest // 256))
+
+    @cached_property
     def context_bucket(self) -> int:
-        """The longest context of the step rounded up to 256 times a power of
-        two.  Launch shapes that depend on context length use this, so that a
-        captured step can be replayed for any context inside the bucket."""
-        need = max(1, -(-self.max_context_len // 256))
-        n = 1
-        while n < need:
-            n *= 2
-        return 256 * n
+        """The longest context of the step rounded up to a multiple of 256.  Launch
+        shapes that depend on context length use this, so that a captured step can
+        be replayed for any context inside the bucket."""
+        return self._bucket(self.max_context_len)
+
+    @cached_property
+    def lead_single(self) -> int:
+        """How many requests at the head of the step bring exactly one token (the
+        scheduler puts decoding requests first)."""
+        n = 0
+        for k in self.new_tokens:
+            if k != 1:
+                break
+            n += 1
+        return n
+
+    @cached_property
+    def lead_context_bucket(self) -> int:
+        """`context_bucket` over the leading single-token requests alone (0: none)."""
+        n = self.lead_single
+        return self._bucket(max(self.context_len[:n])) if n else 0
+
+    SMALL_STEP_TOKENS = 16
+
+    def shape_key(self) -> tuple:
+        """What, beside the counts of rows, requests and wanted rows, a kernel's launch
+        shape may depend on: the most new tokens of a request, the number of leading
+        single-token requests, and the context buckets of the requests that may run
+        split over their keys (all of them when every request brings few tokens; the
+        leading single-token ones otherwise).  Steps with equal keys launch the same
+        kernels with the same grids."""
+        small = self.max_new_tokens <= self.SMALL_STEP_TOKENS
+        return (self.max_new_tokens, self.lead_single,
+                self.context_bucket if small else 0, self.lead_context_bucket)

@@ -286,8 +286,7 @@ class Engine:
             self._graphs.clear()
             self._graph_generation = self.scratch.generation
         host = ctx.host
-        key = (ctx.n_tokens, ctx.n_requests, ctx.n_logit_rows, host.max_new_tokens,
-               host.context_bucket)
+        key = (ctx.n_tokens, ctx.n_requests, ctx.n_logit_rows) + host.shape_key()
         hit = self._graphs.get(key)
         if hit is not None:
             graph, logits, launches = hit

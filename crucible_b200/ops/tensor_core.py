@@ -25,7 +25,6 @@ build.register_module("attention_decode_tcgen05", ["common.cuh", "tc_common.cuh"
 # them to the mma.sync kernel instead (the tests compare the two).
 USE_TCGEN05_ATTENTION = True
 USE_TCGEN05_DECODE = True
-DECODE_TC_BLOCKS = 200      # chunks are doubled while the launch would still have this many blocks
 
 _c_int, _c_void_p = ctypes.c_int, ctypes.c_void_p
 STORE_BF16, STORE_F32, ACCUM_F32, SWIGLU_BF16, ROPE_APPEND = 0, 1, 2, 3, 4
@@ -338,8 +337,22 @@ ATTENTION_LEAN = -1      # the form of the head-size-64 prompt attention: -1 by 
                          # blocks (see the kernel's header), 0 roomy, 1 lean (tests fix it)
 
 
-def _attention_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads, head_dim, scale,
-                       window, ctx, cache) -> bool:
+class _Requests:
+    """A run of consecutive requests of the step, as the attention kernels see one:
+    the metadata arrays from its first request on, how many there are, the most new
+    tokens any of them brings, the context bucket that covers them, and the number of
+    the step's rows up to its end (the split form's scratch is indexed by row)."""
+
+    def __init__(self, ctx, table, first: int, count: int, max_new: int, bucket: int, rows_end: int):
+        self.row_start = ctx.req_row_start[first:]
+        self.first_pos = ctx.req_first_pos[first:]
+        self.table = table[first:]
+        self.table_stride = table.shape[1]
+        self.count, self.max_new, self.bucket, self.rows_end = count, max_new, bucket, rows_end
+
+
+def _attention_tcgen05(qkv, out, k_cache, v_cache, reqs, n_heads, n_kv_heads, head_dim, scale,
+                       window, cache) -> bool:
     """tcgen05 attention for portions of prompts: head size 64 or 128, page size a
     power of two from 8 to 128.  Returns False for anything else."""
     pt = cache.page_tokens
@@ -349,9 +362,9 @@ def _attention_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads, h
     code = lib.cb_attention_tcgen05(
         _c_void_p(qkv.data_ptr()), _c_int(qkv.stride(0)), _c_void_p(out.data_ptr()),
         _c_int(out.stride(0)), _c_void_p(k_cache.data_ptr()), _c_void_p(v_cache.data_ptr()),
-        _c_int(k_cache.shape[0]), _c_void_p(ctx.req_row_start.data_ptr()),
-        _c_void_p(ctx.req_first_pos.data_ptr()), _c_void_p(table.data_ptr()),
-        _c_int(table.shape[1]), _c_int(ctx.n_requests), _c_int(ctx.host.max_new_tokens),
+        _c_int(k_cache.shape[0]), _c_void_p(reqs.row_start.data_ptr()),
+        _c_void_p(reqs.first_pos.data_ptr()), _c_void_p(reqs.table.data_ptr()),
+        _c_int(reqs.table_stride), _c_int(reqs.count), _c_int(reqs.max_new),
         _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim), _c_int(pt),
         ctypes.c_float(scale), _c_int(window or 0), _c_int(ATTENTION_LEAN),
         _c_void_p(status_word(qkv.device).data_ptr()), _stream())
@@ -363,11 +376,11 @@ def _attention_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads, h
     return True
 
 
-def _attention_decode_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads, head_dim,
-                              scale, window, ctx, cache, partial, counters, n_chunks,
+def _attention_decode_tcgen05(qkv, out, k_cache, v_cache, reqs, n_heads, n_kv_heads, head_dim,
+                              scale, window, cache, partial, counters, n_chunks,
                               chunk_keys) -> bool:
     """tcgen05 attention for decoded tokens (at most 16 packed rows per request and
-    KV head): head size 64, page size a power of two from 8 to 128.  Returns False
+    KV head): head size 64 or 128, page size a power of two from 8 to 128.  Returns False
     for anything else."""
     pt = cache.page_tokens
     if pt < 8 or pt > 128 or pt & (pt - 1):
@@ -376,9 +389,9 @@ def _attention_decode_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_h
     code = lib.cb_attention_decode_tcgen05(
         _c_void_p(qkv.data_ptr()), _c_int(qkv.stride(0)), _c_void_p(out.data_ptr()),
         _c_int(out.stride(0)), _c_void_p(k_cache.data_ptr()), _c_void_p(v_cache.data_ptr()),
-        _c_int(k_cache.shape[0]), _c_void_p(ctx.req_row_start.data_ptr()),
-        _c_void_p(ctx.req_first_pos.data_ptr()), _c_void_p(table.data_ptr()),
-        _c_int(table.shape[1]), _c_int(ctx.n_requests), _c_int(ctx.host.max_new_tokens),
+        _c_int(k_cache.shape[0]), _c_void_p(reqs.row_start.data_ptr()),
+        _c_void_p(reqs.first_pos.data_ptr()), _c_void_p(reqs.table.data_ptr()),
+        _c_int(reqs.table_stride), _c_int(reqs.count), _c_int(reqs.max_new),
         _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim), _c_int(pt),
         ctypes.c_float(scale), _c_int(window or 0), _c_void_p(partial.data_ptr()),
         _c_void_p(counters.data_ptr()), _c_int(n_chunks), _c_int(chunk_keys),
@@ -391,77 +404,70 @@ def _attention_decode_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_h
     return True
 
 
+DECODE_TC_TARGET_BLOCKS = 2 * N_SMS      # two blocks of the tcgen05 decode kernel fit an SM
+DECODE_MMA_TARGET_BLOCKS = 4 * N_SMS
+
+
 def decode_chunk_keys(blocks_per_chunk: int, context_bucket: int, tcgen05: bool) -> int:
-    """Keys per block of the split attention for decoded tokens: 256 * 2^k, a function of the
-    step's shape alone (so a captured step replays).  `blocks_per_chunk`: blocks that one chunk
-    of every request takes (requests x KV heads x groups of 16 packed rows)."""
-    # the tcgen05 form keeps two blocks per SM busy with far fewer instructions per key, so it
-    # wants fewer, longer chunks than the mma.sync form
-    enough = DECODE_TC_BLOCKS if tcgen05 else 4 * N_SMS
-    chunk = 256
-    while chunk * 2 <= context_bucket and blocks_per_chunk * (context_bucket // (chunk * 2)) >= enough:
-        chunk *= 2
-    if tcgen05 and chunk >= 512 and chunk * 2 == context_bucket:
-        # Half the bucket is the worst chunk: a context lies in the bucket's upper half, so every
-        # request would bring one full chunk and a scrap of a second.  Quarters while they stay
-        # two waves of blocks (two to an SM), else the whole bucket as one chunk (measured on
-        # B200, 24 requests x 4 KV heads at 2,100 tokens: 0.64 against 0.75 ms per step).
-        chunk = chunk // 2 if blocks_per_chunk * 4 <= 4 * N_SMS else context_bucket
-    return chunk
+    """Keys per block of the split attention for decoded tokens: a function of the step's
+    shape alone (so a captured step replays).  `blocks_per_chunk`: blocks that one chunk of
+    every request takes (requests x KV heads x groups of 16 packed rows).  `context_bucket`:
+    the longest context rounded up to a multiple of 256.  The chunk is the bucket divided
+    into as many equal parts as fill the SMs once (the tcgen05 form keeps two blocks to an
+    SM busy with far fewer instructions per key, so it wants one wave; the mma.sync form
+    wants more, shorter chunks), rounded up to whole tiles of keys."""
+    unit = 128 if tcgen05 else 256
+    target = DECODE_TC_TARGET_BLOCKS if tcgen05 else DECODE_MMA_TARGET_BLOCKS
+    parts = max(1, target // max(1, blocks_per_chunk))
+    chunk = -(-context_bucket // parts)
+    chunk = -(-chunk // unit) * unit
+    return min(max(chunk, unit), -(-context_bucket // unit) * unit)
 
 
-def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx, cache,
-                    binding) -> bool:
-    """Tensor-core attention over the paged cache.  Takes head sizes that are
-    multiples of 16 up to 256 and any head counts, group sizes and page sizes;
-    refuses anything else (the plain kernel then runs).  Steps whose requests
-    bring at most 16 query rows per KV head (decoded tokens, tiny portions) run
-    split over chunks of 256 * 2^k keys; longer portions run as tiles: the
-    tcgen05 kernel for head size 64, the mma.sync kernel of 64-row tiles else."""
-    if (qkv.dtype != torch.bfloat16 or head_dim % 16 != 0 or head_dim > 256
-            or n_heads % n_kv_heads != 0 or qkv.stride(0) % 8 != 0 or out.stride(0) % 2 != 0):
-        return False
-    k_cache, v_cache = cache.keys(binding.slot), cache.values(binding.slot)
-    table = ctx.block_table(binding.group)
-    host = ctx.host
+SPLIT_ROWS = 16          # packed rows (new tokens x heads of a group) the split form takes
+
+
+def _attend(qkv, out, k_cache, v_cache, reqs, n_heads, n_kv_heads, head_dim, scale, window, ctx,
+            cache) -> bool:
+    """One run of requests through the kernel that suits it.  A function of the run's
+    shape (count, most new tokens, bucket) and of the sizes only."""
     n_rep = n_heads // n_kv_heads
-    split = host.max_new_tokens * n_rep <= 16
-    # The split form is launched over chunks of 256 * 2^k keys that cover the step's
-    # context bucket; the chunk is the largest that still gives a few waves of blocks
-    # over the 148 SMs (a function of the step's shape alone, so a captured step
-    # replays; contexts fill about half of their bucket on average).
+    split = reqs.max_new * n_rep <= SPLIT_ROWS
     pt = cache.page_tokens
     decode_tc = (USE_TCGEN05_DECODE and split and head_dim in (64, 128) and out.stride(0) % 2 == 0
                  and 8 <= pt <= 128 and pt & (pt - 1) == 0)
-    chunk_keys = 256
-    if split:
-        blocks_per_chunk = ctx.n_requests * n_kv_heads * (-(-host.max_new_tokens * n_rep // 16))
-        chunk_keys = decode_chunk_keys(blocks_per_chunk, host.context_bucket, decode_tc)
-    n_chunks = host.context_bucket // chunk_keys if split else 0
     partial = counters = None
+    n_chunks, chunk_keys = 0, 256
     if split:
-        floats = ctx.n_tokens * n_heads * n_chunks * (head_dim + 2)
+        groups = -(-reqs.max_new * n_rep // 16)
+        blocks_per_chunk = reqs.count * n_kv_heads * groups
+        chunk_keys = decode_chunk_keys(blocks_per_chunk, reqs.bucket, decode_tc)
+        n_chunks = -(-reqs.bucket // chunk_keys)
+        floats = reqs.rows_end * n_heads * n_chunks * (head_dim + 2)
         partial = ctx.scratch("attn.partial", (floats,), torch.float32)
-        n_counters = ctx.n_requests * n_kv_heads * (-(-host.max_new_tokens * n_rep // 16))
-        counters = _buffer(qkv.device, "attn.counters", n_counters, torch.int32, zero=True)
+        counters = _buffer(qkv.device, "attn.counters", blocks_per_chunk, torch.int32, zero=True)
     if (decode_tc
-            and _attention_decode_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads,
-                                          head_dim, scale, window, ctx, cache, partial, counters,
+            and _attention_decode_tcgen05(qkv, out, k_cache, v_cache, reqs, n_heads, n_kv_heads,
+                                          head_dim, scale, window, cache, partial, counters,
                                           n_chunks, chunk_keys)):
         return True
     if (USE_TCGEN05_ATTENTION and not split and head_dim in (64, 128)
-            and host.max_new_tokens * n_rep >= 64 and out.stride(0) % 8 == 0
-            and _attention_tcgen05(qkv, out, k_cache, v_cache, table, n_heads, n_kv_heads,
-                                   head_dim, scale, window, ctx, cache)):
+            and reqs.max_new * n_rep >= 64 and out.stride(0) % 8 == 0
+            and _attention_tcgen05(qkv, out, k_cache, v_cache, reqs, n_heads, n_kv_heads,
+                                   head_dim, scale, window, cache)):
         return True
+    if split and chunk_keys % 256:
+        # the mma.sync split form walks whole tiles of 256 keys
+        chunk_keys = -(-chunk_keys // 256) * 256
+        n_chunks = -(-reqs.bucket // chunk_keys)
     lib = build.load("attention_mma")
     code = lib.cb_attention_mma(
         _c_void_p(qkv.data_ptr()), _c_int(qkv.stride(0)), _c_void_p(out.data_ptr()),
         _c_int(out.stride(0)), _c_void_p(k_cache.data_ptr()), _c_void_p(v_cache.data_ptr()),
-        _c_void_p(ctx.positions.data_ptr()), _c_void_p(ctx.req_row_start.data_ptr()),
-        _c_void_p(ctx.req_first_pos.data_ptr()), _c_void_p(table.data_ptr()),
-        _c_int(table.shape[1]), _c_int(ctx.n_tokens), _c_int(ctx.n_requests),
-        _c_int(host.max_new_tokens), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
+        _c_void_p(ctx.positions.data_ptr()), _c_void_p(reqs.row_start.data_ptr()),
+        _c_void_p(reqs.first_pos.data_ptr()), _c_void_p(reqs.table.data_ptr()),
+        _c_int(reqs.table_stride), _c_int(reqs.rows_end), _c_int(reqs.count),
+        _c_int(reqs.max_new), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
         _c_int(cache.page_tokens), ctypes.c_float(scale), _c_int(window or 0),
         _c_void_p(partial.data_ptr() if partial is not None else 0),
         _c_void_p(counters.data_ptr() if counters is not None else 0), _c_int(n_chunks),
@@ -472,6 +478,43 @@ def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx,
         raise RuntimeError(f"tensor-core attention failed to launch (CUDA error {code})")
     _count(1)
     return True
+
+
+def paged_attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ctx, cache,
+                    binding) -> bool:
+    """Tensor-core attention over the paged cache.  Takes head sizes that are
+    multiples of 16 up to 256 and any head counts, group sizes and page sizes;
+    refuses anything else (the plain kernel then runs).
+
+    The kernel is chosen per request, not per step: requests that bring at most 16
+    query rows per KV head (decoded tokens, tiny portions) run split over chunks of
+    keys, with the last block of a row group to arrive merging; longer portions run as
+    tiles (the tcgen05 kernel for head sizes 64 and 128, the mma.sync kernel of 64-row
+    tiles else).  A step that holds both kinds (single decoded tokens first, as the
+    scheduler orders them, then portions) is two launches over disjoint runs of its
+    requests; the shapes of both are functions of the step's shape."""
+    if (qkv.dtype != torch.bfloat16 or head_dim % 16 != 0 or head_dim > 256
+            or n_heads % n_kv_heads != 0 or qkv.stride(0) % 8 != 0 or out.stride(0) % 2 != 0):
+        return False
+    k_cache, v_cache = cache.keys(binding.slot), cache.values(binding.slot)
+    table = ctx.block_table(binding.group)
+    host = ctx.host
+    n_rep = n_heads // n_kv_heads
+    args = (n_heads, n_kv_heads, head_dim, scale, window, ctx, cache)
+    lead = host.lead_single
+    if 0 < lead < ctx.n_requests and host.max_new_tokens * n_rep > SPLIT_ROWS:
+        decoding = _Requests(ctx, table, 0, lead, 1, host.lead_context_bucket, lead)
+        portions = _Requests(ctx, table, lead, ctx.n_requests - lead, host.max_new_tokens,
+                             host.context_bucket, ctx.n_tokens)
+        if not _attend(qkv, out, k_cache, v_cache, decoding, *args):
+            return False
+        if not _attend(qkv, out, k_cache, v_cache, portions, *args):
+            raise RuntimeError("the attention kernels took the step's decoded tokens but "
+                               "refused its portions: a rule of sizes is inconsistent")
+        return True
+    whole = _Requests(ctx, table, 0, ctx.n_requests, host.max_new_tokens, host.context_bucket,
+                      ctx.n_tokens)
+    return _attend(qkv, out, k_cache, v_cache, whole, *args)
 
 
 def run_wait_probe(device, limit: int = 4096) -> None:

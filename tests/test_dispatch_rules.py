@@ -38,20 +38,38 @@ def test_tall_tiles_only_where_they_fill_the_sms():
     assert not tensor_core._tall_tiles(512, 28672, 4096)
 
 
-@pytest.mark.parametrize("bucket", [256, 512, 1024, 4096, 8192])
+@pytest.mark.parametrize("bucket", [256, 512, 768, 1024, 2304, 4096, 8192, 8448])
 @pytest.mark.parametrize("blocks", [1, 4, 32, 48, 96, 128, 160, 256, 1000])
 @pytest.mark.parametrize("tcgen05", [True, False])
-def test_decode_chunks_divide_the_bucket(blocks, bucket, tcgen05):
+def test_decode_chunks_cover_the_bucket_in_whole_tiles(blocks, bucket, tcgen05):
+    unit = 128 if tcgen05 else 256
     chunk = tensor_core.decode_chunk_keys(blocks, bucket, tcgen05)
-    assert 256 <= chunk <= bucket and bucket % chunk == 0
-    if tcgen05 and chunk >= 512:
-        assert chunk * 2 != bucket                  # never one full chunk and a scrap
+    assert unit <= chunk <= -(-bucket // unit) * unit and chunk % unit == 0
+    n_chunks = -(-bucket // chunk)
+    assert (n_chunks - 1) * chunk < bucket <= n_chunks * chunk     # no chunk is empty
+    target = tensor_core.DECODE_TC_TARGET_BLOCKS if tcgen05 else tensor_core.DECODE_MMA_TARGET_BLOCKS
+    # never more blocks than the target unless a chunk is already a single tile
+    assert blocks * n_chunks <= max(target, blocks) or chunk == unit
 
 
 def test_decode_chunks_of_the_benchmark_points():
-    # 4 KV heads, contexts of 2,048 to 2,304 tokens (bucket 4,096)
-    assert tensor_core.decode_chunk_keys(1 * 4, 4096, True) == 256
-    assert tensor_core.decode_chunk_keys(8 * 4, 4096, True) == 512
-    assert tensor_core.decode_chunk_keys(24 * 4, 4096, True) == 1024
-    assert tensor_core.decode_chunk_keys(32 * 4, 4096, True) == 1024
-    assert tensor_core.decode_chunk_keys(64 * 4, 4096, True) == 4096
+    # 4 KV heads, contexts of 2,056 to 2,304 tokens (bucket 2,304)
+    assert tensor_core.decode_chunk_keys(1 * 4, 2304, True) == 128         # 18 chunks, 72 blocks
+    assert tensor_core.decode_chunk_keys(8 * 4, 2304, True) == 256         # 9 chunks, 288 blocks
+    assert tensor_core.decode_chunk_keys(16 * 4, 2304, True) == 640        # 4 chunks, 256 blocks
+    assert tensor_core.decode_chunk_keys(64 * 4, 2304, True) == 2304       # a block per request and KV head
+
+
+def test_step_shape_key_follows_what_launches_depend_on():
+    from crucible_b200.engine.context import HostStep
+    decode = HostStep(list("abc"), [1, 1, 1], [2100, 300, 40], [2101, 301, 41], [0, 1, 2])
+    assert decode.context_bucket == 2304 and decode.lead_single == 3
+    assert decode.shape_key() == (1, 3, 2304, 2304)
+    mixed = HostStep(list("abc"), [1, 1, 500], [2100, 300, 4000], [2101, 301, 4500], [0, 1, 2])
+    # the portion's own context does not enter the key: the tile kernels walk it from metadata
+    assert mixed.shape_key() == (500, 2, 0, 2304)
+    assert mixed.lead_context_bucket == 2304 and mixed.context_bucket == 4608
+    later = HostStep(list("abc"), [1, 1, 500], [2101, 301, 4500], [2102, 302, 5000], [0, 1, 2])
+    assert later.shape_key() == mixed.shape_key()
+    prompts = HostStep(list("ab"), [700, 1], [0, 50], [700, 51], [0, 1])
+    assert prompts.shape_key() == (700, 0, 0, 0)
