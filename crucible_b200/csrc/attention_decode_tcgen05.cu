@@ -129,10 +129,11 @@ __device__ __forceinline__ void merge_row(const DecodeParams& p, int tok, int he
     float m = -INFINITY, l = 0.f, acc[F];
 #pragma unroll
     for (int f = 0; f < F; ++f) acc[f] = 0.f;
-    for (int c0 = c_first; c0 <= c_last; c0 += 8) {
-        float mc[8], lc[8], o[8][F];
+    constexpr int ROUND = 8;                             // chunks asked for at once (16: measured slower)
+    for (int c0 = c_first; c0 <= c_last; c0 += ROUND) {
+        float mc[ROUND], lc[ROUND], o[ROUND][F];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < ROUND; ++j) {
             const bool in = c0 + j <= c_last;
             const float* src = base + (size_t)(in ? c0 + j : c_first) * MP;
             mc[j] = in ? __ldcg(src + HD) : -INFINITY;
@@ -146,7 +147,7 @@ __device__ __forceinline__ void merge_row(const DecodeParams& p, int tok, int he
             }
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {                    // ascending chunks
+        for (int j = 0; j < ROUND; ++j) {                // ascending chunks
             const float m_new = fmaxf(m, mc[j]);
             const float off = m_new == -INFINITY ? 0.f : m_new;
             const float keep = exp2f(m - off), take = exp2f(mc[j] - off);
@@ -212,6 +213,7 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             tc::mbar_init(&s.pv_done[b], 1);
         }
         s.abort_flag = 0;
+        s.is_last = 0;
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&map_k);
         tc::prefetch_tensormap(&map_v);
@@ -224,7 +226,6 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         tc::tmem_alloc(&s.tmem_base, TMEM_COLS);  // S^T: columns 0..15 and 16..31, O: from 64
         tc::tmem_relinquish();
     }
-    cb_pdl_wait();
 
     // ---- the loader's thread: one tile of K and V pages into a stage -----------------------
     const int pages_per_tile = KEYS >> p.page_shift;
@@ -278,7 +279,11 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     const int early = n_tiles < STAGES ? n_tiles : STAGES;
 
     // ---- warp 0's thread starts the first tiles' copies; the others stage the query rows
-    // (16-byte pieces into the 128-byte swizzle; rows past the request's are zero) and clear P
+    // (16-byte pieces into the 128-byte swizzle; rows past the request's are zero) and clear P.
+    // The block tables were uploaded before the step began, so the first tiles' lookups need
+    // not wait for the kernels ahead in the stream; the copies do (the product before this
+    // kernel writes this step's keys, and copies asked for while it runs get in its loads' way:
+    // measured, a step is slower with them than without).
     if (warp == 0) {
         if (lane == 0) {
             // the first tiles wait for nothing: all their lookups first, then all their copies
@@ -286,11 +291,15 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             lookup(0, y0);
             if (early > 1) lookup(1, y1);
             if (early > 2) lookup(2, y2);
+            cb_pdl_wait();
             issue(0, y0);
             if (early > 1) issue(1, y1);
             if (early > 2) issue(2, y2);
+        } else {
+            cb_pdl_wait();
         }
     } else {
+        cb_pdl_wait();
         const int tid = threadIdx.x - 32;
         for (int i = tid; i < ROWS * 8 * NH; i += 160) {
             const int r = i / (8 * NH), c = i % (8 * NH);        // row, 16-byte piece of the row
@@ -536,26 +545,33 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                 part[HD] = m;
                 part[HD + 1] = l;
             }
+            if (n_active > 1) {
+                // This warp wrote the chunk's partial: it arrives for the block.  The warp's
+                // stores are ordered before lane 0's arrival by the warp barrier; the arrival
+                // releases them and acquires what the blocks that arrived before released.
+                __syncwarp();
+                if (lane == 0) {
+                    int* counter = p.counters + req * p.n_kv_heads + kv_head;
+                    int prev;
+                    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;"
+                                 : "=r"(prev) : "l"(counter) : "memory");
+                    if (prev == n_active - 1) {
+                        *counter = 0;                     // ready for the next launch
+                        s.is_last = 1;
+                    }
+                }
+            }
         }
     }
     tc::tc_fence_before_sync();
-    __threadfence();
     __syncthreads();
     if (warp == 1) {
         tc::tc_fence_after_sync();
         tc::tmem_dealloc(s.tmem_base, TMEM_COLS);
     }
-    if (n_active == 1 || *abort_flag) return;
     // ---- the last block to arrive for these rows merges their chunks ------------------------
-    if (threadIdx.x == 0) {
-        int* counter = p.counters + req * p.n_kv_heads + kv_head;
-        const int prev = atomicAdd(counter, 1);
-        s.is_last = prev == n_active - 1;
-        if (s.is_last) *counter = 0;                      // ready for the next launch
-    }
-    __syncthreads();
-    if (!s.is_last) return;
-    __threadfence();
+    // (what the arriving thread acquired holds for the whole block after the barrier above)
+    if (n_active == 1 || *abort_flag || !s.is_last) return;
     for (int r = warp; r < n_rows; r += 6) {
         const int tok = row_base + r / n_rep, head = kv_head * n_rep + r % n_rep;
         merge_row<HD>(p, tok, head, first_pos + r / n_rep, lane);

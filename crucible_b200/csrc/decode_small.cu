@@ -65,6 +65,10 @@ struct SmallParams {
     __nv_bfloat16* k_cache;
     __nv_bfloat16* v_cache;
     int n_heads, n_kv_heads, head_dim, page_tokens, write_cache;
+    int trigger_early;            // let the kernel after this one start as soon as this one's weights are asked for
+                                  // (the q/k/v product: measured on B200 at batch 1 / 8, 2,048-token contexts,
+                                  // 0.291 -> 0.286 / 0.345 -> 0.330 ms per step; for the other products 0 to
+                                  // 0.03 ms slower: their successors' weight loads get in the way)
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -132,6 +136,10 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
         vf[i] = in ? __ldg(reinterpret_cast<const uint4*>(wf + kb * 32)) : make_uint4(0, 0, 0, 0);
         vs[i] = in ? __ldg(reinterpret_cast<const uint4*>(ws + kb * 32)) : make_uint4(0, 0, 0, 0);
     }
+    // The kernel after the q/k/v product is the attention over the cache: it may start at
+    // once, so that its blocks are resident and their barriers, tensor memory, metadata and
+    // block-table lookups are done by the time this kernel ends.
+    if (p.trigger_early) cb_pdl_trigger();
     // the weights above are written by no kernel; everything below reads what earlier
     // kernels of the stream produced
     cb_pdl_wait();
@@ -287,7 +295,7 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
     __syncthreads();
     // the step's rows are staged and this block's weights are on their way: the kernel after
     // this one may start and ask for its own
-    cb_pdl_trigger();
+    if (!p.trigger_early) cb_pdl_trigger();
     // ---- multiply: this warp's blocks of K -------------------------------------------------
     float c[MT][4];
 #pragma unroll
@@ -491,6 +499,7 @@ CB_EXPORT int cb_small_qkv_rope_append(const float* x, const float* gain, float 
     p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim;
     p.page_tokens = page_tokens; p.write_cache = write_cache;
+    p.trigger_early = 1;
     cudaStream_t s = (cudaStream_t)stream;
     return x ? launch_rows<true, ROPE_APPEND>(p, s) : launch_rows<false, ROPE_APPEND>(p, s);
 }

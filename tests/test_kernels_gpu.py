@@ -474,10 +474,14 @@ def test_linear_refuses_what_tma_cannot_read():
 # ---------------------------------------------------------------------------
 
 def _paged_case(dtype, n_heads, n_kv, hd, page_tokens, requests, seed, window=None, peak=True,
-                shuffle=True):
+                shuffle=True, released="null"):
     """requests: list of (context_before, new_tokens).  Builds random q, k, v for
     whole sequences, scatters k/v of the context into shuffled pages, and returns
-    what the kernels need plus the reference output for the new rows."""
+    what the kernels need plus the reference output for the new rows.  With a window,
+    pages that lie wholly below the window of a request's first new token are taken
+    away as the cache manager does: their contents become the loud value and their
+    table entries name the null page (`released="null"`: one more page, all zeros, as
+    the engine uploads it) or are -1 (`released="minus"`)."""
     g = torch.Generator(device="cpu").manual_seed(seed)
     rng = random.Random(seed)
     total_pages = sum(-(-(c + n) // page_tokens) for c, n in requests) + 3
@@ -486,7 +490,9 @@ def _paged_case(dtype, n_heads, n_kv, hd, page_tokens, requests, seed, window=No
         rng.shuffle(order)
     else:
         order.reverse()              # pages are handed out in ascending order: runs of pages
-    kv = torch.full((1, 2, total_pages, n_kv, page_tokens, hd), float("nan"))   # poison
+    kv = torch.full((1, 2, total_pages + 1, n_kv, page_tokens, hd), float("nan"))   # poison
+    null_page = total_pages
+    kv[:, :, null_page] = 0.0
     stride = max(-(-(c + n) // page_tokens) for c, n in requests) + 2
     tables = torch.zeros(len(requests), stride, dtype=torch.int32)
     q_rows, refs, positions, row_request, row_start, first_pos = [], [], [], [], [0], []
@@ -510,6 +516,10 @@ def _paged_case(dtype, n_heads, n_kv, hd, page_tokens, requests, seed, window=No
         for pos in range(length):
             kv[0, 0, pages[pos // page_tokens], :, pos % page_tokens] = k[pos].float()
             kv[0, 1, pages[pos // page_tokens], :, pos % page_tokens] = v[pos].float()
+        if window is not None and released:
+            for b in range(max(0, ctx_len - window + 1) // page_tokens):
+                kv[0, :, pages[b]] = float("nan")
+                tables[r, b] = null_page if released == "null" else -1
         qd, kd, vd = q.double(), k.double(), v.double()
         out = torch.zeros(n_new, n_heads, hd, dtype=torch.float64)
         for i, pos in enumerate(range(ctx_len, length)):
@@ -621,8 +631,10 @@ def test_attention_tcgen05_matches_reference_and_mma(case, lean):
     assert tensor_core.USE_TCGEN05_ATTENTION
     try:
         tensor_core.ATTENTION_LEAN = lean
-        assert tensor_core._attention_tcgen05(qkv, out, k_cache, cache.values(0), ctx.block_table(0),
-                                              n_heads, n_kv, hd, 1 / math.sqrt(hd), window, ctx, cache)
+        whole = tensor_core._Requests(ctx, ctx.block_table(0), 0, ctx.n_requests,
+                                      ctx.host.max_new_tokens, ctx.host.context_bucket, ctx.n_tokens)
+        assert tensor_core._attention_tcgen05(qkv, out, k_cache, cache.values(0), whole, n_heads, n_kv,
+                                              hd, 1 / math.sqrt(hd), window, cache)
     finally:
         tensor_core.ATTENTION_LEAN = -1
     torch.cuda.synchronize()
@@ -677,6 +689,41 @@ def test_attention_decode_tcgen05_matches_reference_and_mma(case, shuffle):
     assert tensor_core.paged_attention(qkv, again, n_heads, n_kv, hd, 1 / math.sqrt(hd), window, ctx,
                                        cache, binding)
     assert torch.equal(again, outs[True])
+
+
+@pytest.mark.parametrize("case", [
+    # decoded tokens first, then portions: the step is two launches over its requests
+    (12, 4, 64, 16, [(300, 1), (2047, 1), (0, 1), (0, 130), (17, 40)], None),
+    (8, 2, 128, 16, [(700, 1), (40, 200), (1000, 1)], None),      # a decoded token after a portion: tiles
+    (6, 2, 48, 16, [(257, 1), (900, 1), (5, 33)], None),           # heads of 48: both forms of the mma.sync kernel
+    (4, 2, 64, 32, [(900, 1), (100, 1), (400, 90)], 300),          # a window, with pages given back
+])
+@pytest.mark.parametrize("released", ["null", "minus"])
+def test_attention_of_a_mixed_step_chooses_the_kernel_per_request(case, released):
+    from crucible_b200.ops import tensor_core
+    n_heads, n_kv, hd, page, requests, window = case
+    qkv, ctx, cache, binding, ref = _paged_case(torch.bfloat16, n_heads, n_kv, hd, page, requests,
+                                                11, window, released=released)
+    lead = ctx.host.lead_single
+    assert 0 < lead < len(requests)
+    out = torch.zeros(qkv.shape[0], n_heads * hd, device=DEV, dtype=torch.bfloat16)
+    launches = tensor_core_launches()
+    assert tensor_core.paged_attention(qkv, out, n_heads, n_kv, hd, 1 / math.sqrt(hd), window, ctx,
+                                       cache, binding)
+    assert tensor_core_launches() - launches == 2
+    torch.cuda.synchronize()
+    tensor_core.check_status(DEV)
+    assert rel(out.cpu(), ref) < 1.5e-2
+    # and once more: the split form left its counters at zero
+    again = torch.zeros_like(out)
+    assert tensor_core.paged_attention(qkv, again, n_heads, n_kv, hd, 1 / math.sqrt(hd), window, ctx,
+                                       cache, binding)
+    assert torch.equal(again, out)
+
+
+def tensor_core_launches():
+    from crucible_b200 import ops
+    return ops.LAUNCHES[0]
 
 
 def test_attention_odd_head_size_falls_to_plain_kernel():
