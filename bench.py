@@ -2,7 +2,7 @@
 """Benchmark of the engine on one B200: decode tokens per second (a "step" is
 one decode step) and prefill tokens per second, with roofline fractions.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference|cpu]
 
 Default run: the layer sizes of the 120M shape (12 layers, width 768, 12 query
 and 4 KV heads of size 64, SwiGLU 2048, vocabulary 50,304, tied head) with
@@ -451,6 +451,85 @@ def run_reference(args):
     return 0
 
 
+def run_cpu_baseline(args):
+    """A timed CPU baseline: a plain float32 forward of whole sequences (no cache, no
+    batching; embedding, RMSNorm, half-split RoPE, grouped-query attention, SwiGLU, tied
+    or untied head, written here from the model's formulas with torch's CPU operators) on
+    the two tiny shapes and on one layer of the 120M shape.  The reference's own scalar
+    CPU engine decodes 9.66 tokens/s on its 120M model (`README.md:486-490`); this is the
+    number to hold the GPU figures against on the machine at hand."""
+    import math
+    import torch
+    from crucible_b200.config import parse_config, shape
+    torch.manual_seed(0)
+
+    def forward(cfg, weights, tokens):
+        layer0 = cfg.layers[0]
+        m, f = layer0.mixer, layer0.feed_forward
+        hq, hkv, hd, t = m.n_heads, m.n_kv_heads, m.head_dim, len(tokens)
+        half = hd // 2
+        inv = m.position.theta ** (-torch.arange(half, dtype=torch.float64) * 2.0 / hd)
+        ang = torch.outer(torch.arange(t, dtype=torch.float64), inv)
+        cos, sin = ang.cos().float()[:, None, :], ang.sin().float()[:, None, :]
+
+        def norm(x, g, eps):
+            return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * g
+
+        def rope(x):
+            a, b = x[..., :half], x[..., half:]
+            return torch.cat([a * cos - b * sin, a * sin + b * cos], dim=-1)
+        x = weights["emb"][torch.tensor(tokens)]
+        causal = torch.full((t, t), float("-inf")).triu(1)
+        for w in weights["layers"]:
+            n = norm(x, w["n1"], layer0.mixer_norm.eps)
+            q = rope((n @ w["q"].T).view(t, hq, hd))
+            k = rope((n @ w["k"].T).view(t, hkv, hd)).repeat_interleave(hq // hkv, dim=1)
+            v = (n @ w["v"].T).view(t, hkv, hd).repeat_interleave(hq // hkv, dim=1)
+            sc = torch.einsum("thd,shd->hts", q, k) / math.sqrt(hd) + causal
+            a = torch.einsum("hts,shd->thd", torch.softmax(sc, dim=-1), v).reshape(t, hq * hd)
+            x = x + a @ w["o"].T
+            n = norm(x, w["n2"], layer0.feed_forward_norm.eps)
+            g = n @ w["gate"].T
+            x = x + ((g / (1 + torch.exp(-g))) * (n @ w["up"].T)) @ w["down"].T
+        x = norm(x, weights["norm"], cfg.final_norm.eps)
+        return x @ (weights["emb"] if cfg.tie_word_embeddings else weights["head"]).T
+
+    def random_weights(cfg):
+        layer0 = cfg.layers[0]
+        m, f, d = layer0.mixer, layer0.feed_forward, cfg.hidden_size
+        r = lambda *s_: torch.randn(*s_) * 0.02
+        layers = [dict(n1=torch.ones(d), n2=torch.ones(d), q=r(m.n_heads * m.head_dim, d),
+                       k=r(m.n_kv_heads * m.head_dim, d), v=r(m.n_kv_heads * m.head_dim, d),
+                       o=r(d, m.n_heads * m.head_dim), gate=r(f.intermediate, d),
+                       up=r(f.intermediate, d), down=r(d, f.intermediate))
+                  for _ in range(len(cfg.layers))]
+        return dict(emb=r(cfg.vocab_size, d), head=r(cfg.vocab_size, d), norm=torch.ones(d),
+                    layers=layers)
+
+    out = {}
+    for name, t, layers in (("tiny-a", 64, None), ("tiny-b", 130, None), ("120m", 128, 1)):
+        raw = shape(name)
+        if layers:
+            raw["n_layer"] = layers
+        cfg = parse_config(raw)
+        weights = random_weights(cfg)
+        tokens = [(7 * i + 3) % cfg.vocab_size for i in range(t)]
+        forward(cfg, weights, tokens)
+        reps = 5
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            forward(cfg, weights, tokens)
+        dt = (time.perf_counter() - t0) / reps
+        out[f"{name}_tokens_per_s"] = round(t / dt, 1)
+        out[f"{name}_tokens"] = t
+        out[f"{name}_layers"] = len(cfg.layers)
+    out["threads"] = torch.get_num_threads()
+    out["what"] = "plain float32 forward of a whole sequence on the CPU, no cache"
+    print(json.dumps({"impl": "cpu", "metric": "plain CPU forward, tokens/s", "dtype": "fp32",
+                      "data": "synthetic", "cpu_baseline": out}))
+    return 0
+
+
 def run_profile_case(args):
     """A small workload for a profiler (ncu): builds the 120M shape with
     `--layers` layers, fills `--batch` requests to `--context` tokens, then runs
@@ -508,7 +587,7 @@ def main():
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=256)
     p.add_argument("--warmup", type=int, default=8)
-    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--impl", default="ours", choices=["ours", "reference", "cpu"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=2048)
     p.add_argument("--shape", default="120m", choices=sorted(SHAPE_LABEL),
@@ -525,6 +604,8 @@ def main():
         return 2
     if args.impl == "reference":
         return run_reference(args)
+    if args.impl == "cpu":
+        return run_cpu_baseline(args)
     if args.warmup < 3:
         args.warmup = 3
     return run_ours(args)

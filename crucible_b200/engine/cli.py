@@ -50,7 +50,8 @@ def cmd_generate(args) -> int:
     llm = LLM(args.model, dtype=args.dtype, max_batch=args.max_batch, kv_pages=args.kv_pages,
               page_tokens=args.page_tokens, prefill_token_budget=args.prefill_token_budget,
               prefill_chunk_tokens=args.prefill_chunk_tokens,
-              max_prefill_requests=args.max_prefill_requests, graph=args.graph)
+              max_prefill_requests=args.max_prefill_requests, graph=args.graph,
+              profile=args.profile)
     vocab = llm.config.vocab_size
     if args.prompt_ids is not None:
         prompts = [_ids(p) for p in args.prompt_ids]
@@ -77,6 +78,8 @@ def cmd_generate(args) -> int:
         for s in llm.last_steps:
             print(json.dumps(s.__dict__), file=sys.stderr)
     print(f"total {dt * 1e3:.1f} ms, {len(llm.last_steps)} steps", file=sys.stderr)
+    if llm.engine.profiler is not None:
+        print(llm.engine.profiler.text(), file=sys.stderr)
     return 0
 
 
@@ -165,6 +168,9 @@ def main(argv=None) -> int:
                    help="replay decode steps from captured CUDA graphs (default)")
     g.add_argument("--no-graph", dest="graph", action="store_false")
     g.add_argument("--verbose", action="store_true", help="print every scheduler step")
+    g.add_argument("--profile", action="store_true",
+                   help="time every part of the model with CUDA events (steps run eagerly) and "
+                        "print the stage table")
     _add_engine_options(g)
     g.set_defaults(func=cmd_generate)
 

@@ -62,6 +62,7 @@ class EngineOptions:
     max_requests: int = 16                # the reference's --max-batch default (main.rs:143)
     device: str = "cuda:0"
     graph: bool = True                    # replay decode-only steps as CUDA graphs
+    profile: bool = False                 # CUDA events around every part's forward; steps run eagerly
 
 
 class Engine:
@@ -76,6 +77,11 @@ class Engine:
         self.config = load_config(model_dir)
         self.model = DecoderModel(self.config)
         load_weights(self.model, model_dir, self.dtype, self.device)
+        self.profiler = None
+        if self.options.profile:
+            from .profile import StageProfiler, attach
+            self.profiler = StageProfiler()
+            attach(self.model, self.profiler)
         self._build_storage()
 
     # -- storage ----------------------------------------------------------------
@@ -252,7 +258,9 @@ class Engine:
         ctx = self._make_context(entries, rows)
         if token_source is not None:
             ctx.token_ids.copy_(token_source[:ctx.n_tokens])
-        if self.options.graph and not self._graph_failed:
+        if self.profiler is not None:
+            self.profiler.steps += 1
+        elif self.options.graph and not self._graph_failed:
             if ctx.host.all_single_token:
                 if self.model.graph_safe:
                     return self._replay_or_capture(ctx, at_once=True)

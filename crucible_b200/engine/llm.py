@@ -3,7 +3,8 @@
 Token ids in, token ids out (the reference's tokenizer is outside this engine's
 contract).  Option names and meanings follow the reference's command line where
 it has them (`engine/src/main.rs:130-160`, `:476-497`): `max_batch`, `kv_pages`,
-`prefill_chunk_tokens`, `prefill_token_budget`, `max_prefill_requests`, `graph`.
+`prefill_chunk_tokens`, `prefill_token_budget`, `max_prefill_requests`, `graph`;
+`profile=True` attributes device time to the model's parts (`engine/profile.py`).
 """
 from __future__ import annotations
 
@@ -19,10 +20,11 @@ class LLM:
     def __init__(self, model: str, dtype: str = "bfloat16", device: str = "cuda:0",
                  max_batch: int = 16, kv_pages: Optional[int] = None, page_tokens: int = 16,
                  prefill_token_budget: int = 1024, prefill_chunk_tokens: Optional[int] = None,
-                 max_prefill_requests: Optional[int] = None, graph: bool = True):
+                 max_prefill_requests: Optional[int] = None, graph: bool = True,
+                 profile: bool = False):
         self.engine = Engine(model, EngineOptions(dtype=dtype, page_tokens=page_tokens,
                                                   n_pages=kv_pages, max_requests=max_batch,
-                                                  device=device, graph=graph))
+                                                  device=device, graph=graph, profile=profile))
         self.scheduler_options = SchedulerOptions(
             max_batch=max_batch, prefill_token_budget=prefill_token_budget,
             prefill_chunk_tokens=prefill_chunk_tokens, max_prefill_requests=max_prefill_requests)

@@ -175,14 +175,19 @@ def plain_block(x, cfg, w, layer, cos, sin):
                             w[tensor_name(cfg, "up", layer)], w[tensor_name(cfg, "down", layer)])
 
 
-def plain_forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int]) -> torch.Tensor:
-    """Logits at every position of one whole sequence: [T, vocab]
+def plain_forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int],
+                  rows: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Logits of one whole sequence: [T, vocab] at every position, or [len(rows), vocab]
+    at the positions `rows` only (the layers still run the whole sequence; only the head's
+    product is spared, which for a wide vocabulary is most of the work)
     (`model.py:342-365`; the head is the embedding when tied, `model.py:289`)."""
     dtype = w[tensor_name(cfg, "embed")].dtype
     cos, sin = plain_rope_tables(cfg["head_dim"], len(tokens), cfg["theta"], dtype)
     x = plain_embedding(w[tensor_name(cfg, "embed")], tokens)
     for layer in range(cfg["layers"]):
         x = plain_block(x, cfg, w, layer, cos, sin)
+    if rows is not None:
+        x = x[torch.tensor(list(rows), dtype=torch.long)]
     x = plain_rmsnorm(x, w[tensor_name(cfg, "final_norm")], cfg["eps"])
     head = w[tensor_name(cfg, "embed")] if cfg["tie"] else w[tensor_name(cfg, "head")]
     return x @ head.T

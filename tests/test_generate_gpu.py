@@ -37,6 +37,11 @@ def test_greedy_generation_float32_is_token_identical(tmp_path, name):
     assert got == want
     assert any(s.prefill_tokens and s.decoded for s in llm.last_steps), "no mixed step happened"
     assert not llm.engine._graph_failed
+    assert llm.engine._graph_replays > 0
+    if name == "tiny-b":
+        # portions of 24 tokens beside the same number of decoding requests come again and
+        # again: such a step is captured at its second occurrence and replayed after that
+        assert llm.engine._prompt_graph_replays > 0, "no step with a prompt portion was replayed"
     llm.engine.cache.check_invariants()
     assert not llm.engine.cache.live_requests()
     # the same without graphs and in one piece
@@ -323,3 +328,68 @@ def test_device_token_needs_a_deferred_sample(tmp_path):
     eng.step([StepEntry("b", [1, 2], [1])])                  # takes the same slot
     with pytest.raises(StepError, match="no token on the device"):
         eng.step([StepEntry("b", [DEVICE_TOKEN], [0])])
+
+
+def test_eos_and_cancel_through_the_engine(tmp_path):
+    """`eos_token_id` ends a request at the token the plain model also chooses, and a
+    request cancelled between steps gives back its pages while the others go on."""
+    from crucible_b200 import SamplingParams
+    from crucible_b200.engine.scheduler import Request, Scheduler, SchedulerOptions
+    name = "tiny-a"
+    folder = helpers.make_folder(tmp_path, name)
+    vocab = TINY[name]["config"]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, 90 + i) for i, n in enumerate([9, 30, 21])]
+    cfg, w = pm.read_folder(folder)
+    full = [pm.plain_generate(cfg, w, p, 14) for p in prompts]
+    llm = _llm(folder, "float32", name, max_batch=3, prefill_token_budget=16)
+    # the fifth token of request 0 is made its end-of-sequence token
+    eos = full[0][4]
+    cut = full[0].index(eos) + 1
+    params = [SamplingParams(max_tokens=14, eos_token_id=eos), SamplingParams(max_tokens=14),
+              SamplingParams(max_tokens=14)]
+    got = llm.generate(prompts, params)
+    assert got[0] == full[0][:cut] and got[0][-1] == eos
+    assert got[1] == full[1] and got[2] == full[2]
+    assert not llm.engine.cache.live_requests()
+    # cancel: request 1 is taken out after a few steps; the others are not disturbed
+    sched = Scheduler(llm.engine, SchedulerOptions(max_batch=3, prefill_token_budget=16))
+    for i, p in enumerate(prompts):
+        sched.submit(Request(i, p, SamplingParams(max_tokens=14)))
+    for _ in range(5):
+        sched.step()
+    free_before = llm.engine.cache.free_pages(0)
+    assert sched.cancel(1)
+    assert llm.engine.cache.free_pages(0) > free_before and not llm.engine.has_request(1)
+    done = {c.id: c for c in sched.run_to_completion()}
+    assert done[1].finish_reason == "cancelled" and done[1].tokens == full[1][:len(done[1].tokens)]
+    assert done[0].tokens == full[0] and done[2].tokens == full[2]
+    assert done[0].finish_reason == "length"
+    llm.engine.cache.check_invariants()
+    assert not llm.engine.cache.live_requests()
+
+
+def test_stage_table_attributes_a_step_to_the_parts(tmp_path):
+    """The opt-in stage table: with `profile=True` every part is timed with CUDA events,
+    steps run eagerly, the tokens are the same, and the stages are the model's parts."""
+    from crucible_b200 import SamplingParams
+    name = "tiny-b"
+    folder = helpers.make_folder(tmp_path, name)
+    vocab = TINY[name]["config"]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, 20 + i) for i, n in enumerate([40, 9])]
+    plain = _llm(folder, "float32", name, max_batch=2)
+    assert plain.engine.profiler is None
+    want = plain.generate(prompts, SamplingParams(max_tokens=6))
+    llm = _llm(folder, "float32", name, max_batch=2, profile=True)
+    assert llm.generate(prompts, SamplingParams(max_tokens=6)) == want
+    assert llm.engine._graph_replays == 0 and not llm.engine._graphs
+    rows = {r["stage"]: r for r in llm.engine.profiler.table()}
+    layers = TINY[name]["config"]["num_hidden_layers"]
+    steps = llm.engine.profiler.steps
+    assert steps == len(llm.last_steps) > 5
+    assert rows["layer.mixer[attention]"]["calls"] == steps * layers
+    assert rows["layer.feed_forward[swiglu]"]["calls"] == steps * layers
+    assert rows["layer.mixer_norm"]["calls"] == steps * layers
+    assert rows["embedding"]["calls"] == steps and rows["head"]["calls"] == steps
+    assert all(r["ms"] > 0 for r in rows.values())
+    assert abs(sum(r["share"] for r in rows.values()) - 1.0) < 1e-2
+    assert "layer.mixer[attention]" in llm.engine.profiler.text()

@@ -76,3 +76,40 @@ def test_bfloat16_follows_float32_at_the_benchmark_widths(tmp_path, which):
     assert float((ref[1] - ref[2]).abs().max() / ref[1].abs().max()) < TOLERANCE["float32"]
     worst = max(float((r - g).abs().max() / r.abs().max()) for r, g in zip(ref, got))
     assert worst < TOLERANCE["bfloat16"], worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_benchmark_widths_against_the_plain_model(tmp_path, dtype):
+    """Two layers of the 120M shape (768 wide, 12 / 4 heads of 64, feed-forward 2,048, the
+    vocabulary of 50,304) against the plain implementation itself, not against another path
+    of the engine: a prompt of 1,850 tokens in one step, which in bfloat16 reaches the
+    256 x 256 product tiles, the product with the rotation in its epilogue and the tcgen05
+    attention over 116 pages, then 40 tokens decoded one by one through the few-row products,
+    the split attention and the 50,304-row head; logits wanted at 48 places."""
+    import numpy as np
+    import plain_model as pm
+    from crucible_b200.engine import Engine, EngineOptions, StepEntry
+    from crucible_b200.ops import tensor_core
+    from crucible_b200.weights import write_random_model
+    import helpers
+    raw = _config("120m")
+    folder = write_random_model(raw, str(tmp_path / "model"), seed=3, std=0.05)
+    vocab = raw["vocab_size"]
+    tokens = helpers.random_tokens(vocab, 1890, 77)
+    prompt_places = [0, 1, 15, 16, 17, 255, 256, 511, 1023, 1024, 1848, 1849]
+    places = prompt_places + list(range(1850, 1890))[:36]
+    cfg, w = pm.read_folder(folder)
+    ref = pm.plain_forward(cfg, w, tokens, rows=places).numpy()
+    eng = Engine(folder, EngineOptions(dtype=dtype, page_tokens=16, n_pages=130, max_requests=2))
+    got = [eng.step([StepEntry("a", tokens[:1850], prompt_places)]).float().cpu().numpy()]
+    for i in range(1850, 1890):
+        row = eng.step([StepEntry("a", [tokens[i]], [0])]).float().cpu().numpy()
+        if i in places:
+            got.append(row)
+    tensor_core.check_status(eng.device)
+    got = np.concatenate(got)
+    assert got.shape == ref.shape == (48, vocab)
+    assert eng._graph_replays > 30 and not eng._graph_failed, eng._graph_error
+    for i, pos in enumerate(places):
+        err = helpers.relative_error(got[i], ref[i])
+        assert err <= TOLERANCE[dtype], f"position {pos}: relative error {err:.3g}"
