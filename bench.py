@@ -164,7 +164,7 @@ def run_ours(args):
         folder = write_random_model(raw, os.path.join(tmp, "model"), seed=0)
         max_batch = 64
         page = 16
-        need_tokens = ctx_len + args.steps + args.warmup + 64
+        need_tokens = max(ctx_len + args.steps + args.warmup + 64, cfg.max_context)
         kv_pages = max_batch * (-(-need_tokens // page)) + 64
         llm = LLM(folder, dtype="bfloat16", max_batch=max_batch, kv_pages=kv_pages,
                   page_tokens=page, prefill_token_budget=2048)
@@ -206,7 +206,7 @@ def run_ours(args):
                "tflops": round(prefill_tflops, 1)}
 
     # ---- decode through the step function -------------------------------------------
-    def decode_run(b, steps, warmup):
+    def decode_run(b, steps, warmup, ctx_len=ctx_len):
         ids = [f"d{i}" for i in range(b)]
         for rid in ids:
             engine.step([StepEntry(rid, prompt(ctx_len - 1), [])])
@@ -254,6 +254,18 @@ def run_ours(args):
         points[f"decode_b{b}"] = round(r["tok_s"], 1)
         points[f"decode_b{b}_ms"] = round(r["ms_per_step"], 4)
         points[f"decode_b{b}_frac"] = round(hbm_gbs(r, b) / peaks["hbm_gbs"], 4)
+
+    # further batches and context lengths of the same model (the hand-over between the
+    # few-row kernels and the tiles at 16 / 32 rows; short and long contexts)
+    steps_more = min(args.steps, 64)
+    for b, c in ((16, ctx_len), (32, ctx_len), (8, 512), (64, 512), (8, cfg.max_context - 320),
+                 (64, cfg.max_context - 320)):
+        if c + steps_more + args.warmup + 1 > cfg.max_context or c <= 0:
+            continue
+        r = decode_run(b, steps_more, args.warmup, ctx_len=c)
+        key = f"decode_b{b}" + ("" if c == ctx_len else f"_ctx{c}")
+        points[key + "_ms"] = round(r["ms_per_step"], 4)
+        points[key + "_frac"] = round(hbm_gbs(r, b) / peaks["hbm_gbs"], 4)
 
     # ---- a mixed step: 63 requests decoding beside one 512-token portion ----------------
     # (the decoded tokens go through the split attention kernel, the portion through the
