@@ -13,7 +13,7 @@ final rows) extended so that a decoded token is simply a portion of length one.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from functools import cached_property
+from functools import cached_property, lru_cache
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -27,18 +27,25 @@ class StepLayout:
     table_strides: Tuple[int, ...]
 
     def offsets(self) -> Dict[str, Tuple[int, int]]:
-        t, r, f = self.n_tokens, self.n_requests, self.n_logit_rows
-        out, at = {}, 0
-        for name, n in (("token_ids", t), ("positions", t), ("row_request", t),
-                        ("logit_rows", f), ("req_row_start", r + 1), ("req_context_len", r),
-                        ("req_first_pos", r), ("req_state_slot", r)):
-            out[name] = (at, n)
-            at += (n + 3) // 4 * 4            # keep every piece 16-byte aligned
-        for g, stride in enumerate(self.table_strides):
-            out[f"table{g}"] = (at, r * stride)
-            at += (r * stride + 3) // 4 * 4
-        out["_total"] = (0, at)
-        return out
+        """name -> (offset, length) in ints; the native packer (`csrc/host_step.cpp`) lays
+        a step out by the same rule."""
+        return _offsets(self)
+
+
+@lru_cache(maxsize=256)
+def _offsets(layout: "StepLayout") -> Dict[str, Tuple[int, int]]:
+    t, r, f = layout.n_tokens, layout.n_requests, layout.n_logit_rows
+    out, at = {}, 0
+    for name, n in (("token_ids", t), ("positions", t), ("row_request", t),
+                    ("logit_rows", f), ("req_row_start", r + 1), ("req_context_len", r),
+                    ("req_first_pos", r), ("req_state_slot", r)):
+        out[name] = (at, n)
+        at += (n + 3) // 4 * 4            # keep every piece 16-byte aligned
+    for g, stride in enumerate(layout.table_strides):
+        out[f"table{g}"] = (at, r * stride)
+        at += (r * stride + 3) // 4 * 4
+    out["_total"] = (0, at)
+    return out
 
 
 class CacheStorage:

@@ -13,6 +13,7 @@ are rows of one batch, and the same validation happens first.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass, field
 from typing import Hashable, List, Optional, Sequence
 
@@ -36,6 +37,23 @@ def parse_dtype(name) -> torch.dtype:
     elif name in _DTYPES:
         return _DTYPES[name]
     raise ValueError(f"dtype must be bfloat16 or float32, got {name!r}")
+
+
+class _Packer:
+    """The native step packer (`csrc/host_step.cpp`) with its constant arguments."""
+
+    def __init__(self, table_strides):
+        from ..ops import build
+        lib = build.load("host_step")
+        self.fn = lib.cb_host_pack_step
+        self.fn.restype = ctypes.c_int
+        self.fn.argtypes = ([ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 6
+                            + [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                               ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_char_p,
+                               ctypes.c_int])
+        self._strides = (ctypes.c_int32 * max(1, len(table_strides)))(*table_strides)
+        self.strides = ctypes.cast(self._strides, ctypes.c_void_p)
+        self.err = ctypes.create_string_buffer(256)
 
 
 @dataclass
@@ -127,6 +145,8 @@ class Engine:
         self._failures_seen = tensor_core.FAILURES[0]
         self._shapes_seen = {}
         self._table_rows = {}
+        self._table_ptrs = {}
+        self._packer = _Packer(self.table_strides)
 
     META_RING = 4
 
@@ -213,6 +233,7 @@ class Engine:
         self._has_device_token.discard(slot)
         for g in range(len(self.table_strides)):
             hit = self._table_rows.pop((request, g), None)
+            self._table_ptrs.pop((request, g), None)
             if hit is not None:
                 row, known = hit
                 mine = row[:known]
@@ -245,8 +266,9 @@ class Engine:
                 extended.append(e)
             # the tables that will go to the device: every page in range and no page named
             # by two requests (`engine/src/gpu_model.rs:2809-2934` refuses such a batch)
-            rows = [[self._table_row(e.request, g) for e in entries]
-                    for g in range(len(self.table_strides))]
+            rows = [self._table_row(e.request, g) for g in range(len(self.table_strides))
+                    for e in entries]
+            ctx = self._make_context(entries, rows)
         except Exception:
             # a step that cannot get its pages, or whose tables are not sound, changes nothing
             for e in extended:
@@ -255,7 +277,6 @@ class Engine:
                 self._forget(request)
                 self.cache.remove_request(request)
             raise
-        ctx = self._make_context(entries, rows)
         if token_source is not None:
             ctx.token_ids.copy_(token_source[:ctx.n_tokens])
         if self.profiler is not None:
@@ -353,7 +374,6 @@ class Engine:
         seen = set()
         new_requests = 0
         max_context = self.config.max_context
-        vocab = self.config.vocab_size
         for e in entries:
             if e.request in seen:
                 raise StepError(f"request {e.request!r} appears twice in one step")
@@ -365,10 +385,6 @@ class Engine:
                 if (not cache.has(e.request)
                         or cache.state_slot(e.request) not in self._has_device_token):
                     raise StepError(f"request {e.request!r} has no token on the device yet")
-            elif min(e.tokens) < 0 or max(e.tokens) >= vocab:
-                bad = next(t for t in e.tokens if not 0 <= t < vocab)
-                raise StepError(f"request {e.request!r}: token {bad} is outside the "
-                                f"vocabulary of {vocab}")
             if cache.has(e.request):
                 held = cache.length(e.request)
             else:
@@ -377,28 +393,17 @@ class Engine:
             if held + n > max_context:
                 raise StepError(f"request {e.request!r} would hold {held + n} tokens; the "
                                 f"model's context is {max_context}")
-            want = e.want
-            if len(want) == 1:
-                if not 0 <= int(want[0]) < n:
-                    raise StepError(f"request {e.request!r}: wanted place {want[0]} is outside "
-                                    f"its {n} tokens")
-            elif want:
-                last = -1
-                for w in want:
-                    if not 0 <= int(w) < n:
-                        raise StepError(f"request {e.request!r}: wanted place {w} is outside its "
-                                        f"{n} tokens")
-                    if int(w) <= last:
-                        raise StepError(f"request {e.request!r}: wanted places must ascend")
-                    last = int(w)
+            # token ids and wanted places are checked by the native packer, token by token,
+            # as it writes them (a failure there is rolled back like a failed allocation)
         if new_requests > cache.slots.free_slots:
             raise StepError(f"{new_requests} new requests but only "
                             f"{cache.slots.free_slots} of {self.options.max_requests} "
                             f"request slots are free")
 
-    def _table_row(self, request, group: int) -> np.ndarray:
+    def _table_row(self, request, group: int) -> int:
         """The request's block table of `group` as it goes to the device, padded to the
-        table stride: a numpy row that is only touched when the table changed.  Entries
+        table stride: a numpy row that is only touched when the table changed; returns the
+        row's address for the native packer.  Entries
         given back early name the null page.  Every page that is new to the row is
         checked: inside the pool, and not in the row of another live request."""
         table = self.cache.block_table(request, group)
@@ -409,7 +414,7 @@ class Engine:
             row = np.zeros(self.table_strides[group], dtype=np.int32)
             known = 0
         if len(table) == known and self.cache.policies[group].window is None:
-            return row
+            return self._table_ptrs[key]
         slot = self.cache.state_slot(request)
         owner = self._page_owner[group]
         if self.cache.policies[group].window is not None or len(table) < known:
@@ -439,7 +444,10 @@ class Engine:
         row[first_new:first_new + len(new)] = np.where(new == RELEASED, self.null_page, new)
         row[first_new + len(new):] = 0
         self._table_rows[key] = (row, len(table))
-        return row
+        ptr = self._table_ptrs.get(key)
+        if ptr is None:
+            ptr = self._table_ptrs[key] = row.ctypes.data       # the row object lives as long as the request
+        return ptr
 
     def check_tables(self) -> None:
         """The whole check, over every live request and not only the pages new to a step:
@@ -461,58 +469,41 @@ class Engine:
                     seen[page] = request
 
     def _make_context(self, entries: List[StepEntry], table_rows) -> StepContext:
+        """Packs the step's metadata into a pinned block (the native packer,
+        `csrc/host_step.cpp`, which also checks every token id and wanted place) and
+        sends it to the device.  `table_rows`: addresses of the requests' table rows,
+        group after group."""
         cache = self.cache
-        counts = [len(e.tokens) for e in entries]
-        n_tokens = sum(counts)
-        n_want = sum(len(e.want) for e in entries)
         n_req = len(entries)
+        counts = [len(e.tokens) for e in entries]
+        want_counts = [len(e.want) for e in entries]
+        n_tokens, n_want = sum(counts), sum(want_counts)
         layout = StepLayout(n_tokens, n_req, n_want, self.table_strides)
-        off = layout.offsets()
-        total = off["_total"][1]
+        total = layout.offsets()["_total"][1]
         host_t, dev_t = self._meta_buffers(total)
-        host = host_t.numpy()
-
-        def piece(name):
-            a, n = off[name]
-            return host[a:a + n]
-
         held_after = [cache.length(e.request) for e in entries]
         slots = [cache.state_slot(e.request) for e in entries]
         starts = [h - n for h, n in zip(held_after, counts)]
-        row_starts = [0] * (n_req + 1)
-        for r, n in enumerate(counts):
-            row_starts[r + 1] = row_starts[r] + n
-        if n_tokens == n_req:                                  # every request brings one token
-            tokens = np.fromiter((e.tokens[0] if e.tokens[0] != DEVICE_TOKEN else -(s + 1)
-                                  for e, s in zip(entries, slots)), dtype=np.int64, count=n_req)
-            piece("positions")[:] = starts
-            piece("row_request")[:] = np.arange(n_req, dtype=np.int32)
+        if n_tokens == n_req:
+            tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=n_req)
         else:
-            tokens = np.concatenate([
-                np.asarray(e.tokens if e.tokens[0] != DEVICE_TOKEN or len(e.tokens) > 1
-                           else [-(s + 1)], dtype=np.int64) for e, s in zip(entries, slots)])
-            counts_np = np.asarray(counts)
-            owner = np.repeat(np.arange(n_req, dtype=np.int32), counts_np)
-            piece("row_request")[:] = owner
-            shift = np.asarray(starts) - np.asarray(row_starts[:-1])
-            piece("positions")[:] = np.arange(n_tokens) + shift[owner]
-        piece("token_ids")[:] = tokens
-        if n_want:
-            if all(len(e.want) == 1 for e in entries):
-                piece("logit_rows")[:] = [row_starts[r] + int(e.want[0])
-                                          for r, e in enumerate(entries)]
-            else:
-                piece("logit_rows")[:] = [row_starts[r] + int(w) for r, e in enumerate(entries)
-                                          for w in e.want]
-        piece("req_row_start")[:] = row_starts
-        piece("req_context_len")[:] = held_after
-        piece("req_first_pos")[:] = starts
-        piece("req_state_slot")[:] = slots
-        for g, stride in enumerate(self.table_strides):
-            a, _ = off[f"table{g}"]
-            block = host[a:a + n_req * stride].reshape(n_req, stride)
-            for r, row in enumerate(table_rows[g]):
-                block[r] = row
+            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        if n_want == n_req and all(c == 1 for c in want_counts):
+            wants = np.fromiter((e.want[0] for e in entries), dtype=np.int32, count=n_req)
+        else:
+            wants = np.fromiter((w for e in entries for w in e.want), dtype=np.int32, count=n_want)
+        ints = np.array([counts, starts, slots, want_counts], dtype=np.int32)
+        pack = self._packer
+        n_groups = len(self.table_strides)
+        rows = (ctypes.c_void_p * max(1, n_groups * n_req))(*table_rows)
+        bad = ctypes.c_int32(-1)
+        code = pack.fn(host_t.data_ptr(), n_req, ints[0].ctypes.data, ints[1].ctypes.data,
+                       ints[2].ctypes.data, tokens.ctypes.data, ints[3].ctypes.data,
+                       wants.ctypes.data, n_groups, pack.strides, rows, self.config.vocab_size,
+                       self.config.max_context, DEVICE_TOKEN, ctypes.byref(bad), pack.err, 256)
+        if code != 0:
+            who = entries[bad.value].request if 0 <= bad.value < n_req else None
+            raise StepError(f"request {who!r}: {pack.err.value.decode()}")
         hs = HostStep([e.request for e in entries], counts, starts, held_after, slots)
         self._upload_meta(host_t, total)
         return StepContext(layout=layout, meta=dev_t, caches=self.storages, state=self.state,

@@ -30,8 +30,13 @@ _LIB_DIR = os.path.join(os.path.dirname(_HERE), "lib")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 
+# Host-only sources (C++, no device code): compiled by the same nvcc call, which hands them
+# to the host compiler.
+HOST_SOURCES = {"host_step": "host_step.cpp"}
+
 # source file -> extra headers whose change must trigger a rebuild
 MODULES: Dict[str, List[str]] = {
+    "host_step": [],
     "elementwise": ["common.cuh"],
     "gemm_simt": ["common.cuh"],
     "attention_generic": ["common.cuh"],
@@ -61,11 +66,15 @@ def _nvcc() -> str:
 def _digest(name: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
-    for fn in [name + ".cu"] + MODULES[name]:
+    for fn in [_source(name)] + MODULES[name]:
         with open(os.path.join(CSRC, fn), "rb") as f:
             h.update(fn.encode())
             h.update(f.read())
     return h.hexdigest()[:16]
+
+
+def _source(name: str) -> str:
+    return HOST_SOURCES.get(name, name + ".cu")
 
 
 def _writable_dir() -> str:
@@ -101,8 +110,8 @@ def library_path(name: str) -> str:
             except OSError:
                 pass
     tmp = os.path.join(out_dir, f".{fname}.{os.getpid()}.tmp")
-    cmd = [_nvcc()] + NVCC_FLAGS + ["-I", CSRC, "-o", tmp, os.path.join(CSRC, name + ".cu")]
-    print(f"[crucible_b200] compiling {name}.cu for sm_100a (first use) ...",
+    cmd = [_nvcc()] + NVCC_FLAGS + ["-I", CSRC, "-o", tmp, os.path.join(CSRC, _source(name))]
+    print(f"[crucible_b200] compiling {_source(name)} for sm_100a (first use) ...",
           file=sys.stderr, flush=True)
     t0 = time.time()
     env = dict(os.environ)
@@ -116,7 +125,7 @@ def library_path(name: str) -> str:
             proc.wait(timeout=5)
             break
         except subprocess.TimeoutExpired:
-            print(f"[crucible_b200] ... still compiling {name}.cu ({time.time() - t0:.0f} s)",
+            print(f"[crucible_b200] ... still compiling {_source(name)} ({time.time() - t0:.0f} s)",
                   file=sys.stderr, flush=True)
     reader.join()
     log = b"".join(out_chunks).decode(errors="replace")
@@ -125,7 +134,7 @@ def library_path(name: str) -> str:
             os.remove(tmp)
         except OSError:
             pass
-        raise BuildError(f"nvcc failed on {name}.cu:\n{log}")
+        raise BuildError(f"nvcc failed on {_source(name)}:\n{log}")
     os.replace(tmp, target)
     print(f"[crucible_b200] built {name} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
     return target
