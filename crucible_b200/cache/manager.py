@@ -154,7 +154,10 @@ class CacheManager:
     def remove_request(self, req) -> None:
         r = self._get(req)
         for g, table in enumerate(r.tables):
-            for page in table:
+            # last page first: the pool is a stack, so the next request takes these pages in
+            # the order this one held them, and runs of consecutive pages (which the attention
+            # kernels fetch with one copy per tile instead of one per page) survive reuse
+            for page in reversed(table):
                 if page != RELEASED:
                     self.pools[g].release(page)
             self._reserved[g] -= r.reserved[g]

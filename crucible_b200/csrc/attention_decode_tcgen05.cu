@@ -46,7 +46,7 @@ namespace {
 
 constexpr int KEYS = 128;            // keys per tile = tensor-memory lanes of S^T
 constexpr int ROWS = 16;             // query rows per block (N of the first MMA)
-constexpr int STAGES = 3;            // the loader's first copies are written out for three
+constexpr int MAX_STAGES = 3;        // the loader's first copies are written out for three
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RAISE = 8.0f;
 
@@ -72,7 +72,10 @@ struct DecodeParams {
 
 // HD: the head size, 64 or 128.  Operands whose contracted or free dimension is the head
 // size lie in shared memory as HD / 64 halves of [rows][128 bytes] (one swizzle atom wide).
-template <int HD>
+// STAGES: 3, or 2 for launches whose chunks are at most two tiles long (74 KB instead of 110 KB
+// for head size 64: three blocks to an SM instead of two, so that every block of a launch of a few
+// hundred finds its place while the product before it still runs).
+template <int HD, int STAGES>
 struct Storage {
     alignas(1024) uint8_t q[HD / 64][ROWS * 64 * 2];         // [16 rows][128 B] per half, swizzled
     alignas(1024) uint8_t p[2][2][ROWS * 64 * 2];            // P: two buffers of two halves of 64 keys
@@ -166,14 +169,14 @@ __device__ __forceinline__ void merge_row(const DecodeParams& p, int tok, int he
 
 // RMAX: the most packed rows a block of this instantiation takes (4, 8 or 16): the
 // softmax's per-row loops are unrolled that far and no further.
-template <int HD, int RMAX>
-__global__ void __launch_bounds__(192, HD == 64 ? 2 : 1)
+template <int HD, int RMAX, int STAGES>
+__global__ void __launch_bounds__(192, HD == 64 ? (STAGES == 2 ? 3 : 2) : 1)
 attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                                 const __grid_constant__ CUtensorMap map_v,
                                 const __grid_constant__ CUtensorMap run_k,
                                 const __grid_constant__ CUtensorMap run_v, const DecodeParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    using Store = Storage<HD>;
+    using Store = Storage<HD, STAGES>;
     constexpr int NH = HD / 64;                       // halves of the head size
     constexpr uint32_t TMEM_COLS = HD == 64 ? 128 : 256;
     Store& s = *reinterpret_cast<Store*>(smem_raw);
@@ -579,19 +582,27 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     }
 }
 
-template <int HD, int RMAX>
-int launch_as(dim3 grid, cudaStream_t st, const CUtensorMap& mk, const CUtensorMap& mv,
-              const CUtensorMap& rk, const CUtensorMap& rv, const DecodeParams& p) {
-    const int smem = (int)sizeof(Storage<HD>);
+template <int HD, int RMAX, int STAGES>
+int launch_stages(dim3 grid, cudaStream_t st, const CUtensorMap& mk, const CUtensorMap& mv,
+                  const CUtensorMap& rk, const CUtensorMap& rv, const DecodeParams& p) {
+    const int smem = (int)sizeof(Storage<HD, STAGES>);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_tcgen05_kernel<HD, RMAX>,
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_tcgen05_kernel<HD, RMAX, STAGES>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    cb_launch(attention_decode_tcgen05_kernel<HD, RMAX>, grid, dim3(192), smem, st, mk, mv, rk, rv, p);
+    cb_launch(attention_decode_tcgen05_kernel<HD, RMAX, STAGES>, grid, dim3(192), smem, st, mk, mv, rk, rv, p);
     return cb_last_error();
+}
+
+template <int HD, int RMAX>
+int launch_as(dim3 grid, cudaStream_t st, const CUtensorMap& mk, const CUtensorMap& mv,
+              const CUtensorMap& rk, const CUtensorMap& rv, const DecodeParams& p) {
+    // chunks of at most two tiles never use a third stage
+    if (HD == 64 && p.chunk_keys <= 2 * KEYS) return launch_stages<HD, RMAX, 2>(grid, st, mk, mv, rk, rv, p);
+    return launch_stages<HD, RMAX, MAX_STAGES>(grid, st, mk, mv, rk, rv, p);
 }
 
 }  // namespace

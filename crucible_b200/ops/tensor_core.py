@@ -408,6 +408,8 @@ DECODE_TC_TARGET_BLOCKS = 3 * N_SMS // 2  # two blocks of the tcgen05 decode ker
                                           # start under the q/k/v product, whose blocks each take one
                                           # block's place until they end: a launch of more than about
                                           # one and a half blocks per SM starts in two waves
+DECODE_TC_SHORT_BLOCKS = 22 * N_SMS // 10 # chunks of at most two tiles run with two K/V stages, three
+                                          # blocks to an SM: a launch of up to this many finds its place
 DECODE_MMA_TARGET_BLOCKS = 4 * N_SMS
 
 
@@ -415,18 +417,29 @@ def decode_chunk_keys(blocks_per_chunk: int, context_bucket: int, tcgen05: bool)
     """Keys per block of the split attention for decoded tokens: a function of the step's
     shape alone (so a captured step replays).  `blocks_per_chunk`: blocks that one chunk of
     every request takes (requests x KV heads x groups of 16 packed rows).  `context_bucket`:
-    the longest context rounded up to a multiple of 256.  The chunk is the bucket divided
-    into as many equal parts as bring the launch nearest to the target number of blocks
-    (the tcgen05 form does far fewer instructions per key than the mma.sync form, which
-    wants more, shorter chunks), rounded up to whole tiles of keys.  Measured on B200 at
-    2,048-token contexts, batch 4 / 8 / 32: 0.309 / 0.324 / 0.624 ms per step with this
-    rule against 0.322 / 0.331 / 0.706 ms with chunks for 296 or for 148 blocks."""
+    the longest context rounded up to a multiple of 256.
+
+    tcgen05 form, from sweeps on B200 (120M shape, batch 1 to 64, contexts of 512 to 3,700):
+    one tile of 128 keys per block while that is at most eight chunks (one round of the
+    merge) and the launch finds its place at once; else two tiles per block while the launch
+    finds its place (these short chunks run with two K/V stages, three blocks to an SM);
+    else the bucket divided into as many equal parts as bring the launch nearest to one and
+    a half blocks per SM, in whole tiles (batch 4 / 8 / 32 at 2,048 tokens: 0.307 / 0.321 /
+    0.624 ms per step against 0.322 / 0.331 / 0.706 ms with chunks for 296 or 148 blocks).
+    mma.sync form: the parts that bring the launch nearest to four blocks per SM."""
     unit = 128 if tcgen05 else 256
+    whole = -(-context_bucket // unit) * unit
+    if tcgen05:
+        n_one, n_two = -(-context_bucket // 128), -(-context_bucket // 256)
+        if n_one <= 8 and blocks_per_chunk * n_one <= DECODE_TC_SHORT_BLOCKS:
+            return min(128, whole)
+        if blocks_per_chunk * n_two <= DECODE_TC_SHORT_BLOCKS:
+            return min(256, whole)
     target = DECODE_TC_TARGET_BLOCKS if tcgen05 else DECODE_MMA_TARGET_BLOCKS
     parts = max(1, (2 * target + blocks_per_chunk) // (2 * max(1, blocks_per_chunk)))
     chunk = -(-context_bucket // parts)
     chunk = -(-chunk // unit) * unit
-    return min(max(chunk, unit), -(-context_bucket // unit) * unit)
+    return min(max(chunk, unit), whole)
 
 
 SPLIT_ROWS = 16          # packed rows (new tokens x heads of a group) the split form takes

@@ -48,15 +48,17 @@ def test_decode_chunks_cover_the_bucket_in_whole_tiles(blocks, bucket, tcgen05):
     n_chunks = -(-bucket // chunk)
     assert (n_chunks - 1) * chunk < bucket <= n_chunks * chunk     # no chunk is empty
     target = tensor_core.DECODE_TC_TARGET_BLOCKS if tcgen05 else tensor_core.DECODE_MMA_TARGET_BLOCKS
-    # never far more blocks than the target unless a chunk is already a single tile
-    assert blocks * n_chunks <= max(1.5 * target, blocks) or chunk == unit
+    # never far more blocks than fit at once unless a chunk is already a single tile
+    assert blocks * n_chunks <= max(1.5 * target, tensor_core.DECODE_TC_SHORT_BLOCKS, blocks) or chunk == unit
 
 
 def test_decode_chunks_of_the_benchmark_points():
     # 4 KV heads, contexts of 2,056 to 2,304 tokens (bucket 2,304)
-    assert tensor_core.decode_chunk_keys(1 * 4, 2304, True) == 128         # 18 chunks, 72 blocks
+    assert tensor_core.decode_chunk_keys(1 * 4, 2304, True) == 256         # 9 chunks, 36 blocks
     assert tensor_core.decode_chunk_keys(4 * 4, 2304, True) == 256         # 9 chunks, 144 blocks
-    assert tensor_core.decode_chunk_keys(8 * 4, 2304, True) == 384         # 6 chunks, 192 blocks
+    assert tensor_core.decode_chunk_keys(8 * 4, 2304, True) == 256         # 9 chunks, 288 blocks, three to an SM
+    assert tensor_core.decode_chunk_keys(8 * 4, 768, True) == 128          # short contexts: a tile per block
+    assert tensor_core.decode_chunk_keys(8 * 4, 3840, True) == 640         # 480 blocks of two tiles would not fit
     assert tensor_core.decode_chunk_keys(16 * 4, 2304, True) == 768        # 3 chunks, 192 blocks
     assert tensor_core.decode_chunk_keys(32 * 4, 2304, True) == 1152       # 2 chunks, 256 blocks
     assert tensor_core.decode_chunk_keys(64 * 4, 2304, True) == 2304       # a block per request and KV head
