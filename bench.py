@@ -316,10 +316,10 @@ def run_ours(args):
     h2d = 0
     if decode_steps:
         from crucible_b200.engine.context import StepLayout
-        # the step's metadata block, and the sampler's row of state slots (greedy requests
-        # upload nothing else); back come the chosen ids and the status word behind them
+        # the step's metadata block (greedy requests upload nothing else: the sampler's row of
+        # state slots goes up only when it changes); back come the chosen ids and the status
+        # word behind them
         h2d = StepLayout(batch, batch, batch, engine.table_strides).offsets()["_total"][1] * 4
-        h2d += 4 * max(batch, 64)
     e2e = {"value": round(e2e_tok_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": 4 * (batch + 1), "steps": len(decode_steps)}
 

@@ -88,8 +88,15 @@ class Sampler:
         greedy = all(p.is_greedy for p, _ in rows)
         upload = not greedy or slots is not None
         scatter_index = None
+        slots_fresh = False
         if slots is not None:
-            host[3, :n] = np.asarray(slots, dtype=np.int32).view(np.float32)
+            # the slots of a running batch rarely change from step to step: each ring entry
+            # remembers what its device copy holds and uploads the row only when it differs
+            key = tuple(slots)
+            slots_fresh = buf.get("slots") != key
+            if slots_fresh:
+                host[3, :n] = np.asarray(slots, dtype=np.int32).view(np.float32)
+                buf["slots"] = key
             scatter_index = buf["dev"][3, :n].view(torch.int32)
         max_k = 1
         if not greedy:
@@ -105,8 +112,9 @@ class Sampler:
         if upload:
             # one copy of whole rows of the parameter block (a slice [:, :n] is strided, and a
             # strided host-to-device copy goes through a staging buffer and a copy kernel)
-            first, last = (3, 4) if greedy else (0, 4 if slots is not None else 3)
-            buf["dev"][first:last].copy_(buf["host"][first:last], non_blocking=True)
+            first, last = (3, 4) if greedy else (0, 4 if slots_fresh else 3)
+            if not greedy or slots_fresh:
+                buf["dev"][first:last].copy_(buf["host"][first:last], non_blocking=True)
         out = scatter_out if slots is not None else None
         if greedy:
             ops.argmax_rows(logits, ids, scatter_index, out, status=status)
