@@ -120,20 +120,26 @@ class ClockSampler:
 
 
 def model_numbers(cfg):
-    layer = cfg.layers[0]
-    m, f = layer.mixer, layer.feed_forward
-    d, L, V = cfg.hidden_size, len(cfg.run_order), cfg.vocab_size
-    per_layer = (d * m.n_heads * m.head_dim + 2 * d * m.n_kv_heads * m.head_dim
-                 + m.n_heads * m.head_dim * d + 3 * d * f.intermediate)
-    head = V * d
-    kv_token_bytes = 2 * m.n_kv_heads * m.head_dim * L * 2
-    return dict(per_layer=per_layer, head=head, layers=L, kv_token_bytes=kv_token_bytes,
-                q_width=m.n_heads * m.head_dim)
+    """Matrix elements and cache bytes of the model as its run order says: every entry of
+    the run order counts with its own layer's sizes (layers may differ, run twice, or read
+    another layer's cache, in which case they keep none of their own)."""
+    d, V = cfg.hidden_size, cfg.vocab_size
+    weights = attn_width = kv_token_bytes = 0
+    for entry in cfg.run_order:
+        layer = cfg.layers[entry.layer]
+        m, f = layer.mixer, layer.feed_forward
+        weights += (d * m.n_heads * m.head_dim + 2 * d * m.n_kv_heads * m.head_dim
+                    + m.n_heads * m.head_dim * d + 3 * d * f.intermediate)
+        attn_width += m.n_heads * m.head_dim
+        if entry.cache_of is None:
+            kv_token_bytes += 2 * m.n_kv_heads * m.head_dim * 2
+    return dict(layer_weights=weights, head=V * d, layers=len(cfg.run_order),
+                kv_token_bytes=kv_token_bytes, attn_width=attn_width)
 
 
 def prefill_flops(nums, t):
-    gemm = 2 * t * nums["layers"] * nums["per_layer"] + 2 * nums["head"]
-    attn = nums["layers"] * 2 * 2 * nums["q_width"] * t * (t + 1) // 2
+    gemm = 2 * t * nums["layer_weights"] + 2 * nums["head"]
+    attn = 2 * 2 * nums["attn_width"] * t * (t + 1) // 2
     return gemm + attn
 
 
@@ -240,7 +246,7 @@ def run_ours(args):
         return dict(tok_s=b * steps / (ms / 1e3), ms_per_step=ms / steps, launches=launches,
                     mean_ctx=mean_ctx)
 
-    weight_bytes = (nums["layers"] * nums["per_layer"] + nums["head"]) * 2
+    weight_bytes = (nums["layer_weights"] + nums["head"]) * 2
 
     def hbm_gbs(r, b):
         """Bytes a decode step has to read (every weight once, the live requests' cache
