@@ -20,7 +20,8 @@ from typing import Hashable, List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..cache import CacheManager, GroupPolicy, RELEASED
+from ..cache import CacheManager, GroupPolicy
+from ..cache import pages as cache_codes
 from ..config.registry import load_config
 from ..models.decoder import DecoderModel
 from ..weights.loader import load_weights
@@ -111,9 +112,6 @@ class Engine:
         ctx_pages = -(-self.config.max_context // o.page_tokens)
         n_pages = o.n_pages if o.n_pages is not None else o.max_requests * ctx_pages
         groups = self.model.cache_groups
-        self.cache = CacheManager(
-            [GroupPolicy(o.page_tokens, g.need.window) for g in groups],
-            [n_pages] * len(groups), o.max_requests)
         # One page more than the pool hands out: the null page, never written, all zeros.
         # A table entry whose page the window has passed and given back names it, so a
         # kernel that loads whole tiles of keys reads zeros there (every such key is masked)
@@ -121,11 +119,17 @@ class Engine:
         self.storages = [CacheStorage(len(g.layers), n_pages + 1, o.page_tokens, g.need.kv_heads,
                                       g.need.head_dim, self.dtype, self.device) for g in groups]
         self.null_page = n_pages
-        # which live request (by state slot) each page belongs to, as the tables that went to
-        # the device say: the check that no two requests of a step name the same page
-        self._page_owner = [np.full(n_pages, -1, dtype=np.int32) for _ in groups]
-        self._has_device_token = set()      # state slots whose latest token is on the device
         self.table_strides = tuple(ctx_pages for _ in groups)
+        # The manager keeps every live request's table in the form that goes to the device
+        # (a row of the table stride at a fixed address) and its own ledger of which request
+        # names which page: a step whose growth would let two requests name one page is
+        # refused before anything is written (`engine/src/gpu_model.rs:2809-2934` refuses
+        # such a batch).
+        self.cache = CacheManager(
+            [GroupPolicy(o.page_tokens, g.need.window) for g in groups],
+            [n_pages] * len(groups), o.max_requests, table_strides=self.table_strides,
+            null_pages=[self.null_page] * len(groups))
+        self._has_device_token = set()      # state slots whose latest token is on the device
         self.state = None
         if self.model.state_bytes:
             self.state = torch.zeros((o.max_requests, self.model.state_bytes),
@@ -144,8 +148,6 @@ class Engine:
         from ..ops import tensor_core
         self._failures_seen = tensor_core.FAILURES[0]
         self._shapes_seen = {}
-        self._table_rows = {}
-        self._table_ptrs = {}
         self._packer = _Packer(self.table_strides)
 
     META_RING = 4
@@ -229,17 +231,7 @@ class Engine:
 
     def _forget(self, request) -> None:
         """Drops what the engine itself remembers of a request that is about to go."""
-        slot = self.cache.state_slot(request)
-        self._has_device_token.discard(slot)
-        for g in range(len(self.table_strides)):
-            hit = self._table_rows.pop((request, g), None)
-            self._table_ptrs.pop((request, g), None)
-            if hit is not None:
-                row, known = hit
-                mine = row[:known]
-                mine = mine[mine != self.null_page]
-                owner = self._page_owner[g]
-                owner[mine[owner[mine] == slot]] = -1
+        self._has_device_token.discard(self.cache.state_slot(request))
 
     def held_tokens(self, request) -> int:
         return self.cache.length(request)
@@ -256,26 +248,38 @@ class Engine:
         then placeholders and are not validated against it)."""
         entries = list(entries)
         self._validate(entries)
-        extended, added = [], []
+        cache = self.cache
+        n_req = len(entries)
+        added, grown, ints = [], False, None
         try:
             for e in entries:
-                if not self.cache.has(e.request):
+                if not cache.has(e.request):
                     self.add_request(e.request)
                     added.append(e.request)
-                self.cache.extend(e.request, len(e.tokens))
-                extended.append(e)
-            # the tables that will go to the device: every page in range and no page named
-            # by two requests (`engine/src/gpu_model.rs:2809-2934` refuses such a batch)
-            rows = [self._table_row(e.request, g) for g in range(len(self.table_strides))
-                    for e in entries]
-            ctx = self._make_context(entries, rows)
+            counts = [len(e.tokens) for e in entries]
+            # rows: token counts, first positions (filled by the manager), slots, wanted counts
+            ints = np.array([counts, counts, [cache.state_slot(e.request) for e in entries],
+                             [len(e.want) for e in entries]], dtype=np.int32)
+            rows = (ctypes.c_void_p * max(1, len(self.table_strides) * n_req))()
+            # every request's pages for this step, or nobody's; the tables that will go to
+            # the device come back as the addresses of the manager's rows
+            code = cache.step_raw(n_req, ints[2].ctypes.data, ints[0].ctypes.data,
+                                  self.config.max_context, ints[1].ctypes.data, rows)
+            if code:
+                who = entries[cache.failed_entry()].request
+                if code in (cache_codes.TOO_LONG, cache_codes.ALIASED):
+                    raise StepError(f"request {who!r}: {cache._message()}")
+                cache.raise_for(code, who)
+            grown = True
+            ctx = self._make_context(entries, ints, rows)
         except Exception:
-            # a step that cannot get its pages, or whose tables are not sound, changes nothing
-            for e in extended:
-                self._shrink(e.request, len(e.tokens))
+            # a step that cannot get its pages, or whose tables or tokens are not sound,
+            # changes nothing
+            if grown:
+                cache.unstep_raw(n_req, ints[2].ctypes.data, ints[0].ctypes.data)
             for request in added:
                 self._forget(request)
-                self.cache.remove_request(request)
+                cache.remove_request(request)
             raise
         if token_source is not None:
             ctx.token_ids.copy_(token_source[:ctx.n_tokens])
@@ -352,28 +356,16 @@ class Engine:
             self._graph_error = repr(e)
         return logits
 
-    def _shrink(self, request, n: int) -> None:
-        r = self.cache._get(request)
-        r.length -= n
-        for g, pool in enumerate(self.cache.pools):
-            needed = -(-r.length // pool.page_tokens)
-            while len(r.tables[g]) > needed:
-                page = r.tables[g].pop()
-                pool.release(page)
-                if 0 <= page < pool.n_pages and self._page_owner[g][page] == r.slot:
-                    self._page_owner[g][page] = -1
-            hit = self._table_rows.get((request, g))
-            if hit is not None and hit[1] > needed:
-                hit[0][needed:] = 0
-                self._table_rows[(request, g)] = (hit[0], needed)
-
     def _validate(self, entries: List[StepEntry]) -> None:
+        """What can be said of a step before the cache is asked.  The rest is checked
+        natively as the step is built, and a failure there is rolled back like a failed
+        allocation: a context too long by the cache manager as it grows the request, token
+        ids and wanted places by the packer as it writes them."""
         if not entries:
             raise StepError("a step needs at least one entry")
         cache = self.cache
         seen = set()
         new_requests = 0
-        max_context = self.config.max_context
         for e in entries:
             if e.request in seen:
                 raise StepError(f"request {e.request!r} appears twice in one step")
@@ -381,109 +373,43 @@ class Engine:
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"request {e.request!r} brings no tokens")
+            known = cache.has(e.request)
             if n == 1 and e.tokens[0] == DEVICE_TOKEN:
-                if (not cache.has(e.request)
-                        or cache.state_slot(e.request) not in self._has_device_token):
+                if not known or cache.state_slot(e.request) not in self._has_device_token:
                     raise StepError(f"request {e.request!r} has no token on the device yet")
-            if cache.has(e.request):
-                held = cache.length(e.request)
-            else:
-                held = 0
+            if not known:
                 new_requests += 1
-            if held + n > max_context:
-                raise StepError(f"request {e.request!r} would hold {held + n} tokens; the "
-                                f"model's context is {max_context}")
-            # token ids and wanted places are checked by the native packer, token by token,
-            # as it writes them (a failure there is rolled back like a failed allocation)
-        if new_requests > cache.slots.free_slots:
+                if n > self.config.max_context:
+                    raise StepError(f"request {e.request!r} would hold {n} tokens; the "
+                                    f"model's context is {self.config.max_context}")
+        if new_requests and new_requests > cache.slots.free_slots:
             raise StepError(f"{new_requests} new requests but only "
                             f"{cache.slots.free_slots} of {self.options.max_requests} "
                             f"request slots are free")
 
-    def _table_row(self, request, group: int) -> int:
-        """The request's block table of `group` as it goes to the device, padded to the
-        table stride: a numpy row that is only touched when the table changed; returns the
-        row's address for the native packer.  Entries
-        given back early name the null page.  Every page that is new to the row is
-        checked: inside the pool, and not in the row of another live request."""
-        table = self.cache.block_table(request, group)
-        key = (request, group)
-        row, known = self._table_rows.get(key, (None, 0))
-        n_pages = self.cache.pools[group].n_pages
-        if row is None:
-            row = np.zeros(self.table_strides[group], dtype=np.int32)
-            known = 0
-        if len(table) == known and self.cache.policies[group].window is None:
-            return self._table_ptrs[key]
-        slot = self.cache.state_slot(request)
-        owner = self._page_owner[group]
-        if self.cache.policies[group].window is not None or len(table) < known:
-            # early releases rewrite entries: take the whole table again
-            new = np.asarray(table, dtype=np.int64)
-            old = row[:known]
-            gone = old[:min(known, len(new))][new[:known] == RELEASED]
-            gone = np.concatenate([gone, old[len(new):]]) if len(new) < known else gone
-            gone = gone[gone != self.null_page]
-            owner[gone[owner[gone] == slot]] = -1
-            first_new = 0
-        else:
-            new = np.asarray(table[known:], dtype=np.int64)
-            first_new = known
-        live = new[new != RELEASED]
-        if live.size and (live.min() < 0 or live.max() >= n_pages):
-            bad = int(live[(live < 0) | (live >= n_pages)][0])
-            raise StepError(f"page {bad} of request {request!r} is out of range")
-        theirs = owner[live]
-        clash = (theirs != -1) & (theirs != slot)
-        if clash.any() or np.unique(live).size != live.size:
-            page = int(live[clash][0]) if clash.any() else int(live[0])
-            raise StepError(f"page {page} of cache group {group} is named by request "
-                            f"{request!r} and by another live request (or twice): two "
-                            f"requests would write the same keys")
-        owner[live] = slot
-        row[first_new:first_new + len(new)] = np.where(new == RELEASED, self.null_page, new)
-        row[first_new + len(new):] = 0
-        self._table_rows[key] = (row, len(table))
-        ptr = self._table_ptrs.get(key)
-        if ptr is None:
-            ptr = self._table_ptrs[key] = row.ctypes.data       # the row object lives as long as the request
-        return ptr
-
     def check_tables(self) -> None:
         """The whole check, over every live request and not only the pages new to a step:
-        no page of a cache group is named by two requests, or twice by one.  The step
-        itself checks incrementally (`_table_row`); this is for tests and for a host that
-        suspects its cache manager."""
-        for g, pool in enumerate(self.cache.pools):
-            seen = {}
-            for request in self.cache.live_requests():
-                for page in self.cache.block_table(request, g):
-                    if page == RELEASED:
-                        continue
-                    if not 0 <= page < pool.n_pages:
-                        raise StepError(f"page {page} of request {request!r} is out of range")
-                    if page in seen:
-                        raise StepError(f"page {page} of cache group {g} is named by request "
-                                        f"{request!r} and by another live request (or twice): "
-                                        f"{seen[page]!r}")
-                    seen[page] = request
+        no page of a cache group is named by two requests, or twice by one.  Growth checks
+        the pages it adds; this is for tests and for a host that suspects its allocator."""
+        from ..cache import CacheError
+        try:
+            self.cache.check_tables()
+        except CacheError as e:
+            raise StepError(str(e)) from None
 
-    def _make_context(self, entries: List[StepEntry], table_rows) -> StepContext:
+    def _make_context(self, entries: List[StepEntry], ints: np.ndarray, rows) -> StepContext:
         """Packs the step's metadata into a pinned block (the native packer,
         `csrc/host_step.cpp`, which also checks every token id and wanted place) and
-        sends it to the device.  `table_rows`: addresses of the requests' table rows,
-        group after group."""
-        cache = self.cache
+        sends it to the device.  `ints`: int32 rows of token counts, first positions, state
+        slots and wanted counts, one column per entry; `rows`: addresses of the requests'
+        table rows, group after group."""
         n_req = len(entries)
-        counts = [len(e.tokens) for e in entries]
-        want_counts = [len(e.want) for e in entries]
+        counts, starts, slots, want_counts = ints.tolist()
         n_tokens, n_want = sum(counts), sum(want_counts)
         layout = StepLayout(n_tokens, n_req, n_want, self.table_strides)
         total = layout.offsets()["_total"][1]
         host_t, dev_t = self._meta_buffers(total)
-        held_after = [cache.length(e.request) for e in entries]
-        slots = [cache.state_slot(e.request) for e in entries]
-        starts = [h - n for h, n in zip(held_after, counts)]
+        held_after = [s + n for s, n in zip(starts, counts)]
         if n_tokens == n_req:
             tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=n_req)
         else:
@@ -492,10 +418,8 @@ class Engine:
             wants = np.fromiter((e.want[0] for e in entries), dtype=np.int32, count=n_req)
         else:
             wants = np.fromiter((w for e in entries for w in e.want), dtype=np.int32, count=n_want)
-        ints = np.array([counts, starts, slots, want_counts], dtype=np.int32)
         pack = self._packer
         n_groups = len(self.table_strides)
-        rows = (ctypes.c_void_p * max(1, n_groups * n_req))(*table_rows)
         bad = ctypes.c_int32(-1)
         code = pack.fn(host_t.data_ptr(), n_req, ints[0].ctypes.data, ints[1].ctypes.data,
                        ints[2].ctypes.data, tokens.ctypes.data, ints[3].ctypes.data,

@@ -32,11 +32,12 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", 
 
 # Host-only sources (C++, no device code): compiled by the same nvcc call, which hands them
 # to the host compiler.
-HOST_SOURCES = {"host_step": "host_step.cpp"}
+HOST_SOURCES = {"host_step": "host_step.cpp", "host_cache": "host_cache.cpp"}
 
 # source file -> extra headers whose change must trigger a rebuild
 MODULES: Dict[str, List[str]] = {
     "host_step": [],
+    "host_cache": [],
     "elementwise": ["common.cuh"],
     "gemm_simt": ["common.cuh"],
     "attention_generic": ["common.cuh"],

@@ -289,13 +289,14 @@ def test_step_refuses_a_page_named_by_two_requests(tmp_path):
     before = eng.step([StepEntry("a", tokens[:20], [19])]).clone()
     held = eng.cache.block_table("a", 0)[0]
     pool = eng.cache.pools[0]
-    pool._free.append(held)                       # the fault: a held page looks free
+    free_before = pool.free_pages
+    pool.release(held)                            # the fault: a held page looks free
     with pytest.raises(StepError, match="another live request"):
         eng.step([StepEntry("b", tokens[:5], [4])])
     assert not eng.has_request("b")
-    assert pool._free[-1] == held                 # rolled back to where the fault left it
-    pool._free.pop()                              # undo the fault
-    pool._in_use[held] = True
+    # rolled back to where the fault left it: the same page is the next one handed out
+    assert pool.free_pages == free_before + 1 and not pool.is_in_use(held)
+    assert pool.alloc() == held                   # undo the fault
     eng.cache.check_invariants()
     # request a is untouched: the same logits as a run that never saw the fault
     again = Engine(folder, EngineOptions(dtype="float32", n_pages=8, max_requests=3))
@@ -305,7 +306,7 @@ def test_step_refuses_a_page_named_by_two_requests(tmp_path):
     assert torch.equal(got, want) and torch.equal(before, before)
     # a table entry changed behind the engine's back is found by the full check
     eng.step([StepEntry("c", tokens[:5], [])])
-    eng.cache.block_table("c", 0)[0] = eng.cache.block_table("a", 0)[1]
+    eng.cache._poke("c", 0, 0, eng.cache.block_table("a", 0)[1])
     with pytest.raises(StepError, match="another live request"):
         eng.check_tables()
 
