@@ -116,8 +116,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     __syncthreads();
     tc::tc_fence_after_sync();
     const uint32_t tmem_acc = s.tmem_base;
-    auto load_w = [&](int kb) {
-        const int st = kb % STAGES;
+    auto load_w = [&](int kb, int st) {
         if (EPI == SWIGLU_BF16) {
             const int half = BN / 2;
             tc::tma_load_2d(s.b[st], &map_w, &s.full_bar[st], (kb_first + kb) * BK, n_tile * half);
@@ -134,7 +133,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     if (warp == 0 && lane == 0) {
         for (int kb = 0; kb < w_ahead; ++kb) {
             tc::mbar_expect_tx(&s.full_bar[kb], STAGE_BYTES);
-            load_w(kb);
+            load_w(kb, kb);
         }
     }
     cb_pdl_wait();
@@ -143,23 +142,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     if (warp == 0) {
         // ---- producer: one thread feeds the ring of stages -------------------
         if (lane == 0) {
-            int armed = w_ahead;
+            // (sending a box costs this thread about 180 cycles whatever the box's size, so
+            // the loop around it carries the stage and its parity along instead of dividing)
+            int armed = w_ahead, st = 0;
+            uint32_t parity = 1;                // of the stage's last round, once there was one
             for (int kb = 0; kb < k_blocks; ++kb) {
-                const int st = kb % STAGES;
-                const uint32_t round = kb / STAGES;
-                if (round > 0 && !tc::mbar_wait(&s.empty_bar[st], (round - 1) & 1, abort_flag)) {
+                if (kb >= STAGES && !tc::mbar_wait(&s.empty_bar[st], parity, abort_flag)) {
                     tc::give_up(abort_flag, status, tc::ST_PRODUCER_TIMEOUT);
                     break;
                 }
                 if (kb >= w_ahead) {
                     tc::mbar_expect_tx(&s.full_bar[st], STAGE_BYTES);
-                    load_w(kb);
+                    load_w(kb, st);
                 }
 #pragma unroll
                 for (int mh = 0; mh < MH; ++mh)
                     tc::tma_load_2d(s.a[st] + mh * (BM * BK * 2), &map_a, &s.full_bar[st], (kb_first + kb) * BK,
                                     m0 + mh * BM);
                 if (kb + 1 > armed) armed = kb + 1;
+                if (++st == STAGES) st = 0, parity ^= 1;
             }
             if (*abort_flag) {
                 // let our own copies land before the block's shared memory goes away
@@ -178,29 +179,50 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         }
     } else if (warp == 1) {
         // ---- MMA issuer --------------------------------------------------------
+        // One thread, and for tiles up to 128 columns wide its own instructions are what a
+        // step of K takes: sending a tcgen05.mma costs the thread about 54 cycles (the tensor
+        // cores need 32 to 64 for 64 to 128 columns), a commit about 60, and every dependent
+        // integer instruction of a lone thread about 5.  So the ring is walked by an unrolled
+        // loop: a stage's barriers and operand descriptors are constants away from those of
+        // stage 0 (the descriptor's low word carries the address in 16-byte units, its high
+        // word is the same for every tile), and only the first MMA of the first stage asks
+        // whether it accumulates.
         if (lane == 0) {
             constexpr uint32_t idesc = tc::instr_desc_bf16(BM, BN);
+            constexpr uint32_t A_STEP = sizeof(s.a[0]) >> 4, B_STEP = sizeof(s.b[0]) >> 4;
+            constexpr uint32_t A_HALF = (BM * BK * 2) >> 4;
+            const uint64_t desc0 = tc::smem_desc_sw128(tc::smem_u32(s.a[0]));
+            const uint32_t desc_hi = (uint32_t)(desc0 >> 32);
+            const uint32_t a_lo = (uint32_t)desc0;
+            const uint32_t b_lo = (uint32_t)tc::smem_desc_sw128(tc::smem_u32(s.b[0]));
+            const uint32_t full0 = tc::smem_u32(&s.full_bar[0]), empty0 = tc::smem_u32(&s.empty_bar[0]);
             bool ok = true;
-            for (int kb = 0; kb < k_blocks && ok; ++kb) {
-                const int st = kb % STAGES;
-                if (!tc::mbar_wait(&s.full_bar[st], (kb / STAGES) & 1, abort_flag)) {
-                    tc::give_up(abort_flag, status, tc::ST_MMA_TIMEOUT);
-                    ok = false;
-                    break;
-                }
-                tc::tc_fence_after_sync();
-                const uint64_t b_desc = tc::smem_desc_sw128(tc::smem_u32(s.b[st]));
+            uint32_t phase = 0;
+            for (int kb0 = 0; kb0 < k_blocks && ok; kb0 += STAGES, phase ^= 1) {
 #pragma unroll
-                for (int mh = 0; mh < MH; ++mh) {
-                    const uint64_t a_desc = tc::smem_desc_sw128(tc::smem_u32(s.a[st] + mh * (BM * BK * 2)));
-#pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // advancing 16 elements along K = 32 bytes = 2 descriptor units
-                        tc::umma_bf16(tmem_acc + mh * BN, a_desc + 2 * k, b_desc + 2 * k, idesc,
-                                      (kb > 0 || k > 0) ? 1u : 0u);
+                for (int st = 0; st < STAGES; ++st) {
+                    if (kb0 + st >= k_blocks) break;
+                    if (!tc::mbar_wait_at(full0 + 8 * st, phase, abort_flag)) {
+                        tc::give_up(abort_flag, status, tc::ST_MMA_TIMEOUT);
+                        ok = false;
+                        break;
                     }
+                    tc::tc_fence_after_sync();
+#pragma unroll
+                    for (int mh = 0; mh < MH; ++mh) {
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            // advancing 16 elements along K = 32 bytes = 2 descriptor units
+                            const uint64_t a_desc = tc::desc_of(a_lo + st * A_STEP + mh * A_HALF + 2 * k, desc_hi);
+                            const uint64_t b_desc = tc::desc_of(b_lo + st * B_STEP + 2 * k, desc_hi);
+                            if (st == 0 && k == 0)
+                                tc::umma_bf16(tmem_acc + mh * BN, a_desc, b_desc, idesc, kb0 > 0 ? 1u : 0u);
+                            else
+                                tc::umma_bf16_add(tmem_acc + mh * BN, a_desc, b_desc, idesc);
+                        }
+                    }
+                    tc::umma_commit_at(empty0 + 8 * st);     // stage free once these MMAs are done
                 }
-                tc::umma_commit(&s.empty_bar[st]);      // stage free once these MMAs are done
             }
             if (ok) tc::umma_commit(&s.tmem_full_bar);   // accumulator complete
         }

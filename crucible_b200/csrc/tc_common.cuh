@@ -71,6 +71,29 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     return false;
 }
 
+// The same on a barrier given by its shared-memory address (for loops that reach a
+// stage's barrier as a constant offset from the first).
+__device__ __forceinline__ bool mbar_try_wait_at(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ bool mbar_wait_at(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                             uint32_t limit = WAIT_LIMIT) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_try_wait_at(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    return false;
+}
+
 __device__ __forceinline__ void give_up(volatile int* abort_flag, int* status, int code) {
     *abort_flag = 1;
     if (status) atomicCAS(status, 0, code);
@@ -168,11 +191,37 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
         : "memory");
 }
 
+// The same, always accumulating: no predicate to compute.
+__device__ __forceinline__ void umma_bf16_add(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                              uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.eq.b32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc)
+        : "memory");
+}
+
+// An operand descriptor from its two words: the low one carries the tile's address (in
+// 16-byte units, so a tile 16 * n bytes further is the low word + n, as long as the sum
+// stays below the 14 bits of the field, which every shared-memory address does), the high
+// one is the same for all tiles of one layout.
+__device__ __forceinline__ uint64_t desc_of(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
+
 // The mbarrier gets one arrival when every MMA issued so far by this thread has
 // finished (its reads of shared memory and writes of tensor memory included).
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                      smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void umma_commit_at(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                  : "memory");
 }
 
