@@ -59,7 +59,7 @@ struct DecodeParams {
     const int* req_first_pos;
     const int* block_table;
     int table_stride;
-    int n_heads, n_kv_heads, n_requests, page_shift;
+    int n_heads, n_kv_heads, n_rep, n_requests, page_shift;
     float scale_log2;
     int window;
     float* partial;          // [rows_total * n_heads][n_chunks][head size + 2]
@@ -181,14 +181,13 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     constexpr uint32_t TMEM_COLS = HD == 64 ? 128 : 256;
     Store& s = *reinterpret_cast<Store*>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int chunk = blockIdx.x % p.n_chunks;
-    const int grp = blockIdx.x / p.n_chunks;
-    const int kv_head = grp % p.n_kv_heads;
-    const int req = grp / p.n_kv_heads;
+    // grid (chunks, KV heads, requests): a division by a run-time value costs a thread about
+    // a hundred cycles, and a late block's way to its first copy is on the step's critical path
+    const int chunk = blockIdx.x, kv_head = blockIdx.y, req = blockIdx.z;
     volatile int* abort_flag = &s.abort_flag;
 
     // ---- which keys: everything below is uniform over the block -------------------------
-    const int n_rep = p.n_heads / p.n_kv_heads;
+    const int n_rep = p.n_rep;
     const int row_base = p.req_row_start[req];
     const int n_new = p.req_row_start[req + 1] - row_base;
     const int n_rows = n_new * n_rep;                               // <= 16 (the host checked)
@@ -355,27 +354,44 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         if (lane == 0) {
             constexpr uint32_t idesc_qk = tc::instr_desc_bf16(KEYS, ROWS);
             constexpr uint32_t idesc_pv = tc::instr_desc_bf16_b_mn(128, 64);
+            // Operand descriptors by addition: the low word carries the address in 16-byte
+            // units, the high word is the same for every tile (this thread's own instructions
+            // are what the tensor cores wait for here: nothing is built per MMA from pointers).
+            const uint64_t q_desc0 = tc::smem_desc_sw128(tc::smem_u32(s.q[0]));
+            const uint32_t desc_hi = (uint32_t)(q_desc0 >> 32);
+            const uint32_t q_lo = (uint32_t)q_desc0;
+            const uint32_t k_lo0 = (uint32_t)tc::smem_desc_sw128(tc::smem_u32(s.k[0][0]));
+            const uint32_t v_lo0 = (uint32_t)tc::smem_desc_sw128(tc::smem_u32(s.v[0][0]));
+            const uint32_t p_lo0 = (uint32_t)tc::smem_desc_sw128(tc::smem_u32(s.p[0][0]));
+            constexpr uint32_t Q_HALF = sizeof(s.q[0]) >> 4, KV_HALF = sizeof(s.k[0][0]) >> 4,
+                               KV_STAGE = sizeof(s.k[0]) >> 4, P_HALF = sizeof(s.p[0][0]) >> 4,
+                               P_BUF = sizeof(s.p[0]) >> 4;
             bool ok = true;
             // S^T_j = K_j Q^T into buffer j & 1: K = 64 in four steps of 16
             // `block`: wait for the tile; else only take it if it has landed (true: issued)
+            int qk_st = 0;                        // stage and parity of the next tile of scores
+            uint32_t qk_parity = 0;
             auto issue_qk = [&](int j, bool block) -> bool {
-                const int st = j % STAGES;
                 if (block) {
-                    if (!tc::mbar_wait(&s.kv_full[st], (j / STAGES) & 1, abort_flag)) return false;
-                } else if (!tc::mbar_try_wait(&s.kv_full[st], (j / STAGES) & 1)) {
+                    if (!tc::mbar_wait(&s.kv_full[qk_st], qk_parity, abort_flag)) return false;
+                } else if (!tc::mbar_try_wait(&s.kv_full[qk_st], qk_parity)) {
                     return false;
                 }
                 tc::tc_fence_after_sync();
+                const uint32_t k_lo = k_lo0 + qk_st * KV_STAGE;
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
-                    const uint64_t k_desc = tc::smem_desc_sw128(tc::smem_u32(s.k[st][k >> 2])) + 2 * (k & 3);
-                    const uint64_t q_desc = tc::smem_desc_sw128(tc::smem_u32(s.q[k >> 2])) + 2 * (k & 3);
-                    tc::umma_bf16(tmem_s + (j & 1) * 16, k_desc, q_desc, idesc_qk, k > 0 ? 1u : 0u);
+                    const uint64_t k_desc = tc::desc_of(k_lo + (k >> 2) * KV_HALF + 2 * (k & 3), desc_hi);
+                    const uint64_t q_desc = tc::desc_of(q_lo + (k >> 2) * Q_HALF + 2 * (k & 3), desc_hi);
+                    if (k == 0) tc::umma_bf16(tmem_s + (j & 1) * 16, k_desc, q_desc, idesc_qk, 0u);
+                    else tc::umma_bf16_add(tmem_s + (j & 1) * 16, k_desc, q_desc, idesc_qk);
                 }
                 tc::umma_commit(&s.s_full[j & 1]);
+                if (++qk_st == STAGES) qk_st = 0, qk_parity ^= 1;
                 return true;
             };
             ok = issue_qk(0, true);
+            int st = 0;                           // stage of tile j
             for (int j = 0; j < n_tiles && ok; ++j) {
                 // the next tile's scores first if its keys have landed (their buffer was last
                 // read by the softmax of tile j - 1, whose P this thread has waited for);
@@ -386,20 +402,22 @@ attention_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                     break;
                 }
                 tc::tc_fence_after_sync();
-                const int st = j % STAGES;
+                const uint32_t p_lo = p_lo0 + (j & 1) * P_BUF;
 #pragma unroll
                 for (int h = 0; h < NH; ++h) {                       // 64 output features at a time
-                    const uint64_t v_desc = tc::smem_desc_sw128(tc::smem_u32(s.v[st][h]));
+                    const uint32_t v_lo = v_lo0 + st * KV_STAGE + h * KV_HALF;
 #pragma unroll
                     for (int k = 0; k < KEYS / 16; ++k) {
-                        const uint64_t p_desc =
-                            tc::smem_desc_sw128(tc::smem_u32(s.p[j & 1][k >> 2])) + 2 * (k & 3);
-                        tc::umma_bf16(tmem_o + h * 64, p_desc, v_desc + 128 * k, idesc_pv,
-                                      (j > 0 || k > 0) ? 1u : 0u);
+                        // 16 keys further in V (keys are its rows of 128 bytes): 128 units
+                        const uint64_t p_desc = tc::desc_of(p_lo + (k >> 2) * P_HALF + 2 * (k & 3), desc_hi);
+                        const uint64_t v_desc = tc::desc_of(v_lo + 128 * k, desc_hi);
+                        if (k == 0) tc::umma_bf16(tmem_o + h * 64, p_desc, v_desc, idesc_pv, j > 0 ? 1u : 0u);
+                        else tc::umma_bf16_add(tmem_o + h * 64, p_desc, v_desc, idesc_pv);
                     }
                 }
                 tc::umma_commit(&s.kv_empty[st]);
                 tc::umma_commit(&s.pv_done[j & 1]);
+                if (++st == STAGES) st = 0;
                 if (j + 1 < n_tiles && !ahead) ok = issue_qk(j + 1, true);
             }
             if (!ok) tc::give_up(abort_flag, p.status, tc::ST_MMA_TIMEOUT);
@@ -651,6 +669,7 @@ CB_EXPORT int cb_attention_decode_tcgen05(const void* qkv, int qkv_stride, void*
     p.table_stride = table_stride;
     p.n_heads = n_heads;
     p.n_kv_heads = n_kv_heads;
+    p.n_rep = n_heads / n_kv_heads;
     p.n_requests = n_requests;
     p.page_shift = shift;
     p.scale_log2 = scale * LOG2E;
@@ -661,7 +680,8 @@ CB_EXPORT int cb_attention_decode_tcgen05(const void* qkv, int qkv_stride, void*
     p.chunk_keys = chunk_keys;
     p.status = status;
     const int most_rows = max_new_tokens * (n_heads / n_kv_heads);
-    const dim3 grid(n_chunks * n_kv_heads * n_requests);
+    if (n_kv_heads > 65535 || n_requests > 65535) return CB_ERR_UNSUPPORTED;
+    const dim3 grid(n_chunks, n_kv_heads, n_requests);
     cudaStream_t st = (cudaStream_t)stream;
     if (head_dim == 64) {
         if (most_rows <= 4) return launch_as<64, 4>(grid, st, mk, mv, rk, rv, p);
