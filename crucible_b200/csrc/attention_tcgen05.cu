@@ -47,6 +47,8 @@ struct TcAttnParams {
     int n_heads, n_kv_heads, n_requests, page_tokens, page_shift;
     float scale_log2;
     int window;
+    int n_pages;             // of the pool
+    int runs;                // 1: the 4-D maps may be used for tiles whose pages are consecutive
     int* status;
 };
 
@@ -115,7 +117,9 @@ __device__ __forceinline__ void fma_pair(float& x0, float& x1, float a, float b)
 template <int HD, bool LEAN>
 __global__ void __launch_bounds__(192, LEAN ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
-                         const __grid_constant__ CUtensorMap map_v, const TcAttnParams p) {
+                         const __grid_constant__ CUtensorMap map_v,
+                         const __grid_constant__ CUtensorMap run_k,
+                         const __grid_constant__ CUtensorMap run_v, const TcAttnParams p) {
     // 1024-byte alignment (the swizzled tiles need it) is asked of the declaration
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     using Store = Storage<HD, LEAN>;
@@ -145,6 +149,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&map_k);
         tc::prefetch_tensormap(&map_v);
+        if (p.runs) {
+            tc::prefetch_tensormap(&run_k);
+            tc::prefetch_tensormap(&run_v);
+        }
     }
     if (warp == 1) {
         tc::tmem_alloc(&s.tmem_base, TMEM_COLS);
@@ -179,28 +187,42 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         // the tile's table entries first, all in flight at once: the copies below
         // are ordered against memory and would take the lookups one by one
         const int key0 = key_lo + j * KEYS;
-        int rows_y[16];
+        int pages[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             int index = (key0 >> p.page_shift) + (i < pages_per_tile ? i : 0);
             index = index < p.table_stride ? index : p.table_stride - 1;
-            int page = table[index];
-            page = page < 0 ? 0 : page;               // an entry given back early: never read
-            rows_y[i] = (page * p.n_kv_heads + kv_head) << p.page_shift;
+            const int page = table[index];
+            pages[i] = page < 0 ? 0 : page;           // an entry given back early: never read
         }
+        // pages that follow one another in the pool come in with one copy per tile and operand
+        // (sending a copy costs this thread about 180 cycles whatever the copy's size)
+        bool run = p.runs != 0 && pages[0] + pages_per_tile <= p.n_pages;
+#pragma unroll
+        for (int i = 1; i < 16; ++i)
+            if (i < pages_per_tile && pages[i] != pages[0] + i) run = false;
         if (round > 0 && !tc::mbar_wait(&s.kv_empty[st], (round - 1) & 1, abort_flag)) {
             tc::give_up(abort_flag, p.status, tc::ST_PRODUCER_TIMEOUT);
             return false;
         }
         tc::mbar_expect_tx(&s.kv_full[st], 2 * KEYS * HD * 2);
+        if (run) {
+#pragma unroll
+            for (int h = 0; h < NH; ++h) {
+                tc::tma_load_4d(s.k[st][h], &run_k, &s.kv_full[st], h * 64, 0, kv_head, pages[0]);
+                tc::tma_load_4d(s.v[st][h], &run_v, &s.kv_full[st], h * 64, 0, kv_head, pages[0]);
+            }
+            return true;
+        }
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             if (i < pages_per_tile) {
                 const int dst = (i << p.page_shift) * 128;
+                const int y = (pages[i] * p.n_kv_heads + kv_head) << p.page_shift;
 #pragma unroll
                 for (int h = 0; h < NH; ++h) {
-                    tc::tma_load_2d(s.k[st][h] + dst, &map_k, &s.kv_full[st], h * 64, rows_y[i]);
-                    tc::tma_load_2d(s.v[st][h] + dst, &map_v, &s.kv_full[st], h * 64, rows_y[i]);
+                    tc::tma_load_2d(s.k[st][h] + dst, &map_k, &s.kv_full[st], h * 64, y);
+                    tc::tma_load_2d(s.v[st][h] + dst, &map_v, &s.kv_full[st], h * 64, y);
                 }
             }
         }
@@ -256,31 +278,50 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         if (lane == 0 && n_tiles > 0) {
             constexpr uint32_t idesc_qk = tc::instr_desc_bf16(ROWS, KEYS);
             constexpr uint32_t idesc_pv = tc::instr_desc_bf16_b_mn(ROWS, 64);
+            // Operand descriptors by addition: the low word carries the address in 16-byte
+            // units, the high word is the same for every tile; stages and parities are carried
+            // along.  This thread's own instructions are what a tile's MMAs take (sending one
+            // costs 54 cycles, a dependent integer instruction about 5).
+            const uint64_t q_desc0 = tc::smem_desc_sw128(tc::smem_u32(s.q[0]));
+            const uint32_t desc_hi = (uint32_t)(q_desc0 >> 32);
+            const uint32_t q_lo = (uint32_t)q_desc0;
+            const uint32_t k_lo0 = (uint32_t)tc::smem_desc_sw128(tc::smem_u32(s.k[0][0]));
+            const uint32_t v_lo0 = (uint32_t)tc::smem_desc_sw128(tc::smem_u32(s.v[0][0]));
+            const uint32_t p_lo0 = (uint32_t)tc::smem_desc_sw128(tc::smem_u32(s.p[0][0]));
+            constexpr uint32_t Q_HALF = sizeof(s.q[0]) >> 4, KV_HALF = sizeof(s.k[0][0]) >> 4,
+                               KV_STAGE = sizeof(s.k[0]) >> 4, P_HALF = sizeof(s.p[0][0]) >> 4,
+                               P_BUF = sizeof(s.p[0]) >> 4;
             bool ok = true;
-            // S_j = Q K_j^T into buffer j & 1: the head size in steps of 16.  `block`: wait for
-            // the tile; else only take it if it has landed (true: issued)
+            // S_j = Q K_j^T into buffer j % S_BUFS: the head size in steps of 16.  `block`: wait
+            // for the tile; else only take it if it has landed (true: issued)
+            int qk_st = 0;                        // stage and parity of the next tile of scores
+            uint32_t qk_parity = 0;
             auto issue_qk = [&](int j, bool block) -> bool {
-                const int st = j % STAGES;
                 // one buffer of scores: the softmax of tile j - 1 must have them in registers
                 const bool hand_back = S_BUFS == 1 && j > 0;
                 if (block) {
-                    if (!tc::mbar_wait(&s.kv_full[st], (j / STAGES) & 1, abort_flag)) return false;
+                    if (!tc::mbar_wait(&s.kv_full[qk_st], qk_parity, abort_flag)) return false;
                     if (hand_back && !tc::mbar_wait(&s.s_free, (j - 1) & 1, abort_flag)) return false;
-                } else if (!tc::mbar_try_wait(&s.kv_full[st], (j / STAGES) & 1) ||
+                } else if (!tc::mbar_try_wait(&s.kv_full[qk_st], qk_parity) ||
                            (hand_back && !tc::mbar_try_wait(&s.s_free, (j - 1) & 1))) {
                     return false;
                 }
                 tc::tc_fence_after_sync();
+                const uint32_t k_lo = k_lo0 + qk_st * KV_STAGE;
+                const uint32_t d_s = tmem_s + (j % S_BUFS) * 128;
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
-                    const uint64_t q_desc = tc::smem_desc_sw128(tc::smem_u32(s.q[k >> 2])) + 2 * (k & 3);
-                    const uint64_t k_desc = tc::smem_desc_sw128(tc::smem_u32(s.k[st][k >> 2])) + 2 * (k & 3);
-                    tc::umma_bf16(tmem_s + (j % S_BUFS) * 128, q_desc, k_desc, idesc_qk, k > 0 ? 1u : 0u);
+                    const uint64_t q_desc = tc::desc_of(q_lo + (k >> 2) * Q_HALF + 2 * (k & 3), desc_hi);
+                    const uint64_t k_desc = tc::desc_of(k_lo + (k >> 2) * KV_HALF + 2 * (k & 3), desc_hi);
+                    if (k == 0) tc::umma_bf16(d_s, q_desc, k_desc, idesc_qk, 0u);
+                    else tc::umma_bf16_add(d_s, q_desc, k_desc, idesc_qk);
                 }
                 tc::umma_commit(&s.s_full[j % S_BUFS]);
+                if (++qk_st == STAGES) qk_st = 0, qk_parity ^= 1;
                 return true;
             };
             ok = issue_qk(0, true);
+            int st = 0;                           // stage of tile j
             for (int j = 0; j < n_tiles && ok; ++j) {
                 // the next tile's scores go out first if its keys have landed (their buffer was
                 // last read by the softmax of tile j - 1, whose P this thread has waited for);
@@ -302,21 +343,22 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                     break;
                 }
                 tc::tc_fence_after_sync();
-                const int st = j % STAGES;
+                const uint32_t p_lo = p_lo0 + pb * P_BUF;
 #pragma unroll
                 for (int h = 0; h < NH; ++h) {
-                    const uint64_t v_desc = tc::smem_desc_sw128(tc::smem_u32(s.v[st][h]));
+                    const uint32_t v_lo = v_lo0 + st * KV_STAGE + h * KV_HALF;
 #pragma unroll
                     for (int k = 0; k < KEYS / 16; ++k) {
-                        const uint64_t p_desc =
-                            tc::smem_desc_sw128(tc::smem_u32(s.p[pb][k >> 2])) + 2 * (k & 3);
                         // 16 keys further down V: 16 rows of 128 bytes = 128 descriptor units
-                        tc::umma_bf16(tmem_o + h * 64, p_desc, v_desc + 128 * k, idesc_pv,
-                                      (j > 0 || k > 0) ? 1u : 0u);
+                        const uint64_t p_desc = tc::desc_of(p_lo + (k >> 2) * P_HALF + 2 * (k & 3), desc_hi);
+                        const uint64_t v_desc = tc::desc_of(v_lo + 128 * k, desc_hi);
+                        if (k == 0) tc::umma_bf16(tmem_o + h * 64, p_desc, v_desc, idesc_pv, j > 0 ? 1u : 0u);
+                        else tc::umma_bf16_add(tmem_o + h * 64, p_desc, v_desc, idesc_pv);
                     }
                 }
                 tc::umma_commit(&s.kv_empty[st]);
                 tc::umma_commit(&s.pv_done[pb]);
+                if (++st == STAGES) st = 0;
                 if (j + 1 < n_tiles && !ahead) ok = issue_qk(j + 1, true);
             }
             if (!ok) tc::give_up(abort_flag, p.status, tc::ST_MMA_TIMEOUT);
@@ -405,9 +447,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                 tc::tc_fence_before_sync();
             }
             l *= corr;
-            // P's buffer was last read by the second MMA of tile j - PB
-            if (j >= PB) {
-                ok = wait_all(&s.pv_done[pb], ((j - PB) / PB) & 1);
+            // P's buffer was last read by the second MMA of tile j - PB.  With two buffers
+            // that MMA was sent before this tile's first one, and the commit that announced
+            // this tile's scores covers everything its thread had sent by then: nothing to
+            // wait for (a barrier test costs a warp 100 to 200 cycles even when it passes).
+            if (PB == 1 && j >= 1) {
+                ok = wait_all(&s.pv_done[pb], (j - 1) & 1);
                 if (!ok) break;
             }
             // P = exp2(s * scale - reference), to shared memory in the layout the second MMA
@@ -482,7 +527,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
 
 template <int HD, bool LEAN>
 int launch_as(dim3 grid, cudaStream_t st, const CUtensorMap& mk, const CUtensorMap& mv,
-              const TcAttnParams& p) {
+              const CUtensorMap& rk, const CUtensorMap& rv, const TcAttnParams& p) {
     const int smem = (int)sizeof(Storage<HD, LEAN>);
     static bool configured = false;
     if (!configured) {
@@ -491,7 +536,7 @@ int launch_as(dim3 grid, cudaStream_t st, const CUtensorMap& mk, const CUtensorM
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    cb_launch(attention_tcgen05_kernel<HD, LEAN>, grid, dim3(192), smem, st, mk, mv, p);
+    cb_launch(attention_tcgen05_kernel<HD, LEAN>, grid, dim3(192), smem, st, mk, mv, rk, rv, p);
     return cb_last_error();
 }
 
@@ -518,7 +563,15 @@ CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, i
     const uint64_t rows = (uint64_t)n_pages * n_kv_heads * page_tokens;
     if (!tc::make_map_2d(&mk, k_cache, rows, head_dim, head_dim, page_tokens)) return CB_ERR_UNSUPPORTED;
     if (!tc::make_map_2d(&mv, v_cache, rows, head_dim, head_dim, page_tokens)) return CB_ERR_UNSUPPORTED;
+    // tiles of several pages: a second pair of maps that takes a run of pages at once
+    CUtensorMap rk = mk, rv = mv;
+    const int pages_per_tile = KEYS / page_tokens;
+    const bool runs = pages_per_tile > 1 &&
+                      tc::make_map_pages(&rk, k_cache, n_pages, n_kv_heads, page_tokens, head_dim, pages_per_tile) &&
+                      tc::make_map_pages(&rv, v_cache, n_pages, n_kv_heads, page_tokens, head_dim, pages_per_tile);
     TcAttnParams p;
+    p.n_pages = n_pages;
+    p.runs = runs ? 1 : 0;
     p.qkv = (const __nv_bfloat16*)qkv;
     p.qkv_stride = qkv_stride;
     p.out = (__nv_bfloat16*)out;
@@ -550,7 +603,7 @@ CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, i
         lean = head_dim == 64 && (int)grid.x > 2 * n_sms;
     }
     if (head_dim == 64)
-        return lean ? launch_as<64, true>(grid, (cudaStream_t)stream, mk, mv, p)
-                    : launch_as<64, false>(grid, (cudaStream_t)stream, mk, mv, p);
-    return launch_as<128, false>(grid, (cudaStream_t)stream, mk, mv, p);
+        return lean ? launch_as<64, true>(grid, (cudaStream_t)stream, mk, mv, rk, rv, p)
+                    : launch_as<64, false>(grid, (cudaStream_t)stream, mk, mv, rk, rv, p);
+    return launch_as<128, false>(grid, (cudaStream_t)stream, mk, mv, rk, rv, p);
 }
