@@ -66,9 +66,14 @@ struct TcAttnParams {
 // 1.13 against 1.02 ms).  Head size 128: two stages and one P buffer (what 227 KB hold).
 template <int HD, bool LEAN>
 struct Storage {
-    static constexpr int STAGES = (HD == 64 && !LEAN) ? 3 : 2;
+    static constexpr int STAGES = (HD == 64 && !LEAN) ? 4 : 2;
     static constexpr int PB = (HD == 64 && !LEAN) ? 2 : 1;
     static constexpr int S_BUFS = LEAN ? 1 : 2;
+    // softmax groups of four warps that take the tiles in turn (tile j: group j % GROUPS), each
+    // with its own reference maximum, sum and accumulator, merged at the end
+    static constexpr int GROUPS = (HD == 64 && !LEAN) ? 2 : 1;
+    // loader, MMA thread, four softmax warps a group; two groups: a warp for a second MMA thread
+    static constexpr int THREADS = GROUPS > 1 ? 64 + 128 * GROUPS + 32 : 192;
     alignas(1024) uint8_t q[HD / 64][ROWS * 64 * 2];
     alignas(1024) uint8_t k[STAGES][HD / 64][KEYS * 64 * 2];
     alignas(1024) uint8_t v[STAGES][HD / 64][KEYS * 64 * 2];
@@ -77,6 +82,8 @@ struct Storage {
     uint64_t kv_empty[STAGES];
     uint64_t s_full[2], p_full[2], pv_done[2];
     uint64_t s_free;                                // lean form: a tile's scores are in registers
+    uint64_t s_taken[2];                            // two groups: buffer b's scores are in registers
+    float2 merge[2][ROWS];                          // two groups: a row's (reference, sum) of each
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -115,7 +122,7 @@ __device__ __forceinline__ void fma_pair(float& x0, float& x1, float a, float b)
 }
 
 template <int HD, bool LEAN>
-__global__ void __launch_bounds__(192, LEAN ? 2 : 1)
+__global__ void __launch_bounds__(Storage<HD, LEAN>::THREADS, LEAN ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v,
                          const __grid_constant__ CUtensorMap run_k,
@@ -124,6 +131,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     using Store = Storage<HD, LEAN>;
     constexpr int STAGES = Store::STAGES, PB = Store::PB, NH = HD / 64, S_BUFS = Store::S_BUFS;
+    constexpr int GROUPS = Store::GROUPS;
+    constexpr int PV_WARP = GROUPS > 1 ? 2 + 4 * GROUPS : -1;    // the second MMA thread's warp
+    static_assert(GROUPS == 1 || (PB == 2 && S_BUFS == 2 && HD == 64), "two groups: a buffer of scores, of P and an accumulator each");
     constexpr uint32_t TMEM_COLS = LEAN ? 256 : 512;     // scores: 128 columns a buffer, then O
     Store& s = *reinterpret_cast<Store*>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -145,6 +155,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             tc::mbar_init(&s.pv_done[b], 1);
         }
         tc::mbar_init(&s.s_free, 4);
+        tc::mbar_init(&s.s_taken[0], 4);
+        tc::mbar_init(&s.s_taken[1], 4);
         s.abort_flag = 0;
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&map_k);
@@ -273,8 +285,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                         if (tc::mbar_try_wait(&s.kv_full[j % STAGES], (j / STAGES) & 1)) break;
             }
         }
-    } else if (warp == 1) {
-        // ---- MMA issuer -------------------------------------------------------------------
+    } else if (warp == 1 || warp == PV_WARP) {
+        // ---- MMA issuer: one thread; with two softmax groups two, of different warps: warp 1's
+        // sends the first products (scores), the last warp's the second (P V).  Sending twelve
+        // MMAs, three commits and the barrier tests between them costs a thread some 1,200
+        // cycles a tile, and two groups want a tile every 1,400: one thread would make each
+        // product wait for the other.
         if (lane == 0 && n_tiles > 0) {
             constexpr uint32_t idesc_qk = tc::instr_desc_bf16(ROWS, KEYS);
             constexpr uint32_t idesc_pv = tc::instr_desc_bf16_b_mn(ROWS, 64);
@@ -292,20 +308,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                                KV_STAGE = sizeof(s.k[0]) >> 4, P_HALF = sizeof(s.p[0][0]) >> 4,
                                P_BUF = sizeof(s.p[0]) >> 4;
             bool ok = true;
-            // S_j = Q K_j^T into buffer j % S_BUFS: the head size in steps of 16.  `block`: wait
-            // for the tile; else only take it if it has landed (true: issued)
+            // S_j = Q K_j^T into buffer j % S_BUFS: the head size in steps of 16
             int qk_st = 0;                        // stage and parity of the next tile of scores
             uint32_t qk_parity = 0;
-            auto issue_qk = [&](int j, bool block) -> bool {
-                // one buffer of scores: the softmax of tile j - 1 must have them in registers
-                const bool hand_back = S_BUFS == 1 && j > 0;
-                if (block) {
-                    if (!tc::mbar_wait(&s.kv_full[qk_st], qk_parity, abort_flag)) return false;
-                    if (hand_back && !tc::mbar_wait(&s.s_free, (j - 1) & 1, abort_flag)) return false;
-                } else if (!tc::mbar_try_wait(&s.kv_full[qk_st], qk_parity) ||
-                           (hand_back && !tc::mbar_try_wait(&s.s_free, (j - 1) & 1))) {
-                    return false;
-                }
+            auto send_qk = [&](int j) {
                 tc::tc_fence_after_sync();
                 const uint32_t k_lo = k_lo0 + qk_st * KV_STAGE;
                 const uint32_t d_s = tmem_s + (j % S_BUFS) * 128;
@@ -318,54 +324,93 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                 }
                 tc::umma_commit(&s.s_full[j % S_BUFS]);
                 if (++qk_st == STAGES) qk_st = 0, qk_parity ^= 1;
+            };
+            // `block`: wait for the tile; else only take it if it has landed (true: issued)
+            auto issue_qk = [&](int j, bool block) -> bool {
+                // one buffer of scores: the softmax of tile j - 1 must have them in registers
+                const bool hand_back = S_BUFS == 1 && j > 0;
+                if (block) {
+                    if (!tc::mbar_wait(&s.kv_full[qk_st], qk_parity, abort_flag)) return false;
+                    if (hand_back && !tc::mbar_wait(&s.s_free, (j - 1) & 1, abort_flag)) return false;
+                } else if (!tc::mbar_try_wait(&s.kv_full[qk_st], qk_parity) ||
+                           (hand_back && !tc::mbar_try_wait(&s.s_free, (j - 1) & 1))) {
+                    return false;
+                }
+                send_qk(j);
                 return true;
             };
-            ok = issue_qk(0, true);
-            int st = 0;                           // stage of tile j
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                // the next tile's scores go out first if its keys have landed (their buffer was
-                // last read by the softmax of tile j - 1, whose P this thread has waited for);
-                // else after this tile's second product, which must not wait for a copy
-                bool ahead = j + 1 < n_tiles && issue_qk(j + 1, false);
-                // O += P_j V_j once the softmax has written P_j: 128 keys in eight steps of 16,
-                // 64 output features at a time.  With one buffer of scores the next tile's first
-                // MMA may go as soon as this tile's softmax has the scores in registers, which
-                // happens during this wait.
+            // O += P_j V_j: 128 keys in eight steps of 16, 64 output features at a time
+            int st = 0;                           // stage of the next tile's values
+            auto send_pv = [&](int j) {
                 const int pb = j % PB;
-                bool got = false;
-                for (uint32_t i = 0; i < tc::WAIT_LIMIT && !got; ++i) {
-                    got = tc::mbar_try_wait(&s.p_full[pb], (j / PB) & 1);
-                    if (S_BUFS == 1 && !got && !ahead && j + 1 < n_tiles) ahead = issue_qk(j + 1, false);
-                    if ((i & 1023u) == 1023u && *abort_flag) break;
-                }
-                if (!got) {
-                    ok = false;
-                    break;
-                }
                 tc::tc_fence_after_sync();
                 const uint32_t p_lo = p_lo0 + pb * P_BUF;
 #pragma unroll
                 for (int h = 0; h < NH; ++h) {
                     const uint32_t v_lo = v_lo0 + st * KV_STAGE + h * KV_HALF;
+                    // (two groups: head size 64, so h is 0; a group's accumulator is 64 columns on)
+                    const uint32_t d_o = tmem_o + (GROUPS > 1 ? (uint32_t)(j % GROUPS) * 64 : (uint32_t)h * 64);
 #pragma unroll
                     for (int k = 0; k < KEYS / 16; ++k) {
                         // 16 keys further down V: 16 rows of 128 bytes = 128 descriptor units
                         const uint64_t p_desc = tc::desc_of(p_lo + (k >> 2) * P_HALF + 2 * (k & 3), desc_hi);
                         const uint64_t v_desc = tc::desc_of(v_lo + 128 * k, desc_hi);
-                        if (k == 0) tc::umma_bf16(tmem_o + h * 64, p_desc, v_desc, idesc_pv, j > 0 ? 1u : 0u);
-                        else tc::umma_bf16_add(tmem_o + h * 64, p_desc, v_desc, idesc_pv);
+                        if (k == 0) tc::umma_bf16(d_o, p_desc, v_desc, idesc_pv, j >= GROUPS ? 1u : 0u);
+                        else tc::umma_bf16_add(d_o, p_desc, v_desc, idesc_pv);
                     }
                 }
                 tc::umma_commit(&s.kv_empty[st]);
                 tc::umma_commit(&s.pv_done[pb]);
                 if (++st == STAGES) st = 0;
-                if (j + 1 < n_tiles && !ahead) ok = issue_qk(j + 1, true);
+            };
+            if (GROUPS > 1) {
+                // Two groups of softmax warps take the tiles in turn, so two tiles are in work
+                // at a time.  A tile's first product goes out as soon as its keys have landed
+                // and the scores that its buffer held (two tiles earlier) are in registers; its
+                // second once its P is written.
+                if (warp == 1) {
+                    for (int j = 0; j < n_tiles && ok; ++j) {
+                        ok = tc::mbar_wait(&s.kv_full[qk_st], qk_parity, abort_flag) &&
+                             (j < 2 || tc::mbar_wait(&s.s_taken[j & 1], ((j - 2) >> 1) & 1, abort_flag));
+                        if (ok) send_qk(j);
+                    }
+                } else {
+                    for (int j = 0; j < n_tiles && ok; ++j) {
+                        ok = tc::mbar_wait(&s.p_full[j & 1], (j >> 1) & 1, abort_flag);
+                        if (ok) send_pv(j);
+                    }
+                }
+            } else {
+                ok = issue_qk(0, true);
+                for (int j = 0; j < n_tiles && ok; ++j) {
+                    // the next tile's scores go out first if its keys have landed (their buffer
+                    // was last read by the softmax of tile j - 1, whose P this thread has waited
+                    // for); else after this tile's second product, which must not wait for a copy
+                    bool ahead = j + 1 < n_tiles && issue_qk(j + 1, false);
+                    // With one buffer of scores the next tile's first MMA may go as soon as this
+                    // tile's softmax has the scores in registers, which happens during this wait.
+                    bool got = false;
+                    for (uint32_t i = 0; i < tc::WAIT_LIMIT && !got; ++i) {
+                        got = tc::mbar_try_wait(&s.p_full[j % PB], (j / PB) & 1);
+                        if (S_BUFS == 1 && !got && !ahead && j + 1 < n_tiles) ahead = issue_qk(j + 1, false);
+                        if ((i & 1023u) == 1023u && *abort_flag) break;
+                    }
+                    if (!got) {
+                        ok = false;
+                        break;
+                    }
+                    send_pv(j);
+                    if (j + 1 < n_tiles && !ahead) ok = issue_qk(j + 1, true);
+                }
             }
             if (!ok) tc::give_up(abort_flag, p.status, tc::ST_MMA_TIMEOUT);
         }
-    } else {
-        // ---- softmax: warps 2..5, one thread per row = tensor-memory lane -------------------
+    } else if (warp < 2 + 4 * GROUPS) {
+        // ---- softmax: warps 2..5 (and 6..9: the second group), one thread per row =
+        // tensor-memory lane; a group takes every GROUPS-th tile -------------------------------
         const int quarter = warp & 3;
+        const int group = GROUPS > 1 ? (warp - 2) >> 2 : 0;
+        const uint32_t tmem_mine = tmem_o + (uint32_t)group * 64;
         const int r = quarter * 32 + lane;
         const int row = qt * ROWS + r;
         const bool real = active && row < n_rows;
@@ -381,7 +426,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             if (!got && !*abort_flag) tc::give_up(abort_flag, p.status, tc::ST_EPILOGUE_TIMEOUT);
             return __all_sync(0xffffffffu, got);
         };
-        for (int j = 0; j < n_tiles && ok; ++j) {
+        for (int j = group; j < n_tiles && ok; j += GROUPS) {
             const int key0 = key_lo + j * KEYS;
             const int b = j % S_BUFS;                 // the scores' buffer
             const int pb = j % PB;                    // P's buffer
@@ -395,9 +440,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             for (int c = 0; c < 4; ++c) tc::tmem_ld_32x32(tmem_s + b * 128 + lane_bits + c * 32, sv[c]);
             tc::tmem_ld_wait();
             tc::tc_fence_before_sync();
-            if (S_BUFS == 1) {                        // the buffer may take the next tile's scores
+            if (S_BUFS == 1 || GROUPS > 1) {          // the buffer may take the next tile's scores
                 __syncwarp();
-                if (lane == 0) tc::mbar_arrive(&s.s_free);
+                if (lane == 0) tc::mbar_arrive(GROUPS > 1 ? &s.s_taken[b] : &s.s_free);
             }
             // keys of this tile the row may read: [first, last] relative to key0.  Most tiles
             // lie wholly inside every row's range and skip the test.
@@ -430,29 +475,30 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                 corr = m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx);
                 m_ref = mx;
             }
-            if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-                ok = wait_all(&s.pv_done[(j - 1) % PB], ((j - 1) / PB) & 1);
+            if (j >= GROUPS && __any_sync(0xffffffffu, corr != 1.0f)) {
+                ok = wait_all(&s.pv_done[(j - GROUPS) % PB], ((j - GROUPS) / PB) & 1);
                 if (!ok) break;
                 tc::tc_fence_after_sync();
 #pragma unroll 1
                 for (int c0 = 0; c0 < HD; c0 += 32) {
                     uint32_t v[32];
-                    tc::tmem_ld_32x32(tmem_o + lane_bits + c0, v);
+                    tc::tmem_ld_32x32(tmem_mine + lane_bits + c0, v);
                     tc::tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-                    tc::tmem_st_32x32(tmem_o + lane_bits + c0, v);
+                    tc::tmem_st_32x32(tmem_mine + lane_bits + c0, v);
                 }
                 tc::tmem_st_wait();
                 tc::tc_fence_before_sync();
             }
             l *= corr;
-            // P's buffer was last read by the second MMA of tile j - PB.  With two buffers
-            // that MMA was sent before this tile's first one, and the commit that announced
-            // this tile's scores covers everything its thread had sent by then: nothing to
-            // wait for (a barrier test costs a warp 100 to 200 cycles even when it passes).
-            if (PB == 1 && j >= 1) {
-                ok = wait_all(&s.pv_done[pb], (j - 1) & 1);
+            // P's buffer was last read by the second MMA of tile j - PB.  With two buffers and
+            // one group that MMA was sent before this tile's first one, and the commit that
+            // announced this tile's scores covers everything its thread had sent by then:
+            // nothing to wait for (a barrier test costs a warp 100 to 200 cycles even when it
+            // passes).  With two groups this tile's first MMA may have gone out earlier.
+            if ((PB == 1 || GROUPS > 1) && j >= PB) {
+                ok = wait_all(&s.pv_done[pb], ((j - PB) / PB) & 1);
                 if (!ok) break;
             }
             // P = exp2(s * scale - reference), to shared memory in the layout the second MMA
@@ -489,15 +535,61 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             if (lane == 0) tc::mbar_arrive(&s.p_full[pb]);
         }
         // ---- the output: O / l ------------------------------------------------------------
-        if (ok && n_tiles > 0) ok = wait_all(&s.pv_done[(n_tiles - 1) % PB], ((n_tiles - 1) / PB) & 1);
-        if (ok && n_tiles > 0) {
+        // the group's last tile
+        const int my_tiles = n_tiles > group ? (n_tiles - group + GROUPS - 1) / GROUPS : 0;
+        const int j_last = group + (my_tiles - 1) * GROUPS;
+        if (ok && my_tiles > 0) ok = wait_all(&s.pv_done[j_last % PB], (j_last / PB) & 1);
+        __nv_bfloat16* dst = nullptr;
+        if (real) {
+            const int tok = row_base + row / n_rep, head = kv_head * n_rep + row % n_rep;
+            dst = p.out + (size_t)tok * p.out_stride + (size_t)head * HD;
+        }
+        if (GROUPS > 1) {
+            // Two groups: each holds the sums over its own tiles against its own reference.
+            // A row's two states meet in shared memory; every thread comes to the barrier,
+            // whatever happened to its waits.  Then group g writes features [32 g, 32 g + 32).
+            s.merge[group][r] = make_float2(my_tiles > 0 ? m_ref : -INFINITY, my_tiles > 0 ? l : 0.f);
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (ok && n_tiles > 0 && !*abort_flag) {
+                tc::tc_fence_after_sync();
+                const float2 other = s.merge[group ^ 1][r];
+                const float m_mine = my_tiles > 0 ? m_ref : -INFINITY;
+                const float m_all = fmaxf(m_mine, other.x);
+                const float f_mine = m_mine == -INFINITY ? 0.f : exp2f(m_mine - m_all);
+                const float f_other = other.x == -INFINITY ? 0.f : exp2f(other.x - m_all);
+                const float l_all = (my_tiles > 0 ? l : 0.f) * f_mine + other.y * f_other;
+                const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+                const float w_mine = f_mine * inv, w_other = f_other * inv;
+                const int c0 = group * 32;
+                uint32_t a[32], b[32];
+                // An accumulator that no MMA has written holds whatever was there and is not
+                // read.  Whether a group had tiles is the same for every thread of the block,
+                // as it must be: the loads are the whole warp's (.sync.aligned).  A row that
+                // could read none of a group's keys has weight 0 and finite sums (zeros) there.
+                const bool mine_any = my_tiles > 0, other_any = n_tiles > my_tiles;
+                if (mine_any) tc::tmem_ld_32x32(tmem_mine + lane_bits + c0, a);
+                if (other_any) tc::tmem_ld_32x32(tmem_o + (uint32_t)(group ^ 1) * 64 + lane_bits + c0, b);
+                tc::tmem_ld_wait();
+                if (real) {
+                    float o[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        o[i] = (mine_any ? __uint_as_float(a[i]) * w_mine : 0.f) +
+                               (other_any ? __uint_as_float(b[i]) * w_other : 0.f);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 w;
+                        w.x = pack_bf16(o[8 * q4 + 0], o[8 * q4 + 1]);
+                        w.y = pack_bf16(o[8 * q4 + 2], o[8 * q4 + 3]);
+                        w.z = pack_bf16(o[8 * q4 + 4], o[8 * q4 + 5]);
+                        w.w = pack_bf16(o[8 * q4 + 6], o[8 * q4 + 7]);
+                        *reinterpret_cast<uint4*>(dst + c0 + 8 * q4) = w;
+                    }
+                }
+            }
+        } else if (ok && n_tiles > 0) {
             tc::tc_fence_after_sync();
             const float inv = l > 0.f ? 1.0f / l : 0.f;
-            __nv_bfloat16* dst = nullptr;
-            if (real) {
-                const int tok = row_base + row / n_rep, head = kv_head * n_rep + row % n_rep;
-                dst = p.out + (size_t)tok * p.out_stride + (size_t)head * HD;
-            }
 #pragma unroll 1
             for (int c0 = 0; c0 < HD; c0 += 32) {
                 uint32_t v[32];
@@ -536,7 +628,8 @@ int launch_as(dim3 grid, cudaStream_t st, const CUtensorMap& mk, const CUtensorM
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    cb_launch(attention_tcgen05_kernel<HD, LEAN>, grid, dim3(192), smem, st, mk, mv, rk, rv, p);
+    cb_launch(attention_tcgen05_kernel<HD, LEAN>, grid, dim3(Storage<HD, LEAN>::THREADS), smem, st, mk, mv, rk,
+              rv, p);
     return cb_last_error();
 }
 
