@@ -7,11 +7,21 @@
 // A block takes 128 query rows of one request and one KV head; rows are
 // (position, head within the group) pairs, so every query head that shares the
 // KV head uses the same K and V tiles.  It walks the keys in tiles of 128.
-// Roles: warp 0 loads (one thread: block-table lookups, one TMA box per page),
+// Roles: warp 0 loads (one thread: block-table lookups, then one TMA box per tile and
+// operand where the tile's pages follow one another in the pool, else one per page),
 // warp 1 owns tensor memory and issues the MMAs, warps 2-5 are the softmax.
 // S and P are double-buffered: while the softmax works on tile j, the first MMA
 // of tile j+1 and the second MMA of tile j-1 run, so a block's time per tile is
-// the softmax's alone.
+// the softmax's alone (about 2,000 cycles: 1,260 for the 128 exponentials per thread,
+// their sums and P's way to shared memory, in which the special-function unit's 560 and
+// the other pipes' instructions add up instead of overlapping; the rest maxima, barrier
+// tests of 100 to 200 cycles each, and the scores' way out of tensor memory).
+// Head size 64 with an SM to the block: two such groups of four softmax warps take the
+// tiles in turn (tile j: group j % 2), each with its own buffer of scores and of P, its own
+// reference maximum, sum and accumulator, merged when the keys are through; two tiles are
+// then in work at a time (one group's exponentials beside the other's maxima and waits:
+// 1,750 cycles a tile), and a second thread, of a warp of its own, sends the second products,
+// since one thread cannot send both products of two tiles in time (1,200 cycles a tile).
 //
 // Running maximum: a row keeps a reference maximum that is only raised when the
 // tile's maximum exceeds it by more than 2^8 (in the base-2 exponent), so P
@@ -54,8 +64,9 @@ struct TcAttnParams {
 
 // HD: the head size, 64 or 128.  Operands whose contracted or free dimension is the head
 // size lie in shared memory as HD / 64 halves of [rows][128 bytes] (one swizzle atom wide).
-// Head size 64 has two forms.  The roomy one: three K/V stages, two P buffers, two buffers of
-// scores, an SM to itself (176 KB, all 512 columns of tensor memory); it is the quicker block,
+// Head size 64 has two forms.  The roomy one: four K/V stages, two P buffers, two buffers of
+// scores, two softmax groups, an SM to itself (210 KB, 384 columns of tensor memory: with two
+// tiles in work a tile's keys are asked for three tiles ahead); it is the quicker block,
 // and the right one while all blocks of a launch find a place at once.  The lean one: two
 // stages, one P buffer, one buffer of scores (112 KB, 256 columns), so that two blocks share
 // an SM and one's waits (for a copy, an MMA, the scores' way out of tensor memory) are filled
