@@ -72,9 +72,10 @@ struct TcAttnParams {
 // an SM and one's waits (for a copy, an MMA, the scores' way out of tensor memory) are filled
 // by the other's exponentials; its one buffer of scores is handed back to the MMA thread as
 // soon as the softmax has the scores in registers, so the next tile's first MMA still runs
-// beside this tile's softmax.  It is the right one when the launch has more blocks than places
-// (measured on B200: 4,096-token prompt of the 120M shape 1.84 against 2.01 ms, 2,048 tokens
-// 1.13 against 1.02 ms).  Head size 128: two stages and one P buffer (what 227 KB hold).
+// beside this tile's softmax.  It was the right one for launches with more blocks than places
+// while the roomy form had one softmax group (4,096-token prompt of the 120M shape 1.84 against
+// 2.01 ms); with two groups the roomy form is quicker there too (1.68 ms) and the launcher
+// takes it unless told otherwise.  Head size 128: two stages and one P buffer (what 227 KB hold).
 template <int HD, bool LEAN>
 struct Storage {
     static constexpr int STAGES = (HD == 64 && !LEAN) ? 4 : 2;
@@ -695,17 +696,12 @@ CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, i
     const int n_rep = n_heads / n_kv_heads;
     const int q_tiles = (max_new_tokens * n_rep + ROWS - 1) / ROWS;
     const dim3 grid(q_tiles * n_kv_heads * n_requests);
-    // lean: -1 lets the launch decide (the lean form of head size 64 when there are more blocks
-    // than places for them: two to each of the SMs), 0 and 1 fix the form
-    if (lean < 0) {
-        static const int n_sms = [] {
-            int device = 0, n = 148;
-            if (cudaGetDevice(&device) == cudaSuccess)
-                cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
-            return n;
-        }();
-        lean = head_dim == 64 && (int)grid.x > 2 * n_sms;
-    }
+    // lean: -1 lets the launch decide, 0 and 1 fix the form.  Since the roomy form has two
+    // softmax groups it is the quicker one also for launches with more blocks than places
+    // (measured on B200: 2,048 tokens at the Llama-3.2-1B layer sizes, 512 blocks, 4.63 against
+    // 4.86 ms; 4,096 tokens of the 120M shape, 384 blocks, 1.68 against 1.96 ms), so the launch
+    // decides for it; the lean form stays for callers that ask for it.
+    if (lean < 0) lean = 0;
     if (head_dim == 64)
         return lean ? launch_as<64, true>(grid, (cudaStream_t)stream, mk, mv, rk, rv, p)
                     : launch_as<64, false>(grid, (cudaStream_t)stream, mk, mv, rk, rv, p);

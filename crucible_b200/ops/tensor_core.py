@@ -333,8 +333,8 @@ def linear_rope_append(h, wqkv, qkv, n_heads, n_kv_heads, head_dim, cos, sin, ro
     return True
 
 
-ATTENTION_LEAN = -1      # the form of the head-size-64 prompt attention: -1 by the number of
-                         # blocks (see the kernel's header), 0 roomy, 1 lean (tests fix it)
+ATTENTION_LEAN = -1      # the form of the head-size-64 prompt attention: -1 the launcher's choice
+                         # (the roomy form, see the kernel's header), 0 roomy, 1 lean (tests fix it)
 
 
 class _Requests:
