@@ -463,11 +463,16 @@ __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-// silu(g) = g / (1 + e^-g) in fp32 with the hardware's exponential and reciprocal
-// (a few ulp; the result is then rounded to bfloat16).  The IEEE division costs a
-// hundred dependent cycles per element in an epilogue whose threads have no other work.
+// silu(g) = g / (1 + e^-g) = g (1 + tanh(g / 2)) / 2 in fp32 with the hardware's tanh (relative
+// error about 2^-11; the result is then rounded to bfloat16, 2^-9).  One trip to the
+// special-function unit per element, where the exponential and the reciprocal were two, and that
+// unit is what an epilogue of 128 elements a thread waits for (a warp's `ex2` takes it 5.5
+// cycles); the IEEE division costs a hundred dependent cycles per element.
 __device__ __forceinline__ float silu_fast(float g) {
-    return __fdividef(g, 1.0f + __expf(-g));
+    float t;
+    const float h = 0.5f * g;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(h));
+    return fmaf(h, t, h);
 }
 
 }  // namespace tc
