@@ -220,7 +220,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             pages[i] = page < 0 ? 0 : page;           // an entry given back early: never read
         }
         // pages that follow one another in the pool come in with one copy per tile and operand
-        // (sending a copy costs this thread about 180 cycles whatever the copy's size)
+        // (sending a copy costs this thread about 60 cycles whatever the copy's size, and the
+        // arithmetic around it more)
         bool run = p.runs != 0 && pages[0] + pages_per_tile <= p.n_pages;
 #pragma unroll
         for (int i = 1; i < 16; ++i)

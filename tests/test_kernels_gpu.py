@@ -856,3 +856,19 @@ def test_sample_rows_matches_plain_sampler(vocab):
                         torch.tensor(us, device=DEV), max(min(k, vocab) for k in ks), out)
         want = [pm.plain_sample(logits[i].tolist(), temps[i], ks[i], plains[i]) for i in range(n)]
         assert out.tolist() == want
+
+
+def test_issue_probes_report_what_the_loops_were_shaped_by():
+    """One thread's cost of sending an MMA and a TMA box (`csrc/issue_probe.cu`): the kernels'
+    unrolled loops rest on these being tens and hundreds of cycles, whatever the tile or box."""
+    from crucible_b200.ops import issue_probe
+    narrow = issue_probe.mma_send_cycles(128, 64)
+    wide = issue_probe.mma_send_cycles(128, 256)
+    plain = issue_probe.mma_send_cycles(128, 64, tight=False)
+    assert 30 <= narrow <= 90, narrow                 # 54 measured: the thread, not the 32 of the tensor cores
+    assert 110 <= wide <= 170, wide                   # 128: the tensor cores' own time
+    assert plain >= narrow                            # descriptors and flags per MMA cost on top
+    small = issue_probe.tma_send_cycles(16)
+    big = issue_probe.tma_send_cycles(128)
+    assert 20 <= small[0] <= 300 and 20 <= big[0] <= 300, (small, big)     # 60 and 97 measured
+    assert big[1] >= big[0]
