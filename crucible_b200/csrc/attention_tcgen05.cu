@@ -54,7 +54,7 @@ struct TcAttnParams {
     const int* req_first_pos;
     const int* block_table;
     int table_stride;
-    int n_heads, n_kv_heads, n_requests, page_tokens, page_shift;
+    int n_heads, n_kv_heads, n_rep, n_requests, page_tokens, page_shift;
     float scale_log2;
     int window;
     int n_pages;             // of the pool
@@ -149,11 +149,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     constexpr uint32_t TMEM_COLS = LEAN ? 256 : 512;     // scores: 128 columns a buffer, then O
     Store& s = *reinterpret_cast<Store*>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // one index over (tile rank, request, head) with the tile rank slowest: blocks start in
-    // order of weight over the whole launch, the longest rows first
-    const int kv_head = blockIdx.x % p.n_kv_heads;
-    const int req = (blockIdx.x / p.n_kv_heads) % p.n_requests;
-    const int rank = blockIdx.x / (p.n_kv_heads * p.n_requests);
+    // grid (heads, requests, tile ranks), the tile rank slowest: blocks start in order of
+    // weight over the whole launch, the longest rows first (and no thread divides by a run-time
+    // value to find its place: that costs about a hundred cycles each time)
+    const int kv_head = blockIdx.x, req = blockIdx.y, rank = blockIdx.z;
     volatile int* abort_flag = &s.abort_flag;
 
     if (threadIdx.x == 0) {
@@ -182,9 +181,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         tc::tmem_alloc(&s.tmem_base, TMEM_COLS);
         tc::tmem_relinquish();
     }
-    cb_pdl_wait();
-
-    const int n_rep = p.n_heads / p.n_kv_heads;
+    // What follows reads the step's metadata, which was uploaded before the step began: the
+    // kernels ahead in the stream write none of it, so it is read, and the first tiles'
+    // table entries looked up, before the wait for them.
+    const int n_rep = p.n_rep;
     const int row_base = p.req_row_start[req];
     const int n_new = p.req_row_start[req + 1] - row_base;
     const int n_rows = n_new * n_rep;
@@ -205,13 +205,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
 
     // ---- the loader's thread: one tile of K and V pages into a stage --------------------------
     const int pages_per_tile = KEYS >> p.page_shift;
-    auto load_tile = [&](int j) -> bool {
-        const int st = j % STAGES;
-        const uint32_t round = j / STAGES;
-        // the tile's table entries first, all in flight at once: the copies below
-        // are ordered against memory and would take the lookups one by one
+    auto lookup = [&](int j, int (&pages)[16]) {
+        // the tile's table entries, all in flight at once: the copies are ordered against
+        // memory and would take the lookups one by one
         const int key0 = key_lo + j * KEYS;
-        int pages[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             int index = (key0 >> p.page_shift) + (i < pages_per_tile ? i : 0);
@@ -219,6 +216,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             const int page = table[index];
             pages[i] = page < 0 ? 0 : page;           // an entry given back early: never read
         }
+    };
+    auto issue = [&](int j, const int (&pages)[16]) -> bool {
+        const int st = j % STAGES;
+        const uint32_t round = j / STAGES;
         // pages that follow one another in the pool come in with one copy per tile and operand
         // (sending a copy costs this thread about 60 cycles whatever the copy's size, and the
         // arithmetic around it more)
@@ -258,9 +259,23 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     // ---- the query rows, by warps 1..5: 16-byte pieces into the 128-byte swizzle; warp 0's
     // thread meanwhile starts the first tiles' copies, which wait for nothing -----------------
     if (warp == 0) {
-        if (lane == 0)
-            for (int j = 0; j < early; ++j) load_tile(j);
-    } else if (active) {
+        if (lane == 0) {
+            // the first tiles: all their lookups before the wait, then all their copies (the
+            // keys of this step's own tokens are written by the product before this kernel)
+            int first[STAGES][16];
+#pragma unroll
+            for (int j = 0; j < STAGES; ++j)
+                if (j < early) lookup(j, first[j]);
+            cb_pdl_wait();
+#pragma unroll
+            for (int j = 0; j < STAGES; ++j)
+                if (j < early) issue(j, first[j]);
+        } else {
+            cb_pdl_wait();
+        }
+    } else {
+        cb_pdl_wait();
+        if (active)
         for (int i = threadIdx.x - 32; i < ROWS * 8 * NH; i += blockDim.x - 32) {
             const int r = i / (8 * NH), c = i % (8 * NH);         // row, 16-byte piece of the row
             const int row = qt * ROWS + r;
@@ -288,7 +303,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         if (lane == 0 && n_tiles > 0) {
             int armed = early;
             for (int j = early; j < n_tiles; ++j) {
-                if (!load_tile(j)) break;
+                int pages[16];
+                lookup(j, pages);
+                if (!issue(j, pages)) break;
                 armed = j + 1;
             }
             if (*abort_flag) {
@@ -688,6 +705,7 @@ CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, i
     p.table_stride = table_stride;
     p.n_heads = n_heads;
     p.n_kv_heads = n_kv_heads;
+    p.n_rep = n_heads / n_kv_heads;
     p.n_requests = n_requests;
     p.page_tokens = page_tokens;
     p.page_shift = shift;
@@ -696,7 +714,8 @@ CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, i
     p.status = status;
     const int n_rep = n_heads / n_kv_heads;
     const int q_tiles = (max_new_tokens * n_rep + ROWS - 1) / ROWS;
-    const dim3 grid(q_tiles * n_kv_heads * n_requests);
+    if (n_requests > 65535 || q_tiles > 65535) return CB_ERR_UNSUPPORTED;
+    const dim3 grid(n_kv_heads, n_requests, q_tiles);
     // lean: -1 lets the launch decide, 0 and 1 fix the form.  Since the roomy form has two
     // softmax groups it is the quicker one also for launches with more blocks than places
     // (measured on B200: 2,048 tokens at the Llama-3.2-1B layer sizes, 512 blocks, 4.63 against
