@@ -310,15 +310,24 @@ def run_ours(args):
                 "peaks": peaks["source"]}
 
     # ---- end to end through the Python entry point -----------------------------------
-    prompts = [prompt(ctx_len) for _ in range(batch)]
-    llm.generate(prompts[:1], SamplingParams(max_tokens=2))          # warm the path
-    w0 = time.time()
-    outs = llm.generate(prompts, SamplingParams(max_tokens=args.steps + 1))
-    windows.append((w0, time.time()))
-    decode_steps = [s for s in llm.last_steps if s.prefill_tokens == 0 and s.decoded == batch]
-    wall = sum(s.wall_s for s in decode_steps)
-    e2e_tok_s = len(decode_steps) * batch / wall if wall > 0 else 0.0
-    assert all(len(o) == args.steps + 1 for o in outs)
+    def through_generate(n_req, pure_steps):
+        """Tokens/s over the iterations in which all `n_req` requests decode and no prompt is
+        in work.  Prompts enter one per step (the token budget), so the first request has
+        decoded n_req - 1 tokens beside the others' prompts before the last one joins:
+        that many tokens more are asked for."""
+        prompts = [prompt(ctx_len) for _ in range(n_req)]
+        w0 = time.time()
+        outs = llm.generate(prompts, SamplingParams(max_tokens=pure_steps + n_req))
+        windows.append((w0, time.time()))
+        assert all(len(o) == pure_steps + n_req for o in outs)
+        chosen = [s for s in llm.last_steps if s.prefill_tokens == 0 and s.decoded == n_req]
+        wall = sum(s.wall_s for s in chosen)
+        return (len(chosen) * n_req / wall if wall > 0 else 0.0), chosen
+
+    llm.generate([prompt(ctx_len)], SamplingParams(max_tokens=2))          # warm the path
+    e2e_tok_s, decode_steps = through_generate(batch, args.steps)
+    if batch != 64:
+        points["e2e_b64"] = round(through_generate(64, 16)[0], 1)
     h2d = 0
     if decode_steps:
         from crucible_b200.engine.context import StepLayout
