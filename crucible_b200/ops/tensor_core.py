@@ -10,6 +10,7 @@ row stride of a bfloat16 output must be multiples of 8 elements (TMA needs
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -333,8 +334,9 @@ def linear_rope_append(h, wqkv, qkv, n_heads, n_kv_heads, head_dim, cos, sin, ro
     return True
 
 
-ATTENTION_LEAN = -1      # the form of the head-size-64 prompt attention: -1 the launcher's choice
-                         # (the roomy form, see the kernel's header), 0 roomy, 1 lean (tests fix it)
+# The form of the head-size-64 prompt attention: -1 the launcher's choice (the roomy form, see the
+# kernel's header), 0 roomy, 1 lean (tests fix it; CRUCIBLE_ATTENTION_LEAN=1 for a profile of that form).
+ATTENTION_LEAN = int(os.environ.get("CRUCIBLE_ATTENTION_LEAN", "-1"))
 
 
 class _Requests:
