@@ -415,7 +415,7 @@ DECODE_TC_SHORT_BLOCKS = 22 * N_SMS // 10 # chunks of at most two tiles run with
 DECODE_MMA_TARGET_BLOCKS = 4 * N_SMS
 
 
-def decode_chunk_keys(blocks_per_chunk: int, context_bucket: int, tcgen05: bool) -> int:
+def decode_chunk_keys(blocks_per_chunk: int, context_bucket: int, tcgen05: bool, head_dim: int = 64) -> int:
     """Keys per block of the split attention for decoded tokens: a function of the step's
     shape alone (so a captured step replays).  `blocks_per_chunk`: blocks that one chunk of
     every request takes (requests x KV heads x groups of 16 packed rows).  `context_bucket`:
@@ -428,17 +428,26 @@ def decode_chunk_keys(blocks_per_chunk: int, context_bucket: int, tcgen05: bool)
     else the bucket divided into as many equal parts as bring the launch nearest to one and
     a half blocks per SM, in whole tiles (batch 4 / 8 / 32 at 2,048 tokens: 0.307 / 0.321 /
     0.624 ms per step against 0.322 / 0.331 / 0.706 ms with chunks for 296 or 148 blocks).
+    With heads of more than 64 features a block's three K/V stages are 192 KB, one block to an
+    SM, and a launch of more blocks than SMs runs in two waves: the same rule with one block
+    per SM as the most (Llama-3-8B layer sizes, 2,048 tokens, batch 4 / 8 / 16: 0.714 / 0.753 /
+    0.824 ms per step of four layers against 0.736 / 0.773 / 0.854 ms).
     mma.sync form: the parts that bring the launch nearest to four blocks per SM."""
     unit = 128 if tcgen05 else 256
     whole = -(-context_bucket // unit) * unit
+    one_per_sm = tcgen05 and head_dim > 64
     if tcgen05:
+        short = N_SMS if one_per_sm else DECODE_TC_SHORT_BLOCKS
         n_one, n_two = -(-context_bucket // 128), -(-context_bucket // 256)
-        if n_one <= 8 and blocks_per_chunk * n_one <= DECODE_TC_SHORT_BLOCKS:
+        if n_one <= 8 and blocks_per_chunk * n_one <= short:
             return min(128, whole)
-        if blocks_per_chunk * n_two <= DECODE_TC_SHORT_BLOCKS:
+        if blocks_per_chunk * n_two <= short:
             return min(256, whole)
     target = DECODE_TC_TARGET_BLOCKS if tcgen05 else DECODE_MMA_TARGET_BLOCKS
-    parts = max(1, (2 * target + blocks_per_chunk) // (2 * max(1, blocks_per_chunk)))
+    if one_per_sm:
+        parts = max(1, N_SMS // max(1, blocks_per_chunk))
+    else:
+        parts = max(1, (2 * target + blocks_per_chunk) // (2 * max(1, blocks_per_chunk)))
     chunk = -(-context_bucket // parts)
     chunk = -(-chunk // unit) * unit
     return min(max(chunk, unit), whole)
@@ -461,7 +470,7 @@ def _attend(qkv, out, k_cache, v_cache, reqs, n_heads, n_kv_heads, head_dim, sca
     if split:
         groups = -(-reqs.max_new * n_rep // 16)
         blocks_per_chunk = reqs.count * n_kv_heads * groups
-        chunk_keys = decode_chunk_keys(blocks_per_chunk, reqs.bucket, decode_tc)
+        chunk_keys = decode_chunk_keys(blocks_per_chunk, reqs.bucket, decode_tc, head_dim)
         n_chunks = -(-reqs.bucket // chunk_keys)
         floats = reqs.rows_end * n_heads * n_chunks * (head_dim + 2)
         partial = ctx.scratch("attn.partial", (floats,), torch.float32)

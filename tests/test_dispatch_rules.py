@@ -40,10 +40,10 @@ def test_tall_tiles_only_where_they_fill_the_sms():
 
 @pytest.mark.parametrize("bucket", [256, 512, 768, 1024, 2304, 4096, 8192, 8448])
 @pytest.mark.parametrize("blocks", [1, 4, 32, 48, 96, 128, 160, 256, 1000])
-@pytest.mark.parametrize("tcgen05", [True, False])
-def test_decode_chunks_cover_the_bucket_in_whole_tiles(blocks, bucket, tcgen05):
+@pytest.mark.parametrize("tcgen05, head_dim", [(True, 64), (True, 128), (False, 64)])
+def test_decode_chunks_cover_the_bucket_in_whole_tiles(blocks, bucket, tcgen05, head_dim):
     unit = 128 if tcgen05 else 256
-    chunk = tensor_core.decode_chunk_keys(blocks, bucket, tcgen05)
+    chunk = tensor_core.decode_chunk_keys(blocks, bucket, tcgen05, head_dim)
     assert unit <= chunk <= -(-bucket // unit) * unit and chunk % unit == 0
     n_chunks = -(-bucket // chunk)
     assert (n_chunks - 1) * chunk < bucket <= n_chunks * chunk     # no chunk is empty
@@ -62,6 +62,12 @@ def test_decode_chunks_of_the_benchmark_points():
     assert tensor_core.decode_chunk_keys(16 * 4, 2304, True) == 768        # 3 chunks, 192 blocks
     assert tensor_core.decode_chunk_keys(32 * 4, 2304, True) == 1152       # 2 chunks, 256 blocks
     assert tensor_core.decode_chunk_keys(64 * 4, 2304, True) == 2304       # a block per request and KV head
+    # heads of 128 features, 8 KV heads: one block to an SM, so never more blocks than SMs
+    assert tensor_core.decode_chunk_keys(1 * 8, 2304, True, 128) == 256    # 9 chunks, 72 blocks
+    assert tensor_core.decode_chunk_keys(2 * 8, 2304, True, 128) == 256    # 9 chunks, 144 blocks
+    assert tensor_core.decode_chunk_keys(4 * 8, 2304, True, 128) == 640    # 4 chunks, 128 blocks
+    assert tensor_core.decode_chunk_keys(8 * 8, 2304, True, 128) == 1152   # 2 chunks, 128 blocks
+    assert tensor_core.decode_chunk_keys(16 * 8, 2304, True, 128) == 2304  # a block per request and KV head
 
 
 def test_step_shape_key_follows_what_launches_depend_on():
