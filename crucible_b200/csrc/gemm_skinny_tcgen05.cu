@@ -27,11 +27,12 @@ namespace {
 constexpr int WM = 128;                // rows of W per block
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
+constexpr int STAGES_SHARED = 4;        // 72-96 KB a block: up to three blocks share an SM
+constexpr int STAGES_ALONE = 8;         // 144-192 KB: a block that has its SM to itself
 
 enum Epilogue { STORE_BF16 = 0, STORE_F32 = 1, ACCUM_F32 = 2, SWIGLU_BF16 = 3 };
 
-template <int MT>
+template <int MT, int STAGES>
 struct SkinnyStorage {
     alignas(1024) uint8_t w[STAGES][WM * BK * 2];
     alignas(1024) uint8_t a[STAGES][MT * BK * 2];
@@ -63,14 +64,14 @@ __device__ __forceinline__ void load_acc(uint32_t taddr, float (&v)[MT]) {
     }
 }
 
-template <int MT, int EPI>
+template <int MT, int EPI, int STAGES>
 __global__ void __launch_bounds__(192)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
                    const __grid_constant__ CUtensorMap map_a, void* __restrict__ c_ptr, int M,
                    int N, int K, int ldc, int inter, int splits, float* __restrict__ partial,
                    int* __restrict__ counters, int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
-    using Storage = SkinnyStorage<MT>;
+    using Storage = SkinnyStorage<MT, STAGES>;
     Storage& s = *reinterpret_cast<Storage*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -104,8 +105,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
     __syncthreads();
     tc::tc_fence_after_sync();
     const uint32_t tmem_acc = s.tmem_base;
-    auto load_w = [&](int i) {
-        const int st = i % STAGES;
+    auto load_w = [&](int i, int st) {
         const int kx = (kb0 + i) * BK;
         if (EPI == SWIGLU_BF16) {
             tc::tma_load_2d(s.w[st], &map_w, &s.full_bar[st], kx, tile * (WM / 2));
@@ -122,7 +122,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
     if (warp == 0 && lane == 0) {
         for (int i = 0; i < w_ahead; ++i) {
             tc::mbar_expect_tx(&s.full_bar[i], STAGE_BYTES);
-            load_w(i);
+            load_w(i, i);
         }
     }
     cb_pdl_wait();
@@ -130,20 +130,22 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
 
     if (warp == 0) {
         if (lane == 0) {
-            int armed = w_ahead;
+            // (the stage and its parity are carried along: a division by a run-time value
+            // costs a lone thread about as much as two boxes)
+            int armed = w_ahead, st = 0;
+            uint32_t parity = 1;                // of the stage's last round, once there was one
             for (int i = 0; i < n_kb; ++i) {
-                const int st = i % STAGES;
-                const uint32_t round = i / STAGES;
-                if (round > 0 && !tc::mbar_wait(&s.empty_bar[st], (round - 1) & 1, abort_flag)) {
+                if (i >= STAGES && !tc::mbar_wait(&s.empty_bar[st], parity, abort_flag)) {
                     tc::give_up(abort_flag, status, tc::ST_PRODUCER_TIMEOUT);
                     break;
                 }
                 if (i >= w_ahead) {
                     tc::mbar_expect_tx(&s.full_bar[st], STAGE_BYTES);
-                    load_w(i);
+                    load_w(i, st);
                 }
                 tc::tma_load_2d(s.a[st], &map_a, &s.full_bar[st], (kb0 + i) * BK, 0);
                 if (i + 1 > armed) armed = i + 1;
+                if (++st == STAGES) st = 0, parity ^= 1;
             }
             if (*abort_flag) {
                 const int first = armed > STAGES ? armed - STAGES : 0;
@@ -154,23 +156,40 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
         }
     } else if (warp == 1) {
         if (lane == 0) {
+            // One thread, whose own instructions are what a step of K takes with tiles this
+            // narrow (a block that has its SM to itself streams what this loop can hand on);
+            // so the ring is walked by an unrolled loop in which a stage's barriers and
+            // descriptors are constants away from those of stage 0.
             constexpr uint32_t idesc = tc::instr_desc_bf16(WM, MT);
+            constexpr uint32_t W_STEP = sizeof(s.w[0]) >> 4, A_STEP = sizeof(s.a[0]) >> 4;
+            const uint64_t desc0 = tc::smem_desc_sw128(tc::smem_u32(s.w[0]));
+            const uint32_t desc_hi = (uint32_t)(desc0 >> 32);
+            const uint32_t w_lo = (uint32_t)desc0;
+            const uint32_t a_lo = (uint32_t)tc::smem_desc_sw128(tc::smem_u32(s.a[0]));
+            const uint32_t full0 = tc::smem_u32(&s.full_bar[0]), empty0 = tc::smem_u32(&s.empty_bar[0]);
             bool ok = true;
-            for (int i = 0; i < n_kb; ++i) {
-                const int st = i % STAGES;
-                if (!tc::mbar_wait(&s.full_bar[st], (i / STAGES) & 1, abort_flag)) {
-                    tc::give_up(abort_flag, status, tc::ST_MMA_TIMEOUT);
-                    ok = false;
-                    break;
-                }
-                tc::tc_fence_after_sync();
-                const uint64_t w_desc = tc::smem_desc_sw128(tc::smem_u32(s.w[st]));
-                const uint64_t a_desc = tc::smem_desc_sw128(tc::smem_u32(s.a[st]));
+            uint32_t phase = 0;
+            for (int i0 = 0; i0 < n_kb && ok; i0 += STAGES, phase ^= 1) {
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k)
-                    tc::umma_bf16(tmem_acc, w_desc + 2 * k, a_desc + 2 * k, idesc,
-                                  (i > 0 || k > 0) ? 1u : 0u);
-                tc::umma_commit(&s.empty_bar[st]);
+                for (int st = 0; st < STAGES; ++st) {
+                    if (i0 + st >= n_kb) break;
+                    if (!tc::mbar_wait_at(full0 + 8 * st, phase, abort_flag)) {
+                        tc::give_up(abort_flag, status, tc::ST_MMA_TIMEOUT);
+                        ok = false;
+                        break;
+                    }
+                    tc::tc_fence_after_sync();
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t w_desc = tc::desc_of(w_lo + st * W_STEP + 2 * k, desc_hi);
+                        const uint64_t a_desc = tc::desc_of(a_lo + st * A_STEP + 2 * k, desc_hi);
+                        if (st == 0 && k == 0)
+                            tc::umma_bf16(tmem_acc, w_desc, a_desc, idesc, i0 > 0 ? 1u : 0u);
+                        else
+                            tc::umma_bf16_add(tmem_acc, w_desc, a_desc, idesc);
+                    }
+                    tc::umma_commit_at(empty0 + 8 * st);
+                }
             }
             if (ok && n_kb > 0) tc::umma_commit(&s.tmem_full_bar);
         }
@@ -183,6 +202,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
     float acc[MT];
 #pragma unroll
     for (int i = 0; i < MT; ++i) acc[i] = 0.f;
+    // ACCUM_F32: the values to add to are asked for now, while the products run (every
+    // block asks: which one writes is not known yet, and a tile's values are 8 KB from the L2)
+    constexpr bool EARLY = EPI == ACCUM_F32 && MT <= 32;      // (64 values more would cost a block per SM)
+    float add_to[EARLY ? MT : 1];
+    if (EARLY && epi_warp && tile * WM + w_row < N) {
+        const float* src = (const float*)c_ptr + tile * WM + w_row;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) add_to[m] = m < M ? __ldcg(src + (size_t)m * ldc) : 0.f;
+    }
     bool ok = true;
     if (epi_warp && n_kb > 0) {
         ok = tc::mbar_wait(&s.tmem_full_bar, 0, abort_flag);
@@ -213,11 +241,22 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
             const float* base = partial + (size_t)tile * splits * MT * WM;
 #pragma unroll
             for (int m = 0; m < MT; ++m) acc[m] = 0.f;
-            for (int sp = 0; sp < splits; ++sp) {           // ascending: order-independent result
-                const float* src = base + (size_t)sp * MT * WM + w_row;
+            // summed in ascending order of the splits whichever block came last; the loads of
+            // four splits are on their way at a time (a trip to the L2 each, otherwise)
+            constexpr int AT_ONCE = MT <= 16 ? 4 : (MT <= 32 ? 2 : 1);
+            for (int sp0 = 0; sp0 < splits; sp0 += AT_ONCE) {
+                float part[AT_ONCE][MT];
 #pragma unroll
-                for (int m = 0; m < MT; ++m)
-                    if (m < M) acc[m] += __ldcg(src + m * WM);
+                for (int u = 0; u < AT_ONCE; ++u) {
+                    const float* src = base + (size_t)(sp0 + u) * MT * WM + w_row;
+#pragma unroll
+                    for (int m = 0; m < MT; ++m)
+                        part[u][m] = (sp0 + u < splits && m < M) ? __ldcg(src + m * WM) : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < AT_ONCE; ++u)
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) acc[m] += part[u][m];
             }
         }
         if (s.is_last && threadIdx.x == 0) counters[tile] = 0;    // ready for the next launch
@@ -248,8 +287,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
     } else if (writer && epi_warp) {
         const int col = tile * WM + w_row;
         if (col < N) {
-            if (EPI == ACCUM_F32) {
-                // all residual values first (independent loads), then the sums
+            if (EARLY) {
+#pragma unroll
+                for (int m = 0; m < MT; ++m) acc[m] += add_to[m];
+            } else if (EPI == ACCUM_F32) {
                 const float* src = (const float*)c_ptr + col;
 #pragma unroll
                 for (int m = 0; m < MT; ++m)
@@ -274,21 +315,43 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
     }
 }
 
-template <int MT, int EPI>
-int launch(const CUtensorMap& mw, const CUtensorMap& ma, void* C, int M, int N, int K, int ldc,
-           int inter, int n_tiles, int splits, float* partial, int* counters, int* status,
-           cudaStream_t stream) {
-    const int smem = (int)sizeof(SkinnyStorage<MT>) + 1024;
+template <int MT, int EPI, int STAGES>
+int launch_stages(const CUtensorMap& mw, const CUtensorMap& ma, void* C, int M, int N, int K, int ldc,
+                  int inter, int n_tiles, int splits, float* partial, int* counters, int* status,
+                  cudaStream_t stream) {
+    const int smem = (int)sizeof(SkinnyStorage<MT, STAGES>) + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, EPI>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, EPI, STAGES>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    cb_launch(gemm_skinny_kernel<MT, EPI>, dim3(n_tiles, splits), dim3(192), smem, stream, 
+    cb_launch(gemm_skinny_kernel<MT, EPI, STAGES>, dim3(n_tiles, splits), dim3(192), smem, stream,
         mw, ma, C, M, N, K, ldc, inter, splits, partial, counters, status);
     return cb_last_error();
+}
+
+// A block keeps STAGES tiles of W on their way, and what one block streams is that many
+// bytes per trip to memory and back (about 1.2 us with the hand-over between the threads): 53
+// GB/s with four stages.  A launch of at most one block per SM gets eight.
+template <int MT, int EPI>
+int launch(const CUtensorMap& mw, const CUtensorMap& ma, void* C, int M, int N, int K, int ldc,
+           int inter, int n_tiles, int splits, float* partial, int* counters, int* status,
+           cudaStream_t stream) {
+    static int n_sms = 0;
+    if (n_sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            n_sms = 1;
+    }
+    const int k_blocks = (K + BK - 1) / BK;
+    if ((long)n_tiles * splits <= n_sms && k_blocks > STAGES_SHARED * splits)
+        return launch_stages<MT, EPI, STAGES_ALONE>(mw, ma, C, M, N, K, ldc, inter, n_tiles, splits, partial,
+                                                    counters, status, stream);
+    return launch_stages<MT, EPI, STAGES_SHARED>(mw, ma, C, M, N, K, ldc, inter, n_tiles, splits, partial,
+                                                 counters, status, stream);
 }
 
 template <int MT>

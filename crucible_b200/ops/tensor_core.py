@@ -208,10 +208,13 @@ def _buffer(device, name: str, numel: int, dtype, zero: bool = False) -> torch.T
 
 
 def skinny_splits(m: int, n_tiles: int, k: int) -> int:
-    """Blocks along K per 128-row tile of W: enough blocks to cover the SMs, but
-    never so many that the partial tiles outweigh the weights they stand for."""
+    """Blocks along K per 128-row tile of W: as many as give every SM one block, never more
+    blocks than SMs (a launch of at most one block per SM runs with eight stages, and every
+    further split is a partial tile more for the last block to sum: 50 MB at 8 rows 13.7 us with
+    3 x 48 blocks, 15.9 us with 4 x 48), and never so many that the partial tiles outweigh the
+    weights they stand for."""
     k_blocks = -(-k // 64)
-    want = -(-160 // n_tiles)
+    want = max(1, N_SMS // n_tiles)
     cap = max(1, k // (4 * m))
     return max(1, min(want, k_blocks, cap))
 
@@ -245,10 +248,14 @@ def _gemm_skinny(a, w, out, n, epi, splits=None) -> bool:
 
 
 SKINNY_ROWS = 16     # products with at most this many rows run with W on the MMA's M side ...
-SKINNY_MIN_BYTES = 40 << 20   # ... if W is at least this large (it streams: 3.5-5.5 TB/s; smaller
-                              # ones are latency-bound and the 128-row tiles, with K shared by
-                              # clusters, are quicker: 33 MB at 16 rows 16.0 against 23.4 us).  From
-                              # 17 rows on the 128-row tiles are as fast or faster at every size.
+SKINNY_MIN_BYTES = 40 << 20   # ... if W is at least this large (it streams: 3.6-5.5 TB/s; smaller
+                              # ones are latency-bound: at 33 MB and 16 rows the 128-row tiles, with
+                              # K shared by clusters, take 12.7 us, these 12.4, the few-row kernel 12.1
+                              # at 8 rows).
+SKINNY_MID_ROWS = 32          # ... and up to this many rows between that size and SKINNY_MID_BYTES
+SKINNY_MID_BYTES = 128 << 20  # (50 MB at 32 rows: 16.2 against 17.6 us for the tiles, 117 MB: 29.2
+                              # against 33.3; 235 MB: 46.8 against 44.4).  From 33 rows on the
+                              # 128-row tiles are as fast or faster at every size.
 SKINNY_WIDE_N = 8192 # ... and up to 64 rows if W has at least this many rows (the LM head)
 
 
@@ -270,7 +277,9 @@ def linear(a, w, out, *, accumulate=False, tile=None) -> bool:
         epi = ACCUM_F32 if accumulate else STORE_F32
     else:
         return False
-    if tile is None and ((a.shape[0] <= SKINNY_ROWS and w.numel() * 2 >= SKINNY_MIN_BYTES)
+    w_bytes = w.numel() * 2
+    if tile is None and ((a.shape[0] <= SKINNY_ROWS and w_bytes >= SKINNY_MIN_BYTES)
+                         or (a.shape[0] <= SKINNY_MID_ROWS and SKINNY_MIN_BYTES <= w_bytes <= SKINNY_MID_BYTES)
                          or (a.shape[0] <= 64 and w.shape[0] >= SKINNY_WIDE_N)):
         return _gemm_skinny(a, w, out, w.shape[0], epi)
     if tile is None and _tall_tiles(a.shape[0], w.shape[0], a.shape[1]):
