@@ -59,6 +59,29 @@ struct RopeArgs {
     int n_heads, n_kv_heads, head_dim, page_tokens, write_cache;
 };
 
+// What a product knows of the RMS norm on either side of it.
+//   After it (ACCUM_F32 as the rows' last write before a norm): with `gain` set the epilogue
+//   also leaves bf16(x * gain) of the summed rows x in `scaled` and the tile's share of every
+//   row's sum of squares in `sumsq_out` [tiles along N][M] (summed in the order of the
+//   columns).  The tile of C comes into shared memory by TMA while the products run, so the
+//   thread that holds a row's accumulators also has the values they are added to; C itself
+//   still gets its sums by TMA adds, `scaled` leaves by TMA stores of 32-column boxes (a single
+//   tile of rows: in 64-byte pieces of the threads' own rows).
+//   Tiles up to 128 columns, N a multiple of 32.
+//   Before it (any epilogue): with `sumsq_in` set the rows of A are bf16(x * gain) of rows
+//   not yet divided by their root mean square; the epilogue sums a row's `parts` shares in
+//   their order and multiplies the row's accumulators by 1 / sqrt(sum / width + eps), which
+//   is the same product as with normalised rows up to the rounding of A.
+struct NormArgs {
+    const float* gain;
+    __nv_bfloat16* scaled;
+    float* sumsq_out;
+    int ld_scaled;
+    const float* sumsq_in;
+    int parts;
+    float width, eps;
+};
+
 template <int BN, int STAGES, int MH>
 struct SharedStorage {
     alignas(1024) uint8_t a[STAGES][MH * BM * BK * 2];
@@ -66,18 +89,28 @@ struct SharedStorage {
     alignas(8) uint64_t full_bar[STAGES];
     uint64_t empty_bar[STAGES];
     uint64_t tmem_full_bar;
+    uint64_t c_bar;             // a norm after the product: the tile of C has landed
+    alignas(16) float gain[128];   // ... and the norm's gain for the tile's columns
     long row_base[BM];          // ROPE_APPEND: a row's first element in a cache page / head_dim, or -1
     uint32_t tmem_base;
     int abort_flag;
 };
 
-template <int BN, int STAGES, int EPI, int MH>
+// NORM: what the product has to do with the norm around it, fixed when it is compiled so that
+// the other forms carry none of its code (an epilogue runs once per block, its instructions
+// come from memory, and a tenth more of them cost every product 0.4 us): NORM_NONE, NORM_PRE
+// (the rows of A are ahead of their norm, `sumsq_in`), NORM_EMIT (`gain`: leave the next
+// norm's input).
+enum NormForm { NORM_NONE = 0, NORM_PRE = 1, NORM_EMIT = 2 };
+
+template <int BN, int STAGES, int EPI, int MH, int NORM>
 __global__ void __launch_bounds__(192, (STAGES <= 3 && MH == 1) ? 2 : 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_w,
-                    const __grid_constant__ CUtensorMap map_c, int tma_out,
+                    const __grid_constant__ CUtensorMap map_c,
+                    const __grid_constant__ CUtensorMap map_s, int tma_out,
                     void* __restrict__ c_ptr, int M, int N, int K, int ldc, int inter,
-                    int k_splits, int* __restrict__ status, const RopeArgs ra) {
+                    int k_splits, int* __restrict__ status, const RopeArgs ra, const NormArgs na) {
     extern __shared__ uint8_t smem_raw[];
     using Storage = SharedStorage<BN, STAGES, MH>;
     Storage& s = *reinterpret_cast<Storage*>(
@@ -102,11 +135,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             tc::mbar_init(&s.empty_bar[i], 1);
         }
         tc::mbar_init(&s.tmem_full_bar, 1);
+        tc::mbar_init(&s.c_bar, 1);
         s.abort_flag = 0;
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&map_a);
         tc::prefetch_tensormap(&map_w);
         if (tma_out) tc::prefetch_tensormap(&map_c);
+        if (NORM == NORM_EMIT && M > BM) tc::prefetch_tensormap(&map_s);
     }
     if (warp == 1) {
         tc::tmem_alloc(&s.tmem_base, TMEM_COLS);
@@ -116,6 +151,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     __syncthreads();
     tc::tc_fence_after_sync();
     const uint32_t tmem_acc = s.tmem_base;
+    constexpr bool PRE = NORM == NORM_PRE;
     auto load_w = [&](int kb, int st) {
         if (EPI == SWIGLU_BF16) {
             const int half = BN / 2;
@@ -138,6 +174,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     cb_pdl_wait();
     cb_pdl_trigger();
+
+    // A norm after the product: the tile of C (32-column boxes in the 128-byte swizzle) comes
+    // into its own piece of shared memory behind the stages, asked for by an epilogue thread
+    // that has nothing else to do yet.  Only the block that runs the epilogue asks.
+    const bool emit = NORM == NORM_EMIT && EPI == ACCUM_F32 && MH == 1 && BN <= 128 && split == 0;
+    uint8_t* const c_tile = reinterpret_cast<uint8_t*>(&s) + ((sizeof(Storage) + 1023) & ~(size_t)1023);
+    if (emit && warp >= 2) {
+        // (read in the epilogue, behind a barrier of these four warps)
+        const int i = threadIdx.x - 64;
+        if (i < BN) s.gain[i] = n_tile * BN + i < N ? __ldg(na.gain + n_tile * BN + i) : 0.f;
+    }
+    if (emit && warp == 2 && lane == 0) {
+        int boxes = 0;
+        for (int c = 0; c < BN / 32; ++c) boxes += n_tile * BN + c * 32 < N;
+        tc::mbar_expect_tx(&s.c_bar, (uint32_t)boxes * BM * 128);
+        for (int c = 0; c < BN / 32; ++c)
+            if (n_tile * BN + c * 32 < N)
+                tc::tma_load_2d(c_tile + c * (BM * 128), &map_c, &s.c_bar, n_tile * BN + c * 32, m0);
+    }
 
     if (warp == 0) {
         // ---- producer: one thread feeds the ring of stages -------------------
@@ -256,6 +311,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         // the products run; every epilogue thread publishes its row's place.  For head size 64
         // also its 32 rotation factors, kept in registers for every head.  (Per 128 rows: a
         // block with two accumulators does this again for its second half.)
+        // rows not yet divided by their root mean square: the row's factor, from the shares of
+        // its sum of squares (asked for while the products run)
+        auto row_factor = [&](int at_row) -> float {
+            if (!PRE || at_row >= M) return 1.f;
+            float ss = 0.f;
+#pragma unroll 4
+            for (int t = 0; t < na.parts; ++t) ss += __ldcg(na.sumsq_in + (size_t)t * M + at_row);
+            return 1.0f / sqrtf(ss / na.width + na.eps);
+        };
+        float rf[MH];
+#pragma unroll
+        for (int mh = 0; mh < MH; ++mh) rf[mh] = row_factor(row + mh * BM);
         int row_pos = 0;
         float4 cs_reg[8], sn_reg[8];
         auto rope_rows = [&](int at_row) {
@@ -375,6 +442,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                 }
                 const uint32_t lane_addr_h = lane_addr + mh * BN;
                 const int m0_h = m0 + mh * BM;
+                const float f = mh == 0 ? rf[0] : rf[MH - 1];
                 const float* cs_row = ra.cos_t + (size_t)row_pos * half;
                 const float* sn_row = ra.sin_t + (size_t)row_pos * half;
 #pragma unroll 1
@@ -389,6 +457,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                         tc::tmem_ld_32x32(lane_addr_h + hc + c, lo);
                         tc::tmem_ld_32x32(lane_addr_h + hc + half + c, hi);
                         tc::tmem_ld_wait();
+                        if (PRE) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                lo[i] = __float_as_uint(__uint_as_float(lo[i]) * f);
+                                hi[i] = __float_as_uint(__uint_as_float(hi[i]) * f);
+                            }
+                        }
                         if (is_q || is_k) {
 #pragma unroll
                             for (int q4 = 0; q4 < 8; ++q4) {
@@ -463,9 +538,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                 constexpr int OUT_COLS = EPI == SWIGLU_BF16 ? BN / 2 : BN;     // columns of C per tile
                 constexpr int CHUNK = (EPI == STORE_F32 || EPI == ACCUM_F32) ? 32 : 64;
                 const int n_out = EPI == SWIGLU_BF16 ? inter : N;
+                float ss4[4] = {0.f, 0.f, 0.f, 0.f};
+                uint8_t* const sbuf = ring + (BN / 32) * (BM * 128);     // behind the staged chunks of C
+                static_assert(NORM != NORM_EMIT || EPI != ACCUM_F32 || BN > 128 || MH > 1 ||
+                                  (BN / 32) * (BM * 192) <= (int)(sizeof(s.a) + sizeof(s.b)),
+                              "the staged chunks of C and of the scaled rows must fit in the ring of stages");
+                const bool direct = M <= BM;
+                if (emit) {
+                    asm volatile("bar.sync 1, 128;" ::: "memory");          // the gain is in shared memory
+                    if (!tc::mbar_wait(&s.c_bar, 0, abort_flag)) tc::give_up(abort_flag, status, tc::ST_EPILOGUE_TIMEOUT);
+                }
 #pragma unroll 1
                 for (int mh = 0; mh < MH; ++mh) {                   // one accumulator after the other
                 const uint32_t lane_addr_h = lane_addr + mh * BN;
+                const float f = mh == 0 ? rf[0] : rf[MH - 1];
                 if (mh > 0) {
                     // the staging buffers are used again: the first half's stores must have read them
                     if (warp == 2 && lane == 0) tc::tma_store_wait_read();
@@ -478,11 +564,59 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     if (EPI == STORE_F32 || EPI == ACCUM_F32) {
                         uint32_t v[32];
                         tc::tmem_ld_32x32(lane_addr_h + c * 32, v);
+                        // a norm after the product: the chunk's values of C and the gain come out
+                        // of shared memory while the accumulators come out of tensor memory
+                        constexpr bool EMIT = NORM == NORM_EMIT && EPI == ACCUM_F32 && MH == 1;
+                        const bool emit_chunk = EMIT && emit && n_tile * BN + c * 32 < N;
+                        float4 o[EMIT ? 8 : 1], g[EMIT ? 8 : 1];
+                        if (EMIT && emit_chunk) {
+                            const uint8_t* old_row = c_tile + c * (BM * 128) + r * 128;
+                            const float4* g4 = reinterpret_cast<const float4*>(s.gain + (c * 32 & 127));
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                o[q] = *reinterpret_cast<const float4*>(old_row + ((q ^ (r & 7)) << 4));
+                                g[q] = g4[q];
+                            }
+                        }
                         tc::tmem_ld_wait();
+                        if (PRE) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * f);
+                        }
 #pragma unroll
                         for (int q = 0; q < 8; ++q)
                             *reinterpret_cast<uint4*>(mine + ((q ^ (r & 7)) << 4)) =
                                 make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                        if (EMIT && emit_chunk) {
+                            // The sums as the TMA add will leave them in C (the same two fp32
+                            // operands), their squares in four interleaved chains, and bf16(x * gain):
+                            // for a single tile of rows in 64-byte pieces of the thread's own row
+                            // straight to memory (a TMA store more per chunk and the wait for it
+                            // cost 0.3 us more there), for many rows staged behind the chunks of C
+                            // as [128 rows][64 bytes], unswizzled, and sent as a box.
+                            uint8_t* staged = sbuf + c * (BM * 64) + r * 64;
+                            uint8_t* s_row = direct ? reinterpret_cast<uint8_t*>(na.scaled + (size_t)row * na.ld_scaled +
+                                                                                 n_tile * BN + c * 32)
+                                                    : staged;
+                            uint32_t pk[4];
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                const float x0 = o[q].x + __uint_as_float(v[4 * q]);
+                                const float x1 = o[q].y + __uint_as_float(v[4 * q + 1]);
+                                const float x2 = o[q].z + __uint_as_float(v[4 * q + 2]);
+                                const float x3 = o[q].w + __uint_as_float(v[4 * q + 3]);
+                                ss4[0] = fmaf(x0, x0, ss4[0]);
+                                ss4[1] = fmaf(x1, x1, ss4[1]);
+                                ss4[2] = fmaf(x2, x2, ss4[2]);
+                                ss4[3] = fmaf(x3, x3, ss4[3]);
+                                __nv_bfloat162 a2 = __floats2bfloat162_rn(x0 * g[q].x, x1 * g[q].y);
+                                __nv_bfloat162 b2 = __floats2bfloat162_rn(x2 * g[q].z, x3 * g[q].w);
+                                pk[2 * (q & 1)] = *reinterpret_cast<uint32_t*>(&a2);
+                                pk[2 * (q & 1) + 1] = *reinterpret_cast<uint32_t*>(&b2);
+                                if ((q & 1) && (!direct || row < M))
+                                    *reinterpret_cast<uint4*>(s_row + (q >> 1) * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                            }
+                        }
                     } else {
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
@@ -494,10 +628,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                 tc::tmem_ld_wait();
 #pragma unroll
                                 for (int j = 0; j < 32; ++j)
-                                    v[j] = __float_as_uint(tc::silu_fast(__uint_as_float(v[j])) *
-                                                           __uint_as_float(u[j]));
+                                    v[j] = __float_as_uint(tc::silu_fast(__uint_as_float(v[j]) * f) *
+                                                           (__uint_as_float(u[j]) * f));
                             } else {
                                 tc::tmem_ld_wait();
+                                if (PRE) {
+#pragma unroll
+                                    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * f);
+                                }
                             }
 #pragma unroll
                             for (int q = 0; q < 4; ++q) {
@@ -520,11 +658,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                         if (x < n_out) {
                             if (EPI == ACCUM_F32) tc::tma_reduce_add_2d(&map_c, buf, x, m0 + mh * BM);
                             else tc::tma_store_2d(&map_c, buf, x, m0 + mh * BM);
+
+                            if (NORM == NORM_EMIT && EPI == ACCUM_F32 && MH == 1 && emit && !direct)
+                                tc::tma_store_2d(&map_s, sbuf + c * (BM * 64), x, m0);
                             tc::tma_store_commit();
                         }
                     }
                 }
                 }
+                if (NORM == NORM_EMIT && EPI == ACCUM_F32 && MH == 1 && emit && row < M)
+                    na.sumsq_out[(size_t)n_tile * M + row] = (ss4[0] + ss4[1]) + (ss4[2] + ss4[3]);
                 if (warp == 2 && lane == 0) tc::tma_store_wait_all();
             } else if (EPI == SWIGLU_BF16) {
                 constexpr int HALF = BN / 2;
@@ -542,10 +685,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                             uint32_t packed[8];
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {
-                                const float g0 = __uint_as_float(g[2 * j]);
-                                const float g1 = __uint_as_float(g[2 * j + 1]);
-                                const float h0 = tc::silu_fast(g0) * __uint_as_float(u[2 * j]);
-                                const float h1 = tc::silu_fast(g1) * __uint_as_float(u[2 * j + 1]);
+                                const float g0 = __uint_as_float(g[2 * j]) * rf[0];
+                                const float g1 = __uint_as_float(g[2 * j + 1]) * rf[0];
+                                const float h0 = tc::silu_fast(g0) * (__uint_as_float(u[2 * j]) * rf[0]);
+                                const float h1 = tc::silu_fast(g1) * (__uint_as_float(u[2 * j + 1]) * rf[0]);
                                 __nv_bfloat162 v = __floats2bfloat162_rn(h0, h1);
                                 packed[j] = *reinterpret_cast<uint32_t*>(&v);
                             }
@@ -556,9 +699,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
                             for (int j = 0; j < 16; ++j) {
                                 if (col0 + j < inter) {
-                                    const float gv = __uint_as_float(g[j]);
+                                    const float gv = __uint_as_float(g[j]) * rf[0];
                                     dst[j] = __float2bfloat16_rn(tc::silu_fast(gv) *
-                                                                 __uint_as_float(u[j]));
+                                                                 (__uint_as_float(u[j]) * rf[0]));
                                 }
                             }
                         }
@@ -578,15 +721,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
                         for (int q = 0; q < 8; ++q) {
                             const float4 o = early[(c0 >> 2) + q];
-                            d4[q] = make_float4(o.x + __uint_as_float(r[4 * q]),
-                                                o.y + __uint_as_float(r[4 * q + 1]),
-                                                o.z + __uint_as_float(r[4 * q + 2]),
-                                                o.w + __uint_as_float(r[4 * q + 3]));
+                            d4[q] = make_float4(o.x + __uint_as_float(r[4 * q]) * rf[0],
+                                                o.y + __uint_as_float(r[4 * q + 1]) * rf[0],
+                                                o.z + __uint_as_float(r[4 * q + 2]) * rf[0],
+                                                o.w + __uint_as_float(r[4 * q + 3]) * rf[0]);
                         }
                     } else {
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
-                            if (col0 + j < N) dst[j] += __uint_as_float(r[j]);
+                            if (col0 + j < N) dst[j] += __uint_as_float(r[j]) * rf[0];
                     }
                 }
             } else {
@@ -597,6 +740,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     tc::tmem_ld_wait();
                     const int col0 = n_tile * BN + c0;
                     if (row >= M || col0 >= N) continue;
+                    if (PRE) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rf[0]);
+                    }
                     const bool full = col0 + 32 <= N;
                     if (EPI == STORE_BF16) {
                         __nv_bfloat16* dst = (__nv_bfloat16*)c_ptr + (size_t)row * ldc + col0;
@@ -647,6 +794,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             }
         }
     }
+    if (emit && warp == 2 && lane == 0 && *abort_flag) {
+        // the tile of C may still be on its way into this block's shared memory
+        for (uint32_t i = 0; i < tc::WAIT_LIMIT; ++i)
+            if (tc::mbar_try_wait(&s.c_bar, 0)) break;
+    }
     tc::tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) {
@@ -655,10 +807,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     }
 }
 
-template <int BN, int STAGES, int EPI, int MH = 1>
-int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, int K, int ldc,
-           int inter, int k_splits, int* status, cudaStream_t stream, const RopeArgs& ra = RopeArgs{}) {
+template <int BN, int STAGES, int EPI, int MH, int NORM>
+int launch_norm(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, int K, int ldc,
+                int inter, int k_splits, int* status, cudaStream_t stream, const RopeArgs& ra, const NormArgs& na) {
     if (MH > 1 && k_splits > 1) return CB_ERR_UNSUPPORTED;
+    // a norm after the product: only the epilogue that has the summed rows in registers leaves it
+    const bool emit = na.gain != nullptr;
+    using Storage = SharedStorage<BN, STAGES, MH>;
+    const size_t smem_plain = sizeof(Storage) + 1024;
+    const size_t smem_emit = ((sizeof(Storage) + 1023) & ~(size_t)1023) + (size_t)BM * BN * 4 + 1024;
+    if (emit && (EPI != ACCUM_F32 || BN > 128 || MH != 1 || (N & 31) || (ldc & 3) || (na.ld_scaled & 7) ||
+                 ((uintptr_t)na.scaled & 15) || ((uintptr_t)na.gain & 15) || ((uintptr_t)C & 15) ||
+                 na.scaled == nullptr || na.sumsq_out == nullptr || smem_emit > 227 * 1024))
+        return CB_ERR_UNSUPPORTED;
+    if (na.sumsq_in != nullptr && (na.parts < 1 || !(na.width > 0.f))) return CB_ERR_UNSUPPORTED;
     // shares of K: at most 8 blocks in a cluster, every share at least one block of 64
     // elements, and a block's accumulator (128 x BN fp32) has to fit in the ring of stages
     if (k_splits < 1) k_splits = 1;
@@ -678,31 +840,55 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, 
     const uint64_t map_cols = EPI == ROPE_APPEND ? (uint64_t)ra.n_heads * ra.head_dim : (uint64_t)out_cols;
     if (tma_out && !tc::make_out_map_2d(&mc, C, f32, (uint64_t)M, map_cols, (uint64_t)ldc, BM))
         tma_out = 0;
-    if ((EPI == ROPE_APPEND || MH > 1) && !tma_out) return CB_ERR_UNSUPPORTED;
-    using Storage = SharedStorage<BN, STAGES, MH>;
-    const int smem = (int)sizeof(Storage) + 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, EPI, MH>,
+    if ((EPI == ROPE_APPEND || MH > 1 || emit) && !tma_out) return CB_ERR_UNSUPPORTED;
+    CUtensorMap ms = ma;
+    if (emit && !tc::make_plain_box_map_2d(&ms, na.scaled, (uint64_t)M, (uint64_t)N, (uint64_t)na.ld_scaled, 32, BM))
+        return CB_ERR_UNSUPPORTED;
+    const int smem = (int)(emit ? smem_emit : smem_plain);
+    static int configured = 0;
+    if (configured < smem) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, EPI, MH, NORM>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured = smem;
     }
     const int n_cols = EPI == SWIGLU_BF16 ? 2 * inter : N;
     dim3 grid((n_cols + BN - 1) / BN, (M + BM * MH - 1) / (BM * MH), k_splits);
-    cb_launch_cluster(gemm_tcgen05_kernel<BN, STAGES, EPI, MH>, dim3(grid), dim3(192), smem, stream, k_splits,
-                      ma, mw, mc, tma_out, C, M, N, K, ldc, inter, k_splits, status, ra);
+    cb_launch_cluster(gemm_tcgen05_kernel<BN, STAGES, EPI, MH, NORM>, dim3(grid), dim3(192), smem, stream, k_splits,
+                      ma, mw, mc, ms, tma_out, C, M, N, K, ldc, inter, k_splits, status, ra, na);
     return cb_last_error();
+}
+
+// The forms that exist: rows ahead of their norm for the products that follow a norm (gate/up
+// with SwiGLU, q/k/v with the rotation), the next norm's input from the accumulating product
+// with tiles up to 128 columns.
+template <int BN, int STAGES, int EPI, int MH = 1>
+int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, int K, int ldc,
+           int inter, int k_splits, int* status, cudaStream_t stream, const RopeArgs& ra = RopeArgs{},
+           const NormArgs& na = NormArgs{}) {
+    if (na.gain != nullptr && na.sumsq_in != nullptr) return CB_ERR_UNSUPPORTED;
+    if (na.sumsq_in != nullptr) {
+        if constexpr (EPI == SWIGLU_BF16 || EPI == ROPE_APPEND)
+            return launch_norm<BN, STAGES, EPI, MH, NORM_PRE>(ma, mw, C, M, N, K, ldc, inter, k_splits, status, stream, ra, na);
+        return CB_ERR_UNSUPPORTED;
+    }
+    if (na.gain != nullptr) {
+        if constexpr (EPI == ACCUM_F32 && BN <= 128 && MH == 1)
+            return launch_norm<BN, STAGES, EPI, MH, NORM_EMIT>(ma, mw, C, M, N, K, ldc, inter, k_splits, status, stream, ra, na);
+        return CB_ERR_UNSUPPORTED;
+    }
+    return launch_norm<BN, STAGES, EPI, MH, NORM_NONE>(ma, mw, C, M, N, K, ldc, inter, k_splits, status, stream, ra, na);
 }
 
 template <int BN, int STAGES, int MH = 1>
 int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N,
-               int K, int ldc, int inter, int ks, int* status, cudaStream_t stream) {
+               int K, int ldc, int inter, int ks, int* status, cudaStream_t stream, const NormArgs& na) {
+    const RopeArgs none{};
     switch (epi) {
-        case STORE_BF16: return launch<BN, STAGES, STORE_BF16, MH>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream);
-        case STORE_F32: return launch<BN, STAGES, STORE_F32, MH>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream);
-        case ACCUM_F32: return launch<BN, STAGES, ACCUM_F32, MH>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream);
-        case SWIGLU_BF16: return launch<BN, STAGES, SWIGLU_BF16, MH>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream);
+        case STORE_BF16: return launch<BN, STAGES, STORE_BF16, MH>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream, none, na);
+        case STORE_F32: return launch<BN, STAGES, STORE_F32, MH>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream, none, na);
+        case ACCUM_F32: return launch<BN, STAGES, ACCUM_F32, MH>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream, none, na);
+        case SWIGLU_BF16: return launch<BN, STAGES, SWIGLU_BF16, MH>(ma, mw, C, M, N, K, ldc, inter, ks, status, stream, none, na);
     }
     return CB_ERR_UNSUPPORTED;
 }
@@ -716,10 +902,13 @@ int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, void* C, i
 // epilogue run beside the other's products (tile widths up to 128).
 // status: device int, stays 0 unless a wait ran out.
 // k_splits: 1, or the number of blocks (at most 8) that share a tile's K as a cluster.
+// norm: null, or what the product knows of the norm after or before it (NormArgs; a host
+// pointer, read during the call).
 CB_EXPORT int cb_gemm_tcgen05(const void* A, const void* W, void* C, int M, int N, int K, int lda,
                               int ldw, int ldc, int epi, int bn, int per_sm, int k_splits, int* status,
-                              void* stream) {
+                              void* stream, const void* norm) {
     if (M <= 0 || N <= 0) return 0;
+    const NormArgs na = norm ? *static_cast<const NormArgs*>(norm) : NormArgs{};
     if (K <= 0 || (K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15))
         return CB_ERR_UNSUPPORTED;
     const int w_rows = epi == SWIGLU_BF16 ? 2 * N : N;
@@ -731,24 +920,24 @@ CB_EXPORT int cb_gemm_tcgen05(const void* A, const void* W, void* C, int M, int 
     cudaStream_t s = (cudaStream_t)stream;
     const int inter = epi == SWIGLU_BF16 ? N : 0;
     if (per_sm == 0) {            // two accumulators: 256 x 256 of output per block
-        if (bn == 256) return launch_epi<256, 3, 2>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
+        if (bn == 256) return launch_epi<256, 3, 2>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s, na);
         return CB_ERR_UNSUPPORTED;
     }
     if (per_sm == 2) {
         switch (bn) {
-            case 64: return launch_epi<64, 3>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
-            case 96: return launch_epi<96, 3>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
-            case 128: return launch_epi<128, 3>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
+            case 64: return launch_epi<64, 3>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s, na);
+            case 96: return launch_epi<96, 3>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s, na);
+            case 128: return launch_epi<128, 3>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s, na);
         }
         return CB_ERR_UNSUPPORTED;
     }
     switch (bn) {
-        case 64: return launch_epi<64, 6>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
-        case 96: return launch_epi<96, 6>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
-        case 128: return launch_epi<128, 5>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
-        case 160: return launch_epi<160, 5>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
-        case 192: return launch_epi<192, 5>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
-        case 256: return launch_epi<256, 4>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s);
+        case 64: return launch_epi<64, 6>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s, na);
+        case 96: return launch_epi<96, 6>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s, na);
+        case 128: return launch_epi<128, 5>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s, na);
+        case 160: return launch_epi<160, 5>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s, na);
+        case 192: return launch_epi<192, 5>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s, na);
+        case 256: return launch_epi<256, 4>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s, na);
     }
     return CB_ERR_UNSUPPORTED;
 }
@@ -763,8 +952,9 @@ CB_EXPORT int cb_gemm_tcgen05_rope(const void* A, const void* W, void* q_out, in
                                    const int* block_table, int table_stride, void* k_cache,
                                    void* v_cache, int n_heads, int n_kv_heads, int head_dim,
                                    int page_tokens, int write_cache, int k_splits, int tall, int* status,
-                                   void* stream) {
+                                   void* stream, const void* norm) {
     if (M <= 0) return 0;
+    const NormArgs na = norm ? *static_cast<const NormArgs*>(norm) : NormArgs{};
     if (K <= 0 || (K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) ||
         head_dim <= 0 || (head_dim & 63) || bn % head_dim != 0 || (ldq & 7) || ((uintptr_t)q_out & 15) ||
         ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)cos_t & 15) ||
@@ -782,14 +972,14 @@ CB_EXPORT int cb_gemm_tcgen05_rope(const void* A, const void* W, void* q_out, in
     ra.page_tokens = page_tokens; ra.write_cache = write_cache;
     cudaStream_t s = (cudaStream_t)stream;
     if (tall) {           // two accumulators: 256 rows of output per block
-        if (bn == 256) return launch<256, 3, ROPE_APPEND, 2>(ma, mw, q_out, M, N, K, ldq, 0, 1, status, s, ra);
+        if (bn == 256) return launch<256, 3, ROPE_APPEND, 2>(ma, mw, q_out, M, N, K, ldq, 0, 1, status, s, ra, na);
         return CB_ERR_UNSUPPORTED;
     }
     switch (bn) {
-        case 64: return launch<64, 6, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, k_splits, status, s, ra);
-        case 128: return launch<128, 5, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, k_splits, status, s, ra);
-        case 192: return launch<192, 5, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, k_splits, status, s, ra);
-        case 256: return launch<256, 4, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, k_splits, status, s, ra);
+        case 64: return launch<64, 6, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, k_splits, status, s, ra, na);
+        case 128: return launch<128, 5, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, k_splits, status, s, ra, na);
+        case 192: return launch<192, 5, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, k_splits, status, s, ra, na);
+        case 256: return launch<256, 4, ROPE_APPEND>(ma, mw, q_out, M, N, K, ldq, 0, k_splits, status, s, ra, na);
     }
     return CB_ERR_UNSUPPORTED;
 }

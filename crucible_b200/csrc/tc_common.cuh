@@ -380,6 +380,35 @@ inline bool make_map_2d(CUtensorMap* out, const void* base, uint64_t rows, uint6
     return true;
 }
 
+// A bf16 matrix written in boxes of `box_cols` columns (at most 128 bytes) of `box_rows` rows
+// that lie unswizzled in shared memory, row after row.
+inline bool make_plain_box_map_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
+                                  uint64_t ld, uint32_t box_cols, uint32_t box_rows) {
+    typedef std::tuple<const void*, uint64_t, uint64_t, uint64_t, uint32_t, uint32_t> Key;
+    static std::map<Key, CUtensorMap> cache;
+    static std::mutex mu;
+    Key key(base, rows, cols, ld, box_cols, box_rows);
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return true;
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+    if (cache.size() > 8192) cache.clear();
+    cache[key] = *out;
+    return true;
+}
+
 // K or V pages [n_pages][n_kv_heads][page_tokens][head_dim] bf16 as a 4-D tensor, read in boxes
 // of 64 features of `box_pages` consecutive pages of one KV head (128-byte swizzle): a tile of keys whose pages
 // follow one another in the pool comes in with one copy instead of one per page.

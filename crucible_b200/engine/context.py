@@ -143,6 +143,37 @@ class StepContext:
     def scratch(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         return self._scratch.get(name, shape, dtype)
 
+    # -- a norm announced to the product that writes its rows last ------------
+    # An arrangement that knows which norm reads the residual rows next, through a consumer
+    # that can take rows not yet normalised, announces it before it runs the part in between.
+    # That part's last product into the rows (`ops.linear(..., accumulate=True, closes=ctx)`)
+    # may then leave the norm's input beside its sums and offer it; the norm takes the offer
+    # instead of running a kernel.  Nothing has to happen: an announcement that no product
+    # honours, or an offer that no norm takes, costs nothing and changes no result.
+    norm_after_layer = None      # set by the model before each layer: (norm, consumer) of the
+                                 # layer that runs next, or None
+
+    def announce_norm(self, norm, rows: Optional[torch.Tensor]) -> None:
+        self._announced = (norm, rows.data_ptr(), tuple(rows.shape)) if norm is not None else None
+        self._offer = None
+
+    def norm_ahead(self, rows: torch.Tensor):
+        a = getattr(self, "_announced", None)
+        if a is None or a[1] != rows.data_ptr() or a[2] != tuple(rows.shape):
+            return None
+        return a[0]
+
+    def offer_prenormed(self, rows: torch.Tensor, norm, scaled, sumsq, parts: int) -> None:
+        self._offer = (norm, rows.data_ptr(), tuple(rows.shape), scaled, sumsq, parts)
+        self._announced = None
+
+    def take_prenormed(self, rows: torch.Tensor, norm):
+        o, self._offer = getattr(self, "_offer", None), None
+        self._announced = None
+        if o is None or o[0] is not norm or o[1] != rows.data_ptr() or o[2] != tuple(rows.shape):
+            return None
+        return o[3], o[4], o[5]
+
 
 @dataclass
 class HostStep:

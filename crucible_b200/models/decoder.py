@@ -178,8 +178,14 @@ class DecoderModel:
     def forward(self, ctx) -> torch.Tensor:
         """Runs the step's tokens; returns fp32 logits [wanted rows, vocab]."""
         x = self.embedding.forward(ctx, ctx.token_ids)
-        for entry, binding in zip(self.config.run_order, self.bindings):
+        order = self.config.run_order
+        for i, (entry, binding) in enumerate(zip(order, self.bindings)):
+            # the norm that reads the rows after this layer, for the layer's last product
+            nxt = self.layers[order[i + 1].layer] if i + 1 < len(order) else None
+            entry_norm = getattr(nxt, "entry_norm", None)
+            ctx.norm_after_layer = entry_norm() if entry_norm is not None else None
             self.layers[entry.layer].forward(ctx, x, binding)
+        ctx.norm_after_layer = None
         if ctx.n_logit_rows == 0:
             return ctx.scratch("logits", (0, self.config.vocab_size), torch.float32)
         if ctx.host.all_single_token and ctx.n_logit_rows == ctx.n_tokens:

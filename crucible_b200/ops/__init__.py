@@ -186,20 +186,47 @@ def is_weight(t: torch.Tensor) -> bool:
     return at >= 0 and p < _weight_ends[at]
 
 
-def linear(a, w: torch.Tensor, out: torch.Tensor, *, accumulate: bool = False) -> None:
+def linear(a, w: torch.Tensor, out: torch.Tensor, *, accumulate: bool = False, closes=None) -> None:
     """`a` is a tensor or a `small_batch.LazyNorm` (rows not yet normalised).  `w`: if it was
     declared a weight (`declare_weights`) the bfloat16 kernels may fetch it early; any other
-    matrix, one computed during the step for instance, takes the CUDA-core product."""
+    matrix, one computed during the step for instance, takes the CUDA-core product.
+    `closes`: the step's context, given by a part whose last write to the rows `out` this
+    accumulating product is.  If the arrangement has announced the norm that reads those rows
+    next (`StepContext.announce_norm`), the product may leave that norm's input beside its
+    sums, and the norm then costs no kernel of its own."""
     from . import small_batch
     if w.dtype == torch.bfloat16 and is_weight(w):
         if a.shape[0] <= small_batch.PREFERRED_ROWS and small_batch.linear(a, w, out, accumulate=accumulate):
             return
         a = small_batch.as_tensor(a)
         from . import tensor_core
-        if tensor_core.linear(a, w, out, accumulate=accumulate):
+        emit = _norm_emit(closes, out, tensor_core) if accumulate and closes is not None else None
+        if tensor_core.linear(a, w, out, accumulate=accumulate, emit=emit):
+            if emit is not None and emit.parts:
+                closes.offer_prenormed(out, emit.norm, emit.scaled, emit.sumsq, emit.parts)
             return
     a = small_batch.as_tensor(a)
     linear_plain(a, w, out, accumulate=accumulate)
+
+
+def _norm_emit(ctx, rows: torch.Tensor, tensor_core):
+    """What the accumulate product into `rows` may leave for the norm announced for them."""
+    ahead = getattr(ctx, "norm_ahead", None)
+    norm = ahead(rows) if ahead is not None and tensor_core.NORM_AHEAD else None
+    if norm is None or rows.dtype != torch.float32 or not rows.is_contiguous():
+        return None
+    t, width = rows.shape
+    scaled = ctx.scratch("norm.ahead.scaled", (t, width), torch.bfloat16)
+    sumsq = ctx.scratch("norm.ahead.sumsq", (-(-width // 64), t), torch.float32)
+    emit = tensor_core.NormEmit(norm.gain, scaled, sumsq)
+    emit.norm = norm
+    return emit
+
+
+def _prenormed(h):
+    """`h` if it carries a norm input that a product before it left, else None."""
+    from . import small_batch
+    return h if isinstance(h, small_batch.LazyNorm) and h.scaled is not None else None
 
 
 def linear_swiglu(h, gate_up: torch.Tensor, out: torch.Tensor, ctx) -> None:
@@ -208,8 +235,11 @@ def linear_swiglu(h, gate_up: torch.Tensor, out: torch.Tensor, ctx) -> None:
     if gate_up.dtype == torch.bfloat16 and is_weight(gate_up):
         if h.shape[0] <= small_batch.PREFERRED_ROWS and small_batch.linear_swiglu(h, gate_up, out):
             return
-        h = small_batch.as_tensor(h)
         from . import tensor_core
+        pre = _prenormed(h)
+        if pre is not None and tensor_core.linear_swiglu(pre.scaled, gate_up, out, pre=pre):
+            return
+        h = small_batch.as_tensor(h)
         if tensor_core.linear_swiglu(h, gate_up, out):
             return
     h = small_batch.as_tensor(h)
@@ -236,6 +266,11 @@ def qkv_rope_append(h, wqkv: torch.Tensor, qkv: torch.Tensor, n_heads: int, n_kv
         return
     if wqkv.dtype == torch.bfloat16 and h.shape[0] > small_batch.PREFERRED_ROWS:
         from . import tensor_core
+        pre = _prenormed(h)
+        if pre is not None and tensor_core.linear_rope_append(pre.scaled, wqkv, qkv, n_heads, n_kv_heads,
+                                                              head_dim, cos, sin, rotary_dim, ctx, cache,
+                                                              binding, pre=pre):
+            return
         if tensor_core.linear_rope_append(small_batch.as_tensor(h), wqkv, qkv, n_heads, n_kv_heads,
                                           head_dim, cos, sin, rotary_dim, ctx, cache, binding):
             return

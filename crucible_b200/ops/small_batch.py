@@ -7,7 +7,10 @@ large to be worth it): the caller then runs the general kernels.
 `LazyNorm` is what a norm part hands to a mixer or feed-forward that can fuse
 the normalisation into its first matrix product: the fp32 rows, the gain and
 eps, not yet normalised.  `tensor()` runs the norm kernel (once) for consumers
-that need the normalised rows as a tensor.
+that need the normalised rows as a tensor.  For steps of many rows it may also
+carry what the product that wrote the rows last left for the norm (`scaled`,
+`sumsq`, `parts`: see `tensor_core.NormEmit`); a tensor-core product then takes
+`scaled` as its rows and applies each row's factor in its epilogue.
 """
 from __future__ import annotations
 
@@ -32,8 +35,11 @@ _UNSUPPORTED = 100001
 
 
 class LazyNorm:
-    def __init__(self, x: torch.Tensor, gain: torch.Tensor, eps: float, materialize):
+    def __init__(self, x: torch.Tensor, gain: torch.Tensor, eps: float, materialize,
+                 scaled: Optional[torch.Tensor] = None, sumsq: Optional[torch.Tensor] = None,
+                 parts: int = 0):
         self.x, self.gain, self.eps = x, gain, eps
+        self.scaled, self.sumsq, self.parts = scaled, sumsq, parts
         self._materialize = materialize
         self._tensor: Optional[torch.Tensor] = None
         self.shape = x.shape

@@ -167,26 +167,70 @@ def _tall_tiles(m: int, n_cols: int, k: int) -> bool:
     return blocks / (waves * N_SMS) >= TALL_MIN_FILL
 
 
-def _gemm(a, w, out, n, epi, bn, per_sm=1, splits=None) -> bool:
+NORM_AHEAD = True    # the accumulate products may leave the next norm's input (tests switch it off)
+NORM_AHEAD_MAX_TILE = 128   # widest tile whose epilogue holds a row's sums in registers
+
+
+class _NormArgs(ctypes.Structure):
+    """`NormArgs` of csrc/gemm_tcgen05.cu."""
+    _fields_ = [("gain", ctypes.c_void_p), ("scaled", ctypes.c_void_p), ("sumsq_out", ctypes.c_void_p),
+                ("ld_scaled", ctypes.c_int), ("sumsq_in", ctypes.c_void_p), ("parts", ctypes.c_int),
+                ("width", ctypes.c_float), ("eps", ctypes.c_float)]
+
+
+class NormEmit:
+    """What an accumulate product is asked to leave for the RMS norm that reads its output
+    rows next: `scaled` bf16 [rows, width] = bf16(x * gain), `sumsq` fp32 [parts, rows] = the
+    tiles' shares of every row's sum of squares.  `parts` is set by the product that did it
+    (None: it did not, the norm runs as a kernel of its own)."""
+
+    def __init__(self, gain: torch.Tensor, scaled: torch.Tensor, sumsq: torch.Tensor):
+        self.gain, self.scaled, self.sumsq = gain, scaled, sumsq
+        self.parts = None
+
+
+def _norm_args(emit, pre, rows: int):
+    """The pointer the product kernels take, and the object that keeps it alive."""
+    if emit is None and pre is None:
+        return _c_void_p(0), None
+    args = _NormArgs()
+    if emit is not None:
+        args.gain, args.scaled = emit.gain.data_ptr(), emit.scaled.data_ptr()
+        args.sumsq_out, args.ld_scaled = emit.sumsq.data_ptr(), emit.scaled.stride(0)
+    if pre is not None:
+        if pre.sumsq.stride(0) != rows or pre.sumsq.dtype != torch.float32:
+            raise RuntimeError("shares of the rows' sums of squares must be float32 [parts, rows]")
+        args.sumsq_in, args.parts = pre.sumsq.data_ptr(), pre.parts
+        args.width, args.eps = float(pre.x.shape[1]), float(pre.eps)
+    return ctypes.cast(ctypes.pointer(args), _c_void_p), args
+
+
+def _gemm(a, w, out, n, epi, bn, per_sm=1, splits=None, emit=None, pre=None) -> bool:
     lib = build.load("gemm_tcgen05")
     if per_sm == 0:
         # 256 x 256 tiles; an output that cannot leave by TMA is refused, and the 128-row tiles run
-        if _gemm(a, w, out, n, epi, 256, -1, 1):
+        if _gemm(a, w, out, n, epi, 256, -1, 1, None, pre):
             return True
         per_sm = 1
     if per_sm == -1:
         per_sm, splits = 0, 1
     if splits is None:
         splits = k_splits(a.shape[0], 2 * n if epi == SWIGLU_BF16 else n, a.shape[1], bn)
+    if emit is not None and (epi != ACCUM_F32 or bn > NORM_AHEAD_MAX_TILE or per_sm == 0 or n % 32
+                             or emit.sumsq.shape[0] < -(-n // bn) or emit.sumsq.stride(0) != a.shape[0]):
+        emit = None
+    norm_ptr, keep = _norm_args(emit, pre, a.shape[0])
     code = lib.cb_gemm_tcgen05(
         _c_void_p(a.data_ptr()), _c_void_p(w.data_ptr()), _c_void_p(out.data_ptr()),
         _c_int(a.shape[0]), _c_int(n), _c_int(a.shape[1]), _c_int(a.stride(0)),
         _c_int(w.stride(0)), _c_int(out.stride(0)), _c_int(epi), _c_int(bn), _c_int(per_sm),
-        _c_int(splits), _c_void_p(status_word(a.device).data_ptr()), _stream())
+        _c_int(splits), _c_void_p(status_word(a.device).data_ptr()), _stream(), norm_ptr)
     if code == _UNSUPPORTED:
         return False
     if code != 0:
         raise RuntimeError(f"tensor-core matrix product failed to launch (CUDA error {code})")
+    if emit is not None:
+        emit.parts = -(-n // bn)
     _count(1)
     return True
 
@@ -266,7 +310,10 @@ def _operands_ok(a, w) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def linear(a, w, out, *, accumulate=False, tile=None) -> bool:
+def linear(a, w, out, *, accumulate=False, tile=None, emit=None, pre=None) -> bool:
+    """`emit` (`NormEmit`): with accumulate, also leave the next norm's input if this product's
+    form can (`emit.parts` says whether it did).  `pre` (`small_batch.LazyNorm` with `scaled`):
+    `a` is that norm input, the rows' factors are applied in the epilogue."""
     if not _operands_ok(a, w) or out.stride(1) != 1:
         return False
     if out.dtype == torch.bfloat16:
@@ -281,30 +328,34 @@ def linear(a, w, out, *, accumulate=False, tile=None) -> bool:
     if tile is None and ((a.shape[0] <= SKINNY_ROWS and w_bytes >= SKINNY_MIN_BYTES)
                          or (a.shape[0] <= SKINNY_MID_ROWS and SKINNY_MIN_BYTES <= w_bytes <= SKINNY_MID_BYTES)
                          or (a.shape[0] <= 64 and w.shape[0] >= SKINNY_WIDE_N)):
+        if pre is not None:
+            return False
         return _gemm_skinny(a, w, out, w.shape[0], epi)
     if tile is None and _tall_tiles(a.shape[0], w.shape[0], a.shape[1]):
         tile = (256, 0)
     bn, per_sm, *splits = _tile_of(tile) if tile else _tile_width(a.shape[0], w.shape[0], epi)
-    return _gemm(a, w, out, w.shape[0], epi, bn, per_sm, splits[0] if splits else None)
+    return _gemm(a, w, out, w.shape[0], epi, bn, per_sm, splits[0] if splits else None, emit, pre)
 
 
-def linear_swiglu(h, gate_up, out, tile=None) -> bool:
+def linear_swiglu(h, gate_up, out, tile=None, pre=None) -> bool:
     if not _operands_ok(h, gate_up) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
         return False
     inter = gate_up.shape[0] // 2
     if tile is None and h.shape[0] <= SKINNY_ROWS and gate_up.numel() * 2 >= SKINNY_MIN_BYTES:
+        if pre is not None:
+            return False
         return _gemm_skinny(h, gate_up, out, inter, SWIGLU_BF16)
     if tile is None and _tall_tiles(h.shape[0], 2 * inter, h.shape[1]):
         tile = (256, 0)
     bn, per_sm, *splits = _tile_of(tile) if tile else _tile_width(h.shape[0], 2 * inter, SWIGLU_BF16)
-    return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn, per_sm, splits[0] if splits else None)
+    return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn, per_sm, splits[0] if splits else None, None, pre)
 
 
 ROPE_TALL = None     # tests may fix the form of the q/k/v product (True: 256 x 256 tiles)
 
 
 def linear_rope_append(h, wqkv, qkv, n_heads, n_kv_heads, head_dim, cos, sin, rotary_dim, ctx, cache,
-                       binding) -> bool:
+                       binding, pre=None) -> bool:
     """The q/k/v projection with the rotation and the cache write in the product's
     epilogue (whole head rotated, head size a multiple of 64).  Rotated q lands in the
     first columns of `qkv`; k and v only in the cache.  False: not taken."""
@@ -325,6 +376,7 @@ def linear_rope_append(h, wqkv, qkv, n_heads, n_kv_heads, head_dim, cos, sin, ro
     if bn % head_dim:
         return False
     lib = build.load("gemm_tcgen05")
+    norm_ptr, keep = _norm_args(None, pre, h.shape[0])
     code = lib.cb_gemm_tcgen05_rope(
         _c_void_p(h.data_ptr()), _c_void_p(wqkv.data_ptr()), _c_void_p(qkv.data_ptr()),
         _c_int(h.shape[0]), _c_int(h.shape[1]), _c_int(h.stride(0)), _c_int(wqkv.stride(0)),
@@ -334,7 +386,7 @@ def linear_rope_append(h, wqkv, qkv, n_heads, n_kv_heads, head_dim, cos, sin, ro
         _c_void_p(v_cache.data_ptr()), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
         _c_int(cache.page_tokens), _c_int(1 if binding.write else 0),
         _c_int(1 if tall else k_splits(h.shape[0], wqkv.shape[0], h.shape[1], bn)), _c_int(1 if tall else 0),
-        _c_void_p(status_word(h.device).data_ptr()), _stream())
+        _c_void_p(status_word(h.device).data_ptr()), _stream(), norm_ptr)
     if code == _UNSUPPORTED:
         return False
     if code != 0:

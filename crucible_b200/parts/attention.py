@@ -86,7 +86,7 @@ class PagedAttention(Mixer):
         out = ctx.scratch("attn.out", (t, self.q_width), self.dtype)
         ops.paged_attention(qkv, out, s.n_heads, s.n_kv_heads, s.head_dim, s.softmax_scale,
                             s.window, ctx, cache, binding)
-        ops.linear(out, self.wo, residual, accumulate=True)
+        ops.linear(out, self.wo, residual, accumulate=True, closes=ctx)
 
 
 MIXERS.register("attention", PagedAttention)

@@ -29,6 +29,7 @@ class RMSNorm(Norm):
         self.dtype = dtype
 
     supports_lazy = True
+    supports_ahead = True      # the product that writes the rows last may leave this norm's input
 
     def forward(self, ctx, x: torch.Tensor, lazy: bool = False):
         """`lazy`: the consumer can fuse the normalisation into its first matrix
@@ -38,6 +39,11 @@ class RMSNorm(Norm):
             out = ctx.scratch("norm.out", (x.shape[0], self.spec.width), self.dtype)
             ops.rmsnorm(x, self.gain, self.spec.eps, out)
             return out
+        take = getattr(ctx, "take_prenormed", None)
+        pre = take(x, self) if take is not None else None
+        if lazy and self.dtype == torch.bfloat16 and pre is not None:
+            scaled, sumsq, parts = pre
+            return small_batch.LazyNorm(x, self.gain, self.spec.eps, run, scaled, sumsq, parts)
         if lazy and self.dtype == torch.bfloat16 and x.shape[0] <= small_batch.MAX_LAZY_ROWS:
             return small_batch.LazyNorm(x, self.gain, self.spec.eps, run)
         return run()

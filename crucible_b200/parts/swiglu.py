@@ -38,7 +38,7 @@ class SwiGLU(FeedForward):
         t, i = h.shape[0], self.spec.intermediate
         act = ctx.scratch("ffn.act", (t, i), self.dtype)
         ops.linear_swiglu(h, self.gate_up, act, ctx)
-        ops.linear(act, self.down, residual, accumulate=True)
+        ops.linear(act, self.down, residual, accumulate=True, closes=ctx)
 
 
 FEED_FORWARDS.register("swiglu", SwiGLU)

@@ -336,13 +336,88 @@ def test_small_batch_large_weights_take_other_paths():
     assert small_batch.linear(lazy, huge, torch.empty(m, huge.shape[0], device=DEV)) is False
 
 
+def _rows_ahead_of_their_norm(rows, width, spread, eps, parts=3):
+    """(what the norm hands on, the product's bf16 rows, the normalised rows in float64) for
+    rows whose sums of squares lie in `parts` shares, as the product before them left them."""
+    from crucible_b200.ops import small_batch
+    x = torch.randn(rows, width, device=DEV) * spread
+    x *= torch.linspace(0.1, 4.0, rows, device=DEV).unsqueeze(1)          # rows of very different size
+    gain = 1.0 + 0.2 * torch.randn(width, device=DEV)
+    edges = [round(width * p / parts) for p in range(parts + 1)]
+    sumsq = torch.stack([x[:, a:b].pow(2).sum(1) for a, b in zip(edges[:-1], edges[1:])]).contiguous()
+    scaled = (x * gain).bfloat16()
+    normed = x.double() * torch.rsqrt(x.double().pow(2).mean(-1, keepdim=True) + eps) * gain.double()
+    return small_batch.LazyNorm(x, gain, eps, None, scaled, sumsq, parts), scaled, normed
+
+
+@pytest.mark.parametrize("m,n,k,tile", [(300, 768, 2048, 96), (40, 768, 768, 64), (64, 768, 2048, (64, 1, 4)),
+                                        (130, 96, 320, 128), (2048, 1024, 512, 128)])
+def test_accumulate_product_leaves_the_next_norms_input(m, n, k, tile):
+    """x += a W^T with bf16(x * gain) and the tiles' shares of every row's sum of squares
+    beside it; then a gate/up product that takes those rows and applies the rows' factors."""
+    from crucible_b200.ops import small_batch, tensor_core
+    torch.manual_seed(m + n)
+    a = torch.randn(m, k, device=DEV).bfloat16()
+    w = (torch.randn(n, k, device=DEV) * 0.1).bfloat16()
+    x0 = torch.randn(m, n, device=DEV) * torch.linspace(0.2, 5.0, m, device=DEV).unsqueeze(1)
+    gain = 1.0 + 0.2 * torch.randn(n, device=DEV)
+    x = x0.clone()
+    emit = tensor_core.NormEmit(gain, torch.zeros(m, n, device=DEV, dtype=torch.bfloat16),
+                                torch.zeros(-(-n // 64), m, device=DEV))
+    assert tensor_core.linear(a, w, x, accumulate=True, tile=tile, emit=emit)
+    tensor_core.check_status(DEV)
+    bn = tile if isinstance(tile, int) else tile[0]
+    assert emit.parts == -(-n // bn)
+    ref = x0.double() + a.double() @ w.double().T
+    assert rel(x, ref) < 2e-5
+    assert torch.equal(emit.scaled, (x * gain).bfloat16())                 # of the rows as written
+    shares = torch.stack([x[:, i * bn:(i + 1) * bn].double().pow(2).sum(1) for i in range(emit.parts)])
+    assert rel(emit.sumsq[:emit.parts], shares) < 1e-5
+    # without the request the product is the same to the bit
+    y = x0.clone()
+    assert tensor_core.linear(a, w, y, accumulate=True, tile=tile)
+    assert rel(y, x) < 1e-6
+    # the consumer: gate/up over these rows
+    eps, inter = 1e-5, 160
+    pre = small_batch.LazyNorm(x, gain, eps, None, emit.scaled, emit.sumsq, emit.parts)
+    w2 = (torch.randn(2 * inter, n, device=DEV) * 0.1).bfloat16()
+    for t2 in (64, 128, 256, (256, 0)):
+        act = torch.zeros(m, inter, device=DEV, dtype=torch.bfloat16)
+        assert tensor_core.linear_swiglu(emit.scaled, w2, act, tile=t2, pre=pre)
+        normed = ref * torch.rsqrt(ref.pow(2).mean(-1, keepdim=True) + eps) * gain.double()
+        z = normed @ w2.double().T
+        g, u = z[:, :inter], z[:, inter:]
+        assert rel(act, g / (1 + torch.exp(-g)) * u) < 6e-3, t2
+    # a plain product has no such form: refused, and the norm's own kernel runs for it
+    assert not tensor_core.linear(emit.scaled, w2, torch.zeros(m, 2 * inter, device=DEV), pre=pre)
+    tensor_core.check_status(DEV)
+
+
+def test_a_product_that_cannot_leave_the_norms_input_says_so():
+    from crucible_b200.ops import tensor_core
+    m, n, k = 200, 520, 256                     # 520 columns: the last chunk of 32 is not whole
+    a = torch.randn(m, k, device=DEV).bfloat16()
+    w = (torch.randn(n, k, device=DEV) * 0.1).bfloat16()
+    for n_cols, tile in ((520, 64), (512, 256)):
+        x = torch.zeros(m, n_cols, device=DEV)
+        emit = tensor_core.NormEmit(torch.ones(n_cols, device=DEV),
+                                    torch.zeros(m, n_cols, device=DEV, dtype=torch.bfloat16),
+                                    torch.zeros(16, m, device=DEV))
+        assert tensor_core.linear(a, w[:n_cols], x, accumulate=True, tile=tile, emit=emit)
+        assert emit.parts is None and float(emit.scaled.abs().sum()) == 0
+        assert rel(x, a.double() @ w[:n_cols].double().T) < 2e-5
+
+
 @pytest.mark.parametrize("hd,n_heads,n_kv,rows,d", [(64, 6, 2, 300, 256), (64, 5, 1, 40, 256),
                                                     (128, 3, 1, 150, 256), (64, 6, 2, 60, 1024)])
 @pytest.mark.parametrize("write", [True, False])
 @pytest.mark.parametrize("tall", [False, True])
-def test_linear_rope_append_tensor_core(hd, n_heads, n_kv, rows, d, write, tall):
+@pytest.mark.parametrize("ahead", [False, True])
+def test_linear_rope_append_tensor_core(hd, n_heads, n_kv, rows, d, write, tall, ahead):
     """The q/k/v product for many rows with rotation and cache write in its epilogue (the
-    last case: few tiles and a long K, so clusters share K); `tall`: 256 x 256 tiles."""
+    last case: few tiles and a long K, so clusters share K); `tall`: 256 x 256 tiles;
+    `ahead`: its rows are bf16(x * gain) of rows not yet divided by their root mean square,
+    with every row's sum of squares in three shares."""
     from crucible_b200.ops import tensor_core
     page = 16
     torch.manual_seed(rows)
@@ -363,6 +438,9 @@ def test_linear_rope_append_tensor_core(hd, n_heads, n_kv, rows, d, write, tall)
             tables[r, i] = ids.pop()
     tables = tables.to(DEV)
     h = torch.randn(rows, d, device=DEV).bfloat16()
+    pre, h_ref = None, h.double()
+    if ahead:
+        pre, h, h_ref = _rows_ahead_of_their_norm(rows, d, 3.0 + rows / 100, 1e-5)
     w = (torch.randn((n_heads + 2 * n_kv) * hd, d, device=DEV) * 0.2).bfloat16()
     i = torch.arange(hd // 2, dtype=torch.float64)
     ang = torch.outer(torch.arange(max(positions) + 1, dtype=torch.float64), 10000.0 ** (-2 * i / hd))
@@ -381,12 +459,12 @@ def test_linear_rope_append_tensor_core(hd, n_heads, n_kv, rows, d, write, tall)
     try:
         tensor_core.ROPE_TALL = tall
         assert tensor_core.linear_rope_append(h, w, qkv, n_heads, n_kv, hd, cos, sin, hd, ctx, Cache,
-                                              SimpleNamespace(group=0, slot=0, write=write))
+                                              SimpleNamespace(group=0, slot=0, write=write), pre=pre)
     finally:
         tensor_core.ROPE_TALL = None
     torch.cuda.synchronize()
     tensor_core.check_status(DEV)
-    y = (h.double() @ w.double().T).cpu().view(rows, n_heads + 2 * n_kv, hd)
+    y = (h_ref @ w.double().T).cpu().view(rows, n_heads + 2 * n_kv, hd)
     pos_t = torch.tensor(positions)
     c, s = ang[pos_t].cos()[:, None, :], ang[pos_t].sin()[:, None, :]
 

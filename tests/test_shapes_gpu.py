@@ -113,3 +113,44 @@ def test_the_benchmark_widths_against_the_plain_model(tmp_path, dtype):
     for i, pos in enumerate(places):
         err = helpers.relative_error(got[i], ref[i])
         assert err <= TOLERANCE[dtype], f"position {pos}: relative error {err:.3g}"
+
+
+def test_products_leave_the_next_norms_input_for_steps_of_many_rows(tmp_path):
+    """A step of more than 16 rows: the output and down projections leave the next norm's
+    input (all norms but a step's first and last then cost no launch), the q/k/v and gate/up
+    products apply the rows' factors; the logits follow the float32 engine as they do with
+    every norm a kernel of its own."""
+    from crucible_b200 import ops
+    from crucible_b200.engine import Engine, EngineOptions, StepEntry
+    from crucible_b200.ops import tensor_core
+    from crucible_b200.weights import write_random_model
+    import helpers
+    raw = _config("120m")
+    folder = write_random_model(raw, str(tmp_path / "model"), seed=5, std=0.05)
+    prompt = helpers.random_tokens(raw["vocab_size"], 333, 5)
+    short = helpers.random_tokens(raw["vocab_size"], 40, 6)
+    want = [0, 17, 332]
+
+    def run(dtype, ahead):
+        tensor_core.NORM_AHEAD = ahead
+        try:
+            eng = Engine(folder, EngineOptions(dtype=dtype, page_tokens=16, n_pages=120, max_requests=40))
+            before = ops.LAUNCHES[0]
+            rows = [eng.step([StepEntry("a", prompt, want)]).float().cpu()]
+            launches = ops.LAUNCHES[0] - before
+            # 24 decoded tokens of as many requests, twice (the second step replays its graph)
+            rows.append(eng.step([StepEntry(f"r{i}", short, [39]) for i in range(24)]).float().cpu())
+            for _ in range(2):
+                rows.append(eng.step([StepEntry(f"r{i}", [7 + i], [0]) for i in range(24)]).float().cpu())
+            tensor_core.check_status(eng.device)
+            assert not eng._graph_failed
+            return torch.cat(rows), launches
+        finally:
+            tensor_core.NORM_AHEAD = True
+    ref, _ = run("float32", True)
+    with_it, n_with = run("bfloat16", True)
+    without, n_without = run("bfloat16", False)
+    assert n_without - n_with == 2 * raw["n_layer"] - 1
+    for got in (with_it, without):
+        worst = float(((ref - got).abs().amax(1) / ref.abs().amax(1)).max())
+        assert worst < helpers.TOLERANCE["bfloat16"], worst
