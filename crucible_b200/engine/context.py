@@ -152,13 +152,15 @@ class StepContext:
     # honours, or an offer that no norm takes, costs nothing and changes no result.
     norm_after_layer = None      # set by the model before each layer: (norm, consumer) of the
                                  # layer that runs next, or None
+    _announced = None            # (norm, address and shape of the rows it will read)
+    _offer = None                # (norm, address and shape of the rows, scaled, sumsq, parts)
 
     def announce_norm(self, norm, rows: Optional[torch.Tensor]) -> None:
         self._announced = (norm, rows.data_ptr(), tuple(rows.shape)) if norm is not None else None
         self._offer = None
 
     def norm_ahead(self, rows: torch.Tensor):
-        a = getattr(self, "_announced", None)
+        a = self._announced
         if a is None or a[1] != rows.data_ptr() or a[2] != tuple(rows.shape):
             return None
         return a[0]
@@ -168,7 +170,7 @@ class StepContext:
         self._announced = None
 
     def take_prenormed(self, rows: torch.Tensor, norm):
-        o, self._offer = getattr(self, "_offer", None), None
+        o, self._offer = self._offer, None
         self._announced = None
         if o is None or o[0] is not norm or o[1] != rows.data_ptr() or o[2] != tuple(rows.shape):
             return None

@@ -218,9 +218,7 @@ def _norm_emit(ctx, rows: torch.Tensor, tensor_core):
     t, width = rows.shape
     scaled = ctx.scratch("norm.ahead.scaled", (t, width), torch.bfloat16)
     sumsq = ctx.scratch("norm.ahead.sumsq", (-(-width // 64), t), torch.float32)
-    emit = tensor_core.NormEmit(norm.gain, scaled, sumsq)
-    emit.norm = norm
-    return emit
+    return tensor_core.NormEmit(norm.gain, scaled, sumsq, norm)
 
 
 def _prenormed(h):

@@ -184,8 +184,9 @@ class NormEmit:
     tiles' shares of every row's sum of squares.  `parts` is set by the product that did it
     (None: it did not, the norm runs as a kernel of its own)."""
 
-    def __init__(self, gain: torch.Tensor, scaled: torch.Tensor, sumsq: torch.Tensor):
+    def __init__(self, gain: torch.Tensor, scaled: torch.Tensor, sumsq: torch.Tensor, norm=None):
         self.gain, self.scaled, self.sumsq = gain, scaled, sumsq
+        self.norm = norm              # the part the rows are left for (the caller's own reference)
         self.parts = None
 
 
