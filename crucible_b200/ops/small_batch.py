@@ -90,11 +90,12 @@ def _done(code: int, what: str) -> bool:
 
 # These kernels are built for latency (a few megabytes of weights per launch): 2.6-3.9 us
 # for the 120M shape's matrices at 8 rows, where the 128-row tiles need 5.4-8.0 us.  They
-# stream at 1.7 to 3.7 TB/s; the TMA-fed tensor-core kernel for few rows reaches 3.5 to
-# 5.5 TB/s but costs a norm kernel and a reduction over K more.  Measured on B200: up to 8
-# rows these kernels hold out to 64 MB (67 MB: 18.1 us with the norm inside against 18.5 us
-# and a norm kernel); with 9 to 16 rows to about 40 MB (50 MB: 24.2 against 17.7 us).
-MAX_WEIGHT_BYTES = 64 << 20
+# stream at 1.7 to 3.7 TB/s; the TMA-fed tensor-core kernel for few rows reaches 3.6 to
+# 5.6 TB/s but costs a norm kernel and a reduction over K more (and for the q/k/v product a
+# kernel for the rotation and the cache write).  Measured on B200 in replayed chains: at 34 MB
+# the two are level (8 rows: 11.2-12.1 us here, 10.8-12.1 there), at 50 MB these take 18.0 us
+# and that one 13.0, at 16 rows 24.2 against 13.9.
+MAX_WEIGHT_BYTES = 40 << 20
 MAX_WEIGHT_BYTES_TWO_GROUPS = 40 << 20
 # Every block of a product normalises the step's rows for itself.  That is free while the
 # blocks are few; with thousands of blocks it costs as much as the weights, and one norm
