@@ -315,6 +315,10 @@ def run_ours(args):
         in work.  Prompts enter one per step (the token budget), so the first request has
         decoded n_req - 1 tokens beside the others' prompts before the last one joins:
         that many tokens more are asked for."""
+        # untimed: the same batch for a few steps, so that every shape of step the timed run
+        # replays has been captured (a capture costs the host 4 ms, once per shape and
+        # metadata buffer)
+        llm.generate([prompt(ctx_len) for _ in range(n_req)], SamplingParams(max_tokens=n_req + max(3, args.warmup)))
         prompts = [prompt(ctx_len) for _ in range(n_req)]
         w0 = time.time()
         outs = llm.generate(prompts, SamplingParams(max_tokens=pure_steps + n_req))

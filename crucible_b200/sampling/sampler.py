@@ -48,6 +48,7 @@ class Sampler:
         self.vocab = vocab
         self._cap = 0
         self._at = 0
+        self._copies = None          # the stream the ids travel to the host on
 
     def _buffers(self, n: int):
         if n > self._cap:
@@ -59,7 +60,8 @@ class Sampler:
                                dev=torch.empty((4, cap), dtype=torch.float32, device=self.device),
                                ids=torch.zeros(cap + 1, dtype=torch.int32, device=self.device),
                                ids_host=torch.zeros(cap + 1, dtype=torch.int32, pin_memory=True),
-                               event=torch.cuda.Event(), used=False) for _ in range(self.RING)]
+                               event=torch.cuda.Event(), chosen=torch.cuda.Event(), used=False)
+                          for _ in range(self.RING)]
             self._cap = cap
         self._at = (self._at + 1) % self.RING
         slot = self._ring[self._at]
@@ -121,8 +123,15 @@ class Sampler:
         else:
             ops.sample_rows(logits, buf["dev"][0, :n], buf["dev"][1, :n].view(torch.int32),
                             buf["dev"][2, :n], max_k, ids, scatter_index, out, status=status)
-        buf["ids_host"][:n + 1].copy_(buf["ids"][:n + 1], non_blocking=True)
-        buf["event"].record()
+        # the ids' way to the host runs on a stream of its own, so that the next step's launches
+        # do not queue behind the copy
+        if self._copies is None:
+            self._copies = torch.cuda.Stream(device=self.device)
+        buf["chosen"].record()
+        self._copies.wait_event(buf["chosen"])
+        with torch.cuda.stream(self._copies):
+            buf["ids_host"][:n + 1].copy_(buf["ids"][:n + 1], non_blocking=True)
+            buf["event"].record(self._copies)
         buf["used"] = True
         pending = PendingIds(buf["ids_host"], n, buf["event"], self.device)
         return pending if defer else pending.get()
