@@ -250,6 +250,67 @@ argmax_slices_kernel(const float* __restrict__ logits, int vocab, float* __restr
     }
 }
 
+// Both stages in one launch: every block leaves its slice's winner and arrives at the row's
+// counter (an atomic; no block waits for another); the block that arrives last reduces the
+// row's slices, publishes the id and puts the counter back to zero for the next launch.
+// The winner is the one the two kernels find: the same values meet in the same comparison.
+__global__ void __launch_bounds__(256)
+argmax_fused_kernel(const float* __restrict__ logits, int vocab, float* __restrict__ part_val,
+                    int* __restrict__ part_idx, int* __restrict__ counters,
+                    int* __restrict__ out_ids, const int* __restrict__ scatter_index,
+                    int* __restrict__ scatter_out, const int* __restrict__ status_src,
+                    int* __restrict__ status_dst) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    __shared__ float s_val[32];
+    __shared__ int s_idx[32];
+    __shared__ int is_last;
+    const int row = blockIdx.y, slice = blockIdx.x;
+    const int per = (vocab + ARGMAX_SLICES - 1) / ARGMAX_SLICES;
+    const int lo = slice * per, hi = min(vocab, lo + per);
+    const float* r = logits + (size_t)row * vocab;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float x = r[i];
+        if (x > bv || (x == bv && i < bi)) { bv = x; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { s_val[warp] = bv; s_idx[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (s_val[w] > bv || (s_val[w] == bv && s_idx[w] < bi)) { bv = s_val[w]; bi = s_idx[w]; }
+        if (slice == 0 && r[0] != r[0]) { bv = INFINITY; bi = 0; }      // (as in argmax_slices_kernel)
+        part_val[row * ARGMAX_SLICES + slice] = bv;
+        part_idx[row * ARGMAX_SLICES + slice] = bi;
+        __threadfence();
+        is_last = atomicAdd(&counters[row], 1) == ARGMAX_SLICES - 1;
+    }
+    __syncthreads();
+    if (!is_last || warp != 0) return;
+    __threadfence();
+    bv = __ldcg(part_val + row * ARGMAX_SLICES + lane);
+    bi = __ldcg(part_idx + row * ARGMAX_SLICES + lane);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) {
+        publish(row, bi == 0x7fffffff ? 0 : bi, out_ids, scatter_index, scatter_out);
+        counters[row] = 0;
+        if (row == 0) relay_status(status_src, status_dst);
+    }
+}
+
 __global__ void argmax_final_kernel(const float* __restrict__ part_val,
                                     const int* __restrict__ part_idx, int* __restrict__ out_ids,
                                     const int* __restrict__ scatter_index,
@@ -275,11 +336,13 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_val,
 
 // scratch: n_rows * 32 floats followed by n_rows * 32 ints (cb_argmax_scratch_bytes),
 // or null: then one block per row does the whole row.
+// counters: null, or n_rows ints that are zero before the call and zero again after it:
+// both stages then run as one launch.
 // status_src, status_dst (both or neither): *status_dst = *status_src, by the launch
 // that writes the ids.
 CB_EXPORT int cb_argmax_rows(const float* logits, int n_rows, int vocab, int* out_ids,
                              void* scratch, const int* scatter_index, int* scatter_out,
-                             const int* status_src, int* status_dst, void* stream) {
+                             const int* status_src, int* status_dst, void* stream, int* counters) {
     if (n_rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (scratch == nullptr || vocab < 4096) {
@@ -289,6 +352,11 @@ CB_EXPORT int cb_argmax_rows(const float* logits, int n_rows, int vocab, int* ou
     }
     float* part_val = (float*)scratch;
     int* part_idx = (int*)(part_val + (size_t)n_rows * ARGMAX_SLICES);
+    if (counters != nullptr) {
+        cb_launch(argmax_fused_kernel, dim3(ARGMAX_SLICES, n_rows), dim3(256), 0, s, logits, vocab, part_val,
+                  part_idx, counters, out_ids, scatter_index, scatter_out, status_src, status_dst);
+        return cb_last_error();
+    }
     cb_launch(argmax_slices_kernel, dim3(ARGMAX_SLICES, n_rows), dim3(256), 0, s, logits, vocab, part_val,
                                                                      part_idx);
     cb_launch(argmax_final_kernel, dim3(n_rows), dim3(32), 0, s, (const float*)part_val,

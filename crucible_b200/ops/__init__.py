@@ -360,9 +360,15 @@ def argmax_rows(logits: torch.Tensor, out_ids: torch.Tensor,
     if scratch is None or scratch.numel() < n * 64:
         scratch = torch.empty(max(n, 64) * 64, dtype=torch.int32, device=logits.device)
         _scratch[key] = scratch
+    # the rows' arrival counters of the one-launch form: zero between launches (the kernel puts
+    # them back itself)
+    counters = _scratch.get(key + ("counters",))
+    if counters is None or counters.numel() < n:
+        counters = torch.zeros(max(n, 1024), dtype=torch.int32, device=logits.device)
+        _scratch[key + ("counters",)] = counters
     _check(lib.cb_argmax_rows(_ptr(logits), _c_int(n), _c_int(logits.shape[1]),
                               _ptr(out_ids), _ptr(scratch), _ptr(scatter_index), _ptr(scatter_out),
-                              *_status_pair(status), _stream()), "argmax_rows")
+                              *_status_pair(status), _stream(), _ptr(counters)), "argmax_rows")
 
 
 def max_device_top_k() -> int:
