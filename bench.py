@@ -151,6 +151,7 @@ def run_ours(args):
     from crucible_b200 import LLM, SamplingParams, ops
     from crucible_b200.config import parse_config, shape
     from crucible_b200.engine import StepEntry
+    from crucible_b200.engine.engine import DEVICE_TOKEN
     from crucible_b200.ops import tensor_core
     from crucible_b200.weights import write_random_model
 
@@ -216,15 +217,19 @@ def run_ours(args):
         ids = [f"d{i}" for i in range(b)]
         for rid in ids:
             engine.step([StepEntry(rid, prompt(ctx_len - 1), [])])
-        chosen = torch.zeros(b, dtype=torch.int32, device=dev)
-        entries = [StepEntry(rid, [0], [0]) for rid in ids]
+        # The decode step as generation runs it: the token a step chooses stays on the device
+        # as the request's next one (`Engine.sample_deferred`, an entry of DEVICE_TOKEN), its id
+        # travels to the host beside the next step and is read one step late.
+        greedy = [(SamplingParams(temperature=0.0), None)] * b
+        first = engine.step([StepEntry(rid, [rng.randrange(vocab)], [0]) for rid in ids])
+        in_flight = [engine.sample_deferred(first, greedy, ids)]
+        entries = [StepEntry(rid, [DEVICE_TOKEN], [0]) for rid in ids]
 
         def one():
-            logits = engine.step(entries, token_source=chosen)
-            ops.argmax_rows(logits, chosen)
-        # the first token of each request
-        chosen.copy_(torch.tensor([rng.randrange(vocab) for _ in range(b)], dtype=torch.int32))
-        for _ in range(warmup):
+            logits = engine.step(entries)
+            in_flight.append(engine.sample_deferred(logits, greedy, ids))
+            in_flight.pop(0).get()
+        for _ in range(warmup - 1):
             one()
         torch.cuda.synchronize()
         launches0 = ops.LAUNCHES[0]
