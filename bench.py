@@ -217,17 +217,15 @@ def run_ours(args):
         ids = [f"d{i}" for i in range(b)]
         for rid in ids:
             engine.step([StepEntry(rid, prompt(ctx_len - 1), [])])
-        # The decode step as generation runs it: the token a step chooses stays on the device
-        # as the request's next one (`Engine.sample_deferred`, an entry of DEVICE_TOKEN), its id
+        # The decode step as generation runs it: the step chooses its tokens itself
+        # (`Engine.step_choosing`: greedy, the argmax captured with the step), a chosen token
+        # stays on the device as the request's next one (an entry of DEVICE_TOKEN), and its id
         # travels to the host beside the next step and is read one step late.
-        greedy = [(SamplingParams(temperature=0.0), None)] * b
-        first = engine.step([StepEntry(rid, [rng.randrange(vocab)], [0]) for rid in ids])
-        in_flight = [engine.sample_deferred(first, greedy, ids)]
+        in_flight = [engine.step_choosing([StepEntry(rid, [rng.randrange(vocab)], [0]) for rid in ids])[1]]
         entries = [StepEntry(rid, [DEVICE_TOKEN], [0]) for rid in ids]
 
         def one():
-            logits = engine.step(entries)
-            in_flight.append(engine.sample_deferred(logits, greedy, ids))
+            in_flight.append(engine.step_choosing(entries)[1])
             in_flight.pop(0).get()
         for _ in range(warmup - 1):
             one()

@@ -64,6 +64,19 @@ class StepEntry:
     want: Sequence[int] = field(default_factory=tuple)   # places among `tokens`
 
 
+class _Choice:
+    """The greedy choice of a choosing step: the state slots of its rows, the device buffers
+    the argmax writes (ids with the status word behind them, the slots as the kernel reads
+    them) and, for a captured step, the event behind the last copy of the ids to the host."""
+
+    def __init__(self, slots_key):
+        self.slots_key = slots_key
+        self.ids = None
+        self.slots = None
+        self.copied = None
+        self.keeper = None      # the captured step's own choice, if this one borrowed its buffers
+
+
 class StepError(ValueError):
     pass
 
@@ -256,8 +269,20 @@ class Engine:
 
     # -- the step ---------------------------------------------------------------
 
+    def step_choosing(self, entries: Sequence[StepEntry]):
+        """A step whose every entry wants the logits of its last token and chooses its next
+        token greedily, the choice being part of the step: for a step that replays a captured
+        graph the argmax is a kernel of that graph, not two launches behind it.  The chosen
+        tokens stay on the device as the requests' latest (as `sample_deferred` leaves them).
+        Returns (logits, ids on their way to the host)."""
+        entries = list(entries)
+        for e in entries:
+            if list(e.want) != [len(e.tokens) - 1]:
+                raise StepError("step_choosing: every entry wants the logits of its last token, and no others")
+        return self.step(entries, _choose=True)
+
     def step(self, entries: Sequence[StepEntry],
-             token_source: Optional[torch.Tensor] = None) -> torch.Tensor:
+             token_source: Optional[torch.Tensor] = None, _choose: bool = False) -> torch.Tensor:
         """Runs one packed batch.  Returns fp32 logits [wanted, vocab] on the
         device; the tensor is scratch of the engine and is overwritten by the
         next step.  `token_source`, if given, is a device int32 tensor whose
@@ -299,20 +324,45 @@ class Engine:
                 self._forget(request)
                 cache.remove_request(request)
             raise
+        choice = None
+        if _choose:
+            slots = ints[2].tolist()
+            self._has_device_token.update(slots)
+            choice = _Choice(tuple(slots))
         try:
             if token_source is not None:
                 ctx.token_ids.copy_(token_source[:ctx.n_tokens])
+            logits = None
             if self.profiler is not None:
                 self.profiler.steps += 1
             elif self.options.graph and not self._graph_failed:
                 if ctx.host.all_single_token:
                     if self.model.graph_safe:
-                        return self._replay_or_capture(ctx, at_once=True)
+                        logits = self._replay_or_capture(ctx, at_once=True, choice=choice)
                 elif self.model.graph_safe_prompt_steps:
-                    return self._replay_or_capture(ctx, at_once=False)
-            return self.model.forward(ctx)
+                    logits = self._replay_or_capture(ctx, at_once=False, choice=choice)
+            if logits is None:
+                logits = self.model.forward(ctx)
+                if choice is not None:
+                    self._choose(logits, choice)
         finally:
             self._meta_read()
+        if choice is None:
+            return logits
+        return logits, self._get_sampler().collect(choice.ids, len(choice.slots_key), choice)
+
+    def _choose(self, logits: torch.Tensor, choice: "_Choice") -> None:
+        """The argmax of a choosing step, into the choice's own buffers (a captured step keeps
+        them: they are what its kernels write)."""
+        from .. import ops
+        from ..ops import tensor_core
+        n = len(choice.slots_key)
+        if choice.ids is None:
+            choice.ids = torch.zeros(n + 1, dtype=torch.int32, device=self.device)
+            choice.slots = torch.tensor(choice.slots_key, dtype=torch.int32, device=self.device)
+        # the kernel that writes the ids also leaves the status word right behind them
+        status = (tensor_core.status_word(self.device), choice.ids[n:n + 1])
+        ops.argmax_rows(logits, choice.ids[:n], choice.slots, self.device_tokens, status=status)
 
     # -- CUDA graphs ----------------------------------------------------------------
     #
@@ -328,7 +378,7 @@ class Engine:
 
     MAX_GRAPHS = 128         # two to a shape: one for each metadata buffer
 
-    def _replay_or_capture(self, ctx: StepContext, at_once: bool) -> torch.Tensor:
+    def _replay_or_capture(self, ctx: StepContext, at_once: bool, choice=None) -> torch.Tensor:
         from .. import ops
         from ..ops import tensor_core
         if self._failures_seen != tensor_core.FAILURES[0]:
@@ -341,16 +391,29 @@ class Engine:
             self._graph_generation = self.scratch.generation
         host = ctx.host
         shape = (ctx.n_tokens, ctx.n_requests, ctx.n_logit_rows) + host.shape_key()
-        key = shape + (self._meta_dev_at,)      # a graph's kernels read one of the two metadata buffers
+        # a graph's kernels read one of the two metadata buffers; a choosing step's graph also
+        # holds its argmax
+        key = shape + (self._meta_dev_at, choice is not None)
         hit = self._graphs.get(key)
         if hit is not None:
-            graph, logits, launches = hit
+            graph, logits, launches, kept = hit
+            if choice is not None:
+                # the graph writes the buffers of the choice it was captured with
+                if kept.slots_key != choice.slots_key:
+                    kept.slots.copy_(torch.tensor(choice.slots_key, dtype=torch.int32))
+                    kept.slots_key = choice.slots_key
+                if kept.copied is not None:
+                    # its ids of last time have to be on their way out before they are overwritten
+                    torch.cuda.current_stream(self.device).wait_event(kept.copied)
+                choice.ids, choice.slots, choice.keeper = kept.ids, kept.slots, kept
             graph.replay()
             ops.LAUNCHES[0] += launches
             self._graph_replays += 1
             self._prompt_graph_replays += 0 if at_once else 1
             return logits
         logits = self.model.forward(ctx)           # eager: also sizes the scratch buffers
+        if choice is not None:
+            self._choose(logits, choice)
         if self._graph_generation != self.scratch.generation:
             self._graphs.clear()
             self._graph_generation = self.scratch.generation
@@ -366,13 +429,15 @@ class Engine:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 captured = self.model.forward(ctx)
+                if choice is not None:
+                    self._choose(captured, choice)
             launches = ops.LAUNCHES[0] - before
             ops.LAUNCHES[0] = before
             if self._graph_generation != self.scratch.generation:
                 raise RuntimeError("scratch buffers moved during capture")
             while len(self._graphs) >= self.MAX_GRAPHS:
                 self._graphs.pop(next(iter(self._graphs)))
-            self._graphs[key] = (graph, captured, launches)
+            self._graphs[key] = (graph, captured, launches, choice)
         except Exception as e:                      # stay eager from here on
             self._graph_failed = True
             self._graph_error = repr(e)

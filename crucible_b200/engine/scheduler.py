@@ -186,7 +186,15 @@ class Scheduler:
         info.prefill_requests = len(plan)
         info.batch_tokens = info.decoded + info.prefill_tokens
         if entries:
-            logits = self.executor.step(entries)
+            # every entry chooses a token, greedily, and none can end on it: the choice is part
+            # of the step (an executor that has `step_choosing` captures it with the step)
+            choosing = (len(sample_rows) == len(entries) and hasattr(self.executor, "step_choosing")
+                        and all(live.request.params.is_greedy and live.request.params.eos_token_id is None
+                                for live, _ in sample_rows))
+            if choosing:
+                logits, chosen_ids = self.executor.step_choosing(entries)
+            else:
+                logits = self.executor.step(entries)
             rows = []
             for live, first in sample_rows:
                 if first and not live.request.params.is_greedy:
@@ -196,8 +204,8 @@ class Scheduler:
                      and all(p.eos_token_id is None for p, _ in rows))
             previous, self._in_flight = self._in_flight, None
             if defer:
-                ids = self.executor.sample_deferred(logits, rows,
-                                                    [live.request.id for live, _ in sample_rows])
+                ids = chosen_ids if choosing else self.executor.sample_deferred(
+                    logits, rows, [live.request.id for live, _ in sample_rows])
                 for live, first in sample_rows:
                     live.n_chosen += 1
                     live.next_token = None

@@ -69,6 +69,24 @@ class Sampler:
             slot["event"].synchronize()         # the copy that last read these buffers is done
         return slot
 
+    def collect(self, ids: torch.Tensor, n: int, choice=None) -> PendingIds:
+        """Ids that a step's own kernel has chosen (`ids`: n of them on the device, the status
+        word behind them): sends them to the host on the copies' stream.  `choice`: whose
+        buffers these are; it is told the event behind the copy, so that the step that writes
+        them next can wait for it."""
+        buf = self._buffers(n)
+        if self._copies is None:
+            self._copies = torch.cuda.Stream(device=self.device)
+        buf["chosen"].record()
+        self._copies.wait_event(buf["chosen"])
+        with torch.cuda.stream(self._copies):
+            buf["ids_host"][:n + 1].copy_(ids[:n + 1], non_blocking=True)
+            buf["event"].record(self._copies)
+        buf["used"] = True
+        if choice is not None:
+            (choice.keeper or choice).copied = buf["event"]
+        return PendingIds(buf["ids_host"], n, buf["event"], self.device)
+
     def sample(self, logits: torch.Tensor,
                rows: Sequence[Tuple[SamplingParams, Optional[Xorshift64Star]]],
                slots: Optional[Sequence[int]] = None,

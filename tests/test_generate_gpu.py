@@ -331,6 +331,54 @@ def test_device_token_needs_a_deferred_sample(tmp_path):
         eng.step([StepEntry("b", [DEVICE_TOKEN], [0])])
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_choosing_step_chooses_what_its_logits_say(tmp_path, dtype):
+    """`step_choosing`: the greedy choice is part of the step (captured with it once the
+    step replays a graph).  The ids are the argmax of the step's own logits, they are what
+    `DEVICE_TOKEN` feeds into the next step (an engine fed the same ids explicitly gives the
+    same logits), and a replayed step writes the slots of the requests it is run for, not of
+    those it was captured with."""
+    from crucible_b200.engine import DEVICE_TOKEN, Engine, EngineOptions, StepEntry, StepError
+    folder = helpers.make_folder(tmp_path, "tiny-b")
+    eng = Engine(folder, EngineOptions(dtype=dtype, n_pages=40, max_requests=4))
+    ref = Engine(folder, EngineOptions(dtype=dtype, n_pages=40, max_requests=4))
+    vocab = eng.config.vocab_size
+    prompts = {r: helpers.random_tokens(vocab, 9 + 4 * i, 20 + i) for i, r in enumerate("abc")}
+    with pytest.raises(StepError, match="last token"):
+        eng.step_choosing([StepEntry("a", prompts["a"], [0])])
+
+    def both(names, tokens_of):
+        logits, pending = eng.step_choosing([StepEntry(r, tokens_of[r], [len(tokens_of[r]) - 1]) for r in names])
+        ids = pending.get()
+        assert ids == logits.argmax(dim=-1).tolist()
+        return logits.clone(), ids
+
+    want = ref.step([StepEntry(r, prompts[r], [len(prompts[r]) - 1]) for r in "abc"]).clone()
+    logits, ids = both("abc", prompts)
+    assert torch.equal(logits, want)
+    fed = dict(zip("abc", ids))
+    for step in range(8):                                   # the later ones replay their graphs
+        want = ref.step([StepEntry(r, [fed[r]], [0]) for r in "abc"]).clone()
+        logits, ids = both("abc", {r: [DEVICE_TOKEN] for r in "abc"})
+        assert torch.equal(logits, want), step
+        fed = dict(zip("abc", ids))
+    assert eng._graphs and not eng._graph_failed, eng._graph_error
+    # another set of requests in other slots, the same shape of step
+    eng.finish("a")
+    prompts["d"] = helpers.random_tokens(vocab, 7, 31)
+    _, first = both("d", prompts)
+    names = "bdc"                                           # other slots in other rows than it was captured with
+    fed["d"] = first[0]
+    ref.finish("a")
+    ref.step([StepEntry("d", prompts["d"], [])])
+    for step in range(4):
+        want = ref.step([StepEntry(r, [fed[r]], [0]) for r in names]).clone()
+        logits, ids = both(names, {r: [DEVICE_TOKEN] for r in names})
+        assert torch.equal(logits, want), step
+        fed = dict(zip(names, ids))
+    eng.cache.check_invariants()
+
+
 def test_eos_and_cancel_through_the_engine(tmp_path):
     """`eos_token_id` ends a request at the token the plain model also chooses, and a
     request cancelled between steps gives back its pages while the others go on."""

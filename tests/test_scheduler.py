@@ -224,6 +224,49 @@ def test_token_values_may_lag_one_step_without_changing_the_result():
     assert [c.finish_reason for c in s.run_to_completion()] == ["eos"]
 
 
+class ChoosingExecutor(LaggedExecutor):
+    """An executor whose step can choose its tokens itself, like the engine's `step_choosing`."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.chosen_steps = 0
+
+    def step_choosing(self, entries):
+        assert all(list(e.want) == [len(e.tokens) - 1] for e in entries)
+        self.chosen_steps += 1
+        logits = self.step(entries)
+        rows = [(greedy(1), None)] * len(entries)
+        return logits, self.sample_deferred(logits, rows, [e.request for e in entries])
+
+
+def test_steps_whose_rows_are_all_greedy_choose_for_themselves():
+    """Every entry of the step chooses a token, greedily, and no request can end on a token's
+    value: the scheduler hands the choice to the step; a step with an unfinished portion, a
+    sampled row or an end-of-sequence token goes the usual way.  The tokens are the same."""
+    prompts = {"a": list(range(50)), "b": list(range(20)), "c": [7, 8, 9]}
+
+    def run(executor, sampled=False):
+        s = Scheduler(executor, SchedulerOptions(max_batch=4, prefill_token_budget=32))
+        for name, prompt in prompts.items():
+            params = greedy(5)
+            if sampled and name == "c":
+                params = SamplingParams(max_tokens=5, temperature=0.7, top_k=3, seed=1)
+            s.submit(Request(name, prompt, params))
+        return {c.id: c.tokens for c in s.run_to_completion()}, executor.steps
+
+    want, steps_sync = run(FakeExecutor(n_pages=64))
+    choosing = ChoosingExecutor(n_pages=64)
+    got, steps = run(choosing)
+    assert got == want
+    portions = sum(1 for step in steps if any(not w for _, _, w in step))      # steps with an unfinished portion
+    assert choosing.chosen_steps == len(steps) - portions > 0
+    # one sampled request: its steps are not handed over
+    mixed = ChoosingExecutor(n_pages=64)
+    got_mixed, steps_mixed = run(mixed, sampled=True)
+    assert got_mixed["a"] == want["a"] and got_mixed["b"] == want["b"]
+    assert 0 < mixed.chosen_steps < len(steps_mixed) - sum(1 for st in steps_mixed if any(not w for _, _, w in st))
+
+
 def test_an_executor_that_fails_mid_run_leaves_nothing_behind():
     """The executor raises in the middle of a run (the reference injects a device
     failure the same way, `engine/src/server.rs:1187-1227`): every live request's
