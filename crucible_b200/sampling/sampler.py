@@ -79,6 +79,7 @@ class Sampler:
             self._copies = torch.cuda.Stream(device=self.device)
         buf["chosen"].record()
         self._copies.wait_event(buf["chosen"])
+        ids.record_stream(self._copies)      # (an eager step's buffer may be freed before the copy runs)
         with torch.cuda.stream(self._copies):
             buf["ids_host"][:n + 1].copy_(ids[:n + 1], non_blocking=True)
             buf["event"].record(self._copies)
