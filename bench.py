@@ -150,8 +150,7 @@ def run_ours(args):
     import torch
     from crucible_b200 import LLM, SamplingParams, ops
     from crucible_b200.config import parse_config, shape
-    from crucible_b200.engine import StepEntry
-    from crucible_b200.engine.engine import DEVICE_TOKEN
+    from crucible_b200.engine import DEVICE_TOKEN, StepEntry
     from crucible_b200.ops import tensor_core
     from crucible_b200.weights import write_random_model
 
