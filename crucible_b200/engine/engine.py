@@ -272,7 +272,7 @@ class Engine:
     def step_choosing(self, entries: Sequence[StepEntry]):
         """A step whose every entry wants the logits of its last token and chooses its next
         token greedily, the choice being part of the step: for a step that replays a captured
-        graph the argmax is a kernel of that graph, not two launches behind it.  The chosen
+        graph the argmax is a kernel of that graph, not a launch behind it.  The chosen
         tokens stay on the device as the requests' latest (as `sample_deferred` leaves them).
         Returns (logits, ids on their way to the host)."""
         entries = list(entries)
